@@ -1,0 +1,779 @@
+"""Compiler from expression graphs to execution graphs, and the native-callable cache.
+
+Counterpart of the reference's ``cgt/compilation.py``: ``function`` (:8), the pipeline
+``run_compilation_pipeline`` (:312-367: simplify -> device placement -> transports -> shapes-first
+topological order -> memory owners -> execution graph -> interpreter) and ``nci2callable`` (:529-551,
+hash-keyed shared-library cache for Ops that carry C++/CUDA source).
+
+What is specific to this backend:
+  * placement follows the reference rule (scalars, arguments and shape arithmetic on the host,
+    everything with a native_gpu implementation on the GPU) but honours ``Op.host_inputs`` /
+    ``Op.meta_inputs`` so that launch-time operands are not shipped to the device and shape queries do
+    not ship tensors to the host;
+  * an update's right-hand side is ordered after every other reader of the variable it overwrites;
+  * instructions whose inputs are all compile-time constants are marked to fire once;
+  * the interpreter is the stream-issuing native one in ``libcgt_b200.so``; there is no Python or
+    CPU interpreter in this package.
+"""
+import ctypes
+import os
+import os.path as osp
+import pickle
+import string
+import subprocess
+import sys
+from collections import defaultdict
+from io import StringIO
+
+import numpy as np
+
+from . import core, utils
+
+cgt = core  # filled by attribute access through core.cgt at call time
+
+
+def _cgt():
+    return core.cgt
+
+
+def function(inputs, outputs, dbg=None, updates=None, givens=None):
+    """Compile `outputs` (a Node or list of Nodes) as a function of the Argument nodes `inputs`.
+    `updates` is a list of (shared variable, new value) pairs applied in place on every call."""
+    assert isinstance(inputs, list), "Inputs must be a list"
+    assert all(el.is_argument() for el in inputs), "Invalid input: should be a list of Argument nodes"
+    if isinstance(outputs, list):
+        assert all(isinstance(el, core.Node) for el in outputs), "Invalid output: should all be symbolic variables"
+        return _function_listout(inputs, outputs, dbg, updates, givens)
+    elif isinstance(outputs, core.Node):
+        f_listout = _function_listout(inputs, [outputs], dbg, updates, givens)
+        return _SingleOut(f_listout)
+    raise ValueError("Expected `outputs` to be a Node or a list of Nodes. Got an object of type %s" % type(outputs))
+
+
+class _SingleOut(object):
+    def __init__(self, f):
+        self.f = f
+
+    def __call__(self, *args):
+        return self.f(*args)[0]
+
+    def __getattr__(self, name):
+        return getattr(self.f, name)
+
+
+def _check_updates(updates):
+    if isinstance(updates, dict):
+        updates = list(updates.items())
+    if updates is None:
+        updates = []
+    assert isinstance(updates, list) and all(
+        isinstance(a, tuple) and len(a) == 2 and isinstance(a[0], core.Node) and isinstance(a[1], core.Node)
+        for a in updates), "updates should be a list of pairs (before, after)"
+    assert all(before.is_data() for (before, _) in updates), "lhs of updates must be Data instances"
+    return updates
+
+
+def _function_listout(inputs, outputs, dbg=None, updates=None, givens=None):
+    updates = _check_updates(updates)
+    if dbg:
+        raise core.Todo("debug functionality is broken")
+    outputs = [_cgt().make_tuple(*x) if isinstance(x, tuple) else x for x in outputs]
+    return run_compilation_pipeline(inputs, outputs, updates, givens or [])
+
+
+# ================================================================
+# Phase 1: simplification (shared with the test oracle's evaluator)
+# ================================================================
+
+def simplify_for_execution(outputs, updates, givens=()):
+    """Returns (outputs_simple, update_sources, update_targets_simple, analysis)."""
+    config = core.get_config()
+    outputs_updatetargs = list(outputs) + [after for (_before, after) in updates]
+    if givens:
+        outputs_updatetargs = core.clone(outputs_updatetargs, dict(givens))
+    if config["enable_simplification"]:
+        simple, _analysis, _ = core.simplify_and_analyze(outputs_updatetargs)
+    else:
+        simple = outputs_updatetargs
+    # fresh copy of the graph: later passes rewrite parent lists in place
+    simple = core.clone(simple)
+    analysis = core.init_analysis()
+    repl = {}
+    main_nodes = core.topsorted(simple)
+    for node in main_nodes:
+        core.do_analysis(node, analysis)
+        repl[node] = node
+    if config["enable_simplification"]:
+        # Shape expressions are simplified against the same analysis, so that with fixed input shapes
+        # every extent folds to a constant instead of being recomputed by host instructions on each run.
+        def simp(s):
+            core.update_simplify_map(s, analysis, repl)
+            return repl[s]
+        node2shape = analysis["node2shape"]
+        for node in main_nodes:
+            shp = node2shape[node]
+            if isinstance(shp, tuple):
+                node2shape[node] = tuple([simp(s) for s in arrshp] for arrshp in shp)
+            else:
+                node2shape[node] = [simp(s) for s in shp]
+    n = len(outputs)
+    return simple[:n], [before for (before, _) in updates], simple[n:], analysis
+
+
+# ================================================================
+# Phase 2: devices and transports
+# ================================================================
+
+def _meta_inputs(op, n):
+    f = getattr(op, "meta_inputs", None)
+    return tuple(f(n)) if f else ((0,) if isinstance(op, core.Size) else ())
+
+
+def determine_devices(nodes_sorted, updatetarg2src):
+    """Reference rule (cgt/compilation.py:45-80)."""
+    node2dev = {}
+    home_device = core.Device(devtype="cpu", idx=0)
+    for node in nodes_sorted:
+        default_device = node.props.get("default_device", home_device)
+        if node.is_scalar():
+            device = home_device
+        elif node in updatetarg2src:
+            device = node2dev[updatetarg2src[node]]
+            assert "native_" + device.devtype in node.op.available_impls, \
+                "update only works if final operation can be performed on target device"
+        elif node.is_data():
+            device = node.op.device
+        elif node.is_argument():
+            device = home_device
+        else:
+            impls = node.op.available_impls
+            if ("native_gpu" in impls) and ((default_device.devtype == "gpu") or ("native_cpu" not in impls)):
+                device = core.Device("gpu", default_device.idx)
+            else:
+                device = core.Device(devtype="cpu", idx=default_device.idx)
+        node2dev[node] = device
+    return node2dev
+
+
+def add_transports(nodelist, node2dev, node2shape):
+    """One Transport per (node, consumer device) pair (cgt/compilation.py:285-304); operands that an
+    Op reads on the host stay on the host, operands of which only the shape is used are not moved."""
+    node2child = defaultdict(list)
+    for node in nodelist:
+        for (pos, par) in enumerate(node.parents):
+            node2child[par].append((node, pos))
+    home = core.Device("cpu", 0)
+    for node in nodelist:
+        dev = node2dev[node]
+        dev2copy = {}
+        for (child, pos) in node2child[node]:
+            if child.is_input():
+                continue
+            n = len(child.parents)
+            if pos in _meta_inputs(child.op, n):
+                continue
+            want = home if pos in child.op.host_inputs(n) else node2dev[child]
+            if isinstance(child.op, core.Transport):
+                continue
+            if want.devtype != dev.devtype or (want.devtype == "gpu" and want.idx != dev.idx):
+                if want not in dev2copy:
+                    nodecopy = core.Result(core.Transport(want), [node])
+                    node2dev[nodecopy] = want
+                    dev2copy[want] = nodecopy
+                    node2shape[nodecopy] = node2shape[node]
+                child.parents[pos] = dev2copy[want]
+
+
+# ================================================================
+# Phase 3: ordering, memory owners, execution graph
+# ================================================================
+
+def is_tensor(x):
+    return isinstance(x.typ, core.TensorType)
+
+
+def is_tuple(x):
+    return isinstance(x.typ, core.TupleType)
+
+
+def _update_control_deps(outputs_all, updates):
+    """after -> nodes that must run before it: every other reader of the variable it overwrites."""
+    if not updates:
+        return {}
+    nodelist = core.topsorted(outputs_all)
+    children = defaultdict(list)
+    for node in nodelist:
+        for p in node.parents:
+            children[p].append(node)
+    extra = {}
+    for (before, after) in updates:
+        # descendants of `after` cannot be ordered before it
+        desc = set([after])
+        for node in nodelist:
+            if any(p in desc for p in node.parents):
+                desc.add(node)
+        readers = []
+        stack = list(children[before])
+        seen = set()
+        while stack:
+            c = stack.pop()
+            if c in seen or c in desc:
+                continue
+            seen.add(c)
+            readers.append(c)
+            # views of the variable alias its memory: their readers count too
+            if c.op.return_type == "byval":
+                stack.extend(children[c])
+        extra[after] = readers
+    return extra
+
+
+def topsorted_shapes_first(outputs, node2shape, extra_parents=None):
+    """Topological order in which the shape components of a byref node precede it
+    (cgt/compilation.py:109-148), plus the control dependencies in `extra_parents`."""
+    extra_parents = extra_parents or {}
+    marks = {}
+    out = []
+    stack = []
+    for x in outputs:
+        stack.append((x, 0))
+        while stack:
+            (i, jidx) = stack.pop()
+            if jidx == 0:
+                m = marks.get(i, 0)
+                if m == 0:
+                    marks[i] = 1
+                elif m == 1:
+                    raise ValueError("not a dag")
+                else:
+                    continue
+            ps = list(i.parents)
+            if i.ndim > 0 and not i.is_input() and i.op.return_type == "byref":
+                ps = ps + list(node2shape[i])
+            elif is_tuple(i) and not i.is_input():
+                for arrshp in node2shape[i]:
+                    ps = ps + list(arrshp)
+            ps = ps + extra_parents.get(i, [])
+            if jidx == len(ps):
+                marks[i] = 2
+                out.append(i)
+            else:
+                stack.append((i, jidx + 1))
+                stack.append((ps[jidx], 0))
+    return out
+
+
+def _same_shape(shp1, shp2):
+    if isinstance(shp1, tuple) or isinstance(shp2, tuple) or len(shp1) != len(shp2):
+        return False
+    for (a, b) in zip(shp1, shp2):
+        if a is b:
+            continue
+        if isinstance(a.op, core.Constant) and isinstance(b.op, core.Constant) and a.op.value == b.op.value:
+            continue
+        return False
+    return True
+
+
+def compute_const_nodes(nodes_sorted):
+    """Nodes whose value is the same on every run: constants and pure functions of constants."""
+    const = set()
+    for node in nodes_sorted:
+        if node.is_input():
+            continue
+        if isinstance(node.op, core.Constant):
+            const.add(node)
+        elif node.op.is_random_op:
+            continue
+        elif len(node.parents) > 0 and all(p in const for p in node.parents):
+            const.add(node)
+        elif isinstance(node.op, core.Fill) and len(node.parents) == 0:
+            const.add(node)
+    return const
+
+
+def determine_memowner(nodes_sorted, updates, node2dev, outputs, node2shape, const_nodes):
+    """Which node's memory each node writes into (cgt/compilation.py:150-189).
+
+    In-place reuse of a parent's buffer is limited to elementwise Ops (safe to run in place), to parents
+    with one consumer, equal shape and dtype, and never touches constants (they are computed once).
+    """
+    node2child = defaultdict(list)
+    for node in nodes_sorted:
+        for parent in node.parents:
+            node2child[parent].append(node)
+    node2memowner = {}
+    after2before = {after: before for (before, after) in updates}
+    enable_inplace_opt = core.get_config()["enable_inplace_opt"]
+    outputs = set(outputs)
+    for node in nodes_sorted:
+        base = node
+        if node.is_argument():
+            pass
+        elif node.op.writes_to_input >= 0:
+            base = node2memowner[node.parents[node.op.writes_to_input]]
+        elif node in after2before:
+            base = after2before[node]
+        elif enable_inplace_opt and node.op.return_type == "byref" and isinstance(node.op, (core.ElwiseUnary, core.ElwiseBinary)):
+            for parent in node.parents:
+                parentowner = node2memowner[parent]
+                if (len(node2child[parent]) == 1 and node.dtype == parent.dtype and is_tensor(parent)
+                        and node2dev[node] == node2dev[parent]
+                        and _is_data_mutable(parentowner) and parentowner is parent
+                        and parent not in outputs and parent not in const_nodes
+                        and _same_shape(node2shape[node], node2shape[parent])):
+                    base = parentowner
+                    break
+        node2memowner[node] = base
+    return node2memowner
+
+
+def _is_data_mutable(node):
+    return not node.is_input() and node.op.return_type == "byref"
+
+
+class MemCounter(object):
+    def __init__(self):
+        self.count = 0
+
+    def new_memloc(self, devtype):
+        out = MemLocation(self.count, devtype)
+        self.count += 1
+        return out
+
+
+def create_execution_graph(inputs, nodes_sorted, node2shape, node2memowner, node2dev, once_nodes=()):
+    """Instruction list (cgt/compilation.py:204-248): Argument -> LoadArgument; byref tensor ->
+    Alloc + ReturnByRef; byref tuple -> Alloc per component + BuildTup + ReturnByRef; byval ->
+    ReturnByVal; a node that writes into another node's memory re-uses that location."""
+    instrs = []
+    counter = MemCounter()
+    node2memloc = {}
+    for node in nodes_sorted:
+        if node not in node2dev:
+            node2dev[node] = core.Device("cpu", 0)
+        devtype = node2dev[node].devtype
+        if node.is_argument():
+            write_loc = counter.new_memloc(devtype)
+            instrs.append(LoadArgument(inputs.index(node), write_loc))
+        else:
+            read_locs = [node2memloc[parent] for parent in node.parents]
+            once = node in once_nodes
+            if node.op.return_type == "byref":
+                if node2memowner[node] is node:
+                    if is_tensor(node):
+                        nodeshape = node2shape[node] if node.ndim > 0 else []
+                        shape_locs = [node2memloc[shpel] for shpel in nodeshape]
+                        write_loc = counter.new_memloc(devtype)
+                        instrs.append(Alloc(node.dtype, shape_locs, write_loc))
+                    else:
+                        nodeshape = node2shape[node]
+                        assert isinstance(nodeshape, tuple)
+                        arr_locs = []
+                        for (arrshp, arrtyp) in utils.safezip(nodeshape, node.typ):
+                            arr_loc = counter.new_memloc(devtype)
+                            shape_locs = [node2memloc[shpel] for shpel in arrshp]
+                            instrs.append(Alloc(arrtyp.dtype, shape_locs, arr_loc))
+                            arr_locs.append(arr_loc)
+                        write_loc = counter.new_memloc(devtype)
+                        instrs.append(BuildTup(node.typ, arr_locs, write_loc))
+                else:
+                    assert node2dev[node] == node2dev[node2memowner[node]], \
+                        "a node that writes into another node's memory must live on the same device"
+                    write_loc = node2memloc[node2memowner[node]]
+                instrs.append(ReturnByRef(node.op, [par.typ for par in node.parents], read_locs, write_loc,
+                                          node_props=node.props, once=once))
+            else:
+                assert node.op.return_type == "byval"
+                write_loc = counter.new_memloc(devtype)
+                instrs.append(ReturnByVal(node.op, [par.typ for par in node.parents], read_locs, write_loc,
+                                          node_props=node.props, once=once))
+        node2memloc[node] = write_loc
+    return ExecutionGraph(instrs, len(inputs), counter.count), node2memloc
+
+
+def run_compilation_pipeline(inputs, outputs, updates, givens):
+    config = core.get_config()
+    outputs_simple, updatesrcs, updatetargs_simple, analysis = simplify_for_execution(outputs, updates, givens)
+    all_out = outputs_simple + updatetargs_simple
+    node2shape = analysis["node2shape"]
+
+    nodelist = core.topsorted(all_out)
+    node2dev = determine_devices(nodelist, dict(zip(updatetargs_simple, updatesrcs)))
+    add_transports(nodelist, node2dev, node2shape)
+
+    updates_simple = list(zip(updatesrcs, updatetargs_simple))
+    extra = _update_control_deps(all_out, updates_simple)
+    nodes_sorted = topsorted_shapes_first(all_out, node2shape, extra)
+    const_nodes = compute_const_nodes(nodes_sorted)
+    node2memowner = determine_memowner(nodes_sorted, updates_simple, node2dev, outputs_simple, node2shape, const_nodes)
+    written_into = set(owner for (n, owner) in node2memowner.items() if owner is not n)
+    once_nodes = set(n for n in const_nodes if n not in written_into)
+    eg, node2memloc = create_execution_graph(inputs, nodes_sorted, node2shape, node2memowner, node2dev, once_nodes)
+
+    if config["verbose"]:
+        sys.stderr.write("begin\n" + "\n".join("%i.) \t%r" % (i, instr) for (i, instr) in enumerate(eg.instrs)) + "\nend\n")
+    return create_interpreter(inputs, outputs_simple, eg, node2memloc)
+
+
+def create_interpreter(inputs, outputs, eg, node2memloc):
+    from . import runtime
+    config = core.get_config()
+    if config["backend"] != "native":
+        raise NotImplementedError("this package only has the native GPU interpreter (backend=native)")
+    input_types = [inp.typ for inp in inputs]
+    output_locs = [node2memloc[node] for node in outputs]
+    flags = 0
+    if config["use_cuda_graphs"]:
+        flags |= runtime.INTERP_CUDA_GRAPHS
+    if config["profile"] or profiler.on:
+        flags |= runtime.INTERP_PROFILE
+    interp = runtime.InterpreterWrapper(eg, input_types, output_locs, flags)
+    interp.eg = eg
+    if flags & runtime.INTERP_PROFILE:
+        profiler.register(interp)
+    return interp
+
+
+# ================================================================
+# numeric_eval: evaluate without building a function object
+# ================================================================
+
+def numeric_eval(output, arg2val):
+    """Evaluate `output` (Node or list) given values for its arguments. Compiles a throw-away function."""
+    single = isinstance(output, core.Node)
+    outs = [output] if single else list(output)
+    args = list(arg2val.keys())
+    f = function(args, outs)
+    vals = f(*[arg2val[a] for a in args])
+    return vals[0] if single else vals
+
+
+# ================================================================
+# Execution graph and instructions (cgt/compilation.py:425-517)
+# ================================================================
+
+class ExecutionGraph(object):
+    def __init__(self, instrs, n_args, n_locs):
+        self.instrs = instrs
+        self.n_args = n_args
+        self.n_locs = n_locs
+
+
+class MemLocation(object):
+    def __init__(self, idx, devtype):
+        assert isinstance(idx, int) and devtype in ["cpu", "gpu"]
+        self.index = idx
+        self.devtype = devtype
+
+    def __repr__(self):
+        return "%%%i/%s" % (self.index, self.devtype)
+
+
+class Instr(object):
+    pass
+
+
+class LoadArgument(Instr):
+    def __init__(self, ind, write_loc):
+        self.ind = ind
+        self.write_loc = write_loc
+
+    def __repr__(self):
+        return "%s = LoadArg ind:%i" % (self.write_loc, self.ind)
+
+
+class Alloc(Instr):
+    def __init__(self, dtype, read_locs, write_loc):
+        self.dtype = dtype
+        self.read_locs = read_locs
+        self.write_loc = write_loc
+
+    def __repr__(self):
+        return "%s = Alloc shp:%s dtype:%s" % (self.write_loc, str(self.read_locs), self.dtype)
+
+
+class BuildTup(Instr):
+    def __init__(self, typ, read_locs, write_loc):
+        self.typ = typ
+        self.read_locs = read_locs
+        self.write_loc = write_loc
+
+    def __repr__(self):
+        return "%s = BuildTup args:%s" % (self.write_loc, str(self.read_locs))
+
+
+class _Return(Instr):
+    kindname = "Return"
+
+    def __init__(self, op, input_types, read_locs, write_loc, node_props=None, once=False):
+        self.op = op
+        self.input_types = input_types
+        self.read_locs = read_locs
+        self.write_loc = write_loc
+        self.node_props = node_props
+        self.once = once
+        self._callable = None
+
+    def get_callable(self):
+        if self._callable is None:
+            self._callable = get_callable(self.op, self.input_types, self.write_loc.devtype)
+        return self._callable
+
+    def __repr__(self):
+        return "%s = %s op:%s args:%s" % (self.write_loc, self.kindname, str(self.op), str(self.read_locs))
+
+
+class ReturnByRef(_Return):
+    kindname = "ReturnByRef"
+
+
+class ReturnByVal(_Return):
+    kindname = "ReturnByVal"
+
+
+_QUICK_OPS = (core.Size, core.Reshape, core.MakeTuple, core.TupleIndex, core.GetData)
+
+
+def instr_flags(instr):
+    """Interpreter flags of a Return instruction (quick: host bookkeeping only, cf. cycgt.pyx:356-358)."""
+    from . import runtime
+    flags = 0
+    if isinstance(instr.op, _QUICK_OPS):
+        flags |= runtime.INSTR_QUICK
+    if isinstance(instr.op, core.Transport):
+        flags |= runtime.INSTR_TRANSPORT
+    if getattr(instr, "once", False):
+        flags |= runtime.INSTR_ONCE
+    return flags
+
+
+# ================================================================
+# Callables
+# ================================================================
+
+def get_callable(op, input_types, devtype, prefer_python=False):
+    """Native callable when the Op has one for `devtype`, else its Python function (run through a
+    host trampoline; only valid for host-resident values)."""
+    assert op.available_impls, "need to set op.available_impls"
+    config = core.get_config()
+    if (prefer_python or config["force_python_impl"]) and "python" in op.available_impls:
+        return op.get_py_callable(input_types)
+    if "native_" + devtype in op.available_impls or (devtype == "cpu" and "native_gpu" in op.available_impls and _prebuilt(op, input_types)):
+        return get_native_callable(op, input_types, devtype)
+    if "python" in op.available_impls:
+        if devtype == "gpu":
+            raise RuntimeError("Tried to put Op %s on the GPU but I only have a python impl :(" % op)
+        return op.get_py_callable(input_types)
+    raise RuntimeError("Can't find an implementation of %s for devtype %s. available_impls=%s" % (op, devtype, op.available_impls))
+
+
+def _prebuilt(op, input_types):
+    try:
+        return op.get_native_compile_info(input_types, "cpu").prebuilt is not None
+    except Exception:
+        return False
+
+
+def get_native_callable(op, input_types, devtype):
+    nci = op.get_native_compile_info(input_types, devtype)
+    nci.op_str = str(op)
+    nci.return_type = op.return_type
+    nci.n_in = len(input_types)
+    return nci2callable(nci)
+
+
+CPP_ABI_VERSION = 1  # bump when include/cgt_common.h changes layout, to invalidate cached libraries
+
+
+def nci2callable(nci):
+    from . import runtime
+    cldata = _build_closure(nci.closure_triples)
+    if nci.prebuilt is not None:
+        L = runtime.lib()
+        try:
+            fptr = getattr(L, nci.prebuilt)
+        except AttributeError:
+            raise runtime.BackendError("libcgt_b200.so does not export %s" % nci.prebuilt)
+        return core.NativeCallable(nci.n_in, nci.return_type, nci.op_str, fptr, cldata=cldata,
+                                   store_objects=nci.store_objects, flags=nci.flags)
+    template_code = gen_templated_code(nci.includes, nci.closure_triples, nci.func_code)
+    compile_info = get_compile_info()
+    prefix = utils.hash_seq1(template_code, compile_info["CPP_FLAGS"], str(CPP_ABI_VERSION), *(src.code for src in nci.extra_srcs))
+    d = dict(function=_funcname(prefix), closure=_closurename(prefix), setup=_setupname(prefix), teardown=_teardownname(prefix))
+    srcfiles = [core.SrcFile("c++", string.Template(template_code).substitute(d))]
+    srcfiles.extend(core.SrcFile(sf.lang, string.Template(sf.code).substitute(d)) for sf in nci.extra_srcs)
+    libpath = osp.join(compile_info["CACHE_ROOT"], prefix + ".so")
+    if not osp.exists(libpath):
+        TranslationUnit(srcfiles, nci.link_flags).compile(prefix, libpath)
+    lib = get_or_load_lib(libpath)
+    fptr = getattr(lib, _funcname(prefix))
+    setup_fptr = getattr(lib, _setupname(prefix)) if nci.setup else None
+    teardown_fptr = getattr(lib, _teardownname(prefix)) if nci.teardown else None
+    return core.NativeCallable(nci.n_in, nci.return_type, nci.op_str, fptr, cldata=cldata, setup_fptr=setup_fptr,
+                               teardown_fptr=teardown_fptr, store_objects=nci.store_objects, flags=nci.flags)
+
+
+def _funcname(prefix):
+    return "call_" + prefix
+
+
+def _setupname(prefix):
+    return "setup_" + prefix
+
+
+def _teardownname(prefix):
+    return "teardown_" + prefix
+
+
+def _closurename(prefix):
+    return "closure_" + prefix
+
+
+def gen_templated_code(includes, closure_info, func_code):
+    s = StringIO()
+    for fname in ["cgt_common.h"] + list(includes):
+        s.write('#include "%s"\n' % fname)
+    gen_struct_code(closure_info, s)
+    s.write(func_code)
+    return s.getvalue()
+
+
+def gen_struct_code(triples, outstream):
+    if triples is None:
+        return
+    outstream.write("typedef struct $closure {\n")
+    for (fieldname, fieldtype, _val) in triples:
+        outstream.write("%s %s;\n" % (_ctypes2str[fieldtype], fieldname))
+    outstream.write("} $closure;\n")
+
+
+_LIBRARIES = {}
+
+
+def get_or_load_lib(libname):
+    if libname not in _LIBRARIES:
+        _LIBRARIES[libname] = ctypes.cdll.LoadLibrary(libname)
+    return _LIBRARIES[libname]
+
+
+class TranslationUnit(object):
+    """Sources of one native Op: compiled with c++ (lang "c++") or nvcc for sm_100a (lang "cuda"),
+    linked against libcgt_b200.so into <cache>/<hash>.so."""
+
+    def __init__(self, srcfiles, link_flags):
+        self.srcfiles = srcfiles
+        self.link_flags = link_flags
+
+    def compile(self, prefix, libpath):
+        info = get_compile_info()
+        cache = info["CACHE_ROOT"]
+        objs = []
+        for (i, (lang, code)) in enumerate(self.srcfiles):
+            if lang == "c++":
+                srcpath = osp.join(cache, prefix + "_%i.cpp" % i)
+                cmd = "c++ %s %s -c -o %s.o %s" % (info["CPP_FLAGS"], srcpath, srcpath, info["INCLUDES"])
+            elif lang == "cuda":
+                srcpath = osp.join(cache, prefix + "_%i.cu" % i)
+                cmd = ("nvcc %s -c -o %s.o -gencode arch=compute_100a,code=sm_100a -lineinfo -O3 -std=c++17 "
+                       "-Xcompiler -fPIC %s" % (srcpath, srcpath, info["INCLUDES"]))
+            else:
+                raise NotImplementedError(lang)
+            with open(srcpath, "w") as fh:
+                fh.write(code)
+            _call(cmd)
+            objs.append(srcpath + ".o")
+        _call("c++ %s %s %s %s -o %s" % (info["CPP_FLAGS"], " ".join(objs), info["LINK_FLAGS"], self.link_flags, libpath))
+
+
+def _call(cmd):
+    if core.get_config()["verbose"]:
+        sys.stderr.write("\x1b[32m%s\x1b[0m\n" % cmd)
+    p = subprocess.run(cmd, shell=True, capture_output=True, text=True)
+    if p.returncode != 0:
+        raise RuntimeError("native compilation failed:\n%s\n%s" % (cmd, p.stdout + p.stderr))
+
+
+_COMPILE_CONFIG = None
+
+
+def get_compile_info():
+    global _COMPILE_CONFIG
+    if _COMPILE_CONFIG is None:
+        from . import runtime
+        config = core.get_config()
+        cache = osp.join(runtime.HERE, "_cache") if config["cache_dir"].startswith("~") else osp.expanduser(config["cache_dir"])
+        os.makedirs(cache, exist_ok=True)
+        includes = "-I%s -I/usr/local/cuda/include" % runtime.INCLUDE_DIR
+        link_flags = "-shared -rdynamic -L%s -l:libcgt_b200.so -Wl,-rpath,%s -L/usr/local/cuda/lib64 -lcudart" % (runtime.HERE, runtime.HERE)
+        cpp_flags = "-fvisibility=hidden -std=c++17 -fPIC" + (" -O0 -g" if config["debug_cpp"] else " -O3 -DNDEBUG")
+        _COMPILE_CONFIG = dict(CACHE_ROOT=cache, INCLUDES=includes, LINK_FLAGS=link_flags, CPP_FLAGS=cpp_flags,
+                               CGT_INCLUDE_DIR=runtime.INCLUDE_DIR, CGT_ENABLE_CUDA=True, CGT_ENABLE_CUDNN=False)
+    return _COMPILE_CONFIG
+
+
+_ctypes2str = {
+    ctypes.c_byte: "uint8_t", ctypes.c_bool: "bool", ctypes.c_char: "char", ctypes.c_int: "int",
+    ctypes.c_long: "long", ctypes.c_void_p: "void*", ctypes.c_double: "double", ctypes.c_float: "float",
+}
+
+_struct_cache = {}
+
+
+def _build_closure(triples):
+    if triples is None:
+        return ctypes.c_void_p(0)
+    fields = [(name, typ) for (name, typ, _val) in triples]
+    key = tuple((name, typ.__name__) for (name, typ) in fields)
+    S = _struct_cache.get(key)
+    if S is None:
+        S = type("closure", (ctypes.Structure,), {"_fields_": fields})
+        _struct_cache[key] = S
+    return S(*[val for (_n, _t, val) in triples])
+
+
+# ================================================================
+# Profiler: per-instruction CUDA-event timing in the native interpreter, aggregated per Op
+# (the reference's profiler only works with its Python interpreter, cgt/compilation.py:821-858)
+# ================================================================
+
+class _Profiler(object):
+    def __init__(self):
+        self.on = False
+        self.interps = []
+
+    def start(self):
+        self.on = True
+
+    def stop(self):
+        self.on = False
+
+    def register(self, interp):
+        self.interps.append(interp)
+
+    def clear_stats(self):
+        self.interps = []
+
+    def op_stats(self):
+        """{op string: (count, total ms)} over every profiled function"""
+        out = {}
+        for interp in self.interps:
+            for (instr, (r, ms, count)) in zip(interp.eg.instrs, interp.profile()):
+                if count == 0:
+                    continue
+                key = str(instr.op) if isinstance(instr, _Return) else type(instr).__name__
+                c0, t0 = out.get(key, (0, 0.0))
+                out[key] = (c0 + count, t0 + ms)
+        return out
+
+    def print_stats(self):
+        stats = self.op_stats()
+        total = sum(t for (_c, t) in stats.values()) or 1.0
+        rows = sorted(stats.items(), key=lambda kv: -kv[1][1])
+        sys.stdout.write("Total device time in profiled instructions: %.3f ms\n" % total)
+        sys.stdout.write("%-50s %8s %12s %8s\n" % ("Op", "Count", "Time (ms)", "Frac"))
+        for (k, (c, t)) in rows:
+            sys.stdout.write("%-50s %8d %12.4f %8.3f\n" % (k[:50], c, t, t / total))
+
+
+profiler = _Profiler()

@@ -1,0 +1,31 @@
+// Mul22 / BatchedMul22 entry points: choose between the tcgen05 tensor-core kernel (3xTF32 split
+// precision, gemm_tcgen05.cu) and the fp32 FMA kernel (gemm_simt.cu).
+#include "runtime.h"
+
+namespace cgtb {
+int sgemm_simt(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B,
+               long ldb, long strideB, float* C, long ldc, long strideC);
+// returns 0 done, 1 error, -1 shape not supported by the tensor-core kernel
+int sgemm_tc(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B,
+             long ldb, long strideB, float* C, long ldc, long strideC);
+
+int sgemm_dispatch(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B,
+                   long ldb, long strideB, float* C, long ldc, long strideC, int impl) {
+  if (!require_runtime("sgemm")) return 1;
+  if (impl != 1) {
+    int rc = sgemm_tc(tA, tB, P, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC);
+    if (rc >= 0) return rc;
+    if (impl == 2) return fail("sgemm: shape M=%ld N=%ld K=%ld is not supported by the tensor-core kernel", M, N, K);
+  }
+  return sgemm_simt(tA, tB, P, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC);
+}
+}  // namespace cgtb
+
+CGTB_API int cgtb_sgemm(int tA, int tB, long M, long N, long K, const float* A, long lda, const float* B, long ldb, float* C,
+                        long ldc, int impl) {
+  return cgtb::sgemm_dispatch(tA, tB, 1, M, N, K, A, lda, 0, B, ldb, 0, C, ldc, 0, impl);
+}
+CGTB_API int cgtb_sgemm_batched(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA,
+                                const float* B, long ldb, long strideB, float* C, long ldc, long strideC, int impl) {
+  return cgtb::sgemm_dispatch(tA, tB, P, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC, impl);
+}

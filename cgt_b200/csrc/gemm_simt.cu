@@ -1,0 +1,157 @@
+// fp32 / fp64 FMA GEMM for Mul22 and BatchedMul22 (cgt/core.py:2195-2206, 2272-2286).
+//
+// This is the general-shape path: any M, N, K, any leading dimensions, all four transpose
+// combinations, fp64 as well. The tensor-core path (gemm_tcgen05.cu) takes the fp32 shapes it
+// supports; cgtb_sgemm chooses between the two.
+//
+// 64x64 output tile per CTA, K step 16, 256 threads with a 4x4 register tile each. Skinny products
+// with a long K (weight gradients: M x N of a few thousand elements, K up to 131072) are split along
+// K across CTAs; partial tiles go to scratch memory and are folded in split order by a second kernel,
+// so the result does not depend on scheduling.
+#include "runtime.h"
+
+using namespace cgtb;
+
+namespace {
+
+constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
+
+// element (m,k) of op(A) is A[m*sam + k*sak]; element (k,n) of op(B) is B[k*sbk + n*sbn]
+template <typename T, bool A_KFAST, bool B_NFAST>
+__global__ void __launch_bounds__(256) gemm_simt_kernel(long M, long N, long K, const T* __restrict__ A, long sam, long sak,
+                                                        long strideA, const T* __restrict__ B, long sbk, long sbn,
+                                                        long strideB, T* __restrict__ C, long ldc, long strideC, int nsplit,
+                                                        long kchunk) {
+  __shared__ T As[BK][BM + 4];
+  __shared__ T Bs[BK][BN + 4];
+  const int batch = blockIdx.z / nsplit, split = blockIdx.z % nsplit;
+  A += batch * strideA;
+  B += batch * strideB;
+  // with split-K the output is the scratch slab [batch][split][M][N] (ldc == N there)
+  C += (nsplit > 1) ? ((long)batch * nsplit + split) * M * N : batch * strideC;
+  const long m0 = (long)blockIdx.y * BM, n0 = (long)blockIdx.x * BN;
+  const long k_begin = split * kchunk, k_end = min(K, k_begin + kchunk);
+  const int tid = threadIdx.x;
+  const int tx = tid % 16, ty = tid / 16;  // 16 x 16 threads, each 4 x 4 outputs
+  T acc[TM][TN];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < TN; ++j) acc[i][j] = T(0);
+
+  for (long k0 = k_begin; k0 < k_end; k0 += BK) {
+    // A tile: BM x BK = 1024 elements, 4 per thread
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      int idx = tid + e * 256;
+      int mm, kk;
+      if (A_KFAST) { kk = idx % BK; mm = idx / BK; } else { mm = idx % BM; kk = idx / BM; }
+      long m = m0 + mm, k = k0 + kk;
+      As[kk][mm] = (m < M && k < k_end) ? A[m * sam + k * sak] : T(0);
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      int idx = tid + e * 256;
+      int nn, kk;
+      if (B_NFAST) { nn = idx % BN; kk = idx / BN; } else { kk = idx % BK; nn = idx / BK; }
+      long n = n0 + nn, k = k0 + kk;
+      Bs[kk][nn] = (n < N && k < k_end) ? B[k * sbk + n * sbn] : T(0);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      T a[TM], b[TN];
+#pragma unroll
+      for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
+#pragma unroll
+      for (int j = 0; j < TN; ++j) b[j] = Bs[kk][tx * TN + j];
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = fma(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+  const long ld = (nsplit > 1) ? N : ldc;
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    long m = m0 + ty * TM + i;
+    if (m >= M) continue;
+#pragma unroll
+    for (int j = 0; j < TN; ++j) {
+      long n = n0 + tx * TN + j;
+      if (n < N) C[m * ld + n] = acc[i][j];
+    }
+  }
+}
+
+template <typename T>
+__global__ void splitk_fold_kernel(long P, long M, long N, int nsplit, const T* __restrict__ part, T* __restrict__ C,
+                                   long ldc, long strideC) {
+  long total = P * M * N;
+  for (long f = (long)blockIdx.x * blockDim.x + threadIdx.x; f < total; f += (long)gridDim.x * blockDim.x) {
+    long n = f % N, t = f / N;
+    long m = t % M, p = t / M;
+    const T* src = part + (p * nsplit) * M * N + m * N + n;
+    T acc = src[0];
+    for (int s = 1; s < nsplit; ++s) acc += src[(long)s * M * N];
+    C[p * strideC + m * ldc + n] = acc;
+  }
+}
+
+template <typename T>
+int gemm_simt(int tA, int tB, long P, long M, long N, long K, const T* A, long lda, long strideA, const T* B, long ldb,
+              long strideB, T* C, long ldc, long strideC) {
+  if (P <= 0 || M <= 0 || N <= 0) return 0;
+  long sam = tA ? 1 : lda, sak = tA ? lda : 1;
+  long sbk = tB ? 1 : ldb, sbn = tB ? ldb : 1;
+  long tiles = cgtb_ceil_div(M, BM) * cgtb_ceil_div(N, BN) * P;
+  int nsplit = 1;
+  long want = (long)rt().sm_count * 2;
+  if (tiles < want && K >= 1024) {
+    nsplit = (int)std::min<long>(cgtb_ceil_div(want, tiles), K / 256);
+    if (nsplit < 1) nsplit = 1;
+    if (nsplit > 512) nsplit = 512;
+  }
+  long kchunk = cgtb_ceil_div(cgtb_ceil_div(K, nsplit), BK) * BK;
+  nsplit = (int)cgtb_ceil_div(K > 0 ? K : 1, kchunk > 0 ? kchunk : 1);
+  if (K == 0) { nsplit = 1; kchunk = BK; }
+  if (P * nsplit > 65535) return fail("gemm: batch x split-K = %ld exceeds the grid limit", P * nsplit);
+  T* part = nullptr;
+  if (nsplit > 1) {
+    part = (T*)scratch((size_t)P * nsplit * M * N * sizeof(T));
+    if (!part) return 1;
+  }
+  dim3 grid((unsigned)cgtb_ceil_div(N, BN), (unsigned)cgtb_ceil_div(M, BM), (unsigned)(P * nsplit));
+  T* dst = nsplit > 1 ? part : C;
+#define GEMM_GO(AK, BNF)                                                                                              \
+  CGTB_LAUNCH((gemm_simt_kernel<T, AK, BNF>), grid, 256, 0, M, N, K, A, sam, sak, strideA, B, sbk, sbn, strideB, dst, ldc, \
+              strideC, nsplit, kchunk)
+  if (!tA && !tB) GEMM_GO(true, true);
+  else if (!tA && tB) GEMM_GO(true, false);
+  else if (tA && !tB) GEMM_GO(false, true);
+  else GEMM_GO(false, false);
+#undef GEMM_GO
+  if (nsplit > 1) {
+    long total = P * M * N;
+    long blocks = std::min<long>(cgtb_ceil_div(total, 256), (long)rt().sm_count * 8);
+    CGTB_LAUNCH(splitk_fold_kernel<T>, (unsigned)blocks, 256, 0, P, M, N, nsplit, part, C, ldc, strideC);
+  }
+  CGTB_CHECK_LAUNCH("gemm_simt");
+  return 0;
+}
+
+}  // namespace
+
+namespace cgtb {
+int sgemm_simt(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B,
+               long ldb, long strideB, float* C, long ldc, long strideC) {
+  return gemm_simt<float>(tA, tB, P, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC);
+}
+}  // namespace cgtb
+
+CGTB_API int cgtb_dgemm(int tA, int tB, long M, long N, long K, const double* A, long lda, const double* B, long ldb,
+                        double* C, long ldc) {
+  if (!require_runtime("cgtb_dgemm")) return 1;
+  return gemm_simt<double>(tA, tB, 1, M, N, K, A, lda, 0, B, ldb, 0, C, ldc, 0);
+}

@@ -1,0 +1,636 @@
+// Elementwise unary/binary, reductions and data-movement kernels for sm_100a.
+//
+// Elementwise kernels process 16 bytes of the widest operand per thread per step (128-bit loads and
+// stores where the type allows); the operator is a kernel argument that every thread of the launch
+// agrees on, so the switch costs one uniform branch. The scalar expressions are the reference's C
+// expressions (cgt/core.py:1119-1133, 1141-1151) evaluated with the same promotions: math functions
+// in the input type, sub-expressions with a double literal in double, result narrowed to the output type.
+#include "runtime.h"
+#include <cfloat>
+#include <limits>
+
+using namespace cgtb;
+
+// ------------------------------------------------------------------------------------------------
+// scalar expressions
+// ------------------------------------------------------------------------------------------------
+template <typename TI, typename TO>
+__device__ __forceinline__ TO unary_apply(int op, TI x) {
+  // integer inputs promote to double for the math functions, as C++ overload resolution does
+  typedef typename std::conditional<std::is_floating_point<TI>::value, TI, double>::type TM;
+  switch (op) {
+    case CGTB_U_ABS: return (TO)(fabs((TM)x));
+    case CGTB_U_CEIL: return (TO)(ceil((TM)x));
+    case CGTB_U_COS: return (TO)(cos((TM)x));
+    case CGTB_U_EXP: return (TO)(exp((TM)x));
+    case CGTB_U_ICEIL: return (TO)((int)ceil((TM)x));
+    case CGTB_U_IFLOOR: return (TO)((int)floor((TM)x));
+    case CGTB_U_LOG: return (TO)(log((TM)x));
+    case CGTB_U_NEG: return (TO)(-x);
+    case CGTB_U_SIGN: return (TO)(2 * (x > 0) - 1);
+    case CGTB_U_SIN: return (TO)(sin((TM)x));
+    case CGTB_U_SQUARE: return (TO)(x * x);
+    case CGTB_U_SQRT: return (TO)(sqrt((TM)x));
+    case CGTB_U_TANH: return (TO)(tanh((TM)x));
+    case CGTB_U_SIGMOID: return (TO)(1.0 / (1.0 + exp((TM)(-x))));
+    case CGTB_U_SOFTPLUS: return (TO)((x > 0) ? (x + log(exp((TM)(-x)) + 1)) : log(1 + exp((TM)x)));
+    case CGTB_U_CAST: return (TO)(x);
+  }
+  return TO(0);
+}
+
+template <typename TX, typename TY> struct pow_type { typedef double type; };
+template <> struct pow_type<float, float> { typedef float type; };
+
+template <typename TX, typename TY, typename TO>
+__device__ __forceinline__ TO binary_apply(int op, TX x, TY y) {
+  switch (op) {
+    case CGTB_B_MUL: return (TO)(x * y);
+    case CGTB_B_ADD: return (TO)(x + y);
+    case CGTB_B_SUB: return (TO)(x - y);
+    case CGTB_B_DIV: return (TO)((x + 0.0) / y);
+    case CGTB_B_LT: return (TO)(x < y);
+    case CGTB_B_GT: return (TO)(x > y);
+    case CGTB_B_LE: return (TO)(x <= y);
+    case CGTB_B_GE: return (TO)(x >= y);
+    case CGTB_B_POW: {
+      typedef typename pow_type<TX, TY>::type TP;
+      return (TO)(pow((TP)x, (TP)y));
+    }
+    case CGTB_B_EQ: return (TO)(x == y);
+    case CGTB_B_NE: return (TO)(x != y);
+  }
+  return TO(0);
+}
+
+// ------------------------------------------------------------------------------------------------
+// vector pack: N consecutive elements moved with the widest aligned access that fits
+// ------------------------------------------------------------------------------------------------
+template <typename T, int N>
+struct alignas(sizeof(T) * N <= 16 ? sizeof(T) * N : 16) Pack {
+  T v[N];
+};
+
+template <typename T, int N>
+__device__ __forceinline__ Pack<T, N> load_pack(const T* p) {
+  return *reinterpret_cast<const Pack<T, N>*>(p);
+}
+template <typename T, int N>
+__device__ __forceinline__ void store_pack(T* p, const Pack<T, N>& v) {
+  *reinterpret_cast<Pack<T, N>*>(p) = v;
+}
+
+constexpr int kVec = 4;
+
+template <typename TI, typename TO>
+__global__ void unary_kernel(int op, long n, const TI* __restrict__ in, TO* __restrict__ out, bool aligned) {
+  const long nvec = aligned ? n / kVec : 0;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
+    Pack<TI, kVec> a = load_pack<TI, kVec>(in + i * kVec);
+    Pack<TO, kVec> r;
+#pragma unroll
+    for (int k = 0; k < kVec; ++k) r.v[k] = unary_apply<TI, TO>(op, a.v[k]);
+    store_pack<TO, kVec>(out + i * kVec, r);
+  }
+  for (long i = nvec * kVec + (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x)
+    out[i] = unary_apply<TI, TO>(op, in[i]);
+}
+
+// SX / SY: operand is a 0-d array read at index 0
+template <typename TX, typename TY, typename TO, bool SX, bool SY>
+__global__ void binary_kernel(int op, long n, const TX* __restrict__ x, const TY* __restrict__ y, TO* __restrict__ out,
+                              bool aligned) {
+  const long nvec = aligned ? n / kVec : 0;
+  TX xs = SX ? x[0] : TX(0);
+  TY ys = SY ? y[0] : TY(0);
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
+    Pack<TX, kVec> a;
+    Pack<TY, kVec> b;
+    if (!SX) a = load_pack<TX, kVec>(x + i * kVec);
+    if (!SY) b = load_pack<TY, kVec>(y + i * kVec);
+    Pack<TO, kVec> r;
+#pragma unroll
+    for (int k = 0; k < kVec; ++k) r.v[k] = binary_apply<TX, TY, TO>(op, SX ? xs : a.v[k], SY ? ys : b.v[k]);
+    store_pack<TO, kVec>(out + i * kVec, r);
+  }
+  for (long i = nvec * kVec + (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x)
+    out[i] = binary_apply<TX, TY, TO>(op, SX ? xs : x[i], SY ? ys : y[i]);
+}
+
+static inline bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
+static inline unsigned elem_grid(long n) {
+  long blocks = cgtb_ceil_div(cgtb_ceil_div(n, kVec), 256);
+  long cap = (long)rt().sm_count * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (unsigned)blocks;
+}
+
+#define CGTB_FOR_DTYPE(code, T, ...)                           \
+  switch (code) {                                              \
+    case cgtb_i1: { typedef int8_t T; __VA_ARGS__; } break;    \
+    case cgtb_i4: { typedef int32_t T; __VA_ARGS__; } break;   \
+    case cgtb_i8: { typedef int64_t T; __VA_ARGS__; } break;   \
+    case cgtb_f4: { typedef float T; __VA_ARGS__; } break;     \
+    case cgtb_f8: { typedef double T; __VA_ARGS__; } break;    \
+    default: return fail("unsupported dtype code %d", (int)(code)); \
+  }
+
+template <typename TI, typename TO>
+static int unary_launch(int op, long n, const void* in, void* out) {
+  bool al = aligned16(in) && aligned16(out);
+  CGTB_LAUNCH((unary_kernel<TI, TO>), elem_grid(n), 256, 0, op, n, (const TI*)in, (TO*)out, al);
+  return 0;
+}
+
+CGTB_API int cgtb_unary(int op, int dt_in, int dt_out, long n, const void* in, void* out) {
+  if (!require_runtime("cgtb_unary")) return 1;
+  if (op < 0 || op >= CGTB_U_COUNT) return fail("cgtb_unary: bad opcode %d", op);
+  if (n <= 0) return 0;
+  CGTB_FOR_DTYPE(dt_in, TI, CGTB_FOR_DTYPE(dt_out, TO, { int rc = unary_launch<TI, TO>(op, n, in, out); if (rc) return rc; }));
+  CGTB_CHECK_LAUNCH("unary");
+  return 0;
+}
+
+template <typename TX, typename TY, typename TO>
+static int binary_launch(int op, long n, const void* x, const void* y, void* out, int sx, int sy) {
+  bool al = aligned16(out) && (sx || aligned16(x)) && (sy || aligned16(y));
+  unsigned g = elem_grid(n);
+  if (sx && sy) return fail("cgtb_binary: both operands scalar; scalar-scalar arithmetic stays on the host");
+  if (sx) CGTB_LAUNCH((binary_kernel<TX, TY, TO, true, false>), g, 256, 0, op, n, (const TX*)x, (const TY*)y, (TO*)out, al);
+  else if (sy) CGTB_LAUNCH((binary_kernel<TX, TY, TO, false, true>), g, 256, 0, op, n, (const TX*)x, (const TY*)y, (TO*)out, al);
+  else CGTB_LAUNCH((binary_kernel<TX, TY, TO, false, false>), g, 256, 0, op, n, (const TX*)x, (const TY*)y, (TO*)out, al);
+  return 0;
+}
+
+// Output dtypes the typing rules can produce for a pair of inputs (cgt/core.py:1309-1322): the
+// promoted type, the float type, or i1. Instantiating only these keeps the binary count small.
+template <typename TX, typename TY>
+static int binary_dispatch_out(int op, int dt_out, long n, const void* x, const void* y, void* out, int sx, int sy) {
+  switch (dt_out) {
+    case cgtb_i1: return binary_launch<TX, TY, int8_t>(op, n, x, y, out, sx, sy);
+    case cgtb_i4: return binary_launch<TX, TY, int32_t>(op, n, x, y, out, sx, sy);
+    case cgtb_i8: return binary_launch<TX, TY, int64_t>(op, n, x, y, out, sx, sy);
+    case cgtb_f4: return binary_launch<TX, TY, float>(op, n, x, y, out, sx, sy);
+    case cgtb_f8: return binary_launch<TX, TY, double>(op, n, x, y, out, sx, sy);
+  }
+  return fail("cgtb_binary: unsupported output dtype %d", dt_out);
+}
+
+CGTB_API int cgtb_binary(int op, int dt_x, int dt_y, int dt_out, long n, const void* x, const void* y, void* out,
+                         int scalar_x, int scalar_y) {
+  if (!require_runtime("cgtb_binary")) return 1;
+  if (op < 0 || op >= CGTB_B_COUNT) return fail("cgtb_binary: bad opcode %d", op);
+  if (n <= 0) return 0;
+  CGTB_FOR_DTYPE(dt_x, TX, CGTB_FOR_DTYPE(dt_y, TY, {
+    int rc = binary_dispatch_out<TX, TY>(op, dt_out, n, x, y, out, scalar_x, scalar_y);
+    if (rc) return rc;
+  }));
+  CGTB_CHECK_LAUNCH("binary");
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Reductions (cgt/core.py:1663-1738), keepdims. The reduced index space is split across
+// `nsplit` blocks per output element; each block folds its slice with a warp-shuffle tree and writes
+// one partial, and a second kernel folds the partials in a fixed order, so results are deterministic.
+// Adjacent axes with the same kept/reduced flag are merged on the host before launch.
+// ------------------------------------------------------------------------------------------------
+struct ReduceGeom {
+  int nk, nr;                 // number of kept / reduced merged axes
+  long kshape[CGTB_MAX_NDIM], kstride[CGTB_MAX_NDIM];
+  long rshape[CGTB_MAX_NDIM], rstride[CGTB_MAX_NDIM];
+};
+
+template <typename T>
+__device__ __forceinline__ T red_init(int kind) {
+  return kind == CGTB_R_SUM ? T(0) : -std::numeric_limits<T>::max();
+}
+template <> __device__ __forceinline__ float red_init<float>(int kind) { return kind == CGTB_R_SUM ? 0.f : -FLT_MAX; }
+template <> __device__ __forceinline__ double red_init<double>(int kind) { return kind == CGTB_R_SUM ? 0.0 : -DBL_MAX; }
+
+template <typename T>
+__device__ __forceinline__ T red_op(int kind, T a, T b) {
+  if (kind == CGTB_R_SUM) return a + b;
+  return (T)fmax((double)a, (double)b);
+}
+template <> __device__ __forceinline__ float red_op<float>(int kind, float a, float b) { return kind == CGTB_R_SUM ? a + b : fmaxf(a, b); }
+
+template <typename T>
+__device__ __forceinline__ T shfl_down_t(T v, int d) { return __shfl_down_sync(0xffffffffu, v, d); }
+template <> __device__ __forceinline__ int8_t shfl_down_t<int8_t>(int8_t v, int d) { return (int8_t)__shfl_down_sync(0xffffffffu, (int)v, d); }
+
+template <typename T>
+__global__ void reduce_kernel(int kind, ReduceGeom g, long rsize, long chunk, const T* __restrict__ in, T* __restrict__ out,
+                              int nsplit) {
+  long o = blockIdx.x;
+  int split = blockIdx.y;
+  long base = 0, rem = o;
+  for (int i = g.nk - 1; i >= 0; --i) {
+    long q = rem / g.kshape[i];
+    base += (rem - q * g.kshape[i]) * g.kstride[i];
+    rem = q;
+  }
+  long r0 = split * chunk, r1 = min(r0 + chunk, rsize);
+  T acc = red_init<T>(kind);
+  for (long r = r0 + threadIdx.x; r < r1; r += blockDim.x) {
+    long off = base, rr = r;
+    for (int i = g.nr - 1; i >= 0; --i) {
+      long q = rr / g.rshape[i];
+      off += (rr - q * g.rshape[i]) * g.rstride[i];
+      rr = q;
+    }
+    acc = red_op<T>(kind, acc, in[off]);
+  }
+  __shared__ T warp_part[32];
+  for (int d = 16; d > 0; d >>= 1) acc = red_op<T>(kind, acc, shfl_down_t<T>(acc, d));
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  if (lane == 0) warp_part[wid] = acc;
+  __syncthreads();
+  if (wid == 0) {
+    int nw = blockDim.x >> 5;
+    acc = lane < nw ? warp_part[lane] : red_init<T>(kind);
+    for (int d = 16; d > 0; d >>= 1) acc = red_op<T>(kind, acc, shfl_down_t<T>(acc, d));
+    if (lane == 0) out[o * nsplit + split] = acc;
+  }
+}
+
+template <typename T>
+__global__ void reduce_finish_kernel(int kind, long osize, int nsplit, const T* __restrict__ part, T* __restrict__ out) {
+  for (long o = (long)blockIdx.x * blockDim.x + threadIdx.x; o < osize; o += (long)gridDim.x * blockDim.x) {
+    T acc = red_init<T>(kind);
+    for (int s = 0; s < nsplit; ++s) acc = red_op<T>(kind, acc, part[o * nsplit + s]);
+    out[o] = acc;
+  }
+}
+
+template <typename T>
+static int reduce_launch(int kind, int ndim, const long* shape, const int* reduced, const T* in, T* out) {
+  ReduceGeom g;
+  g.nk = g.nr = 0;
+  long stride[CGTB_MAX_NDIM], acc = 1;
+  for (int i = ndim - 1; i >= 0; --i) { stride[i] = acc; acc *= shape[i]; }
+  if (acc == 0) return 0;
+  long osize = 1, rsize = 1;
+  // merge adjacent axes of the same class: axis i (outer) and i+1 (inner) merge when both are in the
+  // same class, since then stride[i] == shape[i+1]*stride[i+1]
+  for (int i = 0; i < ndim; ++i) {
+    if (shape[i] == 1) continue;
+    bool r = reduced[i] != 0;
+    int& n = r ? g.nr : g.nk;
+    long* sh = r ? g.rshape : g.kshape;
+    long* st = r ? g.rstride : g.kstride;
+    bool merged = false;
+    if (n > 0) {
+      // previous axis of this class is adjacent iff no axis of the other class with extent > 1 lies between
+      bool adjacent = true;
+      for (int j = i - 1; j >= 0; --j) {
+        if (shape[j] == 1) continue;
+        adjacent = ((reduced[j] != 0) == r);
+        break;
+      }
+      if (adjacent) { sh[n - 1] *= shape[i]; st[n - 1] = stride[i]; merged = true; }
+    }
+    if (!merged) { sh[n] = shape[i]; st[n] = stride[i]; n++; }
+    if (r) rsize *= shape[i]; else osize *= shape[i];
+  }
+  int threads = rsize >= 256 ? 256 : (rsize >= 64 ? 64 : 32);
+  // split long reductions so that the grid fills the machine
+  long want = (long)rt().sm_count * 4;
+  int nsplit = 1;
+  if (osize < want && rsize > 4096) {
+    nsplit = (int)std::min<long>(cgtb_ceil_div(want, osize), cgtb_ceil_div(rsize, 2048));
+    if (nsplit > 1024) nsplit = 1024;
+    if (nsplit < 1) nsplit = 1;
+  }
+  long chunk = cgtb_ceil_div(rsize, nsplit);
+  if (osize > 2147483647L) return fail("cgtb_reduce: too many output elements");
+  dim3 grid((unsigned)osize, (unsigned)nsplit);
+  if (nsplit == 1) {
+    CGTB_LAUNCH(reduce_kernel<T>, grid, threads, 0, kind, g, rsize, chunk, in, out, 1);
+  } else {
+    T* part = (T*)scratch((size_t)osize * nsplit * sizeof(T));
+    if (!part) return 1;
+    CGTB_LAUNCH(reduce_kernel<T>, grid, threads, 0, kind, g, rsize, chunk, in, part, nsplit);
+    CGTB_LAUNCH(reduce_finish_kernel<T>, (unsigned)cgtb_ceil_div(osize, 128), 128, 0, kind, osize, nsplit, part, out);
+  }
+  return 0;
+}
+
+CGTB_API int cgtb_reduce(int kind, int dtype, int ndim, const long* shape, const int* reduced, const void* in, void* out) {
+  if (!require_runtime("cgtb_reduce")) return 1;
+  if (ndim > CGTB_MAX_NDIM) return fail("cgtb_reduce: ndim %d too large", ndim);
+  CGTB_FOR_DTYPE(dtype, T, { int rc = reduce_launch<T>(kind, ndim, shape, reduced, (const T*)in, (T*)out); if (rc) return rc; });
+  CGTB_CHECK_LAUNCH("reduce");
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Data movement. Templated on the element size only (1, 2, 4, 8 bytes).
+// ------------------------------------------------------------------------------------------------
+template <int BYTES> struct bytes_type;
+template <> struct bytes_type<1> { typedef uint8_t type; };
+template <> struct bytes_type<2> { typedef uint16_t type; };
+template <> struct bytes_type<4> { typedef uint32_t type; };
+template <> struct bytes_type<8> { typedef uint64_t type; };
+
+static inline int dtype_bytes(int dtype) {
+  switch (dtype) {
+    case cgtb_i1: return 1;
+    case cgtb_i2: return 2;
+    case cgtb_i4: case cgtb_f4: return 4;
+    case cgtb_i8: case cgtb_f8: return 8;
+  }
+  return 0;
+}
+
+#define CGTB_FOR_BYTES(nbytes, U, ...)                                           \
+  switch (nbytes) {                                                              \
+    case 1: { typedef uint8_t U; __VA_ARGS__; } break;                           \
+    case 2: { typedef uint16_t U; __VA_ARGS__; } break;                          \
+    case 4: { typedef uint32_t U; __VA_ARGS__; } break;                          \
+    case 8: { typedef uint64_t U; __VA_ARGS__; } break;                          \
+    default: return fail("unsupported element size %d", (int)(nbytes));          \
+  }
+
+struct GatherGeom {
+  int nd;
+  long oshape[CGTB_MAX_NDIM];
+  long istride[CGTB_MAX_NDIM];  // input stride for each output axis (0 on repeated axes)
+};
+
+// out[flat] = in[sum_k idx_k * istride_k] : serves Repeat and the general Transpose
+template <typename U>
+__global__ void gather_kernel(GatherGeom g, long total, const U* __restrict__ in, U* __restrict__ out) {
+  for (long f = (long)blockIdx.x * blockDim.x + threadIdx.x; f < total; f += (long)gridDim.x * blockDim.x) {
+    long rem = f, off = 0;
+    for (int i = g.nd - 1; i >= 0; --i) {
+      long q = rem / g.oshape[i];
+      off += (rem - q * g.oshape[i]) * g.istride[i];
+      rem = q;
+    }
+    out[f] = in[off];
+  }
+}
+
+static inline unsigned flat_grid(long n, int per_thread = 1) {
+  long blocks = cgtb_ceil_div(cgtb_ceil_div(n, per_thread), 256);
+  long cap = (long)rt().sm_count * 32;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (unsigned)blocks;
+}
+
+CGTB_API int cgtb_repeat(int dtype, int ndim, const long* out_shape, const int* repeated, const void* in, void* out) {
+  if (!require_runtime("cgtb_repeat")) return 1;
+  if (ndim > CGTB_MAX_NDIM) return fail("cgtb_repeat: ndim %d too large", ndim);
+  GatherGeom g;
+  g.nd = 0;
+  long total = 1, acc = 1;
+  long istride[CGTB_MAX_NDIM];
+  for (int i = ndim - 1; i >= 0; --i) {
+    istride[i] = repeated[i] ? 0 : acc;
+    if (!repeated[i]) acc *= out_shape[i];
+    total *= out_shape[i];
+  }
+  if (total <= 0) return 0;
+  // merge adjacent axes: both repeated, or both kept (kept axes are contiguous in the input)
+  for (int i = 0; i < ndim; ++i) {
+    if (out_shape[i] == 1) continue;
+    if (g.nd > 0) {
+      bool prev_rep = g.istride[g.nd - 1] == 0, cur_rep = repeated[i] != 0;
+      if (prev_rep == cur_rep) {
+        g.oshape[g.nd - 1] *= out_shape[i];
+        g.istride[g.nd - 1] = istride[i];
+        continue;
+      }
+    }
+    g.oshape[g.nd] = out_shape[i];
+    g.istride[g.nd] = istride[i];
+    g.nd++;
+  }
+  CGTB_FOR_BYTES(dtype_bytes(dtype), U, CGTB_LAUNCH(gather_kernel<U>, flat_grid(total), 256, 0, g, total, (const U*)in, (U*)out));
+  CGTB_CHECK_LAUNCH("repeat");
+  return 0;
+}
+
+// batched 2-D transpose through a padded shared-memory tile: in [P, R, Cc] -> out [P, Cc, R]
+template <typename U>
+__global__ void transpose_tile_kernel(const U* __restrict__ in, U* __restrict__ out, long R, long Cc) {
+  __shared__ U tile[32][33];
+  long p = blockIdx.z;
+  const U* ip = in + p * R * Cc;
+  U* op = out + p * R * Cc;
+  long c0 = (long)blockIdx.x * 32, r0 = (long)blockIdx.y * 32;
+  for (int dy = threadIdx.y; dy < 32; dy += blockDim.y) {
+    long r = r0 + dy, c = c0 + threadIdx.x;
+    if (r < R && c < Cc) tile[dy][threadIdx.x] = ip[r * Cc + c];
+  }
+  __syncthreads();
+  for (int dy = threadIdx.y; dy < 32; dy += blockDim.y) {
+    long c = c0 + dy, r = r0 + threadIdx.x;
+    if (r < R && c < Cc) op[c * R + r] = tile[threadIdx.x][dy];
+  }
+}
+
+CGTB_API int cgtb_transpose(int dtype, int ndim, const long* in_shape, const int* axes, const void* in, void* out) {
+  if (!require_runtime("cgtb_transpose")) return 1;
+  if (ndim > CGTB_MAX_NDIM) return fail("cgtb_transpose: ndim %d too large", ndim);
+  long istride[CGTB_MAX_NDIM], acc = 1;
+  for (int i = ndim - 1; i >= 0; --i) { istride[i] = acc; acc *= in_shape[i]; }
+  long total = acc;
+  if (total <= 0) return 0;
+  // group output axes: consecutive output axes that are also consecutive input axes travel together
+  int gstart[CGTB_MAX_NDIM], glen[CGTB_MAX_NDIM], ng = 0;
+  for (int k = 0; k < ndim; ++k) {
+    if (in_shape[axes[k]] == 1) continue;
+    if (ng > 0) {
+      // last non-unit input axis of the previous group
+      int last = gstart[ng - 1] + glen[ng - 1] - 1;
+      bool contiguous = axes[k] > last;
+      for (int a = last + 1; a < axes[k] && contiguous; ++a) contiguous = in_shape[a] == 1;
+      if (contiguous) { glen[ng - 1] = axes[k] - gstart[ng - 1] + 1; continue; }
+    }
+    gstart[ng] = axes[k];
+    glen[ng] = 1;
+    ng++;
+  }
+  long gsize[CGTB_MAX_NDIM], gstride[CGTB_MAX_NDIM];
+  for (int q = 0; q < ng; ++q) {
+    gsize[q] = 1;
+    for (int a = gstart[q]; a < gstart[q] + glen[q]; ++a) gsize[q] *= in_shape[a];
+    gstride[q] = istride[gstart[q] + glen[q] - 1];
+  }
+  int nbytes = dtype_bytes(dtype);
+  if (ng <= 1) {  // no data reordering
+    CGTB_CUDA_TRY(cudaMemcpyAsync(out, in, (size_t)total * nbytes, cudaMemcpyDeviceToDevice, rt().stream));
+    return 0;
+  }
+  // fast path: [P, R, Cc] -> [P, Cc, R]
+  bool batched2d = false;
+  long P = 1, R = 0, Cc = 0;
+  if (ng == 2 && gstart[0] > gstart[1]) { R = gsize[1]; Cc = gsize[0]; batched2d = true; }
+  if (ng == 3 && gstart[0] < gstart[2] && gstart[2] < gstart[1] && gstride[0] == gsize[1] * gsize[2]) {
+    P = gsize[0]; R = gsize[2]; Cc = gsize[1]; batched2d = true;
+  }
+  if (batched2d && P <= 65535 && cgtb_ceil_div(R, 32) <= 65535) {
+    // output is [P, Cc, R] with input [P, R, Cc]
+    dim3 grid((unsigned)cgtb_ceil_div(Cc, 32), (unsigned)cgtb_ceil_div(R, 32), (unsigned)P), block(32, 8);
+    CGTB_FOR_BYTES(nbytes, U, CGTB_LAUNCH(transpose_tile_kernel<U>, grid, block, 0, (const U*)in, (U*)out, R, Cc));
+    CGTB_CHECK_LAUNCH("transpose");
+    return 0;
+  }
+  GatherGeom g;
+  g.nd = ng;
+  for (int q = 0; q < ng; ++q) { g.oshape[q] = gsize[q]; g.istride[q] = gstride[q]; }
+  CGTB_FOR_BYTES(nbytes, U, CGTB_LAUNCH(gather_kernel<U>, flat_grid(total), 256, 0, g, total, (const U*)in, (U*)out));
+  CGTB_CHECK_LAUNCH("transpose");
+  return 0;
+}
+
+// strided slice along one axis of a [outer, n, inner] view
+template <typename U>
+__global__ void getsli_kernel(long total, long n_in, long inner, long start, long step, long n_out, const U* __restrict__ in,
+                              U* __restrict__ out) {
+  for (long f = (long)blockIdx.x * blockDim.x + threadIdx.x; f < total; f += (long)gridDim.x * blockDim.x) {
+    long k = f % inner, t = f / inner;
+    long i = t % n_out, o = t / n_out;
+    out[f] = in[(o * n_in + start + step * i) * inner + k];
+  }
+}
+CGTB_API int cgtb_getsli(int dtype, long outer, long n_in, long inner, long start, long step, long n_out, const void* in,
+                         void* out) {
+  if (!require_runtime("cgtb_getsli")) return 1;
+  long total = outer * n_out * inner;
+  if (total <= 0) return 0;
+  long last = start + step * (n_out - 1);
+  if (start < 0 || start >= n_in || last < 0 || last >= n_in) return fail("cgtb_getsli: slice out of range");
+  CGTB_FOR_BYTES(dtype_bytes(dtype), U,
+                 CGTB_LAUNCH(getsli_kernel<U>, flat_grid(total), 256, 0, total, n_in, inner, start, step, n_out, (const U*)in, (U*)out));
+  CGTB_CHECK_LAUNCH("getsli");
+  return 0;
+}
+
+template <typename T>
+__global__ void incsli_kernel(long total, long n_x, long inner, long start, long step, long n_inc, const T* __restrict__ inc,
+                              T* __restrict__ out) {
+  for (long f = (long)blockIdx.x * blockDim.x + threadIdx.x; f < total; f += (long)gridDim.x * blockDim.x) {
+    long k = f % inner, t = f / inner;
+    long i = t % n_inc, o = t / n_inc;
+    out[(o * n_x + start + step * i) * inner + k] += inc[f];
+  }
+}
+CGTB_API int cgtb_incsli(int dtype, long outer, long n_x, long inner, long start, long step, long n_inc, const void* x,
+                         const void* inc, void* out) {
+  if (!require_runtime("cgtb_incsli")) return 1;
+  long xsize = outer * n_x * inner, total = outer * n_inc * inner;
+  if (xsize <= 0) return 0;
+  if (step == 0) return fail("cgtb_incsli: zero step");
+  long last = start + step * (n_inc - 1);
+  if (n_inc > 0 && (start < 0 || start >= n_x || last < 0 || last >= n_x)) return fail("cgtb_incsli: slice out of range");
+  if (out != x) CGTB_CUDA_TRY(cudaMemcpyAsync(out, x, (size_t)xsize * dtype_bytes(dtype), cudaMemcpyDeviceToDevice, rt().stream));
+  if (total <= 0) return 0;
+  CGTB_FOR_DTYPE(dtype, T, CGTB_LAUNCH(incsli_kernel<T>, flat_grid(total), 256, 0, total, n_x, inner, start, step, n_inc, (const T*)inc, (T*)out));
+  CGTB_CHECK_LAUNCH("incsli");
+  return 0;
+}
+
+template <typename U>
+__global__ void getflat_kernel(long n, long xsize_guard, const U* __restrict__ x, const int64_t* __restrict__ k, U* __restrict__ out) {
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) out[i] = x[k[i]];
+}
+CGTB_API int cgtb_getflat(int dtype, long n, const void* x, const int64_t* k, void* out) {
+  if (!require_runtime("cgtb_getflat")) return 1;
+  if (n <= 0) return 0;
+  CGTB_FOR_BYTES(dtype_bytes(dtype), U, CGTB_LAUNCH(getflat_kernel<U>, flat_grid(n), 256, 0, n, 0, (const U*)x, k, (U*)out));
+  CGTB_CHECK_LAUNCH("getflat");
+  return 0;
+}
+
+// IncFlatIndices (cgt/core.py:2012-2023): out.flat[k[i]] += p[i] in index order, so duplicate indices
+// accumulate in the reference's order. Thread i adds p[i] only after every earlier duplicate of k[i]
+// has been added: each thread first folds, in order, all j < i with k[j] == k[i] that nobody else owns.
+// Implemented as: the FIRST occurrence of each index owns the whole ordered sum for that index.
+template <typename T>
+__global__ void incflat_kernel(long n, const int64_t* __restrict__ k, const T* __restrict__ p, T* __restrict__ out) {
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    int64_t me = k[i];
+    bool first = true;
+    for (long j = 0; j < i; ++j)
+      if (k[j] == me) { first = false; break; }
+    if (!first) continue;
+    T acc = out[me];
+    for (long j = i; j < n; ++j)
+      if (k[j] == me) acc += p[j];
+    out[me] = acc;
+  }
+}
+// large index lists: atomics (integer results stay exact; float sums of duplicates may reorder)
+template <typename T>
+__global__ void incflat_atomic_kernel(long n, const int64_t* __restrict__ k, const T* __restrict__ p, T* __restrict__ out) {
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) atomicAdd(&out[k[i]], p[i]);
+}
+template <typename T> struct has_atomic { static const bool value = false; };
+template <> struct has_atomic<float> { static const bool value = true; };
+template <> struct has_atomic<double> { static const bool value = true; };
+template <> struct has_atomic<int32_t> { static const bool value = true; };
+
+template <typename T>
+static int incflat_launch(long n, const int64_t* k, const T* p, T* out) {
+  if (n <= 4096 || !has_atomic<T>::value) {
+    if (n > 65536) return fail("cgtb_incflat: %ld indices of a dtype without atomicAdd", n);
+    CGTB_LAUNCH(incflat_kernel<T>, flat_grid(n), 256, 0, n, k, p, out);
+  } else {
+    if constexpr (has_atomic<T>::value) CGTB_LAUNCH(incflat_atomic_kernel<T>, flat_grid(n), 256, 0, n, k, p, out);
+  }
+  return 0;
+}
+CGTB_API int cgtb_incflat(int dtype, long xsize, long n, const void* x, const int64_t* k, const void* p, void* out) {
+  if (!require_runtime("cgtb_incflat")) return 1;
+  if (xsize <= 0) return 0;
+  if (out != x) CGTB_CUDA_TRY(cudaMemcpyAsync(out, x, (size_t)xsize * dtype_bytes(dtype), cudaMemcpyDeviceToDevice, rt().stream));
+  if (n <= 0) return 0;
+  CGTB_FOR_DTYPE(dtype, T, { int rc = incflat_launch<T>(n, k, (const T*)p, (T*)out); if (rc) return rc; });
+  CGTB_CHECK_LAUNCH("incflat");
+  return 0;
+}
+
+template <typename U>
+__global__ void concat_part_kernel(long total, long n_in, long n_out, long inner, long pos, const U* __restrict__ in,
+                                   U* __restrict__ out) {
+  for (long f = (long)blockIdx.x * blockDim.x + threadIdx.x; f < total; f += (long)gridDim.x * blockDim.x) {
+    long k = f % inner, t = f / inner;
+    long i = t % n_in, o = t / n_in;
+    out[(o * n_out + pos + i) * inner + k] = in[f];
+  }
+}
+CGTB_API int cgtb_concat_part(int dtype, long outer, long n_in, long n_out, long inner, long pos, const void* in, void* out) {
+  if (!require_runtime("cgtb_concat_part")) return 1;
+  long total = outer * n_in * inner;
+  if (total <= 0) return 0;
+  if (pos < 0 || pos + n_in > n_out) return fail("cgtb_concat_part: part does not fit");
+  CGTB_FOR_BYTES(dtype_bytes(dtype), U,
+                 CGTB_LAUNCH(concat_part_kernel<U>, flat_grid(total), 256, 0, total, n_in, n_out, inner, pos, (const U*)in, (U*)out));
+  CGTB_CHECK_LAUNCH("concat");
+  return 0;
+}
+
+template <typename T>
+__global__ void fill_kernel(long n, T v, T* __restrict__ out) {
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) out[i] = v;
+}
+CGTB_API int cgtb_fill(int dtype, long n, double fvalue, long ivalue, void* out) {
+  if (!require_runtime("cgtb_fill")) return 1;
+  if (n <= 0) return 0;
+  switch (dtype) {
+    case cgtb_i1: CGTB_LAUNCH(fill_kernel<int8_t>, flat_grid(n), 256, 0, n, (int8_t)ivalue, (int8_t*)out); break;
+    case cgtb_i4: CGTB_LAUNCH(fill_kernel<int32_t>, flat_grid(n), 256, 0, n, (int32_t)ivalue, (int32_t*)out); break;
+    case cgtb_i8: CGTB_LAUNCH(fill_kernel<int64_t>, flat_grid(n), 256, 0, n, (int64_t)ivalue, (int64_t*)out); break;
+    case cgtb_f4: CGTB_LAUNCH(fill_kernel<float>, flat_grid(n), 256, 0, n, (float)fvalue, (float*)out); break;
+    case cgtb_f8: CGTB_LAUNCH(fill_kernel<double>, flat_grid(n), 256, 0, n, fvalue, (double*)out); break;
+    default: return fail("cgtb_fill: unsupported dtype %d", dtype);
+  }
+  CGTB_CHECK_LAUNCH("fill");
+  return 0;
+}

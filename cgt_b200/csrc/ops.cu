@@ -1,0 +1,391 @@
+// Built-in Op callables: the functions the interpreter reaches through ReturnByRef / ReturnByVal.
+//
+// Each has one of the reference's two callable signatures (include/cgt_common.h:176-177 of the
+// reference) and a closure struct whose fields are the Op's closure triples, in order, exactly as the
+// Python side lays them out with ctypes. Where the reference generates a C++ loop per Op instance
+// (cgt/core.py, cgt/nn_ops/*.py), these read the geometry from the arrays and the closure and launch
+// the CUDA kernels of this library. An array on the host is accepted only where the reference's
+// placement rule puts one: 0-d scalars and shape arithmetic (cgt/compilation.py:63-64); tensor
+// work on host arrays is refused rather than emulated.
+#include "runtime.h"
+#include <cmath>
+#include <cstring>
+#include <limits>
+#include <type_traits>
+
+using namespace cgtb;
+
+namespace cgtb {
+int sgemm_dispatch(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B,
+                   long ldb, long strideB, float* C, long ldc, long strideC, int impl);
+}
+
+#define OP_BYREF(name) CGTB_API void name(void* cl0, cgtObject** reads, cgtObject* write0)
+#define OP_BYVAL(name) CGTB_API cgtObject* name(void* cl0, cgtObject** reads)
+#define ARR(o) ((cgtArray*)(o))
+
+static const long kHostTensorLimit = 64;  // host arrays larger than this are tensor work, not scalar bookkeeping
+
+static bool on_gpu(cgtArray* a) { return a->devtype() == cgtGPU; }
+static bool all_gpu(std::initializer_list<cgtArray*> as) {
+  for (auto a : as) if (!on_gpu(a)) return false;
+  return true;
+}
+static bool host_scalar_ok(const char* op, std::initializer_list<cgtArray*> as) {
+  for (auto a : as) {
+    if (on_gpu(a)) { fail("%s: operands live on different devices (a Transport is missing)", op); return false; }
+    if (a->size() > kHostTensorLimit) {
+      fail("%s: a %ld-element tensor was placed on the host; this backend has no CPU implementation of tensor ops", op, a->size());
+      return false;
+    }
+  }
+  return true;
+}
+static long host_i8(cgtObject* o) { return ARR(o)->at<long>(0); }
+
+// ------------------------------------------------------------------------------------------------
+// host-side scalar expressions (same promotions as the device versions in kernels_elem.cu)
+// ------------------------------------------------------------------------------------------------
+template <typename TI, typename TO>
+static TO h_unary(int op, TI x) {
+  typedef typename std::conditional<std::is_floating_point<TI>::value, TI, double>::type TM;
+  switch (op) {
+    case CGTB_U_ABS: return (TO)(std::fabs((TM)x));
+    case CGTB_U_CEIL: return (TO)(std::ceil((TM)x));
+    case CGTB_U_COS: return (TO)(std::cos((TM)x));
+    case CGTB_U_EXP: return (TO)(std::exp((TM)x));
+    case CGTB_U_ICEIL: return (TO)((int)std::ceil((TM)x));
+    case CGTB_U_IFLOOR: return (TO)((int)std::floor((TM)x));
+    case CGTB_U_LOG: return (TO)(std::log((TM)x));
+    case CGTB_U_NEG: return (TO)(-x);
+    case CGTB_U_SIGN: return (TO)(2 * (x > 0) - 1);
+    case CGTB_U_SIN: return (TO)(std::sin((TM)x));
+    case CGTB_U_SQUARE: return (TO)(x * x);
+    case CGTB_U_SQRT: return (TO)(std::sqrt((TM)x));
+    case CGTB_U_TANH: return (TO)(std::tanh((TM)x));
+    case CGTB_U_SIGMOID: return (TO)(1.0 / (1.0 + std::exp((TM)(-x))));
+    case CGTB_U_SOFTPLUS: return (TO)((x > 0) ? (x + std::log(std::exp((TM)(-x)) + 1)) : std::log(1 + std::exp((TM)x)));
+    case CGTB_U_CAST: return (TO)(x);
+  }
+  return TO(0);
+}
+template <typename TX, typename TY, typename TO>
+static TO h_binary(int op, TX x, TY y) {
+  switch (op) {
+    case CGTB_B_MUL: return (TO)(x * y);
+    case CGTB_B_ADD: return (TO)(x + y);
+    case CGTB_B_SUB: return (TO)(x - y);
+    case CGTB_B_DIV: return (TO)((x + 0.0) / y);
+    case CGTB_B_LT: return (TO)(x < y);
+    case CGTB_B_GT: return (TO)(x > y);
+    case CGTB_B_LE: return (TO)(x <= y);
+    case CGTB_B_GE: return (TO)(x >= y);
+    case CGTB_B_POW: {
+      if (std::is_same<TX, float>::value && std::is_same<TY, float>::value) return (TO)(std::pow((float)x, (float)y));
+      return (TO)(std::pow((double)x, (double)y));
+    }
+    case CGTB_B_EQ: return (TO)(x == y);
+    case CGTB_B_NE: return (TO)(x != y);
+  }
+  return TO(0);
+}
+#define HOST_FOR_DTYPE(code, T, ...)                          \
+  switch (code) {                                             \
+    case cgt_i1: { typedef int8_t T; __VA_ARGS__; } break;    \
+    case cgt_i2: { typedef int16_t T; __VA_ARGS__; } break;   \
+    case cgt_i4: { typedef int32_t T; __VA_ARGS__; } break;   \
+    case cgt_i8: { typedef int64_t T; __VA_ARGS__; } break;   \
+    case cgt_f4: { typedef float T; __VA_ARGS__; } break;     \
+    case cgt_f8: { typedef double T; __VA_ARGS__; } break;    \
+    default: fail("unsupported dtype %d", (int)(code));       \
+  }
+
+// ------------------------------------------------------------------------------------------------
+// ElwiseUnary / ElwiseBinary (cgt/core.py:1160-1378)
+// ------------------------------------------------------------------------------------------------
+struct UnaryClosure { int op; };
+OP_BYREF(cgtb_op_elwise_unary) {
+  UnaryClosure* cl = (UnaryClosure*)cl0;
+  cgtArray *x = ARR(reads[0]), *w = ARR(write0);
+  if (w->size() != x->size()) { fail("ElwiseUnary: output has %ld elements, input %ld", w->size(), x->size()); return; }
+  if (all_gpu({x, w})) { cgtb_unary(cl->op, x->dtype(), w->dtype(), x->size(), x->data(), w->data()); return; }
+  if (!host_scalar_ok("ElwiseUnary", {x, w})) return;
+  long n = x->size();
+  HOST_FOR_DTYPE(x->dtype(), TI, HOST_FOR_DTYPE(w->dtype(), TO, {
+    for (long i = 0; i < n; ++i) w->at<TO>(i) = h_unary<TI, TO>(cl->op, x->at<TI>(i));
+  }));
+}
+
+struct BinaryClosure { int op; int scalar_x; int scalar_y; };
+OP_BYREF(cgtb_op_elwise_binary) {
+  BinaryClosure* cl = (BinaryClosure*)cl0;
+  cgtArray *x = ARR(reads[0]), *y = ARR(reads[1]), *w = ARR(write0);
+  long n = cl->scalar_x ? y->size() : x->size();
+  if (w->size() != n || (!cl->scalar_x && !cl->scalar_y && x->size() != y->size())) {
+    fail("Shape error in elementwise binary operation. You might be missing a call to cgt.broadcast(...)");
+    return;
+  }
+  if (all_gpu({x, y, w})) {
+    cgtb_binary(cl->op, x->dtype(), y->dtype(), w->dtype(), n, x->data(), y->data(), w->data(), cl->scalar_x, cl->scalar_y);
+    return;
+  }
+  if (!host_scalar_ok("ElwiseBinary", {x, y, w})) return;
+  HOST_FOR_DTYPE(x->dtype(), TX, HOST_FOR_DTYPE(y->dtype(), TY, HOST_FOR_DTYPE(w->dtype(), TO, {
+    for (long i = 0; i < n; ++i)
+      w->at<TO>(i) = h_binary<TX, TY, TO>(cl->op, x->at<TX>(cl->scalar_x ? 0 : i), y->at<TY>(cl->scalar_y ? 0 : i));
+  })));
+}
+
+// ------------------------------------------------------------------------------------------------
+// Mul22 / BatchedMul22 (cgt/core.py:2129-2288). Closure layout of the reference: tA, tB, handle.
+// ------------------------------------------------------------------------------------------------
+struct Mul22Closure { bool tA; bool tB; void* handle; };
+OP_BYREF(cgtb_op_mul22) {
+  Mul22Closure* cl = (Mul22Closure*)cl0;
+  cgtArray *A = ARR(reads[0]), *B = ARR(reads[1]), *C = ARR(write0);
+  if (!all_gpu({A, B, C})) { fail("Mul22: operands must be on the GPU; there is no CPU GEMM in this backend"); return; }
+  long lda = A->shape()[1], ldb = B->shape()[1], ldc = C->shape()[1];
+  long M = C->shape()[0], N = C->shape()[1], K = A->shape()[cl->tA ? 0 : 1];
+  long Kb = B->shape()[cl->tB ? 1 : 0], Ma = A->shape()[cl->tA ? 1 : 0], Nb = B->shape()[cl->tB ? 0 : 1];
+  if (K != Kb || M != Ma || N != Nb) { fail("shape mismatch at matrix-matrix multiplication: (%ld x %ld) * (%ld x %ld) -> (%ld x %ld)", Ma, K, Kb, Nb, M, N); return; }
+  if (A->dtype() == cgt_f4)
+    sgemm_dispatch(cl->tA, cl->tB, 1, M, N, K, (const float*)A->data(), lda, 0, (const float*)B->data(), ldb, 0, (float*)C->data(), ldc, 0, 0);
+  else if (A->dtype() == cgt_f8)
+    cgtb_dgemm(cl->tA, cl->tB, M, N, K, (const double*)A->data(), lda, (const double*)B->data(), ldb, (double*)C->data(), ldc);
+  else
+    fail("Mul22: unsupported dtype %d", (int)A->dtype());
+}
+struct BMul22Closure { bool tA; bool tB; };
+OP_BYREF(cgtb_op_batched_mul22) {
+  BMul22Closure* cl = (BMul22Closure*)cl0;
+  cgtArray *A = ARR(reads[0]), *B = ARR(reads[1]), *C = ARR(write0);
+  if (!all_gpu({A, B, C})) { fail("BatchedMul22: operands must be on the GPU"); return; }
+  if (A->dtype() != cgt_f4) { fail("BatchedMul22: only float32 is implemented on the GPU"); return; }
+  long P = A->shape()[0];
+  long lda = A->shape()[2], ldb = B->shape()[2], ldc = C->shape()[2];
+  long M = C->shape()[1], N = C->shape()[2], K = A->shape()[1 + (cl->tA ? 0 : 1)];
+  if (B->shape()[0] != P || C->shape()[0] != P || B->shape()[1 + (cl->tB ? 1 : 0)] != K) { fail("shape mismatch at batched matrix multiplication"); return; }
+  sgemm_dispatch(cl->tA, cl->tB, P, M, N, K, (const float*)A->data(), lda, A->stride(0), (const float*)B->data(), ldb,
+                 B->stride(0), (float*)C->data(), ldc, C->stride(0), 0);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Im2Col / Col2Im / MaxPool / MaxPoolPullback share the reference's conv_closure (include/pooling.h:7-14)
+// ------------------------------------------------------------------------------------------------
+struct ConvClosure { int kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w; };
+OP_BYREF(cgtb_op_im2col) {
+  ConvClosure* cl = (ConvClosure*)cl0;
+  cgtArray *im = ARR(reads[0]), *col = ARR(write0);
+  if (!all_gpu({im, col})) { fail("Im2Col: operands must be on the GPU"); return; }
+  const long* s = im->shape();
+  cgtb_im2col(im->dtype(), im->data(), s[0], (int)s[1], (int)s[2], (int)s[3], cl->kernel_h, cl->kernel_w, cl->pad_h, cl->pad_w,
+              cl->stride_h, cl->stride_w, col->data());
+}
+OP_BYREF(cgtb_op_col2im) {
+  ConvClosure* cl = (ConvClosure*)cl0;
+  cgtArray *col = ARR(reads[0]), *im = ARR(write0);
+  if (!all_gpu({col, im})) { fail("Col2Im: operands must be on the GPU"); return; }
+  long B = host_i8(reads[1]), C = host_i8(reads[2]), H = host_i8(reads[3]), W = host_i8(reads[4]);
+  cgtb_col2im(col->dtype(), col->data(), B, (int)C, (int)H, (int)W, cl->kernel_h, cl->kernel_w, cl->pad_h, cl->pad_w,
+              cl->stride_h, cl->stride_w, im->data());
+}
+OP_BYREF(cgtb_op_max_pool) {
+  ConvClosure* cl = (ConvClosure*)cl0;
+  cgtArray* x = ARR(reads[0]);
+  cgtTuple* out = (cgtTuple*)write0;
+  cgtArray *top = ARR(out->getitem(0)), *mask = ARR(out->getitem(1));
+  if (!all_gpu({x, top, mask})) { fail("MaxPool: operands must be on the GPU"); return; }
+  const long* s = x->shape();
+  cgtb_max_pool(x->dtype(), x->data(), s[0], (int)s[1], (int)s[2], (int)s[3], cl->kernel_h, cl->kernel_w, cl->pad_h, cl->pad_w,
+                cl->stride_h, cl->stride_w, (int)top->shape()[2], (int)top->shape()[3], top->data(), (int32_t*)mask->data());
+}
+OP_BYREF(cgtb_op_max_pool_pullback) {
+  ConvClosure* cl = (ConvClosure*)cl0;
+  // reads: x, pooled, mask, gpooled ; x and pooled only give shapes (include/pooling.h:83-89)
+  cgtArray *x = ARR(reads[0]), *mask = ARR(reads[2]), *gtop = ARR(reads[3]), *gx = ARR(write0);
+  if (!all_gpu({x, mask, gtop, gx})) { fail("MaxPoolPullback: operands must be on the GPU"); return; }
+  const long* s = x->shape();
+  cgtb_max_pool_pullback(gtop->dtype(), (const int32_t*)mask->data(), gtop->data(), s[0], (int)s[1], (int)mask->shape()[2],
+                         (int)mask->shape()[3], (int)s[2], (int)s[3], cl->kernel_h, cl->kernel_w, cl->pad_h, cl->pad_w,
+                         cl->stride_h, cl->stride_w, gx->data());
+}
+
+// ------------------------------------------------------------------------------------------------
+// CrossChannelLRN (cgt/nn_ops/cross_channel_lrn.py:8-13 closure: localsize, alpha, beta)
+// ------------------------------------------------------------------------------------------------
+struct LrnClosure { int localsize; double alpha; double beta; };
+OP_BYREF(cgtb_op_lrn_forward) {
+  LrnClosure* cl = (LrnClosure*)cl0;
+  cgtArray* x = ARR(reads[0]);
+  cgtTuple* out = (cgtTuple*)write0;
+  cgtArray *top = ARR(out->getitem(0)), *scale = ARR(out->getitem(1));
+  if (!all_gpu({x, top, scale})) { fail("CrossChannelLRNForward: operands must be on the GPU"); return; }
+  const long* s = x->shape();
+  cgtb_lrn_forward(x->dtype(), x->data(), s[0], (int)s[1], (int)s[2], (int)s[3], cl->localsize, cl->alpha, cl->beta, top->data(),
+                   scale->data());
+}
+OP_BYREF(cgtb_op_lrn_backward) {
+  LrnClosure* cl = (LrnClosure*)cl0;
+  cgtArray *x = ARR(reads[0]), *top = ARR(reads[1]), *scale = ARR(reads[2]), *gtop = ARR(reads[3]), *gx = ARR(write0);
+  if (!all_gpu({x, top, scale, gtop, gx})) { fail("CrossChannelLRNBackward: operands must be on the GPU"); return; }
+  const long* s = x->shape();
+  cgtb_lrn_backward(x->dtype(), x->data(), top->data(), scale->data(), gtop->data(), s[0], (int)s[1], (int)s[2], (int)s[3],
+                    cl->localsize, cl->alpha, cl->beta, gx->data());
+}
+
+// ------------------------------------------------------------------------------------------------
+// Sum / Max (cgt/core.py:1687-1738). axes are a bit mask.
+// ------------------------------------------------------------------------------------------------
+struct ReduceClosure { int kind; int axes_mask; };
+OP_BYREF(cgtb_op_reduce) {
+  ReduceClosure* cl = (ReduceClosure*)cl0;
+  cgtArray *x = ARR(reads[0]), *w = ARR(write0);
+  int red[CGTB_MAX_NDIM];
+  for (int i = 0; i < x->ndim(); ++i) red[i] = (cl->axes_mask >> i) & 1;
+  if (all_gpu({x, w})) { cgtb_reduce(cl->kind, x->dtype(), x->ndim(), x->shape(), red, x->data(), w->data()); return; }
+  fail("Sum/Max: operands must be on the GPU");
+}
+
+// ------------------------------------------------------------------------------------------------
+// Repeat / Transpose / slices / flat indices / Concatenate / Fill / constants
+// ------------------------------------------------------------------------------------------------
+struct RepeatClosure { int axes_mask; };
+OP_BYREF(cgtb_op_repeat) {
+  RepeatClosure* cl = (RepeatClosure*)cl0;
+  cgtArray *x = ARR(reads[0]), *w = ARR(write0);
+  int rep[CGTB_MAX_NDIM];
+  for (int i = 0; i < w->ndim(); ++i) {
+    rep[i] = (cl->axes_mask >> i) & 1;
+    if (rep[i] && x->shape()[i] != 1) { fail("Repeat: axis %d of the input has extent %ld, expected 1", i, x->shape()[i]); return; }
+  }
+  if (!all_gpu({x, w})) { fail("Repeat: operands must be on the GPU"); return; }
+  cgtb_repeat(x->dtype(), w->ndim(), w->shape(), rep, x->data(), w->data());
+}
+struct TransposeClosure { long perm; };  // 4 bits per output axis
+OP_BYREF(cgtb_op_transpose) {
+  TransposeClosure* cl = (TransposeClosure*)cl0;
+  cgtArray *x = ARR(reads[0]), *w = ARR(write0);
+  int axes[CGTB_MAX_NDIM];
+  for (int i = 0; i < x->ndim(); ++i) axes[i] = (int)((cl->perm >> (4 * i)) & 15);
+  if (!all_gpu({x, w})) { fail("Transpose: operands must be on the GPU"); return; }
+  cgtb_transpose(x->dtype(), x->ndim(), x->shape(), axes, x->data(), w->data());
+}
+struct AxisClosure { int axis; };
+static void split3(cgtArray* a, int axis, long* outer, long* n, long* inner) {
+  *outer = 1; *inner = 1;
+  for (int i = 0; i < axis; ++i) *outer *= a->shape()[i];
+  for (int i = axis + 1; i < a->ndim(); ++i) *inner *= a->shape()[i];
+  *n = a->shape()[axis];
+}
+OP_BYREF(cgtb_op_getsli) {
+  AxisClosure* cl = (AxisClosure*)cl0;
+  cgtArray *x = ARR(reads[0]), *w = ARR(write0);
+  long start = host_i8(reads[1]), step = host_i8(reads[3]);
+  long outer, n_in, inner;
+  split3(x, cl->axis, &outer, &n_in, &inner);
+  if (!all_gpu({x, w})) { fail("GetSli: operands must be on the GPU"); return; }
+  cgtb_getsli(x->dtype(), outer, n_in, inner, start, step, w->shape()[cl->axis], x->data(), w->data());
+}
+OP_BYREF(cgtb_op_incsli) {
+  AxisClosure* cl = (AxisClosure*)cl0;
+  cgtArray *x = ARR(reads[0]), *inc = ARR(reads[4]), *w = ARR(write0);
+  long start = host_i8(reads[1]), step = host_i8(reads[3]);
+  long outer, n_x, inner;
+  split3(x, cl->axis, &outer, &n_x, &inner);
+  if (!all_gpu({x, inc, w})) { fail("IncSli: operands must be on the GPU"); return; }
+  if (x->size() != w->size()) { fail("IncSli: output size differs from input size"); return; }
+  cgtb_incsli(x->dtype(), outer, n_x, inner, start, step, inc->shape()[cl->axis], x->data(), inc->data(), w->data());
+}
+OP_BYREF(cgtb_op_getflat) {
+  cgtArray *x = ARR(reads[0]), *k = ARR(reads[1]), *w = ARR(write0);
+  if (!all_gpu({x, k, w})) { fail("GetFlatIndices: operands must be on the GPU"); return; }
+  if (k->dtype() != cgt_i8) { fail("GetFlatIndices: indices must be int64"); return; }
+  cgtb_getflat(x->dtype(), w->size(), x->data(), (const int64_t*)k->data(), w->data());
+}
+OP_BYREF(cgtb_op_incflat) {
+  cgtArray *x = ARR(reads[0]), *k = ARR(reads[1]), *p = ARR(reads[2]), *w = ARR(write0);
+  if (!all_gpu({x, k, p, w})) { fail("IncFlatIndices: operands must be on the GPU"); return; }
+  if (k->dtype() != cgt_i8) { fail("IncFlatIndices: indices must be int64"); return; }
+  cgtb_incflat(x->dtype(), x->size(), p->size(), x->data(), (const int64_t*)k->data(), p->data(), w->data());
+}
+struct ConcatClosure { int axis; int n_in; };
+OP_BYREF(cgtb_op_concatenate) {
+  ConcatClosure* cl = (ConcatClosure*)cl0;
+  cgtArray* w = ARR(write0);
+  long pos = 0;
+  for (int i = 0; i < cl->n_in; ++i) {
+    cgtArray* x = ARR(reads[i]);
+    if (!all_gpu({x, w})) { fail("Concatenate: operands must be on the GPU"); return; }
+    long outer, n_in, inner;
+    split3(x, cl->axis, &outer, &n_in, &inner);
+    if (cgtb_concat_part(x->dtype(), outer, n_in, w->shape()[cl->axis], inner, pos, x->data(), w->data())) return;
+    pos += n_in;
+  }
+}
+struct FillClosure { double fvalue; long ivalue; };
+OP_BYREF(cgtb_op_fill) {
+  FillClosure* cl = (FillClosure*)cl0;
+  cgtArray* w = ARR(write0);
+  if (on_gpu(w)) { cgtb_fill(w->dtype(), w->size(), cl->fvalue, cl->ivalue, w->data()); return; }
+  if (!host_scalar_ok("Fill", {w})) return;
+  long n = w->size();
+  HOST_FOR_DTYPE(w->dtype(), T, {
+    for (long i = 0; i < n; ++i) w->at<T>(i) = std::is_floating_point<T>::value ? (T)cl->fvalue : (T)cl->ivalue;
+  });
+}
+// ConstantTensor, byref (cgt/core.py:914-935): copy the closure's host buffer into the output,
+// which may live on either device.
+struct ConstClosure { int ndim; void* shape; unsigned char dtype; void* data; };
+OP_BYREF(cgtb_op_constant) {
+  ConstClosure* cl = (ConstClosure*)cl0;
+  cgtArray* w = ARR(write0);
+  cgtb_memcpy((int)w->devtype(), cgtbCPU, w->data(), cl->data, w->nbytes(), 0);
+}
+// Transport (cgt/core.py:1596-1612)
+OP_BYREF(cgtb_op_transport) { cgt_copy_object(write0, reads[0]); }
+
+// ------------------------------------------------------------------------------------------------
+// by-value ops: host bookkeeping that never touches array data
+// ------------------------------------------------------------------------------------------------
+struct ReshapeClosure { int ndim; };
+OP_BYVAL(cgtb_op_reshape) {  // cgt/core.py:1451-1465; the view retains its source
+  ReshapeClosure* cl = (ReshapeClosure*)cl0;
+  cgtArray* in = ARR(reads[0]);
+  long shape[CGTB_MAX_NDIM], total = 1;
+  if (cl->ndim > CGTB_MAX_NDIM) { fail("Reshape: ndim %d too large", cl->ndim); return nullptr; }
+  for (int i = 0; i < cl->ndim; ++i) {
+    shape[i] = host_i8(reads[i + 1]);
+    if (shape[i] < 0) { fail("negative size in reshape not supported"); return nullptr; }
+    total *= shape[i];
+  }
+  if (total != in->size()) { fail("Reshape: cannot view %ld elements as %ld", in->size(), total); return nullptr; }
+  return new cgtArray(cl->ndim, shape, in->dtype(), in->devtype(), in->data(), (cgtObject*)in);
+}
+struct SizeClosure { int ax; };
+OP_BYVAL(cgtb_op_size) {  // cgt/core.py:1421-1430
+  SizeClosure* cl = (SizeClosure*)cl0;
+  cgtArray* out = new cgtArray(0, nullptr, cgt_i8, cgtCPU);
+  out->at<long>(0) = ARR(reads[0])->shape()[cl->ax];
+  return out;
+}
+OP_BYVAL(cgtb_op_arange) {  // cgt/core.py:1037-1048 : host int64 vector
+  long start = host_i8(reads[0]), stop = host_i8(reads[1]), step = host_i8(reads[2]);
+  if (step == 0) { fail("Arange: zero step"); return nullptr; }
+  long size = (stop - start) / step;
+  if (size < 0) size = 0;
+  cgtArray* out = new cgtArray(1, &size, cgt_i8, cgtCPU);
+  for (long i = 0; i < size; ++i) out->at<long>(i) = start + i * step;
+  return out;
+}
+struct TupleIndexClosure { int idx; };
+OP_BYVAL(cgtb_op_tuple_index) {  // cgt/core.py:2437-2442
+  TupleIndexClosure* cl = (TupleIndexClosure*)cl0;
+  cgtTuple* t = (cgtTuple*)reads[0];
+  if (cl->idx < 0 || cl->idx >= t->len) { fail("TupleIndex: index %d out of range", cl->idx); return nullptr; }
+  return t->getitem(cl->idx);
+}
+struct DataClosure { void* pptr; };
+OP_BYVAL(cgtb_op_in_memory_data) {  // cgt/core.py:557-564
+  DataClosure* cl = (DataClosure*)cl0;
+  return *(cgtObject**)cl->pptr;
+}

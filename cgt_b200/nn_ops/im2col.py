@@ -1,0 +1,84 @@
+"""Im2Col / Col2Im Ops (counterpart of the reference's cgt/nn_ops/im2col.py).
+
+Column layout is channels-last, ``[B, Ho, Wo, C*kh*kw]`` with column channel ``(c_im*kh + i)*kw + j``,
+so ``Mul22(F,T)(col.reshape(B*Ho*Wo, Z), W.reshape(L, Z))`` is the cross-correlation.
+"""
+import ctypes
+from collections import namedtuple
+
+from .. import core
+
+Im2ColInfo = namedtuple("Im2ColInfo", ["kernel_h", "kernel_w", "pad_h", "pad_w", "stride_h", "stride_w"])
+
+
+def im2col(x, kernelshape, pad, stride):
+    assert stride[0] > 0 and stride[1] > 0
+    assert kernelshape[0] > 0 and kernelshape[1] > 0
+    kernelshape, pad, stride = map(tuple, (kernelshape, pad, stride))
+    return core.Result(Im2Col(Im2ColInfo(*(kernelshape + pad + stride))), [x])
+
+
+def info2closure(info):
+    """Field order of the reference's conv_closure struct (include/pooling.h:7-14)."""
+    return [(name, ctypes.c_int, int(getattr(info, name)))
+            for name in ("kernel_h", "kernel_w", "pad_h", "pad_w", "stride_h", "stride_w")]
+
+
+class Im2Col(core.Op):
+    available_impls = ("native_cpu", "native_gpu")
+
+    def __init__(self, info):
+        assert info.stride_h > 0 and info.stride_w > 0
+        self.info = info
+
+    def get_diff(self, _):
+        return [True]
+
+    def pullback(self, inputs, _y, gy):
+        return [core.Result(Col2Im(self.info), [gy] + core.cgt.shape(inputs[0]))]
+
+    def shp_apply(self, inputs):
+        info = self.info
+        batch_size, channels, height, width = core.cgt.shape(inputs[0])
+        height_out = (height + 2 * info.pad_h - info.kernel_h) // info.stride_h + 1
+        width_out = (width + 2 * info.pad_w - info.kernel_w) // info.stride_w + 1
+        return [batch_size, height_out, width_out, channels * info.kernel_w * info.kernel_h]
+
+    def typ_apply(self, inputs):
+        assert inputs[0].ndim == 4
+        return core.TensorType(inputs[0].dtype, 4)
+
+    def get_native_compile_info(self, input_types, devtype):
+        return core.NativeCompileInfo(None, prebuilt="cgtb_op_im2col", closure_triples=info2closure(self.info))
+
+    def __repr__(self):
+        return "Im2Col{%s}" % (tuple(self.info),)
+
+
+class Col2Im(core.Op):
+    """(col, B, C, H, W) -> image gradient; the adjoint of Im2Col."""
+    available_impls = ("native_cpu", "native_gpu")
+
+    def __init__(self, info):
+        self.info = info
+
+    def get_diff(self, n):
+        return [True] + [False] * (n - 1)
+
+    def pullback(self, inputs, _y, gy):
+        return [core.Result(Im2Col(self.info), [gy])] + [None] * (len(inputs) - 1)
+
+    def shp_apply(self, inputs):
+        return list(inputs[1:])
+
+    def typ_apply(self, inputs):
+        return core.TensorType(inputs[0].dtype, 4)
+
+    def host_inputs(self, n):
+        return (1, 2, 3, 4)
+
+    def get_native_compile_info(self, input_types, devtype):
+        return core.NativeCompileInfo(None, prebuilt="cgtb_op_col2im", closure_triples=info2closure(self.info))
+
+    def __repr__(self):
+        return "Col2Im{%s}" % (tuple(self.info),)

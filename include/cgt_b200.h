@@ -1,0 +1,166 @@
+/* C ABI of libcgt_b200.so: the B200 (sm_100a) execution backend for CGT compiled graphs.
+ *
+ * Plain C, plain pointers and sizes. Every entry point returns 0 on success and non-zero on failure
+ * unless stated otherwise; the message of the last failure on the calling thread is read with
+ * cgtb_last_error(). Nothing aborts, and no entry point falls back to a CPU implementation:
+ * tensor work always runs as CUDA kernels on the runtime's current stream.
+ *
+ * Each group names the reference interface it replaces (paths inside the reference project).
+ */
+#ifndef CGT_B200_H
+#define CGT_B200_H
+#include <stdint.h>
+#include "cgt_b200_ops.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct cgtbObject cgtbObject; /* a cgtObject* (array or tuple), reference-counted */
+typedef struct cgtbGraph cgtbGraph;   /* execution graph under construction */
+typedef struct cgtbInterp cgtbInterp; /* interpreter bound to one execution graph */
+
+/* ------------------------------------------------------------------------------------------------
+ * Runtime. Replaces the implicit "device 0, default stream, cudaMalloc per array" behaviour of
+ * src/cgt_common.cpp:110-153 and include/cgt_cuda.h.
+ * ---------------------------------------------------------------------------------------------- */
+int cgtb_init(int device);                 /* bind this process to one GPU; creates stream + pools */
+int cgtb_initialized(void);                /* 1 after a successful cgtb_init */
+int cgtb_device(void);                     /* device index bound by cgtb_init, -1 before */
+const char* cgtb_last_error(void);         /* message of the last failure ("" if none) */
+void cgtb_clear_error(void);
+int cgtb_synchronize(void);                /* cudaStreamSynchronize on the runtime stream */
+void* cgtb_stream(void);                   /* the runtime's cudaStream_t */
+int cgtb_pool_stats(long* reserved_bytes, long* in_use_bytes, long* high_water_bytes, long* n_device_mallocs);
+int cgtb_pool_trim(void);                  /* return cached blocks to the driver */
+long cgtb_kernel_launches(void);           /* kernels launched by this library since load */
+int cgtb_sm_count(void);
+
+/* Raw memory. devtype: 0 host (pinned), 1 device. (src/cgt_common.cpp:110-153) */
+void* cgtb_alloc(int devtype, long nbytes);
+void cgtb_free(int devtype, void* p);
+int cgtb_memcpy(int dst_devtype, int src_devtype, void* dst, const void* src, long nbytes, int sync);
+int cgtb_memset(void* dev_ptr, int value, long nbytes);
+
+/* ------------------------------------------------------------------------------------------------
+ * Objects. Replaces numpy<->cgtArray marshalling in src/cycgt.pyx:92-140 and CppArrayWrapper
+ * (src/cycgt.pyx:371-401).
+ * ---------------------------------------------------------------------------------------------- */
+cgtbObject* cgtb_array_new(int ndim, const long* shape, int dtype, int devtype);
+/* copy=1: new owning array on devtype filled from host memory; copy=0: view of host memory */
+cgtbObject* cgtb_array_from_host(int ndim, const long* shape, int dtype, int devtype, void* host, int copy);
+/* non-owning view of device memory the caller keeps alive */
+cgtbObject* cgtb_array_view_device(int ndim, const long* shape, int dtype, void* dev_ptr);
+int cgtb_array_to_host(cgtbObject* a, void* host_dst);          /* synchronous */
+int cgtb_array_set_from_host(cgtbObject* a, const void* host);  /* synchronous */
+int cgtb_array_ndim(cgtbObject* a);
+const long* cgtb_array_shape(cgtbObject* a);
+int cgtb_array_dtype(cgtbObject* a);
+int cgtb_array_devtype(cgtbObject* a);
+void* cgtb_array_data(cgtbObject* a);
+long cgtb_array_nbytes(cgtbObject* a);
+cgtbObject* cgtb_tuple_new(int len);
+int cgtb_tuple_len(cgtbObject* t);
+cgtbObject* cgtb_tuple_get(cgtbObject* t, int i);               /* borrowed */
+int cgtb_tuple_set(cgtbObject* t, int i, cgtbObject* o);        /* retains o */
+int cgtb_object_kind(cgtbObject* o);                            /* 1 array, 2 tuple */
+void cgtb_retain(cgtbObject* o);
+void cgtb_release(cgtbObject* o);
+
+/* ------------------------------------------------------------------------------------------------
+ * Execution graph + interpreter. Replaces the instruction constructors and create_interpreter of
+ * include/execution.h:47-162 and the marshalling in src/cycgt.pyx:338-369, 404-434.
+ * A memory location is (index, devtype). Callables have the reference signatures
+ *   byref: void f(void* closure, cgtObject** reads, cgtObject* write)   (cgt_common.h:176)
+ *   byval: cgtObject* f(void* closure, cgtObject** reads)               (cgt_common.h:177)
+ * ---------------------------------------------------------------------------------------------- */
+#define CGTB_INSTR_QUICK 1        /* host bookkeeping only: never touches array data */
+#define CGTB_INSTR_TRANSPORT 2    /* cross-device copy: runs outside captured CUDA graphs */
+#define CGTB_INSTR_NOCAPTURE 4    /* must not be stream-captured (e.g. a Python callback) */
+#define CGTB_INSTR_ONCE 8         /* inputs are compile-time constants: fire on the first run only */
+
+cgtbGraph* cgtb_graph_new(long n_args, long n_locs);
+void cgtb_graph_free(cgtbGraph* g);
+int cgtb_graph_add_load_argument(cgtbGraph* g, const char* repr, int arg_index, long wloc, int wdev);
+int cgtb_graph_add_alloc(cgtbGraph* g, const char* repr, int dtype, int n_shape, const long* shape_locs, long wloc, int wdev);
+int cgtb_graph_add_build_tup(cgtbGraph* g, const char* repr, int n, const long* read_locs, long wloc, int wdev);
+int cgtb_graph_add_return_byref(cgtbGraph* g, const char* repr, int n, const long* read_locs, const int* read_devs,
+                                long wloc, int wdev, void* fptr, void* closure, int flags);
+int cgtb_graph_add_return_byval(cgtbGraph* g, const char* repr, int n, const long* read_locs, const int* read_devs,
+                                long wloc, int wdev, void* fptr, void* closure, int flags);
+
+#define CGTB_INTERP_CUDA_GRAPHS 1 /* capture steady-state device segments into CUDA graphs and replay them */
+#define CGTB_INTERP_PROFILE 2     /* time every instruction with CUDA events (per-Op table) */
+cgtbInterp* cgtb_interp_new(cgtbGraph* g, int n_out, const long* out_locs, int flags);
+void cgtb_interp_free(cgtbInterp* it);
+/* args: tuple of arrays (host or device). *out: new reference to a tuple of the output objects.
+ * Returns after the runtime stream has been synchronised, so host outputs are readable. */
+int cgtb_interp_run(cgtbInterp* it, cgtbObject* args, cgtbObject** out);
+/* counters: [0] runs, [1] kernels launched by instructions in the last run, [2] graph launches in the
+ * last run, [3] segments captured so far, [4] device instructions in the graph */
+int cgtb_interp_stats(cgtbInterp* it, long* counters, int n);
+/* per-instruction accumulated milliseconds when CGTB_INTERP_PROFILE is set; returns n_instrs */
+int cgtb_interp_profile(cgtbInterp* it, double* ms, long* counts, int cap);
+const char* cgtb_interp_instr_repr(cgtbInterp* it, int i);
+/* call one callable directly (reference: cycgt.apply_byref, src/cycgt.pyx:439-449) */
+int cgtb_apply_byref(void* fptr, void* closure, int n, cgtbObject** reads, cgtbObject* write);
+
+/* ------------------------------------------------------------------------------------------------
+ * Kernels with plain device pointers. All arrays are C-contiguous; all launches go to the runtime
+ * stream. dtype arguments are numpy type numbers (cgtbDtype).
+ * ---------------------------------------------------------------------------------------------- */
+/* Mul22: C[M,N] = op(A) op(B), alpha 1, beta 0, row-major; lda/ldb/ldc are stored row lengths.
+ * Replaces cblas_sgemm / cublasSgemm_v2 in cgt/core.py:2195-2222. 3xTF32 split on tcgen05 tensor
+ * cores where the shape allows, an fp32 FMA kernel otherwise. impl: 0 auto, 1 force FMA, 2 force tensor. */
+int cgtb_sgemm(int tA, int tB, long M, long N, long K, const float* A, long lda, const float* B, long ldb,
+               float* C, long ldc, int impl);
+/* BatchedMul22 (cgt/core.py:2272-2286): P independent products, operands strideX apart */
+int cgtb_sgemm_batched(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA,
+                       const float* B, long ldb, long strideB, float* C, long ldc, long strideC, int impl);
+int cgtb_dgemm(int tA, int tB, long M, long N, long K, const double* A, long lda, const double* B, long ldb,
+               double* C, long ldc);
+
+/* Im2Col / Col2Im (include/im2col.h:6-50, cgt/nn_ops/im2col.py:47-92); col is [B,Ho,Wo,C*kh*kw] */
+int cgtb_im2col(int dtype, const void* x, long B, int C, int H, int W, int kh, int kw, int ph, int pw, int sh,
+                int sw, void* col);
+int cgtb_col2im(int dtype, const void* col, long B, int C, int H, int W, int kh, int kw, int ph, int pw, int sh,
+                int sw, void* im);
+
+/* MaxPool / MaxPoolPullback (include/pooling.h:24-104); mask is int32 h*W+w within the plane */
+int cgtb_max_pool(int dtype, const void* x, long B, int C, int H, int W, int kh, int kw, int ph, int pw, int sh,
+                  int sw, int PH, int PW, void* top, int32_t* mask);
+int cgtb_max_pool_pullback(int dtype, const int32_t* mask, const void* gtop, long B, int C, int PH, int PW, int H,
+                           int W, int kh, int kw, int ph, int pw, int sh, int sw, void* gx);
+
+/* CrossChannelLRN forward/backward (include/lrn.cuh:3-114, cgt/nn_ops/cross_channel_lrn.py:27-37,78-82) */
+int cgtb_lrn_forward(int dtype, const void* x, long N, int C, int H, int W, int size, double alpha, double beta,
+                     void* top, void* scale);
+int cgtb_lrn_backward(int dtype, const void* x, const void* top, const void* scale, const void* gtop, long N, int C,
+                      int H, int W, int size, double alpha, double beta, void* gx);
+
+/* ElwiseUnary / ElwiseBinary (cgt/core.py:1160-1378). scalar_x / scalar_y: operand is a 0-d array
+ * in device memory, read at index 0. */
+int cgtb_unary(int op, int dt_in, int dt_out, long n, const void* in, void* out);
+int cgtb_binary(int op, int dt_x, int dt_y, int dt_out, long n, const void* x, const void* y, void* out,
+                int scalar_x, int scalar_y);
+
+/* Sum / Max over a set of axes, keepdims (cgt/core.py:1663-1738) */
+int cgtb_reduce(int kind, int dtype, int ndim, const long* shape, const int* reduced, const void* in, void* out);
+
+/* Repeat, Transpose, GetSli, IncSli, GetFlatIndices, IncFlatIndices, Concatenate, Fill
+ * (cgt/core.py:1511-1594, 1767-1861, 1960-2023, 1467-1509, 966-1007) */
+int cgtb_repeat(int dtype, int ndim, const long* out_shape, const int* repeated, const void* in, void* out);
+int cgtb_transpose(int dtype, int ndim, const long* in_shape, const int* axes, const void* in, void* out);
+int cgtb_getsli(int dtype, long outer, long n_in, long inner, long start, long step, long n_out, const void* in,
+                void* out);
+int cgtb_incsli(int dtype, long outer, long n_x, long inner, long start, long step, long n_inc, const void* x,
+                const void* inc, void* out);
+int cgtb_getflat(int dtype, long n, const void* x, const int64_t* k, void* out);
+int cgtb_incflat(int dtype, long xsize, long n, const void* x, const int64_t* k, const void* p, void* out);
+int cgtb_concat_part(int dtype, long outer, long n_in, long n_out, long inner, long pos, const void* in, void* out);
+int cgtb_fill(int dtype, long n, double fvalue, long ivalue, void* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

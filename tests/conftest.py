@@ -1,0 +1,20 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a B200; run with `-m gpu` on the GPU box")
+
+
+@pytest.fixture(scope="session")
+def rt():
+    """The runtime module bound to the GPU. GPU tests fail (not skip) when no device can be bound."""
+    from cgt_b200 import runtime
+    runtime.ensure_init()
+    return runtime

@@ -1,0 +1,335 @@
+"""GPU parity: every kernel of the C ABI against the CPU oracle on the same seeded inputs.
+
+Integer / index outputs (pool argmax mask, comparisons, casts to int, gathers) must be bit-exact.
+Float outputs of order-dependent sums that the kernels reproduce in the reference's order (pool
+pullback, col2im) must be bit-exact too. Other float outputs: rtol 1e-4, atol 1e-5.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from tests.gpu_util import Dev, call, code, ints, longs
+
+pytestmark = pytest.mark.gpu
+
+RTOL, ATOL = 1e-4, 1e-5
+
+GEOMS = [
+    # (x shape, kernel, pad, stride)
+    ((2, 2, 5, 17), (4, 7), (3, 6), (1, 1)),     # reference test_conv.py
+    ((2, 1, 28, 28), (4, 4), (0, 0), (1, 1)),    # reference test_imgproc.py test_im2col
+    ((2, 1, 28, 28), (3, 3), (1, 1), (2, 2)),
+    ((2, 1, 28, 28), (3, 3), (1, 1), (3, 3)),
+    ((3, 3, 32, 32), (5, 5), (2, 2), (1, 1)),    # CIFAR conv1 geometry
+    ((2, 32, 15, 15), (5, 5), (2, 2), (1, 1)),   # CIFAR conv2 geometry
+    ((2, 3, 64, 64), (11, 11), (2, 2), (4, 4)),  # wide conv1 geometry
+    ((1, 2, 7, 9), (2, 3), (1, 0), (2, 1)),      # ragged
+    ((1, 1, 3, 3), (3, 3), (0, 0), (1, 1)),      # single output pixel
+]
+
+
+@pytest.mark.parametrize("shape,kernel,pad,stride", GEOMS)
+@pytest.mark.parametrize("dtype", ["f4", "f8"])
+def test_im2col_col2im(rt, shape, kernel, pad, stride, dtype):
+    rs = np.random.RandomState(0)
+    x = rs.randn(*shape).astype(dtype)
+    want = O.im2col(x, kernel, pad, stride)
+    dx, dcol = Dev(x), Dev(shape=want.shape, dtype=dtype)
+    B, C, H, W = shape
+    call("cgtb_im2col", code(dtype), dx.ptr, B, C, H, W, kernel[0], kernel[1], pad[0], pad[1], stride[0], stride[1], dcol.ptr)
+    assert np.array_equal(dcol.get(), want)  # a copy with zero fill: exact
+    g = rs.randn(*want.shape).astype(dtype)
+    want_im = O.col2im(g, shape, kernel, pad, stride)
+    dg, dim = Dev(g), Dev(shape=shape, dtype=dtype)
+    call("cgtb_col2im", code(dtype), dg.ptr, B, C, H, W, kernel[0], kernel[1], pad[0], pad[1], stride[0], stride[1], dim.ptr)
+    assert np.array_equal(dim.get(), want_im)  # same accumulation order as the CPU loop: exact
+
+
+POOLS = [
+    ((2, 3, 5, 7), (4, 4), (0, 0), (1, 1)),      # reference test_imgproc.py test_pool
+    ((4, 32, 32, 32), (3, 3), (0, 0), (2, 2)),   # CIFAR pool1
+    ((4, 32, 15, 15), (3, 3), (0, 0), (2, 2)),
+    ((4, 64, 6, 6), (3, 3), (0, 0), (2, 2)),
+    ((2, 3, 9, 11), (3, 3), (1, 1), (2, 2)),     # padded
+    ((2, 2, 8, 8), (2, 2), (0, 0), (2, 2)),      # non-overlapping
+    ((1, 1, 6, 6), (3, 2), (1, 0), (1, 2)),
+]
+
+
+@pytest.mark.parametrize("shape,kernel,pad,stride", POOLS)
+@pytest.mark.parametrize("dtype", ["f4", "f8"])
+@pytest.mark.parametrize("ties", [False, True])
+def test_max_pool(rt, shape, kernel, pad, stride, dtype, ties):
+    rs = np.random.RandomState(1)
+    x = rs.randn(*shape).astype(dtype)
+    if ties:  # many equal values: the first maximum in scan order must win
+        x = np.round(x).astype(dtype)
+    top, mask = O.max_pool(x, kernel, pad, stride)
+    B, C, H, W = shape
+    PH, PW = top.shape[2:]
+    dx, dtop, dmask = Dev(x), Dev(shape=top.shape, dtype=dtype), Dev(shape=mask.shape, dtype="i4")
+    call("cgtb_max_pool", code(dtype), dx.ptr, B, C, H, W, kernel[0], kernel[1], pad[0], pad[1], stride[0], stride[1], PH, PW,
+         dtop.ptr, dmask.ptr)
+    assert np.array_equal(dmask.get(), mask)
+    assert np.array_equal(dtop.get(), top)
+    g = rs.randn(*top.shape).astype(dtype)
+    want = O.max_pool_pullback(shape, mask, g)
+    dg, dgx = Dev(g), Dev(shape=shape, dtype=dtype)
+    call("cgtb_max_pool_pullback", code(dtype), dmask.ptr, dg.ptr, B, C, PH, PW, H, W, kernel[0], kernel[1], pad[0], pad[1],
+         stride[0], stride[1], dgx.ptr)
+    assert np.array_equal(dgx.get(), want)
+
+
+def test_max_pool_nan_window(rt):
+    """A window of NaNs keeps (-FLT_MAX, -1); the pullback must not scatter through the -1."""
+    x = np.full((1, 1, 4, 4), np.nan, "f4")
+    top, mask = O.max_pool(x, (2, 2), (0, 0), (2, 2))
+    dx, dtop, dmask = Dev(x), Dev(shape=top.shape, dtype="f4"), Dev(shape=mask.shape, dtype="i4")
+    call("cgtb_max_pool", code("f4"), dx.ptr, 1, 1, 4, 4, 2, 2, 0, 0, 2, 2, 2, 2, dtop.ptr, dmask.ptr)
+    assert np.array_equal(dmask.get(), mask) and (mask == -1).all()
+    assert np.array_equal(dtop.get(), top)
+    dg, dgx = Dev(np.ones_like(top)), Dev(shape=x.shape, dtype="f4")
+    call("cgtb_max_pool_pullback", code("f4"), dmask.ptr, dg.ptr, 1, 1, 2, 2, 4, 4, 2, 2, 0, 0, 2, 2, dgx.ptr)
+    assert np.array_equal(dgx.get(), np.zeros_like(x))
+
+
+LRNS = [
+    ((4, 8, 16, 16), 4, 0.1, 0.5),       # reference test_imgproc.py test_lrn
+    ((4, 32, 15, 15), 5, 1e-4, 0.75),    # CIFAR
+    ((2, 96, 15, 15), 5, 1e-4, 0.75),    # wide
+    ((2, 5, 3, 3), 5, 1.0, 0.75),        # channels == localsize
+    ((2, 7, 2, 3), 3, 0.5, 1.0),
+]
+
+
+@pytest.mark.parametrize("shape,size,alpha,beta", LRNS)
+@pytest.mark.parametrize("dtype", ["f4", "f8"])
+def test_lrn(rt, shape, size, alpha, beta, dtype):
+    rs = np.random.RandomState(2)
+    x = rs.randn(*shape).astype(dtype)
+    top, scale = O.lrn_forward(x, size, alpha, beta)
+    N, C, H, W = shape
+    dx, dtop, dscale = Dev(x), Dev(shape=shape, dtype=dtype), Dev(shape=shape, dtype=dtype)
+    call("cgtb_lrn_forward", code(dtype), dx.ptr, N, C, H, W, size, alpha, beta, dtop.ptr, dscale.ptr)
+    np.testing.assert_allclose(dscale.get(), scale, rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(dtop.get(), top, rtol=RTOL, atol=ATOL)
+    g = rs.randn(*shape).astype(dtype)
+    want = O.lrn_backward(x, top, scale, g, size, alpha, beta)
+    dt, ds, dg, dgx = Dev(top), Dev(scale), Dev(g), Dev(shape=shape, dtype=dtype)
+    call("cgtb_lrn_backward", code(dtype), dx.ptr, dt.ptr, ds.ptr, dg.ptr, N, C, H, W, size, alpha, beta, dgx.ptr)
+    np.testing.assert_allclose(dgx.get(), want, rtol=RTOL, atol=ATOL)
+
+
+UNARY_CASES = [
+    ("abs", "f4", "f4"), ("ceil", "f4", "i8"), ("cos", "f4", "f4"), ("exp", "f4", "f4"), ("iceil", "f4", "i8"),
+    ("ifloor", "f4", "i8"), ("log", "f4", "f4"), ("neg", "f4", "f4"), ("sign", "f4", "f4"), ("sin", "f4", "f4"),
+    ("square", "f4", "f4"), ("sqrt", "f4", "f4"), ("tanh", "f4", "f4"), ("sigmoid", "f4", "f4"), ("softplus", "f4", "f4"),
+    ("cast", "i1", "f4"), ("cast", "i8", "f4"), ("cast", "f4", "i8"), ("cast", "f4", "f8"), ("cast", "i4", "i8"),
+    ("neg", "i8", "i8"), ("square", "i8", "i8"), ("exp", "f8", "f8"), ("sigmoid", "f8", "f8"), ("sign", "i8", "i8"),
+]
+
+
+@pytest.mark.parametrize("op,dt_in,dt_out", UNARY_CASES)
+@pytest.mark.parametrize("n", [1, 5, 1000, 40003])
+def test_unary(rt, op, dt_in, dt_out, n):
+    rs = np.random.RandomState(3)
+    if np.dtype(dt_in).kind == "f":
+        x = (rs.randn(n) * 3).astype(dt_in)
+        if op in ("log", "sqrt"):
+            x = np.abs(x) + 0.01
+        x[:1] = 0  # sign(0) == -1 and friends
+    else:
+        x = rs.randint(-100, 100, size=n).astype(dt_in)
+    want = O.unary(op, x, dt_out)
+    dx, dout = Dev(x), Dev(shape=(n,), dtype=dt_out)
+    call("cgtb_unary", O.UNARY[op], code(dt_in), code(dt_out), n, dx.ptr, dout.ptr)
+    got = dout.get()
+    if np.dtype(dt_out).kind == "i" or op in ("abs", "neg", "sign", "square", "cast", "ceil", "sqrt"):
+        assert np.array_equal(got, want)
+    else:
+        np.testing.assert_allclose(got, want, rtol=RTOL, atol=ATOL)
+
+
+BINARY_CASES = [
+    ("*", "f4", "f4", "f4"), ("+", "f4", "f4", "f4"), ("-", "f4", "f4", "f4"), ("/", "f4", "f4", "f4"),
+    ("<", "f4", "f4", "i1"), (">", "f4", "f4", "i1"), ("<=", "f4", "f4", "i1"), (">=", "f4", "f4", "i1"),
+    ("**", "f4", "f4", "f4"), ("==", "f4", "f4", "i1"), ("!=", "f4", "f4", "i1"),
+    ("*", "f4", "i1", "f4"), ("*", "i8", "i8", "i8"), ("+", "i8", "i8", "i8"), ("/", "i8", "i8", "f4"),
+    (">=", "f4", "i8", "i1"), ("/", "f4", "i8", "f4"), ("*", "f8", "f8", "f8"), ("-", "i8", "f4", "f4"),
+    ("**", "f4", "i8", "f4"), ("==", "i8", "i8", "i1"),
+]
+
+
+@pytest.mark.parametrize("op,dtx,dty,dto", BINARY_CASES)
+@pytest.mark.parametrize("mode", ["tt", "ts", "st"])
+@pytest.mark.parametrize("n", [1, 7, 4099])
+def test_binary(rt, op, dtx, dty, dto, mode, n):
+    rs = np.random.RandomState(4)
+
+    def draw(dt, size):
+        if np.dtype(dt).kind == "f":
+            v = rs.randn(*size) * 2
+            if op == "**":
+                v = np.abs(v) + 0.1
+            return v.astype(dt)
+        v = rs.randint(-5, 6, size=size)
+        if op in ("/", "**"):
+            v = np.abs(v) + 1
+        return v.astype(dt)
+    x = draw(dtx, () if mode == "st" else (n,))
+    y = draw(dty, () if mode == "ts" else (n,))
+    if op in ("==", "!=", ">=", "<=") and mode == "tt":
+        y[::3] = x[::3].astype(dty)  # make equality happen
+    want = O.binary(op, x, y, dto)
+    dx, dy, dout = Dev(x), Dev(y), Dev(shape=(n,), dtype=dto)
+    call("cgtb_binary", O.BINARY[op], code(dtx), code(dty), code(dto), n, dx.ptr, dy.ptr, dout.ptr, int(mode == "st"),
+         int(mode == "ts"))
+    got = dout.get()
+    if np.dtype(dto).kind == "i" or op in ("*", "+", "-", "/"):
+        assert np.array_equal(got, want)  # IEEE basic operations: exact
+    else:
+        np.testing.assert_allclose(got, want, rtol=RTOL, atol=ATOL)
+
+
+REDUCE_CASES = [
+    ((128, 10), [1]), ((128, 10), [0]), ((128,), [0]), ((8, 32, 9, 9), [0, 2, 3]), ((100, 784), [1]), ((100, 20), [0, 1]),
+    ((3, 1, 5), [1]), ((2, 3, 4, 5), [1, 3]), ((64, 2048), [0, 1]), ((5, 70000), [1]), ((1,), [0]),
+]
+
+
+@pytest.mark.parametrize("shape,axes", REDUCE_CASES)
+@pytest.mark.parametrize("kind", ["sum", "max"])
+@pytest.mark.parametrize("dtype", ["f4", "f8", "i8"])
+def test_reduce(rt, shape, axes, kind, dtype):
+    rs = np.random.RandomState(5)
+    x = rs.randn(*shape).astype(dtype) if dtype != "i8" else rs.randint(-50, 50, size=shape).astype("i8")
+    want = O.reduce(kind, x, axes)
+    dx, dout = Dev(x), Dev(shape=want.shape, dtype=dtype)
+    red = [1 if i in axes else 0 for i in range(len(shape))]
+    call("cgtb_reduce", {"sum": 0, "max": 1}[kind], code(dtype), len(shape), longs(shape), ints(red), dx.ptr, dout.ptr)
+    got = dout.get()
+    if kind == "max" or dtype == "i8":
+        assert np.array_equal(got, want)
+    else:
+        # a parallel sum cannot follow the sequential fp32 order; both are judged against float64
+        exact = x.astype("f8").sum(axis=tuple(axes), keepdims=True)
+        n = x.size / max(want.size, 1)
+        tol = 1e-4 * np.abs(exact) + 1e-5 * max(1.0, np.sqrt(n))
+        assert (np.abs(got - exact) <= tol).all()
+        assert np.abs(got - exact).max() <= 2 * np.abs(want - exact).max() + 1e-5 * max(1.0, np.sqrt(n))
+
+
+def test_repeat_transpose_slices(rt):
+    rs = np.random.RandomState(6)
+    for dtype in ("f4", "i8", "i1", "f8"):
+        # Repeat: bias [1,L,1,1] -> [B,L,m,n] and [1,n] -> [B,n]
+        for (shape, axes, reps) in [((1, 5, 1, 1), [0, 2, 3], [3, 4, 6]), ((1, 7), [0], [9]), ((3, 1), [1], [5]), ((1, 1), [0, 1], [2, 3])]:
+            x = (rs.randn(*shape) * 10).astype(dtype)
+            want = O.repeat(x, axes, reps)
+            dx, dout = Dev(x), Dev(shape=want.shape, dtype=dtype)
+            call("cgtb_repeat", code(dtype), len(shape), longs(want.shape), ints([1 if i in axes else 0 for i in range(len(shape))]),
+                 dx.ptr, dout.ptr)
+            assert np.array_equal(dout.get(), want)
+        for (shape, axes) in [((4, 6, 5, 3), [0, 3, 1, 2]), ((4, 3, 6, 5), [0, 2, 3, 1]), ((7, 9), [1, 0]), ((2, 3, 4), [2, 0, 1]),
+                              ((2, 3, 4), [1, 0, 2]), ((33, 65), [1, 0]), ((3, 1, 4), [2, 1, 0]), ((5, 4), [0, 1])]:
+            x = (rs.randn(*shape) * 10).astype(dtype)
+            want = O.transpose(x, axes)
+            dx, dout = Dev(x), Dev(shape=want.shape, dtype=dtype)
+            call("cgtb_transpose", code(dtype), len(shape), longs(shape), ints(axes), dx.ptr, dout.ptr)
+            assert np.array_equal(dout.get(), want), (shape, axes)
+        x = (rs.randn(6, 10, 4) * 10).astype(dtype)
+        for (axis, start, stop, step) in [(1, 0, 10, 1), (1, 2, 9, 3), (0, 5, -1, -1), (2, 1, 3, 1), (0, 3, 4, 1)]:
+            want = O.getsli(x, axis, start, stop, step)
+            outer, n_in, inner = O._split(x.shape, axis)
+            dx, dout = Dev(x), Dev(shape=want.shape, dtype=dtype)
+            call("cgtb_getsli", code(dtype), outer, n_in, inner, start, step, want.shape[axis], dx.ptr, dout.ptr)
+            assert np.array_equal(dout.get(), want)
+            inc = (rs.randn(*want.shape) * 10).astype(dtype)
+            want2 = O.incsli(x, axis, start, stop, step, inc)
+            dinc, dout2 = Dev(inc), Dev(shape=x.shape, dtype=dtype)
+            call("cgtb_incsli", code(dtype), outer, n_in, inner, start, step, want.shape[axis], dx.ptr, dinc.ptr, dout2.ptr)
+            assert np.array_equal(dout2.get(), want2)
+        parts = [(rs.randn(3, k, 2) * 10).astype(dtype) for k in (1, 4, 2)]
+        want = O.concatenate(parts, 1)
+        dout = Dev(shape=want.shape, dtype=dtype)
+        pos = 0
+        for p in parts:
+            dp = Dev(p)
+            call("cgtb_concat_part", code(dtype), 3, p.shape[1], want.shape[1], 2, pos, dp.ptr, dout.ptr)
+            pos += p.shape[1]
+        assert np.array_equal(dout.get(), want)
+
+
+def test_flat_indices(rt):
+    rs = np.random.RandomState(7)
+    for dtype in ("f4", "i8", "f8"):
+        x = (rs.randn(128, 10) * 10).astype(dtype)
+        k = (np.arange(128) * 10 + rs.randint(0, 10, size=128)).astype("i8")
+        want = O.getflat(x, k)
+        dx, dk, dout = Dev(x), Dev(k), Dev(shape=(128,), dtype=dtype)
+        call("cgtb_getflat", code(dtype), 128, dx.ptr, dk.ptr, dout.ptr)
+        assert np.array_equal(dout.get(), want)
+        # duplicates accumulate, in index order (reference test_inc_subtensor.py:53-71)
+        kdup = rs.randint(0, 20, size=300).astype("i8")
+        p = (rs.randn(300) * 10).astype(dtype)
+        base = (rs.randn(40) * 10).astype(dtype)
+        want = O.incflat(base, kdup, p)
+        db, dk2, dp, dout2 = Dev(base), Dev(kdup), Dev(p), Dev(shape=(40,), dtype=dtype)
+        call("cgtb_incflat", code(dtype), 40, 300, db.ptr, dk2.ptr, dp.ptr, dout2.ptr)
+        assert np.array_equal(dout2.get(), want)
+    want = O.fill(2.5, (3, 4), "f4")
+    dout = Dev(shape=(3, 4), dtype="f4")
+    call("cgtb_fill", code("f4"), 12, ctypes.c_double(2.5), 0, dout.ptr)
+    assert np.array_equal(dout.get(), want)
+    dout = Dev(shape=(5,), dtype="i8")
+    call("cgtb_fill", code("i8"), 5, ctypes.c_double(0), 7, dout.ptr)
+    assert np.array_equal(dout.get(), np.full(5, 7, "i8"))
+
+
+GEMM_SHAPES = [
+    # (M, N, K)  -- reference test shapes, config shapes scaled to run in seconds, ragged edges
+    (3, 5, 4), (128, 10, 256), (128, 256, 784), (1024, 32, 75), (900, 32, 800), (32, 75, 4096), (64, 800, 1152),
+    (450, 800, 32), (1, 1, 1), (65, 63, 17), (100, 20, 500), (64, 512, 65), (129, 257, 130),
+]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+@pytest.mark.parametrize("tA,tB", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("impl", [1, 0])
+def test_sgemm(rt, M, N, K, tA, tB, impl):
+    rs = np.random.RandomState(8)
+    A = rs.randn(*((K, M) if tA else (M, K))).astype("f4")
+    B = rs.randn(*((N, K) if tB else (K, N))).astype("f4")
+    want = O.mul22(A, B, tA, tB)
+    dA, dB, dC = Dev(A), Dev(B), Dev(shape=(M, N), dtype="f4")
+    call("cgtb_sgemm", tA, tB, M, N, K, dA.ptr, A.shape[1], dB.ptr, B.shape[1], dC.ptr, N, impl)
+    got = dC.get()
+    exact = (A.T if tA else A).astype("f8") @ (B.T if tB else B).astype("f8")
+    # fp32 semantics: the error against float64 must be of the size of OpenBLAS's own fp32 error
+    scale = np.sqrt(K)
+    assert np.abs(got - exact).max() <= 4 * np.abs(want - exact).max() + 1e-5 * scale
+    np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-5 * scale)
+
+
+def test_sgemm_batched_and_dgemm(rt):
+    rs = np.random.RandomState(9)
+    A, B = rs.randn(2, 3, 5).astype("f4"), rs.randn(2, 5, 7).astype("f4")  # reference test_affine.py:364-375
+    want = O.batched_mul22(A, B)
+    dA, dB, dC = Dev(A), Dev(B), Dev(shape=(2, 3, 7), dtype="f4")
+    call("cgtb_sgemm_batched", 0, 0, 2, 3, 7, 5, dA.ptr, 5, 15, dB.ptr, 7, 35, dC.ptr, 7, 21, 0)
+    np.testing.assert_allclose(dC.get(), want, rtol=1e-4, atol=1e-5)
+    A, B = rs.randn(40, 30), rs.randn(50, 30)
+    dA, dB, dC = Dev(A), Dev(B), Dev(shape=(40, 50), dtype="f8")
+    call("cgtb_dgemm", 0, 1, 40, 50, 30, dA.ptr, 30, dB.ptr, 30, dC.ptr, 50)
+    np.testing.assert_allclose(dC.get(), A @ B.T, rtol=1e-12, atol=1e-12)
+
+
+def test_empty_inputs(rt):
+    d = Dev(shape=(1,), dtype="f4")
+    call("cgtb_unary", 3, code("f4"), code("f4"), 0, d.ptr, d.ptr)
+    call("cgtb_binary", 1, code("f4"), code("f4"), code("f4"), 0, d.ptr, d.ptr, d.ptr, 0, 0)
+    call("cgtb_fill", code("f4"), 0, ctypes.c_double(1.0), 0, d.ptr)
+    call("cgtb_im2col", code("f4"), d.ptr, 0, 3, 8, 8, 3, 3, 1, 1, 1, 1, d.ptr)
+    call("cgtb_sgemm", 0, 0, 0, 4, 4, d.ptr, 4, d.ptr, 4, d.ptr, 4, 0)
