@@ -113,7 +113,7 @@ def build_cifar(batch=128, seed=1, lr=0.005):
 # ------------------------------------------------------------------------------------------------
 # C5: wide conv stack (128 examples per GPU)
 # ------------------------------------------------------------------------------------------------
-def build_wide(batch=128, seed=1, lr=0.01):
+def build_wide(batch=128, seed=1, lr=0.0005):
     cgt = _cgt()
     X = cgt.tensor4("X", fixed_shape=(batch, 3, 64, 64))
     y = cgt.vector("y", dtype="i8", fixed_shape=(batch,))
@@ -145,7 +145,7 @@ def build_wide(batch=128, seed=1, lr=0.01):
 # ------------------------------------------------------------------------------------------------
 # C3: two-layer char-level LSTM, unrolled, with gradient clipping at a global norm
 # ------------------------------------------------------------------------------------------------
-def build_lstm(vocab=65, hidden=128, n_layers=2, seq_len=50, batch=64, seed=1, lr=0.01, clip=5.0):
+def build_lstm(vocab=65, hidden=128, n_layers=2, seq_len=50, batch=64, seed=1, lr=0.1, clip=5.0):
     cgt = _cgt()
     x_tnk = cgt.tensor3("x", fixed_shape=(seq_len, batch, vocab))
     targ_tnk = cgt.tensor3("targ", fixed_shape=(seq_len, batch, vocab))

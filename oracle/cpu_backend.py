@@ -118,7 +118,10 @@ class OracleFunction(object):
             i = op.info
             return O.max_pool(p[0], (i.kernel_h, i.kernel_w), (i.pad_h, i.pad_w), (i.stride_h, i.stride_w), impl=self._kimpl())
         if isinstance(op, pool_ops.MaxPoolPullback):
-            return O.max_pool_pullback(np.shape(p[0]), p[2], p[3], impl=self._kimpl())
+            # the reference's scatter writes out of bounds through a mask of -1 (an all-NaN window,
+            # include/pooling.h:96-97): such inputs only go to the guarded restatement
+            ok = bool((np.asarray(p[2]) >= 0).all())
+            return O.max_pool_pullback(np.shape(p[0]), p[2], p[3], impl=self._kimpl(ok))
         if isinstance(op, lrn_ops.CrossChannelLRNForward):
             i = op.info
             return O.lrn_forward(p[0], i.localsize, i.alpha, i.beta, impl=self._kimpl())

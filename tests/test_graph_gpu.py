@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 SMALL = {
     "mlp": dict(batch=128),
     "cifar": dict(batch=16),
-    "wide": dict(batch=4),
+    "wide": dict(batch=4, lr=0.0002),
     "lstm": dict(seq_len=6, batch=8),
     "vae": dict(batch=100),
 }

@@ -170,11 +170,11 @@ def test_binary(rt, op, dtx, dty, dto, mode, n):
 
     def draw(dt, size):
         if np.dtype(dt).kind == "f":
-            v = rs.randn(*size) * 2
+            v = np.asarray(rs.randn(*size) * 2)
             if op == "**":
                 v = np.abs(v) + 0.1
             return v.astype(dt)
-        v = rs.randint(-5, 6, size=size)
+        v = np.asarray(rs.randint(-5, 6, size=size))
         if op in ("/", "**"):
             v = np.abs(v) + 1
         return v.astype(dt)
