@@ -342,6 +342,19 @@ class MemCounter(object):
         return out
 
 
+def _static_shape(shp):
+    """tuple of ints when every extent is a compile-time constant, else None"""
+    if isinstance(shp, tuple):
+        parts = [_static_shape(s) for s in shp]
+        return None if any(p is None for p in parts) else tuple(parts)
+    out = []
+    for s in shp:
+        if not isinstance(s.op, core.Constant):
+            return None
+        out.append(int(s.op.value))
+    return tuple(out)
+
+
 def create_execution_graph(inputs, nodes_sorted, node2shape, node2memowner, node2dev, once_nodes=()):
     """Instruction list (cgt/compilation.py:204-248): Argument -> LoadArgument; byref tensor ->
     Alloc + ReturnByRef; byref tuple -> Alloc per component + BuildTup + ReturnByRef; byval ->
@@ -388,6 +401,11 @@ def create_execution_graph(inputs, nodes_sorted, node2shape, node2memowner, node
                 write_loc = counter.new_memloc(devtype)
                 instrs.append(ReturnByVal(node.op, [par.typ for par in node.parents], read_locs, write_loc,
                                           node_props=node.props, once=once))
+            # static shapes and dtypes, for profiling reports (algorithmic bytes per instruction)
+            instrs[-1].in_shapes = [_static_shape(node2shape[p]) if p in node2shape else None for p in node.parents]
+            instrs[-1].in_dtypes = [p.dtype for p in node.parents]
+            instrs[-1].out_shape = _static_shape(node2shape[node]) if node in node2shape else None
+            instrs[-1].out_dtype = node.dtype
         node2memloc[node] = write_loc
     return ExecutionGraph(instrs, len(inputs), counter.count), node2memloc
 

@@ -49,6 +49,14 @@ class _seeded(object):
         np.random.set_state(self.state)
 
 
+def _sgd(loss, params, lr, grad_hook):
+    """nn.sgd with an optional transformation of the gradient list (data-parallel averaging)."""
+    grads = _cgt().grad(loss, params)
+    if grad_hook is not None:
+        grads = grad_hook(grads)
+    return [(p, p - lr * g) for (p, g) in zip(params, grads)]
+
+
 def _softmax_ce(logits, y, batch):
     cgt = _cgt()
     logprobs = nn.logsoftmax(logits)
@@ -58,7 +66,7 @@ def _softmax_ce(logits, y, batch):
 # ------------------------------------------------------------------------------------------------
 # C1: MLP 784 -> 256 tanh -> 256 tanh -> 10 softmax
 # ------------------------------------------------------------------------------------------------
-def build_mlp(batch=128, seed=1, lr=0.1):
+def build_mlp(batch=128, seed=1, lr=0.1, grad_hook=None):
     cgt = _cgt()
     X = cgt.matrix("X", fixed_shape=(batch, 784))
     y = cgt.vector("y", dtype="i8", fixed_shape=(batch,))
@@ -70,7 +78,7 @@ def build_mlp(batch=128, seed=1, lr=0.1):
     h = cgt.tanh(l2(h))
     loss = _softmax_ce(l3(h), y, batch)
     params = nn.get_parameters(loss)
-    updates = nn.sgd(loss, params, lr)
+    updates = _sgd(loss, params, lr, grad_hook)
 
     def batch_fn(rs):
         return [rs.rand(batch, 784).astype("f4"), rs.randint(0, 10, size=batch).astype("i8")]
@@ -80,7 +88,7 @@ def build_mlp(batch=128, seed=1, lr=0.1):
 # ------------------------------------------------------------------------------------------------
 # C2: CIFAR-shape convnet (the headline configuration)
 # ------------------------------------------------------------------------------------------------
-def build_cifar(batch=128, seed=1, lr=0.005):
+def build_cifar(batch=128, seed=1, lr=0.005, grad_hook=None):
     cgt = _cgt()
     X = cgt.tensor4("X", fixed_shape=(batch, 3, 32, 32))
     y = cgt.vector("y", dtype="i8", fixed_shape=(batch,))
@@ -103,7 +111,7 @@ def build_cifar(batch=128, seed=1, lr=0.005):
         ip = nn.Affine(nfeats, 10, name="ip", weight_init=nn.HeNormal(scale=1.0))
     loss = _softmax_ce(ip(flat), y, batch)
     params = nn.get_parameters(loss)
-    updates = nn.sgd(loss, params, lr)
+    updates = _sgd(loss, params, lr, grad_hook)
 
     def batch_fn(rs):
         return [rs.randn(batch, 3, 32, 32).astype("f4"), rs.randint(0, 10, size=batch).astype("i8")]
@@ -113,7 +121,7 @@ def build_cifar(batch=128, seed=1, lr=0.005):
 # ------------------------------------------------------------------------------------------------
 # C5: wide conv stack (128 examples per GPU)
 # ------------------------------------------------------------------------------------------------
-def build_wide(batch=128, seed=1, lr=0.0005):
+def build_wide(batch=128, seed=1, lr=0.0005, grad_hook=None):
     cgt = _cgt()
     X = cgt.tensor4("X", fixed_shape=(batch, 3, 64, 64))
     y = cgt.vector("y", dtype="i8", fixed_shape=(batch,))
@@ -135,7 +143,7 @@ def build_wide(batch=128, seed=1, lr=0.0005):
     h = nn.rectify(fc1(flat))
     loss = _softmax_ce(fc2(h), y, batch)
     params = nn.get_parameters(loss)
-    updates = nn.sgd(loss, params, lr)
+    updates = _sgd(loss, params, lr, grad_hook)
 
     def batch_fn(rs):
         return [rs.randn(batch, 3, 64, 64).astype("f4"), rs.randint(0, 100, size=batch).astype("i8")]

@@ -1,7 +1,425 @@
-// placeholder until the tcgen05 kernel lands: reports "shape not supported" so the FMA kernel runs
+// Mul22 / BatchedMul22 on the 5th-generation tensor cores of sm_100a: tcgen05.mma kind::tf32 with the
+// accumulator in tensor memory (TMEM), fp32 semantics kept by the 3xTF32 split
+//     a*b ~= a_hi*b_hi + a_lo*b_hi + a_hi*b_lo,   x_hi = tf32(x), x_lo = tf32(x - x_hi)
+// (the dropped a_lo*b_lo term is below 2^-22 relative). Replaces cblas_sgemm / cublasSgemm_v2 in the
+// reference (cgt/core.py:2195-2222).
+//
+// Shape of the kernel
+//   * One CTA computes one 128 x UN output tile (UN a multiple of 16, at most 256) for one K slice.
+//     The operand with the larger output extent is put on the 128-row side ("X"), the other on the UN
+//     side ("Y"); when that is op(B), the tile is written back transposed, so skinny weight-gradient
+//     products (M = 32, K = 131072) still fill the 128 TMEM lanes.
+//   * Warps 0-3 load: global -> registers -> (hi, lo) split -> shared memory, written directly in the
+//     K-major, 128-byte-swizzled layout that the UMMA shared-memory descriptor describes. Going through
+//     registers is what makes the split free, lets any leading dimension and any of the four transpose
+//     combinations feed the same MMA configuration (a transposed source is transposed on the way in),
+//     and zero-fills ragged edges. Loads of a 32-deep K block are all issued before the first is used.
+//   * Warp 4: one thread issues the MMAs (12 per 32-deep K block: 4 K steps x 3 split terms) and
+//     commits them to the stage's "empty" mbarrier; the warp owns the TMEM allocation.
+//   * After the last K block the four loader warps become the epilogue: tcgen05.ld the accumulator
+//     (lane = tile row) and store to C, or to a split-K slab that a second kernel folds in split order.
+//   * Every mbarrier wait is bounded; on expiry the kernel raises a flag in host-mapped memory, skips
+//     the remaining work, still frees its TMEM and returns. The host reports the flag after the stream
+//     has been synchronised.
+//
+// Roofline: the configuration's products are skinny (N of 32..64 outputs per 75..800-long row), so
+// they are bound by streaming A from HBM, not by the tensor pipe: 4*(M*K + K*N + M*N) bytes per call.
 #include "runtime.h"
-namespace cgtb {
-int sgemm_tc(int, int, long, long, long, long, const float*, long, long, const float*, long, long, float*, long, long) {
-  return -1;
+
+using namespace cgtb;
+
+namespace {
+
+constexpr int kLoaderThreads = 128;
+constexpr int kThreads = 160;          // 4 loader/epilogue warps + 1 MMA warp
+constexpr int kBK = 32;                // K depth of one stage: 32 floats = one 128-byte swizzle row
+constexpr int kXRows = 128;            // UMMA M
+constexpr int kMaxStages = 4;
+constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr long long kWaitCycles = 2000000000LL;  // about one second of SM clock: far beyond any legitimate wait
+
+struct Operand {
+  const float* base;
+  long ld;        // stored row length
+  int kcontig;    // 1: element(row, k) = base[row*ld + k]; 0: element(row, k) = base[k*ld + row]
+  long rows;      // valid rows of this operand (M or N of the product)
+  long batch_stride;
+};
+
+struct Params {
+  Operand X, Y;
+  float* C;          // output or split-K slab
+  long ldc;          // row length of C in the product's own (m, n) orientation
+  long c_batch_stride;
+  int swapped;       // X is op(B): tile row i is product column n
+  long K;
+  long kchunk;       // K elements per split (multiple of kBK)
+  int nsplit;
+  long M, N;         // product extents, for the slab layout
+  int UN;            // tile columns
+  int stages;
+  int tmem_cols;
+  int* err;          // host-mapped error flag
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// bounded wait: false when the phase did not complete within the spin limit
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  const long long t0 = clock64();
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    if ((spin & 1023u) == 1023u && clock64() - t0 > kWaitCycles) return false;
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
+  float hf = __uint_as_float(hi);
+  if (!(fabsf(hf) <= 3.0e38f)) {             // x is inf/nan, or rounding overflowed
+    if (fabsf(x) <= 3.0e38f) { hi = __float_as_uint(x) & 0xffffe000u; hf = __uint_as_float(hi); }
+    else { lo = 0u; return; }
+  }
+  float r = x - hf;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(r));
+}
+
+// byte offset of element (row, k) inside a K-major tile with 128-byte rows and the 128B swizzle:
+// 16-byte chunk index XOR (row mod 8); 8-row groups are 1024 bytes apart
+__device__ __forceinline__ uint32_t tile_off(int row, int k) {
+  return (uint32_t)row * 128u + ((((uint32_t)k >> 2) ^ ((uint32_t)row & 7u)) << 4) + (((uint32_t)k & 3u) << 2);
+}
+
+// Load one operand tile (R rows x 32 k) for K block [k0, k0+32) clipped to k_end, split it and store
+// the hi / lo tiles. 128 threads cooperate.
+__device__ __forceinline__ void load_tile(const Operand& op, const float* base, long row0, int R, long k0, long k_end,
+                                          unsigned char* s_hi, unsigned char* s_lo, int tid) {
+  const int warp = tid >> 5, lane = tid & 31;
+  if (op.kcontig) {
+    // lanes along k: 128-byte coalesced row segments; each element lands in its own bank
+    const long k = k0 + lane;
+    const bool kin = k < k_end;
+    for (int r0 = warp; r0 < R; r0 += 32) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        int r = r0 + 4 * u;
+        long rg = row0 + r;
+        v[u] = (r < R && kin && rg < op.rows) ? __ldg(base + rg * op.ld + k) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        int r = r0 + 4 * u;
+        if (r < R) {
+          uint32_t hi, lo;
+          split_tf32(v[u], hi, lo);
+          uint32_t off = tile_off(r, lane);
+          *reinterpret_cast<uint32_t*>(s_hi + off) = hi;
+          *reinterpret_cast<uint32_t*>(s_lo + off) = lo;
+        }
+      }
+    }
+  } else {
+    // threads along rows: each k is a coalesced run of rows; a thread ends up holding a full 128-byte
+    // tile row and writes it as eight 16-byte chunks
+    for (int r = tid; r < R; r += kLoaderThreads) {
+      long rg = row0 + r;
+      const bool rin = rg < op.rows;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float v[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          long k = k0 + half * 16 + u;
+          v[u] = (rin && k < k_end) ? __ldg(base + k * op.ld + rg) : 0.f;
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint4 h, l;
+          split_tf32(v[4 * c + 0], h.x, l.x);
+          split_tf32(v[4 * c + 1], h.y, l.y);
+          split_tf32(v[4 * c + 2], h.z, l.z);
+          split_tf32(v[4 * c + 3], h.w, l.w);
+          uint32_t off = tile_off(r, half * 16 + 4 * c);
+          *reinterpret_cast<uint4*>(s_hi + off) = h;
+          *reinterpret_cast<uint4*>(s_lo + off) = l;
+        }
+      }
+    }
+  }
+}
+
+// shared-memory matrix descriptor: K-major, SWIZZLE_128B, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFFu);      // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                       // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                       // descriptor version for sm_100
+  d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads, 1) sgemm_tc_kernel(const Params p) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[kMaxStages];
+  __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
+  __shared__ __align__(8) uint64_t accum_bar;
+  __shared__ uint32_t tmem_base_slot;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int UN = p.UN, S = p.stages;
+  // tiles start on a 1024-byte boundary so that the swizzle pattern is anchored at offset 0
+  unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t x_bytes = kXRows * 128u, y_bytes = (uint32_t)UN * 128u;
+  const uint32_t stage_bytes = 2 * x_bytes + 2 * y_bytes;
+
+  const int batch = blockIdx.z / p.nsplit, split = blockIdx.z % p.nsplit;
+  const long x0 = (long)blockIdx.x * kXRows, y0 = (long)blockIdx.y * UN;
+  const long k_begin = (long)split * p.kchunk;
+  const long k_end = (k_begin + p.kchunk < p.K) ? k_begin + p.kchunk : p.K;
+  const int nkb = (int)((k_end - k_begin + kBK - 1) / kBK);
+  const float* xbase = p.X.base + batch * p.X.batch_stride;
+  const float* ybase = p.Y.base + batch * p.Y.batch_stride;
+
+  if (tid == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), kLoaderThreads);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    mbar_init(smem_u32(&accum_bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 4) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                 "r"((uint32_t)p.tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_d = tmem_base_slot;
+  bool ok = true;
+
+  if (warp < 4) {
+    // ------------------------------------------------ producers
+    for (int kb = 0; kb < nkb && ok; ++kb) {
+      const int s = kb % S;
+      const uint32_t phase = (uint32_t)(kb / S) & 1u;
+      ok = mbar_wait(smem_u32(&empty_bar[s]), phase ^ 1u);
+      if (!ok) break;
+      unsigned char* st = smem + (size_t)s * stage_bytes;
+      const long k0 = k_begin + (long)kb * kBK;
+      load_tile(p.X, xbase, x0, kXRows, k0, k_end, st, st + x_bytes, tid);
+      load_tile(p.Y, ybase, y0, UN, k0, k_end, st + 2 * x_bytes, st + 2 * x_bytes + y_bytes, tid);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core
+      mbar_arrive(smem_u32(&full_bar[s]));
+    }
+    // ------------------------------------------------ epilogue
+    if (ok && nkb > 0) ok = mbar_wait(smem_u32(&accum_bar), 0);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (!ok) {
+      if (lane == 0) { *(volatile int*)p.err = 1; __threadfence_system(); }
+    } else {
+      const long i_g = x0 + warp * 32 + lane;  // product row (or column, when swapped) held by this thread's TMEM lane
+      const bool i_in = i_g < p.X.rows;
+      float* cbase = (p.nsplit > 1) ? p.C + ((long)batch * p.nsplit + split) * p.M * p.N : p.C + batch * p.c_batch_stride;
+      const long ld = (p.nsplit > 1) ? p.N : p.ldc;
+      for (int c0 = 0; c0 < UN; c0 += 16) {
+        uint32_t r[16];
+        if (nkb > 0) {
+          uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
+          asm volatile(
+              "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+              : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+              : "r"(taddr)
+              : "memory");
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) r[j] = 0u;  // K == 0: the product is all zeros
+        }
+        if (i_in) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            long j_g = y0 + c0 + j;
+            if (j_g < p.Y.rows) {
+              long idx = p.swapped ? (j_g * ld + i_g) : (i_g * ld + j_g);
+              cbase[idx] = __uint_as_float(r[j]);
+            }
+          }
+        }
+      }
+    }
+  } else if (lane == 0) {
+    // ------------------------------------------------ MMA issuer (one thread)
+    // instruction descriptor: D fp32, A/B tf32, both K-major, N = UN, M = 128
+    const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(UN >> 3) << 17) | ((uint32_t)(kXRows >> 4) << 24);
+    for (int kb = 0; kb < nkb && ok; ++kb) {
+      const int s = kb % S;
+      const uint32_t phase = (uint32_t)(kb / S) & 1u;
+      ok = mbar_wait(smem_u32(&full_bar[s]), phase);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t sbase = smem_u32(smem + (size_t)s * stage_bytes);
+      const uint64_t dxh = make_desc(sbase), dxl = make_desc(sbase + x_bytes);
+      const uint64_t dyh = make_desc(sbase + 2 * x_bytes), dyl = make_desc(sbase + 2 * x_bytes + y_bytes);
+#pragma unroll
+      for (int kk = 0; kk < kBK / 8; ++kk) {
+        const uint64_t adv = (uint64_t)((kk * 32) >> 4);  // 8 tf32 = 32 bytes along K inside the swizzle row
+        const uint32_t first = (kb == 0 && kk == 0) ? 0u : 1u;
+        mma_tf32(tmem_d, dxl + adv, dyh + adv, idesc, first);  // small terms first
+        mma_tf32(tmem_d, dxh + adv, dyl + adv, idesc, 1u);
+        mma_tf32(tmem_d, dxh + adv, dyh + adv, idesc, 1u);
+      }
+      mma_commit(smem_u32(&empty_bar[s]));  // frees the stage once these MMAs have read it
+    }
+    if (ok && nkb > 0) mma_commit(smem_u32(&accum_bar));
+    if (!ok) { *(volatile int*)p.err = 2; __threadfence_system(); }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 4) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)p.tmem_cols) : "memory");
+  }
+}
+
+__global__ void splitk_fold_tc_kernel(long P, long MN, int nsplit, const float* __restrict__ part, float* __restrict__ C, long M,
+                                      long N, long ldc, long strideC) {
+  long total = P * MN;
+  for (long f = (long)blockIdx.x * blockDim.x + threadIdx.x; f < total; f += (long)gridDim.x * blockDim.x) {
+    long p = f / MN, e = f - p * MN;
+    long m = e / N, n = e - m * N;
+    const float* src = part + (p * nsplit) * MN + e;
+    float acc = src[0];
+    for (int s = 1; s < nsplit; ++s) acc += src[(long)s * MN];
+    C[p * strideC + m * ldc + n] = acc;
+  }
+}
+
+int* g_err_host = nullptr;  // host-mapped flag written by the kernel on a wait time-out
+int* g_err_dev = nullptr;
+
+}  // namespace
+
+namespace cgtb {
+
+// Reports (and clears) a time-out raised by the tensor-core kernel. Call after the stream is idle.
+int sgemm_tc_check() {
+  if (g_err_host && *g_err_host) {
+    int code = *g_err_host;
+    *g_err_host = 0;
+    return fail("tcgen05 GEMM: a bounded barrier wait expired (code %d); the result of that product is invalid", code);
+  }
+  return 0;
+}
+
+int sgemm_tc(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B, long ldb,
+             long strideB, float* C, long ldc, long strideC) {
+  if (P <= 0 || M <= 0 || N <= 0) return 0;
+  if (K <= 0) return -1;                      // all-zero product: the FMA kernel handles it
+  if (M * N < 1024 && K < 256) return -1;     // tiny: not worth a tensor-core launch
+  if (!g_err_host) {
+    if (cudaHostAlloc((void**)&g_err_host, sizeof(int), cudaHostAllocMapped) != cudaSuccess) return fail("cudaHostAlloc failed");
+    *g_err_host = 0;
+    if (cudaHostGetDevicePointer((void**)&g_err_dev, g_err_host, 0) != cudaSuccess) return fail("cudaHostGetDevicePointer failed");
+  }
+  Params p;
+  Operand opA = {A, lda, tA ? 0 : 1, M, strideA};   // rows of op(A) are m
+  Operand opB = {B, ldb, tB ? 1 : 0, N, strideB};   // rows of op(B)^T are n
+  p.swapped = (N > M) ? 1 : 0;
+  p.X = p.swapped ? opB : opA;
+  p.Y = p.swapped ? opA : opB;
+  long ydim = p.Y.rows;
+  int ytiles = (int)cgtb_ceil_div(ydim, 256);
+  int UN = (int)(cgtb_ceil_div(cgtb_ceil_div(ydim, ytiles), 16) * 16);
+  if (UN < 16) UN = 16;
+  ytiles = (int)cgtb_ceil_div(ydim, UN);
+  long xtiles = cgtb_ceil_div(p.X.rows, kXRows);
+  p.UN = UN;
+  p.tmem_cols = 32;
+  while (p.tmem_cols < UN) p.tmem_cols *= 2;
+  const long stage_bytes = 2L * kXRows * 128 + 2L * UN * 128;
+  long nkb_total = cgtb_ceil_div(K, kBK);
+  // split K when the output tiles alone cannot fill the machine
+  long tiles = xtiles * ytiles * P;
+  int nsplit = 1;
+  long want = (long)rt().sm_count;
+  if (tiles < want && nkb_total >= 8) {
+    nsplit = (int)std::min<long>(cgtb_ceil_div(2 * want, tiles), nkb_total / 4);
+    if (nsplit < 1) nsplit = 1;
+  }
+  long kchunk = cgtb_ceil_div(nkb_total, nsplit) * kBK;
+  nsplit = (int)cgtb_ceil_div(K, kchunk);
+  if ((long)P * nsplit > 65535 || ytiles > 65535) return -1;
+  p.nsplit = nsplit;
+  p.kchunk = kchunk;
+  p.K = K;
+  p.M = M;
+  p.N = N;
+  long nkb = kchunk / kBK;
+  int stages = nkb >= 3 ? 3 : (int)std::max<long>(nkb, 1);
+  while (stages > 1 && stages * stage_bytes + 1024 > 200 * 1024) --stages;
+  // two CTAs per SM hide the load latency of short K loops: keep the footprint under half the SM when cheap
+  if (stages * stage_bytes + 1024 > 100 * 1024 && nkb <= 4 && stages > 2) stages = 2;
+  p.stages = stages;
+  p.ldc = ldc;
+  p.c_batch_stride = strideC;
+  p.err = g_err_dev;
+  float* part = nullptr;
+  if (nsplit > 1) {
+    part = (float*)scratch((size_t)P * nsplit * M * N * sizeof(float));
+    if (!part) return 1;
+    p.C = part;
+  } else {
+    p.C = C;
+  }
+  size_t smem = (size_t)stages * stage_bytes + 1024;
+  static size_t smem_configured = 0;
+  if (smem > smem_configured) {
+    CGTB_CUDA_TRY(cudaFuncSetAttribute(sgemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048));
+    smem_configured = 227 * 1024;
+  }
+  dim3 grid((unsigned)xtiles, (unsigned)ytiles, (unsigned)(P * nsplit));
+  CGTB_LAUNCH(sgemm_tc_kernel, grid, kThreads, smem, p);
+  if (nsplit > 1) {
+    long total = P * M * N;
+    long blocks = std::min<long>(cgtb_ceil_div(total, 256), (long)rt().sm_count * 8);
+    CGTB_LAUNCH(splitk_fold_tc_kernel, (unsigned)blocks, 256, 0, P, M * N, nsplit, part, C, M, N, ldc, strideC);
+  }
+  CGTB_CHECK_LAUNCH("sgemm_tc");
+  return 0;
+}
+
 }  // namespace cgtb

@@ -169,6 +169,40 @@ CGTB_API int cgtb_graph_add_return_byval(cgtbGraph* g, const char* repr, int n, 
 // ------------------------------------------------------------------------------------------------
 // interpreter
 // ------------------------------------------------------------------------------------------------
+// Cut the instruction list into spans at every barrier instruction. A fire-once barrier (a constant's
+// transport) that has already fired no longer separates its neighbours, so after the first run the
+// whole step usually collapses into one span per real transfer.
+static void build_spans(cgtbInterp* it) {
+  for (auto& s : it->spans)
+    if (s.exec) cudaGraphExecDestroy(s.exec);
+  it->spans.clear();
+  auto& instrs = it->g->instrs;
+  int n = (int)instrs.size();
+  auto is_barrier = [&](int k) {
+    Instr& in = instrs[(size_t)k];
+    return in.klass == kBarrier && !((in.flags & CGTB_INSTR_ONCE) && in.fired);
+  };
+  int i = 0;
+  while (i < n) {
+    Span s;
+    s.begin = i;
+    if (is_barrier(i)) {
+      s.barrier = true;
+      s.end = i + 1;
+    } else {
+      int j = i;
+      while (j < n && !is_barrier(j)) {
+        if (instrs[(size_t)j].klass == kDevice) s.n_device++;
+        if (instrs[(size_t)j].klass == kHostData) s.has_hostdata = true;
+        ++j;
+      }
+      s.end = j;
+    }
+    it->spans.push_back(s);
+    i = s.end;
+  }
+}
+
 CGTB_API cgtbInterp* cgtb_interp_new(cgtbGraph* g, int n_out, const long* out_locs, int flags) {
   if (!g) { fail("cgtb_interp_new: null graph"); return nullptr; }
   cgtbInterp* it = new cgtbInterp();
@@ -190,27 +224,7 @@ CGTB_API cgtbInterp* cgtb_interp_new(cgtbGraph* g, int n_out, const long* out_lo
     for (auto& r : in.reads) if (r.dev == cgtbGPU) any_device = true;
   }
   if (any_device && !require_runtime("cgtb_interp_new")) { delete it; return nullptr; }
-  // cut into spans
-  int n = (int)g->instrs.size();
-  int i = 0;
-  while (i < n) {
-    Span s;
-    s.begin = i;
-    if (g->instrs[i].klass == kBarrier) {
-      s.barrier = true;
-      s.end = i + 1;
-    } else {
-      int j = i;
-      while (j < n && g->instrs[j].klass != kBarrier) {
-        if (g->instrs[j].klass == kDevice) s.n_device++;
-        if (g->instrs[j].klass == kHostData) s.has_hostdata = true;
-        ++j;
-      }
-      s.end = j;
-    }
-    it->spans.push_back(s);
-    i = s.end;
-  }
+  build_spans(it);
   return it;
 }
 
@@ -464,9 +478,11 @@ CGTB_API int cgtb_interp_run(cgtbInterp* it, cgtbObject* args_obj, cgtbObject** 
     cudaError_t e = cudaStreamSynchronize(rt().stream);
     it->host_pending = false;
     if (e != cudaSuccess && !rc) rc = fail("device work of this run failed: %s", cudaGetErrorString(e));
+    if (!rc) rc = sgemm_tc_check();
   }
   it->prev_run_allocated = device_malloc_count() != mallocs0;
   it->runs += 1;
+  if (it->runs == 1 && !rc) build_spans(it);  // fire-once barriers are out of the way now
   if (rc) return rc;
   cgtTuple* o = new cgtTuple((int)it->outs.size());
   o->Retain();

@@ -554,15 +554,19 @@ CGTB_API int cgtb_getflat(int dtype, long n, const void* x, const int64_t* k, vo
 // Implemented as: the FIRST occurrence of each index owns the whole ordered sum for that index.
 template <typename T>
 __global__ void incflat_kernel(long n, const int64_t* __restrict__ k, const T* __restrict__ p, T* __restrict__ out) {
+  extern __shared__ __align__(16) unsigned char incflat_smem[];
+  int64_t* ks = reinterpret_cast<int64_t*>(incflat_smem);  // the whole index list, staged once per block
+  for (long j = threadIdx.x; j < n; j += blockDim.x) ks[j] = k[j];
+  __syncthreads();
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
-    int64_t me = k[i];
+    int64_t me = ks[i];
     bool first = true;
     for (long j = 0; j < i; ++j)
-      if (k[j] == me) { first = false; break; }
+      if (ks[j] == me) { first = false; break; }
     if (!first) continue;
     T acc = out[me];
     for (long j = i; j < n; ++j)
-      if (k[j] == me) acc += p[j];
+      if (ks[j] == me) acc += p[j];
     out[me] = acc;
   }
 }
@@ -579,8 +583,8 @@ template <> struct has_atomic<int32_t> { static const bool value = true; };
 template <typename T>
 static int incflat_launch(long n, const int64_t* k, const T* p, T* out) {
   if (n <= 4096 || !has_atomic<T>::value) {
-    if (n > 65536) return fail("cgtb_incflat: %ld indices of a dtype without atomicAdd", n);
-    CGTB_LAUNCH(incflat_kernel<T>, flat_grid(n), 256, 0, n, k, p, out);
+    if (n > 4096) return fail("cgtb_incflat: %ld indices of a dtype without atomicAdd", n);
+    CGTB_LAUNCH(incflat_kernel<T>, flat_grid(n), 256, (size_t)n * sizeof(int64_t), n, k, p, out);
   } else {
     if constexpr (has_atomic<T>::value) CGTB_LAUNCH(incflat_atomic_kernel<T>, flat_grid(n), 256, 0, n, k, p, out);
   }

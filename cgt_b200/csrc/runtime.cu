@@ -213,7 +213,7 @@ CGTB_API void cgtb_clear_error(void) { t_err.clear(); t_status = cgtStatusOK; }
 CGTB_API int cgtb_synchronize(void) {
   if (!require_runtime("cgtb_synchronize")) return 1;
   CGTB_CUDA_TRY(cudaStreamSynchronize(g_rt.stream));
-  return 0;
+  return sgemm_tc_check();
 }
 CGTB_API void* cgtb_stream(void) { return (void*)g_rt.stream; }
 CGTB_API int cgtb_pool_stats(long* reserved, long* in_use, long* high, long* n_mallocs) {
@@ -396,3 +396,31 @@ CGTB_API int cgtb_tuple_set(cgtbObject* o, int i, cgtbObject* v) {
 CGTB_API int cgtb_object_kind(cgtbObject* o) { return (int)((cgtObject*)o)->kind(); }
 CGTB_API void cgtb_retain(cgtbObject* o) { if (o) ((cgtObject*)o)->Retain(); }
 CGTB_API void cgtb_release(cgtbObject* o) { if (o) ((cgtObject*)o)->Release(); }
+
+// ================================================================== C ABI: timing helpers
+CGTB_API void* cgtb_event_new(void) {
+  if (!require_runtime("cgtb_event_new")) return nullptr;
+  cudaEvent_t e = nullptr;
+  if (cudaEventCreate(&e) != cudaSuccess) { fail("cudaEventCreate failed"); return nullptr; }
+  return (void*)e;
+}
+CGTB_API int cgtb_event_record(void* e) {
+  if (!require_runtime("cgtb_event_record")) return 1;
+  CGTB_CUDA_TRY(cudaEventRecord((cudaEvent_t)e, g_rt.stream));
+  return 0;
+}
+CGTB_API int cgtb_event_elapsed_ms(void* e0, void* e1, float* ms) {
+  CGTB_CUDA_TRY(cudaEventSynchronize((cudaEvent_t)e1));
+  CGTB_CUDA_TRY(cudaEventElapsedTime(ms, (cudaEvent_t)e0, (cudaEvent_t)e1));
+  return 0;
+}
+CGTB_API void cgtb_event_free(void* e) { if (e) cudaEventDestroy((cudaEvent_t)e); }
+// overwrite a buffer larger than L2 (126 MB on B200) so that the next kernels start from a cold L2
+CGTB_API int cgtb_l2_flush(void) {
+  if (!require_runtime("cgtb_l2_flush")) return 1;
+  static void* buf = nullptr;
+  static const size_t kBytes = (size_t)256 << 20;
+  if (!buf) CGTB_CUDA_TRY(cudaMalloc(&buf, kBytes));
+  CGTB_CUDA_TRY(cudaMemsetAsync(buf, 0, kBytes, g_rt.stream));
+  return 0;
+}

@@ -43,6 +43,9 @@ long device_malloc_count();
 
 int fail(const char* fmt, ...);  // records the message, returns 1
 
+// non-zero (with a recorded message) when the tensor-core GEMM raised its time-out flag; call on an idle stream
+int sgemm_tc_check();
+
 }  // namespace cgtb
 
 #define CGTB_CUDA_TRY(expr)                                                                      \

@@ -1,0 +1,171 @@
+"""Minibatch-sharded data parallelism: one process per GPU, identical graph and parameters on every
+rank, each rank's gradients summed across ranks by an ``AllReduce`` Op placed between ``cgt.grad``'s
+outputs and the update expressions.
+
+The reference has no multi-device collective; its documented data parallelism splits the batch
+across CPU threads inside one graph (doc/index.rst:212-238). Here the batch is split across
+processes. ``torch.distributed`` (gloo) carries the rendezvous, the NCCL unique id and barriers; the
+gradient bytes move through NCCL over NVLink, queued on the runtime's CUDA stream by the Op's
+native callable.
+"""
+import ctypes
+import os
+import os.path as osp
+
+import numpy as np
+
+from . import core
+
+_state = {"world": 1, "rank": 0, "local_rank": 0, "comm": False}
+
+
+def world_size():
+    return _state["world"]
+
+
+def rank():
+    return _state["rank"]
+
+
+def _find_nccl():
+    cands = []
+    try:
+        import torch
+        base = osp.dirname(osp.dirname(torch.__file__))
+        cands.append(osp.join(base, "nvidia", "nccl", "lib", "libnccl.so.2"))
+    except ImportError:
+        pass
+    cands += ["/usr/lib/x86_64-linux-gnu/libnccl.so.2"]
+    for c in cands:
+        if osp.exists(c):
+            return c
+    raise RuntimeError("no NCCL library found (looked in %s)" % cands)
+
+
+def init_process_group(with_gpu=True):
+    """Join the job described by RANK / WORLD_SIZE / LOCAL_RANK / MASTER_ADDR / MASTER_PORT.
+
+    with_gpu=False sets up only the host-side group (gloo); the AllReduce Op can then be evaluated by
+    the CPU oracle, which is how the multi-rank logic is tested without GPUs."""
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rk = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", str(rk)))
+    _state.update(world=world, rank=rk, local_rank=local)
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group(backend="gloo", rank=rk, world_size=world)
+    if with_gpu:
+        from . import runtime
+        core.update_config(device_index=local, default_device=core.Device("gpu", local))
+        runtime.ensure_init(local)
+        if world > 1 and not _state["comm"]:
+            L = runtime.lib()
+            runtime.check(L.cgtb_comm_load(_find_nccl().encode()), "loading NCCL")
+            idbuf = ctypes.create_string_buffer(128)
+            if rk == 0:
+                runtime.check(L.cgtb_comm_unique_id(idbuf), "ncclGetUniqueId")
+            box = [bytes(idbuf.raw)]
+            dist.broadcast_object_list(box, src=0)
+            runtime.check(L.cgtb_comm_init(box[0], rk, world), "ncclCommInitRank")
+            _state["comm"] = True
+    return rk, world
+
+
+def barrier():
+    if _state["world"] > 1:
+        import torch.distributed as dist
+        dist.barrier()
+
+
+def all_max(value):
+    """max over ranks of a host float (timing reduction)"""
+    if _state["world"] == 1:
+        return float(value)
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor([float(value)], dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def check_health():
+    """Raises when NCCL has reported an asynchronous error (a peer died or a link failed)."""
+    if _state["comm"]:
+        from . import runtime
+        runtime.check(runtime.lib().cgtb_comm_check(), "communicator")
+
+
+def shutdown():
+    if _state["comm"]:
+        from . import runtime
+        runtime.lib().cgtb_comm_destroy()
+        _state["comm"] = False
+    try:
+        import torch.distributed as dist
+        if dist.is_initialized():
+            dist.destroy_process_group()
+    except ImportError:
+        pass
+    _state.update(world=1, rank=0)
+
+
+class AllReduce(core.Op):
+    """(g_1, ..., g_k) -> tuple of their sums over all ranks. All k reductions are queued as one group."""
+    available_impls = ("native_gpu",)
+
+    def __init__(self, n):
+        self.n = n
+
+    def get_diff(self, n):
+        return [False] * n
+
+    def typ_apply(self, input_types):
+        return core.TupleType(*input_types)
+
+    def shp_apply(self, inputs):
+        return tuple(core.cgt.shape(x) for x in inputs)
+
+    def get_native_compile_info(self, input_types, devtype):
+        from . import runtime
+        # stream-ordered, but issued outside captured CUDA graphs (same class as a Transport)
+        return core.NativeCompileInfo(None, prebuilt="cgtb_op_allreduce", closure_triples=[("n", ctypes.c_int, self.n)],
+                                      flags=runtime.INSTR_TRANSPORT)
+
+    def oracle_eval(self, vals):
+        """Host evaluation for the test oracle: torch.distributed (gloo) all_reduce on copies."""
+        if _state["world"] == 1:
+            return tuple(np.array(v, copy=True) for v in vals)
+        import torch
+        import torch.distributed as dist
+        out = []
+        for v in vals:
+            t = torch.from_numpy(np.array(v, copy=True))
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)
+            out.append(t.numpy())
+        return tuple(out)
+
+    def __repr__(self):
+        return "AllReduce{%d}" % self.n
+
+
+def allreduce_mean(grads):
+    """Average a list of gradient nodes over the ranks; the identity when there is one rank."""
+    grads = list(grads)
+    w = world_size()
+    if w == 1:
+        return grads
+    tup = core.Result(AllReduce(len(grads)), grads)
+    inv = np.array(1.0 / w, core.cgt.floatX)
+    return [tup[i] * inv for i in range(len(grads))]
+
+
+def shard(arrays, rank_=None, world=None):
+    """This rank's slice of a global batch along axis 0."""
+    rank_ = rank() if rank_ is None else rank_
+    world = world_size() if world is None else world
+    out = []
+    for a in arrays:
+        n = a.shape[0] // world
+        out.append(np.ascontiguousarray(a[rank_ * n:(rank_ + 1) * n]))
+    return out

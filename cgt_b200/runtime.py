@@ -40,6 +40,13 @@ def _declare(lib):
         "cgtb_last_error": (ctypes.c_char_p, []), "cgtb_clear_error": (None, []), "cgtb_synchronize": (ci, []),
         "cgtb_stream": (vp, []), "cgtb_pool_stats": (ci, [c_long_p] * 4), "cgtb_pool_trim": (ci, []),
         "cgtb_kernel_launches": (cl, []), "cgtb_sm_count": (ci, []),
+        "cgtb_event_new": (vp, []), "cgtb_event_record": (ci, [vp]),
+        "cgtb_event_elapsed_ms": (ci, [vp, vp, ctypes.POINTER(ctypes.c_float)]), "cgtb_event_free": (None, [vp]),
+        "cgtb_l2_flush": (ci, []),
+        "cgtb_comm_load": (ci, [ctypes.c_char_p]), "cgtb_comm_unique_id": (ci, [ctypes.c_char_p]),
+        "cgtb_comm_init": (ci, [ctypes.c_char_p, ci, ci]), "cgtb_comm_world": (ci, []), "cgtb_comm_rank": (ci, []),
+        "cgtb_comm_check": (ci, []), "cgtb_comm_abort": (ci, []), "cgtb_comm_destroy": (ci, []),
+        "cgtb_allreduce_sum": (ci, [ci, ci, ctypes.POINTER(vp), ctypes.POINTER(vp), c_long_p]),
         "cgtb_alloc": (vp, [ci, cl]), "cgtb_free": (None, [ci, vp]), "cgtb_memcpy": (ci, [ci, ci, vp, vp, cl, ci]),
         "cgtb_memset": (ci, [vp, ci, cl]),
         "cgtb_array_new": (vp, [ci, c_long_p, ci, ci]), "cgtb_array_from_host": (vp, [ci, c_long_p, ci, ci, vp, ci]),
@@ -148,6 +155,35 @@ def pool_stats():
     vals = [ctypes.c_long(0) for _ in range(4)]
     lib().cgtb_pool_stats(*[ctypes.byref(v) for v in vals])
     return dict(zip(("reserved_bytes", "in_use_bytes", "high_water_bytes", "n_device_mallocs"), [v.value for v in vals]))
+
+
+class Event(object):
+    """CUDA event on the runtime stream."""
+
+    def __init__(self):
+        ensure_init()
+        self.h = lib().cgtb_event_new()
+        if not self.h:
+            raise BackendError(last_error())
+
+    def record(self):
+        check(lib().cgtb_event_record(self.h), "event record")
+
+    def elapsed_ms(self, later):
+        ms = ctypes.c_float(0)
+        check(lib().cgtb_event_elapsed_ms(self.h, later.h, ctypes.byref(ms)), "event elapsed")
+        return float(ms.value)
+
+    def __del__(self):
+        try:
+            if _lib is not None and self.h:
+                _lib.cgtb_event_free(self.h)
+        except Exception:
+            pass
+
+
+def l2_flush():
+    check(lib().cgtb_l2_flush(), "l2 flush")
 
 
 def _shape_arg(shape):

@@ -36,6 +36,13 @@ int cgtb_pool_trim(void);                  /* return cached blocks to the driver
 long cgtb_kernel_launches(void);           /* kernels launched by this library since load */
 int cgtb_sm_count(void);
 
+/* Timing on the runtime stream (CUDA events) and an L2 flush for benchmarks. */
+void* cgtb_event_new(void);
+int cgtb_event_record(void* event);
+int cgtb_event_elapsed_ms(void* start, void* stop, float* ms); /* waits for `stop` */
+void cgtb_event_free(void* event);
+int cgtb_l2_flush(void);                   /* memset of a 256 MiB device buffer */
+
 /* Raw memory. devtype: 0 host (pinned), 1 device. (src/cgt_common.cpp:110-153) */
 void* cgtb_alloc(int devtype, long nbytes);
 void cgtb_free(int devtype, void* p);
@@ -159,6 +166,22 @@ int cgtb_getflat(int dtype, long n, const void* x, const int64_t* k, void* out);
 int cgtb_incflat(int dtype, long xsize, long n, const void* x, const int64_t* k, const void* p, void* out);
 int cgtb_concat_part(int dtype, long outer, long n_in, long n_out, long inner, long pos, const void* in, void* out);
 int cgtb_fill(int dtype, long n, double fvalue, long ivalue, void* out);
+
+/* ------------------------------------------------------------------------------------------------
+ * Data-parallel gradient exchange (no counterpart in the reference, which has no collectives).
+ * One process per GPU. NCCL is opened at run time from `nccl_path`; rank 0 creates the 128-byte id and
+ * the host side distributes it before every rank calls cgtb_comm_init.
+ * ---------------------------------------------------------------------------------------------- */
+int cgtb_comm_load(const char* nccl_path);
+int cgtb_comm_unique_id(char* out128);
+int cgtb_comm_init(const char* id128, int rank, int world);
+int cgtb_comm_world(void);
+int cgtb_comm_rank(void);
+int cgtb_comm_check(void);   /* non-zero when NCCL reported an asynchronous error */
+int cgtb_comm_abort(void);
+int cgtb_comm_destroy(void);
+/* out[i] = sum over ranks of in[i] for n float buffers, one NCCL group on the runtime stream */
+int cgtb_allreduce_sum(int dtype, int n, const void* const* in, void* const* out, const long* counts);
 
 #ifdef __cplusplus
 }
