@@ -9,15 +9,16 @@
 //     The operand with the larger output extent is put on the 128-row side ("X"), the other on the UN
 //     side ("Y"); when that is op(B), the tile is written back transposed, so skinny weight-gradient
 //     products (M = 32, K = 131072) still fill the 128 TMEM lanes.
-//   * Warps 0-3 load: global -> registers -> (hi, lo) split -> shared memory, written directly in the
+//   * Warps 0-7 load: global -> registers -> (hi, lo) split -> shared memory, written directly in the
 //     K-major, 128-byte-swizzled layout that the UMMA shared-memory descriptor describes. Going through
 //     registers is what makes the split free, lets any leading dimension and any of the four transpose
 //     combinations feed the same MMA configuration (a transposed source is transposed on the way in),
-//     and zero-fills ragged edges. Loads of a 32-deep K block are all issued before the first is used.
-//   * Warp 4: one thread issues the MMAs (12 per 32-deep K block: 4 K steps x 3 split terms) and
+//     and zero-fills ragged edges. The loads of K block kb+1 are issued before block kb is split and
+//     stored, so global-memory latency overlaps the conversion work.
+//   * Warp 8: one thread issues the MMAs (12 per 32-deep K block: 4 K steps x 3 split terms) and
 //     commits them to the stage's "empty" mbarrier; the warp owns the TMEM allocation.
-//   * After the last K block the four loader warps become the epilogue: tcgen05.ld the accumulator
-//     (lane = tile row) and store to C, or to a split-K slab that a second kernel folds in split order.
+//   * After the last K block the eight loader warps become the epilogue: tcgen05.ld the accumulator
+//     (lane = tile row; the two warps of a lane quarter take alternate 16-column chunks) and store to C, or to a split-K slab that a second kernel folds in split order.
 //   * Every mbarrier wait is bounded; on expiry the kernel raises a flag in host-mapped memory, skips
 //     the remaining work, still frees its TMEM and returns. The host reports the flag after the stream
 //     has been synchronised.
@@ -30,8 +31,9 @@ using namespace cgtb;
 
 namespace {
 
-constexpr int kLoaderThreads = 128;
-constexpr int kThreads = 160;          // 4 loader/epilogue warps + 1 MMA warp
+constexpr int kLoaderWarps = 8;
+constexpr int kLoaderThreads = kLoaderWarps * 32;
+constexpr int kThreads = kLoaderThreads + 32;  // 8 loader/epilogue warps + 1 MMA warp
 constexpr int kBK = 32;                // K depth of one stage: 32 floats = one 128-byte swizzle row
 constexpr int kXRows = 128;            // UMMA M
 constexpr int kMaxStages = 4;
@@ -42,6 +44,7 @@ struct Operand {
   const float* base;
   long ld;        // stored row length
   int kcontig;    // 1: element(row, k) = base[row*ld + k]; 0: element(row, k) = base[k*ld + row]
+  int mode;       // loader access pattern (see fetch_tile): 0 rows contiguous, 1 K contiguous, 2 K contiguous + 16-byte aligned
   long rows;      // valid rows of this operand (M or N of the product)
   long batch_stride;
 };
@@ -105,57 +108,108 @@ __device__ __forceinline__ uint32_t tile_off(int row, int k) {
   return (uint32_t)row * 128u + ((((uint32_t)k >> 2) ^ ((uint32_t)row & 7u)) << 4) + (((uint32_t)k & 3u) << 2);
 }
 
-// Load one operand tile (R rows x 32 k) for K block [k0, k0+32) clipped to k_end, split it and store
-// the hi / lo tiles. 128 threads cooperate.
-__device__ __forceinline__ void load_tile(const Operand& op, const float* base, long row0, int R, long k0, long k_end,
-                                          unsigned char* s_hi, unsigned char* s_lo, int tid) {
+// Operand tiles travel global -> registers -> shared memory in two steps so that the loads of K block
+// kb+1 are in flight while block kb is split and stored. Three access patterns, chosen per operand:
+//   mode 0  rows contiguous in memory (a transposed source): threads along rows, 16 k per thread;
+//   mode 1  K contiguous: lanes along k, one 128-byte row segment per warp instruction;
+//   mode 2  K contiguous and 16-byte aligned: 128-bit loads, 8 lanes per row.
+// NV is the number of register slots a thread owns for the tile: 16 for the 128-row X tile, up to 32
+// for a 256-row Y tile; slots beyond the tile are predicated off.
+template <int NV>
+__device__ __forceinline__ void fetch_tile(const Operand& op, int mode, const float* base, long row0, int R, long k0, long k_end,
+                                           float (&v)[NV], int tid) {
   const int warp = tid >> 5, lane = tid & 31;
-  if (op.kcontig) {
-    // lanes along k: 128-byte coalesced row segments; each element lands in its own bank
+  if (mode == 1) {
     const long k = k0 + lane;
     const bool kin = k < k_end;
-    for (int r0 = warp; r0 < R; r0 += 32) {
-      float v[8];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        int r = r0 + 4 * u;
-        long rg = row0 + r;
-        v[u] = (r < R && kin && rg < op.rows) ? __ldg(base + rg * op.ld + k) : 0.f;
-      }
+    for (int u = 0; u < NV; ++u) {
+      int r = warp + kLoaderWarps * u;
+      long rg = row0 + r;
+      v[u] = (r < R && kin && rg < op.rows) ? __ldg(base + rg * op.ld + k) : 0.f;
+    }
+  } else if (mode == 2) {
+    const int sub = lane >> 3, c = lane & 7;  // 4 rows per warp instruction, 8 chunks of 4 floats per row
+    const long k = k0 + 4 * c;
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        int r = r0 + 4 * u;
-        if (r < R) {
-          uint32_t hi, lo;
-          split_tf32(v[u], hi, lo);
-          uint32_t off = tile_off(r, lane);
-          *reinterpret_cast<uint32_t*>(s_hi + off) = hi;
-          *reinterpret_cast<uint32_t*>(s_lo + off) = lo;
+    for (int u = 0; u < NV / 4; ++u) {
+      int r = (warp * 4 + sub) + (kLoaderWarps * 4) * u;
+      long rg = row0 + r;
+      float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (r < R && rg < op.rows) {
+        if (k + 3 < k_end) {
+          q = __ldg(reinterpret_cast<const float4*>(base + rg * op.ld + k));
+        } else {  // ragged end of K: element-wise
+          const float* src = base + rg * op.ld;
+          if (k + 0 < k_end) q.x = __ldg(src + k + 0);
+          if (k + 1 < k_end) q.y = __ldg(src + k + 1);
+          if (k + 2 < k_end) q.z = __ldg(src + k + 2);
         }
+      }
+      v[4 * u + 0] = q.x; v[4 * u + 1] = q.y; v[4 * u + 2] = q.z; v[4 * u + 3] = q.w;
+    }
+  } else {
+    // pair index q -> (row = q % R, khalf = q / R); a thread owns pairs tid, tid + 256, ...
+#pragma unroll
+    for (int pr = 0; pr < NV / 16; ++pr) {
+      int q = tid + kLoaderThreads * pr;
+      int khalf = q / R, r = q - khalf * R;
+      long rg = row0 + r;
+      const bool rin = khalf < 2 && rg < op.rows;
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        long k = k0 + khalf * 16 + u;
+        v[16 * pr + u] = (rin && k < k_end) ? __ldg(base + k * op.ld + rg) : 0.f;
+      }
+    }
+  }
+}
+
+template <int NV>
+__device__ __forceinline__ void stash_tile(int mode, int R, const float (&v)[NV], unsigned char* s_hi, unsigned char* s_lo, int tid) {
+  const int warp = tid >> 5, lane = tid & 31;
+  if (mode == 1) {
+#pragma unroll
+    for (int u = 0; u < NV; ++u) {
+      int r = warp + kLoaderWarps * u;
+      if (r < R) {
+        uint32_t hi, lo;
+        split_tf32(v[u], hi, lo);
+        uint32_t off = tile_off(r, lane);  // 32 lanes -> 32 distinct banks
+        *reinterpret_cast<uint32_t*>(s_hi + off) = hi;
+        *reinterpret_cast<uint32_t*>(s_lo + off) = lo;
+      }
+    }
+  } else if (mode == 2) {
+    const int sub = lane >> 3, c = lane & 7;
+#pragma unroll
+    for (int u = 0; u < NV / 4; ++u) {
+      int r = (warp * 4 + sub) + (kLoaderWarps * 4) * u;
+      if (r < R) {
+        uint4 h, l;
+        split_tf32(v[4 * u + 0], h.x, l.x);
+        split_tf32(v[4 * u + 1], h.y, l.y);
+        split_tf32(v[4 * u + 2], h.z, l.z);
+        split_tf32(v[4 * u + 3], h.w, l.w);
+        uint32_t off = tile_off(r, 4 * c);
+        *reinterpret_cast<uint4*>(s_hi + off) = h;
+        *reinterpret_cast<uint4*>(s_lo + off) = l;
       }
     }
   } else {
-    // threads along rows: each k is a coalesced run of rows; a thread ends up holding a full 128-byte
-    // tile row and writes it as eight 16-byte chunks
-    for (int r = tid; r < R; r += kLoaderThreads) {
-      long rg = row0 + r;
-      const bool rin = rg < op.rows;
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        float v[16];
-#pragma unroll
-        for (int u = 0; u < 16; ++u) {
-          long k = k0 + half * 16 + u;
-          v[u] = (rin && k < k_end) ? __ldg(base + k * op.ld + rg) : 0.f;
-        }
+    for (int pr = 0; pr < NV / 16; ++pr) {
+      int q = tid + kLoaderThreads * pr;
+      int khalf = q / R, r = q - khalf * R;
+      if (khalf < 2) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint4 h, l;
-          split_tf32(v[4 * c + 0], h.x, l.x);
-          split_tf32(v[4 * c + 1], h.y, l.y);
-          split_tf32(v[4 * c + 2], h.z, l.z);
-          split_tf32(v[4 * c + 3], h.w, l.w);
-          uint32_t off = tile_off(r, half * 16 + 4 * c);
+          split_tf32(v[16 * pr + 4 * c + 0], h.x, l.x);
+          split_tf32(v[16 * pr + 4 * c + 1], h.y, l.y);
+          split_tf32(v[16 * pr + 4 * c + 2], h.z, l.z);
+          split_tf32(v[16 * pr + 4 * c + 3], h.w, l.w);
+          uint32_t off = tile_off(r, khalf * 16 + 4 * c);
           *reinterpret_cast<uint4*>(s_hi + off) = h;
           *reinterpret_cast<uint4*>(s_lo + off) = l;
         }
@@ -187,6 +241,7 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+template <int YNV>
 __global__ void __launch_bounds__(kThreads, 1) sgemm_tc_kernel(const Params p) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kMaxStages];
@@ -217,7 +272,7 @@ __global__ void __launch_bounds__(kThreads, 1) sgemm_tc_kernel(const Params p) {
     mbar_init(smem_u32(&accum_bar), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 4) {
+  if (warp == kLoaderWarps) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
                  "r"((uint32_t)p.tmem_cols)
                  : "memory");
@@ -229,19 +284,32 @@ __global__ void __launch_bounds__(kThreads, 1) sgemm_tc_kernel(const Params p) {
   const uint32_t tmem_d = tmem_base_slot;
   bool ok = true;
 
-  if (warp < 4) {
+  if (warp < kLoaderWarps) {
     // ------------------------------------------------ producers
+    float xv[16], yv[YNV], xn[16], yn[YNV];
+    if (nkb > 0) {
+      fetch_tile<16>(p.X, p.X.mode, xbase, x0, kXRows, k_begin, k_end, xv, tid);
+      fetch_tile<YNV>(p.Y, p.Y.mode, ybase, y0, UN, k_begin, k_end, yv, tid);
+    }
     for (int kb = 0; kb < nkb && ok; ++kb) {
       const int s = kb % S;
       const uint32_t phase = (uint32_t)(kb / S) & 1u;
+      if (kb + 1 < nkb) {  // next block's loads fly while this one is split and stored
+        const long k1 = k_begin + (long)(kb + 1) * kBK;
+        fetch_tile<16>(p.X, p.X.mode, xbase, x0, kXRows, k1, k_end, xn, tid);
+        fetch_tile<YNV>(p.Y, p.Y.mode, ybase, y0, UN, k1, k_end, yn, tid);
+      }
       ok = mbar_wait(smem_u32(&empty_bar[s]), phase ^ 1u);
       if (!ok) break;
       unsigned char* st = smem + (size_t)s * stage_bytes;
-      const long k0 = k_begin + (long)kb * kBK;
-      load_tile(p.X, xbase, x0, kXRows, k0, k_end, st, st + x_bytes, tid);
-      load_tile(p.Y, ybase, y0, UN, k0, k_end, st + 2 * x_bytes, st + 2 * x_bytes + y_bytes, tid);
+      stash_tile<16>(p.X.mode, kXRows, xv, st, st + x_bytes, tid);
+      stash_tile<YNV>(p.Y.mode, UN, yv, st + 2 * x_bytes, st + 2 * x_bytes + y_bytes, tid);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core
       mbar_arrive(smem_u32(&full_bar[s]));
+#pragma unroll
+      for (int u = 0; u < 16; ++u) xv[u] = xn[u];
+#pragma unroll
+      for (int u = 0; u < YNV; ++u) yv[u] = yn[u];
     }
     // ------------------------------------------------ epilogue
     if (ok && nkb > 0) ok = mbar_wait(smem_u32(&accum_bar), 0);
@@ -249,25 +317,24 @@ __global__ void __launch_bounds__(kThreads, 1) sgemm_tc_kernel(const Params p) {
     if (!ok) {
       if (lane == 0) { *(volatile int*)p.err = 1; __threadfence_system(); }
     } else {
-      const long i_g = x0 + warp * 32 + lane;  // product row (or column, when swapped) held by this thread's TMEM lane
+      // TMEM lane quarter of a warp is (warp % 4); the two warps of a quarter split the columns
+      const int quarter = warp & 3, colhalf = warp >> 2;
+      const long i_g = x0 + quarter * 32 + lane;  // product row (or column, when swapped) held by this thread's TMEM lane
       const bool i_in = i_g < p.X.rows;
       float* cbase = (p.nsplit > 1) ? p.C + ((long)batch * p.nsplit + split) * p.M * p.N : p.C + batch * p.c_batch_stride;
       const long ld = (p.nsplit > 1) ? p.N : p.ldc;
-      for (int c0 = 0; c0 < UN; c0 += 16) {
+      const int nchunks = UN / 16;
+      for (int ch = colhalf; ch < nchunks; ch += 2) {
+        const int c0 = ch * 16;
         uint32_t r[16];
-        if (nkb > 0) {
-          uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0;
-          asm volatile(
-              "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-              : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-                "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-              : "r"(taddr)
-              : "memory");
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        } else {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) r[j] = 0u;  // K == 0: the product is all zeros
-        }
+        uint32_t taddr = tmem_d + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+              "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+            : "r"(taddr)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (i_in) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -309,7 +376,7 @@ __global__ void __launch_bounds__(kThreads, 1) sgemm_tc_kernel(const Params p) {
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
-  if (warp == 4) {
+  if (warp == kLoaderWarps) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)p.tmem_cols) : "memory");
   }
@@ -356,8 +423,13 @@ int sgemm_tc(int tA, int tB, long P, long M, long N, long K, const float* A, lon
     if (cudaHostGetDevicePointer((void**)&g_err_dev, g_err_host, 0) != cudaSuccess) return fail("cudaHostGetDevicePointer failed");
   }
   Params p;
-  Operand opA = {A, lda, tA ? 0 : 1, M, strideA};   // rows of op(A) are m
-  Operand opB = {B, ldb, tB ? 1 : 0, N, strideB};   // rows of op(B)^T are n
+  auto mode_of = [](const float* base, long ld, long bstride, int kcontig) {
+    if (!kcontig) return 0;
+    bool al = ((uintptr_t)base & 15) == 0 && (ld & 3) == 0 && (bstride & 3) == 0;
+    return al ? 2 : 1;
+  };
+  Operand opA = {A, lda, tA ? 0 : 1, mode_of(A, lda, strideA, tA ? 0 : 1), M, strideA};   // rows of op(A) are m
+  Operand opB = {B, ldb, tB ? 1 : 0, mode_of(B, ldb, strideB, tB ? 1 : 0), N, strideB};   // rows of op(B)^T are n
   p.swapped = (N > M) ? 1 : 0;
   p.X = p.swapped ? opB : opA;
   p.Y = p.swapped ? opA : opB;
@@ -391,8 +463,6 @@ int sgemm_tc(int tA, int tB, long P, long M, long N, long K, const float* A, lon
   long nkb = kchunk / kBK;
   int stages = nkb >= 3 ? 3 : (int)std::max<long>(nkb, 1);
   while (stages > 1 && stages * stage_bytes + 1024 > 200 * 1024) --stages;
-  // two CTAs per SM hide the load latency of short K loops: keep the footprint under half the SM when cheap
-  if (stages * stage_bytes + 1024 > 100 * 1024 && nkb <= 4 && stages > 2) stages = 2;
   p.stages = stages;
   p.ldc = ldc;
   p.c_batch_stride = strideC;
@@ -406,13 +476,17 @@ int sgemm_tc(int tA, int tB, long P, long M, long N, long K, const float* A, lon
     p.C = C;
   }
   size_t smem = (size_t)stages * stage_bytes + 1024;
-  static size_t smem_configured = 0;
-  if (smem > smem_configured) {
-    CGTB_CUDA_TRY(cudaFuncSetAttribute(sgemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048));
-    smem_configured = 227 * 1024;
+  static bool smem_configured = false;
+  if (!smem_configured) {
+    const int cap = 227 * 1024 - 2048;
+    CGTB_CUDA_TRY(cudaFuncSetAttribute(sgemm_tc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap));
+    CGTB_CUDA_TRY(cudaFuncSetAttribute(sgemm_tc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap));
+    smem_configured = true;
   }
   dim3 grid((unsigned)xtiles, (unsigned)ytiles, (unsigned)(P * nsplit));
-  CGTB_LAUNCH(sgemm_tc_kernel, grid, kThreads, smem, p);
+  // register slots for the Y tile: UN*32 elements over 256 loader threads, in units the access patterns need
+  if (UN <= 128) CGTB_LAUNCH(sgemm_tc_kernel<16>, grid, kThreads, smem, p);
+  else CGTB_LAUNCH(sgemm_tc_kernel<32>, grid, kThreads, smem, p);
   if (nsplit > 1) {
     long total = P * M * N;
     long blocks = std::min<long>(cgtb_ceil_div(total, 256), (long)rt().sm_count * 8);
