@@ -13,12 +13,14 @@
 //     K-major, 128-byte-swizzled layout that the UMMA shared-memory descriptor describes. Going through
 //     registers is what makes the split free, lets any leading dimension and any of the four transpose
 //     combinations feed the same MMA configuration (a transposed source is transposed on the way in),
-//     and zero-fills ragged edges. The loads of K block kb+1 are issued before block kb is split and
-//     stored, so global-memory latency overlaps the conversion work.
+//     and zero-fills ragged edges. Each thread keeps the loads of the next two or three K blocks in
+//     flight in registers while the current one is split and stored.
 //   * Warp 8: one thread issues the MMAs (12 per 32-deep K block: 4 K steps x 3 split terms) and
 //     commits them to the stage's "empty" mbarrier; the warp owns the TMEM allocation.
 //   * After the last K block the eight loader warps become the epilogue: tcgen05.ld the accumulator
-//     (lane = tile row; the two warps of a lane quarter take alternate 16-column chunks) and store to C, or to a split-K slab that a second kernel folds in split order.
+//     (lane = tile row; the two warps of a lane quarter take alternate 16-column chunks), stage it in
+//     the idle pipeline memory and write C with coalesced stores, or a split-K slab that a second kernel
+//     folds in split order.
 //   * Every mbarrier wait is bounded; on expiry the kernel raises a flag in host-mapped memory, skips
 //     the remaining work, still frees its TMEM and returns. The host reports the flag after the stream
 //     has been synchronised.
@@ -44,7 +46,7 @@ struct Operand {
   const float* base;
   long ld;        // stored row length
   int kcontig;    // 1: element(row, k) = base[row*ld + k]; 0: element(row, k) = base[k*ld + row]
-  int mode;       // loader access pattern (see fetch_tile): 0 rows contiguous, 1 K contiguous, 2 K contiguous + 16-byte aligned
+  int mode;       // loader access pattern (see TileLoader): 0 rows contiguous, 1 K contiguous, 2 K contiguous + 16-byte aligned
   long rows;      // valid rows of this operand (M or N of the product)
   long batch_stride;
 };
@@ -91,14 +93,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   return false;
 }
 
+// Branch-free 3xTF32 split. Non-finite inputs keep hi = x and lo = 0 so that inf stays inf.
 __device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
-  float hf = __uint_as_float(hi);
-  if (!(fabsf(hf) <= 3.0e38f)) {             // x is inf/nan, or rounding overflowed
-    if (fabsf(x) <= 3.0e38f) { hi = __float_as_uint(x) & 0xffffe000u; hf = __uint_as_float(hi); }
-    else { lo = 0u; return; }
-  }
-  float r = x - hf;
+  float r = x - __uint_as_float(hi);
+  r = (fabsf(r) <= 3.0e38f) ? r : 0.f;  // x or hi is inf/nan
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(r));
 }
 
@@ -108,115 +107,160 @@ __device__ __forceinline__ uint32_t tile_off(int row, int k) {
   return (uint32_t)row * 128u + ((((uint32_t)k >> 2) ^ ((uint32_t)row & 7u)) << 4) + (((uint32_t)k & 3u) << 2);
 }
 
-// Operand tiles travel global -> registers -> shared memory in two steps so that the loads of K block
-// kb+1 are in flight while block kb is split and stored. Three access patterns, chosen per operand:
-//   mode 0  rows contiguous in memory (a transposed source): threads along rows, 16 k per thread;
-//   mode 1  K contiguous: lanes along k, one 128-byte row segment per warp instruction;
-//   mode 2  K contiguous and 16-byte aligned: 128-bit loads, 8 lanes per row.
-// NV is the number of register slots a thread owns for the tile: 16 for the 128-row X tile, up to 32
-// for a 256-row Y tile; slots beyond the tile are predicated off.
-template <int NV>
-__device__ __forceinline__ void fetch_tile(const Operand& op, int mode, const float* base, long row0, int R, long k0, long k_end,
-                                           float (&v)[NV], int tid) {
-  const int warp = tid >> 5, lane = tid & 31;
-  if (mode == 1) {
-    const long k = k0 + lane;
-    const bool kin = k < k_end;
+// Operand tiles travel global -> registers -> shared memory in two steps so that the loads of the
+// next K block are in flight while the current one is split and stored. Three access patterns, fixed
+// at compile time per operand:
+//   MODE 0  rows contiguous in memory (a transposed source): threads along rows, 16 k per thread;
+//   MODE 1  K contiguous: lanes along k, one 128-byte row segment per warp instruction;
+//   MODE 2  K contiguous and 16-byte aligned: 128-bit loads, 8 lanes per row.
+// NV is the number of register slots a thread owns for the tile (16 for the 128-row X tile, 16 or 32
+// for the Y tile). Everything that does not change from one K block to the next -- the thread's row
+// pointer, its shared-memory offset, which of its slots fall inside the matrix -- is computed once.
+template <int MODE, int NV>
+struct TileLoader {
+  const float* p0;   // first element this thread loads in K block 0 (clamped to a valid address)
+  long step;         // element distance between consecutive slots (MODE 0: between consecutive k)
+  uint32_t off0;     // shared-memory byte offset of slot 0
+  uint32_t valid;    // bit u set: slot u (MODE 0: pair u) lies inside the matrix
+  long ld;
+  int kofs;          // this thread's k offset inside the block (MODE 1: lane, MODE 2: 4*(lane&7))
+
+  __device__ __forceinline__ void init(const Operand& op, const float* base, long row0, int R, int tid) {
+    const int warp = tid >> 5, lane = tid & 31;
+    ld = op.ld;
+    valid = 0u;
+    if (MODE == 1) {
+      kofs = lane;
+      const int r0 = warp;
 #pragma unroll
-    for (int u = 0; u < NV; ++u) {
-      int r = warp + kLoaderWarps * u;
-      long rg = row0 + r;
-      v[u] = (r < R && kin && rg < op.rows) ? __ldg(base + rg * op.ld + k) : 0.f;
-    }
-  } else if (mode == 2) {
-    const int sub = lane >> 3, c = lane & 7;  // 4 rows per warp instruction, 8 chunks of 4 floats per row
-    const long k = k0 + 4 * c;
-#pragma unroll
-    for (int u = 0; u < NV / 4; ++u) {
-      int r = (warp * 4 + sub) + (kLoaderWarps * 4) * u;
-      long rg = row0 + r;
-      float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (r < R && rg < op.rows) {
-        if (k + 3 < k_end) {
-          q = __ldg(reinterpret_cast<const float4*>(base + rg * op.ld + k));
-        } else {  // ragged end of K: element-wise
-          const float* src = base + rg * op.ld;
-          if (k + 0 < k_end) q.x = __ldg(src + k + 0);
-          if (k + 1 < k_end) q.y = __ldg(src + k + 1);
-          if (k + 2 < k_end) q.z = __ldg(src + k + 2);
-        }
+      for (int u = 0; u < NV; ++u) {
+        int r = r0 + kLoaderWarps * u;
+        if (r < R && row0 + r < op.rows) valid |= 1u << u;
       }
-      v[4 * u + 0] = q.x; v[4 * u + 1] = q.y; v[4 * u + 2] = q.z; v[4 * u + 3] = q.w;
-    }
-  } else {
-    // pair index q -> (row = q % R, khalf = q / R); a thread owns pairs tid, tid + 256, ...
+      p0 = base + (row0 + r0) * ld + lane;
+      step = (long)kLoaderWarps * ld;
+      off0 = tile_off(r0, lane);           // slot u: + u * 8 rows = + u * 1024 bytes (row mod 8 unchanged)
+    } else if (MODE == 2) {
+      const int sub = lane >> 3, c = lane & 7;
+      kofs = 4 * c;
+      const int r0 = warp * 4 + sub;
 #pragma unroll
-    for (int pr = 0; pr < NV / 16; ++pr) {
-      int q = tid + kLoaderThreads * pr;
-      int khalf = q / R, r = q - khalf * R;
-      long rg = row0 + r;
-      const bool rin = khalf < 2 && rg < op.rows;
+      for (int u = 0; u < NV / 4; ++u) {
+        int r = r0 + kLoaderWarps * 4 * u;
+        if (r < R && row0 + r < op.rows) valid |= 1u << u;
+      }
+      p0 = base + (row0 + r0) * ld + 4 * c;
+      step = (long)kLoaderWarps * 4 * ld;
+      off0 = tile_off(r0, 4 * c);          // slot u: + u * 32 rows = + u * 4096 bytes
+    } else {
+      kofs = 0;
+      p0 = base;
+      step = ld;
+      off0 = 0;
 #pragma unroll
-      for (int u = 0; u < 16; ++u) {
-        long k = k0 + khalf * 16 + u;
-        v[16 * pr + u] = (rin && k < k_end) ? __ldg(base + k * op.ld + rg) : 0.f;
+      for (int pr = 0; pr < NV / 16; ++pr) {
+        int q = tid + kLoaderThreads * pr;
+        int khalf = q / R, r = q - khalf * R;
+        if (khalf < 2 && row0 + r < op.rows) valid |= 1u << pr;
       }
     }
   }
-}
 
-template <int NV>
-__device__ __forceinline__ void stash_tile(int mode, int R, const float (&v)[NV], unsigned char* s_hi, unsigned char* s_lo, int tid) {
-  const int warp = tid >> 5, lane = tid & 31;
-  if (mode == 1) {
+  // full == true: the whole 32-deep block lies inside K (no per-element k checks)
+  __device__ __forceinline__ void fetch(const Operand& op, const float* base, long row0, int R, long k0, long k_end, bool full,
+                                        float (&v)[NV], int tid) const {
+    if (MODE == 1) {
+      const bool kin = full || (k0 + kofs < k_end);
+      const float* p = p0 + k0;
 #pragma unroll
-    for (int u = 0; u < NV; ++u) {
-      int r = warp + kLoaderWarps * u;
-      if (r < R) {
-        uint32_t hi, lo;
-        split_tf32(v[u], hi, lo);
-        uint32_t off = tile_off(r, lane);  // 32 lanes -> 32 distinct banks
-        *reinterpret_cast<uint32_t*>(s_hi + off) = hi;
-        *reinterpret_cast<uint32_t*>(s_lo + off) = lo;
+      for (int u = 0; u < NV; ++u) {
+        v[u] = (((valid >> u) & 1u) && kin) ? __ldg(p) : 0.f;
+        p += step;
+      }
+    } else if (MODE == 2) {
+      const float* p = p0 + k0;
+      const long kk = k0 + kofs;
+#pragma unroll
+      for (int u = 0; u < NV / 4; ++u) {
+        float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+        if ((valid >> u) & 1u) {
+          if (full || kk + 3 < k_end) {
+            q = __ldg(reinterpret_cast<const float4*>(p));
+          } else {
+            if (kk + 0 < k_end) q.x = __ldg(p + 0);
+            if (kk + 1 < k_end) q.y = __ldg(p + 1);
+            if (kk + 2 < k_end) q.z = __ldg(p + 2);
+          }
+        }
+        v[4 * u + 0] = q.x; v[4 * u + 1] = q.y; v[4 * u + 2] = q.z; v[4 * u + 3] = q.w;
+        p += step;
+      }
+    } else {
+#pragma unroll
+      for (int pr = 0; pr < NV / 16; ++pr) {
+        int q = tid + kLoaderThreads * pr;
+        int khalf = q / R, r = q - khalf * R;
+        const bool rin = (valid >> pr) & 1u;
+        const float* p = base + (k0 + khalf * 16) * ld + row0 + r;
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          v[16 * pr + u] = (rin && (full || k0 + khalf * 16 + u < k_end)) ? __ldg(p) : 0.f;
+          p += ld;
+        }
       }
     }
-  } else if (mode == 2) {
-    const int sub = lane >> 3, c = lane & 7;
+  }
+
+  __device__ __forceinline__ void stash(int R, const float (&v)[NV], unsigned char* s_hi, unsigned char* s_lo, int tid) const {
+    const int warp = tid >> 5;
+    if (MODE == 1) {
 #pragma unroll
-    for (int u = 0; u < NV / 4; ++u) {
-      int r = (warp * 4 + sub) + (kLoaderWarps * 4) * u;
-      if (r < R) {
-        uint4 h, l;
-        split_tf32(v[4 * u + 0], h.x, l.x);
-        split_tf32(v[4 * u + 1], h.y, l.y);
-        split_tf32(v[4 * u + 2], h.z, l.z);
-        split_tf32(v[4 * u + 3], h.w, l.w);
-        uint32_t off = tile_off(r, 4 * c);
-        *reinterpret_cast<uint4*>(s_hi + off) = h;
-        *reinterpret_cast<uint4*>(s_lo + off) = l;
+      for (int u = 0; u < NV; ++u) {
+        if (warp + kLoaderWarps * u < R) {
+          uint32_t hi, lo;
+          split_tf32(v[u], hi, lo);
+          const uint32_t off = off0 + (uint32_t)u * 1024u;  // 32 lanes -> 32 distinct banks
+          *reinterpret_cast<uint32_t*>(s_hi + off) = hi;
+          *reinterpret_cast<uint32_t*>(s_lo + off) = lo;
+        }
       }
-    }
-  } else {
+    } else if (MODE == 2) {
+      const int r0 = warp * 4 + ((tid & 31) >> 3);
 #pragma unroll
-    for (int pr = 0; pr < NV / 16; ++pr) {
-      int q = tid + kLoaderThreads * pr;
-      int khalf = q / R, r = q - khalf * R;
-      if (khalf < 2) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
+      for (int u = 0; u < NV / 4; ++u) {
+        if (r0 + kLoaderWarps * 4 * u < R) {
           uint4 h, l;
-          split_tf32(v[16 * pr + 4 * c + 0], h.x, l.x);
-          split_tf32(v[16 * pr + 4 * c + 1], h.y, l.y);
-          split_tf32(v[16 * pr + 4 * c + 2], h.z, l.z);
-          split_tf32(v[16 * pr + 4 * c + 3], h.w, l.w);
-          uint32_t off = tile_off(r, khalf * 16 + 4 * c);
+          split_tf32(v[4 * u + 0], h.x, l.x);
+          split_tf32(v[4 * u + 1], h.y, l.y);
+          split_tf32(v[4 * u + 2], h.z, l.z);
+          split_tf32(v[4 * u + 3], h.w, l.w);
+          const uint32_t off = off0 + (uint32_t)u * 4096u;
           *reinterpret_cast<uint4*>(s_hi + off) = h;
           *reinterpret_cast<uint4*>(s_lo + off) = l;
         }
       }
+    } else {
+#pragma unroll
+      for (int pr = 0; pr < NV / 16; ++pr) {
+        int q = tid + kLoaderThreads * pr;
+        int khalf = q / R, r = q - khalf * R;
+        if (khalf < 2) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint4 h, l;
+            split_tf32(v[16 * pr + 4 * c + 0], h.x, l.x);
+            split_tf32(v[16 * pr + 4 * c + 1], h.y, l.y);
+            split_tf32(v[16 * pr + 4 * c + 2], h.z, l.z);
+            split_tf32(v[16 * pr + 4 * c + 3], h.w, l.w);
+            const uint32_t off = tile_off(r, khalf * 16 + 4 * c);
+            *reinterpret_cast<uint4*>(s_hi + off) = h;
+            *reinterpret_cast<uint4*>(s_lo + off) = l;
+          }
+        }
+      }
     }
   }
-}
+};
 
 // shared-memory matrix descriptor: K-major, SWIZZLE_128B, 8-row groups 1024 bytes apart
 __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
@@ -241,13 +285,14 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-template <int YNV>
-__global__ void __launch_bounds__(kThreads, 1) sgemm_tc_kernel(const Params p) {
+template <int XMODE, int YMODE, int YNV, int DEPTH>
+__global__ void __launch_bounds__(kThreads, (YNV <= 16 ? 2 : 1)) sgemm_tc_kernel(const Params p) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kMaxStages];
   __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
   __shared__ __align__(8) uint64_t accum_bar;
   __shared__ uint32_t tmem_base_slot;
+  __shared__ int epi_fail;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int UN = p.UN, S = p.stages;
@@ -270,6 +315,7 @@ __global__ void __launch_bounds__(kThreads, 1) sgemm_tc_kernel(const Params p) {
       mbar_init(smem_u32(&empty_bar[s]), 1);
     }
     mbar_init(smem_u32(&accum_bar), 1);
+    epi_fail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == kLoaderWarps) {
@@ -286,43 +332,59 @@ __global__ void __launch_bounds__(kThreads, 1) sgemm_tc_kernel(const Params p) {
 
   if (warp < kLoaderWarps) {
     // ------------------------------------------------ producers
-    float xv[16], yv[YNV], xn[16], yn[YNV];
-    if (nkb > 0) {
-      fetch_tile<16>(p.X, p.X.mode, xbase, x0, kXRows, k_begin, k_end, xv, tid);
-      fetch_tile<YNV>(p.Y, p.Y.mode, ybase, y0, UN, k_begin, k_end, yv, tid);
-    }
-    for (int kb = 0; kb < nkb && ok; ++kb) {
-      const int s = kb % S;
-      const uint32_t phase = (uint32_t)(kb / S) & 1u;
-      if (kb + 1 < nkb) {  // next block's loads fly while this one is split and stored
-        const long k1 = k_begin + (long)(kb + 1) * kBK;
-        fetch_tile<16>(p.X, p.X.mode, xbase, x0, kXRows, k1, k_end, xn, tid);
-        fetch_tile<YNV>(p.Y, p.Y.mode, ybase, y0, UN, k1, k_end, yn, tid);
+    // DEPTH register buffers per thread: the loads of blocks kb+1 .. kb+DEPTH-1 are in flight while block
+    // kb is split and stored, which is what keeps enough bytes outstanding to cover HBM latency.
+    float xb[DEPTH][16], yb[DEPTH][YNV];
+    TileLoader<XMODE, 16> lx;
+    TileLoader<YMODE, YNV> ly;
+    lx.init(p.X, xbase, x0, kXRows, tid);
+    ly.init(p.Y, ybase, y0, UN, tid);
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d) {
+      if (d < nkb) {
+        const long k1 = k_begin + (long)d * kBK;
+        const bool full = k1 + kBK <= k_end;
+        lx.fetch(p.X, xbase, x0, kXRows, k1, k_end, full, xb[d], tid);
+        ly.fetch(p.Y, ybase, y0, UN, k1, k_end, full, yb[d], tid);
       }
-      ok = mbar_wait(smem_u32(&empty_bar[s]), phase ^ 1u);
-      if (!ok) break;
-      unsigned char* st = smem + (size_t)s * stage_bytes;
-      stash_tile<16>(p.X.mode, kXRows, xv, st, st + x_bytes, tid);
-      stash_tile<YNV>(p.Y.mode, UN, yv, st + 2 * x_bytes, st + 2 * x_bytes + y_bytes, tid);
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core
-      mbar_arrive(smem_u32(&full_bar[s]));
+    }
+    for (int kb0 = 0; kb0 < nkb && ok; kb0 += DEPTH) {
 #pragma unroll
-      for (int u = 0; u < 16; ++u) xv[u] = xn[u];
-#pragma unroll
-      for (int u = 0; u < YNV; ++u) yv[u] = yn[u];
+      for (int d = 0; d < DEPTH; ++d) {
+        const int kb = kb0 + d;
+        if (kb < nkb && ok) {
+          const int s = kb % S;
+          const uint32_t phase = (uint32_t)(kb / S) & 1u;
+          ok = mbar_wait(smem_u32(&empty_bar[s]), phase ^ 1u);
+          if (ok) {
+            unsigned char* st = smem + (size_t)s * stage_bytes;
+            lx.stash(kXRows, xb[d], st, st + x_bytes, tid);
+            ly.stash(UN, yb[d], st + 2 * x_bytes, st + 2 * x_bytes + y_bytes, tid);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core
+            mbar_arrive(smem_u32(&full_bar[s]));
+            if (kb + DEPTH < nkb) {
+              const long k1 = k_begin + (long)(kb + DEPTH) * kBK;
+              const bool full = k1 + kBK <= k_end;
+              lx.fetch(p.X, xbase, x0, kXRows, k1, k_end, full, xb[d], tid);
+              ly.fetch(p.Y, ybase, y0, UN, k1, k_end, full, yb[d], tid);
+            }
+          }
+        }
+      }
     }
     // ------------------------------------------------ epilogue
     if (ok && nkb > 0) ok = mbar_wait(smem_u32(&accum_bar), 0);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (!ok) {
-      if (lane == 0) { *(volatile int*)p.err = 1; __threadfence_system(); }
+    if (!ok) epi_fail = 1;
+    asm volatile("bar.sync 1, %0;" ::"n"(kLoaderThreads) : "memory");  // the 8 epilogue warps agree on success
+    if (*(volatile int*)&epi_fail) {
+      if (tid == 0) { *(volatile int*)p.err = 1; __threadfence_system(); }
     } else {
-      // TMEM lane quarter of a warp is (warp % 4); the two warps of a quarter split the columns
+      // Accumulator -> shared-memory staging (the pipeline stages are idle now) -> coalesced stores.
+      // TMEM lane quarter of a warp is (warp % 4); the two warps of a quarter take alternate chunks.
+      float* stg = reinterpret_cast<float*>(smem);
+      const int stride = UN + 1;  // odd: conflict-free both for row-wise writes and column-wise reads
       const int quarter = warp & 3, colhalf = warp >> 2;
-      const long i_g = x0 + quarter * 32 + lane;  // product row (or column, when swapped) held by this thread's TMEM lane
-      const bool i_in = i_g < p.X.rows;
-      float* cbase = (p.nsplit > 1) ? p.C + ((long)batch * p.nsplit + split) * p.M * p.N : p.C + batch * p.c_batch_stride;
-      const long ld = (p.nsplit > 1) ? p.N : p.ldc;
       const int nchunks = UN / 16;
       for (int ch = colhalf; ch < nchunks; ch += 2) {
         const int c0 = ch * 16;
@@ -335,14 +397,29 @@ __global__ void __launch_bounds__(kThreads, 1) sgemm_tc_kernel(const Params p) {
             : "r"(taddr)
             : "memory");
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (i_in) {
+        float* dst = stg + (quarter * 32 + lane) * stride + c0;
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            long j_g = y0 + c0 + j;
-            if (j_g < p.Y.rows) {
-              long idx = p.swapped ? (j_g * ld + i_g) : (i_g * ld + j_g);
-              cbase[idx] = __uint_as_float(r[j]);
-            }
+        for (int j = 0; j < 16; ++j) dst[j] = __uint_as_float(r[j]);
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(kLoaderThreads) : "memory");
+      float* cbase = (p.nsplit > 1) ? p.C + ((long)batch * p.nsplit + split) * p.M * p.N : p.C + batch * p.c_batch_stride;
+      const long ld = (p.nsplit > 1) ? p.N : p.ldc;
+      if (!p.swapped) {  // tile row = product row: lanes along the product's columns
+        for (int row = warp; row < kXRows; row += kLoaderWarps) {
+          const long i_g = x0 + row;
+          if (i_g >= p.X.rows) break;
+          for (int col = lane; col < UN; col += 32) {
+            const long j_g = y0 + col;
+            if (j_g < p.Y.rows) cbase[i_g * ld + j_g] = stg[row * stride + col];
+          }
+        }
+      } else {           // tile row = product column: lanes along tile rows
+        for (int col = warp; col < UN; col += kLoaderWarps) {
+          const long j_g = y0 + col;
+          if (j_g >= p.Y.rows) break;
+          for (int row = lane; row < kXRows; row += 32) {
+            const long i_g = x0 + row;
+            if (i_g < p.X.rows) cbase[j_g * ld + i_g] = stg[row * stride + col];
           }
         }
       }
@@ -461,8 +538,12 @@ int sgemm_tc(int tA, int tB, long P, long M, long N, long K, const float* A, lon
   p.M = M;
   p.N = N;
   long nkb = kchunk / kBK;
-  int stages = nkb >= 3 ? 3 : (int)std::max<long>(nkb, 1);
-  while (stages > 1 && stages * stage_bytes + 1024 > 200 * 1024) --stages;
+  // two resident CTAs per SM double the warps that hide instruction latency: prefer a stage count
+  // that leaves room for a second CTA when two stages fit in half of the SM's shared memory
+  const int fit_half = (int)((110L * 1024 - 1024) / stage_bytes);
+  int stages = fit_half >= 2 ? std::min(fit_half, 3) : std::min<int>(3, (int)((200L * 1024) / stage_bytes));
+  if (stages > nkb) stages = (int)std::max<long>(nkb, 1);
+  if (stages < 1) stages = 1;
   p.stages = stages;
   p.ldc = ldc;
   p.c_batch_stride = strideC;
@@ -475,18 +556,27 @@ int sgemm_tc(int tA, int tB, long P, long M, long N, long K, const float* A, lon
   } else {
     p.C = C;
   }
-  size_t smem = (size_t)stages * stage_bytes + 1024;
-  static bool smem_configured = false;
-  if (!smem_configured) {
-    const int cap = 227 * 1024 - 2048;
-    CGTB_CUDA_TRY(cudaFuncSetAttribute(sgemm_tc_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap));
-    CGTB_CUDA_TRY(cudaFuncSetAttribute(sgemm_tc_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap));
-    smem_configured = true;
-  }
+  size_t smem = (size_t)stages * stage_bytes;
+  size_t staging = (size_t)kXRows * (UN + 1) * sizeof(float);  // epilogue staging re-uses the stage memory
+  if (smem < staging) smem = staging;
+  smem += 1024;
   dim3 grid((unsigned)xtiles, (unsigned)ytiles, (unsigned)(P * nsplit));
-  // register slots for the Y tile: UN*32 elements over 256 loader threads, in units the access patterns need
-  if (UN <= 128) CGTB_LAUNCH(sgemm_tc_kernel<16>, grid, kThreads, smem, p);
-  else CGTB_LAUNCH(sgemm_tc_kernel<32>, grid, kThreads, smem, p);
+  const int cap = 227 * 1024 - 2048;
+  // one instantiation per (X access pattern, Y access pattern, Y register slots)
+#define TC_CASE(XM, YM)                                                                                            \
+  if (p.X.mode == XM && p.Y.mode == YM) {                                                                          \
+    if (UN <= 128) {                                                                                               \
+      static bool cfg = false;                                                                                     \
+      if (!cfg) { CGTB_CUDA_TRY(cudaFuncSetAttribute(sgemm_tc_kernel<XM, YM, 16, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap)); cfg = true; } \
+      CGTB_LAUNCH((sgemm_tc_kernel<XM, YM, 16, 2>), grid, kThreads, smem, p);                                       \
+    } else {                                                                                                       \
+      static bool cfg = false;                                                                                     \
+      if (!cfg) { CGTB_CUDA_TRY(cudaFuncSetAttribute(sgemm_tc_kernel<XM, YM, 32, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap)); cfg = true; } \
+      CGTB_LAUNCH((sgemm_tc_kernel<XM, YM, 32, 2>), grid, kThreads, smem, p);                                       \
+    }                                                                                                              \
+  }
+  TC_CASE(0, 0) TC_CASE(0, 1) TC_CASE(0, 2) TC_CASE(1, 0) TC_CASE(1, 1) TC_CASE(1, 2) TC_CASE(2, 0) TC_CASE(2, 1) TC_CASE(2, 2)
+#undef TC_CASE
   if (nsplit > 1) {
     long total = P * M * N;
     long blocks = std::min<long>(cgtb_ceil_div(total, 256), (long)rt().sm_count * 8);
