@@ -265,6 +265,43 @@ __global__ void reduce_finish_kernel(int kind, long osize, int nsplit, const T* 
   }
 }
 
+// Fast path for the layouts the graphs produce: input viewed as [R0, K, R1] with R0 and R1 reduced
+// and K kept (bias gradients Sum{0,2,3} of NCHW, column sums Sum{0}, row sums Sum{1}, full sums).
+// 32-bit index arithmetic without divisions; block (k, split) walks its share of R0 with threads along R1.
+template <typename T>
+__global__ void reduce_rkr_kernel(int kind, int R0, int K, int R1, int r0chunk, int r1chunk, int n1, const T* __restrict__ in,
+                                  T* __restrict__ out, int nsplit) {
+  const int k = blockIdx.x, split = blockIdx.y;
+  const int s0 = split / n1, s1 = split - s0 * n1;  // the split index covers (R0 chunk, R1 chunk)
+  const int a0 = s0 * r0chunk, a1 = min(a0 + r0chunk, R0);
+  const int b0 = s1 * r1chunk, b1 = min(b0 + r1chunk, R1);
+  T acc = red_init<T>(kind);
+  for (int r0 = a0; r0 < a1; ++r0) {
+    const T* row = in + ((size_t)r0 * K + k) * R1;
+    for (int r1 = b0 + threadIdx.x; r1 < b1; r1 += blockDim.x) acc = red_op<T>(kind, acc, row[r1]);
+  }
+  __shared__ T warp_part[32];
+  for (int d = 16; d > 0; d >>= 1) acc = red_op<T>(kind, acc, shfl_down_t<T>(acc, d));
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  if (lane == 0) warp_part[wid] = acc;
+  __syncthreads();
+  if (wid == 0) {
+    int nw = blockDim.x >> 5;
+    acc = lane < nw ? warp_part[lane] : red_init<T>(kind);
+    for (int d = 16; d > 0; d >>= 1) acc = red_op<T>(kind, acc, shfl_down_t<T>(acc, d));
+    if (lane == 0) out[(size_t)k * nsplit + split] = acc;
+  }
+}
+// [R0, K] with R0 reduced and K contiguous: threads along K, coalesced across columns
+template <typename T>
+__global__ void reduce_rk_kernel(int kind, int R0, int K, const T* __restrict__ in, T* __restrict__ out) {
+  for (int k = blockIdx.x * blockDim.x + threadIdx.x; k < K; k += gridDim.x * blockDim.x) {
+    T acc = red_init<T>(kind);
+    for (int r0 = 0; r0 < R0; ++r0) acc = red_op<T>(kind, acc, in[(size_t)r0 * K + k]);
+    out[k] = acc;
+  }
+}
+
 template <typename T>
 static int reduce_launch(int kind, int ndim, const long* shape, const int* reduced, const T* in, T* out) {
   ReduceGeom g;
@@ -294,6 +331,51 @@ static int reduce_launch(int kind, int ndim, const long* shape, const int* reduc
     }
     if (!merged) { sh[n] = shape[i]; st[n] = stride[i]; n++; }
     if (r) rsize *= shape[i]; else osize *= shape[i];
+  }
+  // ---- fast paths on the merged geometry
+  {
+    long R0 = 1, K = 1, R1 = 1;
+    bool match = false;
+    if (g.nk <= 1 && g.nr == 2 && g.nk == 1 && g.rstride[1] == 1 && g.kstride[0] == g.rshape[1] &&
+        g.rstride[0] == g.kshape[0] * g.rshape[1]) {
+      R0 = g.rshape[0]; K = g.kshape[0]; R1 = g.rshape[1]; match = true;            // [R0, K, R1]
+    } else if (g.nr == 1 && g.rstride[0] == 1 && (g.nk == 0 || (g.nk == 1 && g.kstride[0] == g.rshape[0]))) {
+      K = g.nk ? g.kshape[0] : 1; R1 = g.rshape[0]; match = true;                    // [K, R1]
+    } else if (g.nr == 1 && g.nk == 1 && g.kstride[0] == 1 && g.rstride[0] == g.kshape[0]) {
+      R0 = g.rshape[0]; K = g.kshape[0]; R1 = 1; match = true;                       // [R0, K]
+    }
+    if (match && R0 < (1L << 30) && K < 65536L * 16 && R1 < (1L << 30)) {
+      if (R1 == 1 && K >= 1) {
+        if (R0 <= 4096 || K >= 1024) {
+          CGTB_LAUNCH(reduce_rk_kernel<T>, (unsigned)std::min<long>(cgtb_ceil_div(K, 128), 1024), 128, 0, kind, (int)R0, (int)K, in, out);
+          return 0;
+        }
+      } else if (K <= 65535) {
+        int threads = R1 >= 256 ? 256 : (R1 >= 64 ? 64 : 32);
+        long want = (long)rt().sm_count * 4;
+        // spread the work of one output over several blocks: first along R0, then along R1
+        long per_k = cgtb_ceil_div(want, K);
+        int n0 = (K < want && R0 > 1) ? (int)std::min<long>(per_k, R0) : 1;
+        int r0chunk = (int)cgtb_ceil_div(R0, n0);
+        n0 = (int)cgtb_ceil_div(R0, r0chunk);
+        int n1 = 1;
+        if ((long)K * n0 < want && R1 > 8192) n1 = (int)std::min<long>(cgtb_ceil_div(want, (long)K * n0), cgtb_ceil_div(R1, 4096));
+        int r1chunk = (int)cgtb_ceil_div(R1, n1);
+        n1 = (int)cgtb_ceil_div(R1, r1chunk);
+        int nsplit = n0 * n1;
+        if (nsplit > 65535) { n1 = 65535 / n0; r1chunk = (int)cgtb_ceil_div(R1, n1); n1 = (int)cgtb_ceil_div(R1, r1chunk); nsplit = n0 * n1; }
+        dim3 grid((unsigned)K, (unsigned)nsplit);
+        if (nsplit == 1) {
+          CGTB_LAUNCH(reduce_rkr_kernel<T>, grid, threads, 0, kind, (int)R0, (int)K, (int)R1, r0chunk, r1chunk, n1, in, out, 1);
+        } else {
+          T* part = (T*)scratch((size_t)K * nsplit * sizeof(T));
+          if (!part) return 1;
+          CGTB_LAUNCH(reduce_rkr_kernel<T>, grid, threads, 0, kind, (int)R0, (int)K, (int)R1, r0chunk, r1chunk, n1, in, part, nsplit);
+          CGTB_LAUNCH(reduce_finish_kernel<T>, (unsigned)cgtb_ceil_div(K, 128), 128, 0, kind, K, nsplit, part, out);
+        }
+        return 0;
+      }
+    }
   }
   int threads = rsize >= 256 ? 256 : (rsize >= 64 ? 64 : 32);
   // split long reductions so that the grid fills the machine
@@ -382,6 +464,22 @@ static inline unsigned flat_grid(long n, int per_thread = 1) {
   return (unsigned)blocks;
 }
 
+// Repeat fast path: output viewed as [R0, K, R1] with out[r0, k, r1] = in[k] (a bias broadcast).
+// One block row per (r0, k) pair; no per-element division.
+template <typename U>
+__global__ void repeat_rkr_kernel(long rows, int K, int R1, const U* __restrict__ in, U* __restrict__ out) {
+  for (long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const U v = in[row % K];
+    U* dst = out + row * R1;
+    for (int r1 = threadIdx.x; r1 < R1; r1 += blockDim.x) dst[r1] = v;
+  }
+}
+template <typename U>
+__global__ void repeat_rk_kernel(long total, int K, const U* __restrict__ in, U* __restrict__ out) {
+  for (long f = (long)blockIdx.x * blockDim.x + threadIdx.x; f < total; f += (long)gridDim.x * blockDim.x)
+    out[f] = in[(unsigned)(f % K)];
+}
+
 CGTB_API int cgtb_repeat(int dtype, int ndim, const long* out_shape, const int* repeated, const void* in, void* out) {
   if (!require_runtime("cgtb_repeat")) return 1;
   if (ndim > CGTB_MAX_NDIM) return fail("cgtb_repeat: ndim %d too large", ndim);
@@ -410,7 +508,18 @@ CGTB_API int cgtb_repeat(int dtype, int ndim, const long* out_shape, const int* 
     g.istride[g.nd] = istride[i];
     g.nd++;
   }
-  CGTB_FOR_BYTES(dtype_bytes(dtype), U, CGTB_LAUNCH(gather_kernel<U>, flat_grid(total), 256, 0, g, total, (const U*)in, (U*)out));
+  // [R0 repeated, K kept, R1 repeated] and [R0 repeated, K kept]
+  if (g.nd == 3 && g.istride[0] == 0 && g.istride[1] == 1 && g.istride[2] == 0 && g.oshape[1] < (1L << 31) && g.oshape[2] < (1L << 31)) {
+    long rows = g.oshape[0] * g.oshape[1];
+    int R1 = (int)g.oshape[2];
+    int threads = R1 >= 256 ? 256 : (R1 >= 128 ? 128 : (R1 >= 64 ? 64 : 32));
+    unsigned blocks = (unsigned)std::min<long>(rows, (long)rt().sm_count * 32);
+    CGTB_FOR_BYTES(dtype_bytes(dtype), U, CGTB_LAUNCH(repeat_rkr_kernel<U>, blocks, threads, 0, rows, (int)g.oshape[1], R1, (const U*)in, (U*)out));
+  } else if (g.nd == 2 && g.istride[0] == 0 && g.istride[1] == 1 && g.oshape[1] < (1L << 31)) {
+    CGTB_FOR_BYTES(dtype_bytes(dtype), U, CGTB_LAUNCH(repeat_rk_kernel<U>, flat_grid(total), 256, 0, total, (int)g.oshape[1], (const U*)in, (U*)out));
+  } else {
+    CGTB_FOR_BYTES(dtype_bytes(dtype), U, CGTB_LAUNCH(gather_kernel<U>, flat_grid(total), 256, 0, g, total, (const U*)in, (U*)out));
+  }
   CGTB_CHECK_LAUNCH("repeat");
   return 0;
 }
@@ -549,26 +658,30 @@ CGTB_API int cgtb_getflat(int dtype, long n, const void* x, const int64_t* k, vo
 }
 
 // IncFlatIndices (cgt/core.py:2012-2023): out.flat[k[i]] += p[i] in index order, so duplicate indices
-// accumulate in the reference's order. Thread i adds p[i] only after every earlier duplicate of k[i]
-// has been added: each thread first folds, in order, all j < i with k[j] == k[i] that nobody else owns.
-// Implemented as: the FIRST occurrence of each index owns the whole ordered sum for that index.
+// accumulate in the reference's order: the FIRST occurrence of an index owns the whole ordered sum
+// for that index, every later occurrence does nothing.
 template <typename T>
-__global__ void incflat_kernel(long n, const int64_t* __restrict__ k, const T* __restrict__ p, T* __restrict__ out) {
+__global__ void incflat_kernel(int n, const int64_t* __restrict__ k, const T* __restrict__ p, T* __restrict__ out) {
   extern __shared__ __align__(16) unsigned char incflat_smem[];
   int64_t* ks = reinterpret_cast<int64_t*>(incflat_smem);  // the whole index list, staged once per block
-  for (long j = threadIdx.x; j < n; j += blockDim.x) ks[j] = k[j];
+  for (int j = threadIdx.x; j < n; j += blockDim.x) ks[j] = k[j];
   __syncthreads();
-  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
-    int64_t me = ks[i];
-    bool first = true;
-    for (long j = 0; j < i; ++j)
-      if (ks[j] == me) { first = false; break; }
-    if (!first) continue;
-    T acc = out[me];
-    for (long j = i; j < n; ++j)
-      if (ks[j] == me) acc += p[j];
-    out[me] = acc;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int64_t me = ks[i];
+  // one branch-free pass counts the duplicates of this index before and after position i
+  int before = 0, after = 0;
+  for (int j = 0; j < n; ++j) {
+    const bool m = ks[j] == me;
+    before += (m && j < i);
+    after += (m && j > i);
   }
+  if (before) return;  // an earlier occurrence owns the ordered sum for this index
+  T acc = out[me] + p[i];
+  if (after)
+    for (int j = i + 1; j < n; ++j)
+      if (ks[j] == me) acc += p[j];
+  out[me] = acc;
 }
 // large index lists: atomics (integer results stay exact; float sums of duplicates may reorder)
 template <typename T>
@@ -584,7 +697,7 @@ template <typename T>
 static int incflat_launch(long n, const int64_t* k, const T* p, T* out) {
   if (n <= 4096 || !has_atomic<T>::value) {
     if (n > 4096) return fail("cgtb_incflat: %ld indices of a dtype without atomicAdd", n);
-    CGTB_LAUNCH(incflat_kernel<T>, flat_grid(n), 256, (size_t)n * sizeof(int64_t), n, k, p, out);
+    CGTB_LAUNCH(incflat_kernel<T>, (unsigned)cgtb_ceil_div(n, 256), 256, (size_t)n * sizeof(int64_t), (int)n, k, p, out);
   } else {
     if constexpr (has_atomic<T>::value) CGTB_LAUNCH(incflat_atomic_kernel<T>, flat_grid(n), 256, 0, n, k, p, out);
   }
