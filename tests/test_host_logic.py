@@ -1,0 +1,322 @@
+"""CPU tests of the host side (no GPU): the C-ABI library and its symbols, the graph front-end
+(simplifier, autodiff), the compilation pipeline up to the execution graph, run-time compilation of
+Ops that carry C++ source, and the configuration dictionary. Numerics are evaluated with the CPU
+oracle; nothing here touches a device.
+"""
+import ctypes
+import os
+import os.path as osp
+import re
+
+import numpy as np
+import pytest
+
+import cgt_b200 as cgt
+from cgt_b200 import compilation, configs, core, nn, runtime
+from oracle import cpu_backend
+
+ROOT = osp.dirname(osp.dirname(osp.abspath(__file__)))
+
+
+# ------------------------------------------------------------------------------------------------
+# C ABI
+# ------------------------------------------------------------------------------------------------
+def _declared_symbols():
+    text = open(osp.join(ROOT, "include", "cgt_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(cgtb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = runtime.lib()
+    names = _declared_symbols()
+    assert len(names) > 60
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, missing
+    # every symbol the Python side binds is declared in the header
+    undeclared = [n for n in runtime.C_ABI_SYMBOLS if n not in names]
+    assert not undeclared, undeclared
+
+
+def test_builtin_op_callables_are_exported():
+    lib = runtime.lib()
+    for name in ("elwise_unary", "elwise_binary", "mul22", "batched_mul22", "im2col", "col2im", "max_pool", "max_pool_pullback",
+                 "lrn_forward", "lrn_backward", "reduce", "repeat", "transpose", "getsli", "incsli", "getflat", "incflat",
+                 "concatenate", "fill", "constant", "transport", "reshape", "size", "arange", "tuple_index", "in_memory_data",
+                 "allreduce"):
+        assert hasattr(lib, "cgtb_op_" + name), name
+
+
+def test_compute_entry_points_fail_loudly_without_a_gpu():
+    lib = runtime.lib()
+    if lib.cgtb_initialized():
+        pytest.skip("a GPU is bound in this process")
+    buf = (ctypes.c_float * 4)()
+    rc = lib.cgtb_unary(3, 11, 11, 4, buf, buf)
+    assert rc != 0 and "no CPU fallback" in runtime.last_error()
+    assert lib.cgtb_array_new(1, (ctypes.c_long * 1)(4), 11, runtime.GPU) is None
+    with pytest.raises(runtime.BackendError):
+        runtime.device_array(np.zeros(3, "f4"))
+
+
+def test_host_objects_round_trip():
+    a = np.arange(6, dtype="f4").reshape(2, 3)
+    h, keep = runtime.py2cgt_array(a, runtime.CPU, view=True)
+    lib = runtime.lib()
+    assert lib.cgtb_array_ndim(h) == 2 and lib.cgtb_array_dtype(h) == 11 and lib.cgtb_array_devtype(h) == 0
+    assert np.array_equal(runtime.cgt2py_object(h), a)
+    t = lib.cgtb_tuple_new(2)
+    lib.cgtb_tuple_set(t, 0, h)
+    lib.cgtb_tuple_set(t, 1, h)
+    assert lib.cgtb_tuple_len(t) == 2
+    out = runtime.cgt2py_object(t)
+    assert isinstance(out, tuple) and np.array_equal(out[1], a)
+    lib.cgtb_release(t)
+    lib.cgtb_release(h)
+
+
+# ------------------------------------------------------------------------------------------------
+# front-end
+# ------------------------------------------------------------------------------------------------
+def test_simplifier_folds_shapes_and_constants():
+    x = cgt.matrix("x", fixed_shape=(4, 3))
+    y = (x * 1.0 + 0.0).sum(axis=0)
+    assert cgt.infer_shape(y) == (3,)
+    (s,) = cgt.simplify([cgt.size(x, 0) * cgt.size(x, 1)])
+    assert isinstance(s.op, core.Constant) and int(s.op.value) == 12
+    # x*1 and +0 vanish; common subexpressions merge
+    a = cgt.exp(x) + cgt.exp(x)
+    (sa,) = cgt.simplify([a])
+    assert sa.parents[0] is sa.parents[1]
+    (sy,) = cgt.simplify([x * 1.0])
+    assert sy is x or sy.is_argument()
+
+
+def test_broadcast_requires_explicit_pattern():
+    x = cgt.matrix("x", fixed_shape=(4, 3))
+    b = cgt.matrix("b", fixed_shape=(1, 3))
+    z = cgt.broadcast("+", x, b, "xx,1x")
+    f = cpu_backend.function([x, b], z)
+    xv, bv = np.arange(12, dtype="f4").reshape(4, 3), np.float32([[1, 2, 3]])
+    assert np.array_equal(f(xv, bv), xv + bv)
+    with pytest.raises(AssertionError):
+        cgt.vector("v") + x  # rank mismatch: no implicit broadcasting
+
+
+def test_pullback_sums_in_order_and_matches_finite_differences():
+    with cgt.scoped_update_config(precision="double"):
+        x = cgt.matrix("x", fixed_shape=(3, 4))
+        w = cgt.matrix("w", fixed_shape=(4, 2))
+        y = cgt.tanh(x.dot(w))
+        cost = (y * y).sum() + cgt.sigmoid(y).sum() + (cgt.exp(x) / 3.0).sum()
+        gx, gw = cgt.grad(cost, [x, w])
+        f = cpu_backend.function([x, w], [cost, gx, gw])
+        rs = np.random.RandomState(0)
+        xv, wv = rs.randn(3, 4), rs.randn(4, 2)
+        c0, gxv, gwv = f(xv, wv)
+        eps = 1e-6
+        for (arr, g) in ((xv, gxv), (wv, gwv)):
+            for idx in [(0, 0), (1, 1), (2, 1)]:
+                old = arr[idx]
+                arr[idx] = old + eps
+                cp = f(xv, wv)[0]
+                arr[idx] = old - eps
+                cm = f(xv, wv)[0]
+                arr[idx] = old
+                assert abs((cp - cm) / (2 * eps) - g[idx]) < 1e-6
+
+
+def test_convnet_gradients_match_independent_autograd():
+    """Independent cross-check of the autodiff and of the conv / pool / LRN Ops: PyTorch float64 autograd
+    on the same network (sizes chosen so that the pooled extent agrees with PyTorch's formula)."""
+    torch = pytest.importorskip("torch")
+    import torch.nn.functional as F
+    with cgt.scoped_update_config(precision="double"):
+        rs = np.random.RandomState(3)
+        B = 3
+        X = cgt.tensor4("X", fixed_shape=(B, 2, 12, 12))
+        y = cgt.vector("y", dtype="i8", fixed_shape=(B,))
+        Wv, bv = rs.randn(6, 2, 5, 5) * 0.3, rs.randn(1, 6, 1, 1) * 0.1
+        Vv, cv = rs.randn(6 * 5 * 5, 4) * 0.2, rs.randn(1, 4) * 0.1
+        W, b = cgt.shared(Wv, fixed_shape_mask="all"), cgt.shared(bv, fixed_shape_mask="all")
+        V, c = cgt.shared(Vv, fixed_shape_mask="all"), cgt.shared(cv, fixed_shape_mask="all")
+        h = nn.rectify(cgt.broadcast("+", nn.conv2d(X, W, (5, 5), (2, 2)), b, "xxxx,1x11"))
+        h = nn.max_pool_2d(h, (3, 3), stride=(2, 2))          # 12 -> ceil(9/2) = 5, as PyTorch's floor(9/2)+1
+        h = nn.cross_channel_lrn(h, 5, 1e-2, 0.75)
+        flat = h.reshape([B, 6 * 5 * 5])
+        logits = cgt.broadcast("+", flat.dot(V), c, "xx,1x")
+        loss = -cgt.log(nn.softmax(logits))[cgt.arange(B), y].mean()
+        grads = cgt.grad(loss, [W, b, V, c])
+        f = cpu_backend.function([X, y], [loss] + grads)
+        Xv, yv = rs.randn(B, 2, 12, 12), rs.randint(0, 4, size=B)
+        got = f(Xv, yv)
+
+        tW, tb, tV, tc = [torch.tensor(v, requires_grad=True) for v in (Wv, bv, Vv, cv)]
+        th = F.relu(F.conv2d(torch.tensor(Xv), tW, padding=2) + tb)
+        th = F.max_pool2d(th, 3, 2)
+        th = F.local_response_norm(th, 5, alpha=1e-2, beta=0.75, k=1.0)
+        tl = F.cross_entropy(th.reshape(B, -1) @ tV + tc, torch.tensor(yv))
+        tl.backward()
+        np.testing.assert_allclose(got[0], tl.item(), rtol=1e-10)
+        for (g, t) in zip(got[1:], (tW, tb, tV, tc)):
+            np.testing.assert_allclose(g, t.grad.numpy(), rtol=1e-8, atol=1e-10)
+
+
+def test_update_semantics_on_the_oracle():
+    """sgd on scale*x^2 from 1.0 (reference test_optimizers.py golden values)."""
+    for (scale, want) in zip([0.1, 0.2, 0.3], [0.81707280688755, 0.6648326359915, 0.5386151140949]):
+        A = cgt.shared(np.array([1.0], "f4"))
+        cost = (scale * A ** 2).sum()
+        step = cpu_backend.function([], [], updates=nn.sgd(cost, [A], 0.1))
+        for _ in range(10):
+            step()
+        np.testing.assert_allclose(step.get_value(A), want, rtol=1e-5)
+
+
+# ------------------------------------------------------------------------------------------------
+# compilation pipeline (everything before the native interpreter is created)
+# ------------------------------------------------------------------------------------------------
+def _plan(cfg):
+    outs, srcs, targs, analysis = compilation.simplify_for_execution([cfg.loss], cfg.updates)
+    all_out = outs + targs
+    nodelist = core.topsorted(all_out)
+    node2dev = compilation.determine_devices(nodelist, dict(zip(targs, srcs)))
+    compilation.add_transports(nodelist, node2dev, analysis["node2shape"])
+    updates = list(zip(srcs, targs))
+    extra = compilation._update_control_deps(all_out, updates)
+    order = compilation.topsorted_shapes_first(all_out, analysis["node2shape"], extra)
+    const = compilation.compute_const_nodes(order)
+    owner = compilation.determine_memowner(order, updates, node2dev, outs, analysis["node2shape"], const)
+    written = set(o for (n, o) in owner.items() if o is not n)
+    eg, node2memloc = compilation.create_execution_graph(cfg.inputs, order, analysis["node2shape"], owner, node2dev,
+                                                         set(n for n in const if n not in written))
+    return dict(outs=outs, srcs=srcs, targs=targs, order=order, node2dev=node2dev, owner=owner, eg=eg, memloc=node2memloc)
+
+
+def test_placement_transports_and_memory_owners():
+    cfg = configs.build_cifar(batch=4)
+    pl = _plan(cfg)
+    for node in pl["order"]:
+        dev = pl["node2dev"][node]
+        if isinstance(node.op, core.Transport):
+            continue  # the device copy of a scalar operand is the one scalar that lives on the GPU
+        if node.is_scalar() or node.is_argument():
+            assert dev.devtype == "cpu", node
+        elif node.is_data():
+            assert dev.devtype == "gpu"
+    # arguments reach the device through a Transport; every Transport crosses devices
+    transports = [n for n in pl["order"] if isinstance(n.op, core.Transport)]
+    assert any(t.parents[0].is_argument() for t in transports)
+    for t in transports:
+        assert pl["node2dev"][t].devtype != pl["node2dev"][t.parents[0]].devtype
+    # an update's final op writes into the shared variable's own location
+    for (src, targ) in zip(pl["srcs"], pl["targs"]):
+        assert pl["owner"][targ] is src
+        assert pl["memloc"][targ] is pl["memloc"][src]
+    # with fixed shapes every Alloc reads constant shape components, all fired once
+    by_loc = {}
+    for instr in pl["eg"].instrs:
+        by_loc[instr.write_loc.index] = instr
+    for instr in pl["eg"].instrs:
+        if isinstance(instr, compilation.Alloc):
+            for loc in instr.read_locs:
+                src = by_loc[loc.index]
+                assert isinstance(src.op, core.Constant) and src.once
+    kinds = set(type(i).__name__ for i in pl["eg"].instrs)
+    assert kinds == {"LoadArgument", "Alloc", "BuildTup", "ReturnByRef", "ReturnByVal"}
+
+
+def test_update_is_ordered_after_other_readers_of_the_variable():
+    """Updates listed last-layer-first: the dgrad product that still needs the old last-layer weight
+    must be scheduled before the in-place update of that weight."""
+    x = cgt.matrix("x", fixed_shape=(5, 4))
+    w1 = nn.parameter(np.random.RandomState(0).randn(4, 3).astype("f4"), name="w1")
+    w2 = nn.parameter(np.random.RandomState(1).randn(3, 2).astype("f4"), name="w2")
+    loss = cgt.tanh(cgt.tanh(x.dot(w1)).dot(w2)).sum()
+    g1, g2 = cgt.grad(loss, [w1, w2])
+    updates = [(w2, w2 - 0.1 * g2), (w1, w1 - 0.1 * g1)]  # reversed on purpose
+    cfg = configs.Config("t", [x], loss, [w1, w2], updates, None, 5)
+    pl = _plan(cfg)
+    order = pl["order"]
+    pos = {n: i for (i, n) in enumerate(order)}
+    w2_node = pl["srcs"][0]
+    w2_update = pl["targs"][0]
+    readers = [n for n in order if w2_node in n.parents and n is not w2_update]
+    assert readers and all(pos[r] < pos[w2_update] for r in readers)
+    # and the oracle (which applies updates after evaluating everything) agrees with plain numpy
+    f = cpu_backend.function([x], loss, updates=updates)
+    xv = np.random.RandomState(2).randn(5, 4).astype("f4")
+    f(xv)
+    h = np.tanh(xv @ w1.op.get_value())
+    o = np.tanh(h @ w2.op.get_value())
+    go = 1 - o * o
+    gh = (go @ w2.op.get_value().T) * (1 - h * h)
+    np.testing.assert_allclose(f.get_value(w1), w1.op.get_value() - 0.1 * (xv.T @ gh), rtol=1e-5, atol=1e-6)
+
+
+def test_all_configs_build_and_run_on_the_oracle():
+    small = {"mlp": dict(batch=8), "cifar": dict(batch=2), "wide": dict(batch=2), "lstm": dict(seq_len=3, batch=4),
+             "vae": dict(batch=5)}
+    for (name, kw) in small.items():
+        cfg = configs.BUILDERS[name](**kw)
+        f = cpu_backend.function(cfg.inputs, [cfg.loss] + cfg.extra_outputs, updates=cfg.updates)
+        b = cfg.batch(0)
+        l0 = float(f(*b)[0])
+        l1 = float(f(*b)[0])
+        assert np.isfinite(l0) and np.isfinite(l1) and l0 != l1, name
+
+
+# ------------------------------------------------------------------------------------------------
+# Ops that carry C++ source (reference: NativeCompileInfo with $function / $closure templating)
+# ------------------------------------------------------------------------------------------------
+class ScaleBy(core.Op):
+    """User-defined Op in the style of the reference's tests (cgt/tests/test_multi_output.py:32-58)."""
+    available_impls = ("native_cpu",)
+
+    def __init__(self, factor):
+        self.factor = factor
+
+    def typ_apply(self, input_types):
+        return input_types[0]
+
+    def shp_apply(self, inputs):
+        return cgt.shape(inputs[0])
+
+    def get_native_compile_info(self, input_types, devtype):
+        code = r"""
+            CGT_EXPORT_C void $function($closure* cl, cgtArray** reads, cgtArray* write) {
+                for (long i = 0; i < reads[0]->size(); ++i) write->at<float>(i) = cl->factor * reads[0]->at<float>(i);
+            }"""
+        return core.NativeCompileInfo(code, closure_triples=[("factor", ctypes.c_float, self.factor)])
+
+
+def test_op_with_cpp_source_is_compiled_and_callable():
+    op = ScaleBy(2.5)
+    callable_ = compilation.get_native_callable(op, [core.TensorType("f4", 1)], "cpu")
+    x = np.arange(5, dtype="f4")
+    out = np.zeros(5, "f4")
+    callable_.call([x], out)
+    assert np.array_equal(out, 2.5 * x)
+    # the library is cached under its hash
+    again = compilation.get_native_callable(ScaleBy(2.5), [core.TensorType("f4", 1)], "cpu")
+    assert ctypes.cast(again.fptr, ctypes.c_void_p).value == ctypes.cast(callable_.fptr, ctypes.c_void_p).value
+
+
+# ------------------------------------------------------------------------------------------------
+# configuration
+# ------------------------------------------------------------------------------------------------
+def test_config_flags_and_scopes(monkeypatch):
+    assert cgt.get_config()["backend"] == "native"
+    with cgt.scoped_update_config(precision="double", verbose=True):
+        assert cgt.floatX == "f8" and cgt.get_config()["verbose"] is True
+        assert cgt.matrix().dtype == "f8"
+    assert cgt.floatX == "f4" and cgt.get_config()["verbose"] is False
+    with pytest.raises(ValueError):
+        cgt.update_config(no_such_option=1)
+    monkeypatch.setenv("CGT_FLAGS", "use_cuda_graphs=False,num_threads=3")
+    try:
+        cfg = core.get_config(True)
+        assert cfg["use_cuda_graphs"] is False and cfg["num_threads"] == 3
+    finally:
+        monkeypatch.delenv("CGT_FLAGS")
+        core.get_config(True)
