@@ -110,11 +110,11 @@ __device__ __forceinline__ uint32_t tile_off(int row, int k) {
 // Operand tiles travel global -> registers -> shared memory in two steps so that the loads of the
 // next K block are in flight while the current one is split and stored. Three access patterns, fixed
 // at compile time per operand:
-//   MODE 0  rows contiguous in memory (a transposed source): threads along rows, 16 k per thread;
+//   MODE 0  rows contiguous in memory (a transposed source): threads along rows, 4 k per unit;
 //   MODE 1  K contiguous: lanes along k, one 128-byte row segment per warp instruction;
 //   MODE 2  K contiguous and 16-byte aligned: 128-bit loads, 8 lanes per row.
-// NV is the number of register slots a thread owns for the tile (16 for the 128-row X tile, 16 or 32
-// for the Y tile). Everything that does not change from one K block to the next -- the thread's row
+// NV is the number of register slots a thread owns for the tile (16 for the 128-row X tile, R/8 with a
+// minimum of 4 for an R-row Y tile). Everything that does not change from one K block to the next -- the thread's row
 // pointer, its shared-memory offset, which of its slots fall inside the matrix -- is computed once.
 template <int MODE, int NV>
 struct TileLoader {
@@ -157,11 +157,12 @@ struct TileLoader {
       p0 = base;
       step = ld;
       off0 = 0;
+      // unit q -> (row = q % R, k quad = q / R in 0..7); a thread owns units tid, tid + 256, ...
 #pragma unroll
-      for (int pr = 0; pr < NV / 16; ++pr) {
-        int q = tid + kLoaderThreads * pr;
-        int khalf = q / R, r = q - khalf * R;
-        if (khalf < 2 && row0 + r < op.rows) valid |= 1u << pr;
+      for (int un = 0; un < NV / 4; ++un) {
+        int q = tid + kLoaderThreads * un;
+        int kq = q / R, r = q - kq * R;
+        if (kq < 8 && row0 + r < op.rows) valid |= 1u << un;
       }
     }
   }
@@ -197,14 +198,14 @@ struct TileLoader {
       }
     } else {
 #pragma unroll
-      for (int pr = 0; pr < NV / 16; ++pr) {
-        int q = tid + kLoaderThreads * pr;
-        int khalf = q / R, r = q - khalf * R;
-        const bool rin = (valid >> pr) & 1u;
-        const float* p = base + (k0 + khalf * 16) * ld + row0 + r;
+      for (int un = 0; un < NV / 4; ++un) {
+        int q = tid + kLoaderThreads * un;
+        int kq = q / R, r = q - kq * R;
+        const bool rin = (valid >> un) & 1u;
+        const float* p = base + (k0 + kq * 4) * ld + row0 + r;
 #pragma unroll
-        for (int u = 0; u < 16; ++u) {
-          v[16 * pr + u] = (rin && (full || k0 + khalf * 16 + u < k_end)) ? __ldg(p) : 0.f;
+        for (int u = 0; u < 4; ++u) {
+          v[4 * un + u] = (rin && (full || k0 + kq * 4 + u < k_end)) ? __ldg(p) : 0.f;
           p += ld;
         }
       }
@@ -241,21 +242,18 @@ struct TileLoader {
       }
     } else {
 #pragma unroll
-      for (int pr = 0; pr < NV / 16; ++pr) {
-        int q = tid + kLoaderThreads * pr;
-        int khalf = q / R, r = q - khalf * R;
-        if (khalf < 2) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint4 h, l;
-            split_tf32(v[16 * pr + 4 * c + 0], h.x, l.x);
-            split_tf32(v[16 * pr + 4 * c + 1], h.y, l.y);
-            split_tf32(v[16 * pr + 4 * c + 2], h.z, l.z);
-            split_tf32(v[16 * pr + 4 * c + 3], h.w, l.w);
-            const uint32_t off = tile_off(r, khalf * 16 + 4 * c);
-            *reinterpret_cast<uint4*>(s_hi + off) = h;
-            *reinterpret_cast<uint4*>(s_lo + off) = l;
-          }
+      for (int un = 0; un < NV / 4; ++un) {
+        int q = tid + kLoaderThreads * un;
+        int kq = q / R, r = q - kq * R;
+        if (kq < 8) {
+          uint4 h, l;
+          split_tf32(v[4 * un + 0], h.x, l.x);
+          split_tf32(v[4 * un + 1], h.y, l.y);
+          split_tf32(v[4 * un + 2], h.z, l.z);
+          split_tf32(v[4 * un + 3], h.w, l.w);
+          const uint32_t off = tile_off(r, kq * 4);
+          *reinterpret_cast<uint4*>(s_hi + off) = h;
+          *reinterpret_cast<uint4*>(s_lo + off) = l;
         }
       }
     }
@@ -287,6 +285,7 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
 
 template <int XMODE, int YMODE, int YNV, int DEPTH>
 __global__ void __launch_bounds__(kThreads, (YNV <= 16 ? 2 : 1)) sgemm_tc_kernel(const Params p) {
+  static_assert(YNV % 4 == 0 && YNV >= 4, "Y slots come in quads");
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kMaxStages];
   __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
@@ -511,7 +510,7 @@ int sgemm_tc(int tA, int tB, long P, long M, long N, long K, const float* A, lon
   p.X = p.swapped ? opB : opA;
   p.Y = p.swapped ? opA : opB;
   long ydim = p.Y.rows;
-  int ytiles = (int)cgtb_ceil_div(ydim, 256);
+  int ytiles = (int)cgtb_ceil_div(ydim, 128);  // tiles of at most 128 columns keep two CTAs resident per SM
   int UN = (int)(cgtb_ceil_div(cgtb_ceil_div(ydim, ytiles), 16) * 16);
   if (UN < 16) UN = 16;
   ytiles = (int)cgtb_ceil_div(ydim, UN);
@@ -563,20 +562,23 @@ int sgemm_tc(int tA, int tB, long P, long M, long N, long K, const float* A, lon
   dim3 grid((unsigned)xtiles, (unsigned)ytiles, (unsigned)(P * nsplit));
   const int cap = 227 * 1024 - 2048;
   // one instantiation per (X access pattern, Y access pattern, Y register slots)
+#define TC_LAUNCH(XM, YM, NVY, DEP)                                                                                \
+  {                                                                                                                \
+    static bool cfg = false;                                                                                       \
+    if (!cfg) { CGTB_CUDA_TRY(cudaFuncSetAttribute(sgemm_tc_kernel<XM, YM, NVY, DEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap)); cfg = true; } \
+    CGTB_LAUNCH((sgemm_tc_kernel<XM, YM, NVY, DEP>), grid, kThreads, smem, p);                                      \
+  }
+  // Y register slots = UN/8 (minimum 4); small Y tiles leave room for a third register buffer
 #define TC_CASE(XM, YM)                                                                                            \
   if (p.X.mode == XM && p.Y.mode == YM) {                                                                          \
-    if (UN <= 128) {                                                                                               \
-      static bool cfg = false;                                                                                     \
-      if (!cfg) { CGTB_CUDA_TRY(cudaFuncSetAttribute(sgemm_tc_kernel<XM, YM, 16, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap)); cfg = true; } \
-      CGTB_LAUNCH((sgemm_tc_kernel<XM, YM, 16, 2>), grid, kThreads, smem, p);                                       \
-    } else {                                                                                                       \
-      static bool cfg = false;                                                                                     \
-      if (!cfg) { CGTB_CUDA_TRY(cudaFuncSetAttribute(sgemm_tc_kernel<XM, YM, 32, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap)); cfg = true; } \
-      CGTB_LAUNCH((sgemm_tc_kernel<XM, YM, 32, 2>), grid, kThreads, smem, p);                                       \
-    }                                                                                                              \
+    if (UN <= 32) TC_LAUNCH(XM, YM, 4, 3)                                                                          \
+    else if (UN <= 64) TC_LAUNCH(XM, YM, 8, 3)                                                                     \
+    else if (UN <= 128) TC_LAUNCH(XM, YM, 16, 2)                                                                   \
+    else TC_LAUNCH(XM, YM, 32, 2)                                                                                  \
   }
   TC_CASE(0, 0) TC_CASE(0, 1) TC_CASE(0, 2) TC_CASE(1, 0) TC_CASE(1, 1) TC_CASE(1, 2) TC_CASE(2, 0) TC_CASE(2, 1) TC_CASE(2, 2)
 #undef TC_CASE
+#undef TC_LAUNCH
   if (nsplit > 1) {
     long total = P * M * N;
     long blocks = std::min<long>(cgtb_ceil_div(total, 256), (long)rt().sm_count * 8);
