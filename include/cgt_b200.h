@@ -154,6 +154,18 @@ int cgtb_binary(int op, int dt_x, int dt_y, int dt_out, long n, const void* x, c
 /* Sum / Max over a set of axes, keepdims (cgt/core.py:1663-1738) */
 int cgtb_reduce(int kind, int dtype, int ndim, const long* shape, const int* reduced, const void* in, void* out);
 
+/* No counterpart in the reference. Sum (kind 0) or Max (kind 1) of a float32 array viewed as
+ * [R0, K, R1] over R0 and R1, out[K], for callers that must not allocate device or host memory at call
+ * time (latency-critical callbacks, processes whose device memory belongs to another allocator).
+ * Same bits as cgtb_reduce on that layout. The partial results live in one fixed 128 KiB array in
+ * device memory that every call shares: the first call per device looks its address up (set-up work,
+ * do it before any stream capture); calls that overlap in time race on the array, calls issued in
+ * sequence on the runtime stream do not; nothing in the array has to be cleared between calls.
+ * Refused with an error: K > CGTB_REDUCE_STATIC_MAX_K, R0 or R1 >= 2^30. */
+#define CGTB_REDUCE_STATIC_MAX_K 8192
+int cgtb_reduce_rkr_f32_static(int kind, long R0, long K, long R1, const float* in, float* out);
+long cgtb_reduce_static_max_k(void);
+
 /* Repeat, Transpose, GetSli, IncSli, GetFlatIndices, IncFlatIndices, Concatenate, Fill
  * (cgt/core.py:1511-1594, 1767-1861, 1960-2023, 1467-1509, 966-1007) */
 int cgtb_repeat(int dtype, int ndim, const long* out_shape, const int* repeated, const void* in, void* out);
