@@ -1,0 +1,56 @@
+"""Data parallelism on real GPUs: two ranks, one B200 each, gradients summed by the NCCL AllReduce Op.
+The two ranks with half a batch each must end with the same parameters as one GPU with the whole
+batch (float32 tolerance: the mean of two half-batch gradients rounds differently), and the replicas
+must stay bit-identical to each other. Skipped on a box with fewer than two GPUs."""
+import json
+import os
+import os.path as osp
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from cgt_b200 import configs
+import cgt_b200 as cgt
+from tests.test_parallel_cpu import _free_port
+
+pytestmark = pytest.mark.gpu
+HERE = osp.dirname(osp.abspath(__file__))
+
+
+def _n_gpus():
+    import torch
+    return torch.cuda.device_count()
+
+
+@pytest.mark.parametrize("config", ["mlp", "cifar"])
+def test_two_gpu_ranks_match_one_gpu(rt, tmp_path, config):
+    if _n_gpus() < 2:
+        pytest.skip("needs two GPUs")
+    world, per_rank = 2, 8
+    port = _free_port()
+    procs = []
+    for rank in range(world):
+        env = dict(os.environ, RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port), DP_OUT=str(tmp_path / "params"), DP_BACKEND="gpu", DP_CONFIG=config)
+        procs.append(subprocess.Popen([sys.executable, osp.join(HERE, "dp_worker.py")], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.PIPE, text=True))
+    outs = []
+    for p in procs:
+        so, se = p.communicate(timeout=300)
+        assert p.returncode == 0, se[-3000:]
+        outs.append(json.loads(so.strip().splitlines()[-1]))
+    assert all(o["n_allreduce"] == 1 for o in outs)
+    p0 = np.load(str(tmp_path / "params") + ".0.npz")
+    p1 = np.load(str(tmp_path / "params") + ".1.npz")
+    for k in p0.files:
+        assert np.array_equal(p0[k], p1[k])
+    build = getattr(configs, "build_" + config)
+    cfg = build(batch=per_rank * world)
+    f = cgt.function(cfg.inputs, [cfg.loss], updates=cfg.updates)
+    losses = [float(f(*cfg.batch(step))[0]) for step in range(3)]
+    for (k, p) in zip(p0.files, cfg.params):
+        np.testing.assert_allclose(p0[k], p.op.get_value(), rtol=1e-3, atol=1e-5)
+    for step in range(3):
+        np.testing.assert_allclose(np.mean([o["losses"][step] for o in outs]), losses[step], rtol=1e-3)
