@@ -1,5 +1,7 @@
-// Mul22 / BatchedMul22 entry points: choose between the tcgen05 tensor-core kernel (3xTF32 split
-// precision, gemm_tcgen05.cu) and the fp32 FMA kernel (gemm_simt.cu).
+// Mul22 / BatchedMul22 entry points: choose between the tcgen05 tensor-core kernels (3xTF32 split
+// precision; TMA-fed for 16-byte-aligned operands, gemm_tma.cu, register-fed otherwise,
+// gemm_tcgen05.cu) and the fp32 FMA kernel (gemm_simt.cu).
+// impl: 0 automatic, 1 FMA, 2 tensor cores (either feed), 3 register-fed only, 4 TMA-fed only.
 #include "runtime.h"
 
 namespace cgtb {
@@ -9,13 +11,20 @@ int sgemm_simt(int tA, int tB, long P, long M, long N, long K, const float* A, l
 int sgemm_tc(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B,
              long ldb, long strideB, float* C, long ldc, long strideC);
 
+int sgemm_tma(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B,
+              long ldb, long strideB, float* C, long ldc, long strideC);
+
 int sgemm_dispatch(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B,
                    long ldb, long strideB, float* C, long ldc, long strideC, int impl) {
   if (!require_runtime("sgemm")) return 1;
   if (impl != 1) {
-    int rc = sgemm_tc(tA, tB, P, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC);
+    int rc = -1;
+    if (impl != 3) rc = sgemm_tma(tA, tB, P, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC);
     if (rc >= 0) return rc;
-    if (impl == 2) return fail("sgemm: shape M=%ld N=%ld K=%ld is not supported by the tensor-core kernel", M, N, K);
+    if (impl == 4) return fail("sgemm: M=%ld N=%ld K=%ld with these strides is not eligible for the TMA-fed kernel", M, N, K);
+    rc = sgemm_tc(tA, tB, P, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC);
+    if (rc >= 0) return rc;
+    if (impl >= 2) return fail("sgemm: shape M=%ld N=%ld K=%ld is not supported by the tensor-core kernel", M, N, K);
   }
   return sgemm_simt(tA, tB, P, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC);
 }

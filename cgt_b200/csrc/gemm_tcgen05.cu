@@ -15,7 +15,8 @@
 //     combinations feed the same MMA configuration (a transposed source is transposed on the way in),
 //     and zero-fills ragged edges. Each thread keeps the loads of the next two or three K blocks in
 //     flight in registers while the current one is split and stored.
-//   * Warp 8: one thread issues the MMAs (12 per 32-deep K block: 4 K steps x 3 split terms) and
+//   * Warp 8 issues the MMAs through one elected lane (8 per 32-deep K block: per K step
+//     x_hi * [y_hi | y_lo] as one instruction with 2*UN accumulator columns, and x_lo * y_hi) and
 //     commits them to the stage's "empty" mbarrier; the warp owns the TMEM allocation.
 //   * After the last K block the eight loader warps become the epilogue: tcgen05.ld the accumulator
 //     (lane = tile row; the two warps of a lane quarter take alternate 16-column chunks), stage it in
@@ -28,19 +29,17 @@
 // Roofline: the configuration's products are skinny (N of 32..64 outputs per 75..800-long row), so
 // they are bound by streaming A from HBM, not by the tensor pipe: 4*(M*K + K*N + M*N) bytes per call.
 #include "runtime.h"
+#include "tc_util.h"
 
 using namespace cgtb;
+using namespace cgtb::tc;
 
 namespace {
 
 constexpr int kLoaderWarps = 8;
 constexpr int kLoaderThreads = kLoaderWarps * 32;
 constexpr int kThreads = kLoaderThreads + 32;  // 8 loader/epilogue warps + 1 MMA warp
-constexpr int kBK = 32;                // K depth of one stage: 32 floats = one 128-byte swizzle row
-constexpr int kXRows = 128;            // UMMA M
 constexpr int kMaxStages = 4;
-constexpr uint32_t kSpinLimit = 1u << 24;
-constexpr long long kWaitCycles = 2000000000LL;  // about one second of SM clock: far beyond any legitimate wait
 
 struct Operand {
   const float* base;
@@ -66,46 +65,6 @@ struct Params {
   int tmem_cols;
   int* err;          // host-mapped error flag
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-// bounded wait: false when the phase did not complete within the spin limit
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  const long long t0 = clock64();
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-    if ((spin & 1023u) == 1023u && clock64() - t0 > kWaitCycles) return false;
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.b32 %0, 1, 0, p;\n\t}"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    if (done) return true;
-  }
-  return false;
-}
-
-// Branch-free 3xTF32 split. Non-finite inputs keep hi = x and lo = 0 so that inf stays inf.
-__device__ __forceinline__ void split_tf32(float x, uint32_t& hi, uint32_t& lo) {
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
-  float r = x - __uint_as_float(hi);
-  r = (fabsf(r) <= 3.0e38f) ? r : 0.f;  // x or hi is inf/nan
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(r));
-}
-
-// byte offset of element (row, k) inside a K-major tile with 128-byte rows and the 128B swizzle:
-// 16-byte chunk index XOR (row mod 8); 8-row groups are 1024 bytes apart
-__device__ __forceinline__ uint32_t tile_off(int row, int k) {
-  return (uint32_t)row * 128u + ((((uint32_t)k >> 2) ^ ((uint32_t)row & 7u)) << 4) + (((uint32_t)k & 3u) << 2);
-}
 
 // Operand tiles travel global -> registers -> shared memory in two steps so that the loads of the
 // next K block are in flight while the current one is split and stored. Three access patterns, fixed
@@ -231,10 +190,7 @@ struct TileLoader {
       for (int u = 0; u < NV / 4; ++u) {
         if (r0 + kLoaderWarps * 4 * u < R) {
           uint4 h, l;
-          split_tf32(v[4 * u + 0], h.x, l.x);
-          split_tf32(v[4 * u + 1], h.y, l.y);
-          split_tf32(v[4 * u + 2], h.z, l.z);
-          split_tf32(v[4 * u + 3], h.w, l.w);
+          split_tf32x4(v[4 * u + 0], v[4 * u + 1], v[4 * u + 2], v[4 * u + 3], h, l);
           const uint32_t off = off0 + (uint32_t)u * 4096u;
           *reinterpret_cast<uint4*>(s_hi + off) = h;
           *reinterpret_cast<uint4*>(s_lo + off) = l;
@@ -247,10 +203,7 @@ struct TileLoader {
         int kq = q / R, r = q - kq * R;
         if (kq < 8) {
           uint4 h, l;
-          split_tf32(v[4 * un + 0], h.x, l.x);
-          split_tf32(v[4 * un + 1], h.y, l.y);
-          split_tf32(v[4 * un + 2], h.z, l.z);
-          split_tf32(v[4 * un + 3], h.w, l.w);
+          split_tf32x4(v[4 * un + 0], v[4 * un + 1], v[4 * un + 2], v[4 * un + 3], h, l);
           const uint32_t off = tile_off(r, kq * 4);
           *reinterpret_cast<uint4*>(s_hi + off) = h;
           *reinterpret_cast<uint4*>(s_lo + off) = l;
@@ -259,29 +212,6 @@ struct TileLoader {
     }
   }
 };
-
-// shared-memory matrix descriptor: K-major, SWIZZLE_128B, 8-row groups 1024 bytes apart
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((saddr >> 4) & 0x3FFFu);      // start address, 16-byte units
-  d |= (uint64_t)1 << 16;                       // leading byte offset (unused for swizzled K-major)
-  d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset between 8-row groups
-  d |= (uint64_t)1 << 46;                       // descriptor version for sm_100
-  d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
-  return d;
-}
-
-__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
-      : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
 
 template <int XMODE, int YMODE, int YNV, int DEPTH>
 __global__ void __launch_bounds__(kThreads, (YNV <= 16 ? 2 : 1)) sgemm_tc_kernel(const Params p) {
@@ -396,9 +326,11 @@ __global__ void __launch_bounds__(kThreads, (YNV <= 16 ? 2 : 1)) sgemm_tc_kernel
             : "r"(taddr)
             : "memory");
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        uint32_t r2[16];
+        tmem_ld16(taddr + (uint32_t)UN, r2);  // columns [UN, 2UN) hold the x_hi * y_lo term
         float* dst = stg + (quarter * 32 + lane) * stride + c0;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) dst[j] = __uint_as_float(r[j]);
+        for (int j = 0; j < 16; ++j) dst[j] = __uint_as_float(r[j]) + __uint_as_float(r2[j]);
       }
       asm volatile("bar.sync 1, %0;" ::"n"(kLoaderThreads) : "memory");
       float* cbase = (p.nsplit > 1) ? p.C + ((long)batch * p.nsplit + split) * p.M * p.N : p.C + batch * p.c_batch_stride;
@@ -423,10 +355,12 @@ __global__ void __launch_bounds__(kThreads, (YNV <= 16 ? 2 : 1)) sgemm_tc_kernel
         }
       }
     }
-  } else if (lane == 0) {
-    // ------------------------------------------------ MMA issuer (one thread)
-    // instruction descriptor: D fp32, A/B tf32, both K-major, N = UN, M = 128
-    const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(UN >> 3) << 17) | ((uint32_t)(kXRows >> 4) << 24);
+  } else {
+    // ------------------------------------------------ MMA issuer
+    // The whole warp runs the loop so that descriptors and addresses stay warp-uniform (uniform
+    // registers feed tcgen05.mma directly); one elected lane issues. Two instructions per K step:
+    // x_hi * [y_hi | y_lo] into accumulator columns [0, 2UN) and x_lo * y_hi into columns [0, UN).
+    const uint32_t idesc1 = make_idesc_tf32(UN), idesc2 = make_idesc_tf32(2 * UN);
     for (int kb = 0; kb < nkb && ok; ++kb) {
       const int s = kb % S;
       const uint32_t phase = (uint32_t)(kb / S) & 1u;
@@ -435,19 +369,20 @@ __global__ void __launch_bounds__(kThreads, (YNV <= 16 ? 2 : 1)) sgemm_tc_kernel
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t sbase = smem_u32(smem + (size_t)s * stage_bytes);
       const uint64_t dxh = make_desc(sbase), dxl = make_desc(sbase + x_bytes);
-      const uint64_t dyh = make_desc(sbase + 2 * x_bytes), dyl = make_desc(sbase + 2 * x_bytes + y_bytes);
+      const uint64_t dyh = make_desc(sbase + 2 * x_bytes);  // y_lo follows y_hi: one descriptor covers both
 #pragma unroll
       for (int kk = 0; kk < kBK / 8; ++kk) {
         const uint64_t adv = (uint64_t)((kk * 32) >> 4);  // 8 tf32 = 32 bytes along K inside the swizzle row
         const uint32_t first = (kb == 0 && kk == 0) ? 0u : 1u;
-        mma_tf32(tmem_d, dxl + adv, dyh + adv, idesc, first);  // small terms first
-        mma_tf32(tmem_d, dxh + adv, dyl + adv, idesc, 1u);
-        mma_tf32(tmem_d, dxh + adv, dyh + adv, idesc, 1u);
+        mma_tf32_elect(tmem_d, dxh + adv, dyh + adv, idesc2, first);
+        mma_tf32_elect(tmem_d, dxl + adv, dyh + adv, idesc1, 1u);
       }
-      mma_commit(smem_u32(&empty_bar[s]));  // frees the stage once these MMAs have read it
+      if (elect_one()) mma_commit(smem_u32(&empty_bar[s]));  // frees the stage once these MMAs have read it
+      __syncwarp();
     }
-    if (ok && nkb > 0) mma_commit(smem_u32(&accum_bar));
-    if (!ok) { *(volatile int*)p.err = 2; __threadfence_system(); }
+    if (ok && nkb > 0 && elect_one()) mma_commit(smem_u32(&accum_bar));
+    __syncwarp();
+    if (!ok && lane == 0) { *(volatile int*)p.err = 2; __threadfence_system(); }
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -479,6 +414,21 @@ int* g_err_dev = nullptr;
 namespace cgtb {
 
 // Reports (and clears) a time-out raised by the tensor-core kernel. Call after the stream is idle.
+int* tc_error_flag() {
+  if (!g_err_host) {
+    if (cudaHostAlloc((void**)&g_err_host, sizeof(int), cudaHostAllocMapped) != cudaSuccess) { fail("cudaHostAlloc failed"); return nullptr; }
+    *g_err_host = 0;
+    if (cudaHostGetDevicePointer((void**)&g_err_dev, g_err_host, 0) != cudaSuccess) { fail("cudaHostGetDevicePointer failed"); return nullptr; }
+  }
+  return g_err_dev;
+}
+
+void tc_splitk_fold(long P, long M, long N, int nsplit, const float* part, float* C, long ldc, long strideC) {
+  long total = P * M * N;
+  long blocks = std::min<long>(cgtb_ceil_div(total, 256), (long)rt().sm_count * 8);
+  CGTB_LAUNCH(splitk_fold_tc_kernel, (unsigned)blocks, 256, 0, P, M * N, nsplit, part, C, M, N, ldc, strideC);
+}
+
 int sgemm_tc_check() {
   if (g_err_host && *g_err_host) {
     int code = *g_err_host;
@@ -493,11 +443,7 @@ int sgemm_tc(int tA, int tB, long P, long M, long N, long K, const float* A, lon
   if (P <= 0 || M <= 0 || N <= 0) return 0;
   if (K <= 0) return -1;                      // all-zero product: the FMA kernel handles it
   if (M * N < 1024 && K < 256) return -1;     // tiny: not worth a tensor-core launch
-  if (!g_err_host) {
-    if (cudaHostAlloc((void**)&g_err_host, sizeof(int), cudaHostAllocMapped) != cudaSuccess) return fail("cudaHostAlloc failed");
-    *g_err_host = 0;
-    if (cudaHostGetDevicePointer((void**)&g_err_dev, g_err_host, 0) != cudaSuccess) return fail("cudaHostGetDevicePointer failed");
-  }
+  if (!tc_error_flag()) return 1;
   Params p;
   auto mode_of = [](const float* base, long ld, long bstride, int kcontig) {
     if (!kcontig) return 0;
@@ -517,7 +463,7 @@ int sgemm_tc(int tA, int tB, long P, long M, long N, long K, const float* A, lon
   long xtiles = cgtb_ceil_div(p.X.rows, kXRows);
   p.UN = UN;
   p.tmem_cols = 32;
-  while (p.tmem_cols < UN) p.tmem_cols *= 2;
+  while (p.tmem_cols < 2 * UN) p.tmem_cols *= 2;  // hi*hi + lo*hi in [0, UN), hi*lo in [UN, 2UN)
   const long stage_bytes = 2L * kXRows * 128 + 2L * UN * 128;
   long nkb_total = cgtb_ceil_div(K, kBK);
   // split K when the output tiles alone cannot fill the machine
@@ -579,11 +525,7 @@ int sgemm_tc(int tA, int tB, long P, long M, long N, long K, const float* A, lon
   TC_CASE(0, 0) TC_CASE(0, 1) TC_CASE(0, 2) TC_CASE(1, 0) TC_CASE(1, 1) TC_CASE(1, 2) TC_CASE(2, 0) TC_CASE(2, 1) TC_CASE(2, 2)
 #undef TC_CASE
 #undef TC_LAUNCH
-  if (nsplit > 1) {
-    long total = P * M * N;
-    long blocks = std::min<long>(cgtb_ceil_div(total, 256), (long)rt().sm_count * 8);
-    CGTB_LAUNCH(splitk_fold_tc_kernel, (unsigned)blocks, 256, 0, P, M * N, nsplit, part, C, M, N, ldc, strideC);
-  }
+  if (nsplit > 1) tc_splitk_fold(P, M, N, nsplit, part, C, ldc, strideC);
   CGTB_CHECK_LAUNCH("sgemm_tc");
   return 0;
 }

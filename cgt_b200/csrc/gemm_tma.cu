@@ -1,0 +1,490 @@
+// Mul22 / BatchedMul22 for 16-byte-aligned operands: the TMA-fed variant of the tcgen05 3xTF32 GEMM.
+//
+// The products of the configurations are skinny (a 28800 x 800 column matrix against 32 filters), so the
+// kernel is a streaming problem: what matters is how many bytes of the big operand are in flight per
+// SM. Here the tensor-memory accelerator moves raw fp32 tiles global -> shared memory
+// (cp.async.bulk.tensor, completion counted on an mbarrier), so the bytes in flight are set by the
+// depth of a ring of raw stages and not by registers or by what the compiler does with the loads.
+//
+//   warp 9   one thread issues the TMA loads of K block kb into raw stage kb % RS (X tile 128 x 32,
+//            Y tile UN x 32) as soon as that stage has been released;
+//   warps 0-7 convert raw fp32 into the TF32 operands of the 3xTF32 product, in the K-major
+//            128-byte-swizzled layout of the UMMA descriptor, into conversion stage kb % CS:
+//            * a K-contiguous X tile arrives already in that layout (TMA SWIZZLE_128B) and the MMA reads
+//              it in place as x_hi -- the tensor core uses the upper 19 bits of each word, i.e. x with
+//              its low mantissa bits cut -- so only x_lo = x - cut(x) is computed (two fp32-pipe
+//              operations and a mask per element, one 16-byte store per four);
+//            * a row-contiguous X tile (a transposed source) arrives as [k][row] and is transposed by
+//              the conversion's addressing into x_hi and x_lo;
+//            * the small Y tile is always converted into y_hi | y_lo, stored back to back;
+//   warp 8   issues the MMAs through one elected lane of the converged warp (descriptors stay in
+//            uniform registers): per K step x_hi * [y_hi | y_lo] as ONE instruction with 2*UN accumulator
+//            columns, and x_lo * y_hi. Two instructions instead of three matter because a 128 x N x 8
+//            TF32 instruction costs about 45 cycles for every N <= 64. Its commits release the
+//            conversion stage and, for an X tile read in place, the raw stage; it owns the TMEM allocation;
+//   after the last block warps 0-7 are the epilogue: TMEM -> registers, add the two column halves,
+//            store to C or to the split-K slab (float4 rows, or coalesced columns for a swapped tile).
+//
+// What was measured on the way (B200): cvt.rna.tf32.f32 runs on the 16-lane conversion pipe and integer
+// rounding on the 64-lane integer pipe, either of which made the split, not HBM, the limit; one
+// thread issuing tcgen05.mma from divergent code pays ~60 cycles per instruction for moving the
+// descriptors into uniform registers; polling an mbarrier from one lane of a diverged warp starves the
+// working warps, all lanes polling does not.
+//
+// Out-of-range rows and the K tail are zero-filled by the TMA unit. Every wait is bounded and
+// abortable; on expiry the kernel raises the host-mapped flag, the producer waits for its copies in
+// flight, TMEM is freed and the kernel returns.
+//
+// Eligibility (otherwise the register-fed kernel of gemm_tcgen05.cu runs): base addresses 16-byte
+// aligned, leading dimensions and batch strides multiples of 4 floats.
+#include <cuda.h>  // CUtensorMap and its enums; the encoder is looked up at run time, libcuda is not linked
+
+#include "runtime.h"
+#include "tc_util.h"
+
+using namespace cgtb;
+using namespace cgtb::tc;
+
+namespace {
+
+constexpr int kConvWarps = 8;
+constexpr int kConvThreads = kConvWarps * 32;
+constexpr int kThreadsTma = kConvThreads + 64;  // + MMA warp + TMA warp
+constexpr int kMaxRaw = 8;
+constexpr int kMaxConv = 2;
+
+struct TmaParams {
+  float* C;          // output or split-K slab
+  long ldc;
+  long c_batch_stride;
+  int swapped;       // X is op(B): tile row i is product column n
+  long K;
+  long kchunk;       // K elements per split (multiple of kBK)
+  int nsplit;
+  long M, N;
+  long xrows, yrows; // valid rows of X and Y
+  int UN;
+  int raw_stages, conv_stages;
+  int tmem_cols;
+  int* err;
+};
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
+}
+
+// raw K-major tile (already swizzled by the TMA load): linear pass over 16-byte chunks
+__device__ __forceinline__ void convert_kmajor(const unsigned char* raw, unsigned char* hi, unsigned char* lo, int nchunks, int tid) {
+  for (int c0 = tid; c0 < nchunks; c0 += 4 * kConvThreads) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int c = c0 + u * kConvThreads;
+      if (c < nchunks) v[u] = *reinterpret_cast<const uint4*>(raw + (size_t)c * 16);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int c = c0 + u * kConvThreads;
+      if (c < nchunks) {
+        uint4 h, l;
+        split_tf32x4(__uint_as_float(v[u].x), __uint_as_float(v[u].y), __uint_as_float(v[u].z), __uint_as_float(v[u].w), h, l);
+        *reinterpret_cast<uint4*>(hi + (size_t)c * 16) = h;
+        *reinterpret_cast<uint4*>(lo + (size_t)c * 16) = l;
+      }
+    }
+  }
+}
+
+// K-major X tile that the MMA reads in place as the hi operand (the tensor core uses the upper 19 bits
+// of each fp32 word): only lo = x - (x with its 13 low mantissa bits cleared) is computed and stored.
+// No guard is needed: a non-finite x stays non-finite in the raw tile, whatever its lo becomes.
+__device__ __forceinline__ uint32_t lo_of(uint32_t b) {
+  const float r = __fadd_rn(__uint_as_float(b), -__uint_as_float(b & 0xFFFFE000u));
+  return __float_as_uint(r) & 0xFFFFE000u;
+}
+__device__ __forceinline__ void convert_kmajor_lo(const unsigned char* raw, unsigned char* lo, int nchunks, int tid) {
+  for (int c0 = tid; c0 < nchunks; c0 += 4 * kConvThreads) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int c = c0 + u * kConvThreads;
+      if (c < nchunks) v[u] = *reinterpret_cast<const uint4*>(raw + (size_t)c * 16);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int c = c0 + u * kConvThreads;
+      if (c < nchunks) *reinterpret_cast<uint4*>(lo + (size_t)c * 16) = make_uint4(lo_of(v[u].x), lo_of(v[u].y), lo_of(v[u].z), lo_of(v[u].w));
+    }
+  }
+}
+
+// raw [32 k][R rows] tile: unit q -> (row = q % R, k quad = q / R); lanes run along rows on both sides
+__device__ __forceinline__ void convert_mnmajor(const unsigned char* raw, unsigned char* hi, unsigned char* lo, int R, int tid) {
+  const float* src = reinterpret_cast<const float*>(raw);
+  const int units = R * 8;
+  for (int q = tid; q < units; q += kConvThreads) {
+    const int kq = q / R, r = q - kq * R;
+    const float* s = src + (size_t)(4 * kq) * R + r;
+    const float a = s[0], b = s[R], c = s[2 * R], d = s[3 * R];
+    uint4 h, l;
+    split_tf32x4(a, b, c, d, h, l);
+    const uint32_t off = tile_off(r, 4 * kq);
+    *reinterpret_cast<uint4*>(hi + off) = h;
+    *reinterpret_cast<uint4*>(lo + off) = l;
+  }
+}
+
+template <bool XMN, bool YMN>
+__global__ void __launch_bounds__(kThreadsTma, 2)
+sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapY, const TmaParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t raw_full[kMaxRaw];
+  __shared__ __align__(8) uint64_t raw_empty[kMaxRaw];
+  __shared__ __align__(8) uint64_t conv_full[kMaxConv];
+  __shared__ __align__(8) uint64_t conv_empty[kMaxConv];
+  __shared__ __align__(8) uint64_t accum_bar;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int UN = p.UN, RS = p.raw_stages, CS = p.conv_stages;
+  unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t x_bytes = kXRows * 128u, y_bytes = (uint32_t)UN * 128u;
+  constexpr bool XDIRECT = !XMN;  // a K-major X tile is the MMA's hi operand as it lies in the raw stage
+  const uint32_t cx_bytes = XDIRECT ? x_bytes : 2 * x_bytes;  // conversion stage: [X hi] X lo, Y hi, Y lo
+  const uint32_t conv_bytes = cx_bytes + 2 * y_bytes, raw_bytes = x_bytes + y_bytes;
+  unsigned char* conv0 = smem;
+  unsigned char* raw0 = smem + (size_t)CS * conv_bytes;
+
+  const int batch = blockIdx.z / p.nsplit, split = blockIdx.z % p.nsplit;
+  const long x0 = (long)blockIdx.x * kXRows, y0 = (long)blockIdx.y * UN;
+  const long k_begin = (long)split * p.kchunk;
+  const long k_end = (k_begin + p.kchunk < p.K) ? k_begin + p.kchunk : p.K;
+  const int nkb = (int)((k_end - k_begin + kBK - 1) / kBK);
+  volatile int* abortp = &abort_flag;
+
+  if (tid == 0) {
+    for (int s = 0; s < RS; ++s) {
+      mbar_init(smem_u32(&raw_full[s]), 1);
+      mbar_init(smem_u32(&raw_empty[s]), XDIRECT ? 1 : kConvWarps);  // released by the MMAs' commit / by the converters
+    }
+    for (int s = 0; s < CS; ++s) {
+      mbar_init(smem_u32(&conv_full[s]), kConvWarps);
+      mbar_init(smem_u32(&conv_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&accum_bar), 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kConvWarps) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                 "r"((uint32_t)p.tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_d = tmem_base_slot;
+
+  if (warp < kConvWarps) {
+    // ------------------------------------------------ converters
+    bool ok = true;
+    for (int kb = 0; kb < nkb; ++kb) {
+      const int rs = kb % RS, cs = kb % CS;
+      ok = mbar_wait_or_abort(smem_u32(&raw_full[rs]), (uint32_t)(kb / RS) & 1u, abortp);
+      ok = ok && mbar_wait_or_abort(smem_u32(&conv_empty[cs]), ((uint32_t)(kb / CS) & 1u) ^ 1u, abortp);
+      if (!ok) break;
+      const unsigned char* rx = raw0 + (size_t)rs * raw_bytes;
+      const unsigned char* ry = rx + x_bytes;
+      unsigned char* cx = conv0 + (size_t)cs * conv_bytes;
+      unsigned char* cy = cx + cx_bytes;
+      if (XMN) convert_mnmajor(rx, cx, cx + x_bytes, kXRows, tid);
+      else convert_kmajor_lo(rx, cx, kXRows * 8, tid);
+      if (YMN) convert_mnmajor(ry, cy, cy + y_bytes, UN, tid);
+      else convert_kmajor(ry, cy, cy + y_bytes, UN * 8, tid);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(smem_u32(&conv_full[cs]));
+        if (!XDIRECT) mbar_arrive(smem_u32(&raw_empty[rs]));
+      }
+    }
+    // ------------------------------------------------ epilogue
+    if (ok && nkb > 0) ok = mbar_wait_or_abort(smem_u32(&accum_bar), 0, abortp);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (!ok) *abortp = 1;
+    asm volatile("bar.sync 1, %0;" ::"n"(kConvThreads) : "memory");  // the epilogue warps agree on success
+    if (*abortp) {
+      if (tid == 0) { *(volatile int*)p.err = 3; __threadfence_system(); }
+    } else {
+      // Accumulator -> registers -> global memory. A thread owns tile row (quarter*32 + lane) and 8
+      // consecutive columns per chunk (8); columns [0, UN) hold hi*hi + lo*hi and [UN, 2UN) hold hi*lo.
+      const int quarter = warp & 3, colgroup = warp >> 2;
+      const int nchunks = UN / 8;
+      const int row = quarter * 32 + lane;
+      const long i_g = x0 + row;
+      float* cbase = (p.nsplit > 1) ? p.C + ((long)batch * p.nsplit + split) * p.M * p.N : p.C + batch * p.c_batch_stride;
+      const long ld = (p.nsplit > 1) ? p.N : p.ldc;
+      const bool vec_ok = ((ld & 3) == 0) && (((uintptr_t)cbase & 15) == 0);
+      for (int ch = colgroup; ch < nchunks; ch += kConvWarps / 4) {
+        const int c0 = ch * 8;
+        uint32_t r1[8], r2[8];
+        const uint32_t taddr = tmem_d + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+        tmem_ld8(taddr, r1);
+        tmem_ld8(taddr + (uint32_t)UN, r2);
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r1[j]) + __uint_as_float(r2[j]);
+        const long j0 = y0 + c0;
+        if (i_g < p.xrows) {
+          if (!p.swapped) {  // tile row = product row: 32 contiguous bytes per thread
+            float* dst = cbase + i_g * ld + j0;
+            if (vec_ok && j0 + 8 <= p.yrows) {
+              *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+              *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (j0 + j < p.yrows) dst[j] = v[j];
+            }
+          } else {           // tile row = product column: the lanes of a warp write consecutive addresses
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (j0 + j < p.yrows) cbase[(j0 + j) * ld + i_g] = v[j];
+          }
+        }
+      }
+    }
+  } else if (warp == kConvWarps) {
+    // ------------------------------------------------ MMA issuer
+    // The whole warp runs the loop so that descriptors and addresses stay warp-uniform (uniform
+    // registers feed tcgen05.mma directly); one elected lane issues. Two instructions per K step:
+    // x_hi * [y_hi | y_lo] into columns [0, 2UN) and x_lo * y_hi into columns [0, UN).
+    const uint32_t idesc1 = make_idesc_tf32(UN), idesc2 = make_idesc_tf32(2 * UN);
+    bool ok = true;
+    for (int kb = 0; kb < nkb; ++kb) {
+      const int cs = kb % CS;
+      ok = mbar_wait_or_abort(smem_u32(&conv_full[cs]), (uint32_t)(kb / CS) & 1u, abortp);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int rs = kb % RS;
+      const uint32_t sbase = smem_u32(conv0 + (size_t)cs * conv_bytes);
+      const uint64_t dxh = make_desc(XDIRECT ? smem_u32(raw0 + (size_t)rs * raw_bytes) : sbase);
+      const uint64_t dxl = make_desc(XDIRECT ? sbase : sbase + x_bytes);
+      const uint64_t dyh = make_desc(sbase + cx_bytes);  // y_lo follows y_hi: one descriptor covers both
+#pragma unroll
+      for (int kk = 0; kk < kBK / 8; ++kk) {
+        const uint64_t adv = (uint64_t)((kk * 32) >> 4);  // 8 tf32 = 32 bytes along K inside the swizzle row
+        const uint32_t first = (kb == 0 && kk == 0) ? 0u : 1u;
+        mma_tf32_elect(tmem_d, dxh + adv, dyh + adv, idesc2, first);
+        mma_tf32_elect(tmem_d, dxl + adv, dyh + adv, idesc1, 1u);
+      }
+      if (elect_one()) {
+        mma_commit(smem_u32(&conv_empty[cs]));
+        if (XDIRECT) mma_commit(smem_u32(&raw_empty[rs]));
+      }
+      __syncwarp();
+    }
+    if (ok && nkb > 0 && elect_one()) mma_commit(smem_u32(&accum_bar));
+    __syncwarp();
+    if (!ok && lane == 0) { *abortp = 1; *(volatile int*)p.err = 4; __threadfence_system(); }
+  } else if (lane == 0) {
+    // ------------------------------------------------ TMA producer (one thread)
+    int issued = 0;
+    bool ok = true;
+    for (int kb = 0; kb < nkb; ++kb) {
+      const int rs = kb % RS;
+      ok = mbar_wait_or_abort(smem_u32(&raw_empty[rs]), ((uint32_t)(kb / RS) & 1u) ^ 1u, abortp);
+      if (!ok) break;
+      const uint32_t bar = smem_u32(&raw_full[rs]);
+      mbar_arrive_expect_tx(bar, raw_bytes);
+      const int k0 = (int)(k_begin + (long)kb * kBK);
+      const uint32_t dx = smem_u32(raw0 + (size_t)rs * raw_bytes);
+      if (XMN) tma_load_3d(dx, &mapX, (int)x0, k0, batch, bar);
+      else tma_load_3d(dx, &mapX, k0, (int)x0, batch, bar);
+      if (YMN) tma_load_3d(dx + x_bytes, &mapY, (int)y0, k0, batch, bar);
+      else tma_load_3d(dx + x_bytes, &mapY, k0, (int)y0, batch, bar);
+      ++issued;
+    }
+    if (!ok || *abortp) {
+      *abortp = 1;
+      *(volatile int*)p.err = 5;
+      __threadfence_system();
+      // copies already issued still write this CTA's shared memory: wait (bounded) until they have landed
+      for (int j = (issued > RS ? issued - RS : 0); j < issued; ++j) mbar_wait(smem_u32(&raw_full[j % RS]), (uint32_t)(j / RS) & 1u);
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == kConvWarps) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)p.tmem_cols) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encoder() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)ptr;
+    else
+      cudaGetLastError();
+  }
+  return fn;
+}
+
+struct Side {
+  const float* base;
+  long ld;
+  bool mn;        // rows contiguous: element(row, k) = base[k*ld + row]
+  long rows;
+  long bstride;
+};
+
+bool aligned_for_tma(const Side& s, long P) {
+  if (((uintptr_t)s.base & 15) != 0 || (s.ld & 3) != 0 || s.ld <= 0) return false;
+  if (P > 1 && ((s.bstride & 3) != 0 || s.bstride <= 0)) return false;
+  return true;
+}
+
+// 3-d tensor map over (inner, outer, batch); box = one tile of `box_rows` rows by 32 k
+bool encode(CUtensorMap* map, const Side& s, long K, long P, int box_rows) {
+  EncodeTiledFn fn = encoder();
+  if (!fn) return false;
+  cuuint64_t dims[3], strides[2];
+  cuuint32_t box[3], estr[3] = {1, 1, 1};
+  if (s.mn) {
+    dims[0] = (cuuint64_t)s.rows; dims[1] = (cuuint64_t)K;
+    box[0] = (cuuint32_t)box_rows; box[1] = kBK;
+  } else {
+    dims[0] = (cuuint64_t)K; dims[1] = (cuuint64_t)s.rows;
+    box[0] = kBK; box[1] = (cuuint32_t)box_rows;
+  }
+  dims[2] = (cuuint64_t)P;
+  box[2] = 1;
+  strides[0] = (cuuint64_t)s.ld * 4;
+  strides[1] = (cuuint64_t)(P > 1 ? s.bstride : (long)dims[1] * s.ld) * 4;
+  if (dims[0] >= (1ull << 32) || dims[1] >= (1ull << 32) || strides[0] >= (1ull << 40) || strides[1] >= (1ull << 40)) return false;
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)s.base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  s.mn ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+namespace cgtb {
+
+// returns 0 done, 1 error, -1 not eligible (the caller falls back to the register-fed kernel)
+int sgemm_tma(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B, long ldb,
+              long strideB, float* C, long ldc, long strideC) {
+  if (P <= 0 || M <= 0 || N <= 0) return 0;
+  if (K < kBK) return -1;
+  if (M * N < 1024 && K < 256) return -1;
+  if (M >= (1L << 31) || N >= (1L << 31) || K >= (1L << 31)) return -1;
+  Side sA = {A, lda, tA != 0, M, strideA};   // rows of op(A) are m; stored [K, M] when transposed
+  Side sB = {B, ldb, tB == 0, N, strideB};   // rows of op(B)^T are n; stored [K, N] when not transposed
+  if (!aligned_for_tma(sA, P) || !aligned_for_tma(sB, P)) return -1;
+  TmaParams p;
+  p.swapped = (N > M) ? 1 : 0;
+  const Side& X = p.swapped ? sB : sA;
+  const Side& Y = p.swapped ? sA : sB;
+  long ydim = Y.rows;
+  int ytiles = (int)cgtb_ceil_div(ydim, 128);
+  int UN = (int)(cgtb_ceil_div(cgtb_ceil_div(ydim, ytiles), 16) * 16);
+  if (UN < 16) UN = 16;
+  ytiles = (int)cgtb_ceil_div(ydim, UN);
+  long xtiles = cgtb_ceil_div(X.rows, kXRows);
+  p.UN = UN;
+  p.tmem_cols = 32;
+  while (p.tmem_cols < 2 * UN) p.tmem_cols *= 2;  // hi*hi + lo*hi in [0, UN), hi*lo in [UN, 2UN)
+  p.xrows = X.rows;
+  p.yrows = Y.rows;
+  const long cx_bytes = X.mn ? 2L * kXRows * 128 : 1L * kXRows * 128;  // a K-major X is read in place as the hi operand
+  const long conv_bytes = cx_bytes + 2L * UN * 128, raw_bytes = (long)kXRows * 128 + (long)UN * 128;
+  // Two CTAs per SM when one conversion stage and at least two raw stages fit in half of the SM's shared
+  // memory: all tiles of a 1.5-wave grid are then resident at once and share HBM evenly. Otherwise one
+  // CTA per SM with two conversion stages and as many raw stages as fit.
+  int conv_stages, raw_stages;
+  const long half = 110L * 1024 - 1024, whole = 224L * 1024 - 1024;
+  if ((half - 2 * conv_bytes) / raw_bytes >= 3) {
+    conv_stages = 2;
+    raw_stages = (int)std::min<long>(kMaxRaw, (half - 2 * conv_bytes) / raw_bytes);
+  } else if ((half - conv_bytes) / raw_bytes >= 2) {
+    conv_stages = 1;
+    raw_stages = (int)std::min<long>(kMaxRaw, (half - conv_bytes) / raw_bytes);
+  } else {
+    conv_stages = 2;
+    raw_stages = (int)std::min<long>(kMaxRaw, (whole - 2 * conv_bytes) / raw_bytes);
+    if (raw_stages < 2) return -1;
+  }
+  long nkb_total = cgtb_ceil_div(K, kBK);
+  long tiles = xtiles * ytiles * P;
+  int nsplit = 1;
+  long want = (long)rt().sm_count;
+  if (tiles < want && nkb_total >= 8) {
+    nsplit = (int)std::min<long>(cgtb_ceil_div(2 * want, tiles), nkb_total / 4);
+    if (nsplit < 1) nsplit = 1;
+  }
+  long kchunk = cgtb_ceil_div(nkb_total, nsplit) * kBK;
+  nsplit = (int)cgtb_ceil_div(K, kchunk);
+  if ((long)P * nsplit > 65535 || ytiles > 65535) return -1;
+  const long nkb = kchunk / kBK;  // a short K loop needs no deeper rings: smaller CTAs, more of them per SM
+  if (raw_stages > nkb) raw_stages = (int)nkb;
+  if (conv_stages > nkb) conv_stages = (int)nkb;
+  p.conv_stages = conv_stages;
+  p.raw_stages = raw_stages;
+  p.nsplit = nsplit;
+  p.kchunk = kchunk;
+  p.K = K;
+  p.M = M;
+  p.N = N;
+  p.ldc = ldc;
+  p.c_batch_stride = strideC;
+  p.err = tc_error_flag();
+  if (!p.err) return 1;
+  CUtensorMap mapX, mapY;
+  if (!encode(&mapX, X, K, P, kXRows) || !encode(&mapY, Y, K, P, UN)) return -1;
+  float* part = nullptr;
+  if (nsplit > 1) {
+    part = (float*)scratch((size_t)P * nsplit * M * N * sizeof(float));
+    if (!part) return 1;
+    p.C = part;
+  } else {
+    p.C = C;
+  }
+  size_t smem = (size_t)conv_stages * conv_bytes + (size_t)raw_stages * raw_bytes;
+  smem += 1024;
+  dim3 grid((unsigned)xtiles, (unsigned)ytiles, (unsigned)(P * nsplit));
+  const int cap = 227 * 1024 - 2048;
+#define TMA_LAUNCH(XM, YM)                                                                                              \
+  {                                                                                                                     \
+    static bool cfg = false;                                                                                            \
+    if (!cfg) { CGTB_CUDA_TRY(cudaFuncSetAttribute(sgemm_tma_kernel<XM, YM>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap)); cfg = true; } \
+    CGTB_LAUNCH((sgemm_tma_kernel<XM, YM>), grid, kThreadsTma, smem, mapX, mapY, p);                                    \
+  }
+  if (X.mn && Y.mn) TMA_LAUNCH(true, true)
+  else if (X.mn) TMA_LAUNCH(true, false)
+  else if (Y.mn) TMA_LAUNCH(false, true)
+  else TMA_LAUNCH(false, false)
+#undef TMA_LAUNCH
+  if (nsplit > 1) tc_splitk_fold(P, M, N, nsplit, part, C, ldc, strideC);
+  CGTB_CHECK_LAUNCH("sgemm_tma");
+  return 0;
+}
+
+}  // namespace cgtb

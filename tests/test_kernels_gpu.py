@@ -9,6 +9,7 @@ import ctypes
 import numpy as np
 import pytest
 
+from cgt_b200 import runtime
 from oracle import oracle as O
 from tests.gpu_util import Dev, call, code, ints, longs
 
@@ -311,6 +312,76 @@ def test_sgemm(rt, M, N, K, tA, tB, impl):
     scale = np.sqrt(K)
     assert np.abs(got - exact).max() <= 4 * np.abs(want - exact).max() + 1e-5 * scale
     np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-5 * scale)
+
+
+# every extent a multiple of 4 floats, so both tensor-core feeds (4: TMA, 3: registers) accept the operands;
+# ragged against the 128 x UN x 32 tiling, one K block only, split-K (few tiles, long K), several column tiles
+ALIGNED_GEMM_SHAPES = [(128, 12, 256), (900, 32, 800), (32, 76, 4096), (64, 800, 1152), (452, 800, 32), (132, 260, 132),
+                       (2000, 128, 96), (128, 512, 784), (36, 36, 40), (4000, 16, 64)]
+
+
+@pytest.mark.parametrize("M,N,K", ALIGNED_GEMM_SHAPES)
+@pytest.mark.parametrize("tA,tB", [(0, 0), (0, 1), (1, 0), (1, 1)])
+@pytest.mark.parametrize("impl", [4, 3])
+def test_sgemm_tensor_core_feeds(rt, M, N, K, tA, tB, impl):
+    rs = np.random.RandomState(18)
+    A = rs.randn(*((K, M) if tA else (M, K))).astype("f4")
+    B = rs.randn(*((N, K) if tB else (K, N))).astype("f4")
+    A[0, 0] = np.float32(1e20)  # large magnitudes survive the hi/lo split
+    if M > 2:
+        A[(0, 1) if tA else (1, 0)] = np.float32(-3e36)  # beyond the fast split's range: the guarded path
+    want = O.mul22(A, B, tA, tB)
+    dA, dB, dC = Dev(A), Dev(B), Dev(np.full((M, N), np.nan, "f4"))
+    call("cgtb_sgemm", tA, tB, M, N, K, dA.ptr, A.shape[1], dB.ptr, B.shape[1], dC.ptr, N, impl)
+    got = dC.get()
+    exact = (A.T if tA else A).astype("f8") @ (B.T if tB else B).astype("f8")
+    big = np.abs(exact) > 1e15
+    np.testing.assert_allclose(got[big], exact[big], rtol=1e-5)
+    scale = np.sqrt(K)
+    assert np.abs(got - exact)[~big].max() <= 4 * np.abs(want - exact)[~big].max() + 1e-5 * scale
+    np.testing.assert_allclose(got[~big], want[~big], rtol=1e-4, atol=1e-5 * scale)
+
+
+@pytest.mark.parametrize("impl", [4, 3, 0])
+def test_sgemm_batched_strided(rt, impl):
+    rs = np.random.RandomState(19)
+    P, M, N, K = 3, 200, 48, 160
+    A, B = rs.randn(P, M, K).astype("f4"), rs.randn(P, K, N).astype("f4")
+    want = O.batched_mul22(A, B)
+    dA, dB, dC = Dev(A), Dev(B), Dev(shape=(P, M, N), dtype="f4")
+    call("cgtb_sgemm_batched", 0, 0, P, M, N, K, dA.ptr, K, M * K, dB.ptr, N, K * N, dC.ptr, N, M * N, impl)
+    np.testing.assert_allclose(dC.get(), want, rtol=1e-4, atol=1e-4)
+    # a view into wider storage: leading dimensions larger than the extents
+    A2, B2 = rs.randn(M, K + 8).astype("f4"), rs.randn(N, K + 4).astype("f4")
+    dA2, dB2, dC2 = Dev(A2), Dev(B2), Dev(shape=(M, N), dtype="f4")
+    call("cgtb_sgemm", 0, 1, M, N, K, dA2.ptr, K + 8, dB2.ptr, K + 4, dC2.ptr, N, impl)
+    np.testing.assert_allclose(dC2.get(), A2[:, :K].astype("f8") @ B2[:, :K].astype("f8").T, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("impl", [4, 3])
+def test_sgemm_non_finite_inputs_stay_non_finite(rt, impl):
+    rs = np.random.RandomState(20)
+    M, N, K = 256, 32, 64
+    A, B = rs.randn(M, K).astype("f4"), rs.randn(N, K).astype("f4")
+    A[3, 5], A[7, 9], A[200, 63] = np.inf, np.nan, -np.inf
+    A[9, 1] = np.float32(np.frombuffer(np.uint32(0x7F800001).tobytes(), "f4")[0])  # NaN with only low mantissa bits set
+    dA, dB, dC = Dev(A), Dev(B), Dev(shape=(M, N), dtype="f4")
+    call("cgtb_sgemm", 0, 1, M, N, K, dA.ptr, K, dB.ptr, K, dC.ptr, N, impl)
+    got = dC.get()
+    bad = np.zeros(M, bool)
+    bad[[3, 7, 9, 200]] = True
+    assert not np.isfinite(got[bad]).any()
+    assert np.isnan(got[7]).all() and np.isnan(got[9]).all()
+    np.testing.assert_allclose(got[~bad], (A[~bad].astype("f8") @ B.astype("f8").T), rtol=1e-4, atol=1e-4)
+
+
+def test_sgemm_unaligned_is_refused_by_tma_feed(rt):
+    A, B = np.ones((64, 75), "f4"), np.ones((75, 32), "f4")
+    dA, dB, dC = Dev(A), Dev(B), Dev(shape=(64, 32), dtype="f4")
+    rc = runtime.lib().cgtb_sgemm(0, 0, 64, 32, 75, dA.ptr, 75, dB.ptr, 32, dC.ptr, 32, 4)
+    assert rc != 0 and "not eligible" in runtime.last_error()
+    call("cgtb_sgemm", 0, 0, 64, 32, 75, dA.ptr, 75, dB.ptr, 32, dC.ptr, 32, 0)  # automatic choice falls back
+    np.testing.assert_allclose(dC.get(), np.full((64, 32), 75.0, "f4"))
 
 
 def test_sgemm_batched_and_dgemm(rt):
