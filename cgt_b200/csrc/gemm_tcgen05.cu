@@ -393,6 +393,10 @@ __global__ void __launch_bounds__(kThreads, (YNV <= 16 ? 2 : 1)) sgemm_tc_kernel
   }
 }
 
+// Ordered fold of a split-K slab [P][nsplit][M*N] into C. With few splits a thread owns one output and
+// adds the partials in split order. With many splits (a weight gradient whose K is the whole batch)
+// eight threads share an output: thread g adds splits g, g+8, ... in order and the eight sums are
+// combined as a fixed tree, so the result does not depend on scheduling.
 __global__ void splitk_fold_tc_kernel(long P, long MN, int nsplit, const float* __restrict__ part, float* __restrict__ C, long M,
                                       long N, long ldc, long strideC) {
   long total = P * MN;
@@ -403,6 +407,34 @@ __global__ void splitk_fold_tc_kernel(long P, long MN, int nsplit, const float* 
     float acc = src[0];
     for (int s = 1; s < nsplit; ++s) acc += src[(long)s * MN];
     C[p * strideC + m * ldc + n] = acc;
+  }
+}
+constexpr int kFoldGroups = 8;
+__global__ void __launch_bounds__(32 * kFoldGroups) splitk_fold_wide_kernel(long P, long MN, int nsplit, const float* __restrict__ part,
+                                                                           float* __restrict__ C, long M, long N, long ldc,
+                                                                           long strideC) {
+  __shared__ float sums[kFoldGroups][33];
+  const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
+  const long total = P * MN;
+  for (long f0 = (long)blockIdx.x * 32; f0 < total; f0 += (long)gridDim.x * 32) {
+    const long f = f0 + lane;
+    float acc = 0.f;
+    long p = 0, e = 0;
+    if (f < total) {
+      p = f / MN;
+      e = f - p * MN;
+      const float* src = part + (p * nsplit) * MN + e;
+      for (int s = g; s < nsplit; s += kFoldGroups) acc += src[(long)s * MN];
+    }
+    sums[g][lane] = acc;
+    __syncthreads();
+    if (g == 0 && f < total) {
+      const float r = ((sums[0][lane] + sums[1][lane]) + (sums[2][lane] + sums[3][lane])) +
+                      ((sums[4][lane] + sums[5][lane]) + (sums[6][lane] + sums[7][lane]));
+      const long m = e / N, n = e - m * N;
+      C[p * strideC + m * ldc + n] = r;
+    }
+    __syncthreads();
   }
 }
 
@@ -425,8 +457,13 @@ int* tc_error_flag() {
 
 void tc_splitk_fold(long P, long M, long N, int nsplit, const float* part, float* C, long ldc, long strideC) {
   long total = P * M * N;
-  long blocks = std::min<long>(cgtb_ceil_div(total, 256), (long)rt().sm_count * 8);
-  CGTB_LAUNCH(splitk_fold_tc_kernel, (unsigned)blocks, 256, 0, P, M * N, nsplit, part, C, M, N, ldc, strideC);
+  if (nsplit >= 2 * kFoldGroups) {
+    long blocks = std::min<long>(cgtb_ceil_div(total, 32), (long)rt().sm_count * 16);
+    CGTB_LAUNCH(splitk_fold_wide_kernel, (unsigned)blocks, 32 * kFoldGroups, 0, P, M * N, nsplit, part, C, M, N, ldc, strideC);
+  } else {
+    long blocks = std::min<long>(cgtb_ceil_div(total, 256), (long)rt().sm_count * 8);
+    CGTB_LAUNCH(splitk_fold_tc_kernel, (unsigned)blocks, 256, 0, P, M * N, nsplit, part, C, M, N, ldc, strideC);
+  }
 }
 
 int sgemm_tc_check() {

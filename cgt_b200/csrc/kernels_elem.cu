@@ -6,6 +6,7 @@
 // expressions (cgt/core.py:1119-1133, 1141-1151) evaluated with the same promotions: math functions
 // in the input type, sub-expressions with a double literal in double, result narrowed to the output type.
 #include "runtime.h"
+#include "reduce_rkr.h"
 #include <cfloat>
 #include <limits>
 
@@ -265,33 +266,7 @@ __global__ void reduce_finish_kernel(int kind, long osize, int nsplit, const T* 
   }
 }
 
-// Fast path for the layouts the graphs produce: input viewed as [R0, K, R1] with R0 and R1 reduced
-// and K kept (bias gradients Sum{0,2,3} of NCHW, column sums Sum{0}, row sums Sum{1}, full sums).
-// 32-bit index arithmetic without divisions; block (k, split) walks its share of R0 with threads along R1.
-template <typename T>
-__global__ void reduce_rkr_kernel(int kind, int R0, int K, int R1, int r0chunk, int r1chunk, int n1, const T* __restrict__ in,
-                                  T* __restrict__ out, int nsplit) {
-  const int k = blockIdx.x, split = blockIdx.y;
-  const int s0 = split / n1, s1 = split - s0 * n1;  // the split index covers (R0 chunk, R1 chunk)
-  const int a0 = s0 * r0chunk, a1 = min(a0 + r0chunk, R0);
-  const int b0 = s1 * r1chunk, b1 = min(b0 + r1chunk, R1);
-  T acc = red_init<T>(kind);
-  for (int r0 = a0; r0 < a1; ++r0) {
-    const T* row = in + ((size_t)r0 * K + k) * R1;
-    for (int r1 = b0 + threadIdx.x; r1 < b1; r1 += blockDim.x) acc = red_op<T>(kind, acc, row[r1]);
-  }
-  __shared__ T warp_part[32];
-  for (int d = 16; d > 0; d >>= 1) acc = red_op<T>(kind, acc, shfl_down_t<T>(acc, d));
-  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  if (lane == 0) warp_part[wid] = acc;
-  __syncthreads();
-  if (wid == 0) {
-    int nw = blockDim.x >> 5;
-    acc = lane < nw ? warp_part[lane] : red_init<T>(kind);
-    for (int d = 16; d > 0; d >>= 1) acc = red_op<T>(kind, acc, shfl_down_t<T>(acc, d));
-    if (lane == 0) out[(size_t)k * nsplit + split] = acc;
-  }
-}
+// The fast path for an input viewed as [R0, K, R1] with R0 and R1 reduced lives in reduce_rkr.h.
 // [R0, K] with R0 reduced and K contiguous: threads along K, coalesced across columns
 template <typename T>
 __global__ void reduce_rk_kernel(int kind, int R0, int K, const T* __restrict__ in, T* __restrict__ out) {
@@ -351,27 +326,15 @@ static int reduce_launch(int kind, int ndim, const long* shape, const int* reduc
           return 0;
         }
       } else if (K <= 65535) {
-        int threads = R1 >= 256 ? 256 : (R1 >= 64 ? 64 : 32);
-        long want = (long)rt().sm_count * 4;
-        // spread the work of one output over several blocks: first along R0, then along R1
-        long per_k = cgtb_ceil_div(want, K);
-        int n0 = (K < want && R0 > 1) ? (int)std::min<long>(per_k, R0) : 1;
-        int r0chunk = (int)cgtb_ceil_div(R0, n0);
-        n0 = (int)cgtb_ceil_div(R0, r0chunk);
-        int n1 = 1;
-        if ((long)K * n0 < want && R1 > 8192) n1 = (int)std::min<long>(cgtb_ceil_div(want, (long)K * n0), cgtb_ceil_div(R1, 4096));
-        int r1chunk = (int)cgtb_ceil_div(R1, n1);
-        n1 = (int)cgtb_ceil_div(R1, r1chunk);
-        int nsplit = n0 * n1;
-        if (nsplit > 65535) { n1 = 65535 / n0; r1chunk = (int)cgtb_ceil_div(R1, n1); n1 = (int)cgtb_ceil_div(R1, r1chunk); nsplit = n0 * n1; }
-        dim3 grid((unsigned)K, (unsigned)nsplit);
-        if (nsplit == 1) {
-          CGTB_LAUNCH(reduce_rkr_kernel<T>, grid, threads, 0, kind, (int)R0, (int)K, (int)R1, r0chunk, r1chunk, n1, in, out, 1);
+        const rkr::Plan pl = rkr::plan<T>(R0, K, R1, rt().sm_count, in);
+        dim3 grid((unsigned)K, (unsigned)pl.nsplit);
+        if (pl.nsplit == 1) {
+          CGTB_LAUNCH(rkr::partial_kernel<T>, grid, pl.threads, 0, kind, (int)R0, (int)K, (int)R1, pl.r0chunk, pl.r1chunk, pl.n1, pl.vec, pl.cols, in, out, 1);
         } else {
-          T* part = (T*)scratch((size_t)K * nsplit * sizeof(T));
+          T* part = (T*)scratch((size_t)K * pl.nsplit * sizeof(T));
           if (!part) return 1;
-          CGTB_LAUNCH(reduce_rkr_kernel<T>, grid, threads, 0, kind, (int)R0, (int)K, (int)R1, r0chunk, r1chunk, n1, in, part, nsplit);
-          CGTB_LAUNCH(reduce_finish_kernel<T>, (unsigned)cgtb_ceil_div(K, 128), 128, 0, kind, K, nsplit, part, out);
+          CGTB_LAUNCH(rkr::partial_kernel<T>, grid, pl.threads, 0, kind, (int)R0, (int)K, (int)R1, pl.r0chunk, pl.r1chunk, pl.n1, pl.vec, pl.cols, in, part, pl.nsplit);
+          CGTB_LAUNCH(rkr::finish_kernel<T>, (unsigned)cgtb_ceil_div(K, 128), 128, 0, kind, K, pl.nsplit, part, out);
         }
         return 0;
       }

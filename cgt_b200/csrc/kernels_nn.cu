@@ -49,17 +49,38 @@ __global__ void im2col_rows_kernel(const T* __restrict__ x, T* __restrict__ col,
     }
     __syncthreads();
     T* out = col + row * (long)Wo * Z;
-    const int n_out = Wo * Z;
-    // idx -> (w, c) without a division in the loop
-    int w = threadIdx.x / Z;
-    int c = threadIdx.x - w * Z;
-    const int dw = blockDim.x / Z, dc = blockDim.x - dw * Z;
-    for (int idx = threadIdx.x; idx < n_out; idx += blockDim.x) {
-      int win = w * sw + joff[c];
-      out[idx] = (win >= 0 && win < W) ? slab[rowoff[c] + win] : T(0);
-      w += dw;
-      c += dc;
-      if (c >= Z) { c -= Z; w += 1; }
+    // A thread keeps up to four column channels (c = cbase + tid + u*blockDim) with their slab offsets in
+    // registers and walks along w: one shared-memory read, one unsigned range test and one coalesced
+    // store per element.
+    if (Z <= (int)blockDim.x / 2) {
+      // few column channels: G groups of Z threads, group g takes w = g, g + G, ...
+      const int G = blockDim.x / Z, g = threadIdx.x / Z, c = threadIdx.x - g * Z;
+      if (g < G) {
+        const int ro1 = rowoff[c], jo1 = joff[c];
+        for (int w = g; w < Wo; w += G) {
+          const int win = w * sw + jo1;
+          out[(long)w * Z + c] = ((unsigned)win < (unsigned)W) ? slab[ro1 + win] : T(0);
+        }
+      }
+    } else
+    for (int cbase = 0; cbase < Z; cbase += 4 * blockDim.x) {
+      int ro[4], jo[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = cbase + threadIdx.x + u * blockDim.x;
+        ro[u] = c < Z ? rowoff[c] : -1;
+        jo[u] = c < Z ? joff[c] : 0;
+      }
+      for (int w = 0; w < Wo; ++w) {
+        T* orow = out + (long)w * Z + cbase + threadIdx.x;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (ro[u] >= 0) {
+            const int win = w * sw + jo[u];
+            orow[u * blockDim.x] = ((unsigned)win < (unsigned)W) ? slab[ro[u] + win] : T(0);
+          }
+        }
+      }
     }
   }
 }
@@ -122,17 +143,17 @@ CGTB_API int cgtb_im2col(int dtype, const void* x, long B, int C, int H, int W, 
 // which the reference's scatter loop reaches that pixel, so the float sum is bit-identical and no
 // atomics are needed.
 // ================================================================================================
-template <typename T>
-__global__ void col2im_gather_kernel(const T* __restrict__ col, T* __restrict__ im, long total, int C, int H, int W,
+template <typename T, typename I>
+__global__ void col2im_gather_kernel(const T* __restrict__ col, T* __restrict__ im, I total, int C, int H, int W,
                                      int kh, int kw, int ph, int pw, int sh, int sw, int Ho, int Wo) {
   const int Z = C * kh * kw;
-  for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
-    int xw = (int)(idx % W);
-    long t = idx / W;
-    int y = (int)(t % H);
-    t /= H;
-    int c_im = (int)(t % C);
-    long b = t / C;
+  for (I idx = (I)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (I)gridDim.x * blockDim.x) {
+    I t = idx / (I)W;
+    int xw = (int)(idx - t * (I)W);
+    I t2 = t / (I)H;
+    int y = (int)(t - t2 * (I)H);
+    I b = t2 / (I)C;
+    int c_im = (int)(t2 - b * (I)C);
     const T* colb = col + b * (long)Ho * Wo * Z;
     T acc = T(0);
     for (int i = 0; i < kh; ++i) {
@@ -152,13 +173,104 @@ __global__ void col2im_gather_kernel(const T* __restrict__ col, T* __restrict__ 
   }
 }
 
+// Staged variant for images of at most 1024/CG pixels: one block per (image, group of CG channels), one
+// thread per pixel of the group. The block streams its slice of the column matrix exactly once, one
+// output-grid row h at a time (Wo segments of CG*kh*kw contiguous values) through a ring of shared-memory
+// slabs filled by cp.async, from h = Ho-1 down to 0, so that for every pixel the kernel offset
+// i = y + ph - h*sh rises from slab to slab and j rises inside a slab: the (i, j) order of the gather
+// above, bit-identical sums. Lanes run along c, then x: the slab addresses of a warp fall into distinct
+// banks for the usual odd kernels. The result leaves through shared memory as contiguous planes.
+template <typename T, int STAGES>
+__global__ void __launch_bounds__(1024, 2) col2im_image_kernel(const T* __restrict__ col, T* __restrict__ im, int C, int H, int W,
+                                                          int kh, int kw, int ph, int pw, int sh, int sw, int Ho, int Wo,
+                                                          int CG, int ngroups) {
+  extern __shared__ __align__(16) unsigned char smem_img[];
+  T* ring = reinterpret_cast<T*>(smem_img);
+  const int Z = C * kh * kw, CGZ = CG * kh * kw, slab_n = Wo * CGZ;
+  const int b = blockIdx.x / ngroups, g = blockIdx.x - b * ngroups;
+  const int t = threadIdx.x;
+  const int npix = CG * H * W;
+  const int c = t % CG, x = (t / CG) % W, y = t / (CG * W);
+  const bool active = t < npix;
+  const T* colb = col + (size_t)b * Ho * Wo * Z + (size_t)g * CGZ;
+  const int seg16 = CGZ * (int)sizeof(T) / 16;  // 16-byte units per segment
+  auto prefetch = [&](int h, int stage) {
+    if (h >= 0) {
+      unsigned char* dst = reinterpret_cast<unsigned char*>(ring + (size_t)stage * slab_n);
+      const unsigned char* src = reinterpret_cast<const unsigned char*>(colb + (size_t)h * Wo * Z);
+      for (int q = t; q < Wo * seg16; q += blockDim.x) {
+        const int w = q / seg16, r = q - w * seg16;
+        const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst + ((size_t)w * CGZ * sizeof(T) + (size_t)r * 16));
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src + ((size_t)w * Z * sizeof(T) + (size_t)r * 16)) : "memory");
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");  // an empty group keeps the group count uniform
+  };
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) prefetch(Ho - 1 - s, s);
+  T acc = T(0);
+  for (int h = Ho - 1; h >= 0; --h) {
+    const int n = Ho - 1 - h;  // slabs consumed so far
+    prefetch(h - (STAGES - 1), (n + STAGES - 1) % STAGES);
+    asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 1) : "memory");
+    __syncthreads();
+    const int i = y + ph - h * sh;
+    if (active && i >= 0 && i < kh) {
+      const T* base = ring + (size_t)(n % STAGES) * slab_n + (c * kh + i) * kw;
+      if (sw == 1) {  // unit stride: no division, j limited so that 0 <= x + pw - j < Wo
+        const int j0 = max(0, x + pw - (Wo - 1)), j1 = min(kw - 1, x + pw);
+        for (int j = j0; j <= j1; ++j) acc += base[(x + pw - j) * CGZ + j];
+      } else {
+        for (int j = 0; j < kw; ++j) {
+          const int wn = x + pw - j;
+          if (wn < 0) break;
+          const int w = wn / sw;
+          if (w * sw != wn || w >= Wo) continue;
+          acc += base[w * CGZ + j];
+        }
+      }
+    }
+    __syncthreads();  // this slab is the target of the prefetch issued STAGES-1 iterations later
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  T* outb = ring;
+  if (active) outb[(c * H + y) * W + x] = acc;
+  __syncthreads();
+  T* imb = im + ((size_t)b * C + (size_t)g * CG) * H * W;
+  for (int q = t; q < npix; q += blockDim.x) imb[q] = outb[q];
+}
+
 template <typename T>
 static int col2im_launch(const T* col, long B, int C, int H, int W, int kh, int kw, int ph, int pw, int sh, int sw, T* im) {
   int Ho = (H + 2 * ph - kh) / sh + 1, Wo = (W + 2 * pw - kw) / sw + 1;
   long total = B * C * H * W;
   if (total <= 0) return 0;
+  if (Ho > 0 && Wo > 0 && (long)H * W <= 1024 && B * C < (1L << 30)) {
+    // staged kernel: the largest channel group CG dividing C whose pixels fit one block and whose
+    // segments are whole 16-byte units
+    int CG = 0;
+    for (int cand = C; cand >= 1; --cand)
+      if (C % cand == 0 && (long)cand * H * W <= 1024 && ((long)cand * kh * kw * sizeof(T)) % 16 == 0) { CG = cand; break; }
+    constexpr int kStages = 8;  // seven slabs in flight per block: enough bytes outstanding to cover HBM latency
+    if (CG > 0 && ((uintptr_t)col & 15) == 0 && ((long)C * kh * kw * sizeof(T)) % 16 == 0) {
+      const long slab_bytes = (long)Wo * CG * kh * kw * sizeof(T);
+      const size_t smem = (size_t)std::max<long>(kStages * slab_bytes, (long)CG * H * W * sizeof(T));
+      if (smem <= 96 * 1024) {
+        const int threads = (int)(cgtb_ceil_div((long)CG * H * W, 32) * 32);
+        if (smem > 48 * 1024)
+          CGTB_CUDA_TRY(cudaFuncSetAttribute((col2im_image_kernel<T, kStages>), cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        CGTB_LAUNCH((col2im_image_kernel<T, kStages>), (unsigned)(B * (C / CG)), threads, smem, col, im, C, H, W, kh, kw, ph, pw,
+                    sh, sw, Ho, Wo, CG, C / CG);
+        CGTB_CHECK_LAUNCH("col2im");
+        return 0;
+      }
+    }
+  }
   long blocks = std::min<long>(cgtb_ceil_div(total, 256), (long)rt().sm_count * 32);
-  CGTB_LAUNCH(col2im_gather_kernel<T>, (unsigned)blocks, 256, 0, col, im, total, C, H, W, kh, kw, ph, pw, sh, sw, Ho, Wo);
+  if (total < (1L << 31))  // 32-bit index arithmetic: a 64-bit division costs several times a 32-bit one
+    CGTB_LAUNCH((col2im_gather_kernel<T, unsigned>), (unsigned)blocks, 256, 0, col, im, (unsigned)total, C, H, W, kh, kw, ph, pw, sh, sw, Ho, Wo);
+  else
+    CGTB_LAUNCH((col2im_gather_kernel<T, long>), (unsigned)blocks, 256, 0, col, im, total, C, H, W, kh, kw, ph, pw, sh, sw, Ho, Wo);
   CGTB_CHECK_LAUNCH("col2im");
   return 0;
 }
@@ -175,73 +287,100 @@ CGTB_API int cgtb_col2im(int dtype, const void* col, long B, int C, int H, int W
 // ================================================================================================
 // max pool forward (include/pooling.h:24-71). One thread per pooled element; the window is scanned
 // h-major with a strict '>' from (-FLT_MAX, -1), so ties and NaNs resolve exactly as in the CPU loop.
+//
+// Thread layout for both pooling kernels: threadIdx.x runs along the row, threadIdx.y along rows,
+// threadIdx.z over image planes (several small planes share a block), blockIdx.x over plane groups:
+// no thread divides an index. Window extents and strides are template parameters for the common
+// 3x3/2 and 2x2/2 windows (0 = taken from the arguments), which turns the window arithmetic into shifts.
 // ================================================================================================
-template <typename T>
-__global__ void max_pool_kernel(const T* __restrict__ x, T* __restrict__ top, int32_t* __restrict__ mask, long total,
-                                int H, int W, int kh, int kw, int ph, int pw, int sh, int sw, int PH, int PW) {
-  for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
-    int px = (int)(idx % PW);
-    long t = idx / PW;
-    int py = (int)(t % PH);
-    long plane = t / PH;
-    const T* xp = x + plane * (long)H * W;
-    int hstart = py * sh - ph, wstart = px * sw - pw;
-    int hend = min(hstart + kh, H), wend = min(wstart + kw, W);
-    hstart = max(hstart, 0);
-    wstart = max(wstart, 0);
-    T best = T(-FLT_MAX);
-    int besti = -1;
-    for (int h = hstart; h < hend; ++h)
-      for (int w = wstart; w < wend; ++w) {
-        T v = xp[h * W + w];
-        if (v > best) { best = v; besti = h * W + w; }
-      }
-    top[idx] = best;
-    mask[idx] = besti;
-  }
+struct PoolGeom {
+  int H, W, kh, kw, ph, pw, sh, sw, PH, PW;
+};
+
+template <typename T, int KH, int KW, int SH, int SW>
+__global__ void max_pool_kernel(const T* __restrict__ x, T* __restrict__ top, int32_t* __restrict__ mask, long planes,
+                                const PoolGeom g) {
+  const int kh = KH ? KH : g.kh, kw = KW ? KW : g.kw, sh = SH ? SH : g.sh, sw = SW ? SW : g.sw;
+  const int px = blockIdx.z * blockDim.x + threadIdx.x, py = blockIdx.y * blockDim.y + threadIdx.y;
+  const long plane = (long)blockIdx.x * blockDim.z + threadIdx.z;
+  if (px >= g.PW || py >= g.PH || plane >= planes) return;
+  const T* xp = x + plane * (long)g.H * g.W;
+  int hstart = py * sh - g.ph, wstart = px * sw - g.pw;
+  const int hend = min(hstart + kh, g.H), wend = min(wstart + kw, g.W);
+  hstart = max(hstart, 0);
+  wstart = max(wstart, 0);
+  T best = T(-FLT_MAX);
+  int besti = -1;
+  for (int h = hstart; h < hend; ++h)
+    for (int w = wstart; w < wend; ++w) {
+      const T v = xp[h * g.W + w];
+      if (v > best) { best = v; besti = h * g.W + w; }
+    }
+  const long o = (plane * g.PH + py) * g.PW + px;
+  top[o] = best;
+  mask[o] = besti;
 }
 
 // max pool pullback (include/pooling.h:73-104) as a gather: one thread per input pixel visits the
 // pooled windows that can contain it in ascending (ph, pw) order and adds the gradients whose argmax
 // is this pixel; the reference scatter reaches each pixel in the same order.
-template <typename T>
+template <typename T, int KH, int KW, int SH, int SW>
 __global__ void max_pool_pullback_kernel(const int32_t* __restrict__ mask, const T* __restrict__ gtop, T* __restrict__ gx,
-                                         long total, int H, int W, int kh, int kw, int ph, int pw, int sh, int sw,
-                                         int PH, int PW) {
-  for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
-    int w = (int)(idx % W);
-    long t = idx / W;
-    int h = (int)(t % H);
-    long plane = t / H;
-    const int32_t* mp = mask + plane * (long)PH * PW;
-    const T* gp = gtop + plane * (long)PH * PW;
-    // windows with py*sh - ph <= h < py*sh - ph + kh
-    int py0 = (h + ph - kh + 1 <= 0) ? 0 : (h + ph - kh + 1 + sh - 1) / sh;
-    int py1 = min((h + ph) / sh, PH - 1);
-    int px0 = (w + pw - kw + 1 <= 0) ? 0 : (w + pw - kw + 1 + sw - 1) / sw;
-    int px1 = min((w + pw) / sw, PW - 1);
-    const int me = h * W + w;
-    T acc = T(0);
-    for (int py = py0; py <= py1; ++py)
-      for (int px = px0; px <= px1; ++px)
-        if (mp[py * PW + px] == me) acc += gp[py * PW + px];
-    gx[idx] = acc;
-  }
+                                         long planes, const PoolGeom g) {
+  const int kh = KH ? KH : g.kh, kw = KW ? KW : g.kw, sh = SH ? SH : g.sh, sw = SW ? SW : g.sw;
+  const int w = blockIdx.z * blockDim.x + threadIdx.x, h = blockIdx.y * blockDim.y + threadIdx.y;
+  const long plane = (long)blockIdx.x * blockDim.z + threadIdx.z;
+  if (w >= g.W || h >= g.H || plane >= planes) return;
+  const int32_t* mp = mask + plane * (long)g.PH * g.PW;
+  const T* gp = gtop + plane * (long)g.PH * g.PW;
+  // windows with py*sh - ph <= h < py*sh - ph + kh
+  const int hy = h + g.ph - kh + 1, wx = w + g.pw - kw + 1;
+  const int py0 = hy <= 0 ? 0 : (hy + sh - 1) / sh;
+  const int py1 = min((h + g.ph) / sh, g.PH - 1);
+  const int px0 = wx <= 0 ? 0 : (wx + sw - 1) / sw;
+  const int px1 = min((w + g.pw) / sw, g.PW - 1);
+  const int me = h * g.W + w;
+  T acc = T(0);
+  for (int py = py0; py <= py1; ++py)
+    for (int px = px0; px <= px1; ++px)
+      if (mp[py * g.PW + px] == me) acc += gp[py * g.PW + px];
+  gx[(plane * g.H + h) * g.W + w] = acc;
 }
+
+// block (x, y, planes) and grid for a plane of `rows` x `cols` elements
+static void pool_launch_dims(long planes, int rows, int cols, dim3& grid, dim3& block) {
+  int bx = 1;
+  while (bx < 32 && bx < cols) bx *= 2;
+  int by = 1;
+  while (by < 256 / bx && by < rows) by *= 2;
+  int bz = 256 / (bx * by);
+  if (bz > planes) bz = (int)std::max<long>(planes, 1);
+  block = dim3(bx, by, bz);
+  grid = dim3((unsigned)cgtb_ceil_div(planes, bz), (unsigned)cgtb_ceil_div(rows, by), (unsigned)cgtb_ceil_div(cols, bx));
+}
+
+#define CGTB_POOL_DISPATCH(KERNEL, T, ...)                                                             \
+  do {                                                                                                 \
+    if (kh == 3 && kw == 3 && sh == 2 && sw == 2) CGTB_LAUNCH((KERNEL<T, 3, 3, 2, 2>), grid, block, 0, __VA_ARGS__); \
+    else if (kh == 2 && kw == 2 && sh == 2 && sw == 2) CGTB_LAUNCH((KERNEL<T, 2, 2, 2, 2>), grid, block, 0, __VA_ARGS__); \
+    else CGTB_LAUNCH((KERNEL<T, 0, 0, 0, 0>), grid, block, 0, __VA_ARGS__);                                  \
+  } while (0)
 
 CGTB_API int cgtb_max_pool(int dtype, const void* x, long B, int C, int H, int W, int kh, int kw, int ph, int pw, int sh,
                            int sw, int PH, int PW, void* top, int32_t* mask) {
   if (!require_runtime("cgtb_max_pool")) return 1;
   if (kh <= 0 || kw <= 0 || sh <= 0 || sw <= 0) return fail("cgtb_max_pool: kernel and stride must be positive");
-  long total = B * C * PH * PW;
-  if (total <= 0) return 0;
-  long blocks = std::min<long>(cgtb_ceil_div(total, 256), (long)rt().sm_count * 32);
+  const long planes = B * C;
+  if (planes * PH * PW <= 0) return 0;
+  if (planes >= (1L << 31)) return fail("cgtb_max_pool: too many image planes");
+  const PoolGeom g = {H, W, kh, kw, ph, pw, sh, sw, PH, PW};
+  dim3 grid, block;
+  pool_launch_dims(planes, PH, PW, grid, block);
+  if (grid.y > 65535 || grid.z > 65535) return fail("cgtb_max_pool: plane too large");
   if (dtype == cgtb_f4)
-    CGTB_LAUNCH(max_pool_kernel<float>, (unsigned)blocks, 256, 0, (const float*)x, (float*)top, mask, total, H, W, kh, kw,
-                ph, pw, sh, sw, PH, PW);
+    CGTB_POOL_DISPATCH(max_pool_kernel, float, (const float*)x, (float*)top, mask, planes, g);
   else if (dtype == cgtb_f8)
-    CGTB_LAUNCH(max_pool_kernel<double>, (unsigned)blocks, 256, 0, (const double*)x, (double*)top, mask, total, H, W, kh,
-                kw, ph, pw, sh, sw, PH, PW);
+    CGTB_POOL_DISPATCH(max_pool_kernel, double, (const double*)x, (double*)top, mask, planes, g);
   else
     return fail("cgtb_max_pool: unsupported dtype %d", dtype);
   CGTB_CHECK_LAUNCH("max_pool");
@@ -252,15 +391,17 @@ CGTB_API int cgtb_max_pool_pullback(int dtype, const int32_t* mask, const void* 
                                     int H, int W, int kh, int kw, int ph, int pw, int sh, int sw, void* gx) {
   if (!require_runtime("cgtb_max_pool_pullback")) return 1;
   if (kh <= 0 || kw <= 0 || sh <= 0 || sw <= 0) return fail("cgtb_max_pool_pullback: kernel and stride must be positive");
-  long total = B * C * H * W;
-  if (total <= 0) return 0;
-  long blocks = std::min<long>(cgtb_ceil_div(total, 256), (long)rt().sm_count * 32);
+  const long planes = B * C;
+  if (planes * H * W <= 0) return 0;
+  if (planes >= (1L << 31)) return fail("cgtb_max_pool_pullback: too many image planes");
+  const PoolGeom g = {H, W, kh, kw, ph, pw, sh, sw, PH, PW};
+  dim3 grid, block;
+  pool_launch_dims(planes, H, W, grid, block);
+  if (grid.y > 65535 || grid.z > 65535) return fail("cgtb_max_pool_pullback: plane too large");
   if (dtype == cgtb_f4)
-    CGTB_LAUNCH(max_pool_pullback_kernel<float>, (unsigned)blocks, 256, 0, mask, (const float*)gtop, (float*)gx, total, H,
-                W, kh, kw, ph, pw, sh, sw, PH, PW);
+    CGTB_POOL_DISPATCH(max_pool_pullback_kernel, float, mask, (const float*)gtop, (float*)gx, planes, g);
   else if (dtype == cgtb_f8)
-    CGTB_LAUNCH(max_pool_pullback_kernel<double>, (unsigned)blocks, 256, 0, mask, (const double*)gtop, (double*)gx, total,
-                H, W, kh, kw, ph, pw, sh, sw, PH, PW);
+    CGTB_POOL_DISPATCH(max_pool_pullback_kernel, double, mask, (const double*)gtop, (double*)gx, planes, g);
   else
     return fail("cgtb_max_pool_pullback: unsupported dtype %d", dtype);
   CGTB_CHECK_LAUNCH("max_pool_pullback");
@@ -275,16 +416,16 @@ CGTB_API int cgtb_max_pool_pullback(int dtype, const int32_t* mask, const void* 
 //   forward window of channel c : [c - (n-1)/2, c + n - (n-1)/2 - 1]
 //   backward window of channel c: [c - (n - (n+1)/2), c + (n+1)/2 - 1]
 // ================================================================================================
-template <typename T>
-__global__ void lrn_forward_kernel(const T* __restrict__ x, T* __restrict__ top, T* __restrict__ scale, long total,
+template <typename T, typename I>
+__global__ void lrn_forward_kernel(const T* __restrict__ x, T* __restrict__ top, T* __restrict__ scale, I total,
                                    int C, int HW, int size, T alpha_over_size, T negative_beta) {
   const int pre = (size - 1) / 2, post = size - pre - 1;
-  for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
-    int hw = (int)(idx % HW);
-    long t = idx / HW;
-    int c = (int)(t % C);
-    long n = t / C;
-    const T* col = x + n * (long)C * HW + hw;
+  for (I idx = (I)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (I)gridDim.x * blockDim.x) {
+    I t = idx / (I)HW;
+    int hw = (int)(idx - t * (I)HW);
+    I n = t / (I)C;
+    int c = (int)(t - n * (I)C);
+    const T* col = x + (size_t)n * C * HW + hw;
     int lo = max(c - pre, 0), hi = min(c + post, C - 1);
     T acc = T(0);
     for (int k = lo; k <= hi; ++k) {
@@ -297,17 +438,17 @@ __global__ void lrn_forward_kernel(const T* __restrict__ x, T* __restrict__ top,
   }
 }
 
-template <typename T>
+template <typename T, typename I>
 __global__ void lrn_backward_kernel(const T* __restrict__ x, const T* __restrict__ top, const T* __restrict__ scale,
-                                    const T* __restrict__ gtop, T* __restrict__ gx, long total, int C, int HW, int size,
+                                    const T* __restrict__ gtop, T* __restrict__ gx, I total, int C, int HW, int size,
                                     T negative_beta, T cache_ratio) {
   const int pre = size - (size + 1) / 2, post = size - pre - 1;
-  for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
-    int hw = (int)(idx % HW);
-    long t = idx / HW;
-    int c = (int)(t % C);
-    long n = t / C;
-    long base = n * (long)C * HW + hw;
+  for (I idx = (I)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (I)gridDim.x * blockDim.x) {
+    I t = idx / (I)HW;
+    int hw = (int)(idx - t * (I)HW);
+    I n = t / (I)C;
+    int c = (int)(t - n * (I)C);
+    long base = (long)n * C * HW + hw;
     int lo = max(c - pre, 0), hi = min(c + post, C - 1);
     T acc = T(0);
     for (int k = lo; k <= hi; ++k) {
@@ -325,11 +466,14 @@ CGTB_API int cgtb_lrn_forward(int dtype, const void* x, long N, int C, int H, in
   long total = N * C * H * W;
   if (total <= 0) return 0;
   long blocks = std::min<long>(cgtb_ceil_div(total, 256), (long)rt().sm_count * 32);
-  if (dtype == cgtb_f4)
-    CGTB_LAUNCH(lrn_forward_kernel<float>, (unsigned)blocks, 256, 0, (const float*)x, (float*)top, (float*)scale, total, C,
+  if (dtype == cgtb_f4 && total < (1L << 31))
+    CGTB_LAUNCH((lrn_forward_kernel<float, unsigned>), (unsigned)blocks, 256, 0, (const float*)x, (float*)top, (float*)scale, (unsigned)total, C,
+                H * W, size, (float)(alpha / size), (float)(-beta));
+  else if (dtype == cgtb_f4)
+    CGTB_LAUNCH((lrn_forward_kernel<float, long>), (unsigned)blocks, 256, 0, (const float*)x, (float*)top, (float*)scale, total, C,
                 H * W, size, (float)(alpha / size), (float)(-beta));
   else if (dtype == cgtb_f8)
-    CGTB_LAUNCH(lrn_forward_kernel<double>, (unsigned)blocks, 256, 0, (const double*)x, (double*)top, (double*)scale, total,
+    CGTB_LAUNCH((lrn_forward_kernel<double, long>), (unsigned)blocks, 256, 0, (const double*)x, (double*)top, (double*)scale, total,
                 C, H * W, size, alpha / size, -beta);
   else
     return fail("cgtb_lrn_forward: unsupported dtype %d", dtype);
@@ -344,12 +488,16 @@ CGTB_API int cgtb_lrn_backward(int dtype, const void* x, const void* top, const 
   long total = N * C * H * W;
   if (total <= 0) return 0;
   long blocks = std::min<long>(cgtb_ceil_div(total, 256), (long)rt().sm_count * 32);
-  if (dtype == cgtb_f4)
-    CGTB_LAUNCH(lrn_backward_kernel<float>, (unsigned)blocks, 256, 0, (const float*)x, (const float*)top,
+  if (dtype == cgtb_f4 && total < (1L << 31))
+    CGTB_LAUNCH((lrn_backward_kernel<float, unsigned>), (unsigned)blocks, 256, 0, (const float*)x, (const float*)top,
+                (const float*)scale, (const float*)gtop, (float*)gx, (unsigned)total, C, H * W, size, (float)(-beta),
+                (float)(2. * alpha * beta / size));
+  else if (dtype == cgtb_f4)
+    CGTB_LAUNCH((lrn_backward_kernel<float, long>), (unsigned)blocks, 256, 0, (const float*)x, (const float*)top,
                 (const float*)scale, (const float*)gtop, (float*)gx, total, C, H * W, size, (float)(-beta),
                 (float)(2. * alpha * beta / size));
   else if (dtype == cgtb_f8)
-    CGTB_LAUNCH(lrn_backward_kernel<double>, (unsigned)blocks, 256, 0, (const double*)x, (const double*)top,
+    CGTB_LAUNCH((lrn_backward_kernel<double, long>), (unsigned)blocks, 256, 0, (const double*)x, (const double*)top,
                 (const double*)scale, (const double*)gtop, (double*)gx, total, C, H * W, size, -beta,
                 2. * alpha * beta / size);
   else
