@@ -4,6 +4,8 @@ Counterpart of the generated-kernel branch of ElwiseUnary.get_native_compile_inf
 (cgt/core.py:1216-1239): the expression string becomes a `__device__` function inside a vectorised
 grid-stride kernel, compiled by nvcc for sm_100a into the hash-keyed library cache.
 """
+import os
+
 from . import core
 
 _CUDA_TEMPLATE = r"""
@@ -44,3 +46,133 @@ def unary_from_cexpr(op, input_types, devtype):
     d = dict(cdtype0=core.np2c[input_types[0].dtype], cdtype1=core.np2c[out_dtype], cexpr=op.info.cexpr)
     return core.NativeCompileInfo(_CPP_TEMPLATE % d, includes=["math.h", "stdint.h"], link_flags="-lm",
                                   gpu_deref_mask=(True,), extra_srcs=[core.SrcFile("cuda", _CUDA_TEMPLATE % d)])
+
+
+# ================================================================
+# Fused elementwise chains
+# ================================================================
+
+_FUSED_HEAD = r"""
+#include <cuda_runtime.h>
+#include "cgt_elwise.h"
+"""
+
+
+def fused_source(op):
+    """CUDA source of the kernel for one FusedElwise program. Every operation calls the scalar template
+    the separate kernels use (float operands, literal opcode), values stay in registers, scalars are
+    read once per thread. Compiled without multiply-add contraction: the separate kernels round every
+    product before the next Op adds to it."""
+    n_in = len(op.in_kinds)
+    params, hoist, loads = [], [], []
+    for (k, kind) in enumerate(op.in_kinds):
+        if kind == 0:
+            params.append("const float* __restrict__ in%d" % k)
+            loads.append(("pack", "const Pack<float, V> p%d = load_pack<float, V>(in%d + i * V);" % (k, k), "p%d.v[v]" % k))
+        elif kind == 1:
+            params.append("const int8_t* __restrict__ in%d" % k)
+            loads.append(("pack", "const Pack<int8_t, V> p%d = load_pack<int8_t, V>(in%d + i * V);" % (k, k), "(float)p%d.v[v]" % k))
+        elif kind == 2:
+            params.append("const float* __restrict__ in%d" % k)
+            hoist.append("const float s%d = in%d[0];" % (k, k))
+            loads.append(("none", "", "s%d" % k))
+        elif kind == 3:
+            params.append("const long* __restrict__ in%d" % k)
+            hoist.append("const float s%d = (float)in%d[0];" % (k, k))
+            loads.append(("none", "", "s%d" % k))
+        else:
+            params.append("const float* __restrict__ in%d, const long bk%d, const long bi%d" % (k, k, k))
+            loads.append(("pack", "const float b%d = in%d[((i * V) / (I)bi%d) %% (I)bk%d];" % (k, k, k, k), "b%d" % k))
+    outs = []
+    for (q, dt) in enumerate(op.out_dtypes):
+        ctype = "float" if dt == "f4" else "int8_t"
+        params.append("%s* __restrict__ out%d" % (ctype, q))
+        outs.append(ctype)
+    lines = ["// I: index type (32-bit when the element count allows: the broadcast index needs a division)",
+             "template <int V, typename I>", "__global__ void fused_kernel(const I n, %s) {" % ", ".join(params)]
+    lines += ["  " + h for h in hoist]
+    lines.append("  const I nv = n / V;")
+    lines.append("  for (I i = (I)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += (I)gridDim.x * blockDim.x) {")
+    for (_kind, stmt, _expr) in loads:
+        if stmt:
+            lines.append("    " + stmt)
+    for (q, ctype) in enumerate(outs):
+        lines.append("    Pack<%s, V> o%d;" % (ctype, q))
+    lines.append("#pragma unroll")
+    lines.append("    for (int v = 0; v < V; ++v) {")
+    for (k, (_kind, _stmt, expr)) in enumerate(loads):
+        lines.append("      const float r%d = %s;" % (k, expr))
+    for (j, (arity, code, a, b)) in enumerate(op.program):
+        if arity == 1:
+            lines.append("      const float r%d = unary_apply<float, float>(%d, r%d);" % (n_in + j, code, a))
+        else:
+            lines.append("      const float r%d = binary_apply<float, float, float>(%d, r%d, r%d);" % (n_in + j, code, a, b))
+    for (q, (reg, ctype)) in enumerate(zip(op.out_regs, outs)):
+        lines.append("      o%d.v[v] = (%s)r%d;" % (q, ctype, reg))
+    lines.append("    }")
+    for (q, ctype) in enumerate(outs):
+        lines.append("    store_pack<%s, V>(out%d + i * V, o%d);" % (ctype, q, q))
+    lines += ["  }", "}"]
+    args = []
+    for (k, kind) in enumerate(op.in_kinds):
+        ctype = {0: "float", 1: "int8_t", 2: "float", 3: "long", 4: "float"}[kind]
+        args.append("(const %s*)in[%d]" % (ctype, k))
+        if kind == 4:
+            args += ["bk[%d]" % k, "bi[%d]" % k]
+    for (q, ctype) in enumerate(outs):
+        args.append("(%s*)out[%d]" % (ctype, q))
+    lines += [
+        'extern "C" __attribute__((visibility("default"))) int cgtb_fused_launch(long n, const void* const* in, const long* bk,',
+        "    const long* bi, void* const* out, int vectorised, void* stream, int sm_count) {",
+        "  const long work = vectorised ? n / 4 : n;",
+        "  long blocks = (work + 255) / 256;",
+        "  if (blocks > (long)sm_count * 16) blocks = (long)sm_count * 16;",
+        "  if (blocks < 1) blocks = 1;",
+        "  const bool small = n < (1L << 31);",
+        "  if (vectorised && small) fused_kernel<4, unsigned><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((unsigned)n, %s);" % ", ".join(args),
+        "  else if (vectorised) fused_kernel<4, long><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(n, %s);" % ", ".join(args),
+        "  else if (small) fused_kernel<1, unsigned><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((unsigned)n, %s);" % ", ".join(args),
+        "  else fused_kernel<1, long><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(n, %s);" % ", ".join(args),
+        "  return cudaPeekAtLastError() != cudaSuccess;",
+        "}",
+    ]
+    return _FUSED_HEAD + "\n".join(lines) + "\n"
+
+
+_fused_libs = {}
+
+
+def fused_launcher(op):
+    """Address of the generated launcher for this program (compiled into the hash-keyed cache on first
+    use), or None when generation is switched off or the compiler is not available: the library's
+    register-machine kernel then runs the program."""
+    import ctypes
+    import os.path as osp
+    from . import compilation, utils
+    if not core.get_config().get("jit_fused_elementwise", True):
+        return None
+    src = fused_source(op)
+    info = compilation.get_compile_info()
+    prefix = "fused_" + utils.hash_seq1(src, "fmad=false", str(compilation.CPP_ABI_VERSION))
+    if prefix in _fused_libs:
+        return _fused_libs[prefix][1]
+    libpath = osp.join(info["CACHE_ROOT"], prefix + ".so")
+    try:
+        if not osp.exists(libpath):
+            srcpath = osp.join(info["CACHE_ROOT"], prefix + ".cu")
+            with open(srcpath, "w") as fh:
+                fh.write(src)
+            compilation._call("nvcc %s -o %s.tmp -shared -gencode arch=compute_100a,code=sm_100a -lineinfo -O3 -std=c++17 "
+                              "-fmad=false -Xcompiler -fPIC %s -L/usr/local/cuda/lib64 -lcudart"
+                              % (srcpath, libpath, info["INCLUDES"]))
+            os.replace(libpath + ".tmp", libpath)
+        lib = ctypes.CDLL(libpath)
+        addr = ctypes.cast(lib.cgtb_fused_launch, ctypes.c_void_p).value
+    except (RuntimeError, OSError) as err:
+        import sys
+        sys.stderr.write("cgt_b200: no generated kernel for a fused elementwise chain (%s); using the built-in one\n"
+                         % str(err).splitlines()[0])
+        _fused_libs[prefix] = (None, None)
+        return None
+    _fused_libs[prefix] = (lib, addr)
+    return addr

@@ -121,6 +121,228 @@ def simplify_for_execution(outputs, updates, givens=()):
 
 
 # ================================================================
+# Phase 1b: elementwise fusion
+# ================================================================
+
+_FUSABLE_WITH_INT_SCALAR = ("*", "+", "-", "/", "<", ">", "<=", ">=", "==", "!=")
+
+
+def _small_int_constant(node):
+    if not isinstance(node.op, core.Constant):
+        return False
+    v = np.asarray(node.op.value)
+    return v.size == 1 and abs(int(v.reshape(-1)[0])) < (1 << 24)
+
+
+def _fusable(node):
+    """An elementwise node whose arithmetic the fused kernel reproduces bit for bit: float32 (or 0/1
+    truth value) operands and results, built-in operations."""
+    if node.is_input() or node.ndim == 0:
+        return False
+    op = node.op
+    if isinstance(op, core.ElwiseUnary):
+        return node.dtype == "f4" and node.parents[0].dtype == "f4" and op.opname in core.UNARY_OPCODE
+    if isinstance(op, core.ElwiseBinary):
+        if node.dtype not in ("f4", "i1") or op.opname not in core.BINARY_OPCODE:
+            return False
+        kinds = []
+        for par in node.parents:
+            if par.dtype in ("f4", "i1"):
+                kinds.append(par.dtype)
+            elif par.ndim == 0 and par.dtype == "i8" and _small_int_constant(par) and op.opname in _FUSABLE_WITH_INT_SCALAR:
+                kinds.append("i8")
+            else:
+                return False
+        if "f4" not in kinds:
+            return False
+        if op.opname == "**" and kinds != ["f4", "f4"]:
+            return False
+        return True
+    return False
+
+
+def _foldable_repeat(node):
+    """Repeat of a float32 tensor along a prefix and a suffix of its axes (a bias [1,C,1,1] -> [B,C,H,W],
+    a row [1,N] -> [B,N], a column [B,1] -> [B,N]): the fused kernel reads the small operand directly."""
+    if node.is_input() or not isinstance(node.op, core.Repeat) or node.dtype != "f4":
+        return False
+    nd = node.ndim
+    axes = sorted(node.op.axes)
+    kept = [d for d in range(nd) if d not in axes]
+    return all(b - a == 1 for (a, b) in zip(kept[:-1], kept[1:]))
+
+
+def fuse_elementwise(outputs, updatetargs, node2shape):
+    """Replace connected groups of elementwise nodes of one shape by FusedElwise nodes.
+
+    A node joins the group of one of its fusable parents when that cannot create a cycle (no other
+    parent depends on the group). Groups stay within the kernel's limits; a group that would need
+    several outputs while one of them is an update target (which must be written into the variable's
+    own memory) is left alone. Returns the new (outputs, updatetargs)."""
+    all_out = list(outputs) + list(updatetargs)
+    nodes = core.topsorted(all_out)
+    children = defaultdict(list)
+    for node in nodes:
+        for par in node.parents:
+            children[par].append(node)
+    group_of = {}
+    members = defaultdict(list)
+    anc_groups = {}            # node -> groups among its strict ancestors
+    gdeps = defaultdict(set)   # group -> groups that some member depends on through nodes outside the group
+    next_gid = [0]
+
+    def reaches(h, g):
+        """True when group h depends, directly or through other groups, on group g."""
+        stack, seen = [h], set()
+        while stack:
+            k = stack.pop()
+            if k == g:
+                return True
+            if k in seen:
+                continue
+            seen.add(k)
+            stack.extend(gdeps[k])
+        return False
+
+    for node in nodes:
+        anc = set()
+        for par in node.parents:
+            anc |= anc_groups[par]
+            if par in group_of:
+                anc.add(group_of[par])
+        if _fusable(node):
+            chosen = None
+            for par in node.parents:
+                g = group_of.get(par)
+                if g is None or par.ndim == 0 or not _same_shape(node2shape[node], node2shape[par]):
+                    continue
+                if len(members[g]) >= core.FusedElwise.MAX_OPS:
+                    continue
+                # joining g makes g depend on every other group among the node's ancestors: none of
+                # them may depend on g, or the fused nodes would need each other
+                outside = set()
+                for q in node.parents:
+                    if group_of.get(q) != g:
+                        outside |= anc_groups[q]
+                        if q in group_of:
+                            outside.add(group_of[q])
+                if g in outside or any(reaches(h, g) for h in outside):
+                    continue
+                chosen = g
+                gdeps[g] |= (outside - set([g]))
+                break
+            if chosen is None:
+                chosen = next_gid[0]
+                next_gid[0] += 1
+                gdeps[chosen] |= anc
+            group_of[node] = chosen
+            members[chosen].append(node)
+        anc_groups[node] = anc
+    out_set = set(all_out)
+    target_set = set(updatetargs)
+    replace = {}
+    for (g, mem) in members.items():
+        memset = set(mem)
+        inputs, in_kinds, reg_of = [], [], {}
+        folded = 0
+
+        def input_reg(par):
+            key = par
+            if key in reg_of:
+                return reg_of[key]
+            if par.ndim == 0:
+                kind = 2 if par.dtype == "f4" else 3
+                src = par
+            elif _foldable_repeat(par) and all(c in memset for c in children[par]) and par not in out_set:
+                kind, src = 4, par.parents[0]
+            else:
+                kind = 0 if par.dtype == "f4" else 1
+                src = par
+            reg_of[key] = len(inputs)
+            inputs.append(src)
+            in_kinds.append(kind)
+            return reg_of[key]
+
+        program, result_reg = [], {}
+        ok = True
+        # first pass: inputs in order of first use
+        for node in mem:
+            for par in node.parents:
+                if par not in memset:
+                    input_reg(par)
+        n_in = len(inputs)
+        folded = sum(1 for k in in_kinds if k == 4)
+        if len(mem) + folded < 2 or n_in > core.FusedElwise.MAX_IN:
+            continue
+        for (j, node) in enumerate(mem):
+            regs = [result_reg[par] if par in memset else reg_of[par] for par in node.parents]
+            if isinstance(node.op, core.ElwiseUnary):
+                program.append((1, core.UNARY_OPCODE[node.op.opname], regs[0], 0))
+            else:
+                program.append((2, core.BINARY_OPCODE[node.op.opname], regs[0], regs[1]))
+            result_reg[node] = n_in + j
+        outs = [node for node in mem if node in out_set or any(c not in memset for c in children[node])]
+        if not outs or len(outs) > core.FusedElwise.MAX_OUT:
+            continue
+        if len(outs) > 1 and any(o in target_set for o in outs):
+            continue
+        shape_input = None
+        for (k, (src, kind)) in enumerate(zip(inputs, in_kinds)):
+            if kind in (0, 1) and _same_shape(node2shape[src], node2shape[mem[0]]):
+                shape_input = k
+                break
+        if shape_input is None or not ok:
+            continue
+        descr = ",".join(str(node.op) for node in mem)
+        fop = core.FusedElwise(program, in_kinds, [result_reg[o] for o in outs], [o.dtype for o in outs], mem[0].ndim,
+                               shape_input, descr)
+        fnode = core.Result(fop, inputs)
+        shp = node2shape[mem[0]]
+        if len(outs) == 1:
+            node2shape[fnode] = shp
+            replace[outs[0]] = fnode
+            fnode.props.update(outs[0].props)
+        else:
+            node2shape[fnode] = tuple(list(shp) for _ in outs)
+            fnode.props.update(outs[0].props)
+            for (q, o) in enumerate(outs):
+                ti = core.Result(core.TupleIndex(q), [fnode])
+                node2shape[ti] = shp
+                replace[o] = ti
+    if not replace:
+        return list(outputs), list(updatetargs)
+    # rewire every surviving consumer (fused nodes included: their inputs may be outputs of other groups)
+    seen = set()
+    stack = [replace.get(o, o) for o in all_out]
+    while stack:
+        node = stack.pop()
+        if node in seen or node.is_input():
+            continue
+        seen.add(node)
+        for (pos, par) in enumerate(node.parents):
+            if par in replace:
+                node.parents[pos] = replace[par]
+            stack.append(node.parents[pos])
+    return [replace.get(o, o) for o in outputs], [replace.get(o, o) for o in updatetargs]
+
+
+def prebuild_fused_kernels(builders):
+    """Generate and compile the fused-chain kernels of the given configurations into the library cache
+    (no GPU needed: nvcc cross-compiles), so that a later run finds them instead of compiling."""
+    from . import codegen
+    n = 0
+    for build in builders:
+        cfg = build()
+        outs, _usrc, utargs, analysis = simplify_for_execution([cfg.loss] + list(cfg.extra_outputs), cfg.updates)
+        o2, u2 = fuse_elementwise(outs, utargs, analysis["node2shape"])
+        for node in core.topsorted(o2 + u2):
+            if not node.is_input() and isinstance(node.op, core.FusedElwise):
+                if codegen.fused_launcher(node.op):
+                    n += 1
+    return n
+
+
+# ================================================================
 # Phase 2: devices and transports
 # ================================================================
 
@@ -413,8 +635,10 @@ def create_execution_graph(inputs, nodes_sorted, node2shape, node2memowner, node
 def run_compilation_pipeline(inputs, outputs, updates, givens):
     config = core.get_config()
     outputs_simple, updatesrcs, updatetargs_simple, analysis = simplify_for_execution(outputs, updates, givens)
-    all_out = outputs_simple + updatetargs_simple
     node2shape = analysis["node2shape"]
+    if config["fuse_elementwise"]:
+        outputs_simple, updatetargs_simple = fuse_elementwise(outputs_simple, updatetargs_simple, node2shape)
+    all_out = outputs_simple + updatetargs_simple
 
     nodelist = core.topsorted(all_out)
     node2dev = determine_devices(nodelist, dict(zip(updatetargs_simple, updatesrcs)))

@@ -1138,6 +1138,67 @@ class ElwiseBinary(Op):
             ("scalar_y", ctypes.c_int, int(self.scalar_mask[1]))])
 
 
+class FusedElwise(Op):
+    """A connected group of ElwiseUnary / ElwiseBinary nodes over one shape, evaluated by one kernel.
+
+    Not part of the reference's Op set: the compiler forms these nodes after simplification and
+    differentiation (compilation.fuse_elementwise), the reference launches one generated loop per Op
+    (cgt/core.py:1160-1378). ``program`` is a list of (arity, opcode, a, b) over registers: registers
+    0..n_in-1 are the inputs, register n_in+j is the result of operation j. ``in_kinds`` gives each
+    input's form (0 f4 tensor, 1 i1 tensor, 2 f4 scalar, 3 i8 scalar, 4 f4 tensor broadcast along its
+    singleton axes: the operand of a folded Repeat). ``out_regs`` / ``out_dtypes`` name the registers that
+    leave the group. With several outputs the node is tuple-valued."""
+    available_impls = ("native_gpu",)
+    return_type = "byref"
+    MAX_IN, MAX_OPS, MAX_OUT = 8, 16, 4
+
+    def __init__(self, program, in_kinds, out_regs, out_dtypes, ndim, shape_input, descr=""):
+        assert 1 <= len(in_kinds) <= self.MAX_IN and 1 <= len(program) <= self.MAX_OPS and 1 <= len(out_regs) <= self.MAX_OUT
+        self.program = [tuple(p) for p in program]
+        self.in_kinds = list(in_kinds)
+        self.out_regs = list(out_regs)
+        self.out_dtypes = list(out_dtypes)
+        self.ndim = ndim
+        self.shape_input = shape_input
+        self.descr = descr
+
+    def get_diff(self, num_inputs):
+        return [False] * num_inputs
+
+    def shp_apply(self, inputs):
+        shp = cgt.shape(inputs[self.shape_input])
+        return shp if len(self.out_regs) == 1 else tuple(list(shp) for _ in self.out_regs)
+
+    def typ_apply(self, input_types):
+        typs = [TensorType(dt, self.ndim) for dt in self.out_dtypes]
+        return typs[0] if len(typs) == 1 else TupleType(*typs)
+
+    def get_native_compile_info(self, input_types, devtype):
+        def arr(vals, n):
+            vals = list(vals) + [0] * (n - len(vals))
+            return (ctypes.c_int * n)(*vals)
+        code = {"f4": 11, "i1": 1}
+        return NativeCompileInfo(None, prebuilt="cgtb_op_fused_elwise", closure_triples=[
+            ("n_in", ctypes.c_int, len(self.in_kinds)),
+            ("n_ops", ctypes.c_int, len(self.program)),
+            ("n_out", ctypes.c_int, len(self.out_regs)),
+            ("in_kind", ctypes.c_int * self.MAX_IN, arr(self.in_kinds, self.MAX_IN)),
+            ("op_arity", ctypes.c_int * self.MAX_OPS, arr([p[0] for p in self.program], self.MAX_OPS)),
+            ("op_code", ctypes.c_int * self.MAX_OPS, arr([p[1] for p in self.program], self.MAX_OPS)),
+            ("op_a", ctypes.c_int * self.MAX_OPS, arr([p[2] for p in self.program], self.MAX_OPS)),
+            ("op_b", ctypes.c_int * self.MAX_OPS, arr([p[3] for p in self.program], self.MAX_OPS)),
+            ("out_reg", ctypes.c_int * self.MAX_OUT, arr(self.out_regs, self.MAX_OUT)),
+            ("out_dtype", ctypes.c_int * self.MAX_OUT, arr([code[d] for d in self.out_dtypes], self.MAX_OUT)),
+            ("launcher", ctypes.c_void_p, self._launcher())])
+
+    def _launcher(self):
+        from . import codegen
+        return codegen.fused_launcher(self)
+
+    def __repr__(self):
+        return "FusedElwise{%s}" % self.descr
+
+
 def elwise_binary(opname, x, y):
     (x, y) = map(as_node, (x, y))
     scalar_mask = ((x.ndim == 0), (y.ndim == 0))
@@ -2028,7 +2089,7 @@ _DEFAULTS = dict(
     debug=False, precision="single", backend="native", cache_dir="~/.cgt_b200_cache", enable_inplace_opt=True,
     enable_simplification=True, parallel=False, num_threads=1, force_python_impl=False, debug_cpp=False, verbose=False,
     # additions for this backend
-    devtype="gpu", device_index=0, use_cuda_graphs=True, fuse_elementwise=True, profile=False,
+    devtype="gpu", device_index=0, use_cuda_graphs=True, fuse_elementwise=True, jit_fused_elementwise=True, profile=False,
 )
 
 _CONFIG = None

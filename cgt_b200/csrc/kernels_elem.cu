@@ -7,79 +7,11 @@
 // in the input type, sub-expressions with a double literal in double, result narrowed to the output type.
 #include "runtime.h"
 #include "reduce_rkr.h"
+#include "cgt_elwise.h"
 #include <cfloat>
 #include <limits>
 
 using namespace cgtb;
-
-// ------------------------------------------------------------------------------------------------
-// scalar expressions
-// ------------------------------------------------------------------------------------------------
-template <typename TI, typename TO>
-__device__ __forceinline__ TO unary_apply(int op, TI x) {
-  // integer inputs promote to double for the math functions, as C++ overload resolution does
-  typedef typename std::conditional<std::is_floating_point<TI>::value, TI, double>::type TM;
-  switch (op) {
-    case CGTB_U_ABS: return (TO)(fabs((TM)x));
-    case CGTB_U_CEIL: return (TO)(ceil((TM)x));
-    case CGTB_U_COS: return (TO)(cos((TM)x));
-    case CGTB_U_EXP: return (TO)(exp((TM)x));
-    case CGTB_U_ICEIL: return (TO)((int)ceil((TM)x));
-    case CGTB_U_IFLOOR: return (TO)((int)floor((TM)x));
-    case CGTB_U_LOG: return (TO)(log((TM)x));
-    case CGTB_U_NEG: return (TO)(-x);
-    case CGTB_U_SIGN: return (TO)(2 * (x > 0) - 1);
-    case CGTB_U_SIN: return (TO)(sin((TM)x));
-    case CGTB_U_SQUARE: return (TO)(x * x);
-    case CGTB_U_SQRT: return (TO)(sqrt((TM)x));
-    case CGTB_U_TANH: return (TO)(tanh((TM)x));
-    case CGTB_U_SIGMOID: return (TO)(1.0 / (1.0 + exp((TM)(-x))));
-    case CGTB_U_SOFTPLUS: return (TO)((x > 0) ? (x + log(exp((TM)(-x)) + 1)) : log(1 + exp((TM)x)));
-    case CGTB_U_CAST: return (TO)(x);
-  }
-  return TO(0);
-}
-
-template <typename TX, typename TY> struct pow_type { typedef double type; };
-template <> struct pow_type<float, float> { typedef float type; };
-
-template <typename TX, typename TY, typename TO>
-__device__ __forceinline__ TO binary_apply(int op, TX x, TY y) {
-  switch (op) {
-    case CGTB_B_MUL: return (TO)(x * y);
-    case CGTB_B_ADD: return (TO)(x + y);
-    case CGTB_B_SUB: return (TO)(x - y);
-    case CGTB_B_DIV: return (TO)((x + 0.0) / y);
-    case CGTB_B_LT: return (TO)(x < y);
-    case CGTB_B_GT: return (TO)(x > y);
-    case CGTB_B_LE: return (TO)(x <= y);
-    case CGTB_B_GE: return (TO)(x >= y);
-    case CGTB_B_POW: {
-      typedef typename pow_type<TX, TY>::type TP;
-      return (TO)(pow((TP)x, (TP)y));
-    }
-    case CGTB_B_EQ: return (TO)(x == y);
-    case CGTB_B_NE: return (TO)(x != y);
-  }
-  return TO(0);
-}
-
-// ------------------------------------------------------------------------------------------------
-// vector pack: N consecutive elements moved with the widest aligned access that fits
-// ------------------------------------------------------------------------------------------------
-template <typename T, int N>
-struct alignas(sizeof(T) * N <= 16 ? sizeof(T) * N : 16) Pack {
-  T v[N];
-};
-
-template <typename T, int N>
-__device__ __forceinline__ Pack<T, N> load_pack(const T* p) {
-  return *reinterpret_cast<const Pack<T, N>*>(p);
-}
-template <typename T, int N>
-__device__ __forceinline__ void store_pack(T* p, const Pack<T, N>& v) {
-  *reinterpret_cast<Pack<T, N>*>(p) = v;
-}
 
 constexpr int kVec = 4;
 
@@ -189,6 +121,139 @@ CGTB_API int cgtb_binary(int op, int dt_x, int dt_y, int dt_out, long n, const v
     if (rc) return rc;
   }));
   CGTB_CHECK_LAUNCH("binary");
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Fused chains of elementwise Ops: a small register machine over float values. Each operation calls
+// the same unary_apply / binary_apply instantiation that the separate kernels use for float operands
+// (truth values are held as 0.f / 1.f, which is what the separate kernels' int8 -> float conversion
+// yields), so a fused chain and the Op-by-Op sequence agree bit for bit. The register file is indexed
+// with run-time operand numbers and therefore lives in local memory (L1); the chains are HBM-bound.
+// ------------------------------------------------------------------------------------------------
+struct FusedArgs {
+  cgtbFusedProgram prog;
+  const void* in[CGTB_FUSED_MAX_IN];
+  long bk[CGTB_FUSED_MAX_IN], binner[CGTB_FUSED_MAX_IN];
+  void* out[CGTB_FUSED_MAX_OUT];
+  long n;
+};
+
+template <int V>
+__global__ void fused_elwise_kernel(const FusedArgs a) {
+  const cgtbFusedProgram& P = a.prog;
+  const long nv = a.n / V;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += (long)gridDim.x * blockDim.x) {
+    float r[CGTB_FUSED_MAX_IN + CGTB_FUSED_MAX_OPS][V];
+    for (int k = 0; k < P.n_in; ++k) {
+      switch (P.in_kind[k]) {
+        case CGTB_FIN_F4: {
+          Pack<float, V> p = load_pack<float, V>((const float*)a.in[k] + i * V);
+#pragma unroll
+          for (int v = 0; v < V; ++v) r[k][v] = p.v[v];
+        } break;
+        case CGTB_FIN_I1: {
+          Pack<int8_t, V> p = load_pack<int8_t, V>((const int8_t*)a.in[k] + i * V);
+#pragma unroll
+          for (int v = 0; v < V; ++v) r[k][v] = (float)p.v[v];
+        } break;
+        case CGTB_FIN_SCALAR_F4: {
+          const float s = *(const float*)a.in[k];
+#pragma unroll
+          for (int v = 0; v < V; ++v) r[k][v] = s;
+        } break;
+        case CGTB_FIN_SCALAR_I8: {
+          const float s = (float)*(const long*)a.in[k];
+#pragma unroll
+          for (int v = 0; v < V; ++v) r[k][v] = s;
+        } break;
+        default: {  // broadcast: with V > 1 the host guarantees inner % V == 0, one value per pack
+          const float s = ((const float*)a.in[k])[((i * V) / a.binner[k]) % a.bk[k]];
+#pragma unroll
+          for (int v = 0; v < V; ++v) r[k][v] = s;
+        } break;
+      }
+    }
+    for (int o = 0; o < P.n_ops; ++o) {
+      const int dst = P.n_in + o, ra = P.op_a[o], code = P.op_code[o];
+      if (P.op_arity[o] == 1) {
+#pragma unroll
+        for (int v = 0; v < V; ++v) r[dst][v] = unary_apply<float, float>(code, r[ra][v]);
+      } else {
+        const int rb = P.op_b[o];
+#pragma unroll
+        for (int v = 0; v < V; ++v) r[dst][v] = binary_apply<float, float, float>(code, r[ra][v], r[rb][v]);
+      }
+    }
+    for (int q = 0; q < P.n_out; ++q) {
+      const int src = P.out_reg[q];
+      if (P.out_dtype[q] == cgtb_f4) {
+        Pack<float, V> p;
+#pragma unroll
+        for (int v = 0; v < V; ++v) p.v[v] = r[src][v];
+        store_pack<float, V>((float*)a.out[q] + i * V, p);
+      } else {
+        Pack<int8_t, V> p;
+#pragma unroll
+        for (int v = 0; v < V; ++v) p.v[v] = (int8_t)r[src][v];
+        store_pack<int8_t, V>((int8_t*)a.out[q] + i * V, p);
+      }
+    }
+  }
+}
+
+CGTB_API int cgtb_fused_elwise(const cgtbFusedProgram* prog, long n, const void* const* in, const long* bcast_k,
+                               const long* bcast_inner, void* const* out) {
+  if (!require_runtime("cgtb_fused_elwise")) return 1;
+  if (!prog) return fail("cgtb_fused_elwise: null program");
+  if (prog->n_in < 1 || prog->n_in > CGTB_FUSED_MAX_IN || prog->n_ops < 1 || prog->n_ops > CGTB_FUSED_MAX_OPS || prog->n_out < 1 ||
+      prog->n_out > CGTB_FUSED_MAX_OUT)
+    return fail("cgtb_fused_elwise: program of %d inputs, %d operations, %d outputs exceeds the limits", prog->n_in, prog->n_ops,
+                prog->n_out);
+  if (n <= 0) return 0;
+  FusedArgs a;
+  a.prog = *prog;
+  a.n = n;
+  bool vec = (n % kVec) == 0;
+  for (int k = 0; k < prog->n_in; ++k) {
+    a.in[k] = in[k];
+    a.bk[k] = a.binner[k] = 1;
+    const int kind = prog->in_kind[k];
+    if (kind < CGTB_FIN_F4 || kind > CGTB_FIN_BCAST_F4) return fail("cgtb_fused_elwise: bad input kind %d", kind);
+    if (kind == CGTB_FIN_F4) vec = vec && aligned16(in[k]);
+    if (kind == CGTB_FIN_I1) vec = vec && (((uintptr_t)in[k] & 3) == 0);
+    if (kind == CGTB_FIN_BCAST_F4) {
+      if (!bcast_k || !bcast_inner || bcast_k[k] <= 0 || bcast_inner[k] <= 0) return fail("cgtb_fused_elwise: bad broadcast extents");
+      a.bk[k] = bcast_k[k];
+      a.binner[k] = bcast_inner[k];
+      vec = vec && (bcast_inner[k] % kVec) == 0;
+    }
+  }
+  for (int o = 0; o < prog->n_ops; ++o) {
+    const int lim = prog->n_in + o;
+    const bool un = prog->op_arity[o] == 1;
+    if ((!un && prog->op_arity[o] != 2) || prog->op_a[o] < 0 || prog->op_a[o] >= lim || (!un && (prog->op_b[o] < 0 || prog->op_b[o] >= lim)))
+      return fail("cgtb_fused_elwise: operation %d reads a register that is not defined yet", o);
+    if (prog->op_code[o] < 0 || prog->op_code[o] >= (un ? (int)CGTB_U_COUNT : (int)CGTB_B_COUNT)) return fail("cgtb_fused_elwise: bad opcode");
+  }
+  for (int q = 0; q < prog->n_out; ++q) {
+    a.out[q] = out[q];
+    if (prog->out_reg[q] < 0 || prog->out_reg[q] >= prog->n_in + prog->n_ops) return fail("cgtb_fused_elwise: bad output register");
+    if (prog->out_dtype[q] == cgtb_f4) vec = vec && aligned16(out[q]);
+    else if (prog->out_dtype[q] == cgtb_i1) vec = vec && (((uintptr_t)out[q] & 3) == 0);
+    else return fail("cgtb_fused_elwise: outputs are float32 or int8");
+  }
+  if (prog->launcher) {
+    // a kernel generated for exactly this program (same scalar templates, operands in registers)
+    typedef int (*Launcher)(long, const void* const*, const long*, const long*, void* const*, int, void*, int);
+    if (((Launcher)prog->launcher)(n, a.in, a.bk, a.binner, a.out, vec ? 1 : 0, (void*)rt().stream, rt().sm_count))
+      return fail("cgtb_fused_elwise: the generated kernel failed to launch");
+    g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+    return 0;
+  }
+  if (vec) CGTB_LAUNCH(fused_elwise_kernel<kVec>, elem_grid(n), 256, 0, a);
+  else CGTB_LAUNCH(fused_elwise_kernel<1>, elem_grid(n * kVec), 256, 0, a);
+  CGTB_CHECK_LAUNCH("fused_elwise");
   return 0;
 }
 

@@ -136,6 +136,62 @@ OP_BYREF(cgtb_op_elwise_binary) {
   })));
 }
 
+// FusedElwise: closure = the program (include/cgt_b200.h). reads = the program's inputs; write = the
+// output array, or a tuple of arrays when the program has several outputs. Broadcast extents come
+// from the shapes: the input's non-unit axes form one run [d0, d1] of the output's axes.
+OP_BYREF(cgtb_op_fused_elwise) {
+  const cgtbFusedProgram* prog = (const cgtbFusedProgram*)cl0;
+  cgtArray* outs[CGTB_FUSED_MAX_OUT];
+  if (prog->n_out == 1 && write0->kind() == cgtObject::ArrayKind) {
+    outs[0] = ARR(write0);
+  } else {
+    cgtTuple* tup = (cgtTuple*)write0;
+    for (int q = 0; q < prog->n_out; ++q) outs[q] = ARR(tup->getitem(q));
+  }
+  cgtArray* w = outs[0];
+  const long n = w->size();
+  const void* in[CGTB_FUSED_MAX_IN];
+  void* out[CGTB_FUSED_MAX_OUT];
+  long bk[CGTB_FUSED_MAX_IN], binner[CGTB_FUSED_MAX_IN];
+  for (int q = 0; q < prog->n_out; ++q) {
+    if (outs[q]->size() != n || outs[q]->devtype() != cgtGPU) { fail("FusedElwise: outputs must be GPU arrays of one size"); return; }
+    out[q] = outs[q]->data();
+  }
+  for (int k = 0; k < prog->n_in; ++k) {
+    cgtArray* x = ARR(reads[k]);
+    if (x->devtype() != cgtGPU) { fail("FusedElwise: operands must be on the GPU"); return; }
+    in[k] = x->data();
+    bk[k] = binner[k] = 1;
+    const int kind = prog->in_kind[k];
+    if ((kind == CGTB_FIN_F4 || kind == CGTB_FIN_I1) && x->size() != n) {
+      fail("Shape error in a fused elementwise chain. You might be missing a call to cgt.broadcast(...)");
+      return;
+    }
+    if (kind == CGTB_FIN_BCAST_F4) {
+      if (x->ndim() != w->ndim()) { fail("FusedElwise: a broadcast operand must have the rank of the result"); return; }
+      int d0 = -1, d1 = -1;
+      for (int d = 0; d < x->ndim(); ++d) {
+        if (x->shape()[d] != 1) {
+          if (x->shape()[d] != w->shape()[d]) { fail("FusedElwise: broadcast operand does not match the result's shape"); return; }
+          if (d0 < 0) d0 = d;
+          d1 = d;
+        }
+      }
+      long kk = 1, inner = 1;
+      if (d0 >= 0) {
+        for (int d = d0; d <= d1; ++d) {
+          if (x->shape()[d] != w->shape()[d]) { fail("FusedElwise: the kept axes of a broadcast operand must be adjacent"); return; }
+          kk *= w->shape()[d];
+        }
+        for (int d = d1 + 1; d < w->ndim(); ++d) inner *= w->shape()[d];
+      }
+      bk[k] = kk;
+      binner[k] = inner;
+    }
+  }
+  cgtb_fused_elwise(prog, n, in, bk, binner, out);
+}
+
 // ------------------------------------------------------------------------------------------------
 // Mul22 / BatchedMul22 (cgt/core.py:2129-2288). Closure layout of the reference: tA, tB, handle.
 // ------------------------------------------------------------------------------------------------

@@ -84,6 +84,8 @@ def _declare(lib):
         "cgtb_incsli": (ci, [ci, cl, cl, cl, cl, cl, cl, vp, vp, vp]),
         "cgtb_getflat": (ci, [ci, cl, vp, vp, vp]), "cgtb_incflat": (ci, [ci, cl, cl, vp, vp, vp, vp]),
         "cgtb_concat_part": (ci, [ci, cl, cl, cl, cl, cl, vp, vp]), "cgtb_fill": (ci, [ci, cl, cd, cl, vp]),
+        "cgtb_fused_elwise": (ci, [vp, cl, vp, c_long_p, c_long_p, vp]),
+        "cgtb_reduce_rkr_f32_static": (ci, [ci, cl, cl, cl, vp, vp]), "cgtb_reduce_static_max_k": (cl, []),
     }
     for (name, (restype, argtypes)) in sig.items():
         f = getattr(lib, name)

@@ -151,6 +151,34 @@ int cgtb_unary(int op, int dt_in, int dt_out, long n, const void* in, void* out)
 int cgtb_binary(int op, int dt_x, int dt_y, int dt_out, long n, const void* x, const void* y, void* out,
                 int scalar_x, int scalar_y);
 
+/* A chain of ElwiseUnary / ElwiseBinary Ops over one index space evaluated by ONE kernel (no counterpart
+ * in the reference, which launches one generated loop per Op; cgt/core.py:1160-1378 define the Ops).
+ * Values are float32 or 0/1 truth values; every operation is carried out exactly as the separate
+ * kernels of cgtb_unary / cgtb_binary do it, so the results have the same bits.
+ * Registers 0 .. n_in-1 hold the inputs, register n_in+j the result of operation j. */
+#define CGTB_FUSED_MAX_IN 8
+#define CGTB_FUSED_MAX_OPS 16
+#define CGTB_FUSED_MAX_OUT 4
+enum { CGTB_FIN_F4 = 0, CGTB_FIN_I1 = 1, CGTB_FIN_SCALAR_F4 = 2, CGTB_FIN_SCALAR_I8 = 3, CGTB_FIN_BCAST_F4 = 4 };
+typedef struct {
+  int n_in, n_ops, n_out;
+  int in_kind[CGTB_FUSED_MAX_IN];    /* CGTB_FIN_*; a scalar is a 0-d array in device memory */
+  int op_arity[CGTB_FUSED_MAX_OPS];  /* 1: CGTB_U_* opcode, 2: CGTB_B_* opcode */
+  int op_code[CGTB_FUSED_MAX_OPS];
+  int op_a[CGTB_FUSED_MAX_OPS], op_b[CGTB_FUSED_MAX_OPS];
+  int out_reg[CGTB_FUSED_MAX_OUT];
+  int out_dtype[CGTB_FUSED_MAX_OUT]; /* cgtb_f4 or cgtb_i1 */
+  /* NULL: the library's register-machine kernel runs the program. Otherwise the launcher of a kernel
+   * generated for this program: int f(long n, const void* const* in, const long* bcast_k,
+   * const long* bcast_inner, void* const* out, int vectorised, void* stream, int sm_count), 0 on success. */
+  void* launcher;
+} cgtbFusedProgram;
+/* in[k]: device pointer of input k. A CGTB_FIN_BCAST_F4 input holds bcast_k[k] values; element i of the
+ * index space reads value (i / bcast_inner[k]) % bcast_k[k] (a bias [1,C,1,1] over [B,C,H,W]: k = C,
+ * inner = H*W). out[q]: device pointer of output q, n elements each. */
+int cgtb_fused_elwise(const cgtbFusedProgram* prog, long n, const void* const* in, const long* bcast_k,
+                      const long* bcast_inner, void* const* out);
+
 /* Sum / Max over a set of axes, keepdims (cgt/core.py:1663-1738) */
 int cgtb_reduce(int kind, int dtype, int ndim, const long* shape, const int* reduced, const void* in, void* out);
 

@@ -105,3 +105,27 @@ def test_no_cpu_fallback(rt):
     f = cgt.function([x], y)
     with pytest.raises(Exception, match="no CPU implementation"):
         f(np.zeros((100, 100), "f4"))
+
+
+@pytest.mark.parametrize("name,generated", [("mlp", True), ("cifar", True), ("vae", True), ("lstm", True), ("cifar", False),
+                                            ("lstm", False)])
+def test_elementwise_fusion_changes_no_bit(rt, name, generated):
+    """The compiler's fused elementwise chains carry out every operation as the separate kernels do:
+    with fusion on and off the losses and the updated parameters are identical, and fusion did happen.
+    generated=True: kernels generated per chain; False: the library's register-machine kernel."""
+    results = {}
+    for fuse in (False, True):
+        with cgt.scoped_update_config(fuse_elementwise=fuse, jit_fused_elementwise=generated, use_cuda_graphs=False):
+            cfg = configs.BUILDERS[name](**SMALL[name])
+            f = cfg.compile()
+            n_fused = sum(1 for instr in f.eg.instrs if "FusedElwise" in repr(instr))
+            batches = [cfg.batch(seed) for seed in range(2)]
+            losses = [np.asarray(f(*batches[i % 2])[0]).copy() for i in range(4)]
+            params = [np.asarray(p.op.get_value()).copy() for p in cfg.params]
+            results[fuse] = (n_fused, len(f.eg.instrs), losses, params)
+    assert results[False][0] == 0 and results[True][0] > 0
+    assert results[True][1] < results[False][1]
+    for (a, b) in zip(results[False][2], results[True][2]):
+        assert np.array_equal(a, b)
+    for (a, b) in zip(results[False][3], results[True][3]):
+        assert np.array_equal(a, b)

@@ -397,6 +397,56 @@ def test_sgemm_batched_and_dgemm(rt):
     np.testing.assert_allclose(dC.get(), A @ B.T, rtol=1e-12, atol=1e-12)
 
 
+class _FusedProgram(ctypes.Structure):
+    _fields_ = [("n_in", ctypes.c_int), ("n_ops", ctypes.c_int), ("n_out", ctypes.c_int), ("in_kind", ctypes.c_int * 8),
+                ("op_arity", ctypes.c_int * 16), ("op_code", ctypes.c_int * 16), ("op_a", ctypes.c_int * 16),
+                ("op_b", ctypes.c_int * 16), ("out_reg", ctypes.c_int * 4), ("out_dtype", ctypes.c_int * 4),
+                ("launcher", ctypes.c_void_p)]  # NULL: the library's own kernel runs the program
+
+
+@pytest.mark.parametrize("shape", [(8, 32, 15, 15), (4, 6, 5, 7), (3, 5, 2, 2)])
+def test_fused_elwise_matches_separate_kernels(rt, shape):
+    """bias add (operand broadcast from [1,C,1,1]) -> x >= 0 -> x * mask -> sigmoid -> / scalar, in one
+    kernel, against the same chain issued Op by Op through cgtb_repeat / cgtb_binary / cgtb_unary."""
+    rs = np.random.RandomState(31)
+    B, C, H, W = shape
+    n = int(np.prod(shape))
+    x, bias = rs.randn(*shape).astype("f4"), rs.randn(1, C, 1, 1).astype("f4")
+    zero, div = np.array(0, "i8"), np.array(3.0, "f4")
+    dx, db, dz, dd = Dev(x), Dev(bias), Dev(zero), Dev(div)
+    # separate kernels
+    rep, s1, m, s2, s3, s4 = (Dev(shape=shape, dtype=t) for t in ("f4", "f4", "i1", "f4", "f4", "f4"))
+    call("cgtb_repeat", code("f4"), 4, longs(shape), ints([1, 0, 1, 1]), db.ptr, rep.ptr)
+    call("cgtb_binary", 1, code("f4"), code("f4"), code("f4"), n, dx.ptr, rep.ptr, s1.ptr, 0, 0)
+    call("cgtb_binary", 7, code("f4"), code("i8"), code("i1"), n, s1.ptr, dz.ptr, m.ptr, 0, 1)
+    call("cgtb_binary", 0, code("f4"), code("i1"), code("f4"), n, s1.ptr, m.ptr, s2.ptr, 0, 0)
+    call("cgtb_unary", 13, code("f4"), code("f4"), n, s2.ptr, s3.ptr)
+    call("cgtb_binary", 3, code("f4"), code("f4"), code("f4"), n, s3.ptr, dd.ptr, s4.ptr, 0, 1)
+    # one kernel: inputs x (f4), bias (broadcast), 0 (i8 scalar), 3.0 (f4 scalar): registers 0..3
+    P = _FusedProgram()
+    P.n_in, P.n_ops, P.n_out = 4, 5, 3
+    for (k, kind) in enumerate([0, 4, 3, 2]):
+        P.in_kind[k] = kind
+    ops = [(2, 1, 0, 1), (2, 7, 4, 2), (2, 0, 4, 5), (1, 13, 6, 0), (2, 3, 7, 3)]  # registers 4..8
+    for (j, (ar, opc, a, b)) in enumerate(ops):
+        P.op_arity[j], P.op_code[j], P.op_a[j], P.op_b[j] = ar, opc, a, b
+    for (q, (reg, dt)) in enumerate([(5, "i1"), (6, "f4"), (8, "f4")]):
+        P.out_reg[q], P.out_dtype[q] = reg, code(dt)
+    om, o2, o4 = Dev(shape=shape, dtype="i1"), Dev(shape=shape, dtype="f4"), Dev(shape=shape, dtype="f4")
+    ins = (ctypes.c_void_p * 8)(dx.ptr, db.ptr, dz.ptr, dd.ptr)
+    outs = (ctypes.c_void_p * 4)(om.ptr, o2.ptr, o4.ptr)
+    bk, binner = longs([1, C, 1, 1, 1, 1, 1, 1]), longs([1, H * W, 1, 1, 1, 1, 1, 1])
+    call("cgtb_fused_elwise", ctypes.byref(P), n, ins, bk, binner, outs)
+    assert np.array_equal(om.get(), m.get())
+    assert np.array_equal(o2.get(), s2.get())
+    assert np.array_equal(o4.get(), s4.get())
+    # and against the CPU oracle
+    t = x + bias
+    want_mask = (t >= 0)
+    assert np.array_equal(om.get().astype(bool), want_mask)
+    np.testing.assert_allclose(o2.get(), t * want_mask, rtol=RTOL, atol=ATOL)
+
+
 def test_empty_inputs(rt):
     d = Dev(shape=(1,), dtype="f4")
     call("cgtb_unary", 3, code("f4"), code("f4"), 0, d.ptr, d.ptr)
