@@ -1,7 +1,9 @@
 // Mul22 / BatchedMul22 entry points: choose between the tcgen05 tensor-core kernels (3xTF32 split
 // precision; TMA-fed for 16-byte-aligned operands, gemm_tma.cu, register-fed otherwise,
 // gemm_tcgen05.cu) and the fp32 FMA kernel (gemm_simt.cu).
-// impl: 0 automatic, 1 FMA, 2 tensor cores (either feed), 3 register-fed only, 4 TMA-fed only.
+// Products with few outputs and a short K go to a one-thread-per-output kernel (gemm_simt.cu).
+// impl: 0 automatic, 1 FMA (tiled), 2 tensor cores (either feed), 3 register-fed only, 4 TMA-fed only,
+// 5 the small-product kernel only.
 #include "runtime.h"
 
 namespace cgtb {
@@ -14,9 +16,17 @@ int sgemm_tc(int tA, int tB, long P, long M, long N, long K, const float* A, lon
 int sgemm_tma(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B,
               long ldb, long strideB, float* C, long ldc, long strideC);
 
+int sgemm_small(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B,
+                long ldb, long strideB, float* C, long ldc, long strideC);
+
 int sgemm_dispatch(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B,
                    long ldb, long strideB, float* C, long ldc, long strideC, int impl) {
   if (!require_runtime("sgemm")) return 1;
+  if (impl == 0 || impl == 5) {
+    int rc = sgemm_small(tA, tB, P, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC);
+    if (rc >= 0) return rc;
+    if (impl == 5) return fail("sgemm: M=%ld N=%ld K=%ld is not a small product", M, N, K);
+  }
   if (impl != 1) {
     int rc = -1;
     if (impl != 3) rc = sgemm_tma(tA, tB, P, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC);

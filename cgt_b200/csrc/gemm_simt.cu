@@ -143,7 +143,62 @@ int gemm_simt(int tA, int tB, long P, long M, long N, long K, const T* A, long l
 
 }  // namespace
 
+namespace {
+// Products with few outputs and a short K (the classifier layer: 128 x 10 x 256 and its gradients):
+// LANES consecutive threads share one output element, lane l taking k = l, l + LANES, ...; eight
+// products' operands are loaded before the first multiply-add so that a thread has sixteen loads in
+// flight (the kernel is bound by memory latency, not by bytes or flops). The lanes' sums are combined
+// by a shuffle tree: a fixed order, so results are reproducible. A tiled kernel spends its time on
+// pipeline fill and barriers for these shapes.
+template <int LANES>
+__global__ void sgemm_small_kernel(int tA, int tB, long M, long N, long K, const float* __restrict__ A, long lda, long strideA,
+                                   const float* __restrict__ B, long ldb, long strideB, float* __restrict__ C, long ldc,
+                                   long strideC) {
+  const long p = blockIdx.y;
+  const long gthread = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long e = gthread / LANES;
+  const int l = (int)(gthread % LANES);
+  const bool live = e < M * N;
+  const long ee = live ? e : 0;
+  const long m = ee / N, n = ee - m * N;
+  const float* a = A + p * strideA + (tA ? m : m * lda);
+  const float* b = B + p * strideB + (tB ? n * ldb : n);
+  const long sa = tA ? lda : 1, sb = tB ? 1 : ldb;
+  float acc = 0.f;
+  for (long k0 = l; k0 < K; k0 += 8L * LANES) {
+    float av[8], bv[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const long k = k0 + (long)u * LANES;
+      const bool ok = live && k < K;
+      av[u] = ok ? __ldg(a + k * sa) : 0.f;
+      bv[u] = ok ? __ldg(b + k * sb) : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) acc = fmaf(av[u], bv[u], acc);
+  }
+#pragma unroll
+  for (int d = LANES / 2; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+  if (live && l == 0) C[p * strideC + m * ldc + n] = acc;
+}
+}  // namespace
+
 namespace cgtb {
+// returns 0 done, -1 not a small product
+int sgemm_small(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B, long ldb,
+                long strideB, float* C, long ldc, long strideC) {
+  if (P <= 0 || M <= 0 || N <= 0) return 0;
+  if (M * N > 65536 || K > 2048 || M * N * K > (1L << 24) || P > 65535) return -1;
+  const int lanes = K >= 128 ? 32 : (K >= 32 ? 8 : 1);
+  dim3 grid((unsigned)cgtb_ceil_div(M * N * lanes, 256), (unsigned)P);
+  if (lanes == 32) CGTB_LAUNCH(sgemm_small_kernel<32>, grid, 256, 0, tA, tB, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC);
+  else if (lanes == 8) CGTB_LAUNCH(sgemm_small_kernel<8>, grid, 256, 0, tA, tB, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC);
+  else CGTB_LAUNCH(sgemm_small_kernel<1>, grid, 256, 0, tA, tB, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC);
+  cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) return fail("sgemm_small launch failed: %s", cudaGetErrorString(e));
+  return 0;
+}
+
 int sgemm_simt(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B,
                long ldb, long strideB, float* C, long ldc, long strideC) {
   return gemm_simt<float>(tA, tB, P, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC);

@@ -7,79 +7,87 @@
 // added in the same sequence.
 #include "runtime.h"
 #include <cfloat>
+#include <type_traits>
 
 using namespace cgtb;
 
 // ================================================================================================
 // im2col : col[b, h, w, c] = x[b, c_im, h*sh - ph + i, w*sw - pw + j],  c = (c_im*kh + i)*kw + j
-// (include/im2col.h:6-28). One block per (b, h) output row: the C x kh x W input slab that row needs
-// is staged in shared memory with out-of-image rows zero-filled, then written out as Wo*Z contiguous
-// floats with consecutive threads on consecutive column channels.
+// (include/im2col.h:6-28). One block per (b, h) output row (several when rows are short): the
+// C x kh input rows that the output row needs are staged in shared memory, each padded with zeros to
+// Wp = (Wo-1)*sw + kw entries and zero for rows outside the image, so the copy-out needs no range
+// test: col[.., w, c] = slab[offp[c] + w*sw] with offp[c] = (c_im*kh + i)*Wp + j. A thread owns four
+// consecutive column channels (one 16-byte store per w) when Z is a multiple of 4, else single
+// channels, and walks along w; consecutive threads write consecutive addresses.
 // ================================================================================================
 template <typename T>
-__global__ void im2col_rows_kernel(const T* __restrict__ x, T* __restrict__ col, int C, int H, int W, int kh, int kw,
-                                   int ph, int pw, int sh, int sw, int Ho, int Wo, int rows_per_block, long total_rows) {
+__global__ void __launch_bounds__(256, 5) im2col_rows_kernel(const T* __restrict__ x, T* __restrict__ col, int C, int H, int W, int kh, int kw,
+                                   int ph, int pw, int sh, int sw, int Ho, int Wo, int rows_per_block, long total_rows,
+                                   int vec4) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  T* slab = reinterpret_cast<T*>(smem_raw);             // [C][kh][W]
-  const int Z = C * kh * kw;
-  int* rowoff = reinterpret_cast<int*>(slab + (size_t)C * kh * W);  // [Z] : (c_im*kh + i)*W
-  int* joff = rowoff + Z;                               // [Z] : j - pw
-
+  const int Z = C * kh * kw, Wp = (Wo - 1) * sw + kw, nrows = C * kh;
+  int* offp = reinterpret_cast<int*>(smem_raw);                      // [Z], padded to a multiple of 4
+  T* slab = reinterpret_cast<T*>(offp + ((Z + 3) & ~3));             // [C*kh][Wp]
   for (int c = threadIdx.x; c < Z; c += blockDim.x) {
-    int j = c % kw;
-    int i = (c / kw) % kh;
-    int c_im = c / (kw * kh);
-    rowoff[c] = (c_im * kh + i) * W;
-    joff[c] = j - pw;
+    const int j = c % kw, ri = c / kw;
+    offp[c] = ri * Wp + j;
   }
   for (int r = 0; r < rows_per_block; ++r) {
-    long row = (long)blockIdx.x * rows_per_block + r;  // row = b*Ho + h
+    const long row = (long)blockIdx.x * rows_per_block + r;  // row = b*Ho + h
     if (row >= total_rows) break;
-    long b = row / Ho;
-    int h = (int)(row - b * Ho);
+    const long b = row / Ho;
+    const int h = (int)(row - b * Ho);
     const T* xb = x + b * (long)C * H * W;
-    __syncthreads();
-    const int slab_n = C * kh * W;
-    for (int s = threadIdx.x; s < slab_n; s += blockDim.x) {
-      int wq = s % W;
-      int i = (s / W) % kh;
-      int c_im = s / (W * kh);
-      int hin = h * sh - ph + i;
-      slab[s] = (hin >= 0 && hin < H) ? xb[((long)c_im * H + hin) * W + wq] : T(0);
+    __syncthreads();  // the previous row's copy-out has finished reading the slab (and offp is written)
+    // four independent loads per thread are issued before the first is stored: the staging is bound by
+    // the latency of reaching L2 / HBM, not by bytes
+    const int slab_n = nrows * Wp;
+    for (int e0 = threadIdx.x; e0 < slab_n; e0 += 4 * blockDim.x) {
+      T v[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int e = e0 + k * blockDim.x;
+        v[k] = T(0);
+        if (e < slab_n) {
+          const int ri = e / Wp, wq = e - ri * Wp;
+          const int c_im = ri / kh, i = ri - c_im * kh;
+          const int hin = h * sh - ph + i, win = wq - pw;
+          if (hin >= 0 && hin < H && win >= 0 && win < W) v[k] = __ldg(xb + ((long)c_im * H + hin) * W + win);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int e = e0 + k * blockDim.x;
+        if (e < slab_n) slab[e] = v[k];
+      }
     }
     __syncthreads();
     T* out = col + row * (long)Wo * Z;
-    // A thread keeps up to four column channels (c = cbase + tid + u*blockDim) with their slab offsets in
-    // registers and walks along w: one shared-memory read, one unsigned range test and one coalesced
-    // store per element.
-    if (Z <= (int)blockDim.x / 2) {
+    if (vec4) {
+      typedef typename std::conditional<sizeof(T) == 4, float4, double4>::type V4;
+      for (int q = threadIdx.x; q < Z / 4; q += blockDim.x) {
+        const int4 o = *reinterpret_cast<const int4*>(offp + 4 * q);
+        const T *s0 = slab + o.x, *s1 = slab + o.y, *s2 = slab + o.z, *s3 = slab + o.w;
+        V4* dst = reinterpret_cast<V4*>(out + 4 * q);
+        const int zq = Z / 4;
+        for (int w = 0; w < Wo; ++w) {
+          const int k = w * sw;
+          V4 v;
+          v.x = s0[k]; v.y = s1[k]; v.z = s2[k]; v.w = s3[k];
+          dst[(long)w * zq] = v;
+        }
+      }
+    } else if (Z <= (int)blockDim.x / 2) {
       // few column channels: G groups of Z threads, group g takes w = g, g + G, ...
       const int G = blockDim.x / Z, g = threadIdx.x / Z, c = threadIdx.x - g * Z;
       if (g < G) {
-        const int ro1 = rowoff[c], jo1 = joff[c];
-        for (int w = g; w < Wo; w += G) {
-          const int win = w * sw + jo1;
-          out[(long)w * Z + c] = ((unsigned)win < (unsigned)W) ? slab[ro1 + win] : T(0);
-        }
+        const T* s0 = slab + offp[c];
+        for (int w = g; w < Wo; w += G) out[(long)w * Z + c] = s0[w * sw];
       }
-    } else
-    for (int cbase = 0; cbase < Z; cbase += 4 * blockDim.x) {
-      int ro[4], jo[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int c = cbase + threadIdx.x + u * blockDim.x;
-        ro[u] = c < Z ? rowoff[c] : -1;
-        jo[u] = c < Z ? joff[c] : 0;
-      }
-      for (int w = 0; w < Wo; ++w) {
-        T* orow = out + (long)w * Z + cbase + threadIdx.x;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          if (ro[u] >= 0) {
-            const int win = w * sw + jo[u];
-            orow[u * blockDim.x] = ((unsigned)win < (unsigned)W) ? slab[ro[u] + win] : T(0);
-          }
-        }
+    } else {
+      for (int c = threadIdx.x; c < Z; c += blockDim.x) {
+        const T* s0 = slab + offp[c];
+        for (int w = 0; w < Wo; ++w) out[(long)w * Z + c] = s0[w * sw];
       }
     }
   }
@@ -108,7 +116,8 @@ static int im2col_launch(const T* x, long B, int C, int H, int W, int kh, int kw
   int Ho = (H + 2 * ph - kh) / sh + 1, Wo = (W + 2 * pw - kw) / sw + 1;
   if (B <= 0 || Ho <= 0 || Wo <= 0) return 0;
   const int Z = C * kh * kw;
-  size_t smem = (size_t)C * kh * W * sizeof(T) + 2 * (size_t)Z * sizeof(int);
+  const int Wp = (Wo - 1) * sw + kw;
+  size_t smem = (size_t)((Z + 3) & ~3) * sizeof(int) + (size_t)C * kh * Wp * sizeof(T);
   long total_rows = B * Ho;
   if (smem <= 200 * 1024) {
     if (smem > 48 * 1024)
@@ -117,8 +126,9 @@ static int im2col_launch(const T* x, long B, int C, int H, int W, int kh, int kw
     int rpb = 1;
     while ((long)rpb * Wo * Z < 16384 && rpb < 8) rpb *= 2;
     long blocks = cgtb_ceil_div(total_rows, rpb);
+    const int vec4 = ((Z & 3) == 0 && ((uintptr_t)col & (4 * sizeof(T) - 1)) == 0) ? 1 : 0;
     CGTB_LAUNCH(im2col_rows_kernel<T>, (unsigned)blocks, 256, smem, x, col, C, H, W, kh, kw, ph, pw, sh, sw, Ho, Wo, rpb,
-                total_rows);
+                total_rows, vec4);
   } else {
     long total = total_rows * Wo * Z;
     long blocks = std::min<long>(cgtb_ceil_div(total, 256), (long)rt().sm_count * 16);
@@ -194,43 +204,58 @@ __global__ void __launch_bounds__(1024, 2) col2im_image_kernel(const T* __restri
   const bool active = t < npix;
   const T* colb = col + (size_t)b * Ho * Wo * Z + (size_t)g * CGZ;
   const int seg16 = CGZ * (int)sizeof(T) / 16;  // 16-byte units per segment
-  auto prefetch = [&](int h, int stage) {
-    if (h >= 0) {
-      unsigned char* dst = reinterpret_cast<unsigned char*>(ring + (size_t)stage * slab_n);
-      const unsigned char* src = reinterpret_cast<const unsigned char*>(colb + (size_t)h * Wo * Z);
-      for (int q = t; q < Wo * seg16; q += blockDim.x) {
-        const int w = q / seg16, r = q - w * seg16;
-        const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst + ((size_t)w * CGZ * sizeof(T) + (size_t)r * 16));
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src + ((size_t)w * Z * sizeof(T) + (size_t)r * 16)) : "memory");
+  // Slabs travel in groups of G: one commit group, one wait and one pair of block barriers per G
+  // slabs (the barriers, not the bytes, were the cost with 29 warps per block). NG groups form the ring.
+  constexpr int G = 3, NG = STAGES / G;
+  static_assert(STAGES % G == 0 && NG >= 2, "the ring holds whole groups");
+  const int ngroups_total = (Ho + G - 1) / G;
+  auto prefetch_group = [&](int gi) {
+    if (gi < ngroups_total) {
+      const int slot0 = (gi % NG) * G;
+#pragma unroll
+      for (int s2 = 0; s2 < G; ++s2) {
+        const int h = Ho - 1 - (gi * G + s2);
+        if (h >= 0) {
+          unsigned char* dst = reinterpret_cast<unsigned char*>(ring + (size_t)(slot0 + s2) * slab_n);
+          const unsigned char* src = reinterpret_cast<const unsigned char*>(colb + (size_t)h * Wo * Z);
+          for (int q = t; q < Wo * seg16; q += blockDim.x) {
+            const int w = q / seg16, r = q - w * seg16;
+            const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst + ((size_t)w * CGZ * sizeof(T) + (size_t)r * 16));
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src + ((size_t)w * Z * sizeof(T) + (size_t)r * 16)) : "memory");
+          }
+        }
       }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");  // an empty group keeps the group count uniform
   };
 #pragma unroll
-  for (int s = 0; s < STAGES - 1; ++s) prefetch(Ho - 1 - s, s);
+  for (int gi = 0; gi < NG - 1; ++gi) prefetch_group(gi);
   T acc = T(0);
-  for (int h = Ho - 1; h >= 0; --h) {
-    const int n = Ho - 1 - h;  // slabs consumed so far
-    prefetch(h - (STAGES - 1), (n + STAGES - 1) % STAGES);
-    asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 1) : "memory");
+  for (int gi = 0; gi < ngroups_total; ++gi) {
+    prefetch_group(gi + NG - 1);
+    asm volatile("cp.async.wait_group %0;" ::"n"(NG - 1) : "memory");
     __syncthreads();
-    const int i = y + ph - h * sh;
-    if (active && i >= 0 && i < kh) {
-      const T* base = ring + (size_t)(n % STAGES) * slab_n + (c * kh + i) * kw;
-      if (sw == 1) {  // unit stride: no division, j limited so that 0 <= x + pw - j < Wo
-        const int j0 = max(0, x + pw - (Wo - 1)), j1 = min(kw - 1, x + pw);
-        for (int j = j0; j <= j1; ++j) acc += base[(x + pw - j) * CGZ + j];
-      } else {
-        for (int j = 0; j < kw; ++j) {
-          const int wn = x + pw - j;
-          if (wn < 0) break;
-          const int w = wn / sw;
-          if (w * sw != wn || w >= Wo) continue;
-          acc += base[w * CGZ + j];
+#pragma unroll
+    for (int s2 = 0; s2 < G; ++s2) {
+      const int h = Ho - 1 - (gi * G + s2);
+      const int i = y + ph - h * sh;
+      if (h >= 0 && active && i >= 0 && i < kh) {
+        const T* base = ring + (size_t)((gi % NG) * G + s2) * slab_n + (c * kh + i) * kw;
+        if (sw == 1) {  // unit stride: no division, j limited so that 0 <= x + pw - j < Wo
+          const int j0 = max(0, x + pw - (Wo - 1)), j1 = min(kw - 1, x + pw);
+          for (int j = j0; j <= j1; ++j) acc += base[(x + pw - j) * CGZ + j];
+        } else {
+          for (int j = 0; j < kw; ++j) {
+            const int wn = x + pw - j;
+            if (wn < 0) break;
+            const int w = wn / sw;
+            if (w * sw != wn || w >= Wo) continue;
+            acc += base[w * CGZ + j];
+          }
         }
       }
     }
-    __syncthreads();  // this slab is the target of the prefetch issued STAGES-1 iterations later
+    __syncthreads();  // this group's slots are the target of the prefetch issued in the next iteration
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
   T* outb = ring;
@@ -251,7 +276,7 @@ static int col2im_launch(const T* col, long B, int C, int H, int W, int kh, int 
     int CG = 0;
     for (int cand = C; cand >= 1; --cand)
       if (C % cand == 0 && (long)cand * H * W <= 1024 && ((long)cand * kh * kw * sizeof(T)) % 16 == 0) { CG = cand; break; }
-    constexpr int kStages = 8;  // seven slabs in flight per block: enough bytes outstanding to cover HBM latency
+    constexpr int kStages = 9;  // three groups of three slabs: six slabs in flight per block while three are summed
     if (CG > 0 && ((uintptr_t)col & 15) == 0 && ((long)C * kh * kw * sizeof(T)) % 16 == 0) {
       const long slab_bytes = (long)Wo * CG * kh * kw * sizeof(T);
       const size_t smem = (size_t)std::max<long>(kStages * slab_bytes, (long)CG * H * W * sizeof(T));
@@ -305,17 +330,36 @@ __global__ void max_pool_kernel(const T* __restrict__ x, T* __restrict__ top, in
   const long plane = (long)blockIdx.x * blockDim.z + threadIdx.z;
   if (px >= g.PW || py >= g.PH || plane >= planes) return;
   const T* xp = x + plane * (long)g.H * g.W;
-  int hstart = py * sh - g.ph, wstart = px * sw - g.pw;
-  const int hend = min(hstart + kh, g.H), wend = min(wstart + kw, g.W);
-  hstart = max(hstart, 0);
-  wstart = max(wstart, 0);
   T best = T(-FLT_MAX);
   int besti = -1;
-  for (int h = hstart; h < hend; ++h)
-    for (int w = wstart; w < wend; ++w) {
-      const T v = xp[h * g.W + w];
-      if (v > best) { best = v; besti = h * g.W + w; }
-    }
+  if constexpr (KH > 0) {
+    // compile-time window: every load is issued up front (clamped address), the scan order stays h-major
+    const int h0 = py * SH - g.ph, w0 = px * SW - g.pw;
+    T v[KH][KW];
+#pragma unroll
+    for (int dh = 0; dh < KH; ++dh)
+#pragma unroll
+      for (int dw = 0; dw < KW; ++dw) {
+        const int h = h0 + dh, w = w0 + dw;
+        const bool ok = h >= 0 && h < g.H && w >= 0 && w < g.W;
+        v[dh][dw] = ok ? xp[h * g.W + w] : T(-FLT_MAX);  // never greater than `best`: skipped like an outside cell
+      }
+#pragma unroll
+    for (int dh = 0; dh < KH; ++dh)
+#pragma unroll
+      for (int dw = 0; dw < KW; ++dw)
+        if (v[dh][dw] > best) { best = v[dh][dw]; besti = (h0 + dh) * g.W + (w0 + dw); }
+  } else {
+    int hstart = py * sh - g.ph, wstart = px * sw - g.pw;
+    const int hend = min(hstart + kh, g.H), wend = min(wstart + kw, g.W);
+    hstart = max(hstart, 0);
+    wstart = max(wstart, 0);
+    for (int h = hstart; h < hend; ++h)
+      for (int w = wstart; w < wend; ++w) {
+        const T v = xp[h * g.W + w];
+        if (v > best) { best = v; besti = h * g.W + w; }
+      }
+  }
   const long o = (plane * g.PH + py) * g.PW + px;
   top[o] = best;
   mask[o] = besti;
@@ -341,9 +385,32 @@ __global__ void max_pool_pullback_kernel(const int32_t* __restrict__ mask, const
   const int px1 = min((w + g.pw) / sw, g.PW - 1);
   const int me = h * g.W + w;
   T acc = T(0);
-  for (int py = py0; py <= py1; ++py)
-    for (int px = px0; px <= px1; ++px)
-      if (mp[py * g.PW + px] == me) acc += gp[py * g.PW + px];
+  if constexpr (KH > 0) {
+    // at most NY x NX windows cover a pixel: load every mask / gradient pair first (clamped address),
+    // then add the matching ones in (py, px) order
+    constexpr int NY = (KH + SH - 1) / SH, NX = (KW + SW - 1) / SW;
+    int mv[NY][NX];
+    T gv[NY][NX];
+#pragma unroll
+    for (int a = 0; a < NY; ++a)
+#pragma unroll
+      for (int b = 0; b < NX; ++b) {
+        const int py = py0 + a, px = px0 + b;
+        const bool ok = py <= py1 && px <= px1;
+        const int o = ok ? py * g.PW + px : 0;
+        mv[a][b] = ok ? mp[o] : -2;
+        gv[a][b] = gp[o];
+      }
+#pragma unroll
+    for (int a = 0; a < NY; ++a)
+#pragma unroll
+      for (int b = 0; b < NX; ++b)
+        if (mv[a][b] == me) acc += gv[a][b];
+  } else {
+    for (int py = py0; py <= py1; ++py)
+      for (int px = px0; px <= px1; ++px)
+        if (mp[py * g.PW + px] == me) acc += gp[py * g.PW + px];
+  }
   gx[(plane * g.H + h) * g.W + w] = acc;
 }
 

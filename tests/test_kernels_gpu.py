@@ -384,6 +384,21 @@ def test_sgemm_unaligned_is_refused_by_tma_feed(rt):
     np.testing.assert_allclose(dC.get(), np.full((64, 32), 75.0, "f4"))
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 10, 256), (128, 256, 10), (256, 10, 128), (3, 5, 4), (1, 1, 1), (65, 63, 17), (7, 9, 2047)])
+@pytest.mark.parametrize("tA,tB", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_sgemm_small_products(rt, M, N, K, tA, tB):
+    rs = np.random.RandomState(21)
+    A = rs.randn(*((K, M) if tA else (M, K))).astype("f4")
+    B = rs.randn(*((N, K) if tB else (K, N))).astype("f4")
+    want = O.mul22(A, B, tA, tB)
+    dA, dB, dC = Dev(A), Dev(B), Dev(shape=(M, N), dtype="f4")
+    call("cgtb_sgemm", tA, tB, M, N, K, dA.ptr, A.shape[1], dB.ptr, B.shape[1], dC.ptr, N, 5)
+    got = dC.get()
+    exact = (A.T if tA else A).astype("f8") @ (B.T if tB else B).astype("f8")
+    assert np.abs(got - exact).max() <= 4 * np.abs(want - exact).max() + 1e-5 * np.sqrt(K)
+    np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-5 * np.sqrt(K))
+
+
 def test_sgemm_batched_and_dgemm(rt):
     rs = np.random.RandomState(9)
     A, B = rs.randn(2, 3, 5).astype("f4"), rs.randn(2, 5, 7).astype("f4")  # reference test_affine.py:364-375
