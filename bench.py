@@ -236,10 +236,11 @@ def run_b200(args):
                     "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": launches, "clocks": clocks, "final_loss": loss,
         }
-    # roofline of the dominant kernel and the CPU baseline: rank 0, one GPU
-    if world == 1 and not args.no_extras:
+    # roofline of the dominant kernel (rank 0, on the single-GPU graph: the per-GPU work is the same at every
+    # N under weak scaling) and, at N = 1, the CPU baseline
+    if rank == 0 and not args.no_extras:
         peaks = load_peaks()
-        table = profile_ops(builder, dev_batches[0])
+        table = profile_ops(lambda: configs.build_cifar(batch=BATCH), dev_batches[0])
         total_ms = sum(t["ms"] for t in table.values())
         dom = max(table.items(), key=lambda kv: kv[1]["ms"])
         name, t = dom
@@ -261,7 +262,8 @@ def run_b200(args):
         step_bytes = sum(v["bytes"] for v in table.values())
         out["step_roofline"] = {"algorithmic_bytes_per_step": step_bytes, "hbm_floor_ms": step_bytes / (peaks["hbm_gbs"] * 1e9) * 1e3,
                                 "frac": (step_bytes / (peaks["hbm_gbs"] * 1e9) * 1e3) / (ms_dev / args.steps)}
-        out["cpu_baseline"] = cpu_baseline(sample_steps=5, warmup=2)
+        if world == 1:
+            out["cpu_baseline"] = cpu_baseline(sample_steps=5, warmup=2)
     parallel.barrier()
     if rank == 0:
         print(json.dumps(out))

@@ -414,6 +414,54 @@ __global__ void max_pool_pullback_kernel(const int32_t* __restrict__ mask, const
   gx[(plane * g.H + h) * g.W + w] = acc;
 }
 
+// Pullback for rows whose length is a multiple of four (compile-time window): a thread owns four
+// consecutive pixels. The windows that can cover them span NY rows x NXG columns of the pooled plane;
+// their masks and gradients are loaded once (instead of once per pixel), every pixel then adds its
+// matches in (py, px) order, and the four sums leave as one 16-byte store.
+template <typename T, int KH, int KW, int SH, int SW>
+__global__ void max_pool_pullback_vec4_kernel(const int32_t* __restrict__ mask, const T* __restrict__ gtop, T* __restrict__ gx,
+                                              long planes, const PoolGeom g) {
+  constexpr int NY = (KH + SH - 1) / SH, NXG = (KW + 2) / SW + 1;
+  const int w0 = 4 * (blockIdx.z * blockDim.x + threadIdx.x), h = blockIdx.y * blockDim.y + threadIdx.y;
+  const long plane = (long)blockIdx.x * blockDim.z + threadIdx.z;
+  if (w0 >= g.W || h >= g.H || plane >= planes) return;
+  const int32_t* mp = mask + plane * (long)g.PH * g.PW;
+  const T* gp = gtop + plane * (long)g.PH * g.PW;
+  const int hy = h + g.ph - KH + 1, wx = w0 + g.pw - KW + 1;
+  const int py0 = hy <= 0 ? 0 : (hy + SH - 1) / SH;
+  const int py1 = min((h + g.ph) / SH, g.PH - 1);
+  const int px0 = wx <= 0 ? 0 : (wx + SW - 1) / SW;
+  const int px1 = min((w0 + 3 + g.pw) / SW, g.PW - 1);
+  int mv[NY][NXG];
+  T gv[NY][NXG];
+#pragma unroll
+  for (int a = 0; a < NY; ++a)
+#pragma unroll
+    for (int b = 0; b < NXG; ++b) {
+      const int py = py0 + a, px = px0 + b;
+      const bool ok = py <= py1 && px <= px1;
+      const int o = ok ? py * g.PW + px : 0;
+      mv[a][b] = ok ? mp[o] : -2;
+      gv[a][b] = gp[o];
+    }
+  T acc[4];
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    const int me = h * g.W + w0 + p;
+    T s = T(0);
+#pragma unroll
+    for (int a = 0; a < NY; ++a)
+#pragma unroll
+      for (int b = 0; b < NXG; ++b)
+        if (mv[a][b] == me) s += gv[a][b];  // the mask names this pixel only if the window covers it
+    acc[p] = s;
+  }
+  typedef typename std::conditional<sizeof(T) == 4, float4, double4>::type V4;
+  V4 v;
+  v.x = acc[0]; v.y = acc[1]; v.z = acc[2]; v.w = acc[3];
+  *reinterpret_cast<V4*>(gx + (plane * g.H + h) * g.W + w0) = v;
+}
+
 // block (x, y, planes) and grid for a plane of `rows` x `cols` elements
 static void pool_launch_dims(long planes, int rows, int cols, dim3& grid, dim3& block) {
   int bx = 1;
@@ -465,7 +513,12 @@ CGTB_API int cgtb_max_pool_pullback(int dtype, const int32_t* mask, const void* 
   dim3 grid, block;
   pool_launch_dims(planes, H, W, grid, block);
   if (grid.y > 65535 || grid.z > 65535) return fail("cgtb_max_pool_pullback: plane too large");
-  if (dtype == cgtb_f4)
+  const bool known = (kh == 3 && kw == 3 && sh == 2 && sw == 2) || (kh == 2 && kw == 2 && sh == 2 && sw == 2);
+  if (dtype == cgtb_f4 && known && (W % 4) == 0 && ((uintptr_t)gx & 15) == 0) {
+    pool_launch_dims(planes, H, W / 4, grid, block);
+    if (kh == 3) CGTB_LAUNCH((max_pool_pullback_vec4_kernel<float, 3, 3, 2, 2>), grid, block, 0, mask, (const float*)gtop, (float*)gx, planes, g);
+    else CGTB_LAUNCH((max_pool_pullback_vec4_kernel<float, 2, 2, 2, 2>), grid, block, 0, mask, (const float*)gtop, (float*)gx, planes, g);
+  } else if (dtype == cgtb_f4)
     CGTB_POOL_DISPATCH(max_pool_pullback_kernel, float, mask, (const float*)gtop, (float*)gx, planes, g);
   else if (dtype == cgtb_f8)
     CGTB_POOL_DISPATCH(max_pool_pullback_kernel, double, mask, (const double*)gtop, (double*)gx, planes, g);

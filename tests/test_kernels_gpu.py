@@ -55,6 +55,8 @@ POOLS = [
     ((4, 64, 6, 6), (3, 3), (0, 0), (2, 2)),
     ((2, 3, 9, 11), (3, 3), (1, 1), (2, 2)),     # padded
     ((2, 2, 8, 8), (2, 2), (0, 0), (2, 2)),      # non-overlapping
+    ((2, 3, 12, 12), (3, 3), (1, 1), (2, 2)),    # padded, row length a multiple of four (four pixels per thread)
+    ((2, 3, 8, 4), (2, 2), (1, 1), (2, 2)),
     ((1, 1, 6, 6), (3, 2), (1, 0), (1, 2)),
 ]
 
