@@ -39,26 +39,30 @@ __global__ void __launch_bounds__(256, 5) im2col_rows_kernel(const T* __restrict
     const int h = (int)(row - b * Ho);
     const T* xb = x + b * (long)C * H * W;
     __syncthreads();  // the previous row's copy-out has finished reading the slab (and offp is written)
-    // four independent loads per thread are issued before the first is stored: the staging is bound by
-    // the latency of reaching L2 / HBM, not by bytes
-    const int slab_n = nrows * Wp;
-    for (int e0 = threadIdx.x; e0 < slab_n; e0 += 4 * blockDim.x) {
-      T v[4];
+    // staging: a warp takes four slab rows at a time (lanes along the row, no index division per
+    // element) and issues their loads before the first store: bound by latency, not by bytes
+    {
+      const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+      for (int ri0 = warp; ri0 < nrows; ri0 += 4 * nwarps) {
+        const T* src[4];
+        bool rok[4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int e = e0 + k * blockDim.x;
-        v[k] = T(0);
-        if (e < slab_n) {
-          const int ri = e / Wp, wq = e - ri * Wp;
+        for (int u = 0; u < 4; ++u) {
+          const int ri = ri0 + u * nwarps;
           const int c_im = ri / kh, i = ri - c_im * kh;
-          const int hin = h * sh - ph + i, win = wq - pw;
-          if (hin >= 0 && hin < H && win >= 0 && win < W) v[k] = __ldg(xb + ((long)c_im * H + hin) * W + win);
+          const int hin = h * sh - ph + i;
+          rok[u] = ri < nrows && hin >= 0 && hin < H;
+          src[u] = xb + ((long)c_im * H + (rok[u] ? hin : 0)) * W - pw;
         }
-      }
+        for (int wq = lane; wq < Wp; wq += 32) {
+          const bool wok = wq >= pw && wq < W + pw;
+          T v[4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int e = e0 + k * blockDim.x;
-        if (e < slab_n) slab[e] = v[k];
+          for (int u = 0; u < 4; ++u) v[u] = (rok[u] && wok) ? __ldg(src[u] + wq) : T(0);
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (ri0 + u * nwarps < nrows) slab[(ri0 + u * nwarps) * Wp + wq] = v[u];
+        }
       }
     }
     __syncthreads();
@@ -209,6 +213,18 @@ __global__ void __launch_bounds__(1024, 2) col2im_image_kernel(const T* __restri
   constexpr int G = 3, NG = STAGES / G;
   static_assert(STAGES % G == 0 && NG >= 2, "the ring holds whole groups");
   const int ngroups_total = (Ho + G - 1) / G;
+  // a thread copies the same 16-byte units of every slab: their offsets are computed once
+  constexpr int NQ = 2;
+  const int nunits = Wo * seg16;
+  uint32_t soff[NQ], doff[NQ];
+#pragma unroll
+  for (int u = 0; u < NQ; ++u) {
+    const int q = t + u * blockDim.x;
+    const int w = q / seg16, r = q - w * seg16;
+    soff[u] = (uint32_t)((size_t)w * Z * sizeof(T) + (size_t)r * 16);
+    doff[u] = (uint32_t)((size_t)w * CGZ * sizeof(T) + (size_t)r * 16);
+  }
+  const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(ring);
   auto prefetch_group = [&](int gi) {
     if (gi < ngroups_total) {
       const int slot0 = (gi % NG) * G;
@@ -216,12 +232,17 @@ __global__ void __launch_bounds__(1024, 2) col2im_image_kernel(const T* __restri
       for (int s2 = 0; s2 < G; ++s2) {
         const int h = Ho - 1 - (gi * G + s2);
         if (h >= 0) {
-          unsigned char* dst = reinterpret_cast<unsigned char*>(ring + (size_t)(slot0 + s2) * slab_n);
+          const uint32_t dst = ring_s + (uint32_t)((size_t)(slot0 + s2) * slab_n * sizeof(T));
           const unsigned char* src = reinterpret_cast<const unsigned char*>(colb + (size_t)h * Wo * Z);
-          for (int q = t; q < Wo * seg16; q += blockDim.x) {
+#pragma unroll
+          for (int u = 0; u < NQ; ++u)
+            if (t + u * (int)blockDim.x < nunits)
+              asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + doff[u]), "l"(src + soff[u]) : "memory");
+          for (int q = t + NQ * blockDim.x; q < nunits; q += blockDim.x) {  // blocks with few threads
             const int w = q / seg16, r = q - w * seg16;
-            const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst + ((size_t)w * CGZ * sizeof(T) + (size_t)r * 16));
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src + ((size_t)w * Z * sizeof(T) + (size_t)r * 16)) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + (uint32_t)((size_t)w * CGZ * sizeof(T) + (size_t)r * 16)),
+                         "l"(src + ((size_t)w * Z * sizeof(T) + (size_t)r * 16))
+                         : "memory");
           }
         }
       }
@@ -536,47 +557,43 @@ CGTB_API int cgtb_max_pool_pullback(int dtype, const int32_t* mask, const void* 
 //   forward window of channel c : [c - (n-1)/2, c + n - (n-1)/2 - 1]
 //   backward window of channel c: [c - (n - (n+1)/2), c + (n+1)/2 - 1]
 // ================================================================================================
-template <typename T, typename I>
-__global__ void lrn_forward_kernel(const T* __restrict__ x, T* __restrict__ top, T* __restrict__ scale, I total,
-                                   int C, int HW, int size, T alpha_over_size, T negative_beta) {
+// grid = (ceil(HW / blockDim), C, N): the channel and image come from the block index, no thread divides
+template <typename T>
+__global__ void lrn_forward_kernel(const T* __restrict__ x, T* __restrict__ top, T* __restrict__ scale, int C, int HW,
+                                   int size, T alpha_over_size, T negative_beta) {
   const int pre = (size - 1) / 2, post = size - pre - 1;
-  for (I idx = (I)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (I)gridDim.x * blockDim.x) {
-    I t = idx / (I)HW;
-    int hw = (int)(idx - t * (I)HW);
-    I n = t / (I)C;
-    int c = (int)(t - n * (I)C);
-    const T* col = x + (size_t)n * C * HW + hw;
-    int lo = max(c - pre, 0), hi = min(c + post, C - 1);
-    T acc = T(0);
-    for (int k = lo; k <= hi; ++k) {
-      T v = col[(long)k * HW];
-      acc += v * v;
-    }
-    T s = (T)(1. + (double)(acc * alpha_over_size));
-    scale[idx] = s;
-    top[idx] = col[(long)c * HW] * pow(s, negative_beta);
+  const int hw = blockIdx.x * blockDim.x + threadIdx.x, c = blockIdx.y;
+  if (hw >= HW) return;
+  const size_t nbase = (size_t)blockIdx.z * C * HW + hw;
+  const T* col = x + nbase;
+  const int lo = max(c - pre, 0), hi = min(c + post, C - 1);
+  T acc = T(0);
+  for (int k = lo; k <= hi; ++k) {
+    const T v = col[k * HW];
+    acc += v * v;
   }
+  const T s = (T)(1. + (double)(acc * alpha_over_size));
+  const size_t o = nbase + (size_t)c * HW;
+  scale[o] = s;
+  top[o] = col[c * HW] * pow(s, negative_beta);
 }
 
-template <typename T, typename I>
+template <typename T>
 __global__ void lrn_backward_kernel(const T* __restrict__ x, const T* __restrict__ top, const T* __restrict__ scale,
-                                    const T* __restrict__ gtop, T* __restrict__ gx, I total, int C, int HW, int size,
+                                    const T* __restrict__ gtop, T* __restrict__ gx, int C, int HW, int size,
                                     T negative_beta, T cache_ratio) {
   const int pre = size - (size + 1) / 2, post = size - pre - 1;
-  for (I idx = (I)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (I)gridDim.x * blockDim.x) {
-    I t = idx / (I)HW;
-    int hw = (int)(idx - t * (I)HW);
-    I n = t / (I)C;
-    int c = (int)(t - n * (I)C);
-    long base = (long)n * C * HW + hw;
-    int lo = max(c - pre, 0), hi = min(c + post, C - 1);
-    T acc = T(0);
-    for (int k = lo; k <= hi; ++k) {
-      long o = base + (long)k * HW;
-      acc += gtop[o] * top[o] / scale[o];
-    }
-    gx[idx] = gtop[idx] * pow(scale[idx], negative_beta) - cache_ratio * x[idx] * acc;
+  const int hw = blockIdx.x * blockDim.x + threadIdx.x, c = blockIdx.y;
+  if (hw >= HW) return;
+  const size_t nbase = (size_t)blockIdx.z * C * HW + hw;
+  const int lo = max(c - pre, 0), hi = min(c + post, C - 1);
+  T acc = T(0);
+  for (int k = lo; k <= hi; ++k) {
+    const size_t o = nbase + (size_t)k * HW;
+    acc += gtop[o] * top[o] / scale[o];
   }
+  const size_t idx = nbase + (size_t)c * HW;
+  gx[idx] = gtop[idx] * pow(scale[idx], negative_beta) - cache_ratio * x[idx] * acc;
 }
 
 CGTB_API int cgtb_lrn_forward(int dtype, const void* x, long N, int C, int H, int W, int size, double alpha, double beta,
@@ -585,16 +602,16 @@ CGTB_API int cgtb_lrn_forward(int dtype, const void* x, long N, int C, int H, in
   if (size <= 0) return fail("cgtb_lrn_forward: localsize must be positive");
   long total = N * C * H * W;
   if (total <= 0) return 0;
-  long blocks = std::min<long>(cgtb_ceil_div(total, 256), (long)rt().sm_count * 32);
-  if (dtype == cgtb_f4 && total < (1L << 31))
-    CGTB_LAUNCH((lrn_forward_kernel<float, unsigned>), (unsigned)blocks, 256, 0, (const float*)x, (float*)top, (float*)scale, (unsigned)total, C,
-                H * W, size, (float)(alpha / size), (float)(-beta));
-  else if (dtype == cgtb_f4)
-    CGTB_LAUNCH((lrn_forward_kernel<float, long>), (unsigned)blocks, 256, 0, (const float*)x, (float*)top, (float*)scale, total, C,
-                H * W, size, (float)(alpha / size), (float)(-beta));
+  if (N > 65535 || C > 65535 || (long)C * H * W >= (1L << 31)) return fail("cgtb_lrn_forward: extents too large");
+  const int HW = H * W;
+  const int threads = HW >= 256 ? 256 : (HW >= 128 ? 128 : 64);
+  dim3 grid((unsigned)cgtb_ceil_div(HW, threads), (unsigned)C, (unsigned)N);
+  if (dtype == cgtb_f4)
+    CGTB_LAUNCH(lrn_forward_kernel<float>, grid, threads, 0, (const float*)x, (float*)top, (float*)scale, C, HW, size,
+                (float)(alpha / size), (float)(-beta));
   else if (dtype == cgtb_f8)
-    CGTB_LAUNCH((lrn_forward_kernel<double, long>), (unsigned)blocks, 256, 0, (const double*)x, (double*)top, (double*)scale, total,
-                C, H * W, size, alpha / size, -beta);
+    CGTB_LAUNCH(lrn_forward_kernel<double>, grid, threads, 0, (const double*)x, (double*)top, (double*)scale, C, HW, size,
+                alpha / size, -beta);
   else
     return fail("cgtb_lrn_forward: unsupported dtype %d", dtype);
   CGTB_CHECK_LAUNCH("lrn_forward");
@@ -607,19 +624,16 @@ CGTB_API int cgtb_lrn_backward(int dtype, const void* x, const void* top, const 
   if (size <= 0) return fail("cgtb_lrn_backward: localsize must be positive");
   long total = N * C * H * W;
   if (total <= 0) return 0;
-  long blocks = std::min<long>(cgtb_ceil_div(total, 256), (long)rt().sm_count * 32);
-  if (dtype == cgtb_f4 && total < (1L << 31))
-    CGTB_LAUNCH((lrn_backward_kernel<float, unsigned>), (unsigned)blocks, 256, 0, (const float*)x, (const float*)top,
-                (const float*)scale, (const float*)gtop, (float*)gx, (unsigned)total, C, H * W, size, (float)(-beta),
-                (float)(2. * alpha * beta / size));
-  else if (dtype == cgtb_f4)
-    CGTB_LAUNCH((lrn_backward_kernel<float, long>), (unsigned)blocks, 256, 0, (const float*)x, (const float*)top,
-                (const float*)scale, (const float*)gtop, (float*)gx, total, C, H * W, size, (float)(-beta),
-                (float)(2. * alpha * beta / size));
+  if (N > 65535 || C > 65535 || (long)C * H * W >= (1L << 31)) return fail("cgtb_lrn_backward: extents too large");
+  const int HW = H * W;
+  const int threads = HW >= 256 ? 256 : (HW >= 128 ? 128 : 64);
+  dim3 grid((unsigned)cgtb_ceil_div(HW, threads), (unsigned)C, (unsigned)N);
+  if (dtype == cgtb_f4)
+    CGTB_LAUNCH(lrn_backward_kernel<float>, grid, threads, 0, (const float*)x, (const float*)top, (const float*)scale,
+                (const float*)gtop, (float*)gx, C, HW, size, (float)(-beta), (float)(2. * alpha * beta / size));
   else if (dtype == cgtb_f8)
-    CGTB_LAUNCH((lrn_backward_kernel<double, long>), (unsigned)blocks, 256, 0, (const double*)x, (const double*)top,
-                (const double*)scale, (const double*)gtop, (double*)gx, total, C, H * W, size, -beta,
-                2. * alpha * beta / size);
+    CGTB_LAUNCH(lrn_backward_kernel<double>, grid, threads, 0, (const double*)x, (const double*)top, (const double*)scale,
+                (const double*)gtop, (double*)gx, C, HW, size, -beta, 2. * alpha * beta / size);
   else
     return fail("cgtb_lrn_backward: unsupported dtype %d", dtype);
   CGTB_CHECK_LAUNCH("lrn_backward");
