@@ -311,9 +311,13 @@ def fuse_elementwise(outputs, updatetargs, node2shape):
                 replace[o] = ti
     if not replace:
         return list(outputs), list(updatetargs)
-    # rewire every surviving consumer (fused nodes included: their inputs may be outputs of other groups)
+    return _rewire(outputs, updatetargs, replace)
+
+
+def _rewire(outputs, updatetargs, replace):
+    """Point every surviving consumer at the replacement nodes (the replacements' own inputs included)."""
     seen = set()
-    stack = [replace.get(o, o) for o in all_out]
+    stack = [replace.get(o, o) for o in list(outputs) + list(updatetargs)]
     while stack:
         node = stack.pop()
         if node in seen or node.is_input():
@@ -324,6 +328,65 @@ def fuse_elementwise(outputs, updatetargs, node2shape):
                 node.parents[pos] = replace[par]
             stack.append(node.parents[pos])
     return [replace.get(o, o) for o in outputs], [replace.get(o, o) for o in updatetargs]
+
+
+def fuse_conv_dgrad(outputs, updatetargs, node2shape):
+    """Col2Im(Reshape(Mul22{N,N}(Reshape(dy NHWC), Reshape(W)))) -> ConvDgrad(dy, W transposed to
+    [C, kh, kw, Cin]) for stride-1 convolutions whose extents the kernel supports (input channels of the
+    product a multiple of 32, at most 128 image channels in multiples of 16, rows of at most 128 pixels).
+    The intermediate nodes must have no other consumer."""
+    from .nn_ops import im2col as im2col_ops
+    all_out = list(outputs) + list(updatetargs)
+    nodes = core.topsorted(all_out)
+    nchildren = defaultdict(int)
+    for node in nodes:
+        for par in node.parents:
+            nchildren[par] += 1
+    out_set = set(all_out)
+    replace = {}
+    for node in nodes:
+        if node.is_input() or not isinstance(node.op, im2col_ops.Col2Im) or node.dtype != "f4":
+            continue
+        info = node.op.info
+        if info.stride_h != 1 or info.stride_w != 1:
+            continue
+        r1 = node.parents[0]
+        if r1.is_input() or not isinstance(r1.op, core.Reshape) or nchildren[r1] != 1 or r1 in out_set:
+            continue
+        m = r1.parents[0]
+        if m.is_input() or not isinstance(m.op, core.Mul22) or m.op.tA or m.op.tB or nchildren[m] != 1 or m in out_set:
+            continue
+        (a, w2) = m.parents
+        if a.is_input() or w2.is_input() or not isinstance(a.op, core.Reshape) or not isinstance(w2.op, core.Reshape):
+            continue
+        t4, w4 = a.parents[0], w2.parents[0]
+        if t4.ndim != 4 or w4.ndim != 4 or t4.dtype != "f4" or w4.dtype != "f4":
+            continue
+        shapes = [_static_shape(node2shape[x]) if x in node2shape else None for x in (node, t4, w4, a, r1)]
+        if any(sh is None for sh in shapes):
+            continue
+        (dx_s, t4_s, w4_s, a_s, r1_s) = shapes
+        (B, C, H, W) = dx_s
+        (Bt, Ho, Wo, Cin) = t4_s
+        if Bt != B or w4_s != (Cin, C, info.kernel_h, info.kernel_w) or a_s != (B * Ho * Wo, Cin):
+            continue
+        if r1_s != (B, Ho, Wo, C * info.kernel_h * info.kernel_w):
+            continue
+        if Ho != H + 2 * info.pad_h - info.kernel_h + 1 or Wo != W + 2 * info.pad_w - info.kernel_w + 1:
+            continue
+        if Cin % 32 != 0 or C % 16 != 0 or C > 128 or W > 128:
+            continue
+        wr = core.Result(core.Transpose((1, 2, 3, 0)), [w4])
+        ws = node2shape[w4]
+        node2shape[wr] = [ws[1], ws[2], ws[3], ws[0]]
+        wr.props.update(node.props)
+        dx = core.Result(im2col_ops.ConvDgrad(info), [t4, wr] + list(node.parents[1:]))
+        node2shape[dx] = node2shape[node]
+        dx.props.update(node.props)
+        replace[node] = dx
+    if not replace:
+        return list(outputs), list(updatetargs)
+    return _rewire(outputs, updatetargs, replace)
 
 
 def prebuild_fused_kernels(builders):
@@ -636,6 +699,8 @@ def run_compilation_pipeline(inputs, outputs, updates, givens):
     config = core.get_config()
     outputs_simple, updatesrcs, updatetargs_simple, analysis = simplify_for_execution(outputs, updates, givens)
     node2shape = analysis["node2shape"]
+    if config["fuse_conv_dgrad"]:
+        outputs_simple, updatetargs_simple = fuse_conv_dgrad(outputs_simple, updatetargs_simple, node2shape)
     if config["fuse_elementwise"]:
         outputs_simple, updatetargs_simple = fuse_elementwise(outputs_simple, updatetargs_simple, node2shape)
     all_out = outputs_simple + updatetargs_simple

@@ -67,12 +67,30 @@ struct TmaParams {
   int raw_stages, conv_stages;
   int tmem_cols;
   int* err;
+  // Implicit convolution (conv != 0): the X tile of K block kb is not a block of a stored matrix but the
+  // window of the NHWC tensor behind mapX that kernel tap (i, j) of that block addresses; see sgemm_tma_conv.
+  int conv;
+  int cW, cHW;          // width and pixels of an output image
+  int cC;               // output channels (= N of the product)
+  int ckw, ckpt;        // kernel width; K blocks per tap (input channels / 32)
+  int cph, cpw;         // padding
+  int crows, cnimg;     // image rows and images per tile
+  int cnbands;          // tiles per image when an image spans several tiles
+  int cB;               // images
+  int cx_tx;            // bytes one X load delivers (the box may be smaller than 128 rows)
 };
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
       : "memory");
 }
 
@@ -240,7 +258,29 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r1[j]) + __uint_as_float(r2[j]);
         const long j0 = y0 + c0;
-        if (i_g < p.xrows) {
+        if (p.conv) {
+          // tile row = pixel `row` of the tile's image rows; the result goes out as NCHW, the lanes of a
+          // warp writing consecutive pixels of one channel plane
+          const int tile = blockIdx.x;
+          int b, pix;
+          bool valid;
+          if (p.cnimg > 1) {
+            const int li = row / p.cHW;
+            b = tile * p.cnimg + li;
+            pix = row - li * p.cHW;
+            valid = li < p.cnimg && b < p.cB;
+          } else {
+            b = tile / p.cnbands;
+            pix = (tile - b * p.cnbands) * p.crows * p.cW + row;
+            valid = row < p.crows * p.cW && pix < p.cHW;
+          }
+          if (valid) {
+            float* dst = p.C + ((size_t)b * p.cC + j0) * p.cHW + pix;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (j0 + j < p.cC) dst[(size_t)j * p.cHW] = v[j];
+          }
+        } else if (i_g < p.xrows) {
           if (!p.swapped) {  // tile row = product row: 32 contiguous bytes per thread
             float* dst = cbase + i_g * ld + j0;
             if (vec_ok && j0 + 8 <= p.yrows) {
@@ -301,11 +341,23 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       ok = mbar_wait_or_abort(smem_u32(&raw_empty[rs]), ((uint32_t)(kb / RS) & 1u) ^ 1u, abortp);
       if (!ok) break;
       const uint32_t bar = smem_u32(&raw_full[rs]);
-      mbar_arrive_expect_tx(bar, raw_bytes);
       const int k0 = (int)(k_begin + (long)kb * kBK);
       const uint32_t dx = smem_u32(raw0 + (size_t)rs * raw_bytes);
-      if (XMN) tma_load_3d(dx, &mapX, (int)x0, k0, batch, bar);
-      else tma_load_3d(dx, &mapX, k0, (int)x0, batch, bar);
+      if (!XMN && p.conv) {
+        // tap (i, j) of this K block reads the tensor shifted by (ph - i, pw - j); rows and columns that
+        // fall outside the tensor are zero-filled by the TMA unit: that is the convolution's padding
+        mbar_arrive_expect_tx(bar, (uint32_t)p.cx_tx + y_bytes);
+        const int tap = kb / p.ckpt, q = kb - tap * p.ckpt;
+        const int ti = tap / p.ckw, tj = tap - ti * p.ckw;
+        const int tile = blockIdx.x;
+        const int b0 = p.cnimg > 1 ? tile * p.cnimg : tile / p.cnbands;
+        const int yrow0 = p.cnimg > 1 ? 0 : (tile - b0 * p.cnbands) * p.crows;
+        tma_load_4d(dx, &mapX, 32 * q, p.cpw - tj, yrow0 + p.cph - ti, b0, bar);
+      } else {
+        mbar_arrive_expect_tx(bar, raw_bytes);
+        if (XMN) tma_load_3d(dx, &mapX, (int)x0, k0, batch, bar);
+        else tma_load_3d(dx, &mapX, k0, (int)x0, batch, bar);
+      }
       if (YMN) tma_load_3d(dx + x_bytes, &mapY, (int)y0, k0, batch, bar);
       else tma_load_3d(dx + x_bytes, &mapY, k0, (int)y0, batch, bar);
       ++issued;
@@ -400,6 +452,7 @@ int sgemm_tma(int tA, int tB, long P, long M, long N, long K, const float* A, lo
   Side sB = {B, ldb, tB == 0, N, strideB};   // rows of op(B)^T are n; stored [K, N] when not transposed
   if (!aligned_for_tma(sA, P) || !aligned_for_tma(sB, P)) return -1;
   TmaParams p;
+  p.conv = 0;
   p.swapped = (N > M) ? 1 : 0;
   const Side& X = p.swapped ? sB : sA;
   const Side& Y = p.swapped ? sA : sB;
@@ -487,4 +540,117 @@ int sgemm_tma(int tA, int tB, long P, long M, long N, long K, const float* A, lo
   return 0;
 }
 
+// Data gradient of a stride-1 convolution without a column matrix (the reference forms
+// Mul22(dy, W) and then Col2Im: cgt/nn_ops/im2col.py, include/im2col.h:30-50):
+//   dx[b, c, y, x] = sum_{i, j, co} dy[b, y + ph - i, x + pw - j, co] * wr[c, (i*kw + j)*Cin + co]
+// dy is NHWC [B, Ho, Wo, Cin] (the transposed gradient the graph already holds), wr is the filter bank
+// rearranged to [C][kh*kw*Cin], dx is NCHW [B, C, H, W]. It is the GEMM above with M = pixels, N = C,
+// K = kh*kw*Cin whose X operand is never stored: for K block (tap, 32 input channels) the TMA unit
+// loads the window of dy that the tap addresses, a box of whole image rows whose out-of-range rows and
+// columns it zero-fills. A tile is `rows` image rows of one image (rows*W <= 128 pixels) or, for small
+// images, several whole images.
+// returns 0 done, 1 error, -1 not eligible
+int conv_dgrad_tma(const float* dy, long B, int Ho, int Wo, int Cin, const float* wr, int C, int H, int W, int kh, int kw,
+                   int ph, int pw, float* dx) {
+  if (B <= 0 || C <= 0 || H <= 0 || W <= 0) return 0;
+  if (Cin % 32 != 0 || C % 16 != 0 || C > 128 || W > 128 || B >= (1L << 30) || kh <= 0 || kw <= 0) return -1;
+  if (((uintptr_t)dy & 15) != 0 || ((uintptr_t)wr & 15) != 0) return -1;
+  const long K = (long)kh * kw * Cin;
+  const int HW = H * W;
+  TmaParams p;
+  p.conv = 1;
+  p.swapped = 0;
+  p.cW = W;
+  p.cHW = HW;
+  p.cC = C;
+  p.ckw = kw;
+  p.ckpt = Cin / 32;
+  p.cph = ph;
+  p.cpw = pw;
+  p.cB = (int)B;
+  long tiles;
+  if (HW <= 128) {
+    p.cnimg = (int)std::min<long>(128 / HW, B);
+    p.crows = H;
+    p.cnbands = 1;
+    tiles = cgtb_ceil_div(B, p.cnimg);
+  } else {
+    p.cnimg = 1;
+    const int max_rows = 128 / W;
+    p.cnbands = (int)cgtb_ceil_div(H, max_rows);
+    p.crows = (int)cgtb_ceil_div(H, p.cnbands);  // equal bands
+    tiles = B * p.cnbands;
+  }
+  if (tiles > 2147483647L) return -1;
+  p.cx_tx = 32 * W * p.crows * p.cnimg * (int)sizeof(float);
+  const int UN = C;
+  p.UN = UN;
+  p.tmem_cols = 32;
+  while (p.tmem_cols < 2 * UN) p.tmem_cols *= 2;
+  p.xrows = 0;
+  p.yrows = C;
+  const long conv_bytes = 1L * kXRows * 128 + 2L * UN * 128, raw_bytes = (long)kXRows * 128 + (long)UN * 128;
+  int conv_stages, raw_stages;
+  const long half = 110L * 1024 - 1024, whole = 224L * 1024 - 1024;
+  if ((half - 2 * conv_bytes) / raw_bytes >= 3) {
+    conv_stages = 2;
+    raw_stages = (int)std::min<long>(kMaxRaw, (half - 2 * conv_bytes) / raw_bytes);
+  } else if ((half - conv_bytes) / raw_bytes >= 2) {
+    conv_stages = 1;
+    raw_stages = (int)std::min<long>(kMaxRaw, (half - conv_bytes) / raw_bytes);
+  } else {
+    conv_stages = 2;
+    raw_stages = (int)std::min<long>(kMaxRaw, (whole - 2 * conv_bytes) / raw_bytes);
+    if (raw_stages < 2) return -1;
+  }
+  const long nkb = K / kBK;
+  if (raw_stages > nkb) raw_stages = (int)nkb;
+  if (conv_stages > nkb) conv_stages = (int)nkb;
+  p.conv_stages = conv_stages;
+  p.raw_stages = raw_stages;
+  p.nsplit = 1;
+  p.kchunk = K;
+  p.K = K;
+  p.M = B * HW;
+  p.N = C;
+  p.ldc = C;
+  p.c_batch_stride = 0;
+  p.C = dx;
+  p.err = tc_error_flag();
+  if (!p.err) return 1;
+  EncodeTiledFn fn = encoder();
+  if (!fn) return -1;
+  CUtensorMap mapX, mapY;
+  {
+    cuuint64_t dims[4] = {(cuuint64_t)Cin, (cuuint64_t)Wo, (cuuint64_t)Ho, (cuuint64_t)B};
+    cuuint64_t strides[3] = {(cuuint64_t)Cin * 4, (cuuint64_t)Wo * Cin * 4, (cuuint64_t)Ho * Wo * Cin * 4};
+    cuuint32_t box[4] = {32, (cuuint32_t)W, (cuuint32_t)p.crows, (cuuint32_t)p.cnimg};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    if (box[1] > 256 || box[2] > 256 || box[3] > 256) return -1;
+    CUresult r = fn(&mapX, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)dy, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return -1;
+  }
+  Side Y = {wr, K, false, C, 0};
+  if (!encode(&mapY, Y, K, 1, UN)) return -1;
+  size_t smem = (size_t)conv_stages * conv_bytes + (size_t)raw_stages * raw_bytes + 1024;
+  dim3 grid((unsigned)tiles, 1, 1);
+  const int cap = 227 * 1024 - 2048;
+  static bool cfg = false;
+  if (!cfg) { CGTB_CUDA_TRY(cudaFuncSetAttribute(sgemm_tma_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap)); cfg = true; }
+  CGTB_LAUNCH((sgemm_tma_kernel<false, false>), grid, kThreadsTma, smem, mapX, mapY, p);
+  CGTB_CHECK_LAUNCH("conv_dgrad");
+  return 0;
+}
+
 }  // namespace cgtb
+
+CGTB_API int cgtb_conv_dgrad(const float* dy_nhwc, long B, int Ho, int Wo, int Cin, const float* w_rearranged, int C, int H, int W,
+                             int kh, int kw, int ph, int pw, float* dx_nchw) {
+  if (!require_runtime("cgtb_conv_dgrad")) return 1;
+  int rc = cgtb::conv_dgrad_tma(dy_nhwc, B, Ho, Wo, Cin, w_rearranged, C, H, W, kh, kw, ph, pw, dx_nchw);
+  if (rc < 0)
+    return fail("cgtb_conv_dgrad: not supported for Cin=%d (multiple of 32), C=%d (multiple of 16, at most 128), W=%d (at most 128) "
+                "or an unaligned operand; use cgtb_sgemm + cgtb_col2im", Cin, C, W);
+  return rc;
+}

@@ -245,6 +245,21 @@ OP_BYREF(cgtb_op_col2im) {
   cgtb_col2im(col->dtype(), col->data(), B, (int)C, (int)H, (int)W, cl->kernel_h, cl->kernel_w, cl->pad_h, cl->pad_w,
               cl->stride_h, cl->stride_w, im->data());
 }
+// ConvDgrad: (dy NHWC, filters rearranged to [C, kh, kw, Cin], B, C, H, W) -> dx NCHW
+OP_BYREF(cgtb_op_conv_dgrad) {
+  ConvClosure* cl = (ConvClosure*)cl0;
+  cgtArray *dy = ARR(reads[0]), *wr = ARR(reads[1]), *dx = ARR(write0);
+  if (!all_gpu({dy, wr, dx})) { fail("ConvDgrad: operands must be on the GPU"); return; }
+  const long* s = dy->shape();
+  const long* d = dx->shape();
+  if (dy->ndim() != 4 || wr->ndim() != 4 || dx->ndim() != 4 || dy->dtype() != cgt_f4 || wr->shape()[0] != d[1] ||
+      wr->shape()[1] != cl->kernel_h || wr->shape()[2] != cl->kernel_w || wr->shape()[3] != s[3] || s[0] != d[0]) {
+    fail("ConvDgrad: operand shapes do not fit together");
+    return;
+  }
+  cgtb_conv_dgrad((const float*)dy->data(), s[0], (int)s[1], (int)s[2], (int)s[3], (const float*)wr->data(), (int)d[1], (int)d[2],
+                  (int)d[3], cl->kernel_h, cl->kernel_w, cl->pad_h, cl->pad_w, (float*)dx->data());
+}
 OP_BYREF(cgtb_op_max_pool) {
   ConvClosure* cl = (ConvClosure*)cl0;
   cgtArray* x = ARR(reads[0]);

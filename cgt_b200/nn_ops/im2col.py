@@ -82,3 +82,35 @@ class Col2Im(core.Op):
 
     def __repr__(self):
         return "Col2Im{%s}" % (tuple(self.info),)
+
+
+class ConvDgrad(core.Op):
+    """(dy NHWC [B,Ho,Wo,Cin], filters rearranged to [C,kh,kw,Cin], B, C, H, W) -> dx NCHW [B,C,H,W]:
+    the data gradient of a stride-1 convolution in one kernel.
+
+    Not part of the reference's Op set. The compiler substitutes it (compilation.fuse_conv_dgrad) for the
+    pair that Im2Col.pullback produces, Col2Im(Mul22(dy, W)) (cgt/nn_ops/im2col.py, cgt/nn.py conv2d), when
+    the extents allow; the column matrix is then neither written nor read."""
+    available_impls = ("native_gpu",)
+
+    def __init__(self, info):
+        assert info.stride_h == 1 and info.stride_w == 1
+        self.info = info
+
+    def get_diff(self, n):
+        return [False] * n
+
+    def shp_apply(self, inputs):
+        return list(inputs[2:])
+
+    def typ_apply(self, inputs):
+        return core.TensorType("f4", 4)
+
+    def host_inputs(self, n):
+        return tuple(range(2, n))
+
+    def get_native_compile_info(self, input_types, devtype):
+        return core.NativeCompileInfo(None, prebuilt="cgtb_op_conv_dgrad", closure_triples=info2closure(self.info))
+
+    def __repr__(self):
+        return "ConvDgrad{%s}" % (tuple(self.info),)

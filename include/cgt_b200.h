@@ -145,6 +145,16 @@ int cgtb_lrn_forward(int dtype, const void* x, long N, int C, int H, int W, int 
 int cgtb_lrn_backward(int dtype, const void* x, const void* top, const void* scale, const void* gtop, long N, int C,
                       int H, int W, int size, double alpha, double beta, void* gx);
 
+/* Data gradient of a stride-1 convolution in one kernel. Replaces the pair Mul22(dy, W) + Col2Im that the
+ * reference's graph holds for it (cgt/nn_ops/im2col.py:Im2Col.pullback, include/im2col.h:30-50): no column
+ * matrix is written or read.
+ *   dx[b, c, y, x] = sum_{i, j, co} dy[b, y + ph - i, x + pw - j, co] * w_rearranged[c][(i*kw + j)*Cin + co]
+ * dy_nhwc [B, Ho, Wo, Cin]; w_rearranged [C][kh*kw*Cin] (the filter bank [Cin, C, kh, kw] transposed to
+ * [C, kh, kw, Cin]); dx_nchw [B, C, H, W]. float32, 3xTF32 tensor-core arithmetic like cgtb_sgemm.
+ * Supported: Cin a multiple of 32, C a multiple of 16 and at most 128, W at most 128, 16-byte-aligned operands. */
+int cgtb_conv_dgrad(const float* dy_nhwc, long B, int Ho, int Wo, int Cin, const float* w_rearranged, int C, int H, int W,
+                    int kh, int kw, int ph, int pw, float* dx_nchw);
+
 /* ElwiseUnary / ElwiseBinary (cgt/core.py:1160-1378). scalar_x / scalar_y: operand is a 0-d array
  * in device memory, read at index 0. */
 int cgtb_unary(int op, int dt_in, int dt_out, long n, const void* in, void* out);

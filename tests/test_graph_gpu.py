@@ -129,3 +129,22 @@ def test_elementwise_fusion_changes_no_bit(rt, name, generated):
         assert np.array_equal(a, b)
     for (a, b) in zip(results[False][3], results[True][3]):
         assert np.array_equal(a, b)
+
+
+def test_conv_dgrad_substitution(rt):
+    """The compiler replaces Mul22 + Col2Im of the stride-1 convolutions' data gradients by ConvDgrad; the
+    losses and parameters stay within the float32 tolerance of the Op-by-Op graph."""
+    res = {}
+    for fuse in (False, True):
+        with cgt.scoped_update_config(fuse_conv_dgrad=fuse, use_cuda_graphs=False):
+            cfg = configs.BUILDERS["cifar"](**SMALL["cifar"])
+            f = cfg.compile()
+            names = [repr(instr) for instr in f.eg.instrs]
+            batches = [cfg.batch(seed) for seed in range(2)]
+            losses = [float(f(*batches[i % 2])[0]) for i in range(6)]
+            params = [np.asarray(p.op.get_value()).copy() for p in cfg.params]
+            res[fuse] = (sum("ConvDgrad" in n for n in names), sum("Col2Im" in n for n in names), losses, params)
+    assert res[False][0] == 0 and res[True][0] == 2 and res[True][1] == 0
+    np.testing.assert_allclose(res[True][2], res[False][2], rtol=1e-4)
+    for (a, b) in zip(res[True][3], res[False][3]):
+        np.testing.assert_allclose(a, b, rtol=1e-3, atol=1e-5)

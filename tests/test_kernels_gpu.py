@@ -414,6 +414,46 @@ def test_sgemm_batched_and_dgemm(rt):
     np.testing.assert_allclose(dC.get(), A @ B.T, rtol=1e-12, atol=1e-12)
 
 
+CONV_DGRADS = [
+    # (B, C, H, W, Cin, k, pad): CIFAR conv2 and conv3 data gradients (scaled batch), bands that do not divide
+    # the image, several small images per tile, a last tile with missing images, two K blocks per tap
+    (8, 32, 15, 15, 32, 5, 2), (7, 32, 6, 6, 64, 5, 2), (3, 16, 20, 9, 32, 3, 1), (2, 48, 33, 128, 32, 3, 1),
+    (5, 32, 4, 4, 32, 3, 0), (2, 128, 7, 5, 96, 1, 0),
+]
+
+
+@pytest.mark.parametrize("B,C,H,W,Cin,k,pad", CONV_DGRADS)
+def test_conv_dgrad_matches_gemm_then_col2im(rt, B, C, H, W, Cin, k, pad):
+    """cgtb_conv_dgrad against the pair it replaces, evaluated by the CPU oracle: Mul22(dy, W) then Col2Im."""
+    rs = np.random.RandomState(41)
+    Ho, Wo = H + 2 * pad - k + 1, W + 2 * pad - k + 1
+    dy = rs.randn(B, Ho, Wo, Cin).astype("f4")           # NHWC gradient of the convolution's output
+    Wf = (rs.randn(Cin, C, k, k) * 0.2).astype("f4")     # filter bank [output channels of the conv, C, kh, kw]
+    col = O.mul22(dy.reshape(B * Ho * Wo, Cin), Wf.reshape(Cin, C * k * k), 0, 0).reshape(B, Ho, Wo, C * k * k)
+    want = O.col2im(col, (B, C, H, W), (k, k), (pad, pad), (1, 1))
+    wr = np.ascontiguousarray(Wf.transpose(1, 2, 3, 0))  # [C, kh, kw, Cin]
+    ddy, dwr, ddx = Dev(dy), Dev(wr), Dev(np.full((B, C, H, W), np.nan, "f4"))
+    L = runtime.lib()
+    L.cgtb_conv_dgrad.restype = ctypes.c_int
+    L.cgtb_conv_dgrad.argtypes = [ctypes.c_void_p, ctypes.c_long] + [ctypes.c_int] * 3 + [ctypes.c_void_p] + [ctypes.c_int] * 7 + [ctypes.c_void_p]
+    call("cgtb_conv_dgrad", ddy.ptr, B, Ho, Wo, Cin, dwr.ptr, C, H, W, k, k, pad, pad, ddx.ptr)
+    got = ddx.get()
+    exact = np.zeros((B, C, H, W))
+    dy8, W8 = dy.astype("f8"), Wf.astype("f8")
+    for i in range(k):
+        for j in range(k):
+            # dx[b,c,y,x] += sum_co dy[b, y+pad-i, x+pad-j, co] * W[co, c, i, j]
+            ys, xs = np.arange(H) + pad - i, np.arange(W) + pad - j
+            yv, xv = (ys >= 0) & (ys < Ho), (xs >= 0) & (xs < Wo)
+            if not yv.any() or not xv.any():
+                continue
+            sub = dy8[:, ys[yv]][:, :, xs[xv]]                      # [B, ny, nx, Cin]
+            exact[:, :, np.where(yv)[0][:, None], np.where(xv)[0][None, :]] += np.einsum("byxo,oc->bcyx", sub, W8[:, :, i, j])
+    scale = np.sqrt(Cin * k * k)
+    assert np.abs(got - exact).max() <= 4 * np.abs(want - exact).max() + 1e-5 * scale
+    np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-5 * scale)
+
+
 class _FusedProgram(ctypes.Structure):
     _fields_ = [("n_in", ctypes.c_int), ("n_ops", ctypes.c_int), ("n_out", ctypes.c_int), ("in_kind", ctypes.c_int * 8),
                 ("op_arity", ctypes.c_int * 16), ("op_code", ctypes.c_int * 16), ("op_a", ctypes.c_int * 16),
