@@ -275,7 +275,8 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
             valid = row < p.crows * p.cW && pix < p.cHW;
           }
           if (valid) {
-            float* dst = p.C + ((size_t)b * p.cC + j0) * p.cHW + pix;
+            // with K splits every split writes its own copy of the whole result; a fold adds them in order
+            float* dst = p.C + (size_t)split * p.cB * p.cC * p.cHW + ((size_t)b * p.cC + j0) * p.cHW + pix;
 #pragma unroll
             for (int j = 0; j < 8; ++j)
               if (j0 + j < p.cC) dst[(size_t)j * p.cHW] = v[j];
@@ -347,7 +348,8 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         // tap (i, j) of this K block reads the tensor shifted by (ph - i, pw - j); rows and columns that
         // fall outside the tensor are zero-filled by the TMA unit: that is the convolution's padding
         mbar_arrive_expect_tx(bar, (uint32_t)p.cx_tx + y_bytes);
-        const int tap = kb / p.ckpt, q = kb - tap * p.ckpt;
+        const int gkb = (int)(k_begin / kBK) + kb;  // K block within the whole product (this CTA may hold one K split)
+        const int tap = gkb / p.ckpt, q = gkb - tap * p.ckpt;
         const int ti = tap / p.ckw, tj = tap - ti * p.ckw;
         const int tile = blockIdx.x;
         const int b0 = p.cnimg > 1 ? tile * p.cnimg : tile / p.cnbands;
@@ -606,16 +608,35 @@ int conv_dgrad_tma(const float* dy, long B, int Ho, int Wo, int Cin, const float
   const long nkb = K / kBK;
   if (raw_stages > nkb) raw_stages = (int)nkb;
   if (conv_stages > nkb) conv_stages = (int)nkb;
+  // few tiles with a long K loop (small images, many taps): split K over CTAs, each split writing its own
+  // copy of the result
+  int nsplit = 1;
+  const long want = (long)rt().sm_count;
+  if (tiles < want && nkb >= 8) nsplit = (int)std::max<long>(1, std::min<long>(cgtb_ceil_div(2 * want, tiles), nkb / 4));
+  const long kchunk = cgtb_ceil_div(nkb, nsplit) * kBK;
+  nsplit = (int)cgtb_ceil_div(K, kchunk);
+  if (nsplit > 65535) return -1;
+  const long nkb_split = kchunk / kBK;
+  if (raw_stages > nkb_split) raw_stages = (int)nkb_split;
+  if (conv_stages > nkb_split) conv_stages = (int)nkb_split;
   p.conv_stages = conv_stages;
   p.raw_stages = raw_stages;
-  p.nsplit = 1;
-  p.kchunk = K;
+  p.nsplit = nsplit;
+  p.kchunk = kchunk;
   p.K = K;
   p.M = B * HW;
   p.N = C;
   p.ldc = C;
   p.c_batch_stride = 0;
-  p.C = dx;
+  const long total = B * (long)C * HW;
+  float* part = nullptr;
+  if (nsplit > 1) {
+    part = (float*)scratch((size_t)nsplit * total * sizeof(float));
+    if (!part) return 1;
+    p.C = part;
+  } else {
+    p.C = dx;
+  }
   p.err = tc_error_flag();
   if (!p.err) return 1;
   EncodeTiledFn fn = encoder();
@@ -634,11 +655,12 @@ int conv_dgrad_tma(const float* dy, long B, int Ho, int Wo, int Cin, const float
   Side Y = {wr, K, false, C, 0};
   if (!encode(&mapY, Y, K, 1, UN)) return -1;
   size_t smem = (size_t)conv_stages * conv_bytes + (size_t)raw_stages * raw_bytes + 1024;
-  dim3 grid((unsigned)tiles, 1, 1);
+  dim3 grid((unsigned)tiles, 1, (unsigned)nsplit);
   const int cap = 227 * 1024 - 2048;
   static bool cfg = false;
   if (!cfg) { CGTB_CUDA_TRY(cudaFuncSetAttribute(sgemm_tma_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap)); cfg = true; }
   CGTB_LAUNCH((sgemm_tma_kernel<false, false>), grid, kThreadsTma, smem, mapX, mapY, p);
+  if (nsplit > 1) tc_splitk_fold(1, 1, total, nsplit, part, dx, total, 0);
   CGTB_CHECK_LAUNCH("conv_dgrad");
   return 0;
 }
