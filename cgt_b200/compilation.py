@@ -185,31 +185,32 @@ def fuse_elementwise(outputs, updatetargs, node2shape):
     for node in nodes:
         for par in node.parents:
             children[par].append(node)
+    # Group dependencies are kept as Python-int bitmasks (bit g = group g): anc[x] is the set of groups
+    # that x depends on, directly or through other groups, at the time x is visited; gclosure[g] the
+    # set of groups that group g depends on, kept transitively closed as groups grow. Joining g makes g
+    # depend on every group among the node's other ancestors: that is allowed only if none of them
+    # depends on g, or the fused nodes would need each other.
     group_of = {}
     members = defaultdict(list)
-    anc_groups = {}            # node -> groups among its strict ancestors
-    gdeps = defaultdict(set)   # group -> groups that some member depends on through nodes outside the group
-    next_gid = [0]
+    anc = {}
+    gclosure = []
 
-    def reaches(h, g):
-        """True when group h depends, directly or through other groups, on group g."""
-        stack, seen = [h], set()
-        while stack:
-            k = stack.pop()
-            if k == g:
-                return True
-            if k in seen:
-                continue
-            seen.add(k)
-            stack.extend(gdeps[k])
-        return False
+    def closed(mask):
+        """mask plus everything its groups depend on"""
+        out, m = mask, mask
+        while m:
+            low = m & -m
+            out |= gclosure[low.bit_length() - 1]
+            m ^= low
+        return out
 
     for node in nodes:
-        anc = set()
+        parent_masks = []
         for par in node.parents:
-            anc |= anc_groups[par]
+            pm = anc[par]
             if par in group_of:
-                anc.add(group_of[par])
+                pm |= 1 << group_of[par]
+            parent_masks.append(pm)
         if _fusable(node):
             chosen = None
             for par in node.parents:
@@ -218,26 +219,34 @@ def fuse_elementwise(outputs, updatetargs, node2shape):
                     continue
                 if len(members[g]) >= core.FusedElwise.MAX_OPS:
                     continue
-                # joining g makes g depend on every other group among the node's ancestors: none of
-                # them may depend on g, or the fused nodes would need each other
-                outside = set()
-                for q in node.parents:
+                outside = 0
+                for (q, pm) in zip(node.parents, parent_masks):
                     if group_of.get(q) != g:
-                        outside |= anc_groups[q]
-                        if q in group_of:
-                            outside.add(group_of[q])
-                if g in outside or any(reaches(h, g) for h in outside):
+                        outside |= pm
+                outside = closed(outside)
+                if (outside >> g) & 1:
                     continue
                 chosen = g
-                gdeps[g] |= (outside - set([g]))
+                outside &= ~(1 << g)
+                if outside & ~gclosure[g]:
+                    gclosure[g] |= outside
+                    gbit, gc = 1 << g, gclosure[g]
+                    for k in range(len(gclosure)):   # groups that depend on g inherit its new dependencies
+                        if gclosure[k] & gbit:
+                            gclosure[k] |= gc
                 break
             if chosen is None:
-                chosen = next_gid[0]
-                next_gid[0] += 1
-                gdeps[chosen] |= anc
+                chosen = len(gclosure)
+                total = 0
+                for pm in parent_masks:
+                    total |= pm
+                gclosure.append(closed(total))
             group_of[node] = chosen
             members[chosen].append(node)
-        anc_groups[node] = anc
+        total = 0
+        for pm in parent_masks:
+            total |= pm
+        anc[node] = closed(total) & ~((1 << group_of[node]) if node in group_of else 0)
     out_set = set(all_out)
     target_set = set(updatetargs)
     replace = {}
