@@ -508,7 +508,7 @@ int sgemm_tc(int tA, int tB, long P, long M, long N, long K, const float* A, lon
   int nsplit = 1;
   long want = (long)rt().sm_count;
   if (tiles < want && nkb_total >= 8) {
-    nsplit = (int)std::min<long>(cgtb_ceil_div(2 * want, tiles), nkb_total / 4);
+    nsplit = (int)std::min<long>(std::max<long>(1, (2 * want) / tiles), nkb_total / 4);  // at most two CTAs per SM: one wave
     if (nsplit < 1) nsplit = 1;
   }
   long kchunk = cgtb_ceil_div(nkb_total, nsplit) * kBK;

@@ -492,7 +492,7 @@ int sgemm_tma(int tA, int tB, long P, long M, long N, long K, const float* A, lo
   int nsplit = 1;
   long want = (long)rt().sm_count;
   if (tiles < want && nkb_total >= 8) {
-    nsplit = (int)std::min<long>(cgtb_ceil_div(2 * want, tiles), nkb_total / 4);
+    nsplit = (int)std::min<long>(std::max<long>(1, (2 * want) / tiles), nkb_total / 4);  // at most two CTAs per SM: one wave
     if (nsplit < 1) nsplit = 1;
   }
   long kchunk = cgtb_ceil_div(nkb_total, nsplit) * kBK;
@@ -612,7 +612,7 @@ int conv_dgrad_tma(const float* dy, long B, int Ho, int Wo, int Cin, const float
   // copy of the result
   int nsplit = 1;
   const long want = (long)rt().sm_count;
-  if (tiles < want && nkb >= 8) nsplit = (int)std::max<long>(1, std::min<long>(cgtb_ceil_div(2 * want, tiles), nkb / 4));
+  if (tiles < want && nkb >= 8) nsplit = (int)std::max<long>(1, std::min<long>(std::max<long>(1, (2 * want) / tiles), nkb / 4));
   const long kchunk = cgtb_ceil_div(nkb, nsplit) * kBK;
   nsplit = (int)cgtb_ceil_div(K, kchunk);
   if (nsplit > 65535) return -1;
