@@ -82,7 +82,11 @@ def fused_source(op):
             loads.append(("none", "", "s%d" % k))
         else:
             params.append("const float* __restrict__ in%d, const long bk%d, const long bi%d" % (k, k, k))
-            loads.append(("pack", "const float b%d = in%d[((i * V) / (I)bi%d) %% (I)bk%d];" % (k, k, k, k), "b%d" % k))
+            # one value per pack when the run length is a multiple of V, else one index per element
+            loads.append(("pack", "float b%d[V];\n    if ((I)bi%d %% V == 0) {\n      const float t = in%d[((i * V) / (I)bi%d) %% (I)bk%d];\n"
+                          "#pragma unroll\n      for (int v = 0; v < V; ++v) b%d[v] = t;\n    } else {\n"
+                          "#pragma unroll\n      for (int v = 0; v < V; ++v) b%d[v] = in%d[((i * V + v) / (I)bi%d) %% (I)bk%d];\n    }"
+                          % (k, k, k, k, k, k, k, k, k, k), "b%d[v]" % k))
     outs = []
     for (q, dt) in enumerate(op.out_dtypes):
         ctype = "float" if dt == "f4" else "int8_t"

@@ -167,10 +167,16 @@ __global__ void fused_elwise_kernel(const FusedArgs a) {
 #pragma unroll
           for (int v = 0; v < V; ++v) r[k][v] = s;
         } break;
-        default: {  // broadcast: with V > 1 the host guarantees inner % V == 0, one value per pack
-          const float s = ((const float*)a.in[k])[((i * V) / a.binner[k]) % a.bk[k]];
+        default: {  // broadcast: one value per pack when the run length is a multiple of V, else one index per element
+          const float* src = (const float*)a.in[k];
+          if (a.binner[k] % V == 0) {
+            const float s = src[((i * V) / a.binner[k]) % a.bk[k]];
 #pragma unroll
-          for (int v = 0; v < V; ++v) r[k][v] = s;
+            for (int v = 0; v < V; ++v) r[k][v] = s;
+          } else {
+#pragma unroll
+            for (int v = 0; v < V; ++v) r[k][v] = src[((i * V + v) / a.binner[k]) % a.bk[k]];
+          }
         } break;
       }
     }
@@ -226,7 +232,6 @@ CGTB_API int cgtb_fused_elwise(const cgtbFusedProgram* prog, long n, const void*
       if (!bcast_k || !bcast_inner || bcast_k[k] <= 0 || bcast_inner[k] <= 0) return fail("cgtb_fused_elwise: bad broadcast extents");
       a.bk[k] = bcast_k[k];
       a.binner[k] = bcast_inner[k];
-      vec = vec && (bcast_inner[k] % kVec) == 0;
     }
   }
   for (int o = 0; o < prog->n_ops; ++o) {
