@@ -398,6 +398,52 @@ def fuse_conv_dgrad(outputs, updatetargs, node2shape):
     return _rewire(outputs, updatetargs, replace)
 
 
+def fuse_conv_output(outputs, updatetargs, node2shape):
+    """FusedElwise{add bias, >= 0, multiply}(Transpose{0,3,1,2}(Reshape(Mul22{N,T}(col, W)))) -> ConvBiasRelu(col, W, bias).
+    Runs after fuse_elementwise; the GEMM, reshape and transpose nodes must have no other consumer."""
+    from .nn_ops import im2col as im2col_ops
+    all_out = list(outputs) + list(updatetargs)
+    nodes = core.topsorted(all_out)
+    nchildren = defaultdict(int)
+    for node in nodes:
+        for par in node.parents:
+            nchildren[par] += 1
+    out_set = set(all_out)
+    want_program = [(2, core.BINARY_OPCODE["+"], 0, 1), (2, core.BINARY_OPCODE[">="], 3, 2), (2, core.BINARY_OPCODE["*"], 3, 4)]
+    replace = {}
+    for node in nodes:
+        if node.is_input() or not isinstance(node.op, core.FusedElwise):
+            continue
+        op = node.op
+        if (op.program != want_program or op.in_kinds != [0, 4, 3] or op.out_regs != [4, 5] or op.out_dtypes != ["i1", "f4"]
+                or op.ndim != 4):
+            continue
+        (t, bias, zero) = node.parents
+        if not _small_int_constant(zero) or int(np.asarray(zero.op.value).reshape(-1)[0]) != 0:
+            continue
+        if t.is_input() or not isinstance(t.op, core.Transpose) or list(t.op.axes) != [0, 3, 1, 2] or nchildren[t] != 1 or t in out_set:
+            continue
+        r = t.parents[0]
+        if r.is_input() or not isinstance(r.op, core.Reshape) or nchildren[r] != 1 or r in out_set:
+            continue
+        m = r.parents[0]
+        if m.is_input() or not isinstance(m.op, core.Mul22) or m.op.tA or not m.op.tB or nchildren[m] != 1 or m in out_set:
+            continue
+        if m.dtype != "f4" or bias.dtype != "f4" or bias.ndim != 4:
+            continue
+        shp = node2shape[node][0]
+        static = _static_shape(shp)
+        if static is None or static[1] > 384:   # the kernel stages 128 pixels x C channels in shared memory
+            continue
+        new = core.Result(im2col_ops.ConvBiasRelu(), [m.parents[0], m.parents[1], bias] + list(shp))
+        node2shape[new] = node2shape[node]
+        new.props.update(node.props)
+        replace[node] = new
+    if not replace:
+        return list(outputs), list(updatetargs)
+    return _rewire(outputs, updatetargs, replace)
+
+
 def prebuild_fused_kernels(builders):
     """Generate and compile the fused-chain kernels of the given configurations into the library cache
     (no GPU needed: nvcc cross-compiles), so that a later run finds them instead of compiling."""
@@ -712,6 +758,8 @@ def run_compilation_pipeline(inputs, outputs, updates, givens):
         outputs_simple, updatetargs_simple = fuse_conv_dgrad(outputs_simple, updatetargs_simple, node2shape)
     if config["fuse_elementwise"]:
         outputs_simple, updatetargs_simple = fuse_elementwise(outputs_simple, updatetargs_simple, node2shape)
+        if config["fuse_conv_output"]:
+            outputs_simple, updatetargs_simple = fuse_conv_output(outputs_simple, updatetargs_simple, node2shape)
     all_out = outputs_simple + updatetargs_simple
 
     nodelist = core.topsorted(all_out)

@@ -5,16 +5,17 @@
 // impl: 0 automatic, 1 FMA (tiled), 2 tensor cores (either feed), 3 register-fed only, 4 TMA-fed only,
 // 5 the small-product kernel only.
 #include "runtime.h"
+#include "tc_util.h"
 
 namespace cgtb {
 int sgemm_simt(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B,
                long ldb, long strideB, float* C, long ldc, long strideC);
 // returns 0 done, 1 error, -1 shape not supported by the tensor-core kernel
 int sgemm_tc(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B,
-             long ldb, long strideB, float* C, long ldc, long strideC);
+             long ldb, long strideB, float* C, long ldc, long strideC, const ConvEpilogue* ep = nullptr);
 
 int sgemm_tma(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B,
-              long ldb, long strideB, float* C, long ldc, long strideC);
+              long ldb, long strideB, float* C, long ldc, long strideC, const ConvEpilogue* ep = nullptr);
 
 int sgemm_small(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B,
                 long ldb, long strideB, float* C, long ldc, long strideC);
@@ -47,4 +48,114 @@ CGTB_API int cgtb_sgemm(int tA, int tB, long M, long N, long K, const float* A, 
 CGTB_API int cgtb_sgemm_batched(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA,
                                 const float* B, long ldb, long strideB, float* C, long ldc, long strideC, int impl) {
   return cgtb::sgemm_dispatch(tA, tB, P, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC, impl);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Output stage of a convolution layer as the reference's graph spells it (cgt/nn.py:87-100, 44-45,
+// 228-233): Mul22(col, W^T) gives [B*H*W, C] (channels last); Transpose{0,3,1,2} makes it NCHW; the
+// bias [1,C,1,1] is Repeat-ed and added; relu is t * (t >= 0) with an int8 mask that the backward
+// pass re-uses. Here the GEMM result is turned into both outputs in one pass: t = g + bias[c],
+// mask = (t >= 0), y = t * mask, written as NCHW planes. The arithmetic is the separate kernels'
+// (float add, compare with 0.f, float multiply), so the values are bit-identical to the Op-by-Op graph.
+// A block stages 128 pixels x C channels through shared memory: coalesced reads along channels,
+// coalesced writes along pixels.
+// ------------------------------------------------------------------------------------------------
+namespace {
+constexpr int kTilePix = 128;
+__global__ void __launch_bounds__(256) bias_relu_nchw_kernel(const float* __restrict__ g, const float* __restrict__ bias, long M, int C,
+                                                           long HW, float* __restrict__ y, int8_t* __restrict__ mask, int tilepix) {
+  extern __shared__ float tile[];  // [tilepix][C + 1], tilepix = 32 or 128
+  const int stride = C + 1;
+  const long m0 = (long)blockIdx.x * tilepix;
+  const int npix = (int)((M - m0) < tilepix ? (M - m0) : tilepix);
+  const int n = npix * C;
+  const float* src = g + m0 * C;
+  // rows of C contiguous floats: consecutive threads read consecutive addresses; four loads in flight
+  if ((int)blockDim.x % C == 0) {
+    // a thread keeps its channel and walks down the rows: no index division per element
+    const int c = threadIdx.x % C, r0 = threadIdx.x / C, dr = blockDim.x / C;
+    for (int r = r0; r < npix; r += 16 * dr) {  // sixteen loads in flight: one round trip for a 128 x 32 tile
+      float v[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) v[k] = (r + k * dr < npix) ? src[(r + k * dr) * C + c] : 0.f;
+#pragma unroll
+      for (int k = 0; k < 16; ++k)
+        if (r + k * dr < npix) tile[(r + k * dr) * stride + c] = v[k];
+    }
+  } else {
+    for (int e0 = threadIdx.x; e0 < n; e0 += 4 * blockDim.x) {
+      float v[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int e = e0 + k * blockDim.x;
+        v[k] = e < n ? src[e] : 0.f;
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int e = e0 + k * blockDim.x;
+        if (e < n) {
+          const int r = e / C, c = e - r * C;
+          tile[r * stride + c] = v[k];
+        }
+      }
+    }
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  size_t obase[kTilePix / 32];
+  bool ok[kTilePix / 32];
+#pragma unroll
+  for (int q = 0; q < kTilePix / 32; ++q) {
+    const int r = lane + 32 * q;
+    ok[q] = r < npix;  // false for every q beyond a 32-pixel tile
+    const long m = m0 + (ok[q] ? r : 0);
+    const long b = m / HW, pix = m - b * HW;
+    obase[q] = (size_t)b * C * HW + pix;
+  }
+  for (int c = warp; c < C; c += nwarps) {
+    const float bc = bias[c];
+    const size_t coff = (size_t)c * HW;
+    const float* trow = tile + lane * stride + c;
+#pragma unroll
+    for (int q = 0; q < kTilePix / 32; ++q) {
+      if (ok[q]) {
+        const float t = trow[32 * q * stride] + bc;
+        const int8_t mk = (int8_t)(t >= 0.f);
+        const size_t o = obase[q] + coff;
+        mask[o] = mk;
+        y[o] = t * (float)mk;
+      }
+    }
+  }
+}
+}  // namespace
+
+CGTB_API int cgtb_conv_bias_relu(const float* col, long M, long K, const float* w, int C, const float* bias, long HW, float* y_nchw,
+                                 int8_t* mask_nchw) {
+  if (!cgtb::require_runtime("cgtb_conv_bias_relu")) return 1;
+  if (M <= 0 || C <= 0) return 0;
+  if (HW <= 0 || M % HW != 0) return cgtb::fail("cgtb_conv_bias_relu: %ld rows are not whole images of %ld pixels", M, HW);
+  if (C > 384) return cgtb::fail("cgtb_conv_bias_relu: at most 384 channels");
+  {
+    // the tensor-core kernels apply the output stage to the accumulator tile when the product is not split
+    // along K: no intermediate matrix at all
+    cgtb::ConvEpilogue ep = {bias, y_nchw, mask_nchw, HW};
+    int rc = cgtb::sgemm_tma(0, 1, 1, M, C, K, col, K, 0, w, K, 0, nullptr, C, 0, &ep);
+    if (rc < 0) rc = cgtb::sgemm_tc(0, 1, 1, M, C, K, col, K, 0, w, K, 0, nullptr, C, 0, &ep);
+    if (rc >= 0) return rc;
+  }
+  float* g = (float*)cgtb::scratch_outer((size_t)M * C * sizeof(float));  // the product may use scratch() for split-K
+  if (!g) return 1;
+  int rc = cgtb::sgemm_dispatch(0, 1, 1, M, C, K, col, K, 0, w, K, 0, g, C, 0, 0);
+  if (rc) return rc;
+  // small products: 32-pixel tiles so that the grid still covers the machine
+  const int tilepix = (M >= (long)kTilePix * 2 * cgtb::rt().sm_count) ? kTilePix : 32;
+  const size_t smem = (size_t)tilepix * (C + 1) * sizeof(float);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(bias_relu_nchw_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return cgtb::fail("cgtb_conv_bias_relu: %s", cudaGetErrorString(e));
+  }
+  CGTB_LAUNCH(bias_relu_nchw_kernel, (unsigned)cgtb_ceil_div(M, tilepix), 256, smem, g, bias, M, C, HW, y_nchw, mask_nchw, tilepix);
+  CGTB_CHECK_LAUNCH("conv_bias_relu");
+  return 0;
 }

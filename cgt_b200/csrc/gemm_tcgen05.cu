@@ -64,6 +64,7 @@ struct Params {
   int stages;
   int tmem_cols;
   int* err;          // host-mapped error flag
+  ConvEpilogue ep;   // ep.y != nullptr: bias + relu + NCHW output stage instead of storing C
 };
 
 // Operand tiles travel global -> registers -> shared memory in two steps so that the loads of the
@@ -335,7 +336,33 @@ __global__ void __launch_bounds__(kThreads, (YNV <= 16 ? 2 : 1)) sgemm_tc_kernel
       asm volatile("bar.sync 1, %0;" ::"n"(kLoaderThreads) : "memory");
       float* cbase = (p.nsplit > 1) ? p.C + ((long)batch * p.nsplit + split) * p.M * p.N : p.C + batch * p.c_batch_stride;
       const long ld = (p.nsplit > 1) ? p.N : p.ldc;
-      if (!p.swapped) {  // tile row = product row: lanes along the product's columns
+      if (p.ep.y) {      // convolution output stage: lanes along pixels (tile rows), NCHW planes
+        size_t obase[kXRows / 32];
+        bool rok[kXRows / 32];
+#pragma unroll
+        for (int q = 0; q < kXRows / 32; ++q) {
+          const long i_g = x0 + lane + 32 * q;
+          rok[q] = i_g < p.X.rows;
+          const long mm = rok[q] ? i_g : 0;
+          const long b = mm / p.ep.HW, pix = mm - b * p.ep.HW;
+          obase[q] = (size_t)b * p.Y.rows * p.ep.HW + pix;
+        }
+        for (int col = warp; col < UN; col += kLoaderWarps) {
+          const long j_g = y0 + col;
+          if (j_g >= p.Y.rows) break;
+          const float bc = p.ep.bias[j_g];
+          const size_t coff = (size_t)j_g * p.ep.HW;
+#pragma unroll
+          for (int q = 0; q < kXRows / 32; ++q) {
+            if (rok[q]) {
+              const float t = stg[(lane + 32 * q) * stride + col] + bc;
+              const int8_t mk = (int8_t)(t >= 0.f);
+              p.ep.mask[obase[q] + coff] = mk;
+              p.ep.y[obase[q] + coff] = t * (float)mk;
+            }
+          }
+        }
+      } else if (!p.swapped) {  // tile row = product row: lanes along the product's columns
         for (int row = warp; row < kXRows; row += kLoaderWarps) {
           const long i_g = x0 + row;
           if (i_g >= p.X.rows) break;
@@ -476,7 +503,7 @@ int sgemm_tc_check() {
 }
 
 int sgemm_tc(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B, long ldb,
-             long strideB, float* C, long ldc, long strideC) {
+             long strideB, float* C, long ldc, long strideC, const ConvEpilogue* ep) {
   if (P <= 0 || M <= 0 || N <= 0) return 0;
   if (K <= 0) return -1;                      // all-zero product: the FMA kernel handles it
   if (M * N < 1024 && K < 256) return -1;     // tiny: not worth a tensor-core launch
@@ -490,6 +517,11 @@ int sgemm_tc(int tA, int tB, long P, long M, long N, long K, const float* A, lon
   Operand opA = {A, lda, tA ? 0 : 1, mode_of(A, lda, strideA, tA ? 0 : 1), M, strideA};   // rows of op(A) are m
   Operand opB = {B, ldb, tB ? 1 : 0, mode_of(B, ldb, strideB, tB ? 1 : 0), N, strideB};   // rows of op(B)^T are n
   p.swapped = (N > M) ? 1 : 0;
+  p.ep = ConvEpilogue{nullptr, nullptr, nullptr, 1};
+  if (ep) {
+    if (p.swapped || P != 1) return -1;
+    p.ep = *ep;
+  }
   p.X = p.swapped ? opB : opA;
   p.Y = p.swapped ? opA : opB;
   long ydim = p.Y.rows;
@@ -514,6 +546,7 @@ int sgemm_tc(int tA, int tB, long P, long M, long N, long K, const float* A, lon
   long kchunk = cgtb_ceil_div(nkb_total, nsplit) * kBK;
   nsplit = (int)cgtb_ceil_div(K, kchunk);
   if ((long)P * nsplit > 65535 || ytiles > 65535) return -1;
+  if (ep && nsplit > 1) return -1;  // the output stage needs whole sums
   p.nsplit = nsplit;
   p.kchunk = kchunk;
   p.K = K;

@@ -78,6 +78,7 @@ struct TmaParams {
   int cnbands;          // tiles per image when an image spans several tiles
   int cB;               // images
   int cx_tx;            // bytes one X load delivers (the box may be smaller than 128 rows)
+  ConvEpilogue ep;      // ep.y != nullptr: bias + relu + NCHW output stage instead of storing C
 };
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
@@ -281,6 +282,20 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
             for (int j = 0; j < 8; ++j)
               if (j0 + j < p.cC) dst[(size_t)j * p.cHW] = v[j];
           }
+        } else if (p.ep.y) {
+          if (i_g < p.xrows) {
+            const long b = i_g / p.ep.HW, pix = i_g - b * p.ep.HW;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (j0 + j < p.yrows) {
+                const float t = v[j] + p.ep.bias[j0 + j];
+                const int8_t mk = (int8_t)(t >= 0.f);
+                const size_t o = ((size_t)b * p.yrows + (j0 + j)) * p.ep.HW + pix;
+                p.ep.mask[o] = mk;
+                p.ep.y[o] = t * (float)mk;
+              }
+            }
+          }
         } else if (i_g < p.xrows) {
           if (!p.swapped) {  // tile row = product row: 32 contiguous bytes per thread
             float* dst = cbase + i_g * ld + j0;
@@ -445,7 +460,7 @@ namespace cgtb {
 
 // returns 0 done, 1 error, -1 not eligible (the caller falls back to the register-fed kernel)
 int sgemm_tma(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B, long ldb,
-              long strideB, float* C, long ldc, long strideC) {
+              long strideB, float* C, long ldc, long strideC, const ConvEpilogue* ep) {
   if (P <= 0 || M <= 0 || N <= 0) return 0;
   if (K < kBK) return -1;
   if (M * N < 1024 && K < 256) return -1;
@@ -455,7 +470,10 @@ int sgemm_tma(int tA, int tB, long P, long M, long N, long K, const float* A, lo
   if (!aligned_for_tma(sA, P) || !aligned_for_tma(sB, P)) return -1;
   TmaParams p;
   p.conv = 0;
+  p.ep = ConvEpilogue{nullptr, nullptr, nullptr, 1};
+  if (ep) p.ep = *ep;
   p.swapped = (N > M) ? 1 : 0;
+  if (ep && (p.swapped || P != 1)) return -1;
   const Side& X = p.swapped ? sB : sA;
   const Side& Y = p.swapped ? sA : sB;
   long ydim = Y.rows;
@@ -498,6 +516,7 @@ int sgemm_tma(int tA, int tB, long P, long M, long N, long K, const float* A, lo
   long kchunk = cgtb_ceil_div(nkb_total, nsplit) * kBK;
   nsplit = (int)cgtb_ceil_div(K, kchunk);
   if ((long)P * nsplit > 65535 || ytiles > 65535) return -1;
+  if (ep && nsplit > 1) return -1;  // the output stage needs whole sums
   const long nkb = kchunk / kBK;  // a short K loop needs no deeper rings: smaller CTAs, more of them per SM
   if (raw_stages > nkb) raw_stages = (int)nkb;
   if (conv_stages > nkb) conv_stages = (int)nkb;
@@ -561,6 +580,7 @@ int conv_dgrad_tma(const float* dy, long B, int Ho, int Wo, int Cin, const float
   const int HW = H * W;
   TmaParams p;
   p.conv = 1;
+  p.ep = ConvEpilogue{nullptr, nullptr, nullptr, 1};
   p.swapped = 0;
   p.cW = W;
   p.cHW = HW;

@@ -245,6 +245,22 @@ OP_BYREF(cgtb_op_col2im) {
   cgtb_col2im(col->dtype(), col->data(), B, (int)C, (int)H, (int)W, cl->kernel_h, cl->kernel_w, cl->pad_h, cl->pad_w,
               cl->stride_h, cl->stride_w, im->data());
 }
+// ConvBiasRelu: (col [M,K], w [C,K], bias [1,C,1,1], B, C, H, W) -> tuple(mask i1 NCHW, y f4 NCHW)
+OP_BYREF(cgtb_op_conv_bias_relu) {
+  cgtArray *col = ARR(reads[0]), *w = ARR(reads[1]), *bias = ARR(reads[2]);
+  cgtTuple* out = (cgtTuple*)write0;
+  cgtArray *mask = ARR(out->getitem(0)), *y = ARR(out->getitem(1));
+  if (!all_gpu({col, w, bias, mask, y})) { fail("ConvBiasRelu: operands must be on the GPU"); return; }
+  const long* d = y->shape();
+  const long M = col->shape()[0], K = col->shape()[1], C = d[1], HW = d[2] * d[3];
+  if (col->ndim() != 2 || w->ndim() != 2 || y->ndim() != 4 || col->dtype() != cgt_f4 || w->shape()[0] != C || w->shape()[1] != K ||
+      bias->size() != C || M != d[0] * HW || mask->size() != y->size()) {
+    fail("ConvBiasRelu: operand shapes do not fit together");
+    return;
+  }
+  cgtb_conv_bias_relu((const float*)col->data(), M, K, (const float*)w->data(), (int)C, (const float*)bias->data(), HW,
+                      (float*)y->data(), (int8_t*)mask->data());
+}
 // ConvDgrad: (dy NHWC, filters rearranged to [C, kh, kw, Cin], B, C, H, W) -> dx NCHW
 OP_BYREF(cgtb_op_conv_dgrad) {
   ConvClosure* cl = (ConvClosure*)cl0;

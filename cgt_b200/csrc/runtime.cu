@@ -162,6 +162,7 @@ static ScratchOwner g_global_scratch;
 void set_scratch_owner(ScratchOwner* o) { t_scratch_owner = o; }
 void free_scratch_owner(ScratchOwner* o) {
   if (o && o->ptr) { g_dev_pool.put(o->ptr); o->ptr = nullptr; o->cap = 0; }
+  if (o && o->outer_ptr) { g_dev_pool.put(o->outer_ptr); o->outer_ptr = nullptr; o->outer_cap = 0; }
 }
 void* scratch(size_t nbytes) {
   ScratchOwner* o = t_scratch_owner ? t_scratch_owner : &g_global_scratch;
@@ -176,6 +177,19 @@ void* scratch(size_t nbytes) {
   o->ptr = g_dev_pool.get(nbytes);
   o->cap = o->ptr ? size_class(nbytes) : 0;
   return o->ptr;
+}
+
+void* scratch_outer(size_t nbytes) {
+  ScratchOwner* o = t_scratch_owner ? t_scratch_owner : &g_global_scratch;
+  if (o->outer_cap >= nbytes && o->outer_ptr) return o->outer_ptr;
+  if (o->outer_ptr) {
+    g_dev_pool.put(o->outer_ptr);
+    o->outer_ptr = nullptr;
+    o->outer_cap = 0;
+  }
+  o->outer_ptr = g_dev_pool.get(nbytes);
+  o->outer_cap = o->outer_ptr ? size_class(nbytes) : 0;
+  return o->outer_ptr;
 }
 
 }  // namespace cgtb

@@ -28,10 +28,14 @@ extern std::atomic<long> g_kernel_launches;
 // interpreter the block belongs to the running instruction and keeps its address across runs (so a
 // captured CUDA graph stays valid); outside it comes from one process-wide block on the runtime stream.
 void* scratch(size_t nbytes);
+// a second, independent block of the same owner, for a caller that itself invokes code using scratch()
+void* scratch_outer(size_t nbytes);
 
 struct ScratchOwner {  // one per interpreter instruction
   void* ptr = nullptr;
   size_t cap = 0;
+  void* outer_ptr = nullptr;
+  size_t outer_cap = 0;
 };
 void set_scratch_owner(ScratchOwner* o);  // nullptr -> process-wide block
 void free_scratch_owner(ScratchOwner* o);

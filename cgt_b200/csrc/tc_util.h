@@ -189,6 +189,16 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
 
 }  // namespace tc
 
+// Optional output stage of a product whose rows are channels-last pixels (a convolution layer): instead of
+// C[m, n] the kernel writes t = C[m, n] + bias[n], mask = (t >= 0), y = t * mask as NCHW planes
+// y[((m / HW) * N + n) * HW + m % HW]. Only for products that are neither swapped nor split along K.
+struct ConvEpilogue {
+  const float* bias;
+  float* y;
+  int8_t* mask;
+  long HW;
+};
+
 // host-mapped flag that the tensor-core kernels raise on a wait time-out (device address); nullptr on failure
 int* tc_error_flag();
 // ordered fold of a split-K slab [P][nsplit][M*N] into C

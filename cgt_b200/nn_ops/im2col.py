@@ -114,3 +114,32 @@ class ConvDgrad(core.Op):
 
     def __repr__(self):
         return "ConvDgrad{%s}" % (tuple(self.info),)
+
+
+class ConvBiasRelu(core.Op):
+    """(col [M,K], W [C,K], bias [1,C,1,1], B, C, H, W) -> tuple(mask i1, relu f4), both NCHW [B,C,H,W]:
+    the output stage of a convolution layer, Mul22 -> Transpose{0,3,1,2} -> + bias -> relu, in one call.
+
+    Not part of the reference's Op set. The compiler substitutes it (compilation.fuse_conv_output) for the
+    sequence that nn.conv2d / SpatialConvolution / rectify spell out (cgt/nn.py:87-100, 228-233, 44-45); the
+    values are bit-identical to that sequence."""
+    available_impls = ("native_gpu",)
+
+    def get_diff(self, n):
+        return [False] * n
+
+    def shp_apply(self, inputs):
+        shp = list(inputs[3:])
+        return (shp, list(shp))
+
+    def typ_apply(self, inputs):
+        return core.TupleType(core.TensorType("i1", 4), core.TensorType("f4", 4))
+
+    def host_inputs(self, n):
+        return tuple(range(3, n))
+
+    def get_native_compile_info(self, input_types, devtype):
+        return core.NativeCompileInfo(None, prebuilt="cgtb_op_conv_bias_relu")
+
+    def __repr__(self):
+        return "ConvBiasRelu"

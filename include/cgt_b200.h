@@ -155,6 +155,13 @@ int cgtb_lrn_backward(int dtype, const void* x, const void* top, const void* sca
 int cgtb_conv_dgrad(const float* dy_nhwc, long B, int Ho, int Wo, int Cin, const float* w_rearranged, int C, int H, int W,
                     int kh, int kw, int ph, int pw, float* dx_nchw);
 
+/* Output stage of a convolution layer in one call: Mul22(col, w^T) -> NCHW -> + bias -> relu with its mask.
+ * Replaces the Op sequence Mul22, Reshape, Transpose{0,3,1,2}, Repeat, ElwiseBinary +, >=, * of cgt/nn.py:87-100,
+ * 44-45, 228-233; values are bit-identical to that sequence run through cgtb_sgemm and the elementwise kernels.
+ * col [M, K] (M = B*HW rows, channels-last pixels), w [C, K], bias [C]; y_nchw, mask_nchw [B, C, HW]. float32. */
+int cgtb_conv_bias_relu(const float* col, long M, long K, const float* w, int C, const float* bias, long HW, float* y_nchw,
+                        int8_t* mask_nchw);
+
 /* ElwiseUnary / ElwiseBinary (cgt/core.py:1160-1378). scalar_x / scalar_y: operand is a 0-d array
  * in device memory, read at index 0. */
 int cgtb_unary(int op, int dt_in, int dt_out, long n, const void* in, void* out);

@@ -148,3 +148,22 @@ def test_conv_dgrad_substitution(rt):
     np.testing.assert_allclose(res[True][2], res[False][2], rtol=1e-4)
     for (a, b) in zip(res[True][3], res[False][3]):
         np.testing.assert_allclose(a, b, rtol=1e-3, atol=1e-5)
+
+
+def test_conv_output_substitution_changes_no_bit(rt):
+    """ConvBiasRelu (GEMM + NCHW + bias + relu in one call) gives the bits of the Op sequence it replaces."""
+    res = {}
+    for fuse in (False, True):
+        with cgt.scoped_update_config(fuse_conv_output=fuse, use_cuda_graphs=False):
+            cfg = configs.BUILDERS["cifar"](**SMALL["cifar"])
+            f = cfg.compile()
+            names = [repr(instr) for instr in f.eg.instrs]
+            batches = [cfg.batch(seed) for seed in range(2)]
+            losses = [np.asarray(f(*batches[i % 2])[0]).copy() for i in range(4)]
+            params = [np.asarray(p.op.get_value()).copy() for p in cfg.params]
+            res[fuse] = (sum("ConvBiasRelu" in n for n in names), losses, params)
+    assert res[False][0] == 0 and res[True][0] == 3
+    for (a, b) in zip(res[False][1], res[True][1]):
+        assert np.array_equal(a, b)
+    for (a, b) in zip(res[False][2], res[True][2]):
+        assert np.array_equal(a, b)

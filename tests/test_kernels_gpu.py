@@ -454,6 +454,36 @@ def test_conv_dgrad_matches_gemm_then_col2im(rt, B, C, H, W, Cin, k, pad):
     np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-5 * scale)
 
 
+@pytest.mark.parametrize("B,HW,C,K", [(4, 1024, 32, 75), (8, 225, 32, 800), (16, 36, 64, 800), (3, 10, 48, 40), (2, 7, 16, 5)])
+def test_conv_bias_relu_matches_op_sequence(rt, B, HW, C, K):
+    """cgtb_conv_bias_relu against the sequence it replaces, issued through the separate entry points:
+    sgemm -> NHWC->NCHW transpose -> repeat bias -> add -> >= 0 -> multiply. Same bits."""
+    rs = np.random.RandomState(51)
+    M = B * HW
+    col, w, bias = rs.randn(M, K).astype("f4"), (rs.randn(C, K) * 0.1).astype("f4"), rs.randn(C).astype("f4")
+    dcol, dw, db = Dev(col), Dev(w), Dev(bias)
+    y, mask = Dev(shape=(B, C, HW), dtype="f4"), Dev(shape=(B, C, HW), dtype="i1")
+    L = runtime.lib()
+    L.cgtb_conv_bias_relu.restype = ctypes.c_int
+    L.cgtb_conv_bias_relu.argtypes = [ctypes.c_void_p, ctypes.c_long, ctypes.c_long, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p,
+                                      ctypes.c_long, ctypes.c_void_p, ctypes.c_void_p]
+    call("cgtb_conv_bias_relu", dcol.ptr, M, K, dw.ptr, C, db.ptr, HW, y.ptr, mask.ptr)
+    g, gt, rep, t, m2, y2 = (Dev(shape=sh, dtype=dt) for (sh, dt) in [((M, C), "f4"), ((B, C, HW), "f4"), ((B, C, HW), "f4"),
+                                                                       ((B, C, HW), "f4"), ((B, C, HW), "i1"), ((B, C, HW), "f4")])
+    n = B * C * HW
+    call("cgtb_sgemm", 0, 1, M, C, K, dcol.ptr, K, dw.ptr, K, g.ptr, C, 0)
+    call("cgtb_transpose", code("f4"), 3, longs((B, HW, C)), ints((0, 2, 1)), g.ptr, gt.ptr)
+    call("cgtb_repeat", code("f4"), 3, longs((B, C, HW)), ints([1, 0, 1]), db.ptr, rep.ptr)
+    call("cgtb_binary", 1, code("f4"), code("f4"), code("f4"), n, gt.ptr, rep.ptr, t.ptr, 0, 0)
+    zero = Dev(np.array(0, "i8"))
+    call("cgtb_binary", 7, code("f4"), code("i8"), code("i1"), n, t.ptr, zero.ptr, m2.ptr, 0, 1)
+    call("cgtb_binary", 0, code("f4"), code("i1"), code("f4"), n, t.ptr, m2.ptr, y2.ptr, 0, 0)
+    assert np.array_equal(mask.get(), m2.get())
+    assert np.array_equal(y.get(), y2.get())
+    want = np.maximum((col.astype("f8") @ w.astype("f8").T + bias).reshape(B, HW, C).transpose(0, 2, 1), 0)
+    np.testing.assert_allclose(y.get(), want, rtol=1e-4, atol=1e-4)
+
+
 class _FusedProgram(ctypes.Structure):
     _fields_ = [("n_in", ctypes.c_int), ("n_ops", ctypes.c_int), ("n_out", ctypes.c_int), ("in_kind", ctypes.c_int * 8),
                 ("op_arity", ctypes.c_int * 16), ("op_code", ctypes.c_int * 16), ("op_a", ctypes.c_int * 16),
