@@ -444,6 +444,52 @@ def fuse_conv_output(outputs, updatetargs, node2shape):
     return _rewire(outputs, updatetargs, replace)
 
 
+def fuse_conv_grad_input(outputs, updatetargs, node2shape):
+    """X = mask * g (relu pullback, NCHW) consumed only by Transpose{0,2,3,1}(X) and Sum{0,2,3}(X) -> one
+    ReluGradNHWC(mask, g) node whose two outputs replace the transpose and the sum."""
+    from .nn_ops import im2col as im2col_ops
+    all_out = list(outputs) + list(updatetargs)
+    nodes = core.topsorted(all_out)
+    children = defaultdict(list)
+    for node in nodes:
+        for par in node.parents:
+            children[par].append(node)
+    out_set = set(all_out)
+    replace = {}
+    for x in nodes:
+        if x.is_input() or not isinstance(x.op, core.ElwiseBinary) or x.op.opname != "*" or x.ndim != 4 or x.dtype != "f4" or x in out_set:
+            continue
+        (a, b) = x.parents
+        if a.ndim != 4 or b.ndim != 4:
+            continue
+        if a.dtype == "i1" and b.dtype == "f4":
+            (mask, g) = (a, b)
+        elif b.dtype == "i1" and a.dtype == "f4":
+            (mask, g) = (b, a)
+        else:
+            continue
+        cs = children[x]
+        if len(cs) != 2:
+            continue
+        t = [c for c in cs if isinstance(c.op, core.Transpose) and list(c.op.axes) == [0, 2, 3, 1]]
+        sm = [c for c in cs if isinstance(c.op, core.Sum) and tuple(c.op.axes) == (0, 2, 3)]
+        if len(t) != 1 or len(sm) != 1:
+            continue
+        static = _static_shape(node2shape[x]) if x in node2shape else None
+        if static is None or static[1] > 384 or static[0] > 65535:
+            continue
+        new = core.Result(im2col_ops.ReluGradNHWC(), [mask, g])
+        node2shape[new] = (node2shape[t[0]], node2shape[sm[0]])
+        new.props.update(x.props)
+        for (q, old) in enumerate((t[0], sm[0])):
+            ti = core.Result(core.TupleIndex(q), [new])
+            node2shape[ti] = node2shape[old]
+            replace[old] = ti
+    if not replace:
+        return list(outputs), list(updatetargs)
+    return _rewire(outputs, updatetargs, replace)
+
+
 def prebuild_fused_kernels(builders):
     """Generate and compile the fused-chain kernels of the given configurations into the library cache
     (no GPU needed: nvcc cross-compiles), so that a later run finds them instead of compiling."""
@@ -756,6 +802,8 @@ def run_compilation_pipeline(inputs, outputs, updates, givens):
     node2shape = analysis["node2shape"]
     if config["fuse_conv_dgrad"]:
         outputs_simple, updatetargs_simple = fuse_conv_dgrad(outputs_simple, updatetargs_simple, node2shape)
+    if config["fuse_conv_grad_input"]:
+        outputs_simple, updatetargs_simple = fuse_conv_grad_input(outputs_simple, updatetargs_simple, node2shape)
     if config["fuse_elementwise"]:
         outputs_simple, updatetargs_simple = fuse_elementwise(outputs_simple, updatetargs_simple, node2shape)
         if config["fuse_conv_output"]:

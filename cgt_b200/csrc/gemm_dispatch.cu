@@ -159,3 +159,73 @@ CGTB_API int cgtb_conv_bias_relu(const float* col, long M, long K, const float* 
   CGTB_CHECK_LAUNCH("conv_bias_relu");
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Input stage of a convolution layer's backward pass as the reference's graph spells it: the relu
+// pullback g * mask (ElwiseBinary), its Transpose{0,2,3,1} to channels-last for the weight- and
+// data-gradient products, and Sum{0,2,3} of the same tensor for the bias gradient (cgt/nn.py:44-45,
+// 87-100, 228-233 differentiated). One pass: a block takes up to 128 pixels of one image for all
+// channels, multiplies, writes the pixels as channels-last rows (one contiguous run) and leaves one
+// partial channel sum per block; the partial sums are then added in block order by the column-sum
+// kernel, so the bias gradient is reproducible (its summation order differs from Sum's).
+// ------------------------------------------------------------------------------------------------
+namespace {
+__global__ void __launch_bounds__(256) relu_grad_nhwc_kernel(const int8_t* __restrict__ mask, const float* __restrict__ g, int C,
+                                                           long HW, float* __restrict__ gt, float* __restrict__ partial) {
+  extern __shared__ float tile[];  // [128][C + 1]
+  const int stride = C + 1;
+  const long b = blockIdx.y;
+  const long p0 = (long)blockIdx.x * 128;
+  const int npix = (int)((HW - p0) < 128 ? (HW - p0) : 128);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const size_t plane0 = (size_t)b * C * HW + p0;
+  for (int c = warp; c < C; c += nwarps) {
+    const size_t base = plane0 + (size_t)c * HW;
+    float v[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int px = lane + 32 * q;
+      v[q] = px < npix ? (float)mask[base + px] * g[base + px] : 0.f;
+    }
+    float sum = (v[0] + v[1]) + (v[2] + v[3]);
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      if (lane + 32 * q < npix) tile[(lane + 32 * q) * stride + c] = v[q];
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+    if (lane == 0) partial[((size_t)b * gridDim.x + blockIdx.x) * C + c] = sum;
+  }
+  __syncthreads();
+  float* dst = gt + ((size_t)b * HW + p0) * C;  // npix rows of C floats: one contiguous run
+  const int n = npix * C;
+  if ((int)blockDim.x % C == 0) {
+    const int c = threadIdx.x % C, r0 = threadIdx.x / C, dr = blockDim.x / C;
+    for (int r = r0; r < npix; r += dr) dst[r * C + c] = tile[r * stride + c];
+  } else {
+    for (int e = threadIdx.x; e < n; e += blockDim.x) {
+      const int r = e / C, c = e - r * C;
+      dst[e] = tile[r * stride + c];
+    }
+  }
+}
+}  // namespace
+
+CGTB_API int cgtb_relu_grad_nhwc(const int8_t* mask_nchw, const float* g_nchw, long B, int C, long HW, float* gt_nhwc, float* bias_grad) {
+  if (!cgtb::require_runtime("cgtb_relu_grad_nhwc")) return 1;
+  if (B <= 0 || C <= 0 || HW <= 0) return 0;
+  if (C > 384 || B > 65535) return cgtb::fail("cgtb_relu_grad_nhwc: at most 384 channels and 65535 images");
+  const long ntiles = cgtb_ceil_div(HW, 128);
+  float* partial = (float*)cgtb::scratch_outer((size_t)B * ntiles * C * sizeof(float));
+  if (!partial) return 1;
+  const size_t smem = (size_t)128 * (C + 1) * sizeof(float);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(relu_grad_nhwc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return cgtb::fail("cgtb_relu_grad_nhwc: %s", cudaGetErrorString(e));
+  }
+  dim3 grid((unsigned)ntiles, (unsigned)B);
+  CGTB_LAUNCH(relu_grad_nhwc_kernel, grid, 256, smem, mask_nchw, g_nchw, C, HW, gt_nhwc, partial);
+  CGTB_CHECK_LAUNCH("relu_grad_nhwc");
+  const long shape[2] = {B * ntiles, C};
+  const int reduced[2] = {1, 0};
+  return cgtb_reduce(CGTB_R_SUM, cgtb_f4, 2, shape, reduced, partial, bias_grad);
+}

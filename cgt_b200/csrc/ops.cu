@@ -261,6 +261,20 @@ OP_BYREF(cgtb_op_conv_bias_relu) {
   cgtb_conv_bias_relu((const float*)col->data(), M, K, (const float*)w->data(), (int)C, (const float*)bias->data(), HW,
                       (float*)y->data(), (int8_t*)mask->data());
 }
+// ReluGradNHWC: (mask i1 NCHW, g f4 NCHW) -> tuple(mask*g transposed to NHWC, Sum{0,2,3}(mask*g) as [1,C,1,1])
+OP_BYREF(cgtb_op_relu_grad_nhwc) {
+  cgtArray *mask = ARR(reads[0]), *g = ARR(reads[1]);
+  cgtTuple* out = (cgtTuple*)write0;
+  cgtArray *gt = ARR(out->getitem(0)), *bsum = ARR(out->getitem(1));
+  if (!all_gpu({mask, g, gt, bsum})) { fail("ReluGradNHWC: operands must be on the GPU"); return; }
+  const long* d = g->shape();
+  if (g->ndim() != 4 || g->dtype() != cgt_f4 || mask->size() != g->size() || gt->size() != g->size() || bsum->size() != d[1]) {
+    fail("ReluGradNHWC: operand shapes do not fit together");
+    return;
+  }
+  cgtb_relu_grad_nhwc((const int8_t*)mask->data(), (const float*)g->data(), d[0], (int)d[1], d[2] * d[3], (float*)gt->data(),
+                      (float*)bsum->data());
+}
 // ConvDgrad: (dy NHWC, filters rearranged to [C, kh, kw, Cin], B, C, H, W) -> dx NCHW
 OP_BYREF(cgtb_op_conv_dgrad) {
   ConvClosure* cl = (ConvClosure*)cl0;

@@ -143,3 +143,31 @@ class ConvBiasRelu(core.Op):
 
     def __repr__(self):
         return "ConvBiasRelu"
+
+
+class ReluGradNHWC(core.Op):
+    """(mask i1 NCHW, g f4 NCHW) -> tuple(mask*g as NHWC [B,H,W,C], Sum{0,2,3}(mask*g) as [1,C,1,1]): the input
+    stage of a convolution layer's backward pass in one call.
+
+    Not part of the reference's Op set. The compiler substitutes it (compilation.fuse_conv_grad_input) for the relu
+    pullback (ElwiseBinary *), its Transpose{0,2,3,1} and the bias gradient's Sum{0,2,3} that differentiating
+    nn.rectify / conv2d / SpatialConvolution yields (cgt/nn.py:44-45, 87-100, 228-233). The transposed product has the
+    bits of the Op sequence; the bias gradient is summed in a different fixed order."""
+    available_impls = ("native_gpu",)
+
+    def get_diff(self, n):
+        return [False] * n
+
+    def shp_apply(self, inputs):
+        (b, c, h, w) = core.cgt.shape(inputs[1])
+        one = core.cgt.constant(1)
+        return ([b, h, w, c], [one, c, one, one])
+
+    def typ_apply(self, inputs):
+        return core.TupleType(core.TensorType("f4", 4), core.TensorType("f4", 4))
+
+    def get_native_compile_info(self, input_types, devtype):
+        return core.NativeCompileInfo(None, prebuilt="cgtb_op_relu_grad_nhwc")
+
+    def __repr__(self):
+        return "ReluGradNHWC"

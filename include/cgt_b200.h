@@ -162,6 +162,12 @@ int cgtb_conv_dgrad(const float* dy_nhwc, long B, int Ho, int Wo, int Cin, const
 int cgtb_conv_bias_relu(const float* col, long M, long K, const float* w, int C, const float* bias, long HW, float* y_nchw,
                         int8_t* mask_nchw);
 
+/* Input stage of a convolution layer's backward pass in one call: gt = transpose(mask * g) to channels-last and
+ * bias_grad[c] = sum over images and pixels of mask * g. Replaces ElwiseBinary *, Transpose{0,2,3,1} and Sum{0,2,3}
+ * of the differentiated cgt/nn.py:44-45, 87-100, 228-233. mask_nchw (int8), g_nchw [B, C, HW]; gt_nhwc [B, HW, C];
+ * bias_grad [C]. gt has the bits of the Op sequence; bias_grad is summed in a different (fixed) order. */
+int cgtb_relu_grad_nhwc(const int8_t* mask_nchw, const float* g_nchw, long B, int C, long HW, float* gt_nhwc, float* bias_grad);
+
 /* ElwiseUnary / ElwiseBinary (cgt/core.py:1160-1378). scalar_x / scalar_y: operand is a 0-d array
  * in device memory, read at index 0. */
 int cgtb_unary(int op, int dt_in, int dt_out, long n, const void* in, void* out);

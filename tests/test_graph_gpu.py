@@ -167,3 +167,22 @@ def test_conv_output_substitution_changes_no_bit(rt):
         assert np.array_equal(a, b)
     for (a, b) in zip(res[False][2], res[True][2]):
         assert np.array_equal(a, b)
+
+
+def test_conv_grad_input_substitution(rt):
+    """ReluGradNHWC replaces multiply + Transpose{0,2,3,1} + Sum{0,2,3}; only the bias gradients' summation order
+    changes, so losses and parameters agree to float32 tolerance."""
+    res = {}
+    for fuse in (False, True):
+        with cgt.scoped_update_config(fuse_conv_grad_input=fuse, use_cuda_graphs=False):
+            cfg = configs.BUILDERS["cifar"](**SMALL["cifar"])
+            f = cfg.compile()
+            names = [repr(instr) for instr in f.eg.instrs]
+            batches = [cfg.batch(seed) for seed in range(2)]
+            losses = [float(f(*batches[i % 2])[0]) for i in range(6)]
+            params = [np.asarray(p.op.get_value()).copy() for p in cfg.params]
+            res[fuse] = (sum("ReluGradNHWC" in n for n in names), losses, params)
+    assert res[False][0] == 0 and res[True][0] == 3
+    np.testing.assert_allclose(res[True][1], res[False][1], rtol=1e-4)
+    for (a, b) in zip(res[True][2], res[False][2]):
+        np.testing.assert_allclose(a, b, rtol=1e-3, atol=1e-5)

@@ -484,6 +484,34 @@ def test_conv_bias_relu_matches_op_sequence(rt, B, HW, C, K):
     np.testing.assert_allclose(y.get(), want, rtol=1e-4, atol=1e-4)
 
 
+@pytest.mark.parametrize("B,C,H,W", [(4, 32, 32, 32), (8, 32, 15, 15), (16, 64, 6, 6), (3, 48, 5, 3), (2, 16, 20, 13)])
+def test_relu_grad_nhwc_matches_op_sequence(rt, B, C, H, W):
+    """cgtb_relu_grad_nhwc against multiply -> transpose and Sum{0,2,3}: the transposed product bit for bit, the
+    channel sums against float64 like every other sum."""
+    rs = np.random.RandomState(61)
+    mask = (rs.rand(B, C, H, W) > 0.4).astype("i1")
+    g = rs.randn(B, C, H, W).astype("f4")
+    dm, dg = Dev(mask), Dev(g)
+    gt, bs = Dev(shape=(B, H, W, C), dtype="f4"), Dev(shape=(1, C, 1, 1), dtype="f4")
+    L = runtime.lib()
+    L.cgtb_relu_grad_nhwc.restype = ctypes.c_int
+    L.cgtb_relu_grad_nhwc.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_long, ctypes.c_int, ctypes.c_long, ctypes.c_void_p,
+                                      ctypes.c_void_p]
+    call("cgtb_relu_grad_nhwc", dm.ptr, dg.ptr, B, C, H * W, gt.ptr, bs.ptr)
+    n = B * C * H * W
+    prod, prod_t = Dev(shape=(B, C, H, W), dtype="f4"), Dev(shape=(B, H, W, C), dtype="f4")
+    call("cgtb_binary", 0, code("i1"), code("f4"), code("f4"), n, dm.ptr, dg.ptr, prod.ptr, 0, 0)
+    call("cgtb_transpose", code("f4"), 4, longs((B, C, H, W)), ints((0, 2, 3, 1)), prod.ptr, prod_t.ptr)
+    assert np.array_equal(gt.get(), prod_t.get())
+    assert np.array_equal(gt.get(), (mask * g).transpose(0, 2, 3, 1))
+    exact = (mask.astype("f8") * g.astype("f8")).sum(axis=(0, 2, 3))
+    want = O.reduce("sum", (mask * g).astype("f4"), [0, 2, 3]).reshape(C)
+    got = bs.get().reshape(C)
+    tol = 1e-5 * max(1.0, np.sqrt(B * H * W))
+    assert (np.abs(got - exact) <= 1e-4 * np.abs(exact) + tol).all()
+    assert np.abs(got - exact).max() <= 2 * np.abs(want - exact).max() + tol
+
+
 class _FusedProgram(ctypes.Structure):
     _fields_ = [("n_in", ctypes.c_int), ("n_ops", ctypes.c_int), ("n_out", ctypes.c_int), ("in_kind", ctypes.c_int * 8),
                 ("op_arity", ctypes.c_int * 16), ("op_code", ctypes.c_int * 16), ("op_a", ctypes.c_int * 16),
