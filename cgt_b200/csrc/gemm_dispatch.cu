@@ -179,21 +179,32 @@ __global__ void __launch_bounds__(256) relu_grad_nhwc_kernel(const int8_t* __res
   const int npix = (int)((HW - p0) < 128 ? (HW - p0) : 128);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const size_t plane0 = (size_t)b * C * HW + p0;
-  for (int c = warp; c < C; c += nwarps) {
-    const size_t base = plane0 + (size_t)c * HW;
-    float v[4];
+  // a warp takes four channels at a time and issues all their loads (16 mask bytes, 16 gradient words per
+  // lane) before the first use: the pass is bound by latency, not by bytes
+  for (int c0 = warp; c0 < C; c0 += 4 * nwarps) {
+    float v[4][4];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const int px = lane + 32 * q;
-      v[q] = px < npix ? (float)mask[base + px] * g[base + px] : 0.f;
+    for (int u = 0; u < 4; ++u) {
+      const int c = c0 + u * nwarps;
+      const size_t base = plane0 + (size_t)(c < C ? c : 0) * HW;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int px = lane + 32 * q;
+        v[u][q] = (c < C && px < npix) ? (float)mask[base + px] * g[base + px] : 0.f;
+      }
     }
-    float sum = (v[0] + v[1]) + (v[2] + v[3]);
 #pragma unroll
-    for (int q = 0; q < 4; ++q)
-      if (lane + 32 * q < npix) tile[(lane + 32 * q) * stride + c] = v[q];
+    for (int u = 0; u < 4; ++u) {
+      const int c = c0 + u * nwarps;
+      if (c >= C) break;
+      float sum = (v[u][0] + v[u][1]) + (v[u][2] + v[u][3]);
 #pragma unroll
-    for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
-    if (lane == 0) partial[((size_t)b * gridDim.x + blockIdx.x) * C + c] = sum;
+      for (int q = 0; q < 4; ++q)
+        if (lane + 32 * q < npix) tile[(lane + 32 * q) * stride + c] = v[u][q];
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+      if (lane == 0) partial[((size_t)b * gridDim.x + blockIdx.x) * C + c] = sum;
+    }
   }
   __syncthreads();
   float* dst = gt + ((size_t)b * HW + p0) * C;  // npix rows of C floats: one contiguous run
