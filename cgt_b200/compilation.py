@@ -490,6 +490,66 @@ def fuse_conv_grad_input(outputs, updatetargs, node2shape):
     return _rewire(outputs, updatetargs, replace)
 
 
+def pad_conv_columns(outputs, updatetargs, node2shape):
+    """Widen the rows of a float32 column matrix whose length Z = C*kh*kw is not a multiple of four (a 3-channel
+    5x5 convolution: 75) to the next multiple, so that every row starts on a 16-byte boundary and the products
+    that read it can be fed by the tensor-memory accelerator. Applies when Im2Col feeds exactly one
+    Reshape to [M, Z] whose consumers are the forward product (ConvBiasRelu) and / or the filter gradient
+    (Mul22{T,N}(dy, col)); those become ConvBiasRelu on the padded matrix and ConvWgrad{Z}. Runs last."""
+    from .nn_ops import im2col as im2col_ops
+    all_out = list(outputs) + list(updatetargs)
+    nodes = core.topsorted(all_out)
+    children = defaultdict(list)
+    for node in nodes:
+        for par in node.parents:
+            children[par].append(node)
+    out_set = set(all_out)
+    replace = {}
+    for im in nodes:
+        if im.is_input() or not isinstance(im.op, im2col_ops.Im2Col) or im.op.pitch or im.dtype != "f4" or im in out_set:
+            continue
+        if len(children[im]) != 1:
+            continue
+        r = children[im][0]
+        if not isinstance(r.op, core.Reshape) or r in out_set or r.ndim != 2 or r.parents[0] is not im:
+            continue
+        im_s = _static_shape(node2shape[im]) if im in node2shape else None
+        r_s = _static_shape(node2shape[r]) if r in node2shape else None
+        if im_s is None or r_s is None:
+            continue
+        z = im_s[3]
+        if z % 4 == 0 or r_s != (im_s[0] * im_s[1] * im_s[2], z):
+            continue
+        ok = bool(children[r])
+        for c in children[r]:
+            if isinstance(c.op, im2col_ops.ConvBiasRelu) and c.parents[0] is r and r not in c.parents[1:]:
+                continue
+            if (isinstance(c.op, core.Mul22) and c.op.tA and not c.op.tB and c.parents[1] is r and c.parents[0] is not r
+                    and c.dtype == "f4" and c not in out_set):
+                continue
+            ok = False
+        if not ok:
+            continue
+        pitch = (z + 3) // 4 * 4
+        pitch_node = core.cgt.constant(pitch)
+        im2 = core.Result(im2col_ops.Im2Col(im.op.info, pitch=pitch), list(im.parents))
+        node2shape[im2] = list(node2shape[im][:3]) + [pitch_node]
+        im2.props.update(im.props)
+        r2 = core.Result(core.Reshape(), [im2, r.parents[1], pitch_node])
+        node2shape[r2] = [node2shape[r][0], pitch_node]
+        r2.props.update(r.props)
+        replace[r] = r2
+        for c in children[r]:
+            if isinstance(c.op, core.Mul22):
+                wg = core.Result(im2col_ops.ConvWgrad(z), [c.parents[0], r2])
+                node2shape[wg] = node2shape[c]
+                wg.props.update(c.props)
+                replace[c] = wg
+    if not replace:
+        return list(outputs), list(updatetargs)
+    return _rewire(outputs, updatetargs, replace)
+
+
 def prebuild_fused_kernels(builders):
     """Generate and compile the fused-chain kernels of the given configurations into the library cache
     (no GPU needed: nvcc cross-compiles), so that a later run finds them instead of compiling."""
@@ -808,6 +868,8 @@ def run_compilation_pipeline(inputs, outputs, updates, givens):
         outputs_simple, updatetargs_simple = fuse_elementwise(outputs_simple, updatetargs_simple, node2shape)
         if config["fuse_conv_output"]:
             outputs_simple, updatetargs_simple = fuse_conv_output(outputs_simple, updatetargs_simple, node2shape)
+        if config["pad_conv_columns"]:
+            outputs_simple, updatetargs_simple = pad_conv_columns(outputs_simple, updatetargs_simple, node2shape)
     all_out = outputs_simple + updatetargs_simple
 
     nodelist = core.topsorted(all_out)

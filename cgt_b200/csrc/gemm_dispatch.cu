@@ -130,23 +130,60 @@ __global__ void __launch_bounds__(256) bias_relu_nchw_kernel(const float* __rest
 }
 }  // namespace
 
-CGTB_API int cgtb_conv_bias_relu(const float* col, long M, long K, const float* w, int C, const float* bias, long HW, float* y_nchw,
-                                 int8_t* mask_nchw) {
+namespace {
+// dst [R, ld] = src [R, K] with zeros in the columns beyond K
+__global__ void pad_rows_kernel(const float* __restrict__ src, int R, int K, float* __restrict__ dst, int ld) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= R * ld) return;
+  const int r = i / ld, k = i - r * ld;
+  dst[i] = k < K ? src[(size_t)r * K + k] : 0.f;
+}
+}  // namespace
+
+CGTB_API int cgtb_conv_bias_relu_ld(const float* col, long M, long K, long ldcol, const float* w, int C, const float* bias, long HW,
+                                    float* y_nchw, int8_t* mask_nchw) {
   if (!cgtb::require_runtime("cgtb_conv_bias_relu")) return 1;
   if (M <= 0 || C <= 0) return 0;
   if (HW <= 0 || M % HW != 0) return cgtb::fail("cgtb_conv_bias_relu: %ld rows are not whole images of %ld pixels", M, HW);
   if (C > 384) return cgtb::fail("cgtb_conv_bias_relu: at most 384 channels");
+  if (ldcol < K) return cgtb::fail("cgtb_conv_bias_relu: row pitch %ld below the row length %ld", ldcol, K);
+  // Filter rows of K entries start on 16-byte boundaries only when K is a multiple of 4. When the column
+  // matrix has such a pitch but K does not, the (small) filter matrix is copied to the same pitch so that
+  // both operands qualify for the TMA-fed product; the product still runs over K entries.
+  long ldw = K;
+  size_t wpad_bytes = 0;
+  if ((K & 3) != 0 && (ldcol & 3) == 0 && (long)C * ldcol < (1L << 24)) {
+    ldw = ldcol;
+    wpad_bytes = (((size_t)C * ldw * sizeof(float)) + 255) & ~(size_t)255;
+  }
+  auto padded_w = [&](float* dst) {
+    CGTB_LAUNCH(pad_rows_kernel, (unsigned)cgtb_ceil_div((long)C * ldw, 256), 256, 0, w, C, (int)K, dst, (int)ldw);
+  };
+  const float* wuse = w;
+  if (wpad_bytes) {
+    float* wp = (float*)cgtb::scratch_outer(wpad_bytes);
+    if (!wp) return 1;
+    padded_w(wp);
+    wuse = wp;
+  }
   {
     // the tensor-core kernels apply the output stage to the accumulator tile when the product is not split
     // along K: no intermediate matrix at all
     cgtb::ConvEpilogue ep = {bias, y_nchw, mask_nchw, HW};
-    int rc = cgtb::sgemm_tma(0, 1, 1, M, C, K, col, K, 0, w, K, 0, nullptr, C, 0, &ep);
-    if (rc < 0) rc = cgtb::sgemm_tc(0, 1, 1, M, C, K, col, K, 0, w, K, 0, nullptr, C, 0, &ep);
+    int rc = cgtb::sgemm_tma(0, 1, 1, M, C, K, col, ldcol, 0, wuse, ldw, 0, nullptr, C, 0, &ep);
+    if (rc < 0) rc = cgtb::sgemm_tc(0, 1, 1, M, C, K, col, ldcol, 0, wuse, ldw, 0, nullptr, C, 0, &ep);
     if (rc >= 0) return rc;
   }
-  float* g = (float*)cgtb::scratch_outer((size_t)M * C * sizeof(float));  // the product may use scratch() for split-K
-  if (!g) return 1;
-  int rc = cgtb::sgemm_dispatch(0, 1, 1, M, C, K, col, K, 0, w, K, 0, g, C, 0, 0);
+  // the product may use scratch() for split-K; a larger request may move the outer block, so the padded
+  // filters are written again at its start
+  char* blk = (char*)cgtb::scratch_outer(wpad_bytes + (size_t)M * C * sizeof(float));
+  if (!blk) return 1;
+  if (wpad_bytes) {
+    padded_w((float*)blk);
+    wuse = (const float*)blk;
+  }
+  float* g = (float*)(blk + wpad_bytes);
+  int rc = cgtb::sgemm_dispatch(0, 1, 1, M, C, K, col, ldcol, 0, wuse, ldw, 0, g, C, 0, 0);
   if (rc) return rc;
   // small products: 32-pixel tiles so that the grid still covers the machine
   const int tilepix = (M >= (long)kTilePix * 2 * cgtb::rt().sm_count) ? kTilePix : 32;
@@ -158,6 +195,11 @@ CGTB_API int cgtb_conv_bias_relu(const float* col, long M, long K, const float* 
   CGTB_LAUNCH(bias_relu_nchw_kernel, (unsigned)cgtb_ceil_div(M, tilepix), 256, smem, g, bias, M, C, HW, y_nchw, mask_nchw, tilepix);
   CGTB_CHECK_LAUNCH("conv_bias_relu");
   return 0;
+}
+
+CGTB_API int cgtb_conv_bias_relu(const float* col, long M, long K, const float* w, int C, const float* bias, long HW, float* y_nchw,
+                                 int8_t* mask_nchw) {
+  return cgtb_conv_bias_relu_ld(col, M, K, K, w, C, bias, HW, y_nchw, mask_nchw);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -17,21 +17,27 @@ using namespace cgtb;
 // C x kh input rows that the output row needs are staged in shared memory, each padded with zeros to
 // Wp = (Wo-1)*sw + kw entries and zero for rows outside the image, so the copy-out needs no range
 // test: col[.., w, c] = slab[offp[c] + w*sw] with offp[c] = (c_im*kh + i)*Wp + j. A thread owns four
-// consecutive column channels (one 16-byte store per w) when Z is a multiple of 4, else single
-// channels, and walks along w; consecutive threads write consecutive addresses.
+// consecutive column channels (one 16-byte store per w) when the row pitch is a multiple of 4, else
+// single channels, and walks along w; consecutive threads write consecutive addresses.
+// A column row may be wider than Z (pitch Zp > Z, chosen by the caller so that rows start on 16-byte
+// boundaries and the tensor-memory accelerator can address them): the extra entries are written as
+// zeros, read from one all-zero slab row appended for that purpose.
 // ================================================================================================
 template <typename T>
 __global__ void __launch_bounds__(256, 5) im2col_rows_kernel(const T* __restrict__ x, T* __restrict__ col, int C, int H, int W, int kh, int kw,
                                    int ph, int pw, int sh, int sw, int Ho, int Wo, int rows_per_block, long total_rows,
-                                   int vec4) {
+                                   int vec4, int Zp) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int Z = C * kh * kw, Wp = (Wo - 1) * sw + kw, nrows = C * kh;
-  int* offp = reinterpret_cast<int*>(smem_raw);                      // [Z], padded to a multiple of 4
-  T* slab = reinterpret_cast<T*>(offp + ((Z + 3) & ~3));             // [C*kh][Wp]
+  const int Zreal = C * kh * kw, Wp = (Wo - 1) * sw + kw, nrows = C * kh;
+  const int Z = Zp;                                                  // entries per column row as stored
+  int* offp = reinterpret_cast<int*>(smem_raw);                      // [Zp], padded to a multiple of 4
+  T* slab = reinterpret_cast<T*>(offp + ((Z + 3) & ~3));             // [C*kh (+ 1 zero row)][Wp]
   for (int c = threadIdx.x; c < Z; c += blockDim.x) {
     const int j = c % kw, ri = c / kw;
-    offp[c] = ri * Wp + j;
+    offp[c] = c < Zreal ? ri * Wp + j : nrows * Wp;
   }
+  if (Zp > Zreal)
+    for (int q = threadIdx.x; q < Wp; q += blockDim.x) slab[nrows * Wp + q] = T(0);
   for (int r = 0; r < rows_per_block; ++r) {
     const long row = (long)blockIdx.x * rows_per_block + r;  // row = b*Ho + h
     if (row >= total_rows) break;
@@ -69,12 +75,15 @@ __global__ void __launch_bounds__(256, 5) im2col_rows_kernel(const T* __restrict
     T* out = col + row * (long)Wo * Z;
     if (vec4) {
       typedef typename std::conditional<sizeof(T) == 4, float4, double4>::type V4;
-      for (int q = threadIdx.x; q < Z / 4; q += blockDim.x) {
+      // G groups of Z/4 threads when a row has few quads: group g takes w = g, g + G, ...
+      const int zq = Z / 4;
+      const int G = zq < (int)blockDim.x ? (int)blockDim.x / zq : 1;
+      const int g = G > 1 ? (int)threadIdx.x / zq : 0;
+      for (int q = G > 1 ? (int)threadIdx.x - g * zq : (int)threadIdx.x; q < zq && g < G; q += blockDim.x) {
         const int4 o = *reinterpret_cast<const int4*>(offp + 4 * q);
         const T *s0 = slab + o.x, *s1 = slab + o.y, *s2 = slab + o.z, *s3 = slab + o.w;
         V4* dst = reinterpret_cast<V4*>(out + 4 * q);
-        const int zq = Z / 4;
-        for (int w = 0; w < Wo; ++w) {
+        for (int w = g; w < Wo; w += G) {
           const int k = w * sw;
           V4 v;
           v.x = s0[k]; v.y = s1[k]; v.z = s2[k]; v.w = s3[k];
@@ -100,11 +109,12 @@ __global__ void __launch_bounds__(256, 5) im2col_rows_kernel(const T* __restrict
 // fallback when the slab does not fit in shared memory: one thread per output element
 template <typename T>
 __global__ void im2col_direct_kernel(const T* __restrict__ x, T* __restrict__ col, long total, int C, int H, int W,
-                                     int kh, int kw, int ph, int pw, int sh, int sw, int Ho, int Wo) {
+                                     int kh, int kw, int ph, int pw, int sh, int sw, int Ho, int Wo, int Zp) {
   const int Z = C * kh * kw;
   for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
-    int c = (int)(idx % Z);
-    long row = idx / Z;
+    int c = (int)(idx % Zp);
+    long row = idx / Zp;
+    if (c >= Z) { col[idx] = T(0); continue; }
     int w = (int)(row % Wo);
     long t = row / Wo;
     int h = (int)(t % Ho);
@@ -116,39 +126,46 @@ __global__ void im2col_direct_kernel(const T* __restrict__ x, T* __restrict__ co
 }
 
 template <typename T>
-static int im2col_launch(const T* x, long B, int C, int H, int W, int kh, int kw, int ph, int pw, int sh, int sw, T* col) {
+static int im2col_launch(const T* x, long B, int C, int H, int W, int kh, int kw, int ph, int pw, int sh, int sw, long ldcol, T* col) {
   int Ho = (H + 2 * ph - kh) / sh + 1, Wo = (W + 2 * pw - kw) / sw + 1;
   if (B <= 0 || Ho <= 0 || Wo <= 0) return 0;
   const int Z = C * kh * kw;
+  if (ldcol < Z || ldcol > Z + 1024) return fail("cgtb_im2col: row pitch %ld does not fit rows of %d entries", ldcol, Z);
+  const int Zp = (int)ldcol;
   const int Wp = (Wo - 1) * sw + kw;
-  size_t smem = (size_t)((Z + 3) & ~3) * sizeof(int) + (size_t)C * kh * Wp * sizeof(T);
+  size_t smem = (size_t)((Zp + 3) & ~3) * sizeof(int) + (size_t)(C * kh + (Zp > Z ? 1 : 0)) * Wp * sizeof(T);
   long total_rows = B * Ho;
   if (smem <= 200 * 1024) {
     if (smem > 48 * 1024)
       CGTB_CUDA_TRY(cudaFuncSetAttribute(im2col_rows_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     // several rows per block when a row is short, so each block moves at least ~16K elements
     int rpb = 1;
-    while ((long)rpb * Wo * Z < 16384 && rpb < 8) rpb *= 2;
+    while ((long)rpb * Wo * Zp < 16384 && rpb < 8) rpb *= 2;
     long blocks = cgtb_ceil_div(total_rows, rpb);
-    const int vec4 = ((Z & 3) == 0 && ((uintptr_t)col & (4 * sizeof(T) - 1)) == 0) ? 1 : 0;
+    const int vec4 = ((Zp & 3) == 0 && ((uintptr_t)col & (4 * sizeof(T) - 1)) == 0) ? 1 : 0;
     CGTB_LAUNCH(im2col_rows_kernel<T>, (unsigned)blocks, 256, smem, x, col, C, H, W, kh, kw, ph, pw, sh, sw, Ho, Wo, rpb,
-                total_rows, vec4);
+                total_rows, vec4, Zp);
   } else {
-    long total = total_rows * Wo * Z;
+    long total = total_rows * Wo * Zp;
     long blocks = std::min<long>(cgtb_ceil_div(total, 256), (long)rt().sm_count * 16);
-    CGTB_LAUNCH(im2col_direct_kernel<T>, (unsigned)blocks, 256, 0, x, col, total, C, H, W, kh, kw, ph, pw, sh, sw, Ho, Wo);
+    CGTB_LAUNCH(im2col_direct_kernel<T>, (unsigned)blocks, 256, 0, x, col, total, C, H, W, kh, kw, ph, pw, sh, sw, Ho, Wo, Zp);
   }
   CGTB_CHECK_LAUNCH("im2col");
   return 0;
 }
 
-CGTB_API int cgtb_im2col(int dtype, const void* x, long B, int C, int H, int W, int kh, int kw, int ph, int pw, int sh,
-                         int sw, void* col) {
+CGTB_API int cgtb_im2col_ld(int dtype, const void* x, long B, int C, int H, int W, int kh, int kw, int ph, int pw, int sh,
+                            int sw, long ldcol, void* col) {
   if (!require_runtime("cgtb_im2col")) return 1;
   if (kh <= 0 || kw <= 0 || sh <= 0 || sw <= 0) return fail("cgtb_im2col: kernel and stride must be positive");
-  if (dtype == cgtb_f4) return im2col_launch<float>((const float*)x, B, C, H, W, kh, kw, ph, pw, sh, sw, (float*)col);
-  if (dtype == cgtb_f8) return im2col_launch<double>((const double*)x, B, C, H, W, kh, kw, ph, pw, sh, sw, (double*)col);
+  if (dtype == cgtb_f4) return im2col_launch<float>((const float*)x, B, C, H, W, kh, kw, ph, pw, sh, sw, ldcol, (float*)col);
+  if (dtype == cgtb_f8) return im2col_launch<double>((const double*)x, B, C, H, W, kh, kw, ph, pw, sh, sw, ldcol, (double*)col);
   return fail("cgtb_im2col: unsupported dtype %d", dtype);
+}
+
+CGTB_API int cgtb_im2col(int dtype, const void* x, long B, int C, int H, int W, int kh, int kw, int ph, int pw, int sh,
+                         int sw, void* col) {
+  return cgtb_im2col_ld(dtype, x, B, C, H, W, kh, kw, ph, pw, sh, sw, (long)C * kh * kw, col);
 }
 
 // ================================================================================================

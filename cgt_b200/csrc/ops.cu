@@ -234,8 +234,9 @@ OP_BYREF(cgtb_op_im2col) {
   cgtArray *im = ARR(reads[0]), *col = ARR(write0);
   if (!all_gpu({im, col})) { fail("Im2Col: operands must be on the GPU"); return; }
   const long* s = im->shape();
-  cgtb_im2col(im->dtype(), im->data(), s[0], (int)s[1], (int)s[2], (int)s[3], cl->kernel_h, cl->kernel_w, cl->pad_h, cl->pad_w,
-              cl->stride_h, cl->stride_w, col->data());
+  // the output's last extent is the row pitch: C*kh*kw, or more when the compiler asked for padded rows
+  cgtb_im2col_ld(im->dtype(), im->data(), s[0], (int)s[1], (int)s[2], (int)s[3], cl->kernel_h, cl->kernel_w, cl->pad_h, cl->pad_w,
+                 cl->stride_h, cl->stride_w, col->shape()[3], col->data());
 }
 OP_BYREF(cgtb_op_col2im) {
   ConvClosure* cl = (ConvClosure*)cl0;
@@ -252,14 +253,29 @@ OP_BYREF(cgtb_op_conv_bias_relu) {
   cgtArray *mask = ARR(out->getitem(0)), *y = ARR(out->getitem(1));
   if (!all_gpu({col, w, bias, mask, y})) { fail("ConvBiasRelu: operands must be on the GPU"); return; }
   const long* d = y->shape();
-  const long M = col->shape()[0], K = col->shape()[1], C = d[1], HW = d[2] * d[3];
-  if (col->ndim() != 2 || w->ndim() != 2 || y->ndim() != 4 || col->dtype() != cgt_f4 || w->shape()[0] != C || w->shape()[1] != K ||
+  // col rows may be padded beyond the K entries of a filter row (cgtb_im2col_ld)
+  const long M = col->shape()[0], ldcol = col->shape()[1], K = w->shape()[1], C = d[1], HW = d[2] * d[3];
+  if (col->ndim() != 2 || w->ndim() != 2 || y->ndim() != 4 || col->dtype() != cgt_f4 || w->shape()[0] != C || ldcol < K ||
       bias->size() != C || M != d[0] * HW || mask->size() != y->size()) {
     fail("ConvBiasRelu: operand shapes do not fit together");
     return;
   }
-  cgtb_conv_bias_relu((const float*)col->data(), M, K, (const float*)w->data(), (int)C, (const float*)bias->data(), HW,
-                      (float*)y->data(), (int8_t*)mask->data());
+  cgtb_conv_bias_relu_ld((const float*)col->data(), M, K, ldcol, (const float*)w->data(), (int)C, (const float*)bias->data(), HW,
+                         (float*)y->data(), (int8_t*)mask->data());
+}
+// ConvWgrad: (dy [M,C], col [M,ldcol]) -> dy^T * col[:, :K] as [C,K]: the filter gradient from a column matrix
+// with padded rows; K is the output's second extent
+OP_BYREF(cgtb_op_conv_wgrad) {
+  cgtArray *dy = ARR(reads[0]), *col = ARR(reads[1]), *out = ARR(write0);
+  if (!all_gpu({dy, col, out})) { fail("ConvWgrad: operands must be on the GPU"); return; }
+  if (dy->ndim() != 2 || col->ndim() != 2 || out->ndim() != 2 || dy->dtype() != cgt_f4 || col->dtype() != cgt_f4 ||
+      dy->shape()[0] != col->shape()[0] || out->shape()[0] != dy->shape()[1] || out->shape()[1] > col->shape()[1]) {
+    fail("ConvWgrad: operand shapes do not fit together");
+    return;
+  }
+  const long M = dy->shape()[0], C = dy->shape()[1], K = out->shape()[1];
+  sgemm_dispatch(1, 0, 1, C, K, M, (const float*)dy->data(), C, 0, (const float*)col->data(), col->shape()[1], 0,
+                 (float*)out->data(), K, 0, 0);
 }
 // ReluGradNHWC: (mask i1 NCHW, g f4 NCHW) -> tuple(mask*g transposed to NHWC, Sum{0,2,3}(mask*g) as [1,C,1,1])
 OP_BYREF(cgtb_op_relu_grad_nhwc) {

@@ -27,14 +27,18 @@ def info2closure(info):
 class Im2Col(core.Op):
     available_impls = ("native_cpu", "native_gpu")
 
-    def __init__(self, info):
+    def __init__(self, info, pitch=0):
+        """pitch > 0 (set only by compilation.pad_conv_columns, after differentiation): column rows are `pitch`
+        entries apart instead of C*kh*kw, the extra entries zero."""
         assert info.stride_h > 0 and info.stride_w > 0
         self.info = info
+        self.pitch = int(pitch)
 
     def get_diff(self, _):
         return [True]
 
     def pullback(self, inputs, _y, gy):
+        assert not self.pitch, "padded column rows are introduced after differentiation"
         return [core.Result(Col2Im(self.info), [gy] + core.cgt.shape(inputs[0]))]
 
     def shp_apply(self, inputs):
@@ -42,7 +46,8 @@ class Im2Col(core.Op):
         batch_size, channels, height, width = core.cgt.shape(inputs[0])
         height_out = (height + 2 * info.pad_h - info.kernel_h) // info.stride_h + 1
         width_out = (width + 2 * info.pad_w - info.kernel_w) // info.stride_w + 1
-        return [batch_size, height_out, width_out, channels * info.kernel_w * info.kernel_h]
+        rowlen = core.cgt.constant(self.pitch) if self.pitch else channels * info.kernel_w * info.kernel_h
+        return [batch_size, height_out, width_out, rowlen]
 
     def typ_apply(self, inputs):
         assert inputs[0].ndim == 4
@@ -52,7 +57,7 @@ class Im2Col(core.Op):
         return core.NativeCompileInfo(None, prebuilt="cgtb_op_im2col", closure_triples=info2closure(self.info))
 
     def __repr__(self):
-        return "Im2Col{%s}" % (tuple(self.info),)
+        return "Im2Col{%s}" % (tuple(self.info),) + ("/pitch%d" % self.pitch if self.pitch else "")
 
 
 class Col2Im(core.Op):
@@ -171,3 +176,31 @@ class ReluGradNHWC(core.Op):
 
     def __repr__(self):
         return "ReluGradNHWC"
+
+
+class ConvWgrad(core.Op):
+    """(dy [M,C], col [M,pitch]) -> dy^T . col[:, :K] as [C,K]: the filter gradient of a convolution whose column
+    matrix has padded rows.
+
+    Not part of the reference's Op set. The compiler substitutes it (compilation.pad_conv_columns) for the
+    Mul22{T,N}(dy, col) that differentiating nn.conv2d yields (cgt/nn.py:93-100, cgt/core.py:2195-2222) when it
+    widens the rows of that column matrix to a multiple of four entries."""
+    available_impls = ("native_gpu",)
+
+    def __init__(self, k):
+        self.k = int(k)
+
+    def get_diff(self, n):
+        return [False] * n
+
+    def shp_apply(self, inputs):
+        return [core.cgt.size(inputs[0], 1), core.cgt.constant(self.k)]
+
+    def typ_apply(self, inputs):
+        return core.TensorType("f4", 2)
+
+    def get_native_compile_info(self, input_types, devtype):
+        return core.NativeCompileInfo(None, prebuilt="cgtb_op_conv_wgrad")
+
+    def __repr__(self):
+        return "ConvWgrad{%d}" % self.k

@@ -130,6 +130,11 @@ int cgtb_dgemm(int tA, int tB, long M, long N, long K, const double* A, long lda
 /* Im2Col / Col2Im (include/im2col.h:6-50, cgt/nn_ops/im2col.py:47-92); col is [B,Ho,Wo,C*kh*kw] */
 int cgtb_im2col(int dtype, const void* x, long B, int C, int H, int W, int kh, int kw, int ph, int pw, int sh,
                 int sw, void* col);
+/* The same with column rows ldcol >= C*kh*kw entries apart; entries beyond C*kh*kw are written as zeros. A pitch
+ * that is a multiple of 4 puts every row of a float32 column matrix on a 16-byte boundary, which the TMA-fed GEMM
+ * needs (a 3-channel 5x5 convolution has rows of 75 entries). */
+int cgtb_im2col_ld(int dtype, const void* x, long B, int C, int H, int W, int kh, int kw, int ph, int pw, int sh,
+                   int sw, long ldcol, void* col);
 int cgtb_col2im(int dtype, const void* col, long B, int C, int H, int W, int kh, int kw, int ph, int pw, int sh,
                 int sw, void* im);
 
@@ -161,6 +166,9 @@ int cgtb_conv_dgrad(const float* dy_nhwc, long B, int Ho, int Wo, int Cin, const
  * col [M, K] (M = B*HW rows, channels-last pixels), w [C, K], bias [C]; y_nchw, mask_nchw [B, C, HW]. float32. */
 int cgtb_conv_bias_relu(const float* col, long M, long K, const float* w, int C, const float* bias, long HW, float* y_nchw,
                         int8_t* mask_nchw);
+/* The same for a column matrix whose rows are ldcol >= K entries apart (cgtb_im2col_ld); w stays [C, K]. */
+int cgtb_conv_bias_relu_ld(const float* col, long M, long K, long ldcol, const float* w, int C, const float* bias, long HW,
+                           float* y_nchw, int8_t* mask_nchw);
 
 /* Input stage of a convolution layer's backward pass in one call: gt = transpose(mask * g) to channels-last and
  * bias_grad[c] = sum over images and pixels of mask * g. Replaces ElwiseBinary *, Transpose{0,2,3,1} and Sum{0,2,3}

@@ -154,7 +154,8 @@ def test_conv_output_substitution_changes_no_bit(rt):
     """ConvBiasRelu (GEMM + NCHW + bias + relu in one call) gives the bits of the Op sequence it replaces."""
     res = {}
     for fuse in (False, True):
-        with cgt.scoped_update_config(fuse_conv_output=fuse, use_cuda_graphs=False):
+        # padded column rows apply only next to ConvBiasRelu and change which product kernel runs: off here
+        with cgt.scoped_update_config(fuse_conv_output=fuse, pad_conv_columns=False, use_cuda_graphs=False):
             cfg = configs.BUILDERS["cifar"](**SMALL["cifar"])
             f = cfg.compile()
             names = [repr(instr) for instr in f.eg.instrs]
@@ -167,6 +168,26 @@ def test_conv_output_substitution_changes_no_bit(rt):
         assert np.array_equal(a, b)
     for (a, b) in zip(res[False][2], res[True][2]):
         assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("name,n_padded", [("cifar", 1), ("wide", 1)])
+def test_padded_column_rows(rt, name, n_padded):
+    """The first convolution's column matrix (rows of 75 / 363 entries) gets rows of 76 / 364 entries, its products
+    become ConvBiasRelu on the padded matrix and ConvWgrad; losses and parameters stay within float32 tolerance."""
+    res = {}
+    for pad in (False, True):
+        with cgt.scoped_update_config(pad_conv_columns=pad, use_cuda_graphs=False):
+            cfg = configs.BUILDERS[name](**SMALL[name])
+            f = cfg.compile()
+            names = [repr(instr) for instr in f.eg.instrs]
+            batches = [cfg.batch(seed) for seed in range(2)]
+            losses = [float(f(*batches[i % 2])[0]) for i in range(6)]
+            params = [np.asarray(p.op.get_value()).copy() for p in cfg.params]
+            res[pad] = (sum("/pitch" in n for n in names), sum("ConvWgrad" in n for n in names), losses, params)
+    assert res[False][:2] == (0, 0) and res[True][:2] == (n_padded, n_padded)
+    np.testing.assert_allclose(res[True][2], res[False][2], rtol=1e-4)
+    for (a, b) in zip(res[True][3], res[False][3]):
+        np.testing.assert_allclose(a, b, rtol=1e-3, atol=1e-5)
 
 
 def test_conv_grad_input_substitution(rt):

@@ -48,6 +48,32 @@ def test_im2col_col2im(rt, shape, kernel, pad, stride, dtype):
     assert np.array_equal(dim.get(), want_im)  # same accumulation order as the CPU loop: exact
 
 
+@pytest.mark.parametrize("shape,kernel,pad,stride,pitch", [
+    ((3, 3, 32, 32), (5, 5), (2, 2), (1, 1), 76),     # CIFAR conv1: rows of 75 widened to 16-byte multiples
+    ((2, 3, 64, 64), (11, 11), (2, 2), (4, 4), 364),  # wide conv1: 363 -> 364
+    ((2, 3, 9, 11), (3, 3), (1, 1), (2, 2), 28),
+    ((2, 3, 9, 11), (3, 3), (1, 1), (2, 2), 33),      # a pitch that is not a multiple of four: scalar stores
+    ((1, 2, 7, 9), (2, 3), (1, 0), (2, 1), 12),       # pitch == row length
+])
+@pytest.mark.parametrize("dtype", ["f4", "f8"])
+def test_im2col_padded_rows(rt, shape, kernel, pad, stride, pitch, dtype):
+    """cgtb_im2col_ld: the column rows lie `pitch` entries apart, the entries beyond C*kh*kw are zero."""
+    rs = np.random.RandomState(2)
+    x = rs.randn(*shape).astype(dtype)
+    ref = O.im2col(x, kernel, pad, stride)
+    want = np.zeros(ref.shape[:3] + (pitch,), dtype)
+    want[..., :ref.shape[3]] = ref
+    dx, dcol = Dev(x), Dev(np.full(want.shape, 7, dtype))
+    B, C, H, W = shape
+    L = runtime.lib()
+    L.cgtb_im2col_ld.restype = ctypes.c_int
+    L.cgtb_im2col_ld.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_long] + [ctypes.c_int] * 9 + [ctypes.c_long, ctypes.c_void_p]
+    call("cgtb_im2col_ld", code(dtype), dx.ptr, B, C, H, W, kernel[0], kernel[1], pad[0], pad[1], stride[0], stride[1], pitch, dcol.ptr)
+    assert np.array_equal(dcol.get(), want)
+    assert L.cgtb_im2col_ld(code(dtype), dx.ptr, B, C, H, W, kernel[0], kernel[1], pad[0], pad[1], stride[0], stride[1],
+                            ref.shape[3] - 1, dcol.ptr) != 0  # a pitch below the row length is refused
+
+
 POOLS = [
     ((2, 3, 5, 7), (4, 4), (0, 0), (1, 1)),      # reference test_imgproc.py test_pool
     ((4, 32, 32, 32), (3, 3), (0, 0), (2, 2)),   # CIFAR pool1
@@ -482,6 +508,35 @@ def test_conv_bias_relu_matches_op_sequence(rt, B, HW, C, K):
     assert np.array_equal(y.get(), y2.get())
     want = np.maximum((col.astype("f8") @ w.astype("f8").T + bias).reshape(B, HW, C).transpose(0, 2, 1), 0)
     np.testing.assert_allclose(y.get(), want, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("B,HW,C,K,ld", [(4, 1024, 32, 75, 76), (2, 225, 16, 27, 28), (3, 64, 96, 363, 364), (2, 100, 8, 30, 35),
+                                         (130, 1024, 32, 75, 76)])
+def test_conv_bias_relu_and_filter_gradient_on_padded_rows(rt, B, HW, C, K, ld):
+    """cgtb_conv_bias_relu_ld and the filter-gradient product on a column matrix whose rows are `ld` >= K apart give
+    what the unpadded matrix gives; the padding entries (NaN here) are never used."""
+    rs = np.random.RandomState(52)
+    M = B * HW
+    col, w, bias = rs.randn(M, K).astype("f4"), (rs.randn(C, K) * 0.1).astype("f4"), rs.randn(C).astype("f4")
+    colp = np.full((M, ld), np.nan, "f4")
+    colp[:, :K] = col
+    dcol, dw, db = Dev(colp), Dev(w), Dev(bias)
+    y, mask = Dev(shape=(B, C, HW), dtype="f4"), Dev(shape=(B, C, HW), dtype="i1")
+    L = runtime.lib()
+    L.cgtb_conv_bias_relu_ld.restype = ctypes.c_int
+    L.cgtb_conv_bias_relu_ld.argtypes = [ctypes.c_void_p, ctypes.c_long, ctypes.c_long, ctypes.c_long, ctypes.c_void_p, ctypes.c_int,
+                                         ctypes.c_void_p, ctypes.c_long, ctypes.c_void_p, ctypes.c_void_p]
+    call("cgtb_conv_bias_relu_ld", dcol.ptr, M, K, ld, dw.ptr, C, db.ptr, HW, y.ptr, mask.ptr)
+    t = (col.astype("f8") @ w.astype("f8").T + bias).reshape(B, HW, C).transpose(0, 2, 1)
+    np.testing.assert_allclose(y.get(), np.maximum(t, 0), rtol=1e-4, atol=1e-4)
+    sure = np.abs(t) > 1e-3
+    assert np.array_equal(mask.get()[sure], (t >= 0)[sure])
+    # filter gradient: dy^T [C, M] . col[:, :K] -> [C, K] with ldb = ld, ldc = K
+    dy = rs.randn(M, C).astype("f4")
+    ddy, dwg = Dev(dy), Dev(shape=(C, K), dtype="f4")
+    call("cgtb_sgemm", 1, 0, C, K, M, ddy.ptr, C, dcol.ptr, ld, dwg.ptr, K, 0)
+    want = dy.astype("f8").T @ col.astype("f8")
+    np.testing.assert_allclose(dwg.get(), want, rtol=1e-4, atol=1e-4 * np.sqrt(M))
 
 
 @pytest.mark.parametrize("B,C,H,W", [(4, 32, 32, 32), (8, 32, 15, 15), (16, 64, 6, 6), (3, 48, 5, 3), (2, 16, 20, 13)])
