@@ -77,6 +77,8 @@ struct cgtbInterp {
   long runs = 0, last_launches = 0, last_graph_launches = 0, captured = 0;
   long mallocs_at_run_start = 0;
   bool prev_run_allocated = true;
+  void (*before_sync)(void*) = nullptr;  // called once per run after all device work has been queued
+  void* before_sync_ctx = nullptr;
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -474,6 +476,8 @@ CGTB_API int cgtb_interp_run(cgtbInterp* it, cgtbObject* args_obj, cgtbObject** 
     if (rc) break;
   }
   it->args = nullptr;
+  // host work that should overlap this run's device work (e.g. queueing the next batch's upload)
+  if (!rc && it->before_sync) it->before_sync(it->before_sync_ctx);
   if (rt().ready) {
     cudaError_t e = cudaStreamSynchronize(rt().stream);
     it->host_pending = false;
@@ -488,6 +492,13 @@ CGTB_API int cgtb_interp_run(cgtbInterp* it, cgtbObject* args_obj, cgtbObject** 
   o->Retain();
   for (size_t i = 0; i < it->outs.size(); ++i) o->setitem((int)i, get(it, it->outs[i]));
   *out = (cgtbObject*)o;
+  return 0;
+}
+
+CGTB_API int cgtb_interp_set_before_sync(cgtbInterp* it, void (*fn)(void*), void* ctx) {
+  if (!it) return fail("cgtb_interp_set_before_sync: null interpreter");
+  it->before_sync = fn;
+  it->before_sync_ctx = ctx;
   return 0;
 }
 

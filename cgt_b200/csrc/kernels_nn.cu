@@ -141,6 +141,9 @@ static int im2col_launch(const T* x, long B, int C, int H, int W, int kh, int kw
     // several rows per block when a row is short, so each block moves at least ~16K elements
     int rpb = 1;
     while ((long)rpb * Wo * Zp < 16384 && rpb < 8) rpb *= 2;
+    // ... but not at the price of a grid that leaves SMs short of resident blocks (measured: the CIFAR step gains
+    // 2 % when the 6x6 and 32x32 layers get 10 blocks per SM instead of 1.3 and 3.5)
+    while (rpb > 1 && cgtb_ceil_div(total_rows, rpb) < 10L * rt().sm_count) rpb /= 2;
     long blocks = cgtb_ceil_div(total_rows, rpb);
     const int vec4 = ((Zp & 3) == 0 && ((uintptr_t)col & (4 * sizeof(T) - 1)) == 0) ? 1 : 0;
     CGTB_LAUNCH(im2col_rows_kernel<T>, (unsigned)blocks, 256, smem, x, col, C, H, W, kh, kw, ph, pw, sh, sw, Ho, Wo, rpb,

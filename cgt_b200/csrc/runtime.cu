@@ -429,6 +429,66 @@ CGTB_API int cgtb_event_elapsed_ms(void* e0, void* e1, float* ms) {
   return 0;
 }
 CGTB_API void cgtb_event_free(void* e) { if (e) cudaEventDestroy((cudaEvent_t)e); }
+// ================================================================== C ABI: input prefetch on a copy stream
+// Uploading the next batch while the current step computes. A staging slot goes through
+//   begin(slot)   copy stream waits until the step that last read the slot's buffers has finished
+//   h2d(...)      copies on the copy stream
+//   mark(slot)    closes the slot's group of copies
+//   join(slot)    runtime stream waits for that group (not for groups queued behind it)
+//   release(slot) recorded on the runtime stream after the consuming step has been queued
+// No call here synchronises the host. `src` should be page-locked, otherwise the driver stages the copy
+// and it does not overlap.
+namespace {
+constexpr int kPrefetchSlots = 4;
+cudaStream_t g_copy_stream = nullptr;
+cudaEvent_t g_copy_done[kPrefetchSlots] = {}, g_slot_free[kPrefetchSlots] = {};
+bool g_slot_used[kPrefetchSlots] = {};
+bool copy_stream_ready() {
+  if (g_copy_stream) return true;
+  bool ok = cudaStreamCreateWithFlags(&g_copy_stream, cudaStreamNonBlocking) == cudaSuccess;
+  for (int i = 0; ok && i < kPrefetchSlots; ++i)
+    ok = cudaEventCreateWithFlags(&g_copy_done[i], cudaEventDisableTiming) == cudaSuccess &&
+         cudaEventCreateWithFlags(&g_slot_free[i], cudaEventDisableTiming) == cudaSuccess;
+  if (!ok) {
+    g_copy_stream = nullptr;
+    fail("cannot create the copy stream");
+  }
+  return ok;
+}
+bool slot_ok(const char* who, int slot) {
+  if (slot >= 0 && slot < kPrefetchSlots) return true;
+  fail("%s: slot %d out of range", who, slot);
+  return false;
+}
+}  // namespace
+CGTB_API int cgtb_prefetch_begin(int slot) {
+  if (!require_runtime("cgtb_prefetch_begin") || !slot_ok("cgtb_prefetch_begin", slot) || !copy_stream_ready()) return 1;
+  if (g_slot_used[slot]) CGTB_CUDA_TRY(cudaStreamWaitEvent(g_copy_stream, g_slot_free[slot], 0));
+  return 0;
+}
+CGTB_API int cgtb_prefetch_h2d(void* dst_device, const void* src_host, long nbytes) {
+  if (!require_runtime("cgtb_prefetch_h2d")) return 1;
+  if (nbytes < 0 || (nbytes > 0 && (!dst_device || !src_host))) return fail("cgtb_prefetch_h2d: bad arguments");
+  if (!copy_stream_ready()) return 1;
+  if (nbytes > 0) CGTB_CUDA_TRY(cudaMemcpyAsync(dst_device, src_host, (size_t)nbytes, cudaMemcpyHostToDevice, g_copy_stream));
+  return 0;
+}
+CGTB_API int cgtb_prefetch_mark(int slot) {
+  if (!require_runtime("cgtb_prefetch_mark") || !slot_ok("cgtb_prefetch_mark", slot) || !copy_stream_ready()) return 1;
+  CGTB_CUDA_TRY(cudaEventRecord(g_copy_done[slot], g_copy_stream));
+  return 0;
+}
+CGTB_API int cgtb_prefetch_join(int slot) {
+  if (!require_runtime("cgtb_prefetch_join") || !slot_ok("cgtb_prefetch_join", slot) || !copy_stream_ready()) return 1;
+  CGTB_CUDA_TRY(cudaStreamWaitEvent(g_rt.stream, g_copy_done[slot], 0));
+  return 0;
+}
+CGTB_API int cgtb_prefetch_release(int slot) {
+  if (!require_runtime("cgtb_prefetch_release") || !slot_ok("cgtb_prefetch_release", slot) || !copy_stream_ready()) return 1;
+  CGTB_CUDA_TRY(cudaEventRecord(g_slot_free[slot], g_rt.stream));
+  g_slot_used[slot] = true;
+  return 0;
+}
 // overwrite a buffer larger than L2 (126 MB on B200) so that the next kernels start from a cold L2
 CGTB_API int cgtb_l2_flush(void) {
   if (!require_runtime("cgtb_l2_flush")) return 1;

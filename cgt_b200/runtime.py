@@ -43,6 +43,9 @@ def _declare(lib):
         "cgtb_event_new": (vp, []), "cgtb_event_record": (ci, [vp]),
         "cgtb_event_elapsed_ms": (ci, [vp, vp, ctypes.POINTER(ctypes.c_float)]), "cgtb_event_free": (None, [vp]),
         "cgtb_l2_flush": (ci, []),
+        "cgtb_prefetch_h2d": (ci, [vp, vp, cl]),
+        "cgtb_prefetch_begin": (ci, [ci]), "cgtb_prefetch_mark": (ci, [ci]), "cgtb_prefetch_join": (ci, [ci]),
+        "cgtb_prefetch_release": (ci, [ci]),
         "cgtb_comm_load": (ci, [ctypes.c_char_p]), "cgtb_comm_unique_id": (ci, [ctypes.c_char_p]),
         "cgtb_comm_init": (ci, [ctypes.c_char_p, ci, ci]), "cgtb_comm_world": (ci, []), "cgtb_comm_rank": (ci, []),
         "cgtb_comm_check": (ci, []), "cgtb_comm_abort": (ci, []), "cgtb_comm_destroy": (ci, []),
@@ -64,6 +67,7 @@ def _declare(lib):
         "cgtb_graph_add_return_byref": (ci, [vp, ctypes.c_char_p, ci, c_long_p, c_int_p, cl, ci, vp, vp, ci]),
         "cgtb_graph_add_return_byval": (ci, [vp, ctypes.c_char_p, ci, c_long_p, c_int_p, cl, ci, vp, vp, ci]),
         "cgtb_interp_new": (vp, [vp, ci, c_long_p, ci]), "cgtb_interp_free": (None, [vp]),
+        "cgtb_interp_set_before_sync": (ci, [vp, vp, vp]),
         "cgtb_interp_run": (ci, [vp, vp, ctypes.POINTER(vp)]), "cgtb_interp_stats": (ci, [vp, c_long_p, ci]),
         "cgtb_interp_profile": (ci, [vp, ctypes.POINTER(cd), c_long_p, ci]),
         "cgtb_interp_instr_repr": (ctypes.c_char_p, [vp, ci]),
@@ -466,10 +470,72 @@ class InterpreterWrapper(object):
 
     _pending_release = []
 
+    def prefetch(self, *pyargs):
+        """Announce the array arguments of a later call f(*pyargs) so that their host->device copy overlaps a step
+        instead of running inside one. The upload is issued on the copy stream by the next call of f right after
+        that call's own work has been queued (or at once by that call, if it is the one that uses the arrays); the
+        call that receives the same array objects waits on the device for the upload and reads the staged copies.
+        Typical loop: ``f.prefetch(*batch[i + 1]); loss = f(*batch[i])``. Two staging slots alternate. The arrays
+        must not be written between prefetch and the call that uses them. Page-locked arrays
+        (runtime.pinned_empty) make the copy asynchronous. Not part of the reference's API, whose Transport
+        copies inside the step (cgt/core.py:1419-1430)."""
+        assert len(pyargs) == len(self.input_types), "expected %d arguments, got %d" % (len(self.input_types), len(pyargs))
+        self._pf_request = pyargs
+        if not hasattr(self, "_pf_hook"):
+            def hook(_ctx):
+                try:
+                    if self._pf_request is not None:
+                        self._pf_issue()
+                except Exception as e:  # surfaces after the run; an exception cannot cross the C frames
+                    self._pf_error = e
+            self._pf_hook = ctypes.CFUNCTYPE(None, ctypes.c_void_p)(hook)
+            check(lib().cgtb_interp_set_before_sync(self.interp, ctypes.cast(self._pf_hook, ctypes.c_void_p), None), "prefetch")
+
+    def _pf_issue(self):
+        """Queue the uploads of the announced arguments into the next staging slot."""
+        from . import core
+        L = lib()
+        pyargs, self._pf_request = self._pf_request, None
+        if not hasattr(self, "_pf_bufs"):
+            self._pf_bufs, self._pf_slot, self._pf = ({}, {}), 0, {}
+        self._pf_slot ^= 1
+        slot, bufs = self._pf_slot, self._pf_bufs[self._pf_slot]
+        check(L.cgtb_prefetch_begin(slot), "prefetch")
+        staged = {}
+        for (i, (arg, typ)) in enumerate(zip(pyargs, self.input_types)):
+            if isinstance(arg, (ArrayWrapper, tuple)):
+                continue
+            a = core.as_valid_array(arg, typ.dtype)
+            if a.ndim != typ.ndim:
+                raise ValueError("argument %d has %d dimensions, expected %d" % (i, a.ndim, typ.ndim))
+            w = bufs.get(i)
+            if w is None or w.shape != a.shape or np.dtype(w.dtype) != a.dtype:
+                w = bufs[i] = device_array(np.zeros(a.shape, a.dtype))
+            check(L.cgtb_prefetch_h2d(ctypes.c_void_p(w.data), ctypes.c_void_p(a.ctypes.data), ctypes.c_long(a.nbytes)), "prefetch")
+            staged[i] = (arg, a, w)  # `a` stays referenced until the call that consumes the upload
+        check(L.cgtb_prefetch_mark(slot), "prefetch")
+        self._pf[slot] = staged  # replaces an unconsumed upload that used this slot
+
     def __call__(self, *pyargs):
         from . import core
         L = lib()
         assert len(pyargs) == len(self.input_types), "expected %d arguments, got %d" % (len(self.input_types), len(pyargs))
+        request = getattr(self, "_pf_request", None)
+        if request is not None and any(r is a for (r, a) in zip(request, pyargs) if not isinstance(a, (ArrayWrapper, tuple))):
+            self._pf_issue()  # announced for this very call: upload now
+        used_slot = None
+        for (slot, staged) in list(getattr(self, "_pf", {}).items()):
+            hits = [i for (i, (arg, _a, _w)) in staged.items() if pyargs[i] is arg]
+            if hits:
+                pyargs = list(pyargs)
+                for i in hits:
+                    pyargs[i] = staged[i][2]
+                check(L.cgtb_prefetch_join(slot), "prefetch join")
+                # consumed: a later call with the same arrays copies again; the host sources stay referenced
+                # until this call has returned (its result read-back waits for the stream)
+                self._pf_keep = self._pf.pop(slot)
+                used_slot = slot
+                break
         cargs = L.cgtb_tuple_new(len(pyargs))
         keep = []
         for (i, (arg, typ)) in enumerate(zip(pyargs, self.input_types)):
@@ -494,11 +560,17 @@ class InterpreterWrapper(object):
         out = ctypes.c_void_p(0)
         rc = L.cgtb_interp_run(self.interp, cargs, ctypes.byref(out))
         L.cgtb_release(cargs)
+        if used_slot is not None:
+            L.cgtb_prefetch_release(used_slot)  # the slot's buffers are free once this step has run
         for h in self._pending_release:
             L.cgtb_release(h)
         del self._pending_release[:]
         check(rc, "running compiled function")
         try:
+            err = getattr(self, "_pf_error", None)
+            if err is not None:
+                self._pf_error = None
+                raise err
             return list(cgt2py_object(out.value))
         finally:
             L.cgtb_release(out)

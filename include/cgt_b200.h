@@ -47,6 +47,17 @@ int cgtb_l2_flush(void);                   /* memset of a 256 MiB device buffer 
 void* cgtb_alloc(int devtype, long nbytes);
 void cgtb_free(int devtype, void* p);
 int cgtb_memcpy(int dst_devtype, int src_devtype, void* dst, const void* src, long nbytes, int sync);
+/* Input prefetch (no counterpart in the reference, whose Transport copies inside the step: cgt/core.py:1419-1430).
+ * Host->device copies of a later step's inputs on a second stream, into caller-owned staging buffers grouped in
+ * slots 0..3. begin(slot): the copy stream waits until the step that last read the slot has finished (see release);
+ * h2d: one copy, queued and returned at once; mark(slot): closes the slot's group; join(slot): the runtime stream
+ * waits for that group only; release(slot): call after queueing the step that reads the slot. src_host should be
+ * page-locked (cgtb_alloc with devtype 0). None of the calls synchronises the host. */
+int cgtb_prefetch_begin(int slot);
+int cgtb_prefetch_h2d(void* dst_device, const void* src_host, long nbytes);
+int cgtb_prefetch_mark(int slot);
+int cgtb_prefetch_join(int slot);
+int cgtb_prefetch_release(int slot);
 int cgtb_memset(void* dev_ptr, int value, long nbytes);
 
 /* ------------------------------------------------------------------------------------------------
@@ -106,6 +117,9 @@ int cgtb_interp_run(cgtbInterp* it, cgtbObject* args, cgtbObject** out);
 /* counters: [0] runs, [1] kernels launched by instructions in the last run, [2] graph launches in the
  * last run, [3] segments captured so far, [4] device instructions in the graph */
 int cgtb_interp_stats(cgtbInterp* it, long* counters, int n);
+/* fn(ctx) is called in every cgtb_interp_run after the run's device work has been queued and before the run waits
+ * for it: the place for host work that should overlap the step (queueing the next batch's upload). NULL removes it. */
+int cgtb_interp_set_before_sync(cgtbInterp* it, void (*fn)(void*), void* ctx);
 /* per-instruction accumulated milliseconds when CGTB_INTERP_PROFILE is set; returns n_instrs */
 int cgtb_interp_profile(cgtbInterp* it, double* ms, long* counts, int cap);
 const char* cgtb_interp_instr_repr(cgtbInterp* it, int i);

@@ -192,6 +192,41 @@ def test_padded_column_rows(rt, name, n_padded):
         np.testing.assert_allclose(a, b, rtol=1e-3, atol=1e-5)
 
 
+@pytest.mark.parametrize("graphs", [False, True])
+def test_prefetched_inputs_give_the_same_steps(rt, graphs):
+    """f.prefetch(next batch) before f(batch) uploads on the copy stream; losses and parameters are those of the
+    plain calls bit for bit, also when a prefetched batch is never consumed or a batch is called without prefetch."""
+    from cgt_b200 import runtime
+    res = {}
+    for pre in (False, True):
+        with cgt.scoped_update_config(use_cuda_graphs=graphs):
+            cfg = configs.BUILDERS["cifar"](**SMALL["cifar"])
+            f = cfg.compile()
+            batches = []
+            for seed in range(3):
+                pinned = []
+                for a in cfg.batch(seed):
+                    p = runtime.pinned_empty(a.shape, a.dtype)
+                    p[...] = a
+                    pinned.append(p)
+                batches.append(pinned)
+            order = [0, 1, 2, 0, 0, 2, 1, 1]
+            losses = []
+            if pre:
+                f.prefetch(*batches[order[0]])
+            for (i, b) in enumerate(order):
+                if pre and i + 1 < len(order) and i != 3:   # step 4 runs without a prefetched batch
+                    f.prefetch(*batches[order[i + 1]])
+                if pre and i == 5:
+                    f.prefetch(*batches[0])                  # replaces the upload queued for step 6: never consumed
+                losses.append(np.asarray(f(*batches[b])[0]).copy())
+            res[pre] = (losses, [np.asarray(p.op.get_value()).copy() for p in cfg.params])
+    for (a, b) in zip(res[False][0], res[True][0]):
+        assert np.array_equal(a, b)
+    for (a, b) in zip(res[False][1], res[True][1]):
+        assert np.array_equal(a, b)
+
+
 def test_conv_grad_input_substitution(rt):
     """ReluGradNHWC replaces multiply + Transpose{0,2,3,1} + Sum{0,2,3}; only the bias gradients' summation order
     changes, so losses and parameters agree to float32 tolerance."""
