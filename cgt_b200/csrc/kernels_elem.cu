@@ -338,31 +338,31 @@ __global__ void reduce_finish_kernel(int kind, long osize, int nsplit, const T* 
 
 // The fast path for an input viewed as [R0, K, R1] with R0 and R1 reduced lives in reduce_rkr.h.
 // [R0, K] with R0 reduced and K contiguous (column sums: the bias gradient of a dense layer). Block =
-// 32 columns x 8 row groups: lane along K (coalesced rows), row group g adds rows g, g+8, ... with four
-// loads in flight, and the eight partial sums of a column are folded in a fixed order through shared
-// memory. One thread walking all R0 rows of its column would pay the memory latency R0 times.
-template <typename T>
-__global__ void reduce_rk_kernel(int kind, int R0, int K, const T* __restrict__ in, T* __restrict__ out) {
-  __shared__ T part[8][33];
+// 32 columns x G row groups (G = 8, or 32 for many rows): lane along K (coalesced rows), row group g adds rows
+// g, g+G, ... with four loads in flight, and the G partial sums of a column are folded in a fixed order through
+// shared memory. One thread walking all R0 rows of its column would pay the memory latency R0 times.
+template <typename T, int G>
+__global__ void __launch_bounds__(32 * G) reduce_rk_kernel(int kind, int R0, int K, const T* __restrict__ in, T* __restrict__ out) {
+  __shared__ T part[G][33];
   const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
   for (int k0 = blockIdx.x * 32; k0 < K; k0 += gridDim.x * 32) {
     const int k = k0 + lane;
     T acc = red_init<T>(kind);
     if (k < K) {
       int r0 = g;
-      for (; r0 + 24 < R0; r0 += 32) {
-        const T v0 = in[(size_t)r0 * K + k], v1 = in[(size_t)(r0 + 8) * K + k], v2 = in[(size_t)(r0 + 16) * K + k],
-                v3 = in[(size_t)(r0 + 24) * K + k];
+      for (; r0 + 3 * G < R0; r0 += 4 * G) {
+        const T v0 = in[(size_t)r0 * K + k], v1 = in[(size_t)(r0 + G) * K + k], v2 = in[(size_t)(r0 + 2 * G) * K + k],
+                v3 = in[(size_t)(r0 + 3 * G) * K + k];
         acc = red_op<T>(kind, red_op<T>(kind, red_op<T>(kind, red_op<T>(kind, acc, v0), v1), v2), v3);
       }
-      for (; r0 < R0; r0 += 8) acc = red_op<T>(kind, acc, in[(size_t)r0 * K + k]);
+      for (; r0 < R0; r0 += G) acc = red_op<T>(kind, acc, in[(size_t)r0 * K + k]);
     }
     part[g][lane] = acc;
     __syncthreads();
     if (g == 0 && k < K) {
       T r = part[0][lane];
 #pragma unroll
-      for (int q = 1; q < 8; ++q) r = red_op<T>(kind, r, part[q][lane]);
+      for (int q = 1; q < G; ++q) r = red_op<T>(kind, r, part[q][lane]);
       out[k] = r;
     }
     __syncthreads();
@@ -414,7 +414,12 @@ static int reduce_launch(int kind, int ndim, const long* shape, const int* reduc
     if (match && R0 < (1L << 30) && K < 65536L * 16 && R1 < (1L << 30)) {
       if (R1 == 1 && K >= 1) {
         if (R0 <= 4096 || K >= 1024) {
-          CGTB_LAUNCH(reduce_rk_kernel<T>, (unsigned)std::min<long>(cgtb_ceil_div(K, 32), 4096), 256, 0, kind, (int)R0, (int)K, in, out);
+          const unsigned blocks = (unsigned)std::min<long>(cgtb_ceil_div(K, 32), 4096);
+          if (R0 >= 256 && blocks <= 2u * (unsigned)rt().sm_count) {  // few columns, many rows: more row groups
+            CGTB_LAUNCH((reduce_rk_kernel<T, 32>), blocks, 1024, 0, kind, (int)R0, (int)K, in, out);
+          } else {
+            CGTB_LAUNCH((reduce_rk_kernel<T, 8>), blocks, 256, 0, kind, (int)R0, (int)K, in, out);
+          }
           return 0;
         }
       } else if (K <= 65535) {
