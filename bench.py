@@ -288,9 +288,14 @@ def run_b200(args):
 # DRAM traffic of the dominant Op class from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum of one
 # launch, summary under profiles/), as a ratio to that launch's algorithmic bytes; `traffic` scales the class's
 # algorithmic bytes per step by it (the captured launch streams its operands once, like every launch of the class).
-NCU_TRAFFIC_RATIO = {"Mul22": 96.33 / 95.95}
+NCU_TRAFFIC_RATIO = {"Mul22": 96.33 / 95.95, "ConvBiasRelu": 96.33 / 95.95}
 NCU_TRAFFIC_NOTE = {"Mul22": "ncu capture of the conv2 forward product 28800x32x800 (sgemm_tma_kernel): 92.31 MB read + 4.02 MB "
-                             "written against 95.95 MB algorithmic; scaled to the class's algorithmic bytes per step"}
+                             "written against 95.95 MB algorithmic; scaled to the class's algorithmic bytes per step",
+                    "ConvBiasRelu": "same kernel as Mul22 with the output stage in its epilogue. ncu captures of its products: conv2 "
+                                    "28800x32x800 92.31 MB read + 4.02 MB written against 95.95 MB algorithmic; conv1 131072x32x76 "
+                                    "39.90 MB read against 39.85 MB of operand (its 16.8 MB result was still in L2 when the kernel "
+                                    "ended: 0.02 MB written). Operands are streamed once; the conv2 ratio scales the class's "
+                                    "algorithmic bytes per step"}
 
 
 # ------------------------------------------------------------------------------------------------
