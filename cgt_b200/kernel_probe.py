@@ -67,6 +67,11 @@ def stencils(reps):
     x1, col1 = _dev(rs.randn(B, 3, 32, 32).astype("f4")), _dev(shape=(B, 32, 32, 75))
     _timed("im2col conv1", lambda: L.cgtb_im2col(f4, _ptr(x1), B, 3, 32, 32, 5, 5, 2, 2, 1, 1, _ptr(col1)), reps,
            4 * (B * 3 * 1024 + B * 1024 * 75))
+    col1p = _dev(shape=(B, 32, 32, 76))
+    L.cgtb_im2col_ld.restype = ctypes.c_int
+    L.cgtb_im2col_ld.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_long] + [ctypes.c_int] * 9 + [ctypes.c_long, ctypes.c_void_p]
+    _timed("im2col conv1, rows of 76", lambda: L.cgtb_im2col_ld(f4, _ptr(x1), B, 3, 32, 32, 5, 5, 2, 2, 1, 1, 76, _ptr(col1p)), reps,
+           4 * (B * 3 * 1024 + B * 1024 * 76))
     # data gradient of conv2 without a column matrix
     dy, wr, dx = _dev(rs.randn(B, 15, 15, 32).astype("f4")), _dev(rs.randn(32, 5, 5, 32).astype("f4")), _dev(shape=(B, 32, 15, 15))
     L.cgtb_conv_dgrad.restype = ctypes.c_int
