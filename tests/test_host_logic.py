@@ -226,6 +226,39 @@ def test_placement_transports_and_memory_owners():
     assert kinds == {"LoadArgument", "Alloc", "BuildTup", "ReturnByRef", "ReturnByVal"}
 
 
+def test_odd_column_rows_are_padded_for_both_products():
+    """compilation.pad_conv_columns: the column matrix of a 3-channel 5x5 convolution (rows of 75) gets rows of 76,
+    its forward product stays ConvBiasRelu on the padded matrix, its filter gradient becomes ConvWgrad{75} with the
+    unpadded result shape; the 32-channel layers (rows of 800) are left alone."""
+    from cgt_b200.nn_ops import im2col as im2col_ops
+    cfg = configs.build_cifar(batch=4)
+    outs, _usrc, utargs, analysis = compilation.simplify_for_execution([cfg.loss] + list(cfg.extra_outputs), cfg.updates)
+    n2s = analysis["node2shape"]
+    o, u = compilation.fuse_conv_dgrad(outs, utargs, n2s)
+    o, u = compilation.fuse_conv_grad_input(o, u, n2s)
+    o, u = compilation.fuse_elementwise(o, u, n2s)
+    o, u = compilation.fuse_conv_output(o, u, n2s)
+    before = [n for n in core.topsorted(o + u) if not n.is_input() and isinstance(n.op, core.Mul22) and n.op.tA and not n.op.tB]
+    o, u = compilation.pad_conv_columns(o, u, n2s)
+    nodes = [n for n in core.topsorted(o + u) if not n.is_input()]
+    ims = [n for n in nodes if isinstance(n.op, im2col_ops.Im2Col)]
+    assert sorted(n.op.pitch for n in ims) == [0, 0, 76]
+    padded = [n for n in ims if n.op.pitch][0]
+    assert compilation._static_shape(n2s[padded]) == (4, 32, 32, 76)
+    wg = [n for n in nodes if isinstance(n.op, im2col_ops.ConvWgrad)]
+    assert len(wg) == 1 and wg[0].op.k == 75 and compilation._static_shape(n2s[wg[0]]) == (32, 75)
+    after = [n for n in nodes if isinstance(n.op, core.Mul22) and n.op.tA and not n.op.tB]
+    assert len(after) == len(before) - 1
+    # both consumers read the one padded matrix
+    r = wg[0].parents[1]
+    assert isinstance(r.op, core.Reshape) and r.parents[0] is padded and compilation._static_shape(n2s[r]) == (4096, 76)
+    fwd = [n for n in nodes if isinstance(n.op, im2col_ops.ConvBiasRelu) and n.parents[0] is r]
+    assert len(fwd) == 1
+    # a second application finds nothing left to do
+    o2, u2 = compilation.pad_conv_columns(o, u, n2s)
+    assert [n for n in core.topsorted(o2 + u2) if not n.is_input() and isinstance(n.op, im2col_ops.ConvWgrad)] == wg
+
+
 def test_update_is_ordered_after_other_readers_of_the_variable():
     """Updates listed last-layer-first: the dgrad product that still needs the old last-layer weight
     must be scheduled before the in-place update of that weight."""
