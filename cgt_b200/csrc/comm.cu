@@ -8,6 +8,7 @@
 #include "runtime.h"
 #include <dlfcn.h>
 #include <nccl.h>
+#include <algorithm>
 #include <cstring>
 
 using namespace cgtb;
@@ -33,6 +34,32 @@ bool sym(F& f, const char* name) {
   f = (F)dlsym(g.handle, name);
   if (!f) fail("NCCL library lacks symbol %s", name);
   return f != nullptr;
+}
+}  // namespace
+
+// Many small gradients: one collective on a packed copy instead of one per tensor. A group of k small
+// all-reduces runs as k latency-bound rounds (8 tensors, 0.33 MB in all: the eight-GPU step lost 115 us
+// to them); packed, it is one round plus two copy kernels. Words are 4 bytes (a float64 tensor is two
+// words per element), tensor t occupies words [off[t], off[t+1]) of the packed buffer.
+namespace {
+constexpr int kPackMax = 32;
+constexpr long kPackLimitBytes = 4L << 20;
+struct PackArgs {
+  const uint32_t* src[kPackMax];
+  uint32_t* dst[kPackMax];
+  long off[kPackMax + 1];
+  int n;
+};
+// dir 0: tensors -> packed; dir 1: packed -> result tensors
+__global__ void pack_kernel(const PackArgs a, uint32_t* __restrict__ flat, int dir) {
+  const long total = a.off[a.n];
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    int t = 0;
+    while (t + 1 < a.n && i >= a.off[t + 1]) ++t;
+    const long j = i - a.off[t];
+    if (dir == 0) flat[i] = a.src[t][j];
+    else a.dst[t][j] = flat[i];
+  }
 }
 }  // namespace
 
@@ -108,6 +135,28 @@ CGTB_API int cgtb_allreduce_sum(int dtype, int n, const void* const* in, void* c
     for (int i = 0; i < n; ++i)
       if (in[i] != out[i])
         CGTB_CUDA_TRY(cudaMemcpyAsync(out[i], in[i], (size_t)counts[i] * esize, cudaMemcpyDeviceToDevice, rt().stream));
+    return 0;
+  }
+  long total_elems = 0;
+  for (int i = 0; i < n; ++i) total_elems += counts[i] > 0 ? counts[i] : 0;
+  if (n >= 2 && n <= kPackMax && total_elems > 0 && total_elems * (long)esize <= kPackLimitBytes) {
+    const long wpe = (long)esize / 4;  // words per element
+    PackArgs a;
+    a.n = n;
+    a.off[0] = 0;
+    for (int i = 0; i < n; ++i) {
+      a.src[i] = (const uint32_t*)in[i];
+      a.dst[i] = (uint32_t*)out[i];
+      a.off[i + 1] = a.off[i] + (counts[i] > 0 ? counts[i] : 0) * wpe;
+    }
+    uint32_t* flat = (uint32_t*)scratch((size_t)a.off[n] * 4);
+    if (!flat) return 1;
+    const unsigned blocks = (unsigned)std::min<long>(cgtb_ceil_div(a.off[n], 256), 2L * rt().sm_count);
+    CGTB_LAUNCH(pack_kernel, blocks, 256, 0, a, flat, 0);
+    NCCL_TRY(g.AllReduce(flat, flat, (size_t)total_elems, dt, ncclSum, g.comm, rt().stream));
+    g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+    CGTB_LAUNCH(pack_kernel, blocks, 256, 0, a, flat, 1);
+    CGTB_CHECK_LAUNCH("allreduce pack");
     return 0;
   }
   NCCL_TRY(g.GroupStart());
