@@ -674,6 +674,30 @@ def _update_control_deps(outputs_all, updates):
     return extra
 
 
+def _transport_schedule(outputs_all, updatetargs, node2dev):
+    """Copies at the edges of a step, so that the device work between them is one uninterrupted span (one CUDA
+    graph): (first) the host->device Transports of function arguments, which depend on nothing else, are
+    scheduled before everything; (last) a device->host Transport that is a function output and feeds nothing
+    (the loss) is scheduled after every update."""
+    nodelist = core.topsorted(outputs_all)
+    has_children = set()
+    for node in nodelist:
+        for p in node.parents:
+            has_children.add(p)
+    first, last = [], []
+    out_set = set(outputs_all)
+    for node in nodelist:
+        if node.is_input() or not isinstance(node.op, core.Transport):
+            continue
+        src = node.parents[0]
+        if src.is_argument() and node2dev[node].devtype == "gpu":
+            first.append(node)
+        elif (node in out_set and node not in has_children and node not in updatetargs and node2dev[node].devtype == "cpu"
+              and node2dev[src].devtype == "gpu"):
+            last.append(node)
+    return first, last
+
+
 def topsorted_shapes_first(outputs, node2shape, extra_parents=None):
     """Topological order in which the shape components of a byref node precede it
     (cgt/compilation.py:109-148), plus the control dependencies in `extra_parents`."""
@@ -878,7 +902,10 @@ def run_compilation_pipeline(inputs, outputs, updates, givens):
 
     updates_simple = list(zip(updatesrcs, updatetargs_simple))
     extra = _update_control_deps(all_out, updates_simple)
-    nodes_sorted = topsorted_shapes_first(all_out, node2shape, extra)
+    first, last = _transport_schedule(all_out, updatetargs_simple, node2dev)
+    for node in last:
+        extra[node] = extra.get(node, []) + [t for t in updatetargs_simple if t is not node]
+    nodes_sorted = topsorted_shapes_first(first + all_out, node2shape, extra)
     const_nodes = compute_const_nodes(nodes_sorted)
     node2memowner = determine_memowner(nodes_sorted, updates_simple, node2dev, outputs_simple, node2shape, const_nodes)
     written_into = set(owner for (n, owner) in node2memowner.items() if owner is not n)
