@@ -677,24 +677,32 @@ def _update_control_deps(outputs_all, updates):
 def _transport_schedule(outputs_all, updatetargs, node2dev):
     """Copies at the edges of a step, so that the device work between them is one uninterrupted span (one CUDA
     graph): (first) the host->device Transports of function arguments, which depend on nothing else, are
-    scheduled before everything; (last) a device->host Transport that is a function output and feeds nothing
-    (the loss) is scheduled after every update."""
+    scheduled before everything; (last) a device->host Transport whose descendants all live on the host and
+    include no update (the loss and the host arithmetic that finishes it) is scheduled after every update."""
     nodelist = core.topsorted(outputs_all)
-    has_children = set()
+    children = defaultdict(list)
     for node in nodelist:
         for p in node.parents:
-            has_children.add(p)
+            children[p].append(node)
+    targs = set(updatetargs)
     first, last = [], []
-    out_set = set(outputs_all)
     for node in nodelist:
         if node.is_input() or not isinstance(node.op, core.Transport):
             continue
         src = node.parents[0]
         if src.is_argument() and node2dev[node].devtype == "gpu":
             first.append(node)
-        elif (node in out_set and node not in has_children and node not in updatetargs and node2dev[node].devtype == "cpu"
-              and node2dev[src].devtype == "gpu"):
-            last.append(node)
+        elif node2dev[node].devtype == "cpu" and node2dev[src].devtype == "gpu" and node not in targs:
+            ok, seen, stack = True, set(), list(children[node])
+            while stack and ok:
+                c = stack.pop()
+                if c in seen:
+                    continue
+                seen.add(c)
+                ok = node2dev[c].devtype == "cpu" and c not in targs
+                stack.extend(children[c])
+            if ok:
+                last.append(node)
     return first, last
 
 

@@ -471,13 +471,23 @@ CGTB_API int cgtb_interp_run(cgtbInterp* it, cgtbObject* args_obj, cgtbObject** 
   it->last_graph_launches = 0;
   long mallocs0 = device_malloc_count();
   int rc = 0;
-  for (auto& s : it->spans) {
-    rc = run_span(it, s);
+  // The before-sync hook (host work that should overlap this run's device work, e.g. queueing the next batch's
+  // upload) runs as soon as the last span that queues device work or a copy has been issued: the host-only
+  // spans after it (arithmetic on a scalar that was copied back) wait for the stream.
+  long last_queueing = -1;
+  for (size_t i = 0; i < it->spans.size(); ++i)
+    if (it->spans[i].barrier || it->spans[i].n_device > 0) last_queueing = (long)i;
+  bool hooked = false;
+  for (size_t i = 0; i < it->spans.size(); ++i) {
+    rc = run_span(it, it->spans[i]);
     if (rc) break;
+    if ((long)i == last_queueing && it->before_sync) {
+      it->before_sync(it->before_sync_ctx);
+      hooked = true;
+    }
   }
   it->args = nullptr;
-  // host work that should overlap this run's device work (e.g. queueing the next batch's upload)
-  if (!rc && it->before_sync) it->before_sync(it->before_sync_ctx);
+  if (!rc && !hooked && it->before_sync) it->before_sync(it->before_sync_ctx);
   if (rt().ready) {
     cudaError_t e = cudaStreamSynchronize(rt().stream);
     it->host_pending = false;
