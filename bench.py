@@ -91,7 +91,7 @@ class ClockSampler(object):
         return out
 
 
-# ------------------------------------------------------------------------------------------------
+# algorithmic bytes / flops per instruction: every operand and result of an Op crosses HBM once; 2MNK flops per product
 # algorithmic bytes / flops per instruction (per-op figures stated in DESIGN.md)
 # ------------------------------------------------------------------------------------------------
 def _nbytes(shape, dtype):
