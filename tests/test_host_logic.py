@@ -259,6 +259,38 @@ def test_odd_column_rows_are_padded_for_both_products():
     assert [n for n in core.topsorted(o2 + u2) if not n.is_input() and isinstance(n.op, im2col_ops.ConvWgrad)] == wg
 
 
+@pytest.mark.parametrize("name,kw", [("cifar", dict(batch=4)), ("mlp", dict(batch=8)), ("lstm", dict(seq_len=3, batch=2))])
+def test_edge_copies_are_scheduled_at_the_edges(name, kw):
+    """compilation._transport_schedule: the uploads of the function arguments come before every device Op, and a
+    copy-back whose descendants are all host-side (the loss) comes after every update, so the device work between
+    them is one span. A copy-back that an update depends on (the LSTM's gradient norm) stays where it is."""
+    cfg = configs.BUILDERS[name](**kw)
+    outs, srcs, targs, analysis = compilation.simplify_for_execution([cfg.loss] + list(cfg.extra_outputs), cfg.updates)
+    all_out = outs + targs
+    nodelist = core.topsorted(all_out)
+    node2dev = compilation.determine_devices(nodelist, dict(zip(targs, srcs)))
+    compilation.add_transports(nodelist, node2dev, analysis["node2shape"])
+    first, last = compilation._transport_schedule(all_out, targs, node2dev)
+    assert first and all(t.parents[0].is_argument() for t in first)
+    assert last and all(node2dev[t].devtype == "cpu" for t in last)
+    extra = compilation._update_control_deps(all_out, list(zip(srcs, targs)))
+    for node in last:
+        extra[node] = extra.get(node, []) + [t for t in targs if t is not node]
+    order = compilation.topsorted_shapes_first(first + all_out, analysis["node2shape"], extra)
+    assert len(order) == len(set(order)) and set(nodelist) <= set(order)
+    pos = {n: i for (i, n) in enumerate(order)}
+    for node in order:                                   # still a topological order
+        assert all(pos[p] < pos[node] for p in node.parents)
+    device_ops = [n for n in order if not n.is_input() and n in node2dev and node2dev[n].devtype == "gpu" and not isinstance(n.op, core.Transport)
+                  and n.op.return_type == "byref"]
+    assert max(pos[t] for t in first) < min(pos[n] for n in device_ops)
+    assert min(pos[t] for t in last) > max(pos[t] for t in targs)
+    if name == "lstm":   # the clipping factor is computed on the host from a copied-back norm and feeds the updates
+        mid = [n for n in order if not n.is_input() and isinstance(n.op, core.Transport) and n in node2dev and node2dev[n].devtype == "cpu"
+               and n not in last]
+        assert mid and all(pos[n] < max(pos[t] for t in targs) for n in mid)
+
+
 def test_update_is_ordered_after_other_readers_of_the_variable():
     """Updates listed last-layer-first: the dgrad product that still needs the old last-layer weight
     must be scheduled before the in-place update of that weight."""
