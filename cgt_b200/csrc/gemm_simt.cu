@@ -194,8 +194,7 @@ int sgemm_small(int tA, int tB, long P, long M, long N, long K, const float* A, 
   if (lanes == 32) CGTB_LAUNCH(sgemm_small_kernel<32>, grid, 256, 0, tA, tB, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC);
   else if (lanes == 8) CGTB_LAUNCH(sgemm_small_kernel<8>, grid, 256, 0, tA, tB, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC);
   else CGTB_LAUNCH(sgemm_small_kernel<1>, grid, 256, 0, tA, tB, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC);
-  cudaError_t e = cudaPeekAtLastError();
-  if (e != cudaSuccess) return fail("sgemm_small launch failed: %s", cudaGetErrorString(e));
+  CGTB_CHECK_LAUNCH("sgemm_small");
   return 0;
 }
 

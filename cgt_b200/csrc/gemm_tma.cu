@@ -119,11 +119,12 @@ __device__ __forceinline__ void convert_kmajor(const unsigned char* raw, unsigne
 
 // K-major X tile that the MMA reads in place as the hi operand (the tensor core uses the upper 19 bits
 // of each fp32 word): only lo = x - (x with its 13 low mantissa bits cleared) is computed and stored.
-// No guard is needed: a non-finite x stays non-finite in the raw tile, whatever its lo becomes.
 // The difference is exact (at most 13 significant bits) and is stored unmasked: the tensor core cuts its low
-// bits itself, exactly as it cuts those of x.
+// bits itself, exactly as it cuts those of x. A non-finite x (exponent field all ones) gets lo = 0: inf - inf
+// would be NaN and turn a product that fp32 arithmetic gives as +-inf into NaN; a NaN stays NaN through x itself.
 __device__ __forceinline__ uint32_t lo_of(uint32_t b) {
-  return __float_as_uint(__fadd_rn(__uint_as_float(b), -__uint_as_float(b & 0xFFFFE000u)));
+  const uint32_t d = __float_as_uint(__fadd_rn(__uint_as_float(b), -__uint_as_float(b & 0xFFFFE000u)));
+  return ((b & 0x7F800000u) == 0x7F800000u) ? 0u : d;
 }
 __device__ __forceinline__ void convert_kmajor_lo(const unsigned char* raw, unsigned char* lo, int nchunks, int tid) {
   for (int c0 = tid; c0 < nchunks; c0 += 4 * kConvThreads) {

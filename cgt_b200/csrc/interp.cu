@@ -325,7 +325,10 @@ static uint64_t key_of_object(uint64_t h, cgtObject* o, int dev) {
   if (o->kind() == cgtObject::ArrayKind) {
     cgtArray* a = (cgtArray*)o;
     h = mix(h, (uint64_t)(uintptr_t)a->data());
-    h = mix(h, (uint64_t)a->size());
+    // a captured graph bakes shape-derived launch parameters into its nodes, and the pool can hand the same block
+    // to a differently shaped array of equal size: the extents and the dtype are part of the key
+    h = mix(h, ((uint64_t)a->ndim() << 8) | (uint64_t)a->dtype());
+    for (int d = 0; d < a->ndim(); ++d) h = mix(h, (uint64_t)a->shape()[d]);
     if (a->devtype() == cgtCPU && a->nbytes() <= 64 && a->data()) {  // small host operand read at launch time
       uint64_t buf[8] = {0};
       memcpy(buf, a->data(), (size_t)a->nbytes());

@@ -370,12 +370,24 @@ __global__ void __launch_bounds__(32 * G) reduce_rk_kernel(int kind, int R0, int
 }
 
 template <typename T>
+__global__ void reduce_identity_kernel(int kind, long n, T* __restrict__ out) {
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) out[i] = red_init<T>(kind);
+}
+
+template <typename T>
 static int reduce_launch(int kind, int ndim, const long* shape, const int* reduced, const T* in, T* out) {
   ReduceGeom g;
   g.nk = g.nr = 0;
   long stride[CGTB_MAX_NDIM], acc = 1;
   for (int i = ndim - 1; i >= 0; --i) { stride[i] = acc; acc *= shape[i]; }
-  if (acc == 0) return 0;
+  if (acc == 0) {
+    // nothing to reduce: every kept element is the identity of the operation (the reference's loop leaves the
+    // initial value in place, cgt/core.py:1663-1685)
+    long kept = 1;
+    for (int i = 0; i < ndim; ++i) if (!reduced[i]) kept *= shape[i];
+    if (kept > 0) CGTB_LAUNCH(reduce_identity_kernel<T>, (unsigned)std::min<long>(cgtb_ceil_div(kept, 256), 4096), 256, 0, kind, kept, out);
+    return 0;
+  }
   long osize = 1, rsize = 1;
   // merge adjacent axes of the same class: axis i (outer) and i+1 (inner) merge when both are in the
   // same class, since then stride[i] == shape[i+1]*stride[i+1]

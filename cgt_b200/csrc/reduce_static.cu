@@ -51,9 +51,17 @@ CGTB_API int cgtb_reduce_rkr_f32_static(int kind, long R0, long K, long R1, cons
   if (R0 >= (1L << 30) || R1 >= (1L << 30))
     return fail("cgtb_reduce_rkr_f32_static: R0=%ld / R1=%ld beyond the maximum of 2^30-1; use cgtb_reduce", R0, R1);
   if (K == 0) return 0;
+  if (R1 == 1 && R0 > 1)
+    return fail("cgtb_reduce_rkr_f32_static: R1 == 1 (a column reduction [R0, K]) is not split and needs no scratch; use cgtb_reduce");
   const int dev = rt().device;
   if (dev < 0 || dev >= kMaxDevices) return fail("cgtb_reduce_rkr_f32_static: device index %d not supported", dev);
   if (!g_partials_addr[dev]) {
+    // the symbol resolves for the calling thread's CURRENT device: it must be the one the runtime is bound to
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess || cur != dev) {
+      cudaError_t es = cudaSetDevice(dev);
+      if (es != cudaSuccess) return fail("cgtb_reduce_rkr_f32_static: cudaSetDevice(%d) failed: %s", dev, cudaGetErrorString(es));
+    }
     float* p = nullptr;
     cudaError_t e = cudaGetSymbolAddress((void**)&p, g_reduce_static_partials);
     if (e != cudaSuccess || !p)

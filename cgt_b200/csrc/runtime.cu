@@ -498,3 +498,14 @@ CGTB_API int cgtb_l2_flush(void) {
   CGTB_CUDA_TRY(cudaMemsetAsync(buf, 0, kBytes, g_rt.stream));
   return 0;
 }
+
+// A launch that the CUDA runtime refuses on the host (2048 threads per block exceed the limit of 1024): nothing
+// reaches the GPU. Exists so that a test can check that such a refusal is reported once, with its own name, and
+// does not stay behind as the process's "last error" for later, healthy calls to trip over.
+static __global__ void selftest_noop_kernel(int* p) { if (p) *p = 0; }
+CGTB_API int cgtb_selftest_refused_launch(void) {
+  if (!require_runtime("cgtb_selftest_refused_launch")) return 1;
+  CGTB_LAUNCH(selftest_noop_kernel, 1, 2048, 0, (int*)nullptr);
+  CGTB_CHECK_LAUNCH("selftest_refused_launch");
+  return 0;
+}

@@ -67,7 +67,7 @@ int sgemm_tc_check();
 
 #define CGTB_CHECK_LAUNCH(name)                                                                  \
   do {                                                                                           \
-    cudaError_t e_ = cudaPeekAtLastError();                                                      \
+    cudaError_t e_ = cudaGetLastError(); /* reads AND clears: a refused launch must not poison later calls */ \
     if (e_ != cudaSuccess) return cgtb::fail("%s launch failed: %s", name, cudaGetErrorString(e_)); \
   } while (0)
 

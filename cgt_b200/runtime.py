@@ -42,7 +42,7 @@ def _declare(lib):
         "cgtb_kernel_launches": (cl, []), "cgtb_sm_count": (ci, []),
         "cgtb_event_new": (vp, []), "cgtb_event_record": (ci, [vp]),
         "cgtb_event_elapsed_ms": (ci, [vp, vp, ctypes.POINTER(ctypes.c_float)]), "cgtb_event_free": (None, [vp]),
-        "cgtb_l2_flush": (ci, []),
+        "cgtb_l2_flush": (ci, []), "cgtb_selftest_refused_launch": (ci, []),
         "cgtb_prefetch_h2d": (ci, [vp, vp, cl]),
         "cgtb_prefetch_begin": (ci, [ci]), "cgtb_prefetch_mark": (ci, [ci]), "cgtb_prefetch_join": (ci, [ci]),
         "cgtb_prefetch_release": (ci, [ci]),

@@ -42,6 +42,10 @@ int cgtb_event_record(void* event);
 int cgtb_event_elapsed_ms(void* start, void* stop, float* ms); /* waits for `stop` */
 void cgtb_event_free(void* event);
 int cgtb_l2_flush(void);                   /* memset of a 256 MiB device buffer */
+/* Asks the CUDA runtime for a launch it refuses on the host (too many threads per block; nothing reaches the GPU)
+ * and returns that failure. For tests of the error model: the refusal is reported by this call only and later
+ * calls are unaffected. No counterpart in the reference (include/cgt_cuda.h:11-16 prints CUDA errors and goes on). */
+int cgtb_selftest_refused_launch(void);
 
 /* Raw memory. devtype: 0 host (pinned), 1 device. (src/cgt_common.cpp:110-153) */
 void* cgtb_alloc(int devtype, long nbytes);
@@ -230,11 +234,12 @@ int cgtb_reduce(int kind, int dtype, int ndim, const long* shape, const int* red
 /* No counterpart in the reference. Sum (kind 0) or Max (kind 1) of a float32 array viewed as
  * [R0, K, R1] over R0 and R1, out[K], for callers that must not allocate device or host memory at call
  * time (latency-critical callbacks, processes whose device memory belongs to another allocator).
- * Same bits as cgtb_reduce on that layout. The partial results live in one fixed 128 KiB array in
+ * Same bits as cgtb_reduce on that layout (R1 > 1; a pure column reduction, R1 == 1 with R0 > 1, is refused: it
+ * is not split and needs no scratch, use cgtb_reduce). The partial results live in one fixed 128 KiB array in
  * device memory that every call shares: the first call per device looks its address up (set-up work,
  * do it before any stream capture); calls that overlap in time race on the array, calls issued in
  * sequence on the runtime stream do not; nothing in the array has to be cleared between calls.
- * Refused with an error: K > CGTB_REDUCE_STATIC_MAX_K, R0 or R1 >= 2^30. */
+ * Refused with an error: K > CGTB_REDUCE_STATIC_MAX_K, R0 or R1 >= 2^30, R1 == 1 with R0 > 1. */
 #define CGTB_REDUCE_STATIC_MAX_K 8192
 int cgtb_reduce_rkr_f32_static(int kind, long R0, long K, long R1, const float* in, float* out);
 long cgtb_reduce_static_max_k(void);

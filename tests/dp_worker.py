@@ -31,6 +31,7 @@ for step in range(3):
     full = build(batch=per_rank * world).batch(step)  # the global batch, same on every rank
     shard = parallel.shard(full, rank, world)
     losses.append(float(f(*shard)[0]))
+    parallel.check_health()  # raises (and ends this rank) when the communicator reported an asynchronous error
 params = [p.op.get_value() for p in cfg.params] if on_gpu else [f.get_value(p) for p in cfg.params]
 out = {"rank": rank, "world": world, "losses": losses, "n_allreduce": n_allreduce,
        "checksum": [float(np.abs(p).sum()) for p in params], "first": [float(p.ravel()[0]) for p in params]}

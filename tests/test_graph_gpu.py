@@ -97,6 +97,21 @@ def test_shape_change_recaptures(rt):
         np.testing.assert_allclose(f(xv), np.tanh(xv @ w.op.get_value()).sum(axis=1), rtol=1e-4, atol=1e-5)
 
 
+def test_equal_size_shapes_do_not_share_a_captured_graph(rt):
+    """Two input shapes with the same number of elements: the pool hands the same blocks back, so buffer addresses
+    and sizes repeat while the extents differ. A captured graph holds launch parameters derived from the extents and
+    must not be replayed for the other shape."""
+    x = cgt.matrix("x")
+    y = cgt.tanh(x).sum(axis=1)
+    f = cgt.function([x], y)
+    rs = np.random.RandomState(5)
+    for shape in [(4, 6)] * 4 + [(6, 4)] + [(4, 6)] + [(6, 4)] * 4 + [(4, 6)] * 2 + [(2, 12), (12, 2), (2, 12)]:
+        xv = rs.randn(*shape).astype("f4")
+        got = f(xv)
+        assert got.shape == (shape[0],)
+        np.testing.assert_allclose(got, np.tanh(xv).sum(axis=1), rtol=1e-4, atol=1e-5)
+
+
 def test_no_cpu_fallback(rt):
     """Tensor work placed on the host is refused, not emulated."""
     with cgt.scoped_update_config(default_device=cgt.Device("cpu", 0)):

@@ -400,6 +400,9 @@ def test_sgemm_non_finite_inputs_stay_non_finite(rt, impl):
     bad[[3, 7, 9, 200]] = True
     assert not np.isfinite(got[bad]).any()
     assert np.isnan(got[7]).all() and np.isnan(got[9]).all()
+    # an infinite entry gives an infinite product of the sign fp32 arithmetic gives, not NaN (inf - inf in the split)
+    assert np.array_equal(got[3], np.where(B[:, 5] > 0, np.inf, -np.inf).astype("f4"))
+    assert np.array_equal(got[200], np.where(B[:, 63] > 0, -np.inf, np.inf).astype("f4"))
     np.testing.assert_allclose(got[~bad], (A[~bad].astype("f8") @ B.astype("f8").T), rtol=1e-4, atol=1e-4)
 
 
@@ -615,6 +618,16 @@ def test_fused_elwise_matches_separate_kernels(rt, shape):
     want_mask = (t >= 0)
     assert np.array_equal(om.get().astype(bool), want_mask)
     np.testing.assert_allclose(o2.get(), t * want_mask, rtol=RTOL, atol=ATOL)
+
+
+def test_reduce_over_an_empty_axis_gives_the_identity(rt):
+    """Sum / Max over an axis of extent 0: every kept element is the operation's initial value (the reference's
+    loop never runs, cgt/core.py:1663-1685, 1708, 1737)."""
+    x = Dev(shape=(1,), dtype="f4")
+    for (kind, want) in ((0, 0.0), (1, -np.finfo("f4").max)):
+        out = Dev(np.full((4, 1, 3), 9.0, "f4"))
+        call("cgtb_reduce", kind, code("f4"), 3, longs((4, 0, 3)), ints((0, 1, 0)), x.ptr, out.ptr)
+        assert np.array_equal(out.get(), np.full((4, 1, 3), want, "f4"))
 
 
 def test_empty_inputs(rt):

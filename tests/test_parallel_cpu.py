@@ -36,10 +36,20 @@ def test_two_ranks_match_single_process(tmp_path):
         procs.append(subprocess.Popen([sys.executable, osp.join(HERE, "dp_worker.py")], env=env, stdout=subprocess.PIPE,
                                       stderr=subprocess.PIPE, text=True))
     outs = []
-    for p in procs:
-        so, se = p.communicate(timeout=240)
-        assert p.returncode == 0, se[-2000:]
-        outs.append(json.loads(so.strip().splitlines()[-1]))
+    try:
+        for p in procs:
+            so, se = p.communicate(timeout=240)
+            assert p.returncode == 0, se[-3000:]
+            outs.append(json.loads(so.strip().splitlines()[-1]))
+    finally:
+        # a rank that outlives the test (a stalled collective, a peer that failed first) must not keep a device
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+            try:
+                p.wait(timeout=30)
+            except subprocess.TimeoutExpired:
+                pass
     assert [o["rank"] for o in outs] == [0, 1] and all(o["world"] == 2 for o in outs)
     assert all(o["n_allreduce"] == 1 for o in outs)  # one grouped exchange for all parameter gradients
     # replicas stay bit-identical: same averaged gradients applied to the same parameters

@@ -37,10 +37,20 @@ def test_two_gpu_ranks_match_one_gpu(rt, tmp_path, config):
         procs.append(subprocess.Popen([sys.executable, osp.join(HERE, "dp_worker.py")], env=env, stdout=subprocess.PIPE,
                                       stderr=subprocess.PIPE, text=True))
     outs = []
-    for p in procs:
-        so, se = p.communicate(timeout=300)
-        assert p.returncode == 0, se[-3000:]
-        outs.append(json.loads(so.strip().splitlines()[-1]))
+    try:
+        for p in procs:
+            so, se = p.communicate(timeout=300)
+            assert p.returncode == 0, se[-3000:]
+            outs.append(json.loads(so.strip().splitlines()[-1]))
+    finally:
+        # a rank that outlives the test (a stalled collective, a peer that failed first) must not keep a device
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+            try:
+                p.wait(timeout=30)
+            except subprocess.TimeoutExpired:
+                pass
     assert all(o["n_allreduce"] == 1 for o in outs)
     p0 = np.load(str(tmp_path / "params") + ".0.npz")
     p1 = np.load(str(tmp_path / "params") + ".1.npz")

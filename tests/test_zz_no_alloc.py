@@ -84,6 +84,9 @@ def test_static_reduce_allocates_nothing_and_refuses_oversize(rt):
     assert "beyond the maximum" in msg and str(kmax) in msg
     rc = L.cgtb_reduce_rkr_f32_static(0, 1 << 30, 2, 4, x.ptr, out.ptr)
     assert rc != 0 and "beyond the maximum" in runtime.last_error()
+    # a pure column reduction is not split, needs no scratch and is served by cgtb_reduce only
+    rc = L.cgtb_reduce_rkr_f32_static(0, 16, 8, 1, x.ptr, out.ptr)
+    assert rc != 0 and "use cgtb_reduce" in runtime.last_error()
     # an error leaves the entry point usable
     call("cgtb_reduce_rkr_f32_static", 1, 4, 8, 64, x.ptr, out.ptr)
     assert np.array_equal(out.get(), np.ones((8,), "f4"))
