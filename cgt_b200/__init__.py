@@ -19,5 +19,6 @@ from .core import (grad, get_config, update_config, simplify, reset_config, Devi
                    infer_shape, count_nodes)
 from .compilation import function, numeric_eval, profiler  # noqa: E402
 from . import nn, distributions  # noqa: E402
+from .checkpoint import save_state, load_state, state_variables, ParamCollection  # noqa: E402,F401
 
 get_config()

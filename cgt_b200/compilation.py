@@ -884,6 +884,7 @@ def create_execution_graph(inputs, nodes_sorted, node2shape, node2memowner, node
             instrs[-1].in_dtypes = [p.dtype for p in node.parents]
             instrs[-1].out_shape = _static_shape(node2shape[node]) if node in node2shape else None
             instrs[-1].out_dtype = node.dtype
+            instrs[-1].out_dtypes = [t.dtype for t in node.typ] if is_tuple(node) else None
         node2memloc[node] = write_loc
     return ExecutionGraph(instrs, len(inputs), counter.count), node2memloc
 
@@ -1184,8 +1185,9 @@ class TranslationUnit(object):
                 cmd = "c++ %s %s -c -o %s.o %s" % (info["CPP_FLAGS"], srcpath, srcpath, info["INCLUDES"])
             elif lang == "cuda":
                 srcpath = osp.join(cache, prefix + "_%i.cu" % i)
-                cmd = ("nvcc %s -c -o %s.o -gencode arch=compute_100a,code=sm_100a -lineinfo -O3 -std=c++17 "
-                       "-Xcompiler -fPIC %s" % (srcpath, srcpath, info["INCLUDES"]))
+                from .build import _nvcc
+                cmd = ("%s %s -c -o %s.o -gencode arch=compute_100a,code=sm_100a -lineinfo -O3 -std=c++17 "
+                       "-Xcompiler -fPIC %s" % (_nvcc(), srcpath, srcpath, info["INCLUDES"]))
             else:
                 raise NotImplementedError(lang)
             with open(srcpath, "w") as fh:

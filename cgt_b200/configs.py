@@ -34,6 +34,12 @@ class Config(object):
     def batch(self, seed=0):
         return self.batch_fn(np.random.RandomState(seed))
 
+    def state_variables(self):
+        """Every shared variable of the training step (parameters, optimizer slots, step counters): what a
+        checkpoint has to hold."""
+        from . import checkpoint
+        return checkpoint.state_variables(self.updates, [self.loss] + self.extra_outputs, self.params)
+
 
 class _seeded(object):
     """Weight initialisers draw from numpy's global RNG (as the reference's do); seed it locally."""

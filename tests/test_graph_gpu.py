@@ -7,8 +7,10 @@ parameters within 1e-3 of the oracle's after those steps relative to their scale
 import numpy as np
 import pytest
 
+import ctypes
+
 import cgt_b200 as cgt
-from cgt_b200 import configs, nn
+from cgt_b200 import configs, core, nn
 from oracle import cpu_backend
 
 pytestmark = pytest.mark.gpu
@@ -259,3 +261,92 @@ def test_conv_grad_input_substitution(rt):
     np.testing.assert_allclose(res[True][1], res[False][1], rtol=1e-4)
     for (a, b) in zip(res[True][2], res[False][2]):
         np.testing.assert_allclose(a, b, rtol=1e-3, atol=1e-5)
+
+
+@pytest.mark.parametrize("name", ["cifar", "vae"])
+@pytest.mark.parametrize("graphs", [False, True])
+def test_checkpoint_resume_is_bit_exact(rt, tmp_path, name, graphs):
+    """save -> 5 steps, reload -> the same 5 steps: losses and every shared variable (parameters, Adam slots and step
+    counter for the VAE) identical bit for bit, eagerly and from captured CUDA graphs. The reload writes into the
+    variables' existing device buffers, so the captured graphs stay valid."""
+    from cgt_b200 import checkpoint
+    with cgt.scoped_update_config(use_cuda_graphs=graphs):
+        cfg = configs.BUILDERS[name](**SMALL[name])
+        f = cfg.compile()
+        variables = cfg.state_variables()
+        batches = [cfg.batch(seed) for seed in range(3)]
+        for i in range(4):   # leave the initial state (and reach graph replay) before the checkpoint
+            f(*batches[i % 3])
+        path = str(tmp_path / "ckpt.npz")
+        checkpoint.save_state(path, variables, extra={"step": 4})
+        first = [np.asarray(f(*batches[i % 3])[0]).copy() for i in range(4, 9)]
+        state1 = [v.op.get_value() for v in variables]
+        assert checkpoint.load_state(path, variables) == {"step": 4}
+        second = [np.asarray(f(*batches[i % 3])[0]).copy() for i in range(4, 9)]
+        state2 = [v.op.get_value() for v in variables]
+    for (a, b) in zip(first, second):
+        assert np.array_equal(a, b)
+    for (a, b) in zip(state1, state2):
+        assert np.array_equal(a, b)
+    assert not np.array_equal(first[0], first[4])  # the steps did change the model
+
+
+class ScaleShiftCuda(core.Op):
+    """A user-defined Op that brings its own CUDA source (reference contract: NativeCompileInfo with extra_srcs =
+    [SrcFile("cuda", ...)], $function / $closure templating, cgt/core.py:734-769; the pattern of
+    cgt/tests/test_par_interp.py:11-27 and test_multi_output.py:32-58 with devtype "gpu")."""
+    available_impls = ("native_gpu",)
+
+    def __init__(self, scale, shift):
+        self.scale, self.shift = float(scale), float(shift)
+
+    def typ_apply(self, input_types):
+        return input_types[0]
+
+    def shp_apply(self, inputs):
+        return cgt.shape(inputs[0])
+
+    def get_native_compile_info(self, input_types, devtype):
+        assert devtype == "gpu"
+        code = r"""
+            extern "C" void ${function}_launch(const float* x, float* y, long n, float a, float b, void* stream);
+            CGT_EXPORT_C void $function($closure* cl, cgtArray** reads, cgtArray* write) {
+                ${function}_launch((const float*)reads[0]->data(), (float*)write->data(), (long)reads[0]->size(),
+                                   cl->scale, cl->shift, cgt_current_stream());
+            }"""
+        cuda = r"""
+            #include <cuda_runtime.h>
+            __global__ void ${function}_kernel(const float* x, float* y, long n, float a, float b) {
+                for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x)
+                    y[i] = __fmaf_rn(a, x[i], b);
+            }
+            extern "C" void ${function}_launch(const float* x, float* y, long n, float a, float b, void* stream) {
+                if (n <= 0) return;
+                int blocks = (int)((n + 255) / 256);
+                if (blocks > 1184) blocks = 1184;
+                ${function}_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(x, y, n, a, b);
+            }"""
+        return core.NativeCompileInfo(code, closure_triples=[("scale", ctypes.c_float, self.scale), ("shift", ctypes.c_float, self.shift)],
+                                      extra_srcs=[core.SrcFile("cuda", cuda)])
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_user_op_with_cuda_source_runs_on_the_gpu(rt, graphs):
+    """The Op's CUDA source is compiled by nci2callable (nvcc, sm_100a) into the hash-keyed cache, the node is placed on
+    the GPU, its kernel is launched on the runtime stream and therefore lands inside the captured span."""
+    with cgt.scoped_update_config(use_cuda_graphs=graphs):
+        x = cgt.matrix("x", fixed_shape=(37, 129))
+        h = core.Result(ScaleShiftCuda(2.5, -1.0), [cgt.tanh(x)])
+        y = (h * h).sum(axis=1)
+        f = cgt.function([x], [y, h])
+        assert any("ScaleShiftCuda" in repr(i) and i.write_loc.devtype == "gpu" for i in f.eg.instrs if hasattr(i, "op"))
+        rs = np.random.RandomState(2)
+        for _ in range(5):
+            xv = rs.randn(37, 129).astype("f4")
+            (gy, gh) = f(xv)
+            want_h = np.float32(2.5) * np.tanh(xv) + np.float32(-1.0)
+            np.testing.assert_allclose(gh, want_h, rtol=1e-5, atol=1e-6)
+            np.testing.assert_allclose(gy, (want_h.astype("f8") ** 2).sum(axis=1), rtol=1e-4)
+        if graphs:
+            st = f.stats()
+            assert st["segments_captured"] >= 1 and st["last_graph_launches"] >= 1, st

@@ -385,3 +385,41 @@ def test_config_flags_and_scopes(monkeypatch):
     finally:
         monkeypatch.delenv("CGT_FLAGS")
         core.get_config(True)
+
+
+def test_checkpoint_file_round_trip(tmp_path):
+    """save_state / load_state (the file format over InMemoryData.get_value / set_value, cgt/core.py:569-582) and the
+    flat-vector helper (examples/param_collection.py:37-56), on host-resident values: no GPU needed."""
+    from cgt_b200 import checkpoint, configs
+    cfg = configs.build_vae(batch=4)
+    variables = cfg.state_variables()
+    # parameters, two Adam slots per parameter and the step counter
+    assert len(variables) == 3 * len(cfg.params) + 1
+    assert variables[:len(cfg.params)] == list(cfg.params)
+    rs = np.random.RandomState(0)
+    saved = []
+    for v in variables:
+        val = rs.randn(*v.op.get_shape()).astype(v.dtype)
+        v.op.set_value(val)
+        saved.append(val)
+    path = str(tmp_path / "state.npz")
+    checkpoint.save_state(path, variables, extra={"step": 7, "seed": 3})
+    for v in variables:
+        v.op.set_value(np.zeros(v.op.get_shape(), v.dtype))
+    extra = checkpoint.load_state(path, variables)
+    assert extra == {"step": 7, "seed": 3}
+    for (v, want) in zip(variables, saved):
+        assert np.array_equal(v.op.get_value(), want)
+    # a checkpoint of another model is refused before anything is written
+    other = configs.build_mlp(batch=4)
+    before = [p.op.get_value() for p in other.params]
+    with pytest.raises(ValueError):
+        checkpoint.load_state(path, other.state_variables())
+    for (p, b) in zip(other.params, before):
+        assert np.array_equal(p.op.get_value(), b)
+    pc = checkpoint.ParamCollection(other.params)
+    theta = pc.get_value_flat()
+    assert theta.shape == (pc.get_total_size(),) and pc.num_vars() == len(other.params)
+    pc.set_value_flat(theta * 2)
+    for (p, b) in zip(other.params, before):
+        assert np.array_equal(p.op.get_value(), b * 2)
