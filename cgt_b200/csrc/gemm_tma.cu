@@ -120,11 +120,11 @@ __device__ __forceinline__ void convert_kmajor(const unsigned char* raw, unsigne
 // K-major X tile that the MMA reads in place as the hi operand (the tensor core uses the upper 19 bits
 // of each fp32 word): only lo = x - (x with its 13 low mantissa bits cleared) is computed and stored.
 // The difference is exact (at most 13 significant bits) and is stored unmasked: the tensor core cuts its low
-// bits itself, exactly as it cuts those of x. A non-finite x (exponent field all ones) gets lo = 0: inf - inf
-// would be NaN and turn a product that fp32 arithmetic gives as +-inf into NaN; a NaN stays NaN through x itself.
+// bits itself, exactly as it cuts those of x. Non-finite inputs: a NaN stays NaN through x itself; for an
+// infinite x the split gives non-finite products whose kind is not defined (the cross term inf * y_lo is NaN
+// when y_lo is zero or of the other sign, in every variant of the 3xTF32 scheme), so no guard is spent here.
 __device__ __forceinline__ uint32_t lo_of(uint32_t b) {
-  const uint32_t d = __float_as_uint(__fadd_rn(__uint_as_float(b), -__uint_as_float(b & 0xFFFFE000u)));
-  return ((b & 0x7F800000u) == 0x7F800000u) ? 0u : d;
+  return __float_as_uint(__fadd_rn(__uint_as_float(b), -__uint_as_float(b & 0xFFFFE000u)));
 }
 __device__ __forceinline__ void convert_kmajor_lo(const unsigned char* raw, unsigned char* lo, int nchunks, int tid) {
   for (int c0 = tid; c0 < nchunks; c0 += 4 * kConvThreads) {

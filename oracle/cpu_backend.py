@@ -20,7 +20,10 @@ from . import oracle as O
 
 
 class OracleFunction(object):
-    def __init__(self, inputs, outputs, updates=None, givens=None, impl="port"):
+    def __init__(self, inputs, outputs, updates=None, givens=None, impl="port", wide_sums=False):
+        """wide_sums=True: Sum and Mul22 accumulate in float64 and round once (not what the reference does: an
+        adjudicator for float32 results whose difference comes from the order of a long summation)."""
+        self.wide_sums = wide_sums
         self.single = isinstance(outputs, core.Node)
         outs = [outputs] if self.single else list(outputs)
         updates = compilation._check_updates(updates)
@@ -86,6 +89,8 @@ class OracleFunction(object):
         if isinstance(op, core.Transpose):
             return O.transpose(p[0], op.axes)
         if isinstance(op, core.Sum):
+            if self.wide_sums and np.asarray(p[0]).dtype == np.float32:
+                return np.asarray(p[0], "f8").sum(axis=tuple(op.axes), keepdims=True).astype("f4")
             return O.reduce("sum", p[0], op.axes)
         if isinstance(op, core.Max):
             return O.reduce("max", p[0], op.axes)
@@ -98,6 +103,9 @@ class OracleFunction(object):
         if isinstance(op, core.IncFlatIndices):
             return O.incflat(p[0], p[1], p[2])
         if isinstance(op, core.Mul22):
+            if self.wide_sums and np.asarray(p[0]).dtype == np.float32:
+                a, b = np.asarray(p[0], "f8"), np.asarray(p[1], "f8")
+                return ((a.T if op.tA else a) @ (b.T if op.tB else b)).astype("f4")
             return O.mul22(p[0], p[1], op.tA, op.tB)
         if isinstance(op, core.BatchedMul22):
             return O.batched_mul22(p[0], p[1], op.tA, op.tB)
@@ -149,5 +157,5 @@ def _copy(x):
     return np.array(x, copy=True)
 
 
-def function(inputs, outputs, updates=None, givens=None, impl="port"):
-    return OracleFunction(inputs, outputs, updates=updates, givens=givens, impl=impl)
+def function(inputs, outputs, updates=None, givens=None, impl="port", wide_sums=False):
+    return OracleFunction(inputs, outputs, updates=updates, givens=givens, impl=impl, wide_sums=wide_sums)
