@@ -490,6 +490,88 @@ def fuse_conv_grad_input(outputs, updatetargs, node2shape):
     return _rewire(outputs, updatetargs, replace)
 
 
+def fuse_conv_implicit(outputs, updatetargs, node2shape):
+    """ConvBiasRelu(Reshape(Im2Col(x)), Reshape(W), bias, ...) -> ConvFwdBiasRelu(x NHWC, W as [Cout,kh,kw,Cin], bias, ...)
+    and, for the same column matrix, Mul22{T,N}(Reshape(dy NHWC), Reshape(Im2Col(x))) -> ConvWgradImplicit(x NHWC, dy NHWC),
+    for stride-1 convolutions whose extents the kernels support (input channels a multiple of 32, output channels a
+    multiple of 16, rows of at most 32 pixels). Applies only when every consumer of the column matrix is one of the
+    two, so that Im2Col disappears; the one NCHW -> NHWC transpose of x serves both. Runs after fuse_conv_output."""
+    from .nn_ops import im2col as im2col_ops
+    all_out = list(outputs) + list(updatetargs)
+    nodes = core.topsorted(all_out)
+    children = defaultdict(list)
+    for node in nodes:
+        for par in node.parents:
+            children[par].append(node)
+    out_set = set(all_out)
+    replace = {}
+    for im in nodes:
+        if im.is_input() or not isinstance(im.op, im2col_ops.Im2Col) or im.op.pitch or im.dtype != "f4" or im in out_set:
+            continue
+        info = im.op.info
+        if info.stride_h != 1 or info.stride_w != 1 or len(children[im]) != 1:
+            continue
+        r = children[im][0]
+        if not isinstance(r.op, core.Reshape) or r in out_set or r.ndim != 2 or r.parents[0] is not im:
+            continue
+        x = im.parents[0]
+        x_s = _static_shape(node2shape[x]) if x in node2shape else None
+        im_s = _static_shape(node2shape[im]) if im in node2shape else None
+        if x_s is None or im_s is None or len(x_s) != 4:
+            continue
+        (B, Cin, H, W) = x_s
+        (_b, Ho, Wo, Z) = im_s
+        if Cin % 32 != 0 or Wo > 32 or Z != Cin * info.kernel_h * info.kernel_w:
+            continue
+        fwd, wgrads, ok = [], [], bool(children[r])
+        for c in children[r]:
+            if isinstance(c.op, im2col_ops.ConvBiasRelu) and c.parents[0] is r and r not in c.parents[1:]:
+                w2 = c.parents[1]
+                shp = _static_shape(node2shape[c][0]) if c in node2shape else None
+                if (not w2.is_input() and isinstance(w2.op, core.Reshape) and w2.parents[0].ndim == 4 and shp is not None
+                        and _static_shape(node2shape[w2.parents[0]]) == (shp[1], Cin, info.kernel_h, info.kernel_w)
+                        and shp == (B, shp[1], Ho, Wo) and _conv_channels_ok(shp[1])):
+                    fwd.append(c)
+                    continue
+            if (isinstance(c.op, core.Mul22) and c.op.tA and not c.op.tB and c.parents[1] is r and c.parents[0] is not r
+                    and c.dtype == "f4"):
+                a = c.parents[0]
+                if not a.is_input() and isinstance(a.op, core.Reshape) and a.parents[0].ndim == 4 and a.parents[0].dtype == "f4":
+                    dy_s = _static_shape(node2shape[a.parents[0]]) if a.parents[0] in node2shape else None
+                    if dy_s is not None and dy_s[:3] == (B, Ho, Wo) and _conv_channels_ok(dy_s[3]):
+                        wgrads.append(c)
+                        continue
+            ok = False
+        if not ok or not fwd:
+            continue
+        xs = node2shape[x]
+        xt = core.Result(core.Transpose((0, 2, 3, 1)), [x])
+        node2shape[xt] = [xs[0], xs[2], xs[3], xs[1]]
+        xt.props.update(im.props)
+        for c in fwd:
+            w4 = c.parents[1].parents[0]
+            ws = node2shape[w4]
+            wr = core.Result(core.Transpose((0, 2, 3, 1)), [w4])
+            node2shape[wr] = [ws[0], ws[2], ws[3], ws[1]]
+            wr.props.update(c.props)
+            new = core.Result(im2col_ops.ConvFwdBiasRelu(info), [xt, wr] + list(c.parents[2:]))
+            node2shape[new] = node2shape[c]
+            new.props.update(c.props)
+            replace[c] = new
+        for c in wgrads:
+            new = core.Result(im2col_ops.ConvWgradImplicit(info), [xt, c.parents[0].parents[0]])
+            node2shape[new] = node2shape[c]
+            new.props.update(c.props)
+            replace[c] = new
+    if not replace:
+        return list(outputs), list(updatetargs)
+    return _rewire(outputs, updatetargs, replace)
+
+
+def _conv_channels_ok(n):
+    return n % 16 == 0 and (n <= 128 or n % 128 == 0)
+
+
 def pad_conv_columns(outputs, updatetargs, node2shape):
     """Widen the rows of a float32 column matrix whose length Z = C*kh*kw is not a multiple of four (a 3-channel
     5x5 convolution: 75) to the next multiple, so that every row starts on a 16-byte boundary and the products
@@ -901,6 +983,8 @@ def run_compilation_pipeline(inputs, outputs, updates, givens):
         outputs_simple, updatetargs_simple = fuse_elementwise(outputs_simple, updatetargs_simple, node2shape)
         if config["fuse_conv_output"]:
             outputs_simple, updatetargs_simple = fuse_conv_output(outputs_simple, updatetargs_simple, node2shape)
+        if config["fuse_conv_output"] and config["fuse_conv_implicit"]:
+            outputs_simple, updatetargs_simple = fuse_conv_implicit(outputs_simple, updatetargs_simple, node2shape)
         if config["pad_conv_columns"]:
             outputs_simple, updatetargs_simple = pad_conv_columns(outputs_simple, updatetargs_simple, node2shape)
     all_out = outputs_simple + updatetargs_simple

@@ -39,6 +39,9 @@
 // aligned, leading dimensions and batch strides multiples of 4 floats.
 #include <cuda.h>  // CUtensorMap and its enums; the encoder is looked up at run time, libcuda is not linked
 
+#include <algorithm>
+#include <cstring>
+
 #include "runtime.h"
 #include "tc_util.h"
 
@@ -67,19 +70,46 @@ struct TmaParams {
   int raw_stages, conv_stages;
   int tmem_cols;
   int* err;
-  // Implicit convolution (conv != 0): the X tile of K block kb is not a block of a stored matrix but the
-  // window of the NHWC tensor behind mapX that kernel tap (i, j) of that block addresses; see sgemm_tma_conv.
-  int conv;
+  // tile grid: the CTAs of the (persistent) launch walk it with stride gridDim.x
+  int xtiles, ytiles;
+  long total_tiles;  // xtiles * ytiles * batches * nsplit
+  // Implicit convolution (CONV 1: forward product / data gradient): the X tile of K block kb is not a block of a
+  // stored matrix but the window of the NHWC tensor behind mapX that kernel tap (i, j) of that block addresses;
+  // see conv_implicit_tma. CONV 2 (filter gradient): see conv_wgrad_tma.
+  int csign;            // +1: tap (i, j) reads the source at (y + i - ph, x + j - pw); -1: at (y + ph - i, x + pw - j)
   int cW, cHW;          // width and pixels of an output image
   int cC;               // output channels (= N of the product)
-  int ckw, ckpt;        // kernel width; K blocks per tap (input channels / 32)
+  int ckw, ckpt;        // kernel width; K blocks per tap (source channels / 32)
   int cph, cpw;         // padding
   int crows, cnimg;     // image rows and images per tile
   int cnbands;          // tiles per image when an image spans several tiles
   int cB;               // images
   int cx_tx;            // bytes one X load delivers (the box may be smaller than 128 rows)
   ConvEpilogue ep;      // ep.y != nullptr: bias + relu + NCHW output stage instead of storing C
+  // filter gradient (CONV 2)
+  int wunits;           // (tap, 32-channel chunk) units = kh*kw*Cs/32; an X tile holds four of them
+  int wkk;              // kh*kw
+  int wbh, wnrg;        // image rows per K block; K blocks per image
+  int wnpx;             // pixels per K block (wbh * width <= 32); the remaining K slots are zero
 };
+
+struct Tile {
+  int xt, yt, batch, split, nkb;
+  long k_begin;
+};
+__device__ __forceinline__ Tile tile_of(const TmaParams& p, long t) {
+  Tile c;
+  c.xt = (int)(t % p.xtiles);
+  const long r = t / p.xtiles;
+  c.yt = (int)(r % p.ytiles);
+  const int z = (int)(r / p.ytiles);
+  c.batch = z / p.nsplit;
+  c.split = z - c.batch * p.nsplit;
+  c.k_begin = (long)c.split * p.kchunk;
+  const long k_end = (c.k_begin + p.kchunk < p.K) ? c.k_begin + p.kchunk : p.K;
+  c.nkb = (int)((k_end - c.k_begin + kBK - 1) / kBK);
+  return c;
+}
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
   asm volatile(
@@ -142,14 +172,17 @@ __device__ __forceinline__ void convert_kmajor_lo(const unsigned char* raw, unsi
   }
 }
 
-// raw [32 k][R rows] tile: unit q -> (row = q % R, k quad = q / R); lanes run along rows on both sides
-__device__ __forceinline__ void convert_mnmajor(const unsigned char* raw, unsigned char* hi, unsigned char* lo, int R, int tid) {
+// raw [32 k][R rows] tile: unit q -> (row = q % R, k quad = q / R); lanes run along rows on both sides.
+// K slots at or beyond kvalid hold no data (the TMA box was shorter): they become zeros.
+__device__ __forceinline__ void convert_mnmajor(const unsigned char* raw, unsigned char* hi, unsigned char* lo, int R, int tid, int kvalid) {
   const float* src = reinterpret_cast<const float*>(raw);
   const int units = R * 8;
   for (int q = tid; q < units; q += kConvThreads) {
     const int kq = q / R, r = q - kq * R;
     const float* s = src + (size_t)(4 * kq) * R + r;
-    const float a = s[0], b = s[R], c = s[2 * R], d = s[3 * R];
+    const int k0 = 4 * kq;
+    const float a = k0 < kvalid ? s[0] : 0.f, b = k0 + 1 < kvalid ? s[R] : 0.f, c = k0 + 2 < kvalid ? s[2 * R] : 0.f,
+                d = k0 + 3 < kvalid ? s[3 * R] : 0.f;
     uint4 h, l;
     split_tf32x4(a, b, c, d, h, l);
     const uint32_t off = tile_off(r, 4 * kq);
@@ -158,7 +191,29 @@ __device__ __forceinline__ void convert_mnmajor(const unsigned char* raw, unsign
   }
 }
 
-template <bool XMN, bool YMN>
+// raw [4 units][32 k][32 channels] tile of the filter gradient: tile row r = unit (r / 32), channel (r % 32);
+// element (r, k) lies at unit*1024 + k*32 + channel floats. Same output layout as convert_mnmajor.
+__device__ __forceinline__ void convert_units(const unsigned char* raw, unsigned char* hi, unsigned char* lo, int tid, int kvalid) {
+  const float* src = reinterpret_cast<const float*>(raw);
+  for (int q = tid; q < kXRows * 8; q += kConvThreads) {
+    const int kq = q >> 7, r = q & 127;
+    const float* s = src + (r >> 5) * 1024 + (r & 31) + (4 * kq) * 32;
+    const int k0 = 4 * kq;
+    const float a = k0 < kvalid ? s[0] : 0.f, b = k0 + 1 < kvalid ? s[32] : 0.f, c = k0 + 2 < kvalid ? s[64] : 0.f,
+                d = k0 + 3 < kvalid ? s[96] : 0.f;
+    uint4 h, l;
+    split_tf32x4(a, b, c, d, h, l);
+    const uint32_t off = tile_off(r, 4 * kq);
+    *reinterpret_cast<uint4*>(hi + off) = h;
+    *reinterpret_cast<uint4*>(lo + off) = l;
+  }
+}
+
+// One CTA walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... of the tile grid (persistent launch): the
+// barriers, the TMEM allocation and the tensor-map fetch are paid once per CTA, and the TMA producer runs ahead
+// across tile boundaries, so that the K blocks of the next tile are in flight while this tile's accumulator is
+// being stored. Ring positions and barrier phases run on over the tiles.
+template <bool XMN, bool YMN, int CONV>
 __global__ void __launch_bounds__(kThreadsTma, 2)
 sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapY, const TmaParams p) {
   extern __shared__ unsigned char smem_raw[];
@@ -179,12 +234,6 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   const uint32_t conv_bytes = cx_bytes + 2 * y_bytes, raw_bytes = x_bytes + y_bytes;
   unsigned char* conv0 = smem;
   unsigned char* raw0 = smem + (size_t)CS * conv_bytes;
-
-  const int batch = blockIdx.z / p.nsplit, split = blockIdx.z % p.nsplit;
-  const long x0 = (long)blockIdx.x * kXRows, y0 = (long)blockIdx.y * UN;
-  const long k_begin = (long)split * p.kchunk;
-  const long k_end = (k_begin + p.kchunk < p.K) ? k_begin + p.kchunk : p.K;
-  const int nkb = (int)((k_end - k_begin + kBK - 1) / kBK);
   volatile int* abortp = &abort_flag;
 
   if (tid == 0) {
@@ -212,45 +261,92 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   const uint32_t tmem_d = tmem_base_slot;
 
   if (warp < kConvWarps) {
-    // ------------------------------------------------ converters
-    bool ok = true;
-    for (int kb = 0; kb < nkb; ++kb) {
-      const int rs = kb % RS, cs = kb % CS;
-      ok = mbar_wait_or_abort(smem_u32(&raw_full[rs]), (uint32_t)(kb / RS) & 1u, abortp);
-      ok = ok && mbar_wait_or_abort(smem_u32(&conv_empty[cs]), ((uint32_t)(kb / CS) & 1u) ^ 1u, abortp);
-      if (!ok) break;
-      const unsigned char* rx = raw0 + (size_t)rs * raw_bytes;
-      const unsigned char* ry = rx + x_bytes;
-      unsigned char* cx = conv0 + (size_t)cs * conv_bytes;
-      unsigned char* cy = cx + cx_bytes;
-      if (XMN) convert_mnmajor(rx, cx, cx + x_bytes, kXRows, tid);
-      else convert_kmajor_lo(rx, cx, kXRows * 8, tid);
-      if (YMN) convert_mnmajor(ry, cy, cy + y_bytes, UN, tid);
-      else convert_kmajor(ry, cy, cy + y_bytes, UN * 8, tid);
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(smem_u32(&conv_full[cs]));
-        if (!XDIRECT) mbar_arrive(smem_u32(&raw_empty[rs]));
+    // ------------------------------------------------ converters, then the tile's epilogue
+    int rs = 0, cs = 0;
+    uint32_t rphase = 0, cphase = 0, it = 0;
+    for (long t = blockIdx.x; t < p.total_tiles; t += gridDim.x, ++it) {
+      const Tile c = tile_of(p, t);
+      const long x0 = (long)c.xt * kXRows, y0 = (long)c.yt * UN;
+      bool ok = true;
+      for (int kb = 0; kb < c.nkb; ++kb) {
+        ok = mbar_wait_or_abort(smem_u32(&raw_full[rs]), rphase, abortp);
+        ok = ok && mbar_wait_or_abort(smem_u32(&conv_empty[cs]), cphase ^ 1u, abortp);
+        if (!ok) break;
+        const unsigned char* rx = raw0 + (size_t)rs * raw_bytes;
+        const unsigned char* ry = rx + x_bytes;
+        unsigned char* cx = conv0 + (size_t)cs * conv_bytes;
+        unsigned char* cy = cx + cx_bytes;
+        if (CONV == 2) {
+          convert_units(rx, cx, cx + x_bytes, tid, p.wnpx);
+          convert_mnmajor(ry, cy, cy + y_bytes, UN, tid, p.wnpx);
+        } else {
+          if (XMN) convert_mnmajor(rx, cx, cx + x_bytes, kXRows, tid, kBK);
+          else convert_kmajor_lo(rx, cx, kXRows * 8, tid);
+          if (YMN) convert_mnmajor(ry, cy, cy + y_bytes, UN, tid, kBK);
+          else convert_kmajor(ry, cy, cy + y_bytes, UN * 8, tid);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(smem_u32(&conv_full[cs]));
+          if (!XDIRECT) mbar_arrive(smem_u32(&raw_empty[rs]));
+        }
+        if (++rs == RS) { rs = 0; rphase ^= 1u; }
+        if (++cs == CS) { cs = 0; cphase ^= 1u; }
       }
-    }
-    // ------------------------------------------------ epilogue
-    if (ok && nkb > 0) ok = mbar_wait_or_abort(smem_u32(&accum_bar), 0, abortp);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (!ok) *abortp = 1;
-    asm volatile("bar.sync 1, %0;" ::"n"(kConvThreads) : "memory");  // the epilogue warps agree on success
-    if (*abortp) {
-      if (tid == 0) { *(volatile int*)p.err = 3; __threadfence_system(); }
-    } else {
+      // ---------------------------------------------- epilogue of this tile
+      if (ok && c.nkb > 0) ok = mbar_wait_or_abort(smem_u32(&accum_bar), it & 1u, abortp);
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (!ok) *abortp = 1;
+      asm volatile("bar.sync 1, %0;" ::"n"(kConvThreads) : "memory");  // the epilogue warps agree on success
+      if (*abortp) {
+        if (tid == 0) { *(volatile int*)p.err = 3; __threadfence_system(); }
+        break;
+      }
       // Accumulator -> registers -> global memory. A thread owns tile row (quarter*32 + lane) and 8
       // consecutive columns per chunk (8); columns [0, UN) hold hi*hi + lo*hi and [UN, 2UN) hold hi*lo.
       const int quarter = warp & 3, colgroup = warp >> 2;
       const int nchunks = UN / 8;
       const int row = quarter * 32 + lane;
       const long i_g = x0 + row;
+      const int batch = c.batch, split = c.split;
       float* cbase = (p.nsplit > 1) ? p.C + ((long)batch * p.nsplit + split) * p.M * p.N : p.C + batch * p.c_batch_stride;
       const long ld = (p.nsplit > 1) ? p.N : p.ldc;
       const bool vec_ok = ((ld & 3) == 0) && (((uintptr_t)cbase & 15) == 0);
+      // where tile row `row` goes when the result is stored as NCHW planes (implicit convolution, or the output
+      // stage of a convolution layer on a stored column matrix)
+      bool pvalid = false;
+      long pb = 0, ppix = 0, pHW = 1, pC = 1;
+      if (CONV == 1) {
+        const int tile = c.xt;
+        pHW = p.cHW;
+        pC = p.cC;
+        if (p.cnimg > 1) {
+          const int li = row / p.cHW;
+          pb = (long)tile * p.cnimg + li;
+          ppix = row - li * p.cHW;
+          pvalid = li < p.cnimg && pb < p.cB;
+        } else {
+          pb = tile / p.cnbands;
+          ppix = (long)(tile - pb * p.cnbands) * p.crows * p.cW + row;
+          pvalid = row < p.crows * p.cW && ppix < p.cHW;
+        }
+      } else if (CONV == 0 && p.ep.y) {
+        pHW = p.ep.HW;
+        pC = p.yrows;
+        pvalid = i_g < p.xrows;
+        pb = i_g / pHW;
+        ppix = i_g - pb * pHW;
+      }
+      // filter gradient: tile row = (unit, channel) -> column (32*chunk + channel)*kh*kw + tap of the result
+      long wcol = -1;
+      if (CONV == 2) {
+        const int unit = c.xt * 4 + (row >> 5);
+        if (unit < p.wunits) {
+          const int tap = unit / p.ckpt, q = unit - tap * p.ckpt;
+          wcol = (long)(32 * q + (row & 31)) * p.wkk + tap;
+        }
+      }
       for (int ch = colgroup; ch < nchunks; ch += kConvWarps / 4) {
         const int c0 = ch * 8;
         uint32_t r1[8], r2[8];
@@ -261,41 +357,32 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r1[j]) + __uint_as_float(r2[j]);
         const long j0 = y0 + c0;
-        if (p.conv) {
-          // tile row = pixel `row` of the tile's image rows; the result goes out as NCHW, the lanes of a
-          // warp writing consecutive pixels of one channel plane
-          const int tile = blockIdx.x;
-          int b, pix;
-          bool valid;
-          if (p.cnimg > 1) {
-            const int li = row / p.cHW;
-            b = tile * p.cnimg + li;
-            pix = row - li * p.cHW;
-            valid = li < p.cnimg && b < p.cB;
-          } else {
-            b = tile / p.cnbands;
-            pix = (tile - b * p.cnbands) * p.crows * p.cW + row;
-            valid = row < p.crows * p.cW && pix < p.cHW;
-          }
-          if (valid) {
-            // with K splits every split writes its own copy of the whole result; a fold adds them in order
-            float* dst = p.C + (size_t)split * p.cB * p.cC * p.cHW + ((size_t)b * p.cC + j0) * p.cHW + pix;
+        if (CONV == 2) {
+          if (wcol >= 0) {
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-              if (j0 + j < p.cC) dst[(size_t)j * p.cHW] = v[j];
+              if (j0 + j < p.yrows) cbase[(j0 + j) * ld + wcol] = v[j];
           }
-        } else if (p.ep.y) {
-          if (i_g < p.xrows) {
-            const long b = i_g / p.ep.HW, pix = i_g - b * p.ep.HW;
+        } else if (CONV == 1 || p.ep.y) {
+          // NCHW planes: the lanes of a warp write consecutive pixels of one channel plane
+          if (pvalid) {
+            if (p.ep.y) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              if (j0 + j < p.yrows) {
-                const float t = v[j] + p.ep.bias[j0 + j];
-                const int8_t mk = (int8_t)(t >= 0.f);
-                const size_t o = ((size_t)b * p.yrows + (j0 + j)) * p.ep.HW + pix;
-                p.ep.mask[o] = mk;
-                p.ep.y[o] = t * (float)mk;
+              for (int j = 0; j < 8; ++j) {
+                if (j0 + j < pC) {
+                  const float tt = v[j] + p.ep.bias[j0 + j];
+                  const int8_t mk = (int8_t)(tt >= 0.f);
+                  const size_t o = ((size_t)pb * pC + (j0 + j)) * pHW + ppix;
+                  p.ep.mask[o] = mk;
+                  p.ep.y[o] = tt * (float)mk;
+                }
               }
+            } else {
+              // with K splits every split writes its own copy of the whole result; a fold adds them in order
+              float* dst = p.C + (size_t)split * p.cB * pC * pHW + ((size_t)pb * pC + j0) * pHW + ppix;
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (j0 + j < pC) dst[(size_t)j * pHW] = v[j];
             }
           }
         } else if (i_g < p.xrows) {
@@ -316,6 +403,9 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
           }
         }
       }
+      // this warp's reads of the accumulator are complete before it signals anything for the next tile (the
+      // first MMA of the next tile waits for a conversion that every epilogue warp takes part in)
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
   } else if (warp == kConvWarps) {
     // ------------------------------------------------ MMA issuer
@@ -324,69 +414,96 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
     // x_hi * [y_hi | y_lo] into columns [0, 2UN) and x_lo * y_hi into columns [0, UN).
     const uint32_t idesc1 = make_idesc_tf32(UN), idesc2 = make_idesc_tf32(2 * UN);
     bool ok = true;
-    for (int kb = 0; kb < nkb; ++kb) {
-      const int cs = kb % CS;
-      ok = mbar_wait_or_abort(smem_u32(&conv_full[cs]), (uint32_t)(kb / CS) & 1u, abortp);
-      if (!ok) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int rs = kb % RS;
-      const uint32_t sbase = smem_u32(conv0 + (size_t)cs * conv_bytes);
-      const uint64_t dxh = make_desc(XDIRECT ? smem_u32(raw0 + (size_t)rs * raw_bytes) : sbase);
-      const uint64_t dxl = make_desc(XDIRECT ? sbase : sbase + x_bytes);
-      const uint64_t dyh = make_desc(sbase + cx_bytes);  // y_lo follows y_hi: one descriptor covers both
+    int rs = 0, cs = 0;
+    uint32_t cphase = 0;
+    for (long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+      const Tile c = tile_of(p, t);
+      for (int kb = 0; kb < c.nkb; ++kb) {
+        ok = mbar_wait_or_abort(smem_u32(&conv_full[cs]), cphase, abortp);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t sbase = smem_u32(conv0 + (size_t)cs * conv_bytes);
+        const uint64_t dxh = make_desc(XDIRECT ? smem_u32(raw0 + (size_t)rs * raw_bytes) : sbase);
+        const uint64_t dxl = make_desc(XDIRECT ? sbase : sbase + x_bytes);
+        const uint64_t dyh = make_desc(sbase + cx_bytes);  // y_lo follows y_hi: one descriptor covers both
 #pragma unroll
-      for (int kk = 0; kk < kBK / 8; ++kk) {
-        const uint64_t adv = (uint64_t)((kk * 32) >> 4);  // 8 tf32 = 32 bytes along K inside the swizzle row
-        const uint32_t first = (kb == 0 && kk == 0) ? 0u : 1u;
-        mma_tf32_elect(tmem_d, dxh + adv, dyh + adv, idesc2, first);
-        mma_tf32_elect(tmem_d, dxl + adv, dyh + adv, idesc1, 1u);
+        for (int kk = 0; kk < kBK / 8; ++kk) {
+          const uint64_t adv = (uint64_t)((kk * 32) >> 4);  // 8 tf32 = 32 bytes along K inside the swizzle row
+          const uint32_t first = (kb == 0 && kk == 0) ? 0u : 1u;
+          mma_tf32_elect(tmem_d, dxh + adv, dyh + adv, idesc2, first);
+          mma_tf32_elect(tmem_d, dxl + adv, dyh + adv, idesc1, 1u);
+        }
+        if (elect_one()) {
+          mma_commit(smem_u32(&conv_empty[cs]));
+          if (XDIRECT) mma_commit(smem_u32(&raw_empty[rs]));
+        }
+        __syncwarp();
+        if (++rs == RS) rs = 0;
+        if (++cs == CS) { cs = 0; cphase ^= 1u; }
       }
-      if (elect_one()) {
-        mma_commit(smem_u32(&conv_empty[cs]));
-        if (XDIRECT) mma_commit(smem_u32(&raw_empty[rs]));
-      }
+      if (ok && c.nkb > 0 && elect_one()) mma_commit(smem_u32(&accum_bar));
       __syncwarp();
     }
-    if (ok && nkb > 0 && elect_one()) mma_commit(smem_u32(&accum_bar));
-    __syncwarp();
     if (!ok && lane == 0) { *abortp = 1; *(volatile int*)p.err = 4; __threadfence_system(); }
   } else if (lane == 0) {
     // ------------------------------------------------ TMA producer (one thread)
-    int issued = 0;
+    long issued = 0;
     bool ok = true;
-    for (int kb = 0; kb < nkb; ++kb) {
-      const int rs = kb % RS;
-      ok = mbar_wait_or_abort(smem_u32(&raw_empty[rs]), ((uint32_t)(kb / RS) & 1u) ^ 1u, abortp);
-      if (!ok) break;
-      const uint32_t bar = smem_u32(&raw_full[rs]);
-      const int k0 = (int)(k_begin + (long)kb * kBK);
-      const uint32_t dx = smem_u32(raw0 + (size_t)rs * raw_bytes);
-      if (!XMN && p.conv) {
-        // tap (i, j) of this K block reads the tensor shifted by (ph - i, pw - j); rows and columns that
-        // fall outside the tensor are zero-filled by the TMA unit: that is the convolution's padding
-        mbar_arrive_expect_tx(bar, (uint32_t)p.cx_tx + y_bytes);
-        const int gkb = (int)(k_begin / kBK) + kb;  // K block within the whole product (this CTA may hold one K split)
-        const int tap = gkb / p.ckpt, q = gkb - tap * p.ckpt;
-        const int ti = tap / p.ckw, tj = tap - ti * p.ckw;
-        const int tile = blockIdx.x;
-        const int b0 = p.cnimg > 1 ? tile * p.cnimg : tile / p.cnbands;
-        const int yrow0 = p.cnimg > 1 ? 0 : (tile - b0 * p.cnbands) * p.crows;
-        tma_load_4d(dx, &mapX, 32 * q, p.cpw - tj, yrow0 + p.cph - ti, b0, bar);
-      } else {
-        mbar_arrive_expect_tx(bar, raw_bytes);
-        if (XMN) tma_load_3d(dx, &mapX, (int)x0, k0, batch, bar);
-        else tma_load_3d(dx, &mapX, k0, (int)x0, batch, bar);
+    int rs = 0;
+    uint32_t rphase = 0;
+    for (long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+      const Tile c = tile_of(p, t);
+      const long x0 = (long)c.xt * kXRows, y0 = (long)c.yt * UN;
+      for (int kb = 0; kb < c.nkb; ++kb) {
+        ok = mbar_wait_or_abort(smem_u32(&raw_empty[rs]), rphase ^ 1u, abortp);
+        if (!ok) break;
+        const uint32_t bar = smem_u32(&raw_full[rs]);
+        const int k0 = (int)(c.k_begin + (long)kb * kBK);
+        const uint32_t dx = smem_u32(raw0 + (size_t)rs * raw_bytes);
+        if (CONV == 1) {
+          // tap (i, j) of this K block reads the tensor shifted by csign * (i - ph, j - pw); rows and columns that
+          // fall outside the tensor are zero-filled by the TMA unit: that is the convolution's padding
+          mbar_arrive_expect_tx(bar, (uint32_t)p.cx_tx + y_bytes);
+          const int gkb = k0 / kBK;  // K block within the whole product (this tile may hold one K split)
+          const int tap = gkb / p.ckpt, q = gkb - tap * p.ckpt;
+          const int ti = tap / p.ckw, tj = tap - ti * p.ckw;
+          const int tile = c.xt;
+          const int b0 = p.cnimg > 1 ? tile * p.cnimg : tile / p.cnbands;
+          const int yrow0 = p.cnimg > 1 ? 0 : (tile - b0 * p.cnbands) * p.crows;
+          tma_load_4d(dx, &mapX, 32 * q, p.csign * (tj - p.cpw), yrow0 + p.csign * (ti - p.cph), b0, bar);
+          tma_load_3d(dx + x_bytes, &mapY, k0, (int)y0, c.batch, bar);
+        } else if (CONV == 2) {
+          // K block = wbh rows of image b; X = the same pixels of the source shifted by each of the tile's taps
+          const int gkb = k0 / kBK;
+          const int b = gkb / p.wnrg, yrow0 = (gkb - b * p.wnrg) * p.wbh;
+          int nunits = p.wunits - c.xt * 4;
+          nunits = nunits > 4 ? 4 : nunits;
+          const uint32_t px_bytes = (uint32_t)p.wnpx * 128u;
+          mbar_arrive_expect_tx(bar, (uint32_t)nunits * px_bytes + (uint32_t)p.wnpx * (uint32_t)UN * 4u);
+          for (int u = 0; u < nunits; ++u) {
+            const int unit = c.xt * 4 + u;
+            const int tap = unit / p.ckpt, q = unit - tap * p.ckpt;
+            const int ti = tap / p.ckw, tj = tap - ti * p.ckw;
+            tma_load_4d(dx + (uint32_t)u * 4096u, &mapX, 32 * q, tj - p.cpw, yrow0 + ti - p.cph, b, bar);
+          }
+          tma_load_4d(dx + x_bytes, &mapY, (int)y0, 0, yrow0, b, bar);
+        } else {
+          mbar_arrive_expect_tx(bar, raw_bytes);
+          if (XMN) tma_load_3d(dx, &mapX, (int)x0, k0, c.batch, bar);
+          else tma_load_3d(dx, &mapX, k0, (int)x0, c.batch, bar);
+          if (YMN) tma_load_3d(dx + x_bytes, &mapY, (int)y0, k0, c.batch, bar);
+          else tma_load_3d(dx + x_bytes, &mapY, k0, (int)y0, c.batch, bar);
+        }
+        ++issued;
+        if (++rs == RS) { rs = 0; rphase ^= 1u; }
       }
-      if (YMN) tma_load_3d(dx + x_bytes, &mapY, (int)y0, k0, batch, bar);
-      else tma_load_3d(dx + x_bytes, &mapY, k0, (int)y0, batch, bar);
-      ++issued;
     }
     if (!ok || *abortp) {
       *abortp = 1;
       *(volatile int*)p.err = 5;
       __threadfence_system();
       // copies already issued still write this CTA's shared memory: wait (bounded) until they have landed
-      for (int j = (issued > RS ? issued - RS : 0); j < issued; ++j) mbar_wait(smem_u32(&raw_full[j % RS]), (uint32_t)(j / RS) & 1u);
+      for (long j = (issued > RS ? issued - RS : 0); j < issued; ++j) mbar_wait(smem_u32(&raw_full[j % RS]), (uint32_t)(j / RS) & 1u);
     }
   }
 
@@ -456,6 +573,50 @@ bool encode(CUtensorMap* map, const Side& s, long K, long P, int box_rows) {
   return r == CUDA_SUCCESS;
 }
 
+// stage counts for a kernel with conversion stages of conv_bytes and raw stages of raw_bytes: two CTAs per SM when
+// one conversion stage and at least two raw stages fit in half of the SM's shared memory, otherwise one CTA per
+// SM with two conversion stages and as many raw stages as fit. Returns false when nothing fits.
+bool choose_stages(long conv_bytes, long raw_bytes, long nkb, int* conv_stages, int* raw_stages) {
+  const long half = 110L * 1024 - 1024, whole = 224L * 1024 - 1024;
+  int cs, rs;
+  if ((half - 2 * conv_bytes) / raw_bytes >= 3) {
+    cs = 2;
+    rs = (int)std::min<long>(kMaxRaw, (half - 2 * conv_bytes) / raw_bytes);
+  } else if ((half - conv_bytes) / raw_bytes >= 2) {
+    cs = 1;
+    rs = (int)std::min<long>(kMaxRaw, (half - conv_bytes) / raw_bytes);
+  } else {
+    cs = 2;
+    rs = (int)std::min<long>(kMaxRaw, (whole - 2 * conv_bytes) / raw_bytes);
+    if (rs < 2) return false;
+  }
+  (void)nkb;
+  *conv_stages = cs;
+  *raw_stages = rs;
+  return true;
+}
+
+// CTAs of the persistent launch: every tile at once when they all fit on the machine (two CTAs per SM when the
+// shared memory allows), otherwise one full wave that walks the tile grid
+unsigned persistent_grid(long total_tiles, size_t smem_bytes) {
+  const long per_sm = (smem_bytes <= 110u * 1024u) ? 2 : 1;
+  const long slots = (long)rt().sm_count * per_sm;
+  return (unsigned)std::min<long>(total_tiles, slots);
+}
+
+template <bool XMN, bool YMN, int CONV>
+int launch_tma(const CUtensorMap& mapX, const CUtensorMap& mapY, const TmaParams& p, size_t smem) {
+  static bool cfg = false;
+  if (!cfg) {
+    const int cap = 227 * 1024 - 2048;
+    CGTB_CUDA_TRY(cudaFuncSetAttribute(sgemm_tma_kernel<XMN, YMN, CONV>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap));
+    cfg = true;
+  }
+  const unsigned grid = persistent_grid(p.total_tiles, smem);
+  CGTB_LAUNCH((sgemm_tma_kernel<XMN, YMN, CONV>), grid, kThreadsTma, smem, mapX, mapY, p);
+  return 0;
+}
+
 }  // namespace
 
 namespace cgtb {
@@ -471,7 +632,7 @@ int sgemm_tma(int tA, int tB, long P, long M, long N, long K, const float* A, lo
   Side sB = {B, ldb, tB == 0, N, strideB};   // rows of op(B)^T are n; stored [K, N] when not transposed
   if (!aligned_for_tma(sA, P) || !aligned_for_tma(sB, P)) return -1;
   TmaParams p;
-  p.conv = 0;
+  memset(&p, 0, sizeof(p));
   p.ep = ConvEpilogue{nullptr, nullptr, nullptr, 1};
   if (ep) p.ep = *ep;
   p.swapped = (N > M) ? 1 : 0;
@@ -491,23 +652,9 @@ int sgemm_tma(int tA, int tB, long P, long M, long N, long K, const float* A, lo
   p.yrows = Y.rows;
   const long cx_bytes = X.mn ? 2L * kXRows * 128 : 1L * kXRows * 128;  // a K-major X is read in place as the hi operand
   const long conv_bytes = cx_bytes + 2L * UN * 128, raw_bytes = (long)kXRows * 128 + (long)UN * 128;
-  // Two CTAs per SM when one conversion stage and at least two raw stages fit in half of the SM's shared
-  // memory: all tiles of a 1.5-wave grid are then resident at once and share HBM evenly. Otherwise one
-  // CTA per SM with two conversion stages and as many raw stages as fit.
   int conv_stages, raw_stages;
-  const long half = 110L * 1024 - 1024, whole = 224L * 1024 - 1024;
-  if ((half - 2 * conv_bytes) / raw_bytes >= 3) {
-    conv_stages = 2;
-    raw_stages = (int)std::min<long>(kMaxRaw, (half - 2 * conv_bytes) / raw_bytes);
-  } else if ((half - conv_bytes) / raw_bytes >= 2) {
-    conv_stages = 1;
-    raw_stages = (int)std::min<long>(kMaxRaw, (half - conv_bytes) / raw_bytes);
-  } else {
-    conv_stages = 2;
-    raw_stages = (int)std::min<long>(kMaxRaw, (whole - 2 * conv_bytes) / raw_bytes);
-    if (raw_stages < 2) return -1;
-  }
   long nkb_total = cgtb_ceil_div(K, kBK);
+  if (!choose_stages(conv_bytes, raw_bytes, nkb_total, &conv_stages, &raw_stages)) return -1;
   long tiles = xtiles * ytiles * P;
   int nsplit = 1;
   long want = (long)rt().sm_count;
@@ -517,11 +664,8 @@ int sgemm_tma(int tA, int tB, long P, long M, long N, long K, const float* A, lo
   }
   long kchunk = cgtb_ceil_div(nkb_total, nsplit) * kBK;
   nsplit = (int)cgtb_ceil_div(K, kchunk);
-  if ((long)P * nsplit > 65535 || ytiles > 65535) return -1;
+  if (xtiles > 2147483647L / ((long)ytiles * P * nsplit)) return -1;
   if (ep && nsplit > 1) return -1;  // the output stage needs whole sums
-  const long nkb = kchunk / kBK;  // a short K loop needs no deeper rings: smaller CTAs, more of them per SM
-  if (raw_stages > nkb) raw_stages = (int)nkb;
-  if (conv_stages > nkb) conv_stages = (int)nkb;
   p.conv_stages = conv_stages;
   p.raw_stages = raw_stages;
   p.nsplit = nsplit;
@@ -531,6 +675,9 @@ int sgemm_tma(int tA, int tB, long P, long M, long N, long K, const float* A, lo
   p.N = N;
   p.ldc = ldc;
   p.c_batch_stride = strideC;
+  p.xtiles = (int)xtiles;
+  p.ytiles = ytiles;
+  p.total_tiles = xtiles * ytiles * P * nsplit;
   p.err = tc_error_flag();
   if (!p.err) return 1;
   CUtensorMap mapX, mapY;
@@ -545,119 +692,106 @@ int sgemm_tma(int tA, int tB, long P, long M, long N, long K, const float* A, lo
   }
   size_t smem = (size_t)conv_stages * conv_bytes + (size_t)raw_stages * raw_bytes;
   smem += 1024;
-  dim3 grid((unsigned)xtiles, (unsigned)ytiles, (unsigned)(P * nsplit));
-  const int cap = 227 * 1024 - 2048;
-#define TMA_LAUNCH(XM, YM)                                                                                              \
-  {                                                                                                                     \
-    static bool cfg = false;                                                                                            \
-    if (!cfg) { CGTB_CUDA_TRY(cudaFuncSetAttribute(sgemm_tma_kernel<XM, YM>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap)); cfg = true; } \
-    CGTB_LAUNCH((sgemm_tma_kernel<XM, YM>), grid, kThreadsTma, smem, mapX, mapY, p);                                    \
-  }
-  if (X.mn && Y.mn) TMA_LAUNCH(true, true)
-  else if (X.mn) TMA_LAUNCH(true, false)
-  else if (Y.mn) TMA_LAUNCH(false, true)
-  else TMA_LAUNCH(false, false)
-#undef TMA_LAUNCH
+  int rc;
+  if (X.mn && Y.mn) rc = launch_tma<true, true, 0>(mapX, mapY, p, smem);
+  else if (X.mn) rc = launch_tma<true, false, 0>(mapX, mapY, p, smem);
+  else if (Y.mn) rc = launch_tma<false, true, 0>(mapX, mapY, p, smem);
+  else rc = launch_tma<false, false, 0>(mapX, mapY, p, smem);
+  if (rc) return rc;
   if (nsplit > 1) tc_splitk_fold(P, M, N, nsplit, part, C, ldc, strideC);
   CGTB_CHECK_LAUNCH("sgemm_tma");
   return 0;
 }
 
-// Data gradient of a stride-1 convolution without a column matrix (the reference forms
-// Mul22(dy, W) and then Col2Im: cgt/nn_ops/im2col.py, include/im2col.h:30-50):
-//   dx[b, c, y, x] = sum_{i, j, co} dy[b, y + ph - i, x + pw - j, co] * wr[c, (i*kw + j)*Cin + co]
-// dy is NHWC [B, Ho, Wo, Cin] (the transposed gradient the graph already holds), wr is the filter bank
-// rearranged to [C][kh*kw*Cin], dx is NCHW [B, C, H, W]. It is the GEMM above with M = pixels, N = C,
-// K = kh*kw*Cin whose X operand is never stored: for K block (tap, 32 input channels) the TMA unit
-// loads the window of dy that the tap addresses, a box of whole image rows whose out-of-range rows and
-// columns it zero-fills. A tile is `rows` image rows of one image (rows*W <= 128 pixels) or, for small
-// images, several whole images.
+// Stride-1 convolution as an implicit GEMM, without a column matrix: serves the forward product of a layer
+// (sign +1; the reference forms Im2Col then Mul22(col, W^T): cgt/nn.py:93-100, include/im2col.h:6-28) and its data
+// gradient (sign -1; the reference forms Mul22(dy, W) and then Col2Im: cgt/nn_ops/im2col.py, include/im2col.h:30-50):
+//   out[b, n, y, x] = sum_{i, j, c} src[b, y + sign*(i - ph), x + sign*(j - pw), c] * wr[n][(i*kw + j)*Cs + c]
+// src is NHWC [B, Hs, Ws, Cs], wr holds one row of kh*kw*Cs entries per output channel, out is NCHW [B, N, Hd, Wd].
+// It is the GEMM above with M = pixels, N = output channels, K = kh*kw*Cs whose X operand is never stored: for K
+// block (tap, 32 source channels) the TMA unit loads the window of src that the tap addresses, a box of whole image
+// rows whose out-of-range rows and columns it zero-fills (the padding). A tile is `rows` image rows of one image
+// (rows*Wd <= 128 pixels) or, for small images, several whole images. With `ep` the bias / relu / mask output stage
+// is applied to the accumulator (forward product of a layer).
 // returns 0 done, 1 error, -1 not eligible
-int conv_dgrad_tma(const float* dy, long B, int Ho, int Wo, int Cin, const float* wr, int C, int H, int W, int kh, int kw,
-                   int ph, int pw, float* dx) {
-  if (B <= 0 || C <= 0 || H <= 0 || W <= 0) return 0;
-  if (Cin % 32 != 0 || C % 16 != 0 || C > 128 || W > 128 || B >= (1L << 30) || kh <= 0 || kw <= 0) return -1;
-  if (((uintptr_t)dy & 15) != 0 || ((uintptr_t)wr & 15) != 0) return -1;
-  const long K = (long)kh * kw * Cin;
-  const int HW = H * W;
+int conv_implicit_tma(const float* src, long B, int Hs, int Ws, int Cs, const float* wr, int N, int Hd, int Wd, int kh, int kw,
+                      int ph, int pw, int sign, float* out, const ConvEpilogue* ep) {
+  if (B <= 0 || N <= 0 || Hd <= 0 || Wd <= 0) return 0;
+  if (Cs % 32 != 0 || N % 16 != 0 || Wd > 128 || B >= (1L << 30) || kh <= 0 || kw <= 0) return -1;
+  if (((uintptr_t)src & 15) != 0 || ((uintptr_t)wr & 15) != 0) return -1;
+  const long K = (long)kh * kw * Cs;
+  const int HW = Hd * Wd;
   TmaParams p;
-  p.conv = 1;
+  memset(&p, 0, sizeof(p));
   p.ep = ConvEpilogue{nullptr, nullptr, nullptr, 1};
-  p.swapped = 0;
-  p.cW = W;
+  if (ep) p.ep = *ep;
+  p.csign = sign;
+  p.cW = Wd;
   p.cHW = HW;
-  p.cC = C;
+  p.cC = N;
   p.ckw = kw;
-  p.ckpt = Cin / 32;
+  p.ckpt = Cs / 32;
   p.cph = ph;
   p.cpw = pw;
   p.cB = (int)B;
+  const long want = (long)rt().sm_count;
   long tiles;
   if (HW <= 128) {
-    p.cnimg = (int)std::min<long>(128 / HW, B);
-    p.crows = H;
+    // several small images per tile, but not so many that the tile count falls below the number of SMs
+    long nimg = std::min<long>(128 / HW, B);
+    while (nimg > 1 && cgtb_ceil_div(B, nimg) < want) --nimg;
+    p.cnimg = (int)nimg;
+    p.crows = Hd;
     p.cnbands = 1;
     tiles = cgtb_ceil_div(B, p.cnimg);
   } else {
     p.cnimg = 1;
-    const int max_rows = 128 / W;
-    p.cnbands = (int)cgtb_ceil_div(H, max_rows);
-    p.crows = (int)cgtb_ceil_div(H, p.cnbands);  // equal bands
+    const int max_rows = 128 / Wd;
+    p.cnbands = (int)cgtb_ceil_div(Hd, max_rows);
+    p.crows = (int)cgtb_ceil_div(Hd, p.cnbands);  // equal bands
     tiles = B * p.cnbands;
   }
-  if (tiles > 2147483647L) return -1;
-  p.cx_tx = 32 * W * p.crows * p.cnimg * (int)sizeof(float);
-  const int UN = C;
+  if (tiles > 2147483647L / 8) return -1;
+  p.cx_tx = 32 * Wd * p.crows * p.cnimg * (int)sizeof(float);
+  const int ytiles = (int)cgtb_ceil_div(N, 128);
+  int UN = (int)(cgtb_ceil_div(cgtb_ceil_div(N, ytiles), 16) * 16);
+  if (UN * ytiles != N) return -1;  // equal column tiles only
   p.UN = UN;
   p.tmem_cols = 32;
   while (p.tmem_cols < 2 * UN) p.tmem_cols *= 2;
   p.xrows = 0;
-  p.yrows = C;
+  p.yrows = N;
   const long conv_bytes = 1L * kXRows * 128 + 2L * UN * 128, raw_bytes = (long)kXRows * 128 + (long)UN * 128;
   int conv_stages, raw_stages;
-  const long half = 110L * 1024 - 1024, whole = 224L * 1024 - 1024;
-  if ((half - 2 * conv_bytes) / raw_bytes >= 3) {
-    conv_stages = 2;
-    raw_stages = (int)std::min<long>(kMaxRaw, (half - 2 * conv_bytes) / raw_bytes);
-  } else if ((half - conv_bytes) / raw_bytes >= 2) {
-    conv_stages = 1;
-    raw_stages = (int)std::min<long>(kMaxRaw, (half - conv_bytes) / raw_bytes);
-  } else {
-    conv_stages = 2;
-    raw_stages = (int)std::min<long>(kMaxRaw, (whole - 2 * conv_bytes) / raw_bytes);
-    if (raw_stages < 2) return -1;
-  }
   const long nkb = K / kBK;
-  if (raw_stages > nkb) raw_stages = (int)nkb;
-  if (conv_stages > nkb) conv_stages = (int)nkb;
+  if (!choose_stages(conv_bytes, raw_bytes, nkb, &conv_stages, &raw_stages)) return -1;
   // few tiles with a long K loop (small images, many taps): split K over CTAs, each split writing its own
-  // copy of the result
+  // copy of the result. Not with the output stage, which needs whole sums.
   int nsplit = 1;
-  const long want = (long)rt().sm_count;
-  if (tiles < want && nkb >= 8) nsplit = (int)std::max<long>(1, std::min<long>(std::max<long>(1, (2 * want) / tiles), nkb / 4));
+  if (!ep && tiles * ytiles < want && nkb >= 8)
+    nsplit = (int)std::max<long>(1, std::min<long>(std::max<long>(1, (2 * want) / (tiles * ytiles)), nkb / 4));
   const long kchunk = cgtb_ceil_div(nkb, nsplit) * kBK;
   nsplit = (int)cgtb_ceil_div(K, kchunk);
-  if (nsplit > 65535) return -1;
-  const long nkb_split = kchunk / kBK;
-  if (raw_stages > nkb_split) raw_stages = (int)nkb_split;
-  if (conv_stages > nkb_split) conv_stages = (int)nkb_split;
   p.conv_stages = conv_stages;
   p.raw_stages = raw_stages;
   p.nsplit = nsplit;
   p.kchunk = kchunk;
   p.K = K;
   p.M = B * HW;
-  p.N = C;
-  p.ldc = C;
+  p.N = N;
+  p.ldc = N;
   p.c_batch_stride = 0;
-  const long total = B * (long)C * HW;
+  p.xtiles = (int)tiles;
+  p.ytiles = ytiles;
+  p.total_tiles = tiles * ytiles * nsplit;
+  const long total = B * (long)N * HW;
   float* part = nullptr;
   if (nsplit > 1) {
     part = (float*)scratch((size_t)nsplit * total * sizeof(float));
     if (!part) return 1;
     p.C = part;
   } else {
-    p.C = dx;
+    p.C = out;
   }
   p.err = tc_error_flag();
   if (!p.err) return 1;
@@ -665,25 +799,120 @@ int conv_dgrad_tma(const float* dy, long B, int Ho, int Wo, int Cin, const float
   if (!fn) return -1;
   CUtensorMap mapX, mapY;
   {
-    cuuint64_t dims[4] = {(cuuint64_t)Cin, (cuuint64_t)Wo, (cuuint64_t)Ho, (cuuint64_t)B};
-    cuuint64_t strides[3] = {(cuuint64_t)Cin * 4, (cuuint64_t)Wo * Cin * 4, (cuuint64_t)Ho * Wo * Cin * 4};
-    cuuint32_t box[4] = {32, (cuuint32_t)W, (cuuint32_t)p.crows, (cuuint32_t)p.cnimg};
+    cuuint64_t dims[4] = {(cuuint64_t)Cs, (cuuint64_t)Ws, (cuuint64_t)Hs, (cuuint64_t)B};
+    cuuint64_t strides[3] = {(cuuint64_t)Cs * 4, (cuuint64_t)Ws * Cs * 4, (cuuint64_t)Hs * Ws * Cs * 4};
+    cuuint32_t box[4] = {32, (cuuint32_t)Wd, (cuuint32_t)p.crows, (cuuint32_t)p.cnimg};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     if (box[1] > 256 || box[2] > 256 || box[3] > 256) return -1;
-    CUresult r = fn(&mapX, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)dy, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    CUresult r = fn(&mapX, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)src, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return -1;
   }
-  Side Y = {wr, K, false, C, 0};
+  Side Y = {wr, K, false, N, 0};
   if (!encode(&mapY, Y, K, 1, UN)) return -1;
   size_t smem = (size_t)conv_stages * conv_bytes + (size_t)raw_stages * raw_bytes + 1024;
-  dim3 grid((unsigned)tiles, 1, (unsigned)nsplit);
-  const int cap = 227 * 1024 - 2048;
-  static bool cfg = false;
-  if (!cfg) { CGTB_CUDA_TRY(cudaFuncSetAttribute(sgemm_tma_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap)); cfg = true; }
-  CGTB_LAUNCH((sgemm_tma_kernel<false, false>), grid, kThreadsTma, smem, mapX, mapY, p);
-  if (nsplit > 1) tc_splitk_fold(1, 1, total, nsplit, part, dx, total, 0);
-  CGTB_CHECK_LAUNCH("conv_dgrad");
+  int rc = launch_tma<false, false, 1>(mapX, mapY, p, smem);
+  if (rc) return rc;
+  if (nsplit > 1) tc_splitk_fold(1, 1, total, nsplit, part, out, total, 0);
+  CGTB_CHECK_LAUNCH("conv_implicit");
+  return 0;
+}
+
+// Filter gradient of a stride-1 convolution without a column matrix (the reference forms Mul22{T,N}(dy, col) on the
+// Im2Col output: cgt/nn.py:93-100 differentiated, cgt/core.py:2162-2175):
+//   dw[n][c][i][j] = sum_{b, y, x} dy[b, y, x, n] * src[b, y + i - ph, x + j - pw, c]
+// src NHWC [B, Hs, Ws, Cs], dy NHWC [B, Hd, Wd, N], dw [N][Cs*kh*kw] (the filter bank's own layout). It is the product
+// dy^T . col with the sum over pixels as the K dimension: a K block is `wbh` rows of one image (at most 32 pixels, the
+// rest of the block's K slots are zeros); an X tile holds four (tap, 32-channel) units, each the same pixels of src
+// shifted by its tap (one TMA box per unit, out-of-range rows and columns zero-filled); the conversion warps
+// transpose both operands into the K-major layout while splitting them. K is split over CTAs, every split writes
+// its own slab in dw's layout and an ordered fold adds the slabs.
+// returns 0 done, 1 error, -1 not eligible
+int conv_wgrad_tma(const float* src, long B, int Hs, int Ws, int Cs, const float* dy, int Hd, int Wd, int N, int kh, int kw, int ph,
+                   int pw, float* dw) {
+  if (N <= 0 || Cs <= 0 || kh <= 0 || kw <= 0) return 0;
+  if (Cs % 32 != 0 || N % 16 != 0 || Wd > 32 || Wd <= 0 || Hd <= 0 || B <= 0 || B >= (1L << 24)) return -1;
+  if (((uintptr_t)src & 15) != 0 || ((uintptr_t)dy & 15) != 0) return -1;
+  const long Kc = (long)kh * kw * Cs;  // columns of the result
+  TmaParams p;
+  memset(&p, 0, sizeof(p));
+  p.ep = ConvEpilogue{nullptr, nullptr, nullptr, 1};
+  p.ckw = kw;
+  p.ckpt = Cs / 32;
+  p.cph = ph;
+  p.cpw = pw;
+  p.wkk = kh * kw;
+  p.wunits = kh * kw * (Cs / 32);
+  p.wbh = std::min<int>(32 / Wd, Hd);
+  p.wnrg = (int)cgtb_ceil_div(Hd, p.wbh);
+  p.wnpx = p.wbh * Wd;
+  const int ytiles = (int)cgtb_ceil_div(N, 128);
+  int UN = (int)(cgtb_ceil_div(cgtb_ceil_div(N, ytiles), 16) * 16);
+  if (UN * ytiles != N) return -1;
+  p.UN = UN;
+  p.tmem_cols = 32;
+  while (p.tmem_cols < 2 * UN) p.tmem_cols *= 2;
+  p.yrows = N;
+  p.xrows = Kc;
+  const long xtiles = cgtb_ceil_div(p.wunits, 4);
+  const long nkb_total = B * p.wnrg;
+  const long conv_bytes = 2L * kXRows * 128 + 2L * UN * 128, raw_bytes = (long)kXRows * 128 + (long)UN * 128;
+  int conv_stages, raw_stages;
+  if (!choose_stages(conv_bytes, raw_bytes, nkb_total, &conv_stages, &raw_stages)) return -1;
+  const long tiles = xtiles * ytiles;
+  const long want = (long)rt().sm_count;
+  int nsplit = 1;
+  if (tiles < 2 * want && nkb_total >= 8) nsplit = (int)std::max<long>(1, std::min<long>((2 * want) / tiles, nkb_total / 4));
+  const long kchunk = cgtb_ceil_div(nkb_total, nsplit) * kBK;
+  nsplit = (int)cgtb_ceil_div(nkb_total * kBK, kchunk);
+  p.conv_stages = conv_stages;
+  p.raw_stages = raw_stages;
+  p.nsplit = nsplit;
+  p.kchunk = kchunk;
+  p.K = nkb_total * kBK;
+  p.M = N;
+  p.N = Kc;
+  p.ldc = Kc;
+  p.c_batch_stride = 0;
+  p.xtiles = (int)xtiles;
+  p.ytiles = ytiles;
+  p.total_tiles = tiles * nsplit;
+  p.swapped = 1;
+  float* part = nullptr;
+  if (nsplit > 1) {
+    part = (float*)scratch((size_t)nsplit * N * Kc * sizeof(float));
+    if (!part) return 1;
+    p.C = part;
+  } else {
+    p.C = dw;
+  }
+  p.err = tc_error_flag();
+  if (!p.err) return 1;
+  EncodeTiledFn fn = encoder();
+  if (!fn) return -1;
+  CUtensorMap mapX, mapY;
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  {
+    cuuint64_t dims[4] = {(cuuint64_t)Cs, (cuuint64_t)Ws, (cuuint64_t)Hs, (cuuint64_t)B};
+    cuuint64_t strides[3] = {(cuuint64_t)Cs * 4, (cuuint64_t)Ws * Cs * 4, (cuuint64_t)Hs * Ws * Cs * 4};
+    cuuint32_t box[4] = {32, (cuuint32_t)Wd, (cuuint32_t)p.wbh, 1};
+    CUresult r = fn(&mapX, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)src, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return -1;
+  }
+  {
+    cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)Wd, (cuuint64_t)Hd, (cuuint64_t)B};
+    cuuint64_t strides[3] = {(cuuint64_t)N * 4, (cuuint64_t)Wd * N * 4, (cuuint64_t)Hd * Wd * N * 4};
+    cuuint32_t box[4] = {(cuuint32_t)UN, (cuuint32_t)Wd, (cuuint32_t)p.wbh, 1};
+    CUresult r = fn(&mapY, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)dy, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return -1;
+  }
+  size_t smem = (size_t)conv_stages * conv_bytes + (size_t)raw_stages * raw_bytes + 1024;
+  int rc = launch_tma<true, true, 2>(mapX, mapY, p, smem);
+  if (rc) return rc;
+  if (nsplit > 1) tc_splitk_fold(1, N, Kc, nsplit, part, dw, Kc, 0);
+  CGTB_CHECK_LAUNCH("conv_wgrad");
   return 0;
 }
 
@@ -692,9 +921,37 @@ int conv_dgrad_tma(const float* dy, long B, int Ho, int Wo, int Cin, const float
 CGTB_API int cgtb_conv_dgrad(const float* dy_nhwc, long B, int Ho, int Wo, int Cin, const float* w_rearranged, int C, int H, int W,
                              int kh, int kw, int ph, int pw, float* dx_nchw) {
   if (!require_runtime("cgtb_conv_dgrad")) return 1;
-  int rc = cgtb::conv_dgrad_tma(dy_nhwc, B, Ho, Wo, Cin, w_rearranged, C, H, W, kh, kw, ph, pw, dx_nchw);
+  if (C > 128) return fail("cgtb_conv_dgrad: at most 128 image channels");
+  int rc = cgtb::conv_implicit_tma(dy_nhwc, B, Ho, Wo, Cin, w_rearranged, C, H, W, kh, kw, ph, pw, -1, dx_nchw, nullptr);
   if (rc < 0)
     return fail("cgtb_conv_dgrad: not supported for Cin=%d (multiple of 32), C=%d (multiple of 16, at most 128), W=%d (at most 128) "
                 "or an unaligned operand; use cgtb_sgemm + cgtb_col2im", Cin, C, W);
+  return rc;
+}
+
+CGTB_API int cgtb_conv_fwd_bias_relu(const float* x_nhwc, long B, int H, int W, int Cin, const float* w_rearranged, int Cout, int Ho,
+                                     int Wo, int kh, int kw, int ph, int pw, const float* bias, float* y_nchw, int8_t* mask_nchw) {
+  if (!require_runtime("cgtb_conv_fwd_bias_relu")) return 1;
+  if (Ho != H + 2 * ph - kh + 1 || Wo != W + 2 * pw - kw + 1)
+    return fail("cgtb_conv_fwd_bias_relu: output %dx%d is not that of a stride-1 %dx%d convolution of %dx%d with padding %d,%d", Ho, Wo,
+                kh, kw, H, W, ph, pw);
+  cgtb::ConvEpilogue ep = {bias, y_nchw, mask_nchw, (long)Ho * Wo};
+  int rc = cgtb::conv_implicit_tma(x_nhwc, B, H, W, Cin, w_rearranged, Cout, Ho, Wo, kh, kw, ph, pw, +1, nullptr, &ep);
+  if (rc < 0)
+    return fail("cgtb_conv_fwd_bias_relu: not supported for Cin=%d (multiple of 32), Cout=%d (multiple of 16; of 128 when above 128), "
+                "Wo=%d (at most 128) or an unaligned operand; use cgtb_im2col + cgtb_conv_bias_relu", Cin, Cout, Wo);
+  return rc;
+}
+
+CGTB_API int cgtb_conv_wgrad(const float* x_nhwc, long B, int H, int W, int Cin, const float* dy_nhwc, int Ho, int Wo, int Cout, int kh,
+                             int kw, int ph, int pw, float* dw) {
+  if (!require_runtime("cgtb_conv_wgrad")) return 1;
+  if (Ho != H + 2 * ph - kh + 1 || Wo != W + 2 * pw - kw + 1)
+    return fail("cgtb_conv_wgrad: gradient %dx%d is not that of a stride-1 %dx%d convolution of %dx%d with padding %d,%d", Ho, Wo, kh,
+                kw, H, W, ph, pw);
+  int rc = cgtb::conv_wgrad_tma(x_nhwc, B, H, W, Cin, dy_nhwc, Ho, Wo, Cout, kh, kw, ph, pw, dw);
+  if (rc < 0)
+    return fail("cgtb_conv_wgrad: not supported for Cin=%d (multiple of 32), Cout=%d (multiple of 16; of 128 when above 128), Wo=%d "
+                "(at most 32) or an unaligned operand; use cgtb_im2col + cgtb_sgemm", Cin, Cout, Wo);
   return rc;
 }

@@ -306,6 +306,41 @@ OP_BYREF(cgtb_op_conv_dgrad) {
   cgtb_conv_dgrad((const float*)dy->data(), s[0], (int)s[1], (int)s[2], (int)s[3], (const float*)wr->data(), (int)d[1], (int)d[2],
                   (int)d[3], cl->kernel_h, cl->kernel_w, cl->pad_h, cl->pad_w, (float*)dx->data());
 }
+// ConvFwdBiasRelu: (x NHWC [B,H,W,Cin], filters rearranged to [Cout,kh,kw,Cin], bias [1,Cout,1,1], B, Cout, Ho, Wo)
+// -> tuple(mask i1 NCHW, y f4 NCHW): a stride-1 convolution layer's forward pass without a column matrix
+OP_BYREF(cgtb_op_conv_fwd_bias_relu) {
+  ConvClosure* cl = (ConvClosure*)cl0;
+  cgtArray *x = ARR(reads[0]), *wr = ARR(reads[1]), *bias = ARR(reads[2]);
+  cgtTuple* out = (cgtTuple*)write0;
+  cgtArray *mask = ARR(out->getitem(0)), *y = ARR(out->getitem(1));
+  if (!all_gpu({x, wr, bias, mask, y})) { fail("ConvFwdBiasRelu: operands must be on the GPU"); return; }
+  const long* s = x->shape();
+  const long* d = y->shape();
+  if (x->ndim() != 4 || wr->ndim() != 4 || y->ndim() != 4 || x->dtype() != cgt_f4 || wr->shape()[0] != d[1] ||
+      wr->shape()[1] != cl->kernel_h || wr->shape()[2] != cl->kernel_w || wr->shape()[3] != s[3] || s[0] != d[0] ||
+      bias->size() != d[1] || mask->size() != y->size()) {
+    fail("ConvFwdBiasRelu: operand shapes do not fit together");
+    return;
+  }
+  cgtb_conv_fwd_bias_relu((const float*)x->data(), s[0], (int)s[1], (int)s[2], (int)s[3], (const float*)wr->data(), (int)d[1],
+                          (int)d[2], (int)d[3], cl->kernel_h, cl->kernel_w, cl->pad_h, cl->pad_w, (const float*)bias->data(),
+                          (float*)y->data(), (int8_t*)mask->data());
+}
+// ConvWgradImplicit: (x NHWC [B,H,W,Cin], dy NHWC [B,Ho,Wo,Cout]) -> filter gradient [Cout, Cin*kh*kw]
+OP_BYREF(cgtb_op_conv_wgrad_implicit) {
+  ConvClosure* cl = (ConvClosure*)cl0;
+  cgtArray *x = ARR(reads[0]), *dy = ARR(reads[1]), *dw = ARR(write0);
+  if (!all_gpu({x, dy, dw})) { fail("ConvWgradImplicit: operands must be on the GPU"); return; }
+  const long* s = x->shape();
+  const long* g = dy->shape();
+  if (x->ndim() != 4 || dy->ndim() != 4 || dw->ndim() != 2 || x->dtype() != cgt_f4 || dy->dtype() != cgt_f4 || s[0] != g[0] ||
+      dw->shape()[0] != g[3] || dw->shape()[1] != s[3] * cl->kernel_h * cl->kernel_w) {
+    fail("ConvWgradImplicit: operand shapes do not fit together");
+    return;
+  }
+  cgtb_conv_wgrad((const float*)x->data(), s[0], (int)s[1], (int)s[2], (int)s[3], (const float*)dy->data(), (int)g[1], (int)g[2],
+                  (int)g[3], cl->kernel_h, cl->kernel_w, cl->pad_h, cl->pad_w, (float*)dw->data());
+}
 OP_BYREF(cgtb_op_max_pool) {
   ConvClosure* cl = (ConvClosure*)cl0;
   cgtArray* x = ARR(reads[0]);

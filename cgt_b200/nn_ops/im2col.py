@@ -204,3 +204,67 @@ class ConvWgrad(core.Op):
 
     def __repr__(self):
         return "ConvWgrad{%d}" % self.k
+
+
+class ConvFwdBiasRelu(core.Op):
+    """(x NHWC [B,H,W,Cin], filters rearranged to [Cout,kh,kw,Cin], bias [1,Cout,1,1], B, Cout, Ho, Wo) ->
+    tuple(mask i1, relu f4), both NCHW [B,Cout,Ho,Wo]: the forward pass of a stride-1 convolution layer in one kernel.
+
+    Not part of the reference's Op set. The compiler substitutes it (compilation.fuse_conv_implicit) for
+    ConvBiasRelu(Reshape(Im2Col(x)), ...), i.e. for the sequence that nn.conv2d / SpatialConvolution / rectify spell
+    out (cgt/nn.py:87-100, 228-233, 44-45; include/im2col.h:6-28), when the extents allow; the column matrix is then
+    neither written nor read. The sum over a patch runs in (tap, channel) order instead of (channel, tap): float32
+    tolerance against the Op sequence."""
+    available_impls = ("native_gpu",)
+
+    def __init__(self, info):
+        assert info.stride_h == 1 and info.stride_w == 1
+        self.info = info
+
+    def get_diff(self, n):
+        return [False] * n
+
+    def shp_apply(self, inputs):
+        shp = list(inputs[3:])
+        return (shp, list(shp))
+
+    def typ_apply(self, inputs):
+        return core.TupleType(core.TensorType("i1", 4), core.TensorType("f4", 4))
+
+    def host_inputs(self, n):
+        return tuple(range(3, n))
+
+    def get_native_compile_info(self, input_types, devtype):
+        return core.NativeCompileInfo(None, prebuilt="cgtb_op_conv_fwd_bias_relu", closure_triples=info2closure(self.info))
+
+    def __repr__(self):
+        return "ConvFwdBiasRelu{%s}" % (tuple(self.info),)
+
+
+class ConvWgradImplicit(core.Op):
+    """(x NHWC [B,H,W,Cin], dy NHWC [B,Ho,Wo,Cout]) -> filter gradient [Cout, Cin*kh*kw] of a stride-1 convolution.
+
+    Not part of the reference's Op set. The compiler substitutes it (compilation.fuse_conv_implicit) for
+    Mul22{T,N}(dy, Reshape(Im2Col(x))), which differentiating nn.conv2d yields (cgt/nn.py:93-100,
+    cgt/core.py:2162-2175), together with ConvFwdBiasRelu, so that the column matrix disappears from the step."""
+    available_impls = ("native_gpu",)
+
+    def __init__(self, info):
+        assert info.stride_h == 1 and info.stride_w == 1
+        self.info = info
+
+    def get_diff(self, n):
+        return [False] * n
+
+    def shp_apply(self, inputs):
+        cin = core.cgt.size(inputs[0], 3)
+        return [core.cgt.size(inputs[1], 3), cin * (self.info.kernel_h * self.info.kernel_w)]
+
+    def typ_apply(self, inputs):
+        return core.TensorType("f4", 2)
+
+    def get_native_compile_info(self, input_types, devtype):
+        return core.NativeCompileInfo(None, prebuilt="cgtb_op_conv_wgrad_implicit", closure_triples=info2closure(self.info))
+
+    def __repr__(self):
+        return "ConvWgradImplicit{%s}" % (tuple(self.info),)

@@ -80,6 +80,13 @@ def _declare(lib):
         "cgtb_max_pool_pullback": (ci, [ci, vp, vp, cl] + [ci] * 11 + [vp]),
         "cgtb_lrn_forward": (ci, [ci, vp, cl, ci, ci, ci, ci, cd, cd, vp, vp]),
         "cgtb_lrn_backward": (ci, [ci, vp, vp, vp, vp, cl, ci, ci, ci, ci, cd, cd, vp]),
+        "cgtb_conv_dgrad": (ci, [vp, cl, ci, ci, ci, vp] + [ci] * 7 + [vp]),
+        "cgtb_conv_fwd_bias_relu": (ci, [vp, cl, ci, ci, ci, vp] + [ci] * 7 + [vp, vp, vp]),
+        "cgtb_conv_wgrad": (ci, [vp, cl, ci, ci, ci, vp] + [ci] * 7 + [vp]),
+        "cgtb_conv_bias_relu": (ci, [vp, cl, cl, vp, ci, vp, cl, vp, vp]),
+        "cgtb_conv_bias_relu_ld": (ci, [vp, cl, cl, cl, vp, ci, vp, cl, vp, vp]),
+        "cgtb_relu_grad_nhwc": (ci, [vp, vp, cl, ci, cl, vp, vp]),
+        "cgtb_im2col_ld": (ci, [ci, vp, cl] + [ci] * 9 + [cl, vp]),
         "cgtb_unary": (ci, [ci, ci, ci, cl, vp, vp]), "cgtb_binary": (ci, [ci, ci, ci, ci, cl, vp, vp, vp, ci, ci]),
         "cgtb_reduce": (ci, [ci, ci, ci, c_long_p, c_int_p, vp, vp]),
         "cgtb_repeat": (ci, [ci, ci, c_long_p, c_int_p, vp, vp]),

@@ -178,6 +178,24 @@ int cgtb_lrn_backward(int dtype, const void* x, const void* top, const void* sca
 int cgtb_conv_dgrad(const float* dy_nhwc, long B, int Ho, int Wo, int Cin, const float* w_rearranged, int C, int H, int W,
                     int kh, int kw, int ph, int pw, float* dx_nchw);
 
+/* Forward pass of a stride-1 convolution layer in one kernel, without a column matrix: replaces Im2Col, Mul22,
+ * Reshape, Transpose{0,3,1,2}, Repeat, ElwiseBinary +, >=, * of cgt/nn.py:87-100, 44-45, 228-233 (include/im2col.h:6-28).
+ *   t[b, n, y, x] = bias[n] + sum_{i, j, c} x[b, y + i - ph, x + j - pw, c] * w_rearranged[n][(i*kw + j)*Cin + c]
+ *   mask = (t >= 0), y = t * mask
+ * x_nhwc [B, H, W, Cin]; w_rearranged [Cout][kh*kw*Cin] (the filter bank [Cout, Cin, kh, kw] transposed to
+ * [Cout, kh, kw, Cin]); y_nchw, mask_nchw [B, Cout, Ho, Wo] with Ho = H + 2 ph - kh + 1. float32, 3xTF32 like cgtb_sgemm;
+ * the sum runs over (tap, channel) instead of (channel, tap), so values agree with cgtb_conv_bias_relu to float32
+ * rounding, not bit for bit. Supported: Cin a multiple of 32, Cout a multiple of 16 (of 128 above 128), Wo <= 128. */
+int cgtb_conv_fwd_bias_relu(const float* x_nhwc, long B, int H, int W, int Cin, const float* w_rearranged, int Cout, int Ho,
+                            int Wo, int kh, int kw, int ph, int pw, const float* bias, float* y_nchw, int8_t* mask_nchw);
+/* Filter gradient of a stride-1 convolution in one kernel (plus an ordered fold of its K splits), without a column
+ * matrix: replaces Mul22{T,N}(dy, Im2Col(x)) of the differentiated cgt/nn.py:93-100 (cgt/core.py:2162-2175).
+ *   dw[n][c][i][j] = sum_{b, y, x} dy[b, y, x, n] * x[b, y + i - ph, x + j - pw, c]
+ * x_nhwc [B, H, W, Cin]; dy_nhwc [B, Ho, Wo, Cout]; dw [Cout][Cin*kh*kw]. float32, 3xTF32.
+ * Supported: Cin a multiple of 32, Cout a multiple of 16 (of 128 above 128), Wo <= 32. */
+int cgtb_conv_wgrad(const float* x_nhwc, long B, int H, int W, int Cin, const float* dy_nhwc, int Ho, int Wo, int Cout, int kh,
+                    int kw, int ph, int pw, float* dw);
+
 /* Output stage of a convolution layer in one call: Mul22(col, w^T) -> NCHW -> + bias -> relu with its mask.
  * Replaces the Op sequence Mul22, Reshape, Transpose{0,3,1,2}, Repeat, ElwiseBinary +, >=, * of cgt/nn.py:87-100,
  * 44-45, 228-233; values are bit-identical to that sequence run through cgtb_sgemm and the elementwise kernels.

@@ -173,8 +173,9 @@ def test_conv_output_substitution_changes_no_bit(rt):
     """ConvBiasRelu (GEMM + NCHW + bias + relu in one call) gives the bits of the Op sequence it replaces."""
     res = {}
     for fuse in (False, True):
-        # padded column rows apply only next to ConvBiasRelu and change which product kernel runs: off here
-        with cgt.scoped_update_config(fuse_conv_output=fuse, pad_conv_columns=False, use_cuda_graphs=False):
+        # padded column rows apply only next to ConvBiasRelu and change which product kernel runs: off here; the
+        # convolutions without a column matrix sum in another order: off here too
+        with cgt.scoped_update_config(fuse_conv_output=fuse, pad_conv_columns=False, fuse_conv_implicit=False, use_cuda_graphs=False):
             cfg = configs.BUILDERS["cifar"](**SMALL["cifar"])
             f = cfg.compile()
             names = [repr(instr) for instr in f.eg.instrs]
@@ -350,3 +351,27 @@ def test_user_op_with_cuda_source_runs_on_the_gpu(rt, graphs):
         if graphs:
             st = f.stats()
             assert st["segments_captured"] >= 1 and st["last_graph_launches"] >= 1, st
+
+
+@pytest.mark.parametrize("name", ["cifar", "wide"])
+def test_conv_implicit_substitution(rt, name):
+    """ConvFwdBiasRelu / ConvWgradImplicit replace Im2Col + ConvBiasRelu + Mul22{T,N} for the stride-1 convolutions with
+    32-channel-aligned inputs (CIFAR conv2 and conv3, the wide net's conv2): those column matrices disappear; losses and
+    parameters stay within float32 tolerance of the graph that keeps them."""
+    res = {}
+    for fuse in (False, True):
+        with cgt.scoped_update_config(fuse_conv_implicit=fuse, use_cuda_graphs=False):
+            cfg = configs.BUILDERS[name](**SMALL[name])
+            f = cfg.compile()
+            names = [repr(instr) for instr in f.eg.instrs]
+            batches = [cfg.batch(seed) for seed in range(2)]
+            losses = [float(f(*batches[i % 2])[0]) for i in range(6)]
+            params = [np.asarray(p.op.get_value()).copy() for p in cfg.params]
+            res[fuse] = (sum("ConvFwdBiasRelu" in n for n in names), sum("ConvWgradImplicit" in n for n in names),
+                         sum("op:Im2Col" in n for n in names), losses, params)
+    n_conv = {"cifar": 2, "wide": 1}[name]
+    assert res[False][:2] == (0, 0) and res[True][:2] == (n_conv, n_conv)
+    assert res[False][2] == n_conv + 1 and res[True][2] == 1   # only the 3-channel first layer keeps its column matrix
+    np.testing.assert_allclose(res[True][3], res[False][3], rtol=1e-4)
+    for (a, b) in zip(res[True][4], res[False][4]):
+        np.testing.assert_allclose(a, b, rtol=1e-3, atol=1e-5)

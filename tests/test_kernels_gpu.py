@@ -480,6 +480,73 @@ def test_conv_dgrad_matches_gemm_then_col2im(rt, B, C, H, W, Cin, k, pad):
     np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-5 * scale)
 
 
+CONV_IMPLICIT = [
+    # (B, Cin, H, W, Cout, k, pad): CIFAR conv2 / conv3 (scaled batch and batch 128), the wide net's conv2 (three K blocks
+    # per tap, two column tiles), bands that do not divide the image, 1x1 and unpadded kernels, a last tile with missing images
+    (8, 32, 15, 15, 32, 5, 2), (7, 32, 6, 6, 64, 5, 2), (128, 32, 15, 15, 32, 5, 2), (128, 32, 6, 6, 64, 5, 2),
+    (6, 96, 6, 6, 256, 5, 2), (3, 32, 20, 9, 16, 3, 1), (2, 64, 7, 5, 48, 1, 0), (5, 32, 4, 4, 32, 3, 0), (300, 32, 3, 3, 16, 3, 1),
+]
+
+
+@pytest.mark.parametrize("B,Cin,H,W,Cout,k,pad", CONV_IMPLICIT)
+def test_conv_fwd_bias_relu_matches_im2col_then_gemm(rt, B, Cin, H, W, Cout, k, pad):
+    """cgtb_conv_fwd_bias_relu against the sequence it replaces, evaluated by the CPU oracle: Im2Col, Mul22(col, W^T),
+    NCHW, + bias, relu with its mask."""
+    rs = np.random.RandomState(44)
+    Ho, Wo = H + 2 * pad - k + 1, W + 2 * pad - k + 1
+    x = rs.randn(B, Cin, H, W).astype("f4")
+    Wf = (rs.randn(Cout, Cin, k, k) / np.sqrt(Cin * k * k)).astype("f4")
+    bias = (0.1 * rs.randn(Cout)).astype("f4")
+    col = O.im2col(x, (k, k), (pad, pad), (1, 1)).reshape(B * Ho * Wo, Cin * k * k)
+    want_t = (O.mul22(col, Wf.reshape(Cout, -1), 0, 1) + bias).reshape(B, Ho * Wo, Cout).transpose(0, 2, 1)
+    exact_t = (col.astype("f8") @ Wf.reshape(Cout, -1).astype("f8").T + bias.astype("f8")).reshape(B, Ho * Wo, Cout).transpose(0, 2, 1)
+    xn = np.ascontiguousarray(x.transpose(0, 2, 3, 1))
+    wr = np.ascontiguousarray(Wf.transpose(0, 2, 3, 1))
+    dx, dw, db = Dev(xn), Dev(wr), Dev(bias)
+    y, mask = Dev(np.full((B, Cout, Ho * Wo), np.nan, "f4")), Dev(np.full((B, Cout, Ho * Wo), 7, "i1"))
+    call("cgtb_conv_fwd_bias_relu", dx.ptr, B, H, W, Cin, dw.ptr, Cout, Ho, Wo, k, k, pad, pad, db.ptr, y.ptr, mask.ptr)
+    got, gmask = y.get(), mask.get()
+    assert set(np.unique(gmask)) <= {0, 1}
+    K = Cin * k * k
+    sure = np.abs(exact_t) > 1e-4 * np.sqrt(K)
+    assert np.array_equal(gmask[sure], (exact_t >= 0)[sure].astype("i1"))
+    on = gmask == 1
+    scale = np.sqrt(K)
+    assert np.abs(got[on] - exact_t[on]).max() <= 4 * np.abs(want_t[on] - exact_t[on]).max() + 1e-5 * scale
+    np.testing.assert_allclose(got[on], want_t[on], rtol=1e-4, atol=1e-5 * scale)
+    assert (got[~on] == 0).all()
+
+
+@pytest.mark.parametrize("B,Cin,H,W,Cout,k,pad", CONV_IMPLICIT + [(2, 32, 9, 32, 16, 3, 1), (3, 32, 5, 17, 32, 3, 1)])
+def test_conv_wgrad_matches_gemm_on_im2col(rt, B, Cin, H, W, Cout, k, pad):
+    """cgtb_conv_wgrad against the product it replaces, evaluated by the CPU oracle: Mul22{T,N}(dy, Im2Col(x))."""
+    rs = np.random.RandomState(45)
+    Ho, Wo = H + 2 * pad - k + 1, W + 2 * pad - k + 1
+    x = rs.randn(B, Cin, H, W).astype("f4")
+    dy = (rs.randn(B, Ho, Wo, Cout) * (rs.rand(B, Ho, Wo, Cout) > 0.5)).astype("f4")
+    col = O.im2col(x, (k, k), (pad, pad), (1, 1)).reshape(B * Ho * Wo, Cin * k * k)
+    want = O.mul22(dy.reshape(-1, Cout), col, 1, 0)
+    exact = dy.reshape(-1, Cout).astype("f8").T @ col.astype("f8")
+    xn = np.ascontiguousarray(x.transpose(0, 2, 3, 1))
+    dxn, ddy, dwg = Dev(xn), Dev(dy), Dev(np.full((Cout, Cin * k * k), np.nan, "f4"))
+    call("cgtb_conv_wgrad", dxn.ptr, B, H, W, Cin, ddy.ptr, Ho, Wo, Cout, k, k, pad, pad, dwg.ptr)
+    got = dwg.get()
+    scale = np.sqrt(B * Ho * Wo)
+    assert np.abs(got - exact).max() <= 4 * np.abs(want - exact).max() + 1e-5 * scale
+    np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-5 * scale)
+
+
+def test_conv_implicit_refuses_unsupported_extents(rt):
+    d = Dev(shape=(64,), dtype="f4")
+    L = runtime.lib()
+    assert L.cgtb_conv_fwd_bias_relu(d.ptr, 1, 4, 4, 3, d.ptr, 16, 4, 4, 3, 3, 1, 1, d.ptr, d.ptr, d.ptr) != 0
+    assert "not supported" in runtime.last_error()
+    assert L.cgtb_conv_wgrad(d.ptr, 1, 4, 40, 32, d.ptr, 4, 40, 16, 3, 3, 1, 1, d.ptr) != 0
+    assert "not supported" in runtime.last_error()
+    assert L.cgtb_conv_wgrad(d.ptr, 1, 4, 4, 32, d.ptr, 5, 4, 16, 3, 3, 1, 1, d.ptr) != 0
+    assert "stride-1" in runtime.last_error()
+
+
 @pytest.mark.parametrize("B,HW,C,K", [(4, 1024, 32, 75), (8, 225, 32, 800), (16, 36, 64, 800), (3, 10, 48, 40), (2, 7, 16, 5)])
 def test_conv_bias_relu_matches_op_sequence(rt, B, HW, C, K):
     """cgtb_conv_bias_relu against the sequence it replaces, issued through the separate entry points:
