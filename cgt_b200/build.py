@@ -52,7 +52,8 @@ def build(force=False, verbose=False):
         obj = osp.join(OBJDIR, osp.basename(src)[:-3] + ".o")
         objs.append(obj)
         if force or _stale(obj, [src] + deps):
-            cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
+            extra = os.environ.get("CGTB_NVCC_EXTRA", "").split()  # e.g. -DCGTB_TMA_TRACE for a tracing build
+            cmd = [nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
             jobs.append(cmd)
 
     def run(cmd):

@@ -93,6 +93,13 @@ struct TmaParams {
   int wnpx;             // pixels per K block (wbh * width <= 32); the remaining K slots are zero
 };
 
+#ifdef CGTB_TMA_TRACE
+__device__ long long g_tma_trace[128 * 8];
+#define TRACE(kbi, slot) do { if (blockIdx.x == 0 && (kbi) < 128) g_tma_trace[(kbi) * 8 + (slot)] = clock64(); } while (0)
+#else
+#define TRACE(kbi, slot) do { } while (0)
+#endif
+
 struct Tile {
   int xt, yt, batch, split, nkb;
   long k_begin;
@@ -209,6 +216,112 @@ __device__ __forceinline__ void convert_units(const unsigned char* raw, unsigned
   }
 }
 
+// Epilogue of one tile, run by the eight epilogue warps: accumulator (TMEM) -> registers -> global memory.
+template <int CONV, int NCOLGROUPS = kConvWarps / 4>
+__device__ __forceinline__ void store_tile(const TmaParams& p, const Tile& c, uint32_t tmem_d, int quarter, int colgroup, int lane) {
+  const int UN = p.UN;
+  const long x0 = (long)c.xt * kXRows, y0 = (long)c.yt * UN;
+  // Accumulator -> registers -> global memory. A thread owns tile row (quarter*32 + lane) and 8
+  // consecutive columns per chunk (8); columns [0, UN) hold hi*hi + lo*hi and [UN, 2UN) hold hi*lo.
+  const int nchunks = UN / 8;
+  const int row = quarter * 32 + lane;
+  const long i_g = x0 + row;
+  const int batch = c.batch, split = c.split;
+  float* cbase = (p.nsplit > 1) ? p.C + ((long)batch * p.nsplit + split) * p.M * p.N : p.C + batch * p.c_batch_stride;
+  const long ld = (p.nsplit > 1) ? p.N : p.ldc;
+  const bool vec_ok = ((ld & 3) == 0) && (((uintptr_t)cbase & 15) == 0);
+  // where tile row `row` goes when the result is stored as NCHW planes (implicit convolution, or the output
+  // stage of a convolution layer on a stored column matrix)
+  bool pvalid = false;
+  long pb = 0, ppix = 0, pHW = 1, pC = 1;
+  if (CONV == 1) {
+    const int tile = c.xt;
+    pHW = p.cHW;
+    pC = p.cC;
+    if (p.cnimg > 1) {
+      const int li = row / p.cHW;
+      pb = (long)tile * p.cnimg + li;
+      ppix = row - li * p.cHW;
+      pvalid = li < p.cnimg && pb < p.cB;
+    } else {
+      pb = tile / p.cnbands;
+      ppix = (long)(tile - pb * p.cnbands) * p.crows * p.cW + row;
+      pvalid = row < p.crows * p.cW && ppix < p.cHW;
+    }
+  } else if (CONV == 0 && p.ep.y) {
+    pHW = p.ep.HW;
+    pC = p.yrows;
+    pvalid = i_g < p.xrows;
+    pb = i_g / pHW;
+    ppix = i_g - pb * pHW;
+  }
+  // filter gradient: tile row = (unit, channel) -> column (32*chunk + channel)*kh*kw + tap of the result
+  long wcol = -1;
+  if (CONV == 2) {
+    const int unit = c.xt * 4 + (row >> 5);
+    if (unit < p.wunits) {
+      const int tap = unit / p.ckpt, q = unit - tap * p.ckpt;
+      wcol = (long)(32 * q + (row & 31)) * p.wkk + tap;
+    }
+  }
+  for (int ch = colgroup; ch < nchunks; ch += NCOLGROUPS) {
+    const int c0 = ch * 8;
+    uint32_t r1[8], r2[8];
+    const uint32_t taddr = tmem_d + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+    tmem_ld8(taddr, r1);
+    tmem_ld8(taddr + (uint32_t)UN, r2);
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r1[j]) + __uint_as_float(r2[j]);
+    const long j0 = y0 + c0;
+    if (CONV == 2) {
+      if (wcol >= 0) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (j0 + j < p.yrows) cbase[(j0 + j) * ld + wcol] = v[j];
+      }
+    } else if (CONV == 1 || p.ep.y) {
+      // NCHW planes: the lanes of a warp write consecutive pixels of one channel plane
+      if (pvalid) {
+        if (p.ep.y) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (j0 + j < pC) {
+              const float tt = v[j] + p.ep.bias[j0 + j];
+              const int8_t mk = (int8_t)(tt >= 0.f);
+              const size_t o = ((size_t)pb * pC + (j0 + j)) * pHW + ppix;
+              p.ep.mask[o] = mk;
+              p.ep.y[o] = tt * (float)mk;
+            }
+          }
+        } else {
+          // with K splits every split writes its own copy of the whole result; a fold adds them in order
+          float* dst = p.C + (size_t)split * p.cB * pC * pHW + ((size_t)pb * pC + j0) * pHW + ppix;
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (j0 + j < pC) dst[(size_t)j * pHW] = v[j];
+        }
+      }
+    } else if (i_g < p.xrows) {
+      if (!p.swapped) {  // tile row = product row: 32 contiguous bytes per thread
+        float* dst = cbase + i_g * ld + j0;
+        if (vec_ok && j0 + 8 <= p.yrows) {
+          *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+          *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            if (j0 + j < p.yrows) dst[j] = v[j];
+        }
+      } else {           // tile row = product column: the lanes of a warp write consecutive addresses
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (j0 + j < p.yrows) cbase[(j0 + j) * ld + i_g] = v[j];
+      }
+    }
+  }
+}
+
 // One CTA walks tiles t = blockIdx.x, blockIdx.x + gridDim.x, ... of the tile grid (persistent launch): the
 // barriers, the TMEM allocation and the tensor-map fetch are paid once per CTA, and the TMA producer runs ahead
 // across tile boundaries, so that the K blocks of the next tile are in flight while this tile's accumulator is
@@ -263,14 +376,17 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   if (warp < kConvWarps) {
     // ------------------------------------------------ converters, then the tile's epilogue
     int rs = 0, cs = 0;
+    int tkb = 0;
+    (void)tkb;
     uint32_t rphase = 0, cphase = 0, it = 0;
     for (long t = blockIdx.x; t < p.total_tiles; t += gridDim.x, ++it) {
       const Tile c = tile_of(p, t);
-      const long x0 = (long)c.xt * kXRows, y0 = (long)c.yt * UN;
       bool ok = true;
       for (int kb = 0; kb < c.nkb; ++kb) {
         ok = mbar_wait_or_abort(smem_u32(&raw_full[rs]), rphase, abortp);
+        if (tid == 0) TRACE(tkb, 1);
         ok = ok && mbar_wait_or_abort(smem_u32(&conv_empty[cs]), cphase ^ 1u, abortp);
+        if (tid == 0) TRACE(tkb, 2);
         if (!ok) break;
         const unsigned char* rx = raw0 + (size_t)rs * raw_bytes;
         const unsigned char* ry = rx + x_bytes;
@@ -282,8 +398,10 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         } else {
           if (XMN) convert_mnmajor(rx, cx, cx + x_bytes, kXRows, tid, kBK);
           else convert_kmajor_lo(rx, cx, kXRows * 8, tid);
+          if (tid == 0) TRACE(tkb, 6);
           if (YMN) convert_mnmajor(ry, cy, cy + y_bytes, UN, tid, kBK);
           else convert_kmajor(ry, cy, cy + y_bytes, UN * 8, tid);
+          if (tid == 0) TRACE(tkb, 7);
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core
         __syncwarp();
@@ -291,6 +409,8 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
           mbar_arrive(smem_u32(&conv_full[cs]));
           if (!XDIRECT) mbar_arrive(smem_u32(&raw_empty[rs]));
         }
+        if (tid == 0) TRACE(tkb, 3);
+        ++tkb;
         if (++rs == RS) { rs = 0; rphase ^= 1u; }
         if (++cs == CS) { cs = 0; cphase ^= 1u; }
       }
@@ -303,141 +423,47 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         if (tid == 0) { *(volatile int*)p.err = 3; __threadfence_system(); }
         break;
       }
-      // Accumulator -> registers -> global memory. A thread owns tile row (quarter*32 + lane) and 8
-      // consecutive columns per chunk (8); columns [0, UN) hold hi*hi + lo*hi and [UN, 2UN) hold hi*lo.
-      const int quarter = warp & 3, colgroup = warp >> 2;
-      const int nchunks = UN / 8;
-      const int row = quarter * 32 + lane;
-      const long i_g = x0 + row;
-      const int batch = c.batch, split = c.split;
-      float* cbase = (p.nsplit > 1) ? p.C + ((long)batch * p.nsplit + split) * p.M * p.N : p.C + batch * p.c_batch_stride;
-      const long ld = (p.nsplit > 1) ? p.N : p.ldc;
-      const bool vec_ok = ((ld & 3) == 0) && (((uintptr_t)cbase & 15) == 0);
-      // where tile row `row` goes when the result is stored as NCHW planes (implicit convolution, or the output
-      // stage of a convolution layer on a stored column matrix)
-      bool pvalid = false;
-      long pb = 0, ppix = 0, pHW = 1, pC = 1;
-      if (CONV == 1) {
-        const int tile = c.xt;
-        pHW = p.cHW;
-        pC = p.cC;
-        if (p.cnimg > 1) {
-          const int li = row / p.cHW;
-          pb = (long)tile * p.cnimg + li;
-          ppix = row - li * p.cHW;
-          pvalid = li < p.cnimg && pb < p.cB;
-        } else {
-          pb = tile / p.cnbands;
-          ppix = (long)(tile - pb * p.cnbands) * p.crows * p.cW + row;
-          pvalid = row < p.crows * p.cW && ppix < p.cHW;
-        }
-      } else if (CONV == 0 && p.ep.y) {
-        pHW = p.ep.HW;
-        pC = p.yrows;
-        pvalid = i_g < p.xrows;
-        pb = i_g / pHW;
-        ppix = i_g - pb * pHW;
-      }
-      // filter gradient: tile row = (unit, channel) -> column (32*chunk + channel)*kh*kw + tap of the result
-      long wcol = -1;
-      if (CONV == 2) {
-        const int unit = c.xt * 4 + (row >> 5);
-        if (unit < p.wunits) {
-          const int tap = unit / p.ckpt, q = unit - tap * p.ckpt;
-          wcol = (long)(32 * q + (row & 31)) * p.wkk + tap;
-        }
-      }
-      for (int ch = colgroup; ch < nchunks; ch += kConvWarps / 4) {
-        const int c0 = ch * 8;
-        uint32_t r1[8], r2[8];
-        const uint32_t taddr = tmem_d + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
-        tmem_ld8(taddr, r1);
-        tmem_ld8(taddr + (uint32_t)UN, r2);
-        float v[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r1[j]) + __uint_as_float(r2[j]);
-        const long j0 = y0 + c0;
-        if (CONV == 2) {
-          if (wcol >= 0) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              if (j0 + j < p.yrows) cbase[(j0 + j) * ld + wcol] = v[j];
-          }
-        } else if (CONV == 1 || p.ep.y) {
-          // NCHW planes: the lanes of a warp write consecutive pixels of one channel plane
-          if (pvalid) {
-            if (p.ep.y) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                if (j0 + j < pC) {
-                  const float tt = v[j] + p.ep.bias[j0 + j];
-                  const int8_t mk = (int8_t)(tt >= 0.f);
-                  const size_t o = ((size_t)pb * pC + (j0 + j)) * pHW + ppix;
-                  p.ep.mask[o] = mk;
-                  p.ep.y[o] = tt * (float)mk;
-                }
-              }
-            } else {
-              // with K splits every split writes its own copy of the whole result; a fold adds them in order
-              float* dst = p.C + (size_t)split * p.cB * pC * pHW + ((size_t)pb * pC + j0) * pHW + ppix;
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                if (j0 + j < pC) dst[(size_t)j * pHW] = v[j];
-            }
-          }
-        } else if (i_g < p.xrows) {
-          if (!p.swapped) {  // tile row = product row: 32 contiguous bytes per thread
-            float* dst = cbase + i_g * ld + j0;
-            if (vec_ok && j0 + 8 <= p.yrows) {
-              *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
-              *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                if (j0 + j < p.yrows) dst[j] = v[j];
-            }
-          } else {           // tile row = product column: the lanes of a warp write consecutive addresses
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              if (j0 + j < p.yrows) cbase[(j0 + j) * ld + i_g] = v[j];
-          }
-        }
-      }
+      store_tile<CONV>(p, c, tmem_d, warp & 3, warp >> 2, lane);
       // this warp's reads of the accumulator are complete before it signals anything for the next tile (the
       // first MMA of the next tile waits for a conversion that every epilogue warp takes part in)
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
   } else if (warp == kConvWarps) {
     // ------------------------------------------------ MMA issuer
-    // The whole warp runs the loop so that descriptors and addresses stay warp-uniform (uniform
-    // registers feed tcgen05.mma directly); one elected lane issues. Two instructions per K step:
+    // The whole warp runs the loop; per K block one elected lane issues all its MMAs and commits (no election
+    // and no lane-mask operand per instruction: that form issues almost twice as fast). Two instructions per K step:
     // x_hi * [y_hi | y_lo] into columns [0, 2UN) and x_lo * y_hi into columns [0, UN).
     const uint32_t idesc1 = make_idesc_tf32(UN), idesc2 = make_idesc_tf32(2 * UN);
     bool ok = true;
     int rs = 0, cs = 0;
+    int tkb = 0;
+    (void)tkb;
     uint32_t cphase = 0;
     for (long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
       const Tile c = tile_of(p, t);
       for (int kb = 0; kb < c.nkb; ++kb) {
         ok = mbar_wait_or_abort(smem_u32(&conv_full[cs]), cphase, abortp);
         if (!ok) break;
+        if (lane == 0) TRACE(tkb, 4);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t sbase = smem_u32(conv0 + (size_t)cs * conv_bytes);
         const uint64_t dxh = make_desc(XDIRECT ? smem_u32(raw0 + (size_t)rs * raw_bytes) : sbase);
         const uint64_t dxl = make_desc(XDIRECT ? sbase : sbase + x_bytes);
         const uint64_t dyh = make_desc(sbase + cx_bytes);  // y_lo follows y_hi: one descriptor covers both
-#pragma unroll
-        for (int kk = 0; kk < kBK / 8; ++kk) {
-          const uint64_t adv = (uint64_t)((kk * 32) >> 4);  // 8 tf32 = 32 bytes along K inside the swizzle row
-          const uint32_t first = (kb == 0 && kk == 0) ? 0u : 1u;
-          mma_tf32_elect(tmem_d, dxh + adv, dyh + adv, idesc2, first);
-          mma_tf32_elect(tmem_d, dxl + adv, dyh + adv, idesc1, 1u);
-        }
         if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < kBK / 8; ++kk) {
+            const uint64_t adv = (uint64_t)((kk * 32) >> 4);  // 8 tf32 = 32 bytes along K inside the swizzle row
+            const uint32_t first = (kb == 0 && kk == 0) ? 0u : 1u;
+            mma_tf32_one(tmem_d, dxh + adv, dyh + adv, idesc2, first);
+            mma_tf32_one(tmem_d, dxl + adv, dyh + adv, idesc1, 1u);
+          }
           mma_commit(smem_u32(&conv_empty[cs]));
           if (XDIRECT) mma_commit(smem_u32(&raw_empty[rs]));
         }
         __syncwarp();
+        if (lane == 0) TRACE(tkb, 5);
+        ++tkb;
         if (++rs == RS) rs = 0;
         if (++cs == CS) { cs = 0; cphase ^= 1u; }
       }
@@ -457,6 +483,7 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       for (int kb = 0; kb < c.nkb; ++kb) {
         ok = mbar_wait_or_abort(smem_u32(&raw_empty[rs]), rphase ^ 1u, abortp);
         if (!ok) break;
+        TRACE((int)issued, 0);
         const uint32_t bar = smem_u32(&raw_full[rs]);
         const int k0 = (int)(c.k_begin + (long)kb * kBK);
         const uint32_t dx = smem_u32(raw0 + (size_t)rs * raw_bytes);
@@ -512,6 +539,328 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   if (warp == kConvWarps) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)p.tmem_cols) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Implicit convolution (forward product / data gradient) with the input tile resident in shared memory and the
+// X operand in tensor memory.
+//
+// What bounds sgemm_tma_kernel<.., 1> above (measured on B200 with per-role cycle stamps): every kernel tap re-loads
+// its shifted window of the input through the TMA unit (25 boxes of 15 KB per tile of a 5x5 convolution: the L2
+// -> SM path saturates), every tcgen05.mma re-reads its 4 KB X operand from shared memory, and one thread needs a
+// thousand cycles to issue the loads of one K block. Here
+//   * the input rows a tile needs, with their halo, are loaded ONCE per tile (one box per 32 channels) into a
+//     double-buffered shared-memory tile; tap (i, j) of the convolution is then only a different row offset when
+//     the conversion warps read their pixel's 32 channels;
+//   * the conversion warps write x and x_lo = x - cut(x) straight into tensor memory (tcgen05.st), from where the
+//     MMAs take their A operand: shared memory carries the input tile once plus the small filter tiles;
+//   * the filter bank is split once per call into K-major [2][N][K] (hi, lo) by split_rows_kernel, so the TMA
+//     unit delivers [w_hi | w_lo] in its final layout: one box per K block, no conversion in the loop;
+//   * per K block ONE elected thread issues the eight MMAs and the commits.
+// One CTA per SM (it owns all 512 TMEM columns: accumulator + ring of A stages), persistent over the tile grid.
+//   warp 17   halo producer: the tile's input rows into halo buffer it % HB
+//   warp 18   filter producer: [w_hi | w_lo] of K block g into ring stage g % WS
+//   warps 0-15 pixel rows -> registers -> (x, x_lo) -> TMEM A stage g % AS (four groups of four warps, group g % 4);
+//             after the tile's last block: epilogue
+//   warp 16   MMAs: D[0,2UN) += A_hi * [w_hi|w_lo], D[0,UN) += A_lo * w_hi; commits release the A stage and the filter stage
+// ------------------------------------------------------------------------------------------------
+constexpr int kMaxA = 8;
+constexpr int kGroups = 4;                                  // conversion groups of four warps (one per TMEM lane quarter)
+constexpr int kCvtWarps = 4 * kGroups;
+constexpr int kCvtThreads = 32 * kCvtWarps;
+constexpr int kEpiWarps = 4;                                // epilogue warps (one per TMEM lane quarter)
+constexpr int kThreadsConv = kCvtThreads + 3 * 32 + 32 * kEpiWarps;
+
+struct ConvTsaParams {
+  TmaParams t;           // tile grid, convolution geometry, epilogue (raw_stages = filter stages, conv_stages = A stages)
+  int hw, hh;            // halo tile: (Wd + kw - 1) columns, (crows + kh - 1) rows per image
+  int kh;
+  int halo_bufs;         // 1 or 2
+  uint32_t chunk_bytes;  // one 32-channel plane of the halo tile, rounded up to 1024 bytes
+  int hx0, hy0;          // source coordinates of halo element (0, 0) relative to the tile's first output pixel
+  int nacc;              // accumulators in TMEM (2: the epilogue of a tile overlaps the MMAs of the next)
+  int acc_cols;          // TMEM columns of one accumulator
+};
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+        "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+        "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+__global__ void __launch_bounds__(kThreadsConv, 1)
+conv_tsa_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapY, const ConvTsaParams cp) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t halo_full[2];
+  __shared__ __align__(8) uint64_t halo_empty[2];
+  __shared__ __align__(8) uint64_t a_full[kMaxA];    // stage s: TMEM A stage s and filter stage s are both ready
+  __shared__ __align__(8) uint64_t a_empty[kMaxA];   // the MMAs that read stage s have completed
+  __shared__ __align__(8) uint64_t accum_full[2];
+  __shared__ __align__(8) uint64_t accum_empty[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const TmaParams& p = cp.t;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int UN = p.UN, AS = p.conv_stages, HB = cp.halo_bufs;  // AS stages: TMEM A stage + filter stage each
+  unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t w_bytes = 2u * (uint32_t)UN * 128u;                  // [w_hi | w_lo] of one K block
+  const uint32_t halo_bytes = (uint32_t)p.ckpt * cp.chunk_bytes;
+  unsigned char* halo0 = smem;
+  unsigned char* w0 = smem + (size_t)HB * halo_bytes;
+  const int NACC = cp.nacc;
+  const uint32_t acol0 = (uint32_t)(cp.nacc * cp.acc_cols);  // first column of the A stages, behind the accumulator(s)
+  volatile int* abortp = &abort_flag;
+
+  if (tid == 0) {
+    for (int s = 0; s < HB; ++s) {
+      mbar_init(smem_u32(&halo_full[s]), 1);
+      mbar_init(smem_u32(&halo_empty[s]), kCvtWarps);
+    }
+    for (int s = 0; s < AS; ++s) {
+      mbar_init(smem_u32(&a_full[s]), 5);   // the four warps of one conversion group + the filter producer (with its bytes)
+      mbar_init(smem_u32(&a_empty[s]), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&accum_full[s]), 1);
+      mbar_init(smem_u32(&accum_empty[s]), kEpiWarps);
+    }
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == kCvtWarps) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                 "r"((uint32_t)p.tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_d = tmem_base_slot;
+
+  if (warp < kCvtWarps) {
+    // ------------------------------------------------ pixel rows -> tensor memory, then the tile's epilogue
+    // Sixteen warps in four groups; group g converts K blocks g, g + 4, ... of the CTA's block sequence (a block's
+    // conversion is a short chain of dependent steps -- shared-memory loads, the split, tcgen05.st, its wait, the
+    // arrival -- so four blocks in flight hide that latency). Within a group warp w serves TMEM lanes 32*(w%4)..+31:
+    // a thread owns one pixel of the tile and all 32 channels of the K block.
+    const int quarter = warp & 3, group = warp >> 2;
+    const int row = quarter * 32 + lane;   // tile row = TMEM lane = pixel of the tile
+    // halo row of this pixel for tap (0, 0); rows of the tile that hold no pixel read row 0 (never stored)
+    int base_row = 0;
+    {
+      int li = 0, pix = row;
+      if (p.cnimg > 1) { li = row / p.cHW; pix = row - li * p.cHW; }
+      const int ly = pix / p.cW, lx = pix - ly * p.cW;
+      if (li < p.cnimg && ly < p.crows) base_row = (li * cp.hh + ly) * cp.hw + lx;
+    }
+    int as = 0;
+    int tkb = 0;
+    (void)tkb;
+    uint32_t aphase = 0, it = 0, g4 = 0;   // g4: the CTA's K block count modulo 4
+    for (long t = blockIdx.x; t < p.total_tiles; t += gridDim.x, ++it) {
+      const Tile c = tile_of(p, t);
+      const int hb = HB > 1 ? (int)(it & 1u) : 0;
+      const uint32_t hphase = HB > 1 ? (it >> 1) & 1u : it & 1u;
+      bool ok = mbar_wait_or_abort(smem_u32(&halo_full[hb]), hphase, abortp);
+      if (tid == 0) TRACE(tkb, 1);
+      const unsigned char* halo = halo0 + (size_t)hb * halo_bytes;
+      // K block of the whole product = (tap, channel chunk); (ti, tj) = the tap's kernel row and column
+      const int gkb = (int)(c.k_begin / kBK);
+      int tap = gkb / p.ckpt, q = gkb - tap * p.ckpt;
+      int ti = tap / p.ckw, tj = tap - ti * p.ckw;
+      for (int kb = 0; kb < c.nkb && ok; ++kb) {
+        if ((int)g4 == group) {
+          ok = mbar_wait_or_abort(smem_u32(&a_empty[as]), aphase ^ 1u, abortp);
+          if (!ok) break;
+          if (tid == 0) TRACE(tkb, 2);
+          const int oi = p.csign > 0 ? ti : cp.kh - 1 - ti, oj = p.csign > 0 ? tj : p.ckw - 1 - tj;
+          const int hr = base_row + oi * cp.hw + oj;
+          const uint4* rowp = reinterpret_cast<const uint4*>(halo + (size_t)q * cp.chunk_bytes + (size_t)hr * 128);
+          uint32_t hi[32], lo[32];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint4 u = rowp[j ^ (hr & 7)];  // 16-byte chunks swizzled by the TMA unit
+            hi[4 * j] = u.x; hi[4 * j + 1] = u.y; hi[4 * j + 2] = u.z; hi[4 * j + 3] = u.w;
+          }
+#pragma unroll
+          for (int j = 0; j < 32; ++j) lo[j] = lo_of(hi[j]);
+          if (tid == 0) TRACE(tkb, 6);
+          const uint32_t taddr = tmem_d + ((uint32_t)(quarter * 32) << 16) + acol0 + (uint32_t)as * 64u;
+          tmem_st32(taddr, hi);
+          tmem_st32(taddr + 32u, lo);
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          if (tid == 0) TRACE(tkb, 7);
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&a_full[as]));
+          if (tid == 0) TRACE(tkb, 3);
+        }
+        ++tkb;
+        g4 = (g4 + 1u) & 3u;
+        if (++as == AS) { as = 0; aphase ^= 1u; }
+        if (++q == p.ckpt) {
+          q = 0;
+          ++tap;
+          if (++tj == p.ckw) { tj = 0; ++ti; }
+        }
+      }
+      // this warp has read all it needs of the halo tile
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&halo_empty[hb]));
+      if (!ok) {
+        if (lane == 0) { *abortp = 1; *(volatile int*)p.err = 3; __threadfence_system(); }
+        break;
+      }
+    }
+  } else if (warp == kCvtWarps) {
+    // ------------------------------------------------ MMA issuer (whole warp; one elected lane issues per K block)
+    const uint32_t idesc1 = make_idesc_tf32(UN), idesc2 = make_idesc_tf32(2 * UN);
+    bool ok = true;
+    int as = 0;
+    int tkb = 0;
+    (void)tkb;
+    uint32_t aphase = 0;
+    uint32_t it = 0;
+    for (long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++it) {
+      const Tile c = tile_of(p, t);
+      // accumulator it % NACC: the epilogue warps must have drained its previous tile
+      const int ab = NACC > 1 ? (int)(it & 1u) : 0;
+      const uint32_t use = NACC > 1 ? it >> 1 : it;
+      ok = mbar_wait_or_abort(smem_u32(&accum_empty[ab]), (use & 1u) ^ 1u, abortp);
+      if (!ok) break;
+      const uint32_t tmem_acc = tmem_d + (uint32_t)(ab * cp.acc_cols);
+      for (int kb = 0; kb < c.nkb; ++kb) {
+        ok = mbar_wait_or_abort(smem_u32(&a_full[as]), aphase, abortp);
+        if (!ok) break;
+        if (lane == 0) TRACE(tkb, 4);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_hi = tmem_d + acol0 + (uint32_t)as * 64u, a_lo = a_hi + 32u;
+        const uint64_t dyh = make_desc(smem_u32(w0 + (size_t)as * w_bytes));  // w_lo follows w_hi
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < kBK / 8; ++kk) {
+            const uint64_t adv = (uint64_t)((kk * 32) >> 4);
+            const uint32_t first = (kb == 0 && kk == 0) ? 0u : 1u;
+            mma_tf32_ts_one(tmem_acc, a_hi + (uint32_t)(kk * 8), dyh + adv, idesc2, first);
+            mma_tf32_ts_one(tmem_acc, a_lo + (uint32_t)(kk * 8), dyh + adv, idesc1, 1u);
+          }
+          mma_commit(smem_u32(&a_empty[as]));
+        }
+        __syncwarp();
+        if (lane == 0) TRACE(tkb, 5);
+        ++tkb;
+        if (++as == AS) { as = 0; aphase ^= 1u; }
+      }
+      if (ok && elect_one()) mma_commit(smem_u32(&accum_full[ab]));
+      __syncwarp();
+    }
+    if (!ok && lane == 0) { *abortp = 1; *(volatile int*)p.err = 4; __threadfence_system(); }
+  } else if (warp == kCvtWarps + 1) {
+    if (lane == 0) {
+      // ---------------------------------------------- halo producer: the input rows of tile `it` into buffer it % HB
+      bool ok = true;
+      uint32_t it = 0;
+      long issued = 0;
+      for (long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++it) {
+        const Tile c = tile_of(p, t);
+        const int hb = HB > 1 ? (int)(it & 1u) : 0;
+        const uint32_t hphase = HB > 1 ? (it >> 1) & 1u : it & 1u;
+        ok = mbar_wait_or_abort(smem_u32(&halo_empty[hb]), hphase ^ 1u, abortp);
+        if (!ok) break;
+        const int tile = c.xt;
+        const int b0 = p.cnimg > 1 ? tile * p.cnimg : tile / p.cnbands;
+        const int yrow0 = p.cnimg > 1 ? 0 : (tile - b0 * p.cnbands) * p.crows;
+        const uint32_t bar = smem_u32(&halo_full[hb]);
+        mbar_arrive_expect_tx(bar, (uint32_t)p.ckpt * (uint32_t)p.cx_tx);
+        const uint32_t dst = smem_u32(halo0 + (size_t)hb * halo_bytes);
+        for (int q = 0; q < p.ckpt; ++q) tma_load_4d(dst + (uint32_t)q * cp.chunk_bytes, &mapX, 32 * q, cp.hx0, yrow0 + cp.hy0, b0, bar);
+        ++issued;
+      }
+      if (!ok || *abortp) {
+        *abortp = 1;
+        *(volatile int*)p.err = 5;
+        __threadfence_system();
+        for (long j = (issued > HB ? issued - HB : 0); j < issued; ++j)
+          mbar_wait(smem_u32(&halo_full[HB > 1 ? (j & 1) : 0]), HB > 1 ? (uint32_t)(j >> 1) & 1u : (uint32_t)j & 1u);
+      }
+    }
+  } else if (warp == kCvtWarps + 2) {
+   if (lane == 0) {
+    // ------------------------------------------------ filter producer: [w_hi | w_lo] of every K block
+    bool ok = true;
+    int as = 0;
+    uint32_t aphase = 0;
+    long issued = 0;
+    for (long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+      const Tile c = tile_of(p, t);
+      const int y0 = c.yt * UN;
+      for (int kb = 0; kb < c.nkb; ++kb) {
+        ok = mbar_wait_or_abort(smem_u32(&a_empty[as]), aphase ^ 1u, abortp);
+        if (!ok) break;
+        TRACE((int)issued, 0);
+        const uint32_t bar = smem_u32(&a_full[as]);
+        mbar_arrive_expect_tx(bar, w_bytes);
+        tma_load_3d(smem_u32(w0 + (size_t)as * w_bytes), &mapY, (int)(c.k_begin + (long)kb * kBK), y0, 0, bar);
+        ++issued;
+        if (++as == AS) { as = 0; aphase ^= 1u; }
+      }
+    }
+    if (!ok || *abortp) {
+      *abortp = 1;
+      *(volatile int*)p.err = 6;
+      __threadfence_system();
+      // Copies already issued still write this CTA's shared memory. Their barrier also counts the conversion
+      // warps, which may never arrive now: wait for the bytes by polling a bounded time instead.
+      const long long t0 = clock64();
+      while (clock64() - t0 < 4000000LL) { }
+    }
+   }
+  } else {
+    // ------------------------------------------------ epilogue warps: accumulator it % NACC -> global memory
+    const int quarter = warp & 3;
+    bool ok = true;
+    uint32_t it = 0;
+    for (long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++it) {
+      const Tile c = tile_of(p, t);
+      const int ab = NACC > 1 ? (int)(it & 1u) : 0;
+      const uint32_t use = NACC > 1 ? it >> 1 : it;
+      ok = mbar_wait_or_abort(smem_u32(&accum_full[ab]), use & 1u, abortp);
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      store_tile<1, 1>(p, c, tmem_d + (uint32_t)(ab * cp.acc_cols), quarter, 0, lane);
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&accum_empty[ab]));
+    }
+    if (!ok && lane == 0) { *abortp = 1; *(volatile int*)p.err = 7; __threadfence_system(); }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == kCvtWarps) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)p.tmem_cols) : "memory");
+  }
+}
+
+// Y [rows] x [K] (element (r, k) at Y[r*ld + k], or Y[k*ld + r] when `mn`) -> out[0][r][k] = y rounded to TF32,
+// out[1][r][k] = the rest cut to TF32, rows of Kp >= K entries, zeros beyond K.
+__global__ void split_rows_kernel(const float* __restrict__ Y, long rows, long K, long ld, int mn, float* __restrict__ out, long Kp) {
+  const long n = rows * Kp;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    const long r = mn ? i % rows : i / Kp, k = mn ? i / rows : i - (i / Kp) * Kp;  // consecutive threads read consecutive addresses
+    uint32_t h = 0, l = 0;
+    if (k < K) split_tf32(mn ? Y[k * ld + r] : Y[r * ld + k], h, l);
+    out[r * Kp + k] = __uint_as_float(h);
+    out[n + r * Kp + k] = __uint_as_float(l);
   }
 }
 
@@ -615,6 +964,33 @@ int launch_tma(const CUtensorMap& mapX, const CUtensorMap& mapY, const TmaParams
   const unsigned grid = persistent_grid(p.total_tiles, smem);
   CGTB_LAUNCH((sgemm_tma_kernel<XMN, YMN, CONV>), grid, kThreadsTma, smem, mapX, mapY, p);
   return 0;
+}
+
+// The convolution kernel with the input tile in shared memory and X in tensor memory is the default;
+// CGTB_CONV_TSA=0 selects the kernel that loads a box per tap (for comparisons).
+bool use_tsa() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("CGTB_CONV_TSA");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v != 0;
+}
+
+// Pre-split Y (rows x K) into [2][rows][Kp] at `dst` and build its tensor map (box 32 x UN x 1, third coordinate
+// 0 = hi, 1 = lo).
+bool split_y(const Side& Y, long K, int UN, float* dst, long Kp, CUtensorMap* mapY) {
+  const long n = Y.rows * Kp;
+  const unsigned blocks = (unsigned)std::min<long>(cgtb_ceil_div(n, 256), 8L * rt().sm_count);
+  CGTB_LAUNCH(split_rows_kernel, blocks, 256, 0, Y.base, Y.rows, K, Y.ld, Y.mn ? 1 : 0, dst, Kp);
+  EncodeTiledFn fn = encoder();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)Kp, (cuuint64_t)Y.rows, 2};
+  cuuint64_t strides[2] = {(cuuint64_t)Kp * 4, (cuuint64_t)Y.rows * Kp * 4};
+  cuuint32_t box[3] = {kBK, (cuuint32_t)UN, 2}, estr[3] = {1, 1, 1};
+  if (strides[0] >= (1ull << 40) || strides[1] >= (1ull << 40)) return false;
+  return fn(mapY, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)dst, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 }  // namespace
@@ -721,8 +1097,9 @@ int conv_implicit_tma(const float* src, long B, int Hs, int Ws, int Cs, const fl
   if (((uintptr_t)src & 15) != 0 || ((uintptr_t)wr & 15) != 0) return -1;
   const long K = (long)kh * kw * Cs;
   const int HW = Hd * Wd;
-  TmaParams p;
-  memset(&p, 0, sizeof(p));
+  ConvTsaParams cp;
+  memset(&cp, 0, sizeof(cp));
+  TmaParams& p = cp.t;
   p.ep = ConvEpilogue{nullptr, nullptr, nullptr, 1};
   if (ep) p.ep = *ep;
   p.csign = sign;
@@ -735,45 +1112,103 @@ int conv_implicit_tma(const float* src, long B, int Hs, int Ws, int Cs, const fl
   p.cpw = pw;
   p.cB = (int)B;
   const long want = (long)rt().sm_count;
-  long tiles;
-  if (HW <= 128) {
-    // several small images per tile, but not so many that the tile count falls below the number of SMs
-    long nimg = std::min<long>(128 / HW, B);
-    while (nimg > 1 && cgtb_ceil_div(B, nimg) < want) --nimg;
-    p.cnimg = (int)nimg;
-    p.crows = Hd;
-    p.cnbands = 1;
-    tiles = cgtb_ceil_div(B, p.cnimg);
-  } else {
+  const int ytiles = (int)cgtb_ceil_div(N, 128);
+  const int UN = (int)(cgtb_ceil_div(cgtb_ceil_div(N, ytiles), 16) * 16);
+  if (UN * ytiles != N) return -1;  // equal column tiles only
+  p.UN = UN;
+  p.xrows = 0;
+  p.yrows = N;
+  const long nkb = K / kBK;
+  EncodeTiledFn fn = encoder();
+  if (!fn) return -1;
+  cuuint64_t dims[4] = {(cuuint64_t)Cs, (cuuint64_t)Ws, (cuuint64_t)Hs, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)Cs * 4, (cuuint64_t)Ws * Cs * 4, (cuuint64_t)Hs * Ws * Cs * 4};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+
+  // tile = `crows` image rows of one image (crows*Wd <= 128 pixels) or, for small images, several whole images
+  auto tile_geometry = [&](long max_imgs) {
+    if (HW <= 128) {
+      // several small images per tile, but not so many that the tile count falls below the number of SMs
+      long nimg = std::min<long>(std::min<long>(128 / HW, B), max_imgs);
+      while (nimg > 1 && cgtb_ceil_div(B, nimg) * ytiles < want) --nimg;
+      p.cnimg = (int)nimg;
+      p.crows = Hd;
+      p.cnbands = 1;
+      return cgtb_ceil_div(B, p.cnimg);
+    }
     p.cnimg = 1;
     const int max_rows = 128 / Wd;
     p.cnbands = (int)cgtb_ceil_div(Hd, max_rows);
     p.crows = (int)cgtb_ceil_div(Hd, p.cnbands);  // equal bands
-    tiles = B * p.cnbands;
+    return B * p.cnbands;
+  };
+
+  bool tsa = use_tsa();
+  size_t smem = 0;
+  long tiles = 0;
+  int conv_stages = 0, raw_stages = 0;
+  if (tsa) {
+    // shared memory: HB halo tiles + a ring of filter stages; TMEM: accumulator + A stages of 64 columns
+    // TMEM: one or two accumulators of 2*UN columns (rounded to 64), then A stages of 64 columns
+    cp.acc_cols = (2 * UN + 63) & ~63;
+    cp.nacc = (512 - 2 * cp.acc_cols) / 64 >= 3 ? 2 : 1;
+    const int as = std::min<int>(kMaxA, (512 - cp.nacc * cp.acc_cols) / 64);
+    const long w_bytes = 2L * UN * 128;
+    const long budget = 222L * 1024;
+    long max_imgs = 128;
+    bool fits = false;
+    for (int attempt = 0; attempt < 8 && !fits; ++attempt) {
+      tiles = tile_geometry(max_imgs);
+      cp.hw = Wd + kw - 1;
+      cp.hh = p.crows + kh - 1;
+      const long rows = (long)cp.hw * cp.hh * p.cnimg;
+      cp.chunk_bytes = (uint32_t)((rows * 128 + 1023) & ~1023L);
+      const long halo_bytes = (long)p.ckpt * cp.chunk_bytes;
+      if (2 * halo_bytes + 3 * w_bytes <= budget) cp.halo_bufs = 2;
+      else if (halo_bytes + 2 * w_bytes <= budget) cp.halo_bufs = 1;
+      else cp.halo_bufs = 0;
+      if (cp.halo_bufs && cp.hw <= 256 && cp.hh <= 256) {
+        fits = true;
+        // a stage = 64 TMEM columns (x, x_lo of one K block) + one filter tile pair in shared memory
+        conv_stages = (int)std::min<long>(as, (budget - cp.halo_bufs * halo_bytes) / w_bytes);
+        raw_stages = conv_stages;
+        smem = std::max<size_t>((size_t)(cp.halo_bufs * halo_bytes + conv_stages * w_bytes + 1024), (size_t)120 * 1024);
+      } else if (p.cnimg > 1) {
+        max_imgs = p.cnimg - 1;   // fewer images per tile: a smaller halo tile
+      } else {
+        break;
+      }
+    }
+    if (!fits || conv_stages < 2) {
+      tsa = false;
+    } else {
+      p.tmem_cols = 512;
+      p.cx_tx = (int)((long)cp.hw * cp.hh * p.cnimg * 128);
+      cp.kh = kh;
+      cp.hx0 = sign > 0 ? -pw : pw - (kw - 1);
+      cp.hy0 = sign > 0 ? -ph : ph - (kh - 1);
+    }
+  }
+  if (!tsa) {
+    tiles = tile_geometry(128);
+    p.cx_tx = 32 * Wd * p.crows * p.cnimg * (int)sizeof(float);
+    p.tmem_cols = 32;
+    while (p.tmem_cols < 2 * UN) p.tmem_cols *= 2;
+    const long conv_bytes = 1L * kXRows * 128 + 2L * UN * 128, raw_bytes = (long)kXRows * 128 + (long)UN * 128;
+    if (!choose_stages(conv_bytes, raw_bytes, nkb, &conv_stages, &raw_stages)) return -1;
+    smem = (size_t)conv_stages * conv_bytes + (size_t)raw_stages * raw_bytes + 1024;
   }
   if (tiles > 2147483647L / 8) return -1;
-  p.cx_tx = 32 * Wd * p.crows * p.cnimg * (int)sizeof(float);
-  const int ytiles = (int)cgtb_ceil_div(N, 128);
-  int UN = (int)(cgtb_ceil_div(cgtb_ceil_div(N, ytiles), 16) * 16);
-  if (UN * ytiles != N) return -1;  // equal column tiles only
-  p.UN = UN;
-  p.tmem_cols = 32;
-  while (p.tmem_cols < 2 * UN) p.tmem_cols *= 2;
-  p.xrows = 0;
-  p.yrows = N;
-  const long conv_bytes = 1L * kXRows * 128 + 2L * UN * 128, raw_bytes = (long)kXRows * 128 + (long)UN * 128;
-  int conv_stages, raw_stages;
-  const long nkb = K / kBK;
-  if (!choose_stages(conv_bytes, raw_bytes, nkb, &conv_stages, &raw_stages)) return -1;
+  p.conv_stages = conv_stages;
+  p.raw_stages = raw_stages;
   // few tiles with a long K loop (small images, many taps): split K over CTAs, each split writing its own
   // copy of the result. Not with the output stage, which needs whole sums.
   int nsplit = 1;
+  const long slots = tsa ? want : 2 * want;  // CTAs resident at once
   if (!ep && tiles * ytiles < want && nkb >= 8)
-    nsplit = (int)std::max<long>(1, std::min<long>(std::max<long>(1, (2 * want) / (tiles * ytiles)), nkb / 4));
+    nsplit = (int)std::max<long>(1, std::min<long>(std::max<long>(1, slots / (tiles * ytiles)), nkb / 4));
   const long kchunk = cgtb_ceil_div(nkb, nsplit) * kBK;
   nsplit = (int)cgtb_ceil_div(K, kchunk);
-  p.conv_stages = conv_stages;
-  p.raw_stages = raw_stages;
   p.nsplit = nsplit;
   p.kchunk = kchunk;
   p.K = K;
@@ -785,34 +1220,40 @@ int conv_implicit_tma(const float* src, long B, int Hs, int Ws, int Cs, const fl
   p.ytiles = ytiles;
   p.total_tiles = tiles * ytiles * nsplit;
   const long total = B * (long)N * HW;
-  float* part = nullptr;
-  if (nsplit > 1) {
-    part = (float*)scratch((size_t)nsplit * total * sizeof(float));
-    if (!part) return 1;
-    p.C = part;
-  } else {
-    p.C = out;
+  const size_t split_bytes = tsa ? ((((size_t)2 * N * K * sizeof(float)) + 255) & ~(size_t)255) : 0;
+  const size_t slab_bytes = nsplit > 1 ? (size_t)nsplit * total * sizeof(float) : 0;
+  char* blk = nullptr;
+  if (split_bytes + slab_bytes) {
+    blk = (char*)scratch(split_bytes + slab_bytes);
+    if (!blk) return 1;
   }
+  float* part = (float*)(blk + split_bytes);
+  p.C = nsplit > 1 ? part : out;
   p.err = tc_error_flag();
   if (!p.err) return 1;
-  EncodeTiledFn fn = encoder();
-  if (!fn) return -1;
   CUtensorMap mapX, mapY;
   {
-    cuuint64_t dims[4] = {(cuuint64_t)Cs, (cuuint64_t)Ws, (cuuint64_t)Hs, (cuuint64_t)B};
-    cuuint64_t strides[3] = {(cuuint64_t)Cs * 4, (cuuint64_t)Ws * Cs * 4, (cuuint64_t)Hs * Ws * Cs * 4};
-    cuuint32_t box[4] = {32, (cuuint32_t)Wd, (cuuint32_t)p.crows, (cuuint32_t)p.cnimg};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
+    cuuint32_t box[4] = {32, (cuuint32_t)(tsa ? cp.hw : Wd), (cuuint32_t)(tsa ? cp.hh : p.crows), (cuuint32_t)p.cnimg};
     if (box[1] > 256 || box[2] > 256 || box[3] > 256) return -1;
     CUresult r = fn(&mapX, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)src, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return -1;
   }
   Side Y = {wr, K, false, N, 0};
-  if (!encode(&mapY, Y, K, 1, UN)) return -1;
-  size_t smem = (size_t)conv_stages * conv_bytes + (size_t)raw_stages * raw_bytes + 1024;
-  int rc = launch_tma<false, false, 1>(mapX, mapY, p, smem);
-  if (rc) return rc;
+  if (tsa) {
+    if (!split_y(Y, K, UN, (float*)blk, K, &mapY)) return -1;
+    static bool cfg = false;
+    if (!cfg) {
+      CGTB_CUDA_TRY(cudaFuncSetAttribute(conv_tsa_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048));
+      cfg = true;
+    }
+    const unsigned grid = (unsigned)std::min<long>(p.total_tiles, want);  // one CTA per SM
+    CGTB_LAUNCH(conv_tsa_kernel, grid, kThreadsConv, smem, mapX, mapY, cp);
+  } else {
+    if (!encode(&mapY, Y, K, 1, UN)) return -1;
+    int rc = launch_tma<false, false, 1>(mapX, mapY, p, smem);
+    if (rc) return rc;
+  }
   if (nsplit > 1) tc_splitk_fold(1, 1, total, nsplit, part, out, total, 0);
   CGTB_CHECK_LAUNCH("conv_implicit");
   return 0;
@@ -955,3 +1396,10 @@ CGTB_API int cgtb_conv_wgrad(const float* x_nhwc, long B, int H, int W, int Cin,
                 "(at most 32) or an unaligned operand; use cgtb_im2col + cgtb_sgemm", Cin, Cout, Wo);
   return rc;
 }
+
+#ifdef CGTB_TMA_TRACE
+CGTB_API int cgtb_debug_tma_trace(long long* host) {
+  cudaStreamSynchronize(rt().stream);
+  return cudaMemcpyFromSymbol(host, g_tma_trace, sizeof(long long) * 128 * 8) == cudaSuccess ? 0 : 1;
+}
+#endif

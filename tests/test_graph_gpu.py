@@ -2,7 +2,7 @@
 B200 against the same graph evaluated by the CPU oracle, for every benchmark configuration.
 
 Tolerances: fp32 losses within 1e-3 relative after 10 update steps (and every step on the way),
-parameters within 1e-3 of the oracle's after those steps relative to their scale.
+parameters within 1e-3 of the oracle's after those steps relative to their scale (plus 1e-5 absolute).
 """
 import numpy as np
 import pytest
@@ -49,7 +49,9 @@ def test_ten_step_loss_parity(rt, name, graphs):
     for p in cfg.params:
         got, want = p.op.get_value(), f_cpu.get_value(p)
         scale = max(np.abs(want).max(), 1e-6)
-        assert np.abs(got - want).max() <= 1e-3 * scale, p.name
+        # 1e-3 of the parameter's scale, plus the per-Op absolute bar for parameters that are still tiny (a bias that
+        # started at zero is 1e-4 after ten small steps: its relative error is the float32 noise of everything upstream)
+        assert np.abs(got - want).max() <= 1e-3 * scale + 1e-5, p.name
     if graphs:
         st = f_gpu.stats()
         assert st["segments_captured"] >= 1 and st["last_graph_launches"] >= 1, st
@@ -132,9 +134,10 @@ def test_elementwise_fusion_changes_no_bit(rt, name, generated):
     generated=True: kernels generated per chain; False: the library's register-machine kernel."""
     results = {}
     for fuse in (False, True):
-        # padded column rows need the fused output stage, which needs the fused chains: off on both sides here
+        # padded column rows and the convolutions without a column matrix need the fused output stage, which needs the
+        # fused chains, and they change the order of the sums: off on both sides here
         with cgt.scoped_update_config(fuse_elementwise=fuse, jit_fused_elementwise=generated, pad_conv_columns=False,
-                                      use_cuda_graphs=False):
+                                      fuse_conv_implicit=False, use_cuda_graphs=False):
             cfg = configs.BUILDERS[name](**SMALL[name])
             f = cfg.compile()
             n_fused = sum(1 for instr in f.eg.instrs if "FusedElwise" in repr(instr))
@@ -203,7 +206,7 @@ def test_padded_column_rows(rt, name, n_padded):
             batches = [cfg.batch(seed) for seed in range(2)]
             losses = [float(f(*batches[i % 2])[0]) for i in range(6)]
             params = [np.asarray(p.op.get_value()).copy() for p in cfg.params]
-            res[pad] = (sum("/pitch" in n for n in names), sum("ConvWgrad" in n for n in names), losses, params)
+            res[pad] = (sum("/pitch" in n for n in names), sum("ConvWgrad{" in n for n in names), losses, params)
     assert res[False][:2] == (0, 0) and res[True][:2] == (n_padded, n_padded)
     np.testing.assert_allclose(res[True][2], res[False][2], rtol=1e-4)
     for (a, b) in zip(res[True][3], res[False][3]):
