@@ -3,13 +3,19 @@ backward + SGD update) of the CIFAR-shape convnet at batch 128 per GPU, on synth
 
     python bench.py --gpus N --steps K --warmup W            # this backend (one rank per GPU under torchrun)
     python bench.py --impl reference --steps K --warmup W    # the reference's CPU path on the host cores
+    python bench.py --config wide ...                        # the wide conv stack (128 examples per GPU) instead
 
 Prints ONE JSON line (rank 0). `value` is measured with the batch already resident in device memory;
 `e2e` goes through the public API with pinned host buffers (host->device copy of the batch and
 device->host read of the loss inside every timed step). Every timed step is bracketed by CUDA events on
-the runtime stream and preceded by an L2 flush that is not timed; per-rank totals are reduced with max.
+the runtime stream and preceded by an L2 flush that is not timed. The block of K steps is repeated R times
+(--repeats, default 15) inside one invocation; each block is bracketed by a barrier and a synchronisation, its
+time is the max over ranks, and the reported figure is the median block (`spread` gives the fastest and the
+slowest one). `per_kernel` times every C-ABI entry point of the step at the step's own shapes in a loop of cold-L2
+launches; `roofline` is the entry of that list with the largest share of the step.
 """
 import argparse
+import ctypes
 import json
 import os
 import os.path as osp
@@ -23,9 +29,15 @@ import numpy as np
 ROOT = osp.dirname(osp.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-METRIC = "train examples/sec (fwd+bwd+SGD) CIFAR-shape convnet b128"
 UNIT = "examples/s"
 BATCH = 128
+CONFIGS = {
+    "cifar": dict(builder="build_cifar", metric="train examples/sec (fwd+bwd+SGD) CIFAR-shape convnet b128",
+                  workload="CIFAR-shape convnet, batch 128 per GPU, fwd+bwd+SGD (BASELINE configs[1])"),
+    "wide": dict(builder="build_wide", metric="train examples/sec (fwd+bwd+SGD) wide conv stack b128 per GPU",
+                 workload="wide conv stack 3x64x64 -> conv96/11/4 -> LRN -> pool -> conv256/5 -> pool -> fc4096 -> fc100, "
+                          "batch 128 per GPU, fwd+bwd+SGD (BASELINE configs[4])"),
+}
 
 
 def load_peaks():
@@ -91,83 +103,201 @@ class ClockSampler(object):
         return out
 
 
-# algorithmic bytes / flops per instruction: every operand and result of an Op crosses HBM once; 2MNK flops per product
-# algorithmic bytes / flops per instruction (per-op figures stated in DESIGN.md)
+# ------------------------------------------------------------------------------------------------
+# algorithmic bytes / flops per instruction: every operand and result of an Op crosses HBM once, each at its
+# own element size; 2MNK flops per product
 # ------------------------------------------------------------------------------------------------
 def _nbytes(shape, dtype):
-    if shape is None:
+    if shape is None or not isinstance(dtype, str) or len(dtype) < 2 or not dtype[1:].isdigit():
+        return 0  # unknown extent, or a tuple-typed operand (its members are counted where they are produced)
+    if shape and isinstance(shape[0], tuple):
         return 0
     return int(np.prod(shape, dtype=np.int64)) * int(dtype[1:])
 
 
 def algorithmic_cost(instr):
     """(bytes, flops) that the instruction must move / compute, from its static shapes."""
-    from cgt_b200 import core
     op = instr.op
     name = type(op).__name__
     ins = [(s, d) for (s, d) in zip(instr.in_shapes, instr.in_dtypes)]
     out_shape, out_dtype = instr.out_shape, instr.out_dtype
-    if name == "MaxPool":  # values + int32 mask
-        top = out_shape[0]
-        return _nbytes(ins[0][0], ins[0][1]) + _nbytes(top, ins[0][1]) + _nbytes(top, "i4"), 0
-    if name == "CrossChannelLRNForward":
-        return 3 * _nbytes(ins[0][0], ins[0][1]), 0
-    if isinstance(out_shape, tuple) and out_shape and isinstance(out_shape[0], tuple):
-        return sum(_nbytes(s, d) for (s, d) in ins) + sum(_nbytes(s, ins[0][1]) for s in out_shape), 0
-    out_b = _nbytes(out_shape, out_dtype)
-    if name == "MaxPoolPullback":  # mask + pooled gradient read, input gradient written; x and pooled give shapes only
-        return _nbytes(ins[2][0], ins[2][1]) + _nbytes(ins[3][0], ins[3][1]) + out_b, 0
-    if name in ("Mul22",):
-        (sa, _), (sb, _) = ins[0], ins[1]
-        M, N = out_shape
-        K = sa[0] if op.tA else sa[1]
-        return 4 * (M * K + K * N + M * N), 2 * M * N * K
-    if name in ("Reshape", "Size", "TupleIndex", "InMemoryData", "Arange"):
-        return 0, 0
     host = set(op.host_inputs(len(ins))) if hasattr(op, "host_inputs") else set()
     in_b = sum(_nbytes(s, d) for (i, (s, d)) in enumerate(ins) if i not in host)
+    if name == "MaxPoolPullback":  # mask + pooled gradient read, input gradient written; x and pooled give shapes only
+        return _nbytes(ins[2][0], ins[2][1]) + _nbytes(ins[3][0], ins[3][1]) + _nbytes(out_shape, out_dtype), 0
+    if name in ("Reshape", "Size", "TupleIndex", "InMemoryData", "Arange"):
+        return 0, 0
     if name in ("IncSli", "IncFlatIndices"):  # in place: read the increment and the touched part, write it back
         return 3 * _nbytes(ins[-1][0], ins[-1][1]), 0
-    return in_b + out_b, 0
+    if isinstance(out_shape, tuple) and out_shape and isinstance(out_shape[0], tuple):  # tuple-valued: members at their own dtypes
+        dts = getattr(instr, "out_dtypes", None) or [ins[0][1]] * len(out_shape)
+        out_b = sum(_nbytes(s, d) for (s, d) in zip(out_shape, dts))
+    else:
+        out_b = _nbytes(out_shape, out_dtype)
+    flops = 0
+    if name == "Mul22":
+        (sa, _), _ = ins[0], ins[1]
+        M, N = out_shape
+        K = sa[0] if op.tA else sa[1]
+        flops = 2 * M * N * K
+    elif name in ("ConvBiasRelu",):
+        (M, ld), (C, K) = ins[0][0], ins[1][0]
+        flops = 2 * M * C * K
+    elif name in ("ConvFwdBiasRelu", "ConvDgrad"):
+        (B, H, W, Cs), wshape = ins[0][0], ins[1][0]
+        flops = 2 * B * H * W * int(np.prod(wshape))
+    elif name in ("ConvWgradImplicit",):
+        (B, H, W, Cs), (_b, Ho, Wo, N) = ins[0][0], ins[1][0]
+        flops = 2 * B * Ho * Wo * N * int(out_shape[1])
+    elif name == "ConvWgrad":
+        (M, C), (_m, ld) = ins[0][0], ins[1][0]
+        flops = 2 * M * C * int(out_shape[1])
+    return in_b + out_b, flops
 
 
-def profile_ops(cfg_builder, batch_dev, steps=20):
-    """Per-Op device time from a profiled pass (CUDA events around every instruction), with the
-    algorithmic bytes / flops of each Op class per step."""
-    import cgt_b200 as cgt
-    from cgt_b200 import compilation, runtime
-    with cgt.scoped_update_config(profile=True, use_cuda_graphs=False):
-        cfg = cfg_builder()
-        f = cfg.compile()
-    for _ in range(3):
-        f(*batch_dev)
-    base = {i: (ms, c) for (i, (_r, ms, c)) in enumerate(f.profile())}
-    for _ in range(steps):
-        runtime.l2_flush()
-        f(*batch_dev)
-    table = {}
-    for (i, (instr, (_r, ms, c))) in enumerate(zip(f.eg.instrs, f.profile())):
-        ms -= base[i][0]
-        c -= base[i][1]
-        if c <= 0 or not isinstance(instr, compilation._Return):
-            continue
-        key = type(instr.op).__name__
-        b, fl = algorithmic_cost(instr)
-        t = table.setdefault(key, dict(ms=0.0, launches=0, bytes=0, flops=0))
-        t["ms"] += ms / steps
-        t["launches"] += c / steps
-        t["bytes"] += b
-        t["flops"] += fl
+def step_algorithmic_bytes(f):
+    from cgt_b200 import compilation
+    total_b, total_f = 0, 0
+    for instr in f.eg.instrs:
+        if isinstance(instr, compilation._Return) and not getattr(instr, "once", False) and instr.write_loc.devtype == "gpu":
+            b, fl = algorithmic_cost(instr)
+            total_b += b
+            total_f += fl
+    return total_b, total_f
+
+
+# ------------------------------------------------------------------------------------------------
+# per-kernel loop: every tensor / stencil entry point of the step through the C ABI at the step's shapes
+# ------------------------------------------------------------------------------------------------
+def _dev(arr):
+    from cgt_b200 import runtime
+    return runtime.device_array(np.ascontiguousarray(arr))
+
+
+def _ptr(w):
+    return ctypes.c_void_p(w.data)
+
+
+def cifar_kernel_table(B=BATCH):
+    """[(name, shape string, per-step count, algorithmic bytes, flops, launcher)] of the CIFAR batch-B training step.
+    The launchers call the same C-ABI entry points the Ops of the compiled step call, on synthetic operands."""
+    from cgt_b200 import runtime
+    L = runtime.lib()
+    rs = np.random.RandomState(0)
+    f4 = runtime._dtype_code(np.dtype("f4"))
+    d = ctypes.c_double
+    table = []
+
+    def add(name, shape, nbytes, flops, fn):
+        table.append(dict(name=name, shape=shape, bytes=int(nbytes), flops=int(flops), fn=fn))
+
+    # conv1: 3 -> 32 channels, 32x32, through a column matrix with rows of 76 entries
+    x1 = _dev(rs.randn(B, 3, 32, 32).astype("f4"))
+    col1 = _dev(np.zeros((B * 1024, 76), "f4"))
+    w1, b1 = _dev((rs.randn(32, 75) * 0.1).astype("f4")), _dev(rs.randn(32).astype("f4"))
+    y1, m1 = _dev(np.zeros((B, 32, 1024), "f4")), _dev(np.zeros((B, 32, 1024), "i1"))
+    dy1, dw1 = _dev(rs.randn(B * 1024, 32).astype("f4")), _dev(np.zeros((32, 75), "f4"))
+    M1 = B * 1024
+    add("cgtb_im2col_ld", "conv1 %dx3x32x32 k5 p2 -> [%d,76]" % (B, M1), 4 * (B * 3 * 1024 + M1 * 76), 0,
+        lambda: L.cgtb_im2col_ld(f4, _ptr(x1), B, 3, 32, 32, 5, 5, 2, 2, 1, 1, 76, _ptr(col1)))
+    add("cgtb_conv_bias_relu_ld", "conv1 forward %dx32x75 (ld 76) + bias + relu -> NCHW" % M1,
+        4 * (M1 * 76 + 32 * 75 + 32 + M1 * 32) + M1 * 32, 2 * M1 * 32 * 75,
+        lambda: L.cgtb_conv_bias_relu_ld(_ptr(col1), M1, 75, 76, _ptr(w1), 32, _ptr(b1), 1024, _ptr(y1), _ptr(m1)))
+    add("cgtb_sgemm", "conv1 filter gradient 32x75 K=%d (ldb 76)" % M1, 4 * (M1 * 32 + M1 * 76 + 32 * 75), 2 * M1 * 32 * 75,
+        lambda: L.cgtb_sgemm(1, 0, 32, 75, M1, _ptr(dy1), 32, _ptr(col1), 76, _ptr(dw1), 75, 0))
+
+    # conv2 / conv3: stride-1 convolutions on 32-channel inputs, without a column matrix
+    def conv_layer(tag, Cin, H, Cout):
+        HW = H * H
+        xn = _dev(rs.randn(B, H, H, Cin).astype("f4"))
+        xc = _dev(rs.randn(B, Cin, H, H).astype("f4"))
+        wb = _dev((rs.randn(Cout, Cin, 5, 5) * 0.05).astype("f4"))
+        bias = _dev(rs.randn(Cout).astype("f4"))
+        y, mask = _dev(np.zeros((B, Cout, HW), "f4")), _dev(np.zeros((B, Cout, HW), "i1"))
+        dyn = _dev(rs.randn(B, H, H, Cout).astype("f4"))
+        dx, dw = _dev(np.zeros((B, Cin, HW), "f4")), _dev(np.zeros((Cout, Cin * 25), "f4"))
+        g = _dev(rs.randn(B, Cout, HW).astype("f4"))
+        gt, bs = _dev(np.zeros((B, HW, Cout), "f4")), _dev(np.zeros((Cout,), "f4"))
+        longs = (ctypes.c_long * 4)(B, Cin, H, H)
+        axes = (ctypes.c_int * 4)(0, 2, 3, 1)
+        nx, ny, nw = B * Cin * HW, B * Cout * HW, Cout * Cin * 25
+        fl = 2 * B * HW * Cout * Cin * 25
+        add("cgtb_transpose", "%s input NCHW -> NHWC %dx%dx%dx%d" % (tag, B, Cin, H, H), 8 * nx, 0,
+            lambda: L.cgtb_transpose(f4, 4, longs, axes, _ptr(xc), _ptr(xn)))
+        add("cgtb_conv_fwd_bias_relu_bank", "%s forward %dx%dx%dx%d * %dx%dx5x5 + bias + relu" % (tag, B, H, H, Cin, Cout, Cin),
+            4 * (nx + nw + Cout + ny) + ny, fl,
+            lambda: L.cgtb_conv_fwd_bias_relu_bank(_ptr(xn), B, H, H, Cin, _ptr(wb), Cout, H, H, 5, 5, 2, 2, _ptr(bias), _ptr(y), _ptr(mask)))
+        add("cgtb_relu_grad_nhwc", "%s relu gradient + NHWC + bias gradient %dx%dx%d" % (tag, B, Cout, HW), ny + 4 * ny + 4 * ny + 4 * Cout, 0,
+            lambda: L.cgtb_relu_grad_nhwc(_ptr(mask), _ptr(g), B, Cout, HW, _ptr(gt), _ptr(bs)))
+        add("cgtb_conv_dgrad_bank", "%s data gradient %dx%dx%dx%d -> %dx%dx%dx%d" % (tag, B, H, H, Cout, B, Cin, H, H), 4 * (ny + nw + nx), fl,
+            lambda: L.cgtb_conv_dgrad_bank(_ptr(dyn), B, H, H, Cout, _ptr(wb), Cin, H, H, 5, 5, 2, 2, _ptr(dx)))
+        add("cgtb_conv_wgrad", "%s filter gradient %dx%d over %d pixels" % (tag, Cout, Cin * 25, B * HW), 4 * (nx + ny + nw), fl,
+            lambda: L.cgtb_conv_wgrad(_ptr(xn), B, H, H, Cin, _ptr(dyn), H, H, Cout, 5, 5, 2, 2, _ptr(dw)))
+
+    conv_layer("conv2", 32, 15, 32)
+    conv_layer("conv3", 32, 6, 64)
+
+    # pooling 3x3 / 2 (three layers), LRN on the first pooled activations, relu gradient of conv1
+    def pool(tag, C, H, PH):
+        x = _dev(rs.randn(B, C, H, H).astype("f4"))
+        top, mask, gx = _dev(np.zeros((B, C, PH, PH), "f4")), _dev(np.zeros((B, C, PH, PH), "i4")), _dev(np.zeros((B, C, H, H), "f4"))
+        nin, nout = B * C * H * H, B * C * PH * PH
+        add("cgtb_max_pool", "%s %dx%dx%dx%d -> %dx%d" % (tag, B, C, H, H, PH, PH), 4 * nin + 8 * nout, 0,
+            lambda: L.cgtb_max_pool(f4, _ptr(x), B, C, H, H, 3, 3, 0, 0, 2, 2, PH, PH, _ptr(top), _ptr(mask)))
+        add("cgtb_max_pool_pullback", "%s %dx%dx%dx%d <- %dx%d" % (tag, B, C, H, H, PH, PH), 8 * nout + 4 * nin, 0,
+            lambda: L.cgtb_max_pool_pullback(f4, _ptr(mask), _ptr(top), B, C, PH, PH, H, H, 3, 3, 0, 0, 2, 2, _ptr(gx)))
+
+    pool("pool1", 32, 32, 15)
+    pool("pool2", 32, 15, 6)
+    pool("pool3", 64, 6, 2)
+    xl = _dev(rs.randn(B, 32, 15, 15).astype("f4"))
+    t, sc, gl = (_dev(np.zeros((B, 32, 15, 15), "f4")) for _ in range(3))
+    nl = B * 32 * 225
+    add("cgtb_lrn_forward", "LRN(5) %dx32x15x15" % B, 12 * nl, 0,
+        lambda: L.cgtb_lrn_forward(f4, _ptr(xl), B, 32, 15, 15, 5, d(1e-4), d(0.75), _ptr(t), _ptr(sc)))
+    add("cgtb_lrn_backward", "LRN(5) gradient %dx32x15x15" % B, 20 * nl, 0,
+        lambda: L.cgtb_lrn_backward(f4, _ptr(xl), _ptr(t), _ptr(sc), _ptr(xl), B, 32, 15, 15, 5, d(1e-4), d(0.75), _ptr(gl)))
+    g1 = _dev(rs.randn(B, 32, 1024).astype("f4"))
+    gt1, bs1 = _dev(np.zeros((B, 1024, 32), "f4")), _dev(np.zeros((32,), "f4"))
+    n1 = B * 32 * 1024
+    add("cgtb_relu_grad_nhwc", "conv1 relu gradient + NHWC + bias gradient %dx32x1024" % B, n1 + 8 * n1 + 128, 0,
+        lambda: L.cgtb_relu_grad_nhwc(_ptr(m1), _ptr(g1), B, 32, 1024, _ptr(gt1), _ptr(bs1)))
     return table
+
+
+def measure_kernels(table, launches=200):
+    """Median device time of each entry over `launches` cold-L2 launches: flush, event, call, event, all queued
+    without a host synchronisation in between (so no launch gap is timed); one synchronisation at the end."""
+    from cgt_b200 import runtime
+    out = []
+    for ent in table:
+        for _ in range(3):
+            runtime.check(ent["fn"](), ent["name"])
+        runtime.synchronize()
+        k0 = runtime.kernel_launches()
+        runtime.check(ent["fn"](), ent["name"])
+        n_kernels = runtime.kernel_launches() - k0
+        evs = [(runtime.Event(), runtime.Event()) for _ in range(launches)]
+        for (e0, e1) in evs:
+            runtime.l2_flush()
+            e0.record()
+            runtime.check(ent["fn"](), ent["name"])
+            e1.record()
+        runtime.synchronize()
+        ts = np.array([e0.elapsed_ms(e1) * 1e3 for (e0, e1) in evs])
+        out.append(dict(name=ent["name"], shape=ent["shape"], us=float(np.median(ts)), us_min=float(ts.min()), kernels=int(n_kernels),
+                        bytes=ent["bytes"], flops=ent["flops"]))
+    return out
 
 
 # ------------------------------------------------------------------------------------------------
 # timed loops
 # ------------------------------------------------------------------------------------------------
-def timed_steps(f, batches, steps, warmup, flush=True, prefetch=False):
-    """Returns (total device ms over `steps`, last loss). Each step: untimed L2 flush, event, step, event.
-    prefetch: inside every timed step the NEXT step's batch is handed to f.prefetch before the step is called, so
-    its host->device copy (one per step, like without prefetch) runs on the copy stream beside the step."""
+def timed_blocks(f, batches, steps, warmup, repeats, flush=True, prefetch=False):
+    """`repeats` blocks of `steps` steps after `warmup` steps. Returns (list of block times in device ms, each the max
+    over ranks; last loss). Each step: untimed L2 flush, event, step, event. prefetch: inside every timed step the
+    NEXT step's batch is handed to f.prefetch before the step is called, so its host->device copy (one per step)
+    runs on the copy stream beside the step."""
     from cgt_b200 import parallel, runtime
     nb = len(batches)
     if prefetch:
@@ -177,36 +307,74 @@ def timed_steps(f, batches, steps, warmup, flush=True, prefetch=False):
             f.prefetch(*batches[(i + 1) % nb])
         f(*batches[i % nb])
     e0, e1 = runtime.Event(), runtime.Event()
-    parallel.barrier()
-    runtime.synchronize()
-    total = 0.0
-    loss = None
+    blocks, loss, it = [], None, warmup
+    for _ in range(repeats):
+        parallel.barrier()
+        runtime.synchronize()
+        total = 0.0
+        for _i in range(steps):
+            if flush:
+                runtime.l2_flush()
+                runtime.synchronize()
+            e0.record()
+            if prefetch:
+                f.prefetch(*batches[(it + 1) % nb])
+            loss = f(*batches[it % nb])[0]
+            e1.record()
+            total += e0.elapsed_ms(e1)
+            it += 1
+        runtime.synchronize()
+        parallel.barrier()
+        blocks.append(parallel.all_max(total))
+    return blocks, float(loss)
+
+
+def _summary(blocks, n_examples_per_block):
+    med = float(np.median(blocks))
+    return dict(value=n_examples_per_block / (med / 1e3), ms_block=med,
+                spread={"min": n_examples_per_block / (max(blocks) / 1e3), "max": n_examples_per_block / (min(blocks) / 1e3)})
+
+
+def parity_check(config, steps=3):
+    """`steps` update steps from a fresh seed on the GPU and on the CPU oracle: largest relative loss error."""
+    from cgt_b200 import configs
+    from oracle import cpu_backend, oracle
+    build = getattr(configs, CONFIGS[config]["builder"])
+    ref, cfg = build(batch=BATCH, seed=7), build(batch=BATCH, seed=7)
+    f_cpu = cpu_backend.function(ref.inputs, [ref.loss], updates=ref.updates, impl="ref" if oracle.have_ref() else "port")
+    f_gpu = cfg.compile()
+    worst = 0.0
     for i in range(steps):
-        if flush:
-            runtime.l2_flush()
-            runtime.synchronize()
-        e0.record()
-        if prefetch:
-            f.prefetch(*batches[(warmup + i + 1) % nb])
-        loss = f(*batches[(warmup + i) % nb])[0] if prefetch else f(*batches[i % nb])[0]
-        e1.record()
-        total += e0.elapsed_ms(e1)
-    runtime.synchronize()
-    parallel.barrier()
-    return parallel.all_max(total), float(loss)
+        b = ref.batch(100 + i)
+        g, c = float(f_gpu(*b)[0]), float(f_cpu(*b)[0])
+        worst = max(worst, abs(g - c) / max(abs(c), 1e-12))
+    return {"loss_rel_err": worst, "steps": steps, "against": "CPU oracle (reference kernels where built)", "bar": 1e-3}
+
+
+def replica_diff(params):
+    """max over ranks and parameters of |param - rank 0's param| (0.0 when the replicas stayed identical)."""
+    import torch
+    import torch.distributed as dist
+    worst = 0.0
+    for p in params:
+        mine = torch.from_numpy(np.ascontiguousarray(p.op.get_value()).copy())
+        ref = mine.clone()
+        dist.broadcast(ref, src=0)
+        worst = max(worst, float((mine - ref).abs().max()))
+    t = torch.tensor([worst], dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
 
 
 def run_b200(args):
-    import cgt_b200 as cgt
     from cgt_b200 import configs, parallel, runtime
     rank, world = parallel.init_process_group() if int(os.environ.get("WORLD_SIZE", "1")) > 1 else (0, 1)
     if world == 1:
         runtime.ensure_init()
     assert world == args.gpus, "--gpus %d but WORLD_SIZE is %d (launch with torch.distributed.run)" % (args.gpus, world)
-
-    def builder():
-        return configs.build_cifar(batch=BATCH, grad_hook=parallel.allreduce_mean)
-    cfg = builder()
+    meta = CONFIGS[args.config]
+    build = getattr(configs, meta["builder"])
+    cfg = build(batch=BATCH, grad_hook=parallel.allreduce_mean)
     f = cfg.compile()
     # every rank draws its own 128-example shard (weak scaling); 4 batches are cycled
     host_batches, dev_batches = [], []
@@ -224,60 +392,75 @@ def run_b200(args):
     sampler = ClockSampler(runtime.lib().cgtb_device())
     if rank == 0:
         sampler.start()
-    ms_dev, loss = timed_steps(f, dev_batches, args.steps, args.warmup)
+    K, R = args.steps, args.repeats
+    dev_blocks, loss = timed_blocks(f, dev_batches, K, args.warmup, R)
     st = f.stats()
-    launches = int(st["last_kernel_launches"]) * args.steps
-    ms_e2e_serial, _ = timed_steps(f, host_batches, args.steps, max(3, args.warmup // 4))
-    ms_e2e, _ = timed_steps(f, host_batches, args.steps, max(3, args.warmup // 4), prefetch=True)
+    launches = int(st["last_kernel_launches"]) * K * R
+    e2e_serial_blocks, _ = timed_blocks(f, host_batches, K, max(3, args.warmup // 4), max(3, R // 3))
+    e2e_blocks, _ = timed_blocks(f, host_batches, K, max(3, args.warmup // 4), R, prefetch=True)
     clocks = sampler.stop() if rank == 0 else None
+    rdiff = replica_diff(cfg.params) if world > 1 else None
 
     out = None
     if rank == 0:
-        n_examples = BATCH * world * args.steps
+        n_block = BATCH * world * K
+        dev, e2e, e2e_serial = _summary(dev_blocks, n_block), _summary(e2e_blocks, n_block), _summary(e2e_serial_blocks, n_block)
         out = {
-            "metric": METRIC, "value": n_examples / (ms_dev / 1e3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_dev / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32 (3xTF32 tensor-core GEMM where used, fp32 elsewhere)", "data": "synthetic",
-            "config": {"workload": "CIFAR-shape convnet, batch 128 per GPU, fwd+bwd+SGD (BASELINE configs[1])",
-                       "global_batch": BATCH * world, "parallelism": "dp%d" % world,
+            "metric": meta["metric"], "value": dev["value"], "unit": UNIT, "n_gpus": world, "steps": K, "repeats": R,
+            "warmup": args.warmup, "ms_per_step": dev["ms_block"] / K, "spread": dev["spread"], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32 (3xTF32 tensor-core GEMM where used, fp32 elsewhere)",
+            "data": "synthetic",
+            "config": {"workload": meta["workload"], "global_batch": BATCH * world, "parallelism": "dp%d" % world,
                        "l2": "flushed between timed steps (256 MiB memset, untimed)", "cuda_graphs": bool(st["segments_captured"]),
+                       "timing": "median of %d blocks of %d steps; every block between a barrier and a synchronisation, max over ranks" % (R, K),
                        "kernels_per_step": int(st["last_kernel_launches"]), "graph_launches_per_step": int(st["last_graph_launches"])},
-            "e2e": {"value": n_examples / (ms_e2e / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
-                    "ms_per_step": ms_e2e / args.steps,
+            "e2e": {"value": e2e["value"], "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
+                    "ms_per_step": e2e["ms_block"] / K, "spread": e2e["spread"],
                     "input_upload": "pinned host batch -> f.prefetch: copied on the copy stream while the step before it runs; one copy per timed step",
-                    "value_copy_inside_step": n_examples / (ms_e2e_serial / 1e3)},
+                    "value_copy_inside_step": e2e_serial["value"]},
             "gpu_launches": launches, "clocks": clocks, "final_loss": loss,
         }
-    # roofline of the dominant kernel (rank 0, on the single-GPU graph: the per-GPU work is the same at every
-    # N under weak scaling) and, at N = 1, the CPU baseline
+        if rdiff is not None:
+            out["replica_max_abs_diff"] = rdiff
+    # roofline of the dominant kernel (rank 0; the per-GPU work is the same at every N under weak scaling) and, at
+    # N = 1, parity against the CPU oracle and the CPU baseline
     if rank == 0 and not args.no_extras:
         peaks = load_peaks()
-        table = profile_ops(lambda: configs.build_cifar(batch=BATCH), dev_batches[0])
-        total_ms = sum(t["ms"] for t in table.values())
-        dom = max(table.items(), key=lambda kv: kv[1]["ms"])
-        name, t = dom
-        sec = t["ms"] / 1e3
-        gbs = t["bytes"] / sec / 1e9 if sec > 0 else 0.0
-        tfl = t["flops"] / sec / 1e12 if sec > 0 else 0.0
         tf32_peak = peaks["bf16_tflops"] / 2.0  # dense TF32 runs at half the bf16 rate on this part
-        hbm_floor, tensor_floor = t["bytes"] / (peaks["hbm_gbs"] * 1e9), t["flops"] / (tf32_peak * 1e12)
-        if t["flops"] and tensor_floor > hbm_floor:
-            roof = {"bound": "tensor", "achieved": tfl, "peak": tf32_peak, "unit": "TFLOP/s", "frac": tfl / tf32_peak}
-        else:
-            roof = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"]}
-        ratio = NCU_TRAFFIC_RATIO.get(name)
-        roof.update({"kernel": name, "traffic": (ratio * t["bytes"]) if ratio else None,
-                     "traffic_note": NCU_TRAFFIC_NOTE.get(name), "peak_source": peaks["source"],
-                     "share_of_step": t["ms"] / total_ms, "launches_per_step": t["launches"],
-                     "algorithmic_bytes_per_step": t["bytes"], "ms_per_step": t["ms"]})
-        out["roofline"] = roof
-        out["per_op"] = {k: {"ms": round(v["ms"], 4), "GB/s": round(v["bytes"] / (v["ms"] / 1e3) / 1e9, 1) if v["ms"] > 0 else None,
-                             "share": round(v["ms"] / total_ms, 3)} for (k, v) in sorted(table.items(), key=lambda kv: -kv[1]["ms"])}
-        step_bytes = sum(v["bytes"] for v in table.values())
-        out["step_roofline"] = {"algorithmic_bytes_per_step": step_bytes, "hbm_floor_ms": step_bytes / (peaks["hbm_gbs"] * 1e9) * 1e3,
-                                "frac": (step_bytes / (peaks["hbm_gbs"] * 1e9) * 1e3) / (ms_dev / args.steps)}
+        step_b, step_f = step_algorithmic_bytes(f)
+        ms_step = out["ms_per_step"]
+        out["step_roofline"] = {"algorithmic_bytes_per_step": step_b, "algorithmic_flops_per_step": step_f,
+                                "hbm_floor_ms": step_b / (peaks["hbm_gbs"] * 1e9) * 1e3,
+                                "frac": (step_b / (peaks["hbm_gbs"] * 1e9) * 1e3) / ms_step}
+        if args.config == "cifar":
+            per = measure_kernels(cifar_kernel_table(), launches=args.kernel_launches)
+            total_us = sum(k["us"] for k in per)
+            for k in per:
+                sec = k["us"] * 1e-6
+                hbm_floor, tensor_floor = k["bytes"] / (peaks["hbm_gbs"] * 1e9), k["flops"] / (tf32_peak * 1e12)
+                k["GB/s"] = k["bytes"] / sec / 1e9
+                k["TFLOP/s"] = k["flops"] / sec / 1e12
+                k["bound"] = "tensor" if tensor_floor > hbm_floor else "hbm"
+                k["frac"] = (k["TFLOP/s"] / tf32_peak) if k["bound"] == "tensor" else (k["GB/s"] / peaks["hbm_gbs"])
+                k["share"] = k["us"] / total_us
+            dom = max(per, key=lambda k: k["us"])
+            out["roofline"] = {
+                "bound": dom["bound"], "achieved": dom["TFLOP/s"] if dom["bound"] == "tensor" else dom["GB/s"],
+                "peak": tf32_peak if dom["bound"] == "tensor" else peaks["hbm_gbs"],
+                "unit": "TFLOP/s" if dom["bound"] == "tensor" else "GB/s", "frac": dom["frac"], "kernel": dom["name"], "shape": dom["shape"],
+                "us_per_launch": dom["us"], "algorithmic_bytes": dom["bytes"], "algorithmic_flops": dom["flops"],
+                "traffic": NCU_TRAFFIC.get(dom["name"]), "traffic_note": NCU_TRAFFIC_NOTE.get(dom["name"]),
+                "peak_source": peaks["source"], "share_of_listed_kernels": dom["share"],
+                "timing": "median of %d cold-L2 launches through the C ABI, CUDA events on the launching stream" % args.kernel_launches,
+                "tf32_peak_note": "dense TF32 peak taken as half of the measured bf16 peak; 3xTF32 issues three tensor MACs per algorithmic MAC",
+            }
+            out["per_kernel"] = [{"name": k["name"], "shape": k["shape"], "us": round(k["us"], 2), "kernels": k["kernels"], "bytes": k["bytes"],
+                                  "GB/s": round(k["GB/s"], 1), "TFLOP/s": round(k["TFLOP/s"], 2), "bound": k["bound"],
+                                  "frac": round(k["frac"], 4), "share": round(k["share"], 4)} for k in sorted(per, key=lambda k: -k["us"])]
         if world == 1:
-            out["cpu_baseline"] = cpu_baseline(sample_steps=5, warmup=2)
+            out["parity"] = parity_check(args.config)
+            if args.config == "cifar":
+                out["cpu_baseline"] = cpu_baseline(sample_steps=5, warmup=2)
     parallel.barrier()
     if rank == 0:
         print(json.dumps(out))
@@ -285,28 +468,21 @@ def run_b200(args):
         parallel.shutdown()
 
 
-# DRAM traffic of the dominant Op class from an ncu capture (dram__bytes_read.sum + dram__bytes_write.sum of one
-# launch, summary under profiles/), as a ratio to that launch's algorithmic bytes; `traffic` scales the class's
-# algorithmic bytes per step by it (the captured launch streams its operands once, like every launch of the class).
-NCU_TRAFFIC_RATIO = {"Mul22": 96.33 / 95.95, "ConvBiasRelu": 96.33 / 95.95}
-NCU_TRAFFIC_NOTE = {"Mul22": "ncu capture of the conv2 forward product 28800x32x800 (sgemm_tma_kernel): 92.31 MB read + 4.02 MB "
-                             "written against 95.95 MB algorithmic; scaled to the class's algorithmic bytes per step",
-                    "ConvBiasRelu": "same kernel as Mul22 with the output stage in its epilogue. ncu captures of its products: conv2 "
-                                    "28800x32x800 92.31 MB read + 4.02 MB written against 95.95 MB algorithmic; conv1 131072x32x76 "
-                                    "39.90 MB read against 39.85 MB of operand (its 16.8 MB result was still in L2 when the kernel "
-                                    "ended: 0.02 MB written). Operands are streamed once; the conv2 ratio scales the class's "
-                                    "algorithmic bytes per step"}
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum, bytes per launch) of an entry point's main kernel from an
+# ncu capture at the shape listed in `per_kernel`; the summaries are under profiles/.
+NCU_TRAFFIC = {}
+NCU_TRAFFIC_NOTE = {}
 
 
 # ------------------------------------------------------------------------------------------------
 # CPU arm: the reference's CPU implementation of the path (its own im2col.h / pooling.h / lrn.cuh-as-C++
 # when oracle/_ref is built, restated loops otherwise, OpenBLAS sgemm on all host cores)
 # ------------------------------------------------------------------------------------------------
-def _cpu_function(batch):
+def _cpu_function(batch, config="cifar"):
     import cgt_b200  # noqa: F401  (graph front-end only; nothing is placed on a GPU here)
     from cgt_b200 import configs
     from oracle import cpu_backend, oracle
-    cfg = configs.build_cifar(batch=batch)
+    cfg = getattr(configs, CONFIGS[config]["builder"])(batch=batch)
     kind = "reference" if oracle.have_ref() else "port"
     f = cpu_backend.function(cfg.inputs, [cfg.loss], updates=cfg.updates, impl="ref" if kind == "reference" else "port")
     return cfg, f, kind
@@ -333,7 +509,8 @@ def run_reference(args):
     if rank != 0:
         return
     budget_s = 150.0
-    cfg, f, kind = _cpu_function(BATCH)
+    meta = CONFIGS[args.config]
+    cfg, f, kind = _cpu_function(BATCH, args.config)
     b = cfg.batch(0)
     t0 = time.perf_counter()
     f(*b)
@@ -342,7 +519,7 @@ def run_reference(args):
     total_steps = args.steps + args.warmup
     if t1 * total_steps > budget_s:  # bounded sample: a smaller batch per step, same network
         batch = int(max(1, min(BATCH, BATCH * budget_s / (t1 * total_steps))))
-        cfg, f, kind = _cpu_function(batch)
+        cfg, f, kind = _cpu_function(batch, args.config)
         b = cfg.batch(0)
     for _ in range(args.warmup):
         f(*b)
@@ -354,10 +531,10 @@ def run_reference(args):
     value = batch * args.steps / dt
     sample = "each step is one full training step on %d of the %d examples of a batch (same network and op sequence)" % (batch, BATCH)
     out = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "impl": "reference", "metric": meta["metric"], "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "CIFAR-shape convnet, fwd+bwd+SGD (BASELINE configs[1]) on the host cores", "batch_per_step": batch},
+        "config": {"workload": meta["workload"] + " on the host cores", "batch_per_step": batch},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": os.cpu_count(), "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "final_loss": float(loss),
@@ -368,12 +545,16 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--repeats", type=int, default=15, help="timed blocks of --steps steps; the median block is reported")
+    ap.add_argument("--kernel-launches", type=int, default=200, help="cold-L2 launches per entry of the per-kernel list")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--no-extras", action="store_true", help="skip the per-Op profile pass and the CPU baseline (for ncu runs)")
+    ap.add_argument("--config", default="cifar", choices=sorted(CONFIGS))
+    ap.add_argument("--no-extras", action="store_true", help="skip the per-kernel loop, parity and the CPU baseline (for ncu runs)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    args.repeats = max(args.repeats, 1)
     if args.impl == "reference":
         run_reference(args)
     else:

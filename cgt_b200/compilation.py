@@ -340,8 +340,8 @@ def _rewire(outputs, updatetargs, replace):
 
 
 def fuse_conv_dgrad(outputs, updatetargs, node2shape):
-    """Col2Im(Reshape(Mul22{N,N}(Reshape(dy NHWC), Reshape(W)))) -> ConvDgrad(dy, W transposed to
-    [C, kh, kw, Cin]) for stride-1 convolutions whose extents the kernel supports (input channels of the
+    """Col2Im(Reshape(Mul22{N,N}(Reshape(dy NHWC), Reshape(W)))) -> ConvDgrad(dy, W) (the filter bank as stored;
+    the kernel's filter-splitting pass rearranges it) for stride-1 convolutions whose extents the kernel supports (input channels of the
     product a multiple of 32, at most 128 image channels in multiples of 16, rows of at most 128 pixels).
     The intermediate nodes must have no other consumer."""
     from .nn_ops import im2col as im2col_ops
@@ -385,11 +385,7 @@ def fuse_conv_dgrad(outputs, updatetargs, node2shape):
             continue
         if Cin % 32 != 0 or C % 16 != 0 or C > 128 or W > 128:
             continue
-        wr = core.Result(core.Transpose((1, 2, 3, 0)), [w4])
-        ws = node2shape[w4]
-        node2shape[wr] = [ws[1], ws[2], ws[3], ws[0]]
-        wr.props.update(node.props)
-        dx = core.Result(im2col_ops.ConvDgrad(info), [t4, wr] + list(node.parents[1:]))
+        dx = core.Result(im2col_ops.ConvDgrad(info, w_bank=True), [t4, w4] + list(node.parents[1:]))
         node2shape[dx] = node2shape[node]
         dx.props.update(node.props)
         replace[node] = dx
@@ -491,7 +487,7 @@ def fuse_conv_grad_input(outputs, updatetargs, node2shape):
 
 
 def fuse_conv_implicit(outputs, updatetargs, node2shape):
-    """ConvBiasRelu(Reshape(Im2Col(x)), Reshape(W), bias, ...) -> ConvFwdBiasRelu(x NHWC, W as [Cout,kh,kw,Cin], bias, ...)
+    """ConvBiasRelu(Reshape(Im2Col(x)), Reshape(W), bias, ...) -> ConvFwdBiasRelu(x NHWC, W, bias, ...)
     and, for the same column matrix, Mul22{T,N}(Reshape(dy NHWC), Reshape(Im2Col(x))) -> ConvWgradImplicit(x NHWC, dy NHWC),
     for stride-1 convolutions whose extents the kernels support (input channels a multiple of 32, output channels a
     multiple of 16, rows of at most 32 pixels). Applies only when every consumer of the column matrix is one of the
@@ -550,11 +546,7 @@ def fuse_conv_implicit(outputs, updatetargs, node2shape):
         xt.props.update(im.props)
         for c in fwd:
             w4 = c.parents[1].parents[0]
-            ws = node2shape[w4]
-            wr = core.Result(core.Transpose((0, 2, 3, 1)), [w4])
-            node2shape[wr] = [ws[0], ws[2], ws[3], ws[1]]
-            wr.props.update(c.props)
-            new = core.Result(im2col_ops.ConvFwdBiasRelu(info), [xt, wr] + list(c.parents[2:]))
+            new = core.Result(im2col_ops.ConvFwdBiasRelu(info, w_bank=True), [xt, w4] + list(c.parents[2:]))
             node2shape[new] = node2shape[c]
             new.props.update(c.props)
             replace[c] = new

@@ -832,7 +832,7 @@ conv_tsa_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant_
       const Tile c = tile_of(p, t);
       const int ab = NACC > 1 ? (int)(it & 1u) : 0;
       const uint32_t use = NACC > 1 ? it >> 1 : it;
-      ok = mbar_wait_or_abort(smem_u32(&accum_full[ab]), use & 1u, abortp);
+      ok = mbar_wait_sleepy(smem_u32(&accum_full[ab]), use & 1u, abortp);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       store_tile<1, 1>(p, c, tmem_d + (uint32_t)(ab * cp.acc_cols), quarter, 0, lane);
@@ -861,6 +861,31 @@ __global__ void split_rows_kernel(const float* __restrict__ Y, long rows, long K
     if (k < K) split_tf32(mn ? Y[k * ld + r] : Y[r * ld + k], h, l);
     out[r * Kp + k] = __uint_as_float(h);
     out[n + r * Kp + k] = __uint_as_float(l);
+  }
+}
+
+// Filter bank -> the K-major operand of the implicit convolution: row r (an output channel of the product), entry
+// k = tap*Cs + c. layout 0: already so, W[r*K + k]; 1: bank [N][Cs][kk] (a layer's filters as stored, forward
+// product): W[(r*Cs + c)*kk + tap]; 2: bank [Cs][N][kk] (the same filters, data gradient): W[(c*N + r)*kk + tap].
+// split != 0: out[0][r][k] = w rounded to TF32, out[1][r][k] = the rest cut to TF32; split == 0: out[r][k] = w.
+__global__ void split_filter_kernel(const float* __restrict__ W, int N, int Cs, int kk, int layout, int split, float* __restrict__ out) {
+  const long K = (long)kk * Cs, n = (long)N * K;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / K);
+    const int k = (int)(i - (long)r * K);
+    const int tap = k / Cs, c = k - tap * Cs;
+    float w;
+    if (layout == 1) w = W[((long)r * Cs + c) * kk + tap];
+    else if (layout == 2) w = W[((long)c * N + r) * kk + tap];
+    else w = W[i];
+    if (split) {
+      uint32_t h, l;
+      split_tf32(w, h, l);
+      out[i] = __uint_as_float(h);
+      out[n + i] = __uint_as_float(l);
+    } else {
+      out[i] = w;
+    }
   }
 }
 
@@ -979,10 +1004,11 @@ bool use_tsa() {
 
 // Pre-split Y (rows x K) into [2][rows][Kp] at `dst` and build its tensor map (box 32 x UN x 1, third coordinate
 // 0 = hi, 1 = lo).
-bool split_y(const Side& Y, long K, int UN, float* dst, long Kp, CUtensorMap* mapY) {
+bool split_y(const Side& Y, long K, int UN, float* dst, long Kp, CUtensorMap* mapY, int filter_layout = 0, int Cs = 0, int kk = 0) {
   const long n = Y.rows * Kp;
   const unsigned blocks = (unsigned)std::min<long>(cgtb_ceil_div(n, 256), 8L * rt().sm_count);
-  CGTB_LAUNCH(split_rows_kernel, blocks, 256, 0, Y.base, Y.rows, K, Y.ld, Y.mn ? 1 : 0, dst, Kp);
+  if (filter_layout) CGTB_LAUNCH(split_filter_kernel, blocks, 256, 0, Y.base, (int)Y.rows, Cs, kk, filter_layout, 1, dst);
+  else CGTB_LAUNCH(split_rows_kernel, blocks, 256, 0, Y.base, Y.rows, K, Y.ld, Y.mn ? 1 : 0, dst, Kp);
   EncodeTiledFn fn = encoder();
   if (!fn) return false;
   cuuint64_t dims[3] = {(cuuint64_t)Kp, (cuuint64_t)Y.rows, 2};
@@ -1090,8 +1116,8 @@ int sgemm_tma(int tA, int tB, long P, long M, long N, long K, const float* A, lo
 // (rows*Wd <= 128 pixels) or, for small images, several whole images. With `ep` the bias / relu / mask output stage
 // is applied to the accumulator (forward product of a layer).
 // returns 0 done, 1 error, -1 not eligible
-int conv_implicit_tma(const float* src, long B, int Hs, int Ws, int Cs, const float* wr, int N, int Hd, int Wd, int kh, int kw,
-                      int ph, int pw, int sign, float* out, const ConvEpilogue* ep) {
+int conv_implicit_tma(const float* src, long B, int Hs, int Ws, int Cs, const float* wr, int w_layout, int N, int Hd, int Wd, int kh,
+                      int kw, int ph, int pw, int sign, float* out, const ConvEpilogue* ep) {
   if (B <= 0 || N <= 0 || Hd <= 0 || Wd <= 0) return 0;
   if (Cs % 32 != 0 || N % 16 != 0 || Wd > 128 || B >= (1L << 30) || kh <= 0 || kw <= 0) return -1;
   if (((uintptr_t)src & 15) != 0 || ((uintptr_t)wr & 15) != 0) return -1;
@@ -1220,7 +1246,9 @@ int conv_implicit_tma(const float* src, long B, int Hs, int Ws, int Cs, const fl
   p.ytiles = ytiles;
   p.total_tiles = tiles * ytiles * nsplit;
   const long total = B * (long)N * HW;
-  const size_t split_bytes = tsa ? ((((size_t)2 * N * K * sizeof(float)) + 255) & ~(size_t)255) : 0;
+  // the pre-split filters (or, for the kernel that converts in its loop, the rearranged copy of a filter bank)
+  const size_t split_bytes = tsa ? ((((size_t)2 * N * K * sizeof(float)) + 255) & ~(size_t)255)
+                                 : (w_layout ? ((((size_t)N * K * sizeof(float)) + 255) & ~(size_t)255) : 0);
   const size_t slab_bytes = nsplit > 1 ? (size_t)nsplit * total * sizeof(float) : 0;
   char* blk = nullptr;
   if (split_bytes + slab_bytes) {
@@ -1241,7 +1269,7 @@ int conv_implicit_tma(const float* src, long B, int Hs, int Ws, int Cs, const fl
   }
   Side Y = {wr, K, false, N, 0};
   if (tsa) {
-    if (!split_y(Y, K, UN, (float*)blk, K, &mapY)) return -1;
+    if (!split_y(Y, K, UN, (float*)blk, K, &mapY, w_layout, Cs, kh * kw)) return -1;
     static bool cfg = false;
     if (!cfg) {
       CGTB_CUDA_TRY(cudaFuncSetAttribute(conv_tsa_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048));
@@ -1250,6 +1278,11 @@ int conv_implicit_tma(const float* src, long B, int Hs, int Ws, int Cs, const fl
     const unsigned grid = (unsigned)std::min<long>(p.total_tiles, want);  // one CTA per SM
     CGTB_LAUNCH(conv_tsa_kernel, grid, kThreadsConv, smem, mapX, mapY, cp);
   } else {
+    if (w_layout) {
+      const unsigned blocks = (unsigned)std::min<long>(cgtb_ceil_div((long)N * K, 256), 8L * rt().sm_count);
+      CGTB_LAUNCH(split_filter_kernel, blocks, 256, 0, wr, N, Cs, kh * kw, w_layout, 0, (float*)blk);
+      Y.base = (const float*)blk;
+    }
     if (!encode(&mapY, Y, K, 1, UN)) return -1;
     int rc = launch_tma<false, false, 1>(mapX, mapY, p, smem);
     if (rc) return rc;
@@ -1359,29 +1392,45 @@ int conv_wgrad_tma(const float* src, long B, int Hs, int Ws, int Cs, const float
 
 }  // namespace cgtb
 
-CGTB_API int cgtb_conv_dgrad(const float* dy_nhwc, long B, int Ho, int Wo, int Cin, const float* w_rearranged, int C, int H, int W,
-                             int kh, int kw, int ph, int pw, float* dx_nchw) {
+static int conv_dgrad_any(const float* dy_nhwc, long B, int Ho, int Wo, int Cin, const float* w, int layout, int C, int H, int W, int kh,
+                          int kw, int ph, int pw, float* dx_nchw) {
   if (!require_runtime("cgtb_conv_dgrad")) return 1;
   if (C > 128) return fail("cgtb_conv_dgrad: at most 128 image channels");
-  int rc = cgtb::conv_implicit_tma(dy_nhwc, B, Ho, Wo, Cin, w_rearranged, C, H, W, kh, kw, ph, pw, -1, dx_nchw, nullptr);
+  int rc = cgtb::conv_implicit_tma(dy_nhwc, B, Ho, Wo, Cin, w, layout, C, H, W, kh, kw, ph, pw, -1, dx_nchw, nullptr);
   if (rc < 0)
     return fail("cgtb_conv_dgrad: not supported for Cin=%d (multiple of 32), C=%d (multiple of 16, at most 128), W=%d (at most 128) "
                 "or an unaligned operand; use cgtb_sgemm + cgtb_col2im", Cin, C, W);
   return rc;
 }
+CGTB_API int cgtb_conv_dgrad(const float* dy_nhwc, long B, int Ho, int Wo, int Cin, const float* w_rearranged, int C, int H, int W,
+                             int kh, int kw, int ph, int pw, float* dx_nchw) {
+  return conv_dgrad_any(dy_nhwc, B, Ho, Wo, Cin, w_rearranged, 0, C, H, W, kh, kw, ph, pw, dx_nchw);
+}
+CGTB_API int cgtb_conv_dgrad_bank(const float* dy_nhwc, long B, int Ho, int Wo, int Cin, const float* w_bank, int C, int H, int W,
+                                  int kh, int kw, int ph, int pw, float* dx_nchw) {
+  return conv_dgrad_any(dy_nhwc, B, Ho, Wo, Cin, w_bank, 2, C, H, W, kh, kw, ph, pw, dx_nchw);
+}
 
-CGTB_API int cgtb_conv_fwd_bias_relu(const float* x_nhwc, long B, int H, int W, int Cin, const float* w_rearranged, int Cout, int Ho,
-                                     int Wo, int kh, int kw, int ph, int pw, const float* bias, float* y_nchw, int8_t* mask_nchw) {
+static int conv_fwd_any(const float* x_nhwc, long B, int H, int W, int Cin, const float* w, int layout, int Cout, int Ho, int Wo, int kh,
+                        int kw, int ph, int pw, const float* bias, float* y_nchw, int8_t* mask_nchw) {
   if (!require_runtime("cgtb_conv_fwd_bias_relu")) return 1;
   if (Ho != H + 2 * ph - kh + 1 || Wo != W + 2 * pw - kw + 1)
     return fail("cgtb_conv_fwd_bias_relu: output %dx%d is not that of a stride-1 %dx%d convolution of %dx%d with padding %d,%d", Ho, Wo,
                 kh, kw, H, W, ph, pw);
   cgtb::ConvEpilogue ep = {bias, y_nchw, mask_nchw, (long)Ho * Wo};
-  int rc = cgtb::conv_implicit_tma(x_nhwc, B, H, W, Cin, w_rearranged, Cout, Ho, Wo, kh, kw, ph, pw, +1, nullptr, &ep);
+  int rc = cgtb::conv_implicit_tma(x_nhwc, B, H, W, Cin, w, layout, Cout, Ho, Wo, kh, kw, ph, pw, +1, nullptr, &ep);
   if (rc < 0)
     return fail("cgtb_conv_fwd_bias_relu: not supported for Cin=%d (multiple of 32), Cout=%d (multiple of 16; of 128 when above 128), "
                 "Wo=%d (at most 128) or an unaligned operand; use cgtb_im2col + cgtb_conv_bias_relu", Cin, Cout, Wo);
   return rc;
+}
+CGTB_API int cgtb_conv_fwd_bias_relu(const float* x_nhwc, long B, int H, int W, int Cin, const float* w_rearranged, int Cout, int Ho,
+                                     int Wo, int kh, int kw, int ph, int pw, const float* bias, float* y_nchw, int8_t* mask_nchw) {
+  return conv_fwd_any(x_nhwc, B, H, W, Cin, w_rearranged, 0, Cout, Ho, Wo, kh, kw, ph, pw, bias, y_nchw, mask_nchw);
+}
+CGTB_API int cgtb_conv_fwd_bias_relu_bank(const float* x_nhwc, long B, int H, int W, int Cin, const float* w_bank, int Cout, int Ho,
+                                          int Wo, int kh, int kw, int ph, int pw, const float* bias, float* y_nchw, int8_t* mask_nchw) {
+  return conv_fwd_any(x_nhwc, B, H, W, Cin, w_bank, 1, Cout, Ho, Wo, kh, kw, ph, pw, bias, y_nchw, mask_nchw);
 }
 
 CGTB_API int cgtb_conv_wgrad(const float* x_nhwc, long B, int H, int W, int Cin, const float* dy_nhwc, int Ho, int Wo, int Cout, int kh,

@@ -15,6 +15,7 @@
 //     the span's device instructions see is unchanged, so a shape change, a set_value() on a shared
 //     variable or a changed host scalar falls back to eager issue and re-capture.
 #include "runtime.h"
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -368,6 +369,142 @@ static int fire_profiled(cgtbInterp* it, Instr& in) {
   return rc;
 }
 
+// ------------------------------------------------------------------------------------------------
+// Capture with several streams. Stream capture of a single stream yields a linear chain of kernel nodes; the
+// step's data flow is wider than that (filter gradients next to the data-gradient chain, eight parameter updates,
+// the operand preparations of a layer). During capture every device instruction is given the address ranges it
+// reads and writes (its operands' device buffers, views and in-place results included, since ranges are
+// compared, not locations); an instruction depends on the earlier ones whose writes overlap what it touches or
+// whose reads overlap what it writes. It is issued on one of a few side streams that join the capture through
+// events: the stream of a dependency if that dependency is the stream's last instruction, otherwise the stream
+// idle for longest, after waiting for the events of its dependencies. The graph then holds the true edges and
+// independent kernels run side by side. Arithmetic is untouched: the same kernels on the same buffers.
+// ------------------------------------------------------------------------------------------------
+struct AddrRange { uintptr_t lo, hi; };
+
+static void collect_ranges(cgtObject* o, std::vector<AddrRange>& out) {
+  if (!o) return;
+  if (o->kind() == cgtObject::ArrayKind) {
+    cgtArray* a = (cgtArray*)o;
+    if (a->devtype() == cgtGPU && a->data() && a->nbytes() > 0) out.push_back({(uintptr_t)a->data(), (uintptr_t)a->data() + (uintptr_t)a->nbytes()});
+  } else {
+    cgtTuple* t = (cgtTuple*)o;
+    for (int i = 0; i < t->len; ++i) collect_ranges(t->getitem(i), out);
+  }
+}
+static bool overlap(const std::vector<AddrRange>& a, const std::vector<AddrRange>& b) {
+  for (const AddrRange& x : a)
+    for (const AddrRange& y : b)
+      if (x.lo < y.hi && y.lo < x.hi) return true;
+  return false;
+}
+
+constexpr int kMaxGraphStreams = 8;
+static cudaStream_t g_side_streams[kMaxGraphStreams];
+static int g_n_side_streams = 0;
+static std::vector<cudaEvent_t> g_capture_events;
+
+static int graph_streams() {
+  static int n = -1;
+  if (n < 0) {
+    const char* e = getenv("CGTB_GRAPH_STREAMS");
+    n = e ? atoi(e) : 4;
+    if (n < 1) n = 1;
+    if (n > kMaxGraphStreams) n = kMaxGraphStreams;
+  }
+  return n;
+}
+static cudaEvent_t capture_event(size_t i) {
+  while (g_capture_events.size() <= i) {
+    cudaEvent_t e = nullptr;
+    if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    g_capture_events.push_back(e);
+  }
+  return g_capture_events[i];
+}
+
+// Fires the device instructions of span s inside the running capture of `origin`, spread over side streams.
+static int fire_span_multistream(cgtbInterp* it, Span& s, cudaStream_t origin) {
+  auto& instrs = it->g->instrs;
+  const int NS = graph_streams();
+  while (g_n_side_streams < NS) {
+    if (cudaStreamCreateWithFlags(&g_side_streams[g_n_side_streams], cudaStreamNonBlocking) != cudaSuccess) return fail("cudaStreamCreate failed");
+    ++g_n_side_streams;
+  }
+  struct Node { int instr; int stream; std::vector<AddrRange> rd, wr; bool opaque; };
+  std::vector<Node> nodes;
+  std::vector<int> last_on_stream((size_t)NS, -1);   // node index of the last instruction issued on each stream
+  std::vector<long> last_use((size_t)NS, -1);
+  std::vector<bool> joined((size_t)NS, false);
+  // event 0: the fork point on the origin stream
+  cudaEvent_t fork = capture_event(0);
+  if (!fork) return fail("cudaEventCreate failed");
+  CGTB_CUDA_TRY(cudaEventRecord(fork, origin));
+  int rc = 0;
+  long tick = 0;
+  for (int i = s.begin; i < s.end && !rc; ++i) {
+    Instr& in = instrs[(size_t)i];
+    if (in.klass != kDevice) continue;
+    if ((in.flags & CGTB_INSTR_ONCE) && in.fired) continue;
+    Node nd;
+    nd.instr = i;
+    nd.opaque = (in.kind != kReturnByRef);   // a device instruction that creates its own result: ordered against everything
+    for (auto& r : in.reads) collect_ranges(get(it, r), nd.rd);
+    if (!nd.opaque) collect_ranges(get(it, in.write), nd.wr);
+    // dependencies: the latest conflicting instruction per stream is enough (a stream is ordered)
+    std::vector<int> dep_of_stream((size_t)NS, -1);
+    for (int j = (int)nodes.size() - 1; j >= 0; --j) {
+      const Node& e = nodes[(size_t)j];
+      if (dep_of_stream[(size_t)e.stream] >= 0) continue;
+      if (nd.opaque || e.opaque || overlap(e.wr, nd.rd) || overlap(e.wr, nd.wr) || overlap(e.rd, nd.wr)) dep_of_stream[(size_t)e.stream] = j;
+    }
+    // stream choice
+    int chosen = -1;
+    for (int st = 0; st < NS; ++st)
+      if (dep_of_stream[(size_t)st] >= 0 && dep_of_stream[(size_t)st] == last_on_stream[(size_t)st] && (chosen < 0 || dep_of_stream[(size_t)st] > dep_of_stream[(size_t)chosen])) chosen = st;
+    if (chosen < 0) {
+      for (int st = 0; st < NS; ++st)
+        if (chosen < 0 || last_use[(size_t)st] < last_use[(size_t)chosen]) chosen = st;
+    }
+    cudaStream_t cs = g_side_streams[chosen];
+    if (!joined[(size_t)chosen]) {
+      CGTB_CUDA_TRY(cudaStreamWaitEvent(cs, fork, 0));
+      joined[(size_t)chosen] = true;
+    }
+    for (int st = 0; st < NS; ++st) {
+      const int d = dep_of_stream[(size_t)st];
+      if (d < 0 || st == chosen) continue;
+      cudaEvent_t ev = capture_event((size_t)d + 1);
+      if (!ev) return fail("cudaEventCreate failed");
+      CGTB_CUDA_TRY(cudaStreamWaitEvent(cs, ev, 0));
+    }
+    nd.stream = chosen;
+    cudaStream_t saved = rt().stream;
+    rt().stream = cs;
+    rc = fire(it, in);
+    rt().stream = saved;
+    if (rc) break;
+    cudaEvent_t mine = capture_event(nodes.size() + 1);
+    if (!mine) return fail("cudaEventCreate failed");
+    CGTB_CUDA_TRY(cudaEventRecord(mine, cs));
+    last_on_stream[(size_t)chosen] = (int)nodes.size();
+    last_use[(size_t)chosen] = tick++;
+    nodes.push_back(std::move(nd));
+  }
+  // join every side stream back into the origin
+  for (int st = 0; st < NS; ++st) {
+    if (!joined[(size_t)st]) continue;
+    const int l = last_on_stream[(size_t)st];
+    if (l >= 0) CGTB_CUDA_TRY(cudaStreamWaitEvent(origin, capture_event((size_t)l + 1), 0));
+    else {
+      cudaEvent_t ev = capture_event(nodes.size() + 2 + (size_t)st);
+      CGTB_CUDA_TRY(cudaEventRecord(ev, g_side_streams[st]));
+      CGTB_CUDA_TRY(cudaStreamWaitEvent(origin, ev, 0));
+    }
+  }
+  return rc;
+}
+
 static int run_span(cgtbInterp* it, Span& s) {
   auto& instrs = it->g->instrs;
   const bool profile = (it->flags & CGTB_INTERP_PROFILE) && rt().ready;
@@ -417,11 +554,15 @@ static int run_span(cgtbInterp* it, Span& s) {
     if (e == cudaSuccess) {
       set_capturing(true);
       int rc = 0;
-      for (int i = s.begin; i < s.end && !rc; ++i) {
-        Instr& in = instrs[(size_t)i];
-        if (in.klass != kDevice) continue;
-        if ((in.flags & CGTB_INSTR_ONCE) && in.fired) continue;
-        rc = fire(it, in);
+      if (graph_streams() > 1) {
+        rc = fire_span_multistream(it, s, rt().stream);
+      } else {
+        for (int i = s.begin; i < s.end && !rc; ++i) {
+          Instr& in = instrs[(size_t)i];
+          if (in.klass != kDevice) continue;
+          if ((in.flags & CGTB_INSTR_ONCE) && in.fired) continue;
+          rc = fire(it, in);
+        }
       }
       set_capturing(false);
       cudaGraph_t graph = nullptr;

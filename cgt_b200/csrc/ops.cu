@@ -229,6 +229,8 @@ OP_BYREF(cgtb_op_batched_mul22) {
 // Im2Col / Col2Im / MaxPool / MaxPoolPullback share the reference's conv_closure (include/pooling.h:7-14)
 // ------------------------------------------------------------------------------------------------
 struct ConvClosure { int kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w; };
+// the same followed by a flag: the filter operand is the layer's bank in its own layout, not a rearranged copy
+struct ConvClosureW { int kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w, w_bank; };
 OP_BYREF(cgtb_op_im2col) {
   ConvClosure* cl = (ConvClosure*)cl0;
   cgtArray *im = ARR(reads[0]), *col = ARR(write0);
@@ -293,36 +295,40 @@ OP_BYREF(cgtb_op_relu_grad_nhwc) {
 }
 // ConvDgrad: (dy NHWC, filters rearranged to [C, kh, kw, Cin], B, C, H, W) -> dx NCHW
 OP_BYREF(cgtb_op_conv_dgrad) {
-  ConvClosure* cl = (ConvClosure*)cl0;
+  ConvClosureW* cl = (ConvClosureW*)cl0;
   cgtArray *dy = ARR(reads[0]), *wr = ARR(reads[1]), *dx = ARR(write0);
   if (!all_gpu({dy, wr, dx})) { fail("ConvDgrad: operands must be on the GPU"); return; }
   const long* s = dy->shape();
   const long* d = dx->shape();
-  if (dy->ndim() != 4 || wr->ndim() != 4 || dx->ndim() != 4 || dy->dtype() != cgt_f4 || wr->shape()[0] != d[1] ||
-      wr->shape()[1] != cl->kernel_h || wr->shape()[2] != cl->kernel_w || wr->shape()[3] != s[3] || s[0] != d[0]) {
+  const long* ws = wr->shape();
+  const bool wok = cl->w_bank ? (ws[0] == s[3] && ws[1] == d[1] && ws[2] == cl->kernel_h && ws[3] == cl->kernel_w)
+                              : (ws[0] == d[1] && ws[1] == cl->kernel_h && ws[2] == cl->kernel_w && ws[3] == s[3]);
+  if (dy->ndim() != 4 || wr->ndim() != 4 || dx->ndim() != 4 || dy->dtype() != cgt_f4 || !wok || s[0] != d[0]) {
     fail("ConvDgrad: operand shapes do not fit together");
     return;
   }
-  cgtb_conv_dgrad((const float*)dy->data(), s[0], (int)s[1], (int)s[2], (int)s[3], (const float*)wr->data(), (int)d[1], (int)d[2],
+  (cl->w_bank ? cgtb_conv_dgrad_bank : cgtb_conv_dgrad)((const float*)dy->data(), s[0], (int)s[1], (int)s[2], (int)s[3], (const float*)wr->data(), (int)d[1], (int)d[2],
                   (int)d[3], cl->kernel_h, cl->kernel_w, cl->pad_h, cl->pad_w, (float*)dx->data());
 }
 // ConvFwdBiasRelu: (x NHWC [B,H,W,Cin], filters rearranged to [Cout,kh,kw,Cin], bias [1,Cout,1,1], B, Cout, Ho, Wo)
 // -> tuple(mask i1 NCHW, y f4 NCHW): a stride-1 convolution layer's forward pass without a column matrix
 OP_BYREF(cgtb_op_conv_fwd_bias_relu) {
-  ConvClosure* cl = (ConvClosure*)cl0;
+  ConvClosureW* cl = (ConvClosureW*)cl0;
   cgtArray *x = ARR(reads[0]), *wr = ARR(reads[1]), *bias = ARR(reads[2]);
   cgtTuple* out = (cgtTuple*)write0;
   cgtArray *mask = ARR(out->getitem(0)), *y = ARR(out->getitem(1));
   if (!all_gpu({x, wr, bias, mask, y})) { fail("ConvFwdBiasRelu: operands must be on the GPU"); return; }
   const long* s = x->shape();
   const long* d = y->shape();
-  if (x->ndim() != 4 || wr->ndim() != 4 || y->ndim() != 4 || x->dtype() != cgt_f4 || wr->shape()[0] != d[1] ||
-      wr->shape()[1] != cl->kernel_h || wr->shape()[2] != cl->kernel_w || wr->shape()[3] != s[3] || s[0] != d[0] ||
+  const long* ws = wr->shape();
+  const bool wok = cl->w_bank ? (ws[0] == d[1] && ws[1] == s[3] && ws[2] == cl->kernel_h && ws[3] == cl->kernel_w)
+                              : (ws[0] == d[1] && ws[1] == cl->kernel_h && ws[2] == cl->kernel_w && ws[3] == s[3]);
+  if (x->ndim() != 4 || wr->ndim() != 4 || y->ndim() != 4 || x->dtype() != cgt_f4 || !wok || s[0] != d[0] ||
       bias->size() != d[1] || mask->size() != y->size()) {
     fail("ConvFwdBiasRelu: operand shapes do not fit together");
     return;
   }
-  cgtb_conv_fwd_bias_relu((const float*)x->data(), s[0], (int)s[1], (int)s[2], (int)s[3], (const float*)wr->data(), (int)d[1],
+  (cl->w_bank ? cgtb_conv_fwd_bias_relu_bank : cgtb_conv_fwd_bias_relu)((const float*)x->data(), s[0], (int)s[1], (int)s[2], (int)s[3], (const float*)wr->data(), (int)d[1],
                           (int)d[2], (int)d[3], cl->kernel_h, cl->kernel_w, cl->pad_h, cl->pad_w, (const float*)bias->data(),
                           (float*)y->data(), (int8_t*)mask->data());
 }

@@ -90,17 +90,19 @@ class Col2Im(core.Op):
 
 
 class ConvDgrad(core.Op):
-    """(dy NHWC [B,Ho,Wo,Cin], filters rearranged to [C,kh,kw,Cin], B, C, H, W) -> dx NCHW [B,C,H,W]:
-    the data gradient of a stride-1 convolution in one kernel.
+    """(dy NHWC [B,Ho,Wo,Cin], filters, B, C, H, W) -> dx NCHW [B,C,H,W]: the data gradient of a stride-1 convolution
+    in one kernel. The filters are the layer's bank [Cin,C,kh,kw] as stored (w_bank=True, what the compiler passes)
+    or a copy rearranged to [C,kh,kw,Cin].
 
     Not part of the reference's Op set. The compiler substitutes it (compilation.fuse_conv_dgrad) for the
     pair that Im2Col.pullback produces, Col2Im(Mul22(dy, W)) (cgt/nn_ops/im2col.py, cgt/nn.py conv2d), when
     the extents allow; the column matrix is then neither written nor read."""
     available_impls = ("native_gpu",)
 
-    def __init__(self, info):
+    def __init__(self, info, w_bank=False):
         assert info.stride_h == 1 and info.stride_w == 1
         self.info = info
+        self.w_bank = bool(w_bank)
 
     def get_diff(self, n):
         return [False] * n
@@ -115,7 +117,8 @@ class ConvDgrad(core.Op):
         return tuple(range(2, n))
 
     def get_native_compile_info(self, input_types, devtype):
-        return core.NativeCompileInfo(None, prebuilt="cgtb_op_conv_dgrad", closure_triples=info2closure(self.info))
+        return core.NativeCompileInfo(None, prebuilt="cgtb_op_conv_dgrad",
+                                      closure_triples=info2closure(self.info) + [("w_bank", ctypes.c_int, int(self.w_bank))])
 
     def __repr__(self):
         return "ConvDgrad{%s}" % (tuple(self.info),)
@@ -207,8 +210,9 @@ class ConvWgrad(core.Op):
 
 
 class ConvFwdBiasRelu(core.Op):
-    """(x NHWC [B,H,W,Cin], filters rearranged to [Cout,kh,kw,Cin], bias [1,Cout,1,1], B, Cout, Ho, Wo) ->
-    tuple(mask i1, relu f4), both NCHW [B,Cout,Ho,Wo]: the forward pass of a stride-1 convolution layer in one kernel.
+    """(x NHWC [B,H,W,Cin], filters, bias [1,Cout,1,1], B, Cout, Ho, Wo) -> tuple(mask i1, relu f4), both NCHW
+    [B,Cout,Ho,Wo]: the forward pass of a stride-1 convolution layer in one kernel. The filters are the layer's bank
+    [Cout,Cin,kh,kw] as stored (w_bank=True, what the compiler passes) or a copy rearranged to [Cout,kh,kw,Cin].
 
     Not part of the reference's Op set. The compiler substitutes it (compilation.fuse_conv_implicit) for
     ConvBiasRelu(Reshape(Im2Col(x)), ...), i.e. for the sequence that nn.conv2d / SpatialConvolution / rectify spell
@@ -217,9 +221,10 @@ class ConvFwdBiasRelu(core.Op):
     tolerance against the Op sequence."""
     available_impls = ("native_gpu",)
 
-    def __init__(self, info):
+    def __init__(self, info, w_bank=False):
         assert info.stride_h == 1 and info.stride_w == 1
         self.info = info
+        self.w_bank = bool(w_bank)
 
     def get_diff(self, n):
         return [False] * n
@@ -235,7 +240,8 @@ class ConvFwdBiasRelu(core.Op):
         return tuple(range(3, n))
 
     def get_native_compile_info(self, input_types, devtype):
-        return core.NativeCompileInfo(None, prebuilt="cgtb_op_conv_fwd_bias_relu", closure_triples=info2closure(self.info))
+        return core.NativeCompileInfo(None, prebuilt="cgtb_op_conv_fwd_bias_relu",
+                                      closure_triples=info2closure(self.info) + [("w_bank", ctypes.c_int, int(self.w_bank))])
 
     def __repr__(self):
         return "ConvFwdBiasRelu{%s}" % (tuple(self.info),)

@@ -188,6 +188,10 @@ int cgtb_conv_dgrad(const float* dy_nhwc, long B, int Ho, int Wo, int Cin, const
  * rounding, not bit for bit. Supported: Cin a multiple of 32, Cout a multiple of 16 (of 128 above 128), Wo <= 128. */
 int cgtb_conv_fwd_bias_relu(const float* x_nhwc, long B, int H, int W, int Cin, const float* w_rearranged, int Cout, int Ho,
                             int Wo, int kh, int kw, int ph, int pw, const float* bias, float* y_nchw, int8_t* mask_nchw);
+/* The same with the filter bank as the layer stores it, w_bank [Cout, Cin, kh, kw]: the rearrangement is part of the
+ * call's filter-splitting kernel, no transposed copy is needed. */
+int cgtb_conv_fwd_bias_relu_bank(const float* x_nhwc, long B, int H, int W, int Cin, const float* w_bank, int Cout, int Ho,
+                                 int Wo, int kh, int kw, int ph, int pw, const float* bias, float* y_nchw, int8_t* mask_nchw);
 /* Filter gradient of a stride-1 convolution in one kernel (plus an ordered fold of its K splits), without a column
  * matrix: replaces Mul22{T,N}(dy, Im2Col(x)) of the differentiated cgt/nn.py:93-100 (cgt/core.py:2162-2175).
  *   dw[n][c][i][j] = sum_{b, y, x} dy[b, y, x, n] * x[b, y + i - ph, x + j - pw, c]
@@ -195,6 +199,10 @@ int cgtb_conv_fwd_bias_relu(const float* x_nhwc, long B, int H, int W, int Cin, 
  * Supported: Cin a multiple of 32, Cout a multiple of 16 (of 128 above 128), Wo <= 32. */
 int cgtb_conv_wgrad(const float* x_nhwc, long B, int H, int W, int Cin, const float* dy_nhwc, int Ho, int Wo, int Cout, int kh,
                     int kw, int ph, int pw, float* dw);
+
+/* cgtb_conv_dgrad with the filter bank as the layer stores it, w_bank [Cin, C, kh, kw] (Cin = channels of dy). */
+int cgtb_conv_dgrad_bank(const float* dy_nhwc, long B, int Ho, int Wo, int Cin, const float* w_bank, int C, int H, int W,
+                         int kh, int kw, int ph, int pw, float* dx_nchw);
 
 /* Output stage of a convolution layer in one call: Mul22(col, w^T) -> NCHW -> + bias -> relu with its mask.
  * Replaces the Op sequence Mul22, Reshape, Transpose{0,3,1,2}, Repeat, ElwiseBinary +, >=, * of cgt/nn.py:87-100,

@@ -449,7 +449,8 @@ CONV_DGRADS = [
 
 
 @pytest.mark.parametrize("B,C,H,W,Cin,k,pad", CONV_DGRADS)
-def test_conv_dgrad_matches_gemm_then_col2im(rt, B, C, H, W, Cin, k, pad):
+@pytest.mark.parametrize("bank", [False, True])
+def test_conv_dgrad_matches_gemm_then_col2im(rt, B, C, H, W, Cin, k, pad, bank):
     """cgtb_conv_dgrad against the pair it replaces, evaluated by the CPU oracle: Mul22(dy, W) then Col2Im."""
     rs = np.random.RandomState(41)
     Ho, Wo = H + 2 * pad - k + 1, W + 2 * pad - k + 1
@@ -457,12 +458,9 @@ def test_conv_dgrad_matches_gemm_then_col2im(rt, B, C, H, W, Cin, k, pad):
     Wf = (rs.randn(Cin, C, k, k) * 0.2).astype("f4")     # filter bank [output channels of the conv, C, kh, kw]
     col = O.mul22(dy.reshape(B * Ho * Wo, Cin), Wf.reshape(Cin, C * k * k), 0, 0).reshape(B, Ho, Wo, C * k * k)
     want = O.col2im(col, (B, C, H, W), (k, k), (pad, pad), (1, 1))
-    wr = np.ascontiguousarray(Wf.transpose(1, 2, 3, 0))  # [C, kh, kw, Cin]
+    wr = Wf if bank else np.ascontiguousarray(Wf.transpose(1, 2, 3, 0))  # the bank as stored, or [C, kh, kw, Cin]
     ddy, dwr, ddx = Dev(dy), Dev(wr), Dev(np.full((B, C, H, W), np.nan, "f4"))
-    L = runtime.lib()
-    L.cgtb_conv_dgrad.restype = ctypes.c_int
-    L.cgtb_conv_dgrad.argtypes = [ctypes.c_void_p, ctypes.c_long] + [ctypes.c_int] * 3 + [ctypes.c_void_p] + [ctypes.c_int] * 7 + [ctypes.c_void_p]
-    call("cgtb_conv_dgrad", ddy.ptr, B, Ho, Wo, Cin, dwr.ptr, C, H, W, k, k, pad, pad, ddx.ptr)
+    call("cgtb_conv_dgrad_bank" if bank else "cgtb_conv_dgrad", ddy.ptr, B, Ho, Wo, Cin, dwr.ptr, C, H, W, k, k, pad, pad, ddx.ptr)
     got = ddx.get()
     exact = np.zeros((B, C, H, W))
     dy8, W8 = dy.astype("f8"), Wf.astype("f8")
@@ -489,7 +487,8 @@ CONV_IMPLICIT = [
 
 
 @pytest.mark.parametrize("B,Cin,H,W,Cout,k,pad", CONV_IMPLICIT)
-def test_conv_fwd_bias_relu_matches_im2col_then_gemm(rt, B, Cin, H, W, Cout, k, pad):
+@pytest.mark.parametrize("bank", [False, True])
+def test_conv_fwd_bias_relu_matches_im2col_then_gemm(rt, B, Cin, H, W, Cout, k, pad, bank):
     """cgtb_conv_fwd_bias_relu against the sequence it replaces, evaluated by the CPU oracle: Im2Col, Mul22(col, W^T),
     NCHW, + bias, relu with its mask."""
     rs = np.random.RandomState(44)
@@ -501,10 +500,11 @@ def test_conv_fwd_bias_relu_matches_im2col_then_gemm(rt, B, Cin, H, W, Cout, k, 
     want_t = (O.mul22(col, Wf.reshape(Cout, -1), 0, 1) + bias).reshape(B, Ho * Wo, Cout).transpose(0, 2, 1)
     exact_t = (col.astype("f8") @ Wf.reshape(Cout, -1).astype("f8").T + bias.astype("f8")).reshape(B, Ho * Wo, Cout).transpose(0, 2, 1)
     xn = np.ascontiguousarray(x.transpose(0, 2, 3, 1))
-    wr = np.ascontiguousarray(Wf.transpose(0, 2, 3, 1))
+    # the filter bank as the layer stores it, or a copy rearranged to [Cout, kh, kw, Cin]
+    wr = Wf if bank else np.ascontiguousarray(Wf.transpose(0, 2, 3, 1))
     dx, dw, db = Dev(xn), Dev(wr), Dev(bias)
     y, mask = Dev(np.full((B, Cout, Ho * Wo), np.nan, "f4")), Dev(np.full((B, Cout, Ho * Wo), 7, "i1"))
-    call("cgtb_conv_fwd_bias_relu", dx.ptr, B, H, W, Cin, dw.ptr, Cout, Ho, Wo, k, k, pad, pad, db.ptr, y.ptr, mask.ptr)
+    call("cgtb_conv_fwd_bias_relu_bank" if bank else "cgtb_conv_fwd_bias_relu", dx.ptr, B, H, W, Cin, dw.ptr, Cout, Ho, Wo, k, k, pad, pad, db.ptr, y.ptr, mask.ptr)
     got, gmask = y.get(), mask.get()
     assert set(np.unique(gmask)) <= {0, 1}
     K = Cin * k * k
