@@ -963,6 +963,73 @@ def create_execution_graph(inputs, nodes_sorted, node2shape, node2memowner, node
     return ExecutionGraph(instrs, len(inputs), counter.count), node2memloc
 
 
+def merge_parameter_updates(eg, update_locs):
+    """Instruction-list pass: the update instructions of a step that run one and the same single-output FusedElwise
+    program on float32 tensors / scalars (SGD: p - lr * g for every parameter) become ONE MultiFusedElwise instruction
+    at the position of the last of them. `update_locs`: indices of the memory locations that updates write (the
+    variables' own storage). An update is moved only if no instruction between its old and its new position touches its
+    result location, so every reader still sees the value it saw before."""
+    instrs = eg.instrs
+    groups = defaultdict(list)
+    for (i, ins) in enumerate(instrs):
+        if not isinstance(ins, ReturnByRef) or not isinstance(ins.op, core.FusedElwise) or ins.once:
+            continue
+        op = ins.op
+        if len(op.out_regs) != 1 or op.out_dtypes != ["f4"] or len(op.in_kinds) > 4 or any(k not in (0, 2, 3) for k in op.in_kinds):
+            continue
+        if ins.write_loc.index not in update_locs or ins.write_loc.devtype != "gpu":
+            continue
+        key = (tuple(op.program), tuple(op.in_kinds), tuple(op.out_regs))
+        groups[key].append(i)
+    for (key, idxs) in groups.items():
+        last = idxs[-1]
+        movable = []
+        for i in idxs:
+            w = instrs[i].write_loc.index
+            ok = True
+            for j in range(i + 1, last + 1):
+                other = instrs[j]
+                if j in idxs:
+                    if any(r.index == w for r in other.read_locs if j != i) and w != other.write_loc.index:
+                        ok = False
+                    continue
+                locs = [r.index for r in getattr(other, "read_locs", [])] + [other.write_loc.index]
+                if w in locs:
+                    ok = False
+                    break
+            if ok:
+                movable.append(i)
+        movable = movable[:24]
+        if len(movable) < 2:
+            continue
+        first = instrs[movable[0]]
+        reads, types, in_shapes, in_dtypes = [], [], [], []
+        for i in movable:
+            reads += list(instrs[i].read_locs)
+            types += list(instrs[i].input_types)
+            in_shapes += list(instrs[i].in_shapes)
+            in_dtypes += list(instrs[i].in_dtypes)
+        extra = [instrs[i].write_loc for i in movable[1:]]
+        merged = ReturnByRef(core.MultiFusedElwise(first.op, len(movable)), types + [None] * len(extra), reads + extra, first.write_loc,
+                             node_props=first.node_props)
+        merged.in_shapes, merged.in_dtypes = in_shapes, in_dtypes
+        merged.out_shape, merged.out_dtype, merged.out_dtypes = None, "f4", None
+        merged.extra_out_shapes = [instrs[i].out_shape for i in movable]
+        pos = movable[-1]
+        drop = set(movable)
+        new_instrs = []
+        for (j, ins) in enumerate(instrs):
+            if j == pos:
+                new_instrs.append(merged)
+            elif j not in drop:
+                new_instrs.append(ins)
+        instrs = new_instrs
+        eg.instrs = instrs
+        # indices changed: recompute the remaining groups on the new list
+        return merge_parameter_updates(eg, update_locs)
+    return eg
+
+
 def run_compilation_pipeline(inputs, outputs, updates, givens):
     config = core.get_config()
     outputs_simple, updatesrcs, updatetargs_simple, analysis = simplify_for_execution(outputs, updates, givens)
@@ -996,6 +1063,8 @@ def run_compilation_pipeline(inputs, outputs, updates, givens):
     written_into = set(owner for (n, owner) in node2memowner.items() if owner is not n)
     once_nodes = set(n for n in const_nodes if n not in written_into)
     eg, node2memloc = create_execution_graph(inputs, nodes_sorted, node2shape, node2memowner, node2dev, once_nodes)
+    if config["merge_parameter_updates"] and updates_simple:
+        merge_parameter_updates(eg, set(node2memloc[t].index for t in updatetargs_simple))
 
     if config["verbose"]:
         sys.stderr.write("begin\n" + "\n".join("%i.) \t%r" % (i, instr) for (i, instr) in enumerate(eg.instrs)) + "\nend\n")

@@ -1199,6 +1199,30 @@ class FusedElwise(Op):
         return "FusedElwise{%s}" % self.descr
 
 
+class MultiFusedElwise(Op):
+    """k FusedElwise instructions with one and the same single-output program, issued as one launch.
+
+    Not part of the reference's Op set and never a graph node: the compiler forms it on the instruction list
+    (compilation.merge_parameter_updates) from the k update instructions of a training step, which are k tiny launches
+    of the same chain (p - lr * g). Its callable reads the k operand lists back to back, then the result arrays of
+    tensors 1..k-1; the instruction's own write location is tensor 0's result."""
+    available_impls = ("native_gpu",)
+    return_type = "byref"
+
+    def __init__(self, fused, k):
+        assert isinstance(fused, FusedElwise) and len(fused.out_regs) == 1 and k >= 2
+        self.fused = fused
+        self.k = int(k)
+
+    def get_native_compile_info(self, input_types, devtype):
+        triples = list(self.fused.get_native_compile_info(input_types, devtype).closure_triples)
+        triples = [t for t in triples if t[0] != "launcher"] + [("launcher", ctypes.c_void_p, None), ("k", ctypes.c_int, self.k)]
+        return NativeCompileInfo(None, prebuilt="cgtb_op_multi_fused_elwise", closure_triples=triples)
+
+    def __repr__(self):
+        return "MultiFusedElwise{%d x %s}" % (self.k, self.fused.descr)
+
+
 def elwise_binary(opname, x, y):
     (x, y) = map(as_node, (x, y))
     scalar_mask = ((x.ndim == 0), (y.ndim == 0))
@@ -2089,7 +2113,7 @@ _DEFAULTS = dict(
     debug=False, precision="single", backend="native", cache_dir="~/.cgt_b200_cache", enable_inplace_opt=True,
     enable_simplification=True, parallel=False, num_threads=1, force_python_impl=False, debug_cpp=False, verbose=False,
     # additions for this backend
-    devtype="gpu", device_index=0, use_cuda_graphs=True, fuse_elementwise=True, jit_fused_elementwise=True, fuse_conv_dgrad=True, fuse_conv_output=True, fuse_conv_grad_input=True, fuse_conv_implicit=True,
+    devtype="gpu", device_index=0, use_cuda_graphs=True, fuse_elementwise=True, jit_fused_elementwise=True, fuse_conv_dgrad=True, fuse_conv_output=True, fuse_conv_grad_input=True, fuse_conv_implicit=True, merge_parameter_updates=True,
     pad_conv_columns=True, profile=False,
 )
 

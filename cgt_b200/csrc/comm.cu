@@ -169,6 +169,41 @@ CGTB_API int cgtb_allreduce_sum(int dtype, int n, const void* const* in, void* c
   return 0;
 }
 
+namespace cgtb {
+bool peer_ready(size_t bytes);
+int peer_allreduce(int n, const void* const* in, void* const* out, const long* counts);
+}  // namespace cgtb
+
+// Op callable of the peer-memory variant (small float32 payloads; capturable: an ordinary kernel launch). Fails
+// loudly when the payload does not fit the symmetric buffer: it never falls back to the library collective, which
+// must stay outside captured graphs.
+CGTB_API void cgtb_op_allreduce_peer(void* cl0, cgtObject** reads, cgtObject* write0) {
+  struct Closure { int n; };
+  Closure* cl = (Closure*)cl0;
+  cgtTuple* out = (cgtTuple*)write0;
+  const void* in[32];
+  void* dst[32];
+  long counts[32];
+  if (cl->n > 32) { fail("AllReduce (peer memory): more than 32 tensors in one group"); return; }
+  long total = 0;
+  for (int i = 0; i < cl->n; ++i) {
+    cgtArray *a = (cgtArray*)reads[i], *o = (cgtArray*)out->getitem(i);
+    if (a->devtype() != cgtGPU || o->devtype() != cgtGPU || a->dtype() != cgt_f4 || a->size() != o->size()) {
+      fail("AllReduce (peer memory): operands must be float32 device arrays of equal sizes");
+      return;
+    }
+    in[i] = a->data();
+    dst[i] = o->data();
+    counts[i] = a->size();
+    total += a->size();
+  }
+  if (!cgtb::peer_ready((size_t)total * 4)) {
+    fail("AllReduce (peer memory): no peer group, or %ld bytes exceed its slot", total * 4);
+    return;
+  }
+  cgtb::peer_allreduce(cl->n, in, dst, counts);
+}
+
 // Op callable: reads g_1..g_k (device arrays), writes a tuple of k arrays with the rank-sums.
 struct AllReduceClosure { int n; };
 CGTB_API void cgtb_op_allreduce(void* cl0, cgtObject** reads, cgtObject* write0) {

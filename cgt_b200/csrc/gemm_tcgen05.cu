@@ -497,7 +497,8 @@ int sgemm_tc_check() {
   if (g_err_host && *g_err_host) {
     int code = *g_err_host;
     *g_err_host = 0;
-    return fail("tcgen05 GEMM: a bounded barrier wait expired (code %d); the result of that product is invalid", code);
+    return fail("a bounded device-side wait expired (code %d: 3-7 a barrier of the tensor-core GEMM / convolution kernels, 8 a rank "
+                "of the peer-memory all-reduce did not arrive); the result of that call is invalid", code);
   }
   return 0;
 }

@@ -262,6 +262,102 @@ CGTB_API int cgtb_fused_elwise(const cgtbFusedProgram* prog, long n, const void*
   return 0;
 }
 
+// The same program applied to several independent tensors in ONE launch (blockIdx.y = tensor): the parameter
+// updates of a training step are eight tiny tensors with one and the same chain (p - lr * g), and as separate
+// launches each costs a few microseconds of launch and dependency latency, far more than its bytes. One output of
+// float32, inputs that are float32 tensors of the output's size or scalars. Same scalar templates as the single-tensor
+// kernel: same bits.
+constexpr int kMultiMaxTensors = 24;
+constexpr int kMultiMaxIn = 4;
+struct FusedMultiArgs {
+  cgtbFusedProgram prog;
+  int ntensors;
+  long n[kMultiMaxTensors];
+  const void* in[kMultiMaxTensors][kMultiMaxIn];
+  float* out[kMultiMaxTensors];
+};
+template <int V>
+__global__ void fused_elwise_multi_kernel(const FusedMultiArgs a) {
+  const cgtbFusedProgram& P = a.prog;
+  const int t = blockIdx.y;
+  const long n = a.n[t] / V;   // V = 4 only when every tensor's size is a multiple of 4 and its arrays are 16-byte aligned
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    float r[kMultiMaxIn + CGTB_FUSED_MAX_OPS][V];
+    for (int k = 0; k < P.n_in; ++k) {
+      if (P.in_kind[k] == CGTB_FIN_F4) {
+        if (V == 4) {
+          const float4 v = ((const float4*)a.in[t][k])[i];
+          r[k][0] = v.x; r[k][1 % V] = v.y; r[k][2 % V] = v.z; r[k][3 % V] = v.w;
+        } else {
+          r[k][0] = ((const float*)a.in[t][k])[i];
+        }
+      } else {
+        const float v = P.in_kind[k] == CGTB_FIN_SCALAR_F4 ? *(const float*)a.in[t][k] : (float)*(const long*)a.in[t][k];
+#pragma unroll
+        for (int q = 0; q < V; ++q) r[k][q] = v;
+      }
+    }
+    for (int o = 0; o < P.n_ops; ++o) {
+      const int dst = P.n_in + o, ra = P.op_a[o], code = P.op_code[o];
+      if (P.op_arity[o] == 1) {
+#pragma unroll
+        for (int q = 0; q < V; ++q) r[dst][q] = unary_apply<float, float>(code, r[ra][q]);
+      } else {
+        const int rb = P.op_b[o];
+#pragma unroll
+        for (int q = 0; q < V; ++q) r[dst][q] = binary_apply<float, float, float>(code, r[ra][q], r[rb][q]);
+      }
+    }
+    const int ro = P.out_reg[0];
+    if (V == 4) ((float4*)a.out[t])[i] = make_float4(r[ro][0], r[ro][1 % V], r[ro][2 % V], r[ro][3 % V]);
+    else a.out[t][i] = r[ro][0];
+  }
+}
+
+// in: ntensors * prog->n_in device pointers, tensor-major; n[t] elements and out[t] per tensor
+CGTB_API int cgtb_fused_elwise_multi(const cgtbFusedProgram* prog, int ntensors, const long* n, const void* const* in, void* const* out) {
+  if (!require_runtime("cgtb_fused_elwise_multi")) return 1;
+  if (!prog || prog->n_in < 1 || prog->n_in > kMultiMaxIn || prog->n_ops < 1 || prog->n_ops > CGTB_FUSED_MAX_OPS || prog->n_out != 1 ||
+      prog->out_dtype[0] != cgtb_f4)
+    return fail("cgtb_fused_elwise_multi: one float32 output, at most %d inputs", kMultiMaxIn);
+  if (ntensors < 1 || ntensors > kMultiMaxTensors) return fail("cgtb_fused_elwise_multi: between 1 and %d tensors", kMultiMaxTensors);
+  for (int k = 0; k < prog->n_in; ++k)
+    if (prog->in_kind[k] != CGTB_FIN_F4 && prog->in_kind[k] != CGTB_FIN_SCALAR_F4 && prog->in_kind[k] != CGTB_FIN_SCALAR_I8)
+      return fail("cgtb_fused_elwise_multi: inputs must be float32 tensors or scalars");
+  for (int o = 0; o < prog->n_ops; ++o) {
+    const int lim = prog->n_in + o;
+    const bool un = prog->op_arity[o] == 1;
+    if ((!un && prog->op_arity[o] != 2) || prog->op_a[o] < 0 || prog->op_a[o] >= lim || (!un && (prog->op_b[o] < 0 || prog->op_b[o] >= lim)) ||
+        prog->op_code[o] < 0 || prog->op_code[o] >= (un ? (int)CGTB_U_COUNT : (int)CGTB_B_COUNT))
+      return fail("cgtb_fused_elwise_multi: malformed program");
+  }
+  if (prog->out_reg[0] < 0 || prog->out_reg[0] >= prog->n_in + prog->n_ops) return fail("cgtb_fused_elwise_multi: bad output register");
+  FusedMultiArgs a;
+  a.prog = *prog;
+  a.ntensors = ntensors;
+  long nmax = 0;
+  for (int t = 0; t < ntensors; ++t) {
+    a.n[t] = n[t] > 0 ? n[t] : 0;
+    nmax = std::max(nmax, a.n[t]);
+    a.out[t] = (float*)out[t];
+    for (int k = 0; k < prog->n_in; ++k) a.in[t][k] = in[(size_t)t * prog->n_in + k];
+  }
+  if (nmax == 0) return 0;
+  bool vec = true;
+  for (int t = 0; t < ntensors && vec; ++t) {
+    if (a.n[t] % 4 != 0 || ((uintptr_t)a.out[t] & 15) != 0) vec = false;
+    for (int k = 0; k < prog->n_in && vec; ++k)
+      if (prog->in_kind[k] == CGTB_FIN_F4 && ((uintptr_t)a.in[t][k] & 15) != 0) vec = false;
+  }
+  // the largest tensor sets the row of blocks; smaller tensors leave the tail of their row idle
+  const long per_block = 256L * (vec ? 4 : 1);
+  dim3 grid((unsigned)std::min<long>(cgtb_ceil_div(nmax, per_block), 2L * rt().sm_count), (unsigned)ntensors);
+  if (vec) CGTB_LAUNCH(fused_elwise_multi_kernel<4>, grid, 256, 0, a);
+  else CGTB_LAUNCH(fused_elwise_multi_kernel<1>, grid, 256, 0, a);
+  CGTB_CHECK_LAUNCH("fused_elwise_multi");
+  return 0;
+}
+
 // ------------------------------------------------------------------------------------------------
 // Reductions (cgt/core.py:1663-1738), keepdims. The reduced index space is split across
 // `nsplit` blocks per output element; each block folds its slice with a warp-shuffle tree and writes

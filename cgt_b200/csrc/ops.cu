@@ -139,6 +139,31 @@ OP_BYREF(cgtb_op_elwise_binary) {
 // FusedElwise: closure = the program (include/cgt_b200.h). reads = the program's inputs; write = the
 // output array, or a tuple of arrays when the program has several outputs. Broadcast extents come
 // from the shapes: the input's non-unit axes form one run [d0, d1] of the output's axes.
+// MultiFusedElwise: one FusedElwise program over k independent tensors in one launch. The closure is the program
+// followed by k; reads = the k operand lists back to back (n_in each), then the result arrays of tensors 1..k-1
+// (the instruction's own write location is tensor 0's result). The compiler forms it from k parameter updates.
+struct MultiFusedClosure { cgtbFusedProgram prog; int k; };
+OP_BYREF(cgtb_op_multi_fused_elwise) {
+  const MultiFusedClosure* cl = (const MultiFusedClosure*)cl0;
+  const int k = cl->k, n_in = cl->prog.n_in;
+  if (k < 1 || k > 24 || n_in < 1 || n_in > 4) { fail("MultiFusedElwise: unsupported group of %d tensors with %d inputs", k, n_in); return; }
+  const void* in[24 * 4];
+  void* out[24];
+  long n[24];
+  for (int t = 0; t < k; ++t) {
+    cgtArray* w = ARR(t == 0 ? write0 : reads[k * n_in + t - 1]);
+    if (w->devtype() != cgtGPU || w->dtype() != cgt_f4) { fail("MultiFusedElwise: results must be float32 GPU arrays"); return; }
+    out[t] = w->data();
+    n[t] = w->size();
+    for (int q = 0; q < n_in; ++q) {
+      cgtArray* x = ARR(reads[t * n_in + q]);
+      if (x->devtype() != cgtGPU) { fail("MultiFusedElwise: operands must be on the GPU"); return; }
+      if (cl->prog.in_kind[q] == CGTB_FIN_F4 && x->size() != n[t]) { fail("MultiFusedElwise: operand and result sizes differ"); return; }
+      in[t * n_in + q] = x->data();
+    }
+  }
+  cgtb_fused_elwise_multi(&cl->prog, k, n, in, out);
+}
 OP_BYREF(cgtb_op_fused_elwise) {
   const cgtbFusedProgram* prog = (const cgtbFusedProgram*)cl0;
   cgtArray* outs[CGTB_FUSED_MAX_OUT];

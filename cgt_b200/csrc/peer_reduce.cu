@@ -1,0 +1,277 @@
+// Gradient all-reduce over peer memory for small payloads: one kernel per call, no library collective.
+//
+// Why: the CIFAR-shape convnet's gradients are 0.33 MB. Through NCCL that exchange is latency-bound and, being a
+// library call that may not be stream-captured here, it cuts the step's CUDA graph in two. This kernel is an
+// ordinary launch on the runtime stream: it can be captured with the rest of the step (one graph launch per
+// step at every number of GPUs) and it does pack, exchange, sum and unpack in one go.
+//
+// Every rank owns one "symmetric" device buffer (cudaMalloc'd on its own GPU, exported with cudaIpcGetMemHandle
+// and mapped by the other ranks' processes with cudaIpcOpenMemHandle; the host side carries the 64-byte handles):
+//   [ header: epoch, block counters | flag of slot 0 | flag of slot 1 | data slot 0 | data slot 1 ]
+// One call = one epoch e, using data slot e % 2:
+//   1. the blocks copy this rank's tensors into its own slot (packed); the last block to finish publishes
+//      flag[slot] = e with a system-scope release;
+//   2. every block waits, with a cycle budget, until the flag of every rank's slot reads e (system-scope acquire
+//      loads from peer memory over NVLink);
+//   3. every block sums its share of the elements over the ranks' slots IN RANK ORDER (plain peer loads) and
+//      writes the sums to the result tensors: all ranks add in the same order, so replicas stay bit-identical;
+//   4. the last block to finish advances the epoch.
+// Two slots are enough: a rank can begin epoch e + 2 (which overwrites slot e % 2) only after it has seen every
+// rank's flag of epoch e + 1, i.e. after every rank has finished its kernel of epoch e.
+// A wait that runs out of budget raises the host-mapped error flag (code 8), the kernel skips the sum, still
+// advances its epoch and returns: the context stays usable and the host reports the failure at the next
+// synchronisation. Nothing here uses multicast or TMA on peer memory: plain loads and stores only.
+#include "runtime.h"
+#include "tc_util.h"
+
+#include <algorithm>
+#include <cstring>
+
+using namespace cgtb;
+
+namespace {
+
+constexpr int kMaxRanks = 8;
+constexpr int kMaxTensors = 32;
+constexpr size_t kHeaderBytes = 1024;   // header + the two flags, each on its own 128-byte line
+
+struct Header {
+  unsigned long long epoch;     // last completed epoch of this rank
+  unsigned int packed_blocks;   // blocks that have finished packing in the running call
+  unsigned int done_blocks;     // blocks that have finished the running call
+};
+
+struct PeerTable {
+  char* base[kMaxRanks];   // every rank's symmetric buffer as mapped in this process (base[rank] = the local one)
+};
+struct TensorTable {
+  const float* src[kMaxTensors];
+  float* dst[kMaxTensors];
+  long off[kMaxTensors + 1];   // tensor t occupies elements [off[t], off[t+1]) of the packed payload
+  int n;
+};
+
+struct State {
+  int rank = 0, world = 1;
+  char* local = nullptr;
+  bool local_owned = false;
+  char* mapped[kMaxRanks] = {nullptr};
+  bool opened[kMaxRanks] = {false};
+  size_t slot_bytes = 0;
+  long long wait_cycles = 2000000000LL;
+  char* fake_peer = nullptr;   // self-test: a second buffer in this process that stands for a rank that never arrives
+  unsigned long long fake_epoch = 0;
+} g;
+
+__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+__device__ __forceinline__ unsigned long long* flag_of(char* base, int slot) {
+  return reinterpret_cast<unsigned long long*>(base + 256 + 128 * slot);
+}
+__device__ __forceinline__ float* slot_of(char* base, int slot, size_t slot_bytes) {
+  return reinterpret_cast<float*>(base + kHeaderBytes + (size_t)slot * slot_bytes);
+}
+
+__global__ void __launch_bounds__(256) peer_allreduce_kernel(const TensorTable tt, const PeerTable pt, int rank, int world, size_t slot_bytes,
+                                                           long long wait_cycles, int* err) {
+  __shared__ int failed;
+  Header* hdr = reinterpret_cast<Header*>(pt.base[rank]);
+  const unsigned long long epoch = hdr->epoch + 1;   // stable during the call: only the call's last block writes it, at the end
+  const int slot = (int)(epoch & 1ull);
+  const long total = tt.off[tt.n];
+  if (threadIdx.x == 0) failed = 0;
+  // 1. pack this rank's tensors into its own slot
+  float* mine = slot_of(pt.base[rank], slot, slot_bytes);
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    int t = 0;
+    while (t + 1 < tt.n && i >= tt.off[t + 1]) ++t;
+    mine[i] = tt.src[t][i - tt.off[t]];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(&hdr->packed_blocks, 1u);
+    if (prev == gridDim.x - 1) {
+      hdr->packed_blocks = 0;
+      st_release_sys(flag_of(pt.base[rank], slot), epoch);   // every block's slot writes happen-before this store
+    }
+  }
+  // 2. wait (bounded) for every rank's flag of this epoch
+  if ((int)threadIdx.x < world) {
+    const unsigned long long* f = flag_of(pt.base[threadIdx.x], slot);
+    const long long t0 = clock64();
+    bool ok = false;
+    for (unsigned int spin = 0; spin < (1u << 30); ++spin) {
+      if (ld_acquire_sys(f) == epoch) { ok = true; break; }
+      if ((spin & 63u) == 63u && clock64() - t0 > wait_cycles) break;
+    }
+    if (!ok) failed = 1;
+  }
+  __syncthreads();
+  if (failed) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) { *(volatile int*)err = 8; __threadfence_system(); }
+  } else {
+    // 3. sum over the ranks' slots in rank order, straight into the result tensors
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+      // cache-global loads: a line of a peer's slot must not be served from this SM's L1
+      float acc = __ldcg(slot_of(pt.base[0], slot, slot_bytes) + i);
+      for (int r = 1; r < world; ++r) acc += __ldcg(slot_of(pt.base[r], slot, slot_bytes) + i);
+      int t = 0;
+      while (t + 1 < tt.n && i >= tt.off[t + 1]) ++t;
+      tt.dst[t][i - tt.off[t]] = acc;
+    }
+  }
+  // 4. the last block advances the epoch
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int prev = atomicAdd(&hdr->done_blocks, 1u);
+    if (prev == gridDim.x - 1) {
+      hdr->done_blocks = 0;
+      hdr->epoch = epoch;
+    }
+  }
+}
+
+int alloc_buffer(size_t slot_bytes, char** out) {
+  char* p = nullptr;
+  const size_t bytes = kHeaderBytes + 2 * slot_bytes;
+  CGTB_CUDA_TRY(cudaMalloc((void**)&p, bytes));
+  CGTB_CUDA_TRY(cudaMemset(p, 0, bytes));
+  *out = p;
+  return 0;
+}
+
+}  // namespace
+
+namespace cgtb {
+// true when the peer-memory all-reduce can take a payload of `bytes`
+bool peer_ready(size_t bytes) { return g.local && g.world > 1 && bytes <= g.slot_bytes; }
+
+int peer_allreduce(int n, const void* const* in, void* const* out, const long* counts) {
+  TensorTable tt;
+  tt.n = n;
+  tt.off[0] = 0;
+  for (int i = 0; i < n; ++i) {
+    tt.src[i] = (const float*)in[i];
+    tt.dst[i] = (float*)out[i];
+    tt.off[i + 1] = tt.off[i] + (counts[i] > 0 ? counts[i] : 0);
+  }
+  const long total = tt.off[n];
+  if (total == 0) return 0;
+  PeerTable pt;
+  for (int r = 0; r < kMaxRanks; ++r) pt.base[r] = r < g.world ? g.mapped[r] : nullptr;
+  int* err = tc_error_flag();
+  if (!err) return 1;
+  // few blocks: the payload is small and every block polls every rank's flag
+  const unsigned blocks = (unsigned)std::max<long>(1, std::min<long>(cgtb_ceil_div(total, 2048), 64));
+  CGTB_LAUNCH(peer_allreduce_kernel, blocks, 256, 0, tt, pt, g.rank, g.world, g.slot_bytes, g.wait_cycles, err);
+  CGTB_CHECK_LAUNCH("peer_allreduce");
+  return 0;
+}
+}  // namespace cgtb
+
+// Allocate this rank's symmetric buffer (two slots of slot_bytes) and return its 64-byte IPC handle.
+CGTB_API int cgtb_peer_alloc(long slot_bytes, char* handle64) {
+  if (!require_runtime("cgtb_peer_alloc")) return 1;
+  if (g.local) return fail("cgtb_peer_alloc: the symmetric buffer already exists");
+  if (slot_bytes <= 0 || slot_bytes > (64L << 20)) return fail("cgtb_peer_alloc: slot size %ld out of range", slot_bytes);
+  const size_t sb = ((size_t)slot_bytes + 255) & ~(size_t)255;
+  if (alloc_buffer(sb, &g.local)) return 1;
+  g.local_owned = true;
+  g.slot_bytes = sb;
+  cudaIpcMemHandle_t h;
+  CGTB_CUDA_TRY(cudaIpcGetMemHandle(&h, g.local));
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  memcpy(handle64, &h, 64);
+  return 0;
+}
+// Map the other ranks' buffers: handles = world * 64 bytes in rank order (this rank's own entry is ignored).
+CGTB_API int cgtb_peer_open(const char* handles, int rank, int world) {
+  if (!require_runtime("cgtb_peer_open")) return 1;
+  if (!g.local) return fail("cgtb_peer_open: call cgtb_peer_alloc first");
+  if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world) return fail("cgtb_peer_open: rank %d of %d not supported (at most %d)", rank, world, kMaxRanks);
+  for (int r = 0; r < world; ++r) {
+    if (r == rank) { g.mapped[r] = g.local; continue; }
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handles + 64 * r, 64);
+    void* p = nullptr;
+    CGTB_CUDA_TRY(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    g.mapped[r] = (char*)p;
+    g.opened[r] = true;
+  }
+  g.rank = rank;
+  g.world = world;
+  return 0;
+}
+CGTB_API int cgtb_peer_close(void) {
+  if (rt().ready) cudaStreamSynchronize(rt().stream);
+  for (int r = 0; r < kMaxRanks; ++r) {
+    if (g.opened[r]) cudaIpcCloseMemHandle(g.mapped[r]);
+    g.opened[r] = false;
+    g.mapped[r] = nullptr;
+  }
+  if (g.fake_peer) { cudaFree(g.fake_peer); g.fake_peer = nullptr; }
+  if (g.local && g.local_owned) cudaFree(g.local);
+  g.local = nullptr;
+  g.world = 1;
+  g.rank = 0;
+  g.slot_bytes = 0;
+  return 0;
+}
+CGTB_API int cgtb_peer_world(void) { return g.local ? g.world : 1; }
+CGTB_API long cgtb_peer_slot_bytes(void) { return (long)g.slot_bytes; }
+// cycle budget of the kernel's flag waits (default about one second of SM clock)
+CGTB_API int cgtb_peer_set_wait_cycles(long cycles) {
+  if (cycles <= 0) return fail("cgtb_peer_set_wait_cycles: must be positive");
+  g.wait_cycles = cycles;
+  return 0;
+}
+// out[i] = sum over ranks of in[i] for n float32 buffers through the peer-memory kernel
+CGTB_API int cgtb_peer_allreduce_sum(int n, const void* const* in, void* const* out, const long* counts) {
+  if (!require_runtime("cgtb_peer_allreduce_sum")) return 1;
+  if (!g.local || g.world < 2) return fail("cgtb_peer_allreduce_sum: no peer group (cgtb_peer_alloc / cgtb_peer_open)");
+  if (n < 1 || n > kMaxTensors) return fail("cgtb_peer_allreduce_sum: between 1 and %d tensors", kMaxTensors);
+  long total = 0;
+  for (int i = 0; i < n; ++i) total += counts[i] > 0 ? counts[i] : 0;
+  if ((size_t)total * 4 > g.slot_bytes) return fail("cgtb_peer_allreduce_sum: %ld bytes exceed the slot of %ld bytes", total * 4, (long)g.slot_bytes);
+  return cgtb::peer_allreduce(n, in, out, counts);
+}
+
+// Self-test on ONE GPU: a group of two "ranks" in this process, rank 0 real, rank 1 a second buffer that nobody
+// drives. A call then waits for a flag that is never set: the bounded wait must expire, the error must be reported and
+// the library must stay usable. cgtb_peer_selftest_post() plays the missing rank for the NEXT call: it writes that rank's
+// payload and flag from the host, so that call completes with the sum.
+CGTB_API int cgtb_peer_selftest_open(long slot_bytes) {
+  if (!require_runtime("cgtb_peer_selftest_open")) return 1;
+  if (g.local) return fail("cgtb_peer_selftest_open: a peer group already exists");
+  const size_t sb = ((size_t)slot_bytes + 255) & ~(size_t)255;
+  if (alloc_buffer(sb, &g.local)) return 1;
+  if (alloc_buffer(sb, &g.fake_peer)) return 1;
+  g.local_owned = true;
+  g.slot_bytes = sb;
+  g.rank = 0;
+  g.world = 2;
+  g.mapped[0] = g.local;
+  g.mapped[1] = g.fake_peer;
+  return 0;
+}
+CGTB_API int cgtb_peer_selftest_post(const float* host_payload, long count) {
+  if (!g.fake_peer) return fail("cgtb_peer_selftest_post: no self-test group");
+  if ((size_t)count * 4 > g.slot_bytes) return fail("cgtb_peer_selftest_post: payload too large");
+  CGTB_CUDA_TRY(cudaStreamSynchronize(rt().stream));
+  Header h;
+  CGTB_CUDA_TRY(cudaMemcpy(&h, g.local, sizeof(h), cudaMemcpyDeviceToHost));
+  const unsigned long long epoch = h.epoch + 1;
+  const int slot = (int)(epoch & 1ull);
+  CGTB_CUDA_TRY(cudaMemcpy(g.fake_peer + kHeaderBytes + (size_t)slot * g.slot_bytes, host_payload, (size_t)count * 4, cudaMemcpyHostToDevice));
+  CGTB_CUDA_TRY(cudaMemcpy(g.fake_peer + 256 + 128 * slot, &epoch, sizeof(epoch), cudaMemcpyHostToDevice));
+  return 0;
+}

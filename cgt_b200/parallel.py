@@ -16,7 +16,9 @@ import numpy as np
 
 from . import core
 
-_state = {"world": 1, "rank": 0, "local_rank": 0, "comm": False}
+_state = {"world": 1, "rank": 0, "local_rank": 0, "comm": False, "peer": False}
+
+PEER_SLOT_BYTES = 4 << 20   # payloads up to this size go through the peer-memory kernel instead of NCCL
 
 
 def world_size():
@@ -69,7 +71,23 @@ def init_process_group(with_gpu=True):
             dist.broadcast_object_list(box, src=0)
             runtime.check(L.cgtb_comm_init(box[0], rk, world), "ncclCommInitRank")
             _state["comm"] = True
+            if os.environ.get("CGTB_PEER_ALLREDUCE", "1") != "0" and world <= 8:
+                _open_peer_group(L, rk, world)
     return rk, world
+
+
+def _open_peer_group(L, rk, world):
+    """Symmetric buffers for the peer-memory all-reduce: every rank allocates one, the 64-byte IPC handles travel
+    through the host group, every rank maps the others'. Ranks must share a node (NVLink / PCIe peer access)."""
+    import torch.distributed as dist
+    from . import runtime
+    h = ctypes.create_string_buffer(64)
+    runtime.check(L.cgtb_peer_alloc(PEER_SLOT_BYTES, h), "cgtb_peer_alloc")
+    handles = [None] * world
+    dist.all_gather_object(handles, bytes(h.raw))
+    runtime.check(L.cgtb_peer_open(b"".join(handles), rk, world), "cgtb_peer_open")
+    dist.barrier()
+    _state["peer"] = True
 
 
 def barrier():
@@ -97,6 +115,11 @@ def check_health():
 
 
 def shutdown():
+    if _state["peer"]:
+        from . import runtime
+        barrier()   # nobody unmaps a buffer that a peer's kernel may still read
+        runtime.lib().cgtb_peer_close()
+        _state["peer"] = False
     if _state["comm"]:
         from . import runtime
         runtime.lib().cgtb_comm_destroy()
@@ -114,8 +137,11 @@ class AllReduce(core.Op):
     """(g_1, ..., g_k) -> tuple of their sums over all ranks. All k reductions are queued as one group."""
     available_impls = ("native_gpu",)
 
-    def __init__(self, n):
+    def __init__(self, n, peer=False):
+        """peer=True: the exchange runs as one kernel over peer memory (small float32 payloads; an ordinary launch,
+        so it stays inside the step's captured CUDA graph); otherwise through NCCL, outside captured graphs."""
         self.n = n
+        self.peer = bool(peer)
 
     def get_diff(self, n):
         return [False] * n
@@ -128,6 +154,8 @@ class AllReduce(core.Op):
 
     def get_native_compile_info(self, input_types, devtype):
         from . import runtime
+        if self.peer:
+            return core.NativeCompileInfo(None, prebuilt="cgtb_op_allreduce_peer", closure_triples=[("n", ctypes.c_int, self.n)])
         # stream-ordered, but issued outside captured CUDA graphs (same class as a Transport)
         return core.NativeCompileInfo(None, prebuilt="cgtb_op_allreduce", closure_triples=[("n", ctypes.c_int, self.n)],
                                       flags=runtime.INSTR_TRANSPORT)
@@ -146,7 +174,7 @@ class AllReduce(core.Op):
         return tuple(out)
 
     def __repr__(self):
-        return "AllReduce{%d}" % self.n
+        return "AllReduce{%d%s}" % (self.n, ",peer" if self.peer else "")
 
 
 def allreduce_mean(grads):
@@ -155,9 +183,27 @@ def allreduce_mean(grads):
     w = world_size()
     if w == 1:
         return grads
-    tup = core.Result(AllReduce(len(grads)), grads)
+    tup = core.Result(AllReduce(len(grads), peer=_fits_peer_path(grads)), grads)
     inv = np.array(1.0 / w, core.cgt.floatX)
     return [tup[i] * inv for i in range(len(grads))]
+
+
+def _fits_peer_path(grads):
+    """True when a peer group is open and the gradients are float32 tensors of static shape that fit its slot together."""
+    if not _state["peer"] or len(grads) > 32:
+        return False
+    total = 0
+    for g in grads:
+        if g.dtype != "f4":
+            return False
+        try:
+            shp = core.cgt.infer_shape(g)
+        except Exception:
+            return False
+        if shp is None or any(s is None for s in shp):
+            return False
+        total += int(np.prod(shp)) * 4
+    return total <= PEER_SLOT_BYTES
 
 
 def shard(arrays, rank_=None, world=None):

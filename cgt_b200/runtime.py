@@ -50,6 +50,11 @@ def _declare(lib):
         "cgtb_comm_init": (ci, [ctypes.c_char_p, ci, ci]), "cgtb_comm_world": (ci, []), "cgtb_comm_rank": (ci, []),
         "cgtb_comm_check": (ci, []), "cgtb_comm_abort": (ci, []), "cgtb_comm_destroy": (ci, []),
         "cgtb_allreduce_sum": (ci, [ci, ci, ctypes.POINTER(vp), ctypes.POINTER(vp), c_long_p]),
+        "cgtb_peer_alloc": (ci, [cl, ctypes.c_char_p]), "cgtb_peer_open": (ci, [ctypes.c_char_p, ci, ci]),
+        "cgtb_peer_close": (ci, []), "cgtb_peer_world": (ci, []), "cgtb_peer_slot_bytes": (cl, []),
+        "cgtb_peer_set_wait_cycles": (ci, [cl]),
+        "cgtb_peer_allreduce_sum": (ci, [ci, ctypes.POINTER(vp), ctypes.POINTER(vp), c_long_p]),
+        "cgtb_peer_selftest_open": (ci, [cl]), "cgtb_peer_selftest_post": (ci, [vp, cl]),
         "cgtb_alloc": (vp, [ci, cl]), "cgtb_free": (None, [ci, vp]), "cgtb_memcpy": (ci, [ci, ci, vp, vp, cl, ci]),
         "cgtb_memset": (ci, [vp, ci, cl]),
         "cgtb_array_new": (vp, [ci, c_long_p, ci, ci]), "cgtb_array_from_host": (vp, [ci, c_long_p, ci, ci, vp, ci]),
@@ -98,6 +103,7 @@ def _declare(lib):
         "cgtb_getflat": (ci, [ci, cl, vp, vp, vp]), "cgtb_incflat": (ci, [ci, cl, cl, vp, vp, vp, vp]),
         "cgtb_concat_part": (ci, [ci, cl, cl, cl, cl, cl, vp, vp]), "cgtb_fill": (ci, [ci, cl, cd, cl, vp]),
         "cgtb_fused_elwise": (ci, [vp, cl, vp, c_long_p, c_long_p, vp]),
+        "cgtb_fused_elwise_multi": (ci, [vp, ci, c_long_p, vp, vp]),
         "cgtb_reduce_rkr_f32_static": (ci, [ci, cl, cl, cl, vp, vp]), "cgtb_reduce_static_max_k": (cl, []),
     }
     for (name, (restype, argtypes)) in sig.items():

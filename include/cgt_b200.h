@@ -254,6 +254,12 @@ typedef struct {
 int cgtb_fused_elwise(const cgtbFusedProgram* prog, long n, const void* const* in, const long* bcast_k,
                       const long* bcast_inner, void* const* out);
 
+/* The same program over several independent tensors in one launch (the parameter updates of a training step): one
+ * float32 output per tensor, at most 4 inputs, each a float32 tensor of the output's size or a scalar; `in` holds
+ * ntensors * prog->n_in device pointers, tensor-major. Same bits as cgtb_fused_elwise per tensor. No counterpart in
+ * the reference. */
+int cgtb_fused_elwise_multi(const cgtbFusedProgram* prog, int ntensors, const long* n, const void* const* in, void* const* out);
+
 /* Sum / Max over a set of axes, keepdims (cgt/core.py:1663-1738) */
 int cgtb_reduce(int kind, int dtype, int ndim, const long* shape, const int* reduced, const void* in, void* out);
 
@@ -298,6 +304,25 @@ int cgtb_comm_abort(void);
 int cgtb_comm_destroy(void);
 /* out[i] = sum over ranks of in[i] for n float buffers, one NCCL group on the runtime stream */
 int cgtb_allreduce_sum(int dtype, int n, const void* const* in, void* const* out, const long* counts);
+
+/* The same exchange for small float32 payloads as ONE kernel over peer memory (no library collective, so the call is
+ * an ordinary launch that a CUDA graph can hold). Every rank: cgtb_peer_alloc (its symmetric buffer: two slots of
+ * slot_bytes; returns the 64-byte cudaIpc handle), the host side gathers the handles of all ranks, cgtb_peer_open maps
+ * them (ranks on one node, at most 8). cgtb_peer_allreduce_sum: out[i] = sum over ranks of in[i], summed in rank order on
+ * every rank (replicas stay bit-identical). The kernel's waits for the other ranks are bounded by a cycle budget
+ * (cgtb_peer_set_wait_cycles, default about a second): on expiry the call's result is invalid, the failure is
+ * reported by the next cgtb_synchronize / cgtb_interp_run, and the library stays usable.
+ * cgtb_peer_selftest_*: a two-rank group inside one process whose second rank never arrives (post() plays it for the
+ * next call), for testing the bounded wait on one GPU without faulting or hanging anything. */
+int cgtb_peer_alloc(long slot_bytes, char* handle64);
+int cgtb_peer_open(const char* handles, int rank, int world);
+int cgtb_peer_close(void);
+int cgtb_peer_world(void);
+long cgtb_peer_slot_bytes(void);
+int cgtb_peer_set_wait_cycles(long cycles);
+int cgtb_peer_allreduce_sum(int n, const void* const* in, void* const* out, const long* counts);
+int cgtb_peer_selftest_open(long slot_bytes);
+int cgtb_peer_selftest_post(const float* host_payload, long count);
 
 #ifdef __cplusplus
 }

@@ -33,7 +33,9 @@ for step in range(3):
     losses.append(float(f(*shard)[0]))
     parallel.check_health()  # raises (and ends this rank) when the communicator reported an asynchronous error
 params = [p.op.get_value() for p in cfg.params] if on_gpu else [f.get_value(p) for p in cfg.params]
+stats = f.stats() if on_gpu else {}
 out = {"rank": rank, "world": world, "losses": losses, "n_allreduce": n_allreduce,
+       "graph_launches": int(stats.get("last_graph_launches", 0)), "peer": bool(parallel._state["peer"]),
        "checksum": [float(np.abs(p).sum()) for p in params], "first": [float(p.ravel()[0]) for p in params]}
 np.savez(os.environ["DP_OUT"] + ".%d.npz" % rank, *params)
 print(json.dumps(out))

@@ -52,6 +52,8 @@ def test_two_gpu_ranks_match_one_gpu(rt, tmp_path, config):
             except subprocess.TimeoutExpired:
                 pass
     assert all(o["n_allreduce"] == 1 for o in outs)
+    # small gradients travel through the peer-memory kernel, which stays inside the step's captured graph
+    assert all(o["peer"] and o["graph_launches"] == 1 for o in outs), outs
     p0 = np.load(str(tmp_path / "params") + ".0.npz")
     p1 = np.load(str(tmp_path / "params") + ".1.npz")
     for k in p0.files:
