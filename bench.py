@@ -400,6 +400,15 @@ def run_b200(args):
     e2e_blocks, _ = timed_blocks(f, host_batches, K, max(3, args.warmup // 4), R, prefetch=True)
     clocks = sampler.stop() if rank == 0 else None
     rdiff = replica_diff(cfg.params) if world > 1 else None
+    exchange = None
+    if world > 1 and parallel._state["peer"]:
+        # the peer-memory all-reduce kernel's own clock (block 0): how long it waited for the slower ranks' flags
+        # and how long the whole kernel ran, averaged over all calls of this process
+        import ctypes
+        t = (ctypes.c_long * 3)()
+        if runtime.lib().cgtb_peer_timing(t) == 0 and t[0] > 0:
+            exchange = {"kernel": "peer_allreduce_kernel", "calls": int(t[0]), "us_until_all_flags_seen": t[1] / t[0] / 1e3,
+                        "us_total": t[2] / t[0] / 1e3}
 
     out = None
     if rank == 0:
@@ -422,6 +431,8 @@ def run_b200(args):
         }
         if rdiff is not None:
             out["replica_max_abs_diff"] = rdiff
+        if exchange is not None:
+            out["exchange"] = exchange
     # roofline of the dominant kernel (rank 0; the per-GPU work is the same at every N under weak scaling) and, at
     # N = 1, parity against the CPU oracle and the CPU baseline
     if rank == 0 and not args.no_extras:

@@ -172,8 +172,42 @@ def _foldable_repeat(node):
     return all(b - a == 1 for (a, b) in zip(kept[:-1], kept[1:]))
 
 
-def fuse_elementwise(outputs, updatetargs, node2shape):
-    """Replace connected groups of elementwise nodes of one shape by FusedElwise nodes.
+def _row_member(node, node2shape):
+    """(R, C) when `node` can live in a FusedRows group over [R, C] rows: an elementwise float32 node of static shape
+    [R, C] or [R, 1] (C is None then: it fits any row length), a Sum over axis 1 of an [R, C] node, or the Repeat of
+    an [R, 1] node along axis 1. None otherwise."""
+    if node.is_input() or node.ndim != 2 or node.dtype != "f4":
+        return None
+    shp = _static_shape(node2shape[node])
+    if shp is None:
+        return None
+    (R, Cn) = shp
+    op = node.op
+    max_c = core.FusedRows.MAX_C
+    if isinstance(op, core.Sum):
+        par = node.parents[0]
+        pshp = _static_shape(node2shape[par])
+        if tuple(op.axes) != (1,) or par.dtype != "f4" or pshp is None or not (1 < pshp[1] <= max_c):
+            return None
+        return (R, pshp[1])
+    if isinstance(op, core.Repeat):
+        par = node.parents[0]
+        pshp = _static_shape(node2shape[par])
+        if list(op.axes) != [1] or par.dtype != "f4" or pshp is None or pshp != (R, 1) or not (1 < Cn <= max_c):
+            return None
+        return (R, Cn)
+    if _fusable(node) and all(par.dtype == "f4" or par.ndim == 0 for par in node.parents):
+        if Cn == 1:
+            return (R, None)
+        if Cn <= max_c:
+            return (R, Cn)
+    return None
+
+
+def fuse_elementwise(outputs, updatetargs, node2shape, rows=False):
+    """Replace connected groups of elementwise nodes of one shape by FusedElwise nodes; with rows=True, connected
+    groups of elementwise nodes, sums along axis 1 and repeats along axis 1 over [R, C] rows that contain at least one
+    such sum by FusedRows nodes (groups without a sum are left for the plain pass).
 
     A node joins the group of one of its fusable parents when that cannot create a cycle (no other
     parent depends on the group). Groups stay within the kernel's limits; a group that would need
@@ -194,6 +228,24 @@ def fuse_elementwise(outputs, updatetargs, node2shape):
     members = defaultdict(list)
     anc = {}
     gclosure = []
+    topo_index = dict((node, i) for (i, node) in enumerate(nodes))
+    row_class = {}    # rows mode: node -> (R, C or None)
+    group_rc = {}     # rows mode: group -> [R, C or None]
+
+    def joinable(node, par, g):
+        if par.ndim == 0:
+            return False
+        if not rows:
+            return _same_shape(node2shape[node], node2shape[par])
+        (R, C) = row_class[node]
+        (Rg, Cg) = group_rc[g]
+        return R == Rg and (C is None or Cg is None or C == Cg)
+
+    def mergeable(g, g2):
+        if not rows:
+            return True
+        (R, C), (R2, C2) = group_rc[g], group_rc[g2]
+        return R == R2 and (C is None or C2 is None or C == C2)
 
     def closed(mask):
         """mask plus everything its groups depend on"""
@@ -211,29 +263,57 @@ def fuse_elementwise(outputs, updatetargs, node2shape):
             if par in group_of:
                 pm |= 1 << group_of[par]
             parent_masks.append(pm)
-        if _fusable(node):
-            chosen = None
+        if rows:
+            row_class[node] = _row_member(node, node2shape)
+        if (row_class[node] is not None) if rows else _fusable(node):
+            cands = []
             for par in node.parents:
                 g = group_of.get(par)
-                if g is None or par.ndim == 0 or not _same_shape(node2shape[node], node2shape[par]):
+                if g is None or g in cands or not joinable(node, par, g):
                     continue
+                cands.append(g)
+            chosen = None
+            for g in cands:
                 if len(members[g]) >= core.FusedElwise.MAX_OPS:
                     continue
+                # other parents' groups that neither depend on g nor g on them (x.W + b and h.U + c: two
+                # independent chains that meet in this node) are merged into g
+                merged = [g]
+                for g2 in cands:
+                    if g2 == g or any((gclosure[m] >> g2) & 1 or (gclosure[g2] >> m) & 1 for m in merged):
+                        continue
+                    if not all(mergeable(m, g2) for m in merged):
+                        continue
+                    if sum(len(members[m]) for m in merged) + len(members[g2]) >= core.FusedElwise.MAX_OPS:
+                        continue
+                    merged.append(g2)
                 outside = 0
                 for (q, pm) in zip(node.parents, parent_masks):
-                    if group_of.get(q) != g:
+                    if group_of.get(q) not in merged:
                         outside |= pm
                 outside = closed(outside)
-                if (outside >> g) & 1:
+                if any((outside >> m) & 1 for m in merged):
                     continue
                 chosen = g
-                outside &= ~(1 << g)
-                if outside & ~gclosure[g]:
-                    gclosure[g] |= outside
-                    gbit, gc = 1 << g, gclosure[g]
-                    for k in range(len(gclosure)):   # groups that depend on g inherit its new dependencies
-                        if gclosure[k] & gbit:
-                            gclosure[k] |= gc
+                deps = outside
+                bits = 0
+                for m in merged:
+                    deps |= gclosure[m]
+                    bits |= 1 << m
+                for g2 in merged[1:]:
+                    for mnode in members[g2]:
+                        group_of[mnode] = g
+                    members[g] = sorted(members[g] + members[g2], key=topo_index.__getitem__)
+                    members[g2] = []
+                    if rows and group_rc[g][1] is None:
+                        group_rc[g][1] = group_rc[g2][1]
+                if deps & ~gclosure[g] or len(merged) > 1:
+                    for k in range(len(gclosure)):   # groups that depend on a merged group inherit the new dependencies
+                        if gclosure[k] & bits:
+                            gclosure[k] |= deps | (1 << g)
+                    gclosure[g] = deps
+                    for g2 in merged[1:]:
+                        gclosure[g2] = deps | (1 << g)   # a stale reference to an emptied group sees the merged one
                 break
             if chosen is None:
                 chosen = len(gclosure)
@@ -243,6 +323,10 @@ def fuse_elementwise(outputs, updatetargs, node2shape):
                 gclosure.append(closed(total))
             group_of[node] = chosen
             members[chosen].append(node)
+            if rows:
+                rc = group_rc.setdefault(chosen, list(row_class[node]))
+                if rc[1] is None:
+                    rc[1] = row_class[node][1]
         total = 0
         for pm in parent_masks:
             total |= pm
@@ -250,39 +334,46 @@ def fuse_elementwise(outputs, updatetargs, node2shape):
     out_set = set(all_out)
     target_set = set(updatetargs)
     replace = {}
-    for (g, mem) in members.items():
+    def emit(mem):
+        """One FusedElwise node for `mem` (topologically ordered); a group beyond the kernel's limits is cut in two
+        (a prefix and the rest of a topological order cannot need each other both ways) and each part tried again."""
         memset = set(mem)
         inputs, in_kinds, reg_of = [], [], {}
-        folded = 0
 
         def input_reg(par):
-            key = par
-            if key in reg_of:
-                return reg_of[key]
+            if par in reg_of:
+                return reg_of[par]
             if par.ndim == 0:
                 kind = 2 if par.dtype == "f4" else 3
                 src = par
-            elif _foldable_repeat(par) and all(c in memset for c in children[par]) and par not in out_set:
+            elif _foldable_repeat(par):
+                # the small operand is read directly; the Repeat node itself stays for whoever else uses it
                 kind, src = 4, par.parents[0]
             else:
                 kind = 0 if par.dtype == "f4" else 1
                 src = par
-            reg_of[key] = len(inputs)
+            reg_of[par] = len(inputs)
             inputs.append(src)
             in_kinds.append(kind)
-            return reg_of[key]
+            return reg_of[par]
 
-        program, result_reg = [], {}
-        ok = True
-        # first pass: inputs in order of first use
-        for node in mem:
+        for node in mem:   # inputs in order of first use
             for par in node.parents:
                 if par not in memset:
                     input_reg(par)
         n_in = len(inputs)
         folded = sum(1 for k in in_kinds if k == 4)
-        if len(mem) + folded < 2 or n_in > core.FusedElwise.MAX_IN:
-            continue
+        if len(mem) + folded < 2:
+            return
+        outs = [node for node in mem if node in out_set or any(c not in memset for c in children[node])]
+        if n_in > core.FusedElwise.MAX_IN or len(outs) > core.FusedElwise.MAX_OUT or len(mem) > core.FusedElwise.MAX_OPS:
+            if len(mem) >= 2:
+                emit(mem[:len(mem) // 2])
+                emit(mem[len(mem) // 2:])
+            return
+        if not outs or (len(outs) > 1 and any(o in target_set for o in outs)):
+            return
+        program, result_reg = [], {}
         for (j, node) in enumerate(mem):
             regs = [result_reg[par] if par in memset else reg_of[par] for par in node.parents]
             if isinstance(node.op, core.ElwiseUnary):
@@ -290,18 +381,13 @@ def fuse_elementwise(outputs, updatetargs, node2shape):
             else:
                 program.append((2, core.BINARY_OPCODE[node.op.opname], regs[0], regs[1]))
             result_reg[node] = n_in + j
-        outs = [node for node in mem if node in out_set or any(c not in memset for c in children[node])]
-        if not outs or len(outs) > core.FusedElwise.MAX_OUT:
-            continue
-        if len(outs) > 1 and any(o in target_set for o in outs):
-            continue
         shape_input = None
         for (k, (src, kind)) in enumerate(zip(inputs, in_kinds)):
             if kind in (0, 1) and _same_shape(node2shape[src], node2shape[mem[0]]):
                 shape_input = k
                 break
-        if shape_input is None or not ok:
-            continue
+        if shape_input is None:
+            return
         descr = ",".join(str(node.op) for node in mem)
         fop = core.FusedElwise(program, in_kinds, [result_reg[o] for o in outs], [o.dtype for o in outs], mem[0].ndim,
                                shape_input, descr)
@@ -318,6 +404,99 @@ def fuse_elementwise(outputs, updatetargs, node2shape):
                 ti = core.Result(core.TupleIndex(q), [fnode])
                 node2shape[ti] = shp
                 replace[o] = ti
+
+    def emit_rows(mem):
+        """One FusedRows node for `mem`, if it holds a sum; halves of a group beyond the kernel's limits are tried again."""
+        if not any(isinstance(node.op, core.Sum) for node in mem):
+            return
+        F = core.FusedElwise
+        memset = set(mem)
+        C = None
+        for node in mem:
+            C = C or row_class[node][1]
+        if C is None:
+            return
+        inputs, in_kinds, reg_of = [], [], {}
+
+        def data_parents(node):
+            return node.parents[:1] if isinstance(node.op, (core.Sum, core.Repeat)) else node.parents
+
+        def input_reg(par):
+            if par in reg_of:
+                return reg_of[par]
+            src = par
+            if par.ndim == 0:
+                kind = 2 if par.dtype == "f4" else 3
+            else:
+                shp = _static_shape(node2shape[par])
+                if par.dtype != "f4" or shp is None or len(shp) != 2:
+                    return None
+                if isinstance(par.op, core.Repeat) and not par.is_input() and list(par.op.axes) == [0] and shp[1] == C \
+                        and par.parents[0].dtype == "f4":
+                    kind, src = 6, par.parents[0]      # a [1, C] row repeated down the rows: read the row itself
+                elif shp[1] == C:
+                    kind = 0
+                elif shp[1] == 1:
+                    kind = 5
+                else:
+                    return None
+            reg_of[par] = len(inputs)
+            inputs.append(src)
+            in_kinds.append(kind)
+            return reg_of[par]
+
+        for node in mem:
+            for par in data_parents(node):
+                if par not in memset and input_reg(par) is None:
+                    return
+        n_in = len(inputs)
+        n_ops = sum(1 for node in mem if not isinstance(node.op, core.Repeat))
+        outs = [node for node in mem if node in out_set or any(c not in memset for c in children[node])]
+        if n_in > F.MAX_IN or len(outs) > F.MAX_OUT or n_ops > F.MAX_OPS:
+            if len(mem) >= 2:
+                emit_rows(mem[:len(mem) // 2])
+                emit_rows(mem[len(mem) // 2:])
+            return
+        if not outs or any(o in target_set for o in outs) or n_ops < 2:
+            return
+        program, result_reg = [], {}
+        for node in mem:
+            regs = [result_reg[par] if par in memset else reg_of[par] for par in data_parents(node)]
+            if isinstance(node.op, core.Repeat):
+                result_reg[node] = regs[0]     # one value per row already sits in every lane
+                continue
+            if isinstance(node.op, core.Sum):
+                program.append((3, 0, regs[0], 0))
+            elif isinstance(node.op, core.ElwiseUnary):
+                program.append((1, core.UNARY_OPCODE[node.op.opname], regs[0], 0))
+            else:
+                program.append((2, core.BINARY_OPCODE[node.op.opname], regs[0], regs[1]))
+            result_reg[node] = n_in + len(program) - 1
+        shape_input = None
+        for (k, kind) in enumerate(in_kinds):
+            if kind in (0, 5):
+                shape_input = k
+                break
+        if shape_input is None:
+            return
+        descr = ",".join(str(node.op) for node in mem if not isinstance(node.op, core.Repeat))
+        out_cols = [_static_shape(node2shape[o])[1] == 1 for o in outs]
+        fop = core.FusedRows(program, in_kinds, [result_reg[o] for o in outs], out_cols, C, shape_input, descr)
+        fnode = core.Result(fop, inputs)
+        fnode.props.update(outs[0].props)
+        if len(outs) == 1:
+            node2shape[fnode] = node2shape[outs[0]]
+            replace[outs[0]] = fnode
+        else:
+            node2shape[fnode] = tuple(list(node2shape[o]) for o in outs)
+            for (q, o) in enumerate(outs):
+                ti = core.Result(core.TupleIndex(q), [fnode])
+                node2shape[ti] = node2shape[o]
+                replace[o] = ti
+
+    for mem in list(members.values()):
+        if mem:
+            (emit_rows if rows else emit)(mem)
     if not replace:
         return list(outputs), list(updatetargs)
     return _rewire(outputs, updatetargs, replace)
@@ -1039,6 +1218,8 @@ def run_compilation_pipeline(inputs, outputs, updates, givens):
     if config["fuse_conv_grad_input"]:
         outputs_simple, updatetargs_simple = fuse_conv_grad_input(outputs_simple, updatetargs_simple, node2shape)
     if config["fuse_elementwise"]:
+        if config["fuse_rows"]:
+            outputs_simple, updatetargs_simple = fuse_elementwise(outputs_simple, updatetargs_simple, node2shape, rows=True)
         outputs_simple, updatetargs_simple = fuse_elementwise(outputs_simple, updatetargs_simple, node2shape)
         if config["fuse_conv_output"]:
             outputs_simple, updatetargs_simple = fuse_conv_output(outputs_simple, updatetargs_simple, node2shape)

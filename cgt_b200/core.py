@@ -515,6 +515,7 @@ class InMemoryData(GetData):
         else:
             was_live = self._value is not None and self._value.handle is not None
             self._value = runtime.ArrayWrapper.from_numpy(value, self.device.devtype)
+            runtime.lib().cgtb_state_version_bump()   # compiled functions must look at their storage again
             if was_live:  # compiled functions hold the address of `dataptr`: keep it pointing at a live array
                 self.dataptr.value = self._value.ptr
 
@@ -1221,6 +1222,65 @@ class MultiFusedElwise(Op):
 
     def __repr__(self):
         return "MultiFusedElwise{%d x %s}" % (self.k, self.fused.descr)
+
+
+class FusedRows(Op):
+    """Elementwise operations and sums along axis 1 over an [R, C] matrix (C <= 128) evaluated by one kernel, one warp per
+    row: a softmax, its logarithm and its pullback are such chains, and as separate launches on a [batch, classes] matrix
+    each costs far more in launch latency than in bytes.
+
+    Not part of the reference's Op set: compilation.fuse_elementwise(rows=True) forms these nodes. ``program`` as in
+    FusedElwise plus (3, 0, a, 0): the sum of register a over the row. ``in_kinds``: 0 an [R, C] array, 5 an [R, 1]
+    array, 6 a [1, C] array, 2 / 3 scalars. ``out_cols[j]``: output j is [R, 1] rather than [R, C]. ``shape_input``: an
+    input whose axis 0 gives R."""
+    available_impls = ("native_gpu",)
+    return_type = "byref"
+    MAX_C = 128
+
+    def __init__(self, program, in_kinds, out_regs, out_cols, C, shape_input, descr=""):
+        F = FusedElwise
+        assert 1 <= len(in_kinds) <= F.MAX_IN and 1 <= len(program) <= F.MAX_OPS and 1 <= len(out_regs) <= F.MAX_OUT
+        self.program = [tuple(p) for p in program]
+        self.in_kinds = list(in_kinds)
+        self.out_regs = list(out_regs)
+        self.out_cols = [int(bool(c)) for c in out_cols]
+        self.C = int(C)
+        self.shape_input = shape_input
+        self.descr = descr
+
+    def get_diff(self, num_inputs):
+        return [False] * num_inputs
+
+    def shp_apply(self, inputs):
+        R = cgt.size(inputs[self.shape_input], 0)
+        shps = [[R, cgt.constant(np.array(1 if col else self.C, "i8"))] for col in self.out_cols]
+        return shps[0] if len(shps) == 1 else tuple(shps)
+
+    def typ_apply(self, input_types):
+        typs = [TensorType("f4", 2) for _ in self.out_regs]
+        return typs[0] if len(typs) == 1 else TupleType(*typs)
+
+    def get_native_compile_info(self, input_types, devtype):
+        F = FusedElwise
+
+        def arr(vals, n):
+            vals = list(vals) + [0] * (n - len(vals))
+            return (ctypes.c_int * n)(*vals)
+        return NativeCompileInfo(None, prebuilt="cgtb_op_fused_rows", closure_triples=[
+            ("n_in", ctypes.c_int, len(self.in_kinds)),
+            ("n_ops", ctypes.c_int, len(self.program)),
+            ("n_out", ctypes.c_int, len(self.out_regs)),
+            ("in_kind", ctypes.c_int * F.MAX_IN, arr(self.in_kinds, F.MAX_IN)),
+            ("op_arity", ctypes.c_int * F.MAX_OPS, arr([p[0] for p in self.program], F.MAX_OPS)),
+            ("op_code", ctypes.c_int * F.MAX_OPS, arr([p[1] for p in self.program], F.MAX_OPS)),
+            ("op_a", ctypes.c_int * F.MAX_OPS, arr([p[2] for p in self.program], F.MAX_OPS)),
+            ("op_b", ctypes.c_int * F.MAX_OPS, arr([p[3] for p in self.program], F.MAX_OPS)),
+            ("out_reg", ctypes.c_int * F.MAX_OUT, arr(self.out_regs, F.MAX_OUT)),
+            ("out_col", ctypes.c_int * F.MAX_OUT, arr(self.out_cols, F.MAX_OUT)),
+            ("C", ctypes.c_int, self.C)])
+
+    def __repr__(self):
+        return "FusedRows{%s}" % self.descr
 
 
 def elwise_binary(opname, x, y):
@@ -2113,7 +2173,7 @@ _DEFAULTS = dict(
     debug=False, precision="single", backend="native", cache_dir="~/.cgt_b200_cache", enable_inplace_opt=True,
     enable_simplification=True, parallel=False, num_threads=1, force_python_impl=False, debug_cpp=False, verbose=False,
     # additions for this backend
-    devtype="gpu", device_index=0, use_cuda_graphs=True, fuse_elementwise=True, jit_fused_elementwise=True, fuse_conv_dgrad=True, fuse_conv_output=True, fuse_conv_grad_input=True, fuse_conv_implicit=True, merge_parameter_updates=True,
+    devtype="gpu", device_index=0, use_cuda_graphs=True, fuse_elementwise=True, jit_fused_elementwise=True, fuse_conv_dgrad=True, fuse_conv_output=True, fuse_conv_grad_input=True, fuse_conv_implicit=True, merge_parameter_updates=True, fuse_rows=True,
     pad_conv_columns=True, profile=False,
 )
 

@@ -19,14 +19,24 @@ int sgemm_tma(int tA, int tB, long P, long M, long N, long K, const float* A, lo
 
 int sgemm_small(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B,
                 long ldb, long strideB, float* C, long ldc, long strideC);
+int sgemm_tile16(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B,
+                 long ldb, long strideB, float* C, long ldc, long strideC);
 
 int sgemm_dispatch(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B,
                    long ldb, long strideB, float* C, long ldc, long strideC, int impl) {
   if (!require_runtime("sgemm")) return 1;
-  if (impl == 0 || impl == 5) {
+  // one warp per output suits few outputs, or operands that both run along K in memory (its lanes read along K);
+  // the FMA tiles take the other products below the size at which the tensor-core kernels' fixed cost is repaid
+  const bool warp_per_output = impl == 5 || (impl == 0 && (M * N <= 2048 || (!tA && tB)));
+  if (warp_per_output) {
     int rc = sgemm_small(tA, tB, P, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC);
     if (rc >= 0) return rc;
     if (impl == 5) return fail("sgemm: M=%ld N=%ld K=%ld is not a small product", M, N, K);
+  }
+  if (impl == 0 || impl == 6) {
+    int rc = sgemm_tile16(tA, tB, P, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC);
+    if (rc >= 0) return rc;
+    if (impl == 6) return fail("sgemm: M=%ld N=%ld K=%ld is too large for the FMA-tile kernel", M, N, K);
   }
   if (impl != 1) {
     int rc = -1;

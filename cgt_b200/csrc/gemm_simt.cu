@@ -183,7 +183,78 @@ __global__ void sgemm_small_kernel(int tA, int tB, long M, long N, long K, const
 }
 }  // namespace
 
+// Products too large for one warp per output and too small to repay the tensor-core kernel's fixed cost (tensor-map
+// fetch, tensor-memory allocation, a multi-stage ring that such a product never fills: 10-25 us for the 64 x 512 x 128
+// products of the unrolled LSTM): plain FMA tiles. A block owns a 16 x 16 tile of C; its KS groups of 256 threads
+// walk interleaved 16-wide slices of K, each thread one output, operands staged through shared memory with loads
+// that are contiguous for either storage order, the next slice's words already in flight while the current one is
+// used; the groups' partial sums are added in group order. One fixed order of operations: reproducible.
+namespace {
+template <int KS>
+__global__ void __launch_bounds__(256 * KS) sgemm_tile16_kernel(int tA, int tB, long M, long N, long K, const float* __restrict__ A, long lda,
+                                                               long strideA, const float* __restrict__ B, long ldb, long strideB,
+                                                               float* __restrict__ C, long ldc, long strideC) {
+  __shared__ float As[KS][16][17];  // [m][k]
+  __shared__ float Bs[KS][16][17];  // [k][n]
+  const int tx = threadIdx.x & 15, ty = (threadIdx.x >> 4) & 15, kz = threadIdx.x >> 8;
+  const long m0 = (long)blockIdx.y * 16, n0 = (long)blockIdx.x * 16;
+  A += (long)blockIdx.z * strideA;
+  B += (long)blockIdx.z * strideB;
+  C += (long)blockIdx.z * strideC;
+  const long niter = (K + 16L * KS - 1) / (16L * KS);
+  auto load_a = [&](long k0) -> float {
+    if (!tA) { const long m = m0 + ty, k = k0 + tx; return (m < M && k < K) ? A[m * lda + k] : 0.f; }
+    const long m = m0 + tx, k = k0 + ty;
+    return (m < M && k < K) ? A[k * lda + m] : 0.f;
+  };
+  auto load_b = [&](long k0) -> float {
+    if (!tB) { const long k = k0 + ty, n = n0 + tx; return (k < K && n < N) ? B[k * ldb + n] : 0.f; }
+    const long n = n0 + ty, k = k0 + tx;
+    return (k < K && n < N) ? B[n * ldb + k] : 0.f;
+  };
+  float acc = 0.f;
+  float a = load_a((long)kz * 16), b = load_b((long)kz * 16);
+  for (long it = 0; it < niter; ++it) {
+    if (!tA) As[kz][ty][tx] = a; else As[kz][tx][ty] = a;
+    if (!tB) Bs[kz][ty][tx] = b; else Bs[kz][tx][ty] = b;
+    __syncthreads();
+    if (it + 1 < niter) {
+      const long k0 = ((it + 1) * KS + kz) * 16;
+      a = load_a(k0);
+      b = load_b(k0);
+    }
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) acc = fmaf(As[kz][ty][kk], Bs[kz][kk][tx], acc);
+    __syncthreads();
+  }
+  if (KS > 1) {
+    As[kz][ty][tx] = acc;
+    __syncthreads();
+    if (kz == 0) {
+#pragma unroll
+      for (int z = 1; z < KS; ++z) acc += As[z][ty][tx];
+    }
+  }
+  if (kz == 0 && m0 + ty < M && n0 + tx < N) C[(m0 + ty) * ldc + n0 + tx] = acc;
+}
+}  // namespace
+
 namespace cgtb {
+// returns 0 done, -1 not eligible
+int sgemm_tile16(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B, long ldb,
+                 long strideB, float* C, long ldc, long strideC) {
+  if (P <= 0 || M <= 0 || N <= 0) return 0;
+  if (K <= 0 || M * N * K > (1L << 25) || P > 65535 || cgtb_ceil_div(M, 16) > 65535) return -1;
+  dim3 grid((unsigned)cgtb_ceil_div(N, 16), (unsigned)cgtb_ceil_div(M, 16), (unsigned)P);
+  const long blocks = (long)grid.x * grid.y * grid.z;
+  if (blocks < 4L * rt().sm_count && K >= 64)
+    CGTB_LAUNCH(sgemm_tile16_kernel<4>, grid, 1024, 0, tA, tB, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC);
+  else
+    CGTB_LAUNCH(sgemm_tile16_kernel<1>, grid, 256, 0, tA, tB, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC);
+  CGTB_CHECK_LAUNCH("sgemm_tile16");
+  return 0;
+}
+
 // returns 0 done, -1 not a small product
 int sgemm_small(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B, long ldb,
                 long strideB, float* C, long ldc, long strideC) {

@@ -358,6 +358,111 @@ CGTB_API int cgtb_fused_elwise_multi(const cgtbFusedProgram* prog, int ntensors,
   return 0;
 }
 
+// Elementwise operations and row sums over the rows of an [R, C] matrix in one launch: one warp per row, element
+// c of the row lives in lane c % 32, slot c / 32 (E slots per lane, C <= 32 E). A register holds a value per element or,
+// after a row sum, the same value in every lane and slot; elementwise operations do not need to know which. Lanes
+// beyond C compute on zeros and take part neither in sums nor in stores.
+struct RowArgs {
+  cgtbRowProgram prog;
+  long R, C;
+  const void* in[CGTB_FUSED_MAX_IN];
+  void* out[CGTB_FUSED_MAX_OUT];
+};
+template <int E>
+__global__ void fused_rows_kernel(const RowArgs a) {
+  const cgtbRowProgram& P = a.prog;
+  const int lane = threadIdx.x & 31;
+  const long row = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= a.R) return;
+  const long C = a.C;
+  float r[CGTB_FUSED_MAX_IN + CGTB_FUSED_MAX_OPS][E];
+  for (int k = 0; k < P.n_in; ++k) {
+    const int kind = P.in_kind[k];
+    if (kind == CGTB_FIN_F4 || kind == CGTB_FIN_ROW) {
+      const float* src = (const float*)a.in[k] + (kind == CGTB_FIN_F4 ? row * C : 0);
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const long c = lane + 32 * e;
+        r[k][e] = c < C ? src[c] : 0.0f;
+      }
+    } else {
+      const float v = kind == CGTB_FIN_COL ? ((const float*)a.in[k])[row]
+                                           : (kind == CGTB_FIN_SCALAR_F4 ? *(const float*)a.in[k] : (float)*(const long*)a.in[k]);
+#pragma unroll
+      for (int e = 0; e < E; ++e) r[k][e] = v;
+    }
+  }
+  for (int o = 0; o < P.n_ops; ++o) {
+    const int dst = P.n_in + o, ra = P.op_a[o], code = P.op_code[o], arity = P.op_arity[o];
+    if (arity == 1) {
+#pragma unroll
+      for (int e = 0; e < E; ++e) r[dst][e] = unary_apply<float, float>(code, r[ra][e]);
+    } else if (arity == 2) {
+      const int rb = P.op_b[o];
+#pragma unroll
+      for (int e = 0; e < E; ++e) r[dst][e] = binary_apply<float, float, float>(code, r[ra][e], r[rb][e]);
+    } else {
+      float s = 0.0f;
+#pragma unroll
+      for (int e = 0; e < E; ++e)
+        if (lane + 32 * e < C) s += r[ra][e];
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+#pragma unroll
+      for (int e = 0; e < E; ++e) r[dst][e] = s;
+    }
+  }
+  for (int j = 0; j < P.n_out; ++j) {
+    const int ro = P.out_reg[j];
+    if (P.out_col[j]) {
+      if (lane == 0) ((float*)a.out[j])[row] = r[ro][0];
+    } else {
+      float* dst = (float*)a.out[j] + row * C;
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const long c = lane + 32 * e;
+        if (c < C) dst[c] = r[ro][e];
+      }
+    }
+  }
+}
+
+CGTB_API int cgtb_fused_rows(const cgtbRowProgram* prog, long R, long C, const void* const* in, void* const* out) {
+  if (!require_runtime("cgtb_fused_rows")) return 1;
+  if (!prog || prog->n_in < 1 || prog->n_in > CGTB_FUSED_MAX_IN || prog->n_ops < 1 || prog->n_ops > CGTB_FUSED_MAX_OPS || prog->n_out < 1 ||
+      prog->n_out > CGTB_FUSED_MAX_OUT)
+    return fail("cgtb_fused_rows: program outside the limits");
+  if (C < 1 || C > 128) return fail("cgtb_fused_rows: rows of 1 to 128 elements, got %ld", C);
+  for (int k = 0; k < prog->n_in; ++k) {
+    const int kind = prog->in_kind[k];
+    if (kind != CGTB_FIN_F4 && kind != CGTB_FIN_SCALAR_F4 && kind != CGTB_FIN_SCALAR_I8 && kind != CGTB_FIN_COL && kind != CGTB_FIN_ROW)
+      return fail("cgtb_fused_rows: unsupported input kind %d", kind);
+  }
+  for (int o = 0; o < prog->n_ops; ++o) {
+    const int lim = prog->n_in + o, ar = prog->op_arity[o];
+    if (ar < 1 || ar > 3 || prog->op_a[o] < 0 || prog->op_a[o] >= lim || (ar == 2 && (prog->op_b[o] < 0 || prog->op_b[o] >= lim)) ||
+        (ar == 1 && (prog->op_code[o] < 0 || prog->op_code[o] >= (int)CGTB_U_COUNT)) ||
+        (ar == 2 && (prog->op_code[o] < 0 || prog->op_code[o] >= (int)CGTB_B_COUNT)))
+      return fail("cgtb_fused_rows: malformed program");
+  }
+  for (int j = 0; j < prog->n_out; ++j)
+    if (prog->out_reg[j] < 0 || prog->out_reg[j] >= prog->n_in + prog->n_ops) return fail("cgtb_fused_rows: bad output register");
+  if (R <= 0) return 0;
+  RowArgs a;
+  a.prog = *prog;
+  a.R = R;
+  a.C = C;
+  for (int k = 0; k < prog->n_in; ++k) a.in[k] = in[k];
+  for (int j = 0; j < prog->n_out; ++j) a.out[j] = out[j];
+  const int warps = 4;
+  const unsigned blocks = (unsigned)cgtb_ceil_div(R, warps);
+  if (C <= 32) CGTB_LAUNCH(fused_rows_kernel<1>, blocks, warps * 32, 0, a);
+  else if (C <= 64) CGTB_LAUNCH(fused_rows_kernel<2>, blocks, warps * 32, 0, a);
+  else CGTB_LAUNCH(fused_rows_kernel<4>, blocks, warps * 32, 0, a);
+  CGTB_CHECK_LAUNCH("fused_rows");
+  return 0;
+}
+
 // ------------------------------------------------------------------------------------------------
 // Reductions (cgt/core.py:1663-1738), keepdims. The reduced index space is split across
 // `nsplit` blocks per output element; each block folds its slice with a warp-shuffle tree and writes

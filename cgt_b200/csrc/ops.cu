@@ -139,6 +139,43 @@ OP_BYREF(cgtb_op_elwise_binary) {
 // FusedElwise: closure = the program (include/cgt_b200.h). reads = the program's inputs; write = the
 // output array, or a tuple of arrays when the program has several outputs. Broadcast extents come
 // from the shapes: the input's non-unit axes form one run [d0, d1] of the output's axes.
+// FusedRows: elementwise operations and row sums over the rows of an [R, C] matrix. The closure is the program
+// followed by C; R comes from the first result (which has R or R*C elements).
+struct FusedRowsClosure { cgtbRowProgram prog; int C; };
+OP_BYREF(cgtb_op_fused_rows) {
+  const FusedRowsClosure* cl = (const FusedRowsClosure*)cl0;
+  const cgtbRowProgram& P = cl->prog;
+  cgtArray* outs[CGTB_FUSED_MAX_OUT];
+  if (P.n_out == 1) outs[0] = ARR(write0);
+  else {
+    cgtTuple* tup = (cgtTuple*)write0;
+    for (int j = 0; j < P.n_out; ++j) outs[j] = (cgtArray*)tup->getitem(j);
+  }
+  const long C = cl->C;
+  const long R = P.out_col[0] ? outs[0]->size() : outs[0]->size() / C;
+  const void* in[CGTB_FUSED_MAX_IN];
+  void* out[CGTB_FUSED_MAX_OUT];
+  for (int j = 0; j < P.n_out; ++j) {
+    if (outs[j]->devtype() != cgtGPU || outs[j]->dtype() != cgt_f4 || outs[j]->size() != (P.out_col[j] ? R : R * C)) {
+      fail("FusedRows: result %d is not a float32 GPU array of the expected size", j);
+      return;
+    }
+    out[j] = outs[j]->data();
+  }
+  for (int k = 0; k < P.n_in; ++k) {
+    cgtArray* x = ARR(reads[k]);
+    const int kind = P.in_kind[k];
+    const long want = kind == CGTB_FIN_F4 ? R * C : (kind == CGTB_FIN_COL ? R : (kind == CGTB_FIN_ROW ? C : 1));
+    const bool scalar_i8 = kind == CGTB_FIN_SCALAR_I8;
+    if (x->devtype() != cgtGPU || x->size() != want || x->dtype() != (scalar_i8 ? cgt_i8 : cgt_f4)) {
+      fail("FusedRows: operand %d has the wrong size, dtype or device", k);
+      return;
+    }
+    in[k] = x->data();
+  }
+  cgtb_fused_rows(&P, R, C, in, out);
+}
+
 // MultiFusedElwise: one FusedElwise program over k independent tensors in one launch. The closure is the program
 // followed by k; reads = the k operand lists back to back (n_in each), then the result arrays of tensors 1..k-1
 // (the instruction's own write location is tensor 0's result). The compiler forms it from k parameter updates.

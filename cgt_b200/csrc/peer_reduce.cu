@@ -39,6 +39,8 @@ struct Header {
   unsigned long long epoch;     // last completed epoch of this rank
   unsigned int packed_blocks;   // blocks that have finished packing in the running call
   unsigned int done_blocks;     // blocks that have finished the running call
+  // block 0's nanosecond stamps of the last call (%globaltimer): start, after the wait for the peers, end; and sums
+  unsigned long long t_start, t_waited, t_end, sum_wait_ns, sum_total_ns, calls;
 };
 
 struct PeerTable {
@@ -87,6 +89,9 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const TensorTable t
   const int slot = (int)(epoch & 1ull);
   const long total = tt.off[tt.n];
   if (threadIdx.x == 0) failed = 0;
+  const bool stamps = blockIdx.x == 0 && threadIdx.x == 0;
+  unsigned long long t_start = 0, t_waited = 0;
+  if (stamps) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_start));
   // 1. pack this rank's tensors into its own slot
   float* mine = slot_of(pt.base[rank], slot, slot_bytes);
   for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
@@ -115,6 +120,7 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const TensorTable t
     if (!ok) failed = 1;
   }
   __syncthreads();
+  if (stamps) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_waited));
   if (failed) {
     if (threadIdx.x == 0 && blockIdx.x == 0) { *(volatile int*)err = 8; __threadfence_system(); }
   } else {
@@ -130,6 +136,16 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const TensorTable t
   }
   // 4. the last block advances the epoch
   __syncthreads();
+  if (stamps) {
+    unsigned long long t_end;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_end));
+    hdr->t_start = t_start;
+    hdr->t_waited = t_waited;
+    hdr->t_end = t_end;
+    hdr->sum_wait_ns += t_waited - t_start;   // packing included: it is a few hundred nanoseconds
+    hdr->sum_total_ns += t_end - t_start;
+    hdr->calls += 1;
+  }
   if (threadIdx.x == 0) {
     __threadfence();
     const unsigned int prev = atomicAdd(&hdr->done_blocks, 1u);
@@ -177,6 +193,19 @@ int peer_allreduce(int n, const void* const* in, void* const* out, const long* c
   return 0;
 }
 }  // namespace cgtb
+
+// Block 0's timing of the calls so far: out[0] calls, out[1] nanoseconds from kernel start until every rank's flag was
+// seen (packing and the wait for slower ranks), out[2] nanoseconds from start to end, both summed over the calls.
+CGTB_API int cgtb_peer_timing(long* out3) {
+  if (!g.local) return fail("cgtb_peer_timing: no symmetric buffer");
+  Header h;
+  CGTB_CUDA_TRY(cudaStreamSynchronize(rt().stream));
+  CGTB_CUDA_TRY(cudaMemcpy(&h, g.local, sizeof(h), cudaMemcpyDeviceToHost));
+  out3[0] = (long)h.calls;
+  out3[1] = (long)h.sum_wait_ns;
+  out3[2] = (long)h.sum_total_ns;
+  return 0;
+}
 
 // Allocate this rank's symmetric buffer (two slots of slot_bytes) and return its 64-byte IPC handle.
 CGTB_API int cgtb_peer_alloc(long slot_bytes, char* handle64) {

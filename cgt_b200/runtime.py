@@ -52,7 +52,7 @@ def _declare(lib):
         "cgtb_allreduce_sum": (ci, [ci, ci, ctypes.POINTER(vp), ctypes.POINTER(vp), c_long_p]),
         "cgtb_peer_alloc": (ci, [cl, ctypes.c_char_p]), "cgtb_peer_open": (ci, [ctypes.c_char_p, ci, ci]),
         "cgtb_peer_close": (ci, []), "cgtb_peer_world": (ci, []), "cgtb_peer_slot_bytes": (cl, []),
-        "cgtb_peer_set_wait_cycles": (ci, [cl]),
+        "cgtb_peer_set_wait_cycles": (ci, [cl]), "cgtb_peer_timing": (ci, [c_long_p]),
         "cgtb_peer_allreduce_sum": (ci, [ci, ctypes.POINTER(vp), ctypes.POINTER(vp), c_long_p]),
         "cgtb_peer_selftest_open": (ci, [cl]), "cgtb_peer_selftest_post": (ci, [vp, cl]),
         "cgtb_alloc": (vp, [ci, cl]), "cgtb_free": (None, [ci, vp]), "cgtb_memcpy": (ci, [ci, ci, vp, vp, cl, ci]),
@@ -73,7 +73,7 @@ def _declare(lib):
         "cgtb_graph_add_return_byval": (ci, [vp, ctypes.c_char_p, ci, c_long_p, c_int_p, cl, ci, vp, vp, ci]),
         "cgtb_interp_new": (vp, [vp, ci, c_long_p, ci]), "cgtb_interp_free": (None, [vp]),
         "cgtb_interp_set_before_sync": (ci, [vp, vp, vp]),
-        "cgtb_interp_run": (ci, [vp, vp, ctypes.POINTER(vp)]), "cgtb_interp_stats": (ci, [vp, c_long_p, ci]),
+        "cgtb_interp_run": (ci, [vp, vp, ctypes.POINTER(vp)]), "cgtb_interp_stats": (ci, [vp, c_long_p, ci]), "cgtb_state_version_bump": (None, []),
         "cgtb_interp_profile": (ci, [vp, ctypes.POINTER(cd), c_long_p, ci]),
         "cgtb_interp_instr_repr": (ctypes.c_char_p, [vp, ci]),
         "cgtb_apply_byref": (ci, [vp, vp, ci, ctypes.POINTER(vp), vp]),
@@ -104,6 +104,7 @@ def _declare(lib):
         "cgtb_concat_part": (ci, [ci, cl, cl, cl, cl, cl, vp, vp]), "cgtb_fill": (ci, [ci, cl, cd, cl, vp]),
         "cgtb_fused_elwise": (ci, [vp, cl, vp, c_long_p, c_long_p, vp]),
         "cgtb_fused_elwise_multi": (ci, [vp, ci, c_long_p, vp, vp]),
+        "cgtb_fused_rows": (ci, [vp, cl, cl, vp, vp]),
         "cgtb_reduce_rkr_f32_static": (ci, [ci, cl, cl, cl, vp, vp]), "cgtb_reduce_static_max_k": (cl, []),
     }
     for (name, (restype, argtypes)) in sig.items():
@@ -591,10 +592,10 @@ class InterpreterWrapper(object):
             L.cgtb_release(out)
 
     def stats(self):
-        vals = (ctypes.c_long * 6)()
-        lib().cgtb_interp_stats(self.interp, vals, 6)
+        vals = (ctypes.c_long * 8)()
+        lib().cgtb_interp_stats(self.interp, vals, 8)
         return dict(zip(("runs", "last_kernel_launches", "last_graph_launches", "segments_captured", "graph_kernels",
-                         "device_instructions"), list(vals)))
+                         "device_instructions", "last_host_ns", "steady_runs"), list(vals)))
 
     def profile(self):
         """[(instruction repr, total ms, count)] when the interpreter was created with profiling on"""

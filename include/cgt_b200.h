@@ -119,8 +119,13 @@ void cgtb_interp_free(cgtbInterp* it);
  * Returns after the runtime stream has been synchronised, so host outputs are readable. */
 int cgtb_interp_run(cgtbInterp* it, cgtbObject* args, cgtbObject** out);
 /* counters: [0] runs, [1] kernels launched by instructions in the last run, [2] graph launches in the
- * last run, [3] segments captured so far, [4] device instructions in the graph */
+ * last run, [3] segments captured so far, [4] kernels inside captured graphs, [5] device instructions in the graph,
+ * [6] host nanoseconds of the last run up to its final wait for the stream, [7] steady runs so far (runs that
+ * repeated the arguments' buffers and shapes of the run before and skipped the host bookkeeping) */
 int cgtb_interp_stats(cgtbInterp* it, long* counters, int n);
+/* Tell every interpreter that a shared variable's array was replaced (not merely overwritten): the next run of each
+ * does its host bookkeeping in full. */
+void cgtb_state_version_bump(void);
 /* fn(ctx) is called in every cgtb_interp_run after the run's device work has been queued and before the run waits
  * for it: the place for host work that should overlap the step (queueing the next batch's upload). NULL removes it. */
 int cgtb_interp_set_before_sync(cgtbInterp* it, void (*fn)(void*), void* ctx);
@@ -136,7 +141,10 @@ int cgtb_apply_byref(void* fptr, void* closure, int n, cgtbObject** reads, cgtbO
  * ---------------------------------------------------------------------------------------------- */
 /* Mul22: C[M,N] = op(A) op(B), alpha 1, beta 0, row-major; lda/ldb/ldc are stored row lengths.
  * Replaces cblas_sgemm / cublasSgemm_v2 in cgt/core.py:2195-2222. 3xTF32 split on tcgen05 tensor
- * cores where the shape allows, an fp32 FMA kernel otherwise. impl: 0 auto, 1 force FMA, 2 force tensor. */
+ * cores where the shape allows, fp32 FMA kernels otherwise and for products too small to repay the tensor-core
+ * kernels' fixed cost. impl: 0 auto, 1 generic FMA kernel, 2 any tensor-core kernel, 3 register-fed tensor-core kernel,
+ * 4 TMA-fed tensor-core kernel, 5 one warp per output (few outputs), 6 16 x 16 FMA tiles (M*N*K <= 2^25); a forced
+ * choice that does not accept the shape fails. */
 int cgtb_sgemm(int tA, int tB, long M, long N, long K, const float* A, long lda, const float* B, long ldb,
                float* C, long ldc, int impl);
 /* BatchedMul22 (cgt/core.py:2272-2286): P independent products, operands strideX apart */
@@ -260,6 +268,25 @@ int cgtb_fused_elwise(const cgtbFusedProgram* prog, long n, const void* const* i
  * the reference. */
 int cgtb_fused_elwise_multi(const cgtbFusedProgram* prog, int ntensors, const long* n, const void* const* in, void* const* out);
 
+/* A chain of elementwise operations and row sums over the rows of an [R, C] matrix, C <= 128, in one launch (a softmax,
+ * its logarithm and its pullback are such chains): one warp per row, values in registers, a row sum by warp shuffles.
+ * Registers hold either one value per element of the row or one value per row; in_kind: CGTB_FIN_F4 an [R, C] array,
+ * CGTB_FIN_COL an [R] array (one value per row), CGTB_FIN_ROW a [C] array (the same for every row), or a scalar.
+ * op_arity 1 / 2 as in cgtbFusedProgram; op_arity 3: the sum of register op_a over the row (kept in every lane).
+ * out_col[j] != 0: output j has one value per row ([R]), else [R, C]. The sum order differs from cgtb_reduce: results
+ * agree with the separate launches to rounding, not bit for bit. No counterpart in the reference. */
+enum { CGTB_FIN_COL = 5, CGTB_FIN_ROW = 6 };
+typedef struct {
+  int n_in, n_ops, n_out;
+  int in_kind[CGTB_FUSED_MAX_IN];
+  int op_arity[CGTB_FUSED_MAX_OPS];
+  int op_code[CGTB_FUSED_MAX_OPS];
+  int op_a[CGTB_FUSED_MAX_OPS], op_b[CGTB_FUSED_MAX_OPS];
+  int out_reg[CGTB_FUSED_MAX_OUT];
+  int out_col[CGTB_FUSED_MAX_OUT];
+} cgtbRowProgram;
+int cgtb_fused_rows(const cgtbRowProgram* prog, long R, long C, const void* const* in, void* const* out);
+
 /* Sum / Max over a set of axes, keepdims (cgt/core.py:1663-1738) */
 int cgtb_reduce(int kind, int dtype, int ndim, const long* shape, const int* reduced, const void* in, void* out);
 
@@ -320,6 +347,9 @@ int cgtb_peer_close(void);
 int cgtb_peer_world(void);
 long cgtb_peer_slot_bytes(void);
 int cgtb_peer_set_wait_cycles(long cycles);
+/* out3: calls so far, nanoseconds spent until every rank's flag was seen, nanoseconds start to end (block 0's clock,
+ * summed over the calls): tells waiting for slower ranks from the exchange itself */
+int cgtb_peer_timing(long* out3);
 int cgtb_peer_allreduce_sum(int n, const void* const* in, void* const* out, const long* counts);
 int cgtb_peer_selftest_open(long slot_bytes);
 int cgtb_peer_selftest_post(const float* host_payload, long count);

@@ -34,8 +34,18 @@ def build_restatement(force=False):
     return out
 
 
-def build_reference(reference_root="/root/reference", force=False):
+def default_reference_root():
+    """The reference checkout: $CGT_REFERENCE_ROOT, else a directory `reference` beside this repository."""
+    env = os.environ.get("CGT_REFERENCE_ROOT")
+    if env:
+        return env
+    return osp.join(osp.dirname(osp.dirname(HERE)), "reference")
+
+
+def build_reference(reference_root=None, force=False):
     """Returns the path of the built library, or None when the reference tree is absent."""
+    if reference_root is None:
+        reference_root = default_reference_root()
     inc = osp.join(reference_root, "include")
     common = osp.join(reference_root, "src", "cgt_common.cpp")
     if not (osp.isdir(inc) and osp.exists(common)):
@@ -50,6 +60,6 @@ def build_reference(reference_root="/root/reference", force=False):
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    root = sys.argv[1] if len(sys.argv) > 1 else default_reference_root()
     print(build_restatement(force=True))
     print(build_reference(root, force=True))

@@ -136,8 +136,9 @@ def test_elementwise_fusion_changes_no_bit(rt, name, generated):
     for fuse in (False, True):
         # padded column rows and the convolutions without a column matrix need the fused output stage, which needs the
         # fused chains, and they change the order of the sums: off on both sides here
+        # (the row chains sum in another order as well: off)
         with cgt.scoped_update_config(fuse_elementwise=fuse, jit_fused_elementwise=generated, pad_conv_columns=False,
-                                      fuse_conv_implicit=False, use_cuda_graphs=False):
+                                      fuse_conv_implicit=False, fuse_rows=False, use_cuda_graphs=False):
             cfg = configs.BUILDERS[name](**SMALL[name])
             f = cfg.compile()
             n_fused = sum(1 for instr in f.eg.instrs if "FusedElwise" in repr(instr))
@@ -146,6 +147,50 @@ def test_elementwise_fusion_changes_no_bit(rt, name, generated):
             params = [np.asarray(p.op.get_value()).copy() for p in cfg.params]
             results[fuse] = (n_fused, len(f.eg.instrs), losses, params)
     assert results[False][0] == 0 and results[True][0] > 0
+    assert results[True][1] < results[False][1]
+    for (a, b) in zip(results[False][2], results[True][2]):
+        assert np.array_equal(a, b)
+    for (a, b) in zip(results[False][3], results[True][3]):
+        assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("name", ["mlp", "cifar", "lstm"])
+def test_row_fusion_matches_separate_kernels(rt, name):
+    """Softmax, its logarithm and its pullback as one FusedRows launch per [batch, classes] matrix: the row sums are
+    taken in another order than the reduction kernel's, so losses and parameters agree to rounding, not bit for bit."""
+    results = {}
+    for fuse in (False, True):
+        with cgt.scoped_update_config(fuse_rows=fuse, use_cuda_graphs=False):
+            cfg = configs.BUILDERS[name](**SMALL[name])
+            f = cfg.compile()
+            n_rows = sum(1 for instr in f.eg.instrs if "FusedRows" in repr(instr))
+            batches = [cfg.batch(seed) for seed in range(2)]
+            losses = [np.asarray(f(*batches[i % 2])[0]).copy() for i in range(4)]
+            params = [np.asarray(p.op.get_value()).copy() for p in cfg.params]
+            results[fuse] = (n_rows, len(f.eg.instrs), losses, params)
+    assert results[False][0] == 0 and results[True][0] > 0
+    assert results[True][1] < results[False][1]
+    for (a, b) in zip(results[False][2], results[True][2]):
+        np.testing.assert_allclose(a, b, rtol=2e-5)
+    for (a, b) in zip(results[False][3], results[True][3]):
+        np.testing.assert_allclose(a, b, rtol=1e-4, atol=1e-6 * max(1.0, float(np.abs(a).max())))
+
+
+@pytest.mark.parametrize("name", ["mlp", "cifar", "lstm"])
+def test_merged_parameter_updates_change_no_bit(rt, name):
+    """The step's parameter updates as one multi-tensor launch: the same operations on the same values as one launch
+    per parameter, so losses and parameters are identical."""
+    results = {}
+    for merge in (False, True):
+        with cgt.scoped_update_config(merge_parameter_updates=merge, use_cuda_graphs=False):
+            cfg = configs.BUILDERS[name](**SMALL[name])
+            f = cfg.compile()
+            n_multi = sum(1 for instr in f.eg.instrs if "MultiFusedElwise" in repr(instr))
+            batches = [cfg.batch(seed) for seed in range(2)]
+            losses = [np.asarray(f(*batches[i % 2])[0]).copy() for i in range(4)]
+            params = [np.asarray(p.op.get_value()).copy() for p in cfg.params]
+            results[merge] = (n_multi, len(f.eg.instrs), losses, params)
+    assert results[False][0] == 0 and results[True][0] >= 1
     assert results[True][1] < results[False][1]
     for (a, b) in zip(results[False][2], results[True][2]):
         assert np.array_equal(a, b)

@@ -321,13 +321,19 @@ GEMM_SHAPES = [
     # (M, N, K)  -- reference test shapes, config shapes scaled to run in seconds, ragged edges
     (3, 5, 4), (128, 10, 256), (128, 256, 784), (1024, 32, 75), (900, 32, 800), (32, 75, 4096), (64, 800, 1152),
     (450, 800, 32), (1, 1, 1), (65, 63, 17), (100, 20, 500), (64, 512, 65), (129, 257, 130),
+    # the unrolled LSTM's products (hidden 128, batch 64)
+    (64, 512, 128), (128, 512, 64), (64, 128, 512),
 ]
 
 
 @pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
 @pytest.mark.parametrize("tA,tB", [(0, 0), (0, 1), (1, 0), (1, 1)])
-@pytest.mark.parametrize("impl", [1, 0])
+@pytest.mark.parametrize("impl", [1, 0, 6])
 def test_sgemm(rt, M, N, K, tA, tB, impl):
+    """impl 0: the dispatcher's choice; 1: the generic FMA kernel; 6: the 16 x 16 FMA-tile kernel for products below the
+    tensor-core kernels' break-even size."""
+    if impl == 6 and M * N * K > (1 << 25):
+        pytest.skip("beyond the FMA-tile kernel's size limit")
     rs = np.random.RandomState(8)
     A = rs.randn(*((K, M) if tA else (M, K))).astype("f4")
     B = rs.randn(*((N, K) if tB else (K, N))).astype("f4")
@@ -683,6 +689,63 @@ def test_fused_elwise_matches_separate_kernels(rt, shape):
     want_mask = (t >= 0)
     assert np.array_equal(om.get().astype(bool), want_mask)
     np.testing.assert_allclose(o2.get(), t * want_mask, rtol=RTOL, atol=ATOL)
+
+
+class _RowProgram(ctypes.Structure):
+    _fields_ = [("n_in", ctypes.c_int), ("n_ops", ctypes.c_int), ("n_out", ctypes.c_int), ("in_kind", ctypes.c_int * 8),
+                ("op_arity", ctypes.c_int * 16), ("op_code", ctypes.c_int * 16), ("op_a", ctypes.c_int * 16),
+                ("op_b", ctypes.c_int * 16), ("out_reg", ctypes.c_int * 4), ("out_col", ctypes.c_int * 4)]
+
+
+@pytest.mark.parametrize("R,C", [(128, 10), (64, 65), (1, 1), (5, 32), (1000, 33), (7, 100), (300, 128)])
+def test_fused_rows_softmax_chain(rt, R, C):
+    """log(exp(x + bias) / rowsum(exp(x + bias))) with its pullback against a target matrix, the chain a softmax loss
+    compiles to (cgt/nn.py:55-62), in one launch: against float64 numpy, and against the row sums of cgtb_reduce."""
+    rs = np.random.RandomState(R * 131 + C)
+    x, bias = rs.randn(R, C).astype("f4"), rs.randn(1, C).astype("f4")
+    g, scale = rs.randn(R, C).astype("f4"), np.array(-1.0 / R, "f4")
+    dx, db, dg, dsc = Dev(x), Dev(bias), Dev(g), Dev(scale)
+    # registers: 0 x [R,C], 1 bias [1,C], 2 g [R,C], 3 scale (scalar)
+    # 4 = x + bias, 5 = exp, 6 = rowsum(5), 7 = 5 / 6 (softmax), 8 = log(7), 9 = g * scale, 10 = 9 / 7 (d softmax),
+    # 11 = 10 * 7, 12 = rowsum(11), 13 = 10 - 12, 14 = 13 * 7 (d logits)
+    ops = [(2, 1, 0, 1), (1, 3, 4, 0), (3, 0, 5, 0), (2, 3, 5, 6), (1, 6, 7, 0), (2, 0, 2, 3), (2, 3, 9, 7),
+           (2, 0, 10, 7), (3, 0, 11, 0), (2, 2, 10, 12), (2, 0, 13, 7)]
+    P = _RowProgram()
+    P.n_in, P.n_ops, P.n_out = 4, len(ops), 3
+    for (k, kind) in enumerate([0, 6, 0, 2]):
+        P.in_kind[k] = kind
+    for (j, (ar, opc, a, b)) in enumerate(ops):
+        P.op_arity[j], P.op_code[j], P.op_a[j], P.op_b[j] = ar, opc, a, b
+    for (q, (reg, col)) in enumerate([(8, 0), (6, 1), (14, 0)]):
+        P.out_reg[q], P.out_col[q] = reg, col
+    o_log, o_sum, o_dl = Dev(shape=(R, C), dtype="f4"), Dev(shape=(R, 1), dtype="f4"), Dev(shape=(R, C), dtype="f4")
+    ins = (ctypes.c_void_p * 8)(dx.ptr, db.ptr, dg.ptr, dsc.ptr)
+    outs = (ctypes.c_void_p * 4)(o_log.ptr, o_sum.ptr, o_dl.ptr)
+    call("cgtb_fused_rows", ctypes.byref(P), R, C, ins, outs)
+    e = np.exp(x.astype("f8") + bias.astype("f8"))
+    ssum = e.sum(axis=1, keepdims=True)
+    sm = e / ssum
+    dsm = g.astype("f8") * float(scale) / sm
+    dl = (dsm - (dsm * sm).sum(axis=1, keepdims=True)) * sm
+    np.testing.assert_allclose(o_sum.get(), ssum, rtol=2e-6)
+    np.testing.assert_allclose(o_log.get(), np.log(sm), rtol=1e-5, atol=2e-6)
+    np.testing.assert_allclose(o_dl.get(), dl, rtol=1e-4, atol=1e-5 * np.abs(dl).max())
+    # the separate reduction kernel over the same exponentials
+    e4 = Dev(np.exp(x + bias).astype("f4"))
+    red = Dev(shape=(R, 1), dtype="f4")
+    call("cgtb_reduce", 0, code("f4"), 2, longs((R, C)), ints((0, 1)), e4.ptr, red.ptr)
+    np.testing.assert_allclose(o_sum.get(), red.get(), rtol=3e-6)
+
+
+def test_fused_rows_refuses_long_rows(rt):
+    P = _RowProgram()
+    P.n_in, P.n_ops, P.n_out = 1, 1, 1
+    P.op_arity[0], P.op_a[0] = 3, 0
+    P.out_reg[0], P.out_col[0] = 1, 1
+    d = Dev(shape=(4, 129), dtype="f4")
+    o = Dev(shape=(4, 1), dtype="f4")
+    rc = runtime.lib().cgtb_fused_rows(ctypes.byref(P), 4, 129, (ctypes.c_void_p * 8)(d.ptr), (ctypes.c_void_p * 4)(o.ptr))
+    assert rc != 0 and "128" in runtime.last_error()
 
 
 def test_reduce_over_an_empty_axis_gives_the_identity(rt):
