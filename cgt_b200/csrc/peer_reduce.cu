@@ -49,7 +49,8 @@ struct PeerTable {
 struct TensorTable {
   const float* src[kMaxTensors];
   float* dst[kMaxTensors];
-  long off[kMaxTensors + 1];   // tensor t occupies elements [off[t], off[t+1]) of the packed payload
+  long off[kMaxTensors + 1];   // tensor t starts at element off[t] of the packed payload (a multiple of four)
+  long cnt[kMaxTensors];       // and has cnt[t] elements; off[t+1] - off[t] is cnt[t] rounded up to four
   int n;
 };
 
@@ -92,12 +93,26 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const TensorTable t
   const bool stamps = blockIdx.x == 0 && threadIdx.x == 0;
   unsigned long long t_start = 0, t_waited = 0;
   if (stamps) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_start));
-  // 1. pack this rank's tensors into its own slot
+  // 1. pack this rank's tensors into its own slot. Every tensor starts on a 16-byte boundary of the slot (off[] are
+  // multiples of four elements), so a group of four elements never straddles two tensors.
   float* mine = slot_of(pt.base[rank], slot, slot_bytes);
-  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+  const long ngroups = total >> 2;   // total is a multiple of four as well
+  for (long q = (long)blockIdx.x * blockDim.x + threadIdx.x; q < ngroups; q += (long)gridDim.x * blockDim.x) {
+    const long i = q << 2;
     int t = 0;
     while (t + 1 < tt.n && i >= tt.off[t + 1]) ++t;
-    mine[i] = tt.src[t][i - tt.off[t]];
+    const long j = i - tt.off[t], cnt = tt.cnt[t];
+    const float* src = tt.src[t] + j;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (j + 4 <= cnt && (((uintptr_t)src) & 15) == 0) {
+      v = *reinterpret_cast<const float4*>(src);
+    } else {
+      if (j < cnt) v.x = src[0];
+      if (j + 1 < cnt) v.y = src[1];
+      if (j + 2 < cnt) v.z = src[2];
+      if (j + 3 < cnt) v.w = src[3];
+    }
+    *reinterpret_cast<float4*>(mine + i) = v;
   }
   __threadfence_system();
   __syncthreads();
@@ -124,14 +139,31 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const TensorTable t
   if (failed) {
     if (threadIdx.x == 0 && blockIdx.x == 0) { *(volatile int*)err = 8; __threadfence_system(); }
   } else {
-    // 3. sum over the ranks' slots in rank order, straight into the result tensors
-    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
-      // cache-global loads: a line of a peer's slot must not be served from this SM's L1
-      float acc = __ldcg(slot_of(pt.base[0], slot, slot_bytes) + i);
-      for (int r = 1; r < world; ++r) acc += __ldcg(slot_of(pt.base[r], slot, slot_bytes) + i);
+    // 3. sum over the ranks' slots in rank order, straight into the result tensors: four elements per thread, the
+    // loads of all ranks in flight before the first addition
+    for (long q = (long)blockIdx.x * blockDim.x + threadIdx.x; q < ngroups; q += (long)gridDim.x * blockDim.x) {
+      const long i = q << 2;
+      float4 v[kMaxRanks];
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r)
+        if (r < world)   // cache-global loads: a line of a peer's slot must not be served from this SM's L1
+          v[r] = __ldcg(reinterpret_cast<const float4*>(slot_of(pt.base[r], slot, slot_bytes) + i));
+      float4 acc = v[0];
+#pragma unroll
+      for (int r = 1; r < kMaxRanks; ++r)
+        if (r < world) { acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w; }
       int t = 0;
       while (t + 1 < tt.n && i >= tt.off[t + 1]) ++t;
-      tt.dst[t][i - tt.off[t]] = acc;
+      const long j = i - tt.off[t], cnt = tt.cnt[t];
+      float* dst = tt.dst[t] + j;
+      if (j + 4 <= cnt && (((uintptr_t)dst) & 15) == 0) {
+        *reinterpret_cast<float4*>(dst) = acc;
+      } else {
+        if (j < cnt) dst[0] = acc.x;
+        if (j + 1 < cnt) dst[1] = acc.y;
+        if (j + 2 < cnt) dst[2] = acc.z;
+        if (j + 3 < cnt) dst[3] = acc.w;
+      }
     }
   }
   // 4. the last block advances the epoch
@@ -169,7 +201,7 @@ int alloc_buffer(size_t slot_bytes, char** out) {
 
 namespace cgtb {
 // true when the peer-memory all-reduce can take a payload of `bytes`
-bool peer_ready(size_t bytes) { return g.local && g.world > 1 && bytes <= g.slot_bytes; }
+bool peer_ready(size_t bytes) { return g.local && g.world > 1 && bytes + 16 * kMaxTensors <= g.slot_bytes; }  // padding to 16 bytes per tensor
 
 int peer_allreduce(int n, const void* const* in, void* const* out, const long* counts) {
   TensorTable tt;
@@ -178,8 +210,10 @@ int peer_allreduce(int n, const void* const* in, void* const* out, const long* c
   for (int i = 0; i < n; ++i) {
     tt.src[i] = (const float*)in[i];
     tt.dst[i] = (float*)out[i];
-    tt.off[i + 1] = tt.off[i] + (counts[i] > 0 ? counts[i] : 0);
+    tt.cnt[i] = counts[i] > 0 ? counts[i] : 0;
+    tt.off[i + 1] = tt.off[i] + ((tt.cnt[i] + 3) & ~3L);
   }
+  if ((size_t)tt.off[n] * sizeof(float) > g.slot_bytes) return fail("peer all-reduce: %ld bytes (tensors padded to 16 bytes) exceed the slot", tt.off[n] * 4);
   const long total = tt.off[n];
   if (total == 0) return 0;
   PeerTable pt;
@@ -187,7 +221,7 @@ int peer_allreduce(int n, const void* const* in, void* const* out, const long* c
   int* err = tc_error_flag();
   if (!err) return 1;
   // few blocks: the payload is small and every block polls every rank's flag
-  const unsigned blocks = (unsigned)std::max<long>(1, std::min<long>(cgtb_ceil_div(total, 2048), 64));
+  const unsigned blocks = (unsigned)std::max<long>(1, std::min<long>(cgtb_ceil_div(total, 1024), 128));  // one group of four per thread
   CGTB_LAUNCH(peer_allreduce_kernel, blocks, 256, 0, tt, pt, g.rank, g.world, g.slot_bytes, g.wait_cycles, err);
   CGTB_CHECK_LAUNCH("peer_allreduce");
   return 0;
@@ -268,8 +302,8 @@ CGTB_API int cgtb_peer_allreduce_sum(int n, const void* const* in, void* const* 
   if (!require_runtime("cgtb_peer_allreduce_sum")) return 1;
   if (!g.local || g.world < 2) return fail("cgtb_peer_allreduce_sum: no peer group (cgtb_peer_alloc / cgtb_peer_open)");
   if (n < 1 || n > kMaxTensors) return fail("cgtb_peer_allreduce_sum: between 1 and %d tensors", kMaxTensors);
-  long total = 0;
-  for (int i = 0; i < n; ++i) total += counts[i] > 0 ? counts[i] : 0;
+  long total = 0;   // in the slot every tensor starts on a 16-byte boundary
+  for (int i = 0; i < n; ++i) total += ((counts[i] > 0 ? counts[i] : 0) + 3) & ~3L;
   if ((size_t)total * 4 > g.slot_bytes) return fail("cgtb_peer_allreduce_sum: %ld bytes exceed the slot of %ld bytes", total * 4, (long)g.slot_bytes);
   return cgtb::peer_allreduce(n, in, out, counts);
 }

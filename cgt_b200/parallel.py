@@ -203,7 +203,7 @@ def _fits_peer_path(grads):
         if shp is None or any(s is None for s in shp):
             return False
         total += int(np.prod(shp)) * 4
-    return total <= PEER_SLOT_BYTES
+    return total + 16 * 32 <= PEER_SLOT_BYTES   # in the slot every tensor starts on a 16-byte boundary
 
 
 def shard(arrays, rank_=None, world=None):

@@ -339,8 +339,11 @@ int cgtb_allreduce_sum(int dtype, int n, const void* const* in, void* const* out
  * every rank (replicas stay bit-identical). The kernel's waits for the other ranks are bounded by a cycle budget
  * (cgtb_peer_set_wait_cycles, default about a second): on expiry the call's result is invalid, the failure is
  * reported by the next cgtb_synchronize / cgtb_interp_run, and the library stays usable.
+ * In a slot the tensors lie back to back, each starting at a multiple of four elements (the payload that fits is the
+ * sum of the tensors' sizes, each rounded up to 16 bytes).
  * cgtb_peer_selftest_*: a two-rank group inside one process whose second rank never arrives (post() plays it for the
- * next call), for testing the bounded wait on one GPU without faulting or hanging anything. */
+ * next call, with a payload in the slot's layout), for testing the bounded wait on one GPU without faulting or
+ * hanging anything. */
 int cgtb_peer_alloc(long slot_bytes, char* handle64);
 int cgtb_peer_open(const char* handles, int rank, int world);
 int cgtb_peer_close(void);

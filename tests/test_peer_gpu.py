@@ -29,7 +29,7 @@ def test_missing_rank_times_out_and_the_library_stays_usable(rt):
         assert L.cgtb_peer_world() == 2 and L.cgtb_peer_slot_bytes() == 1 << 16
         runtime.check(L.cgtb_peer_set_wait_cycles(2_000_000), "wait budget")   # about a millisecond
         rs = np.random.RandomState(3)
-        a, b = rs.randn(1000).astype("f4"), rs.randn(7, 11).astype("f4")
+        a, b = rs.randn(1001).astype("f4"), rs.randn(7, 11).astype("f4")
         da, db = Dev(a), Dev(b)
         oa, ob = Dev(np.full(a.shape, 5.0, "f4")), Dev(np.full(b.shape, 5.0, "f4"))
         # 1. the other rank never arrives: the call returns, the failure surfaces at the synchronisation
@@ -44,12 +44,16 @@ def test_missing_rank_times_out_and_the_library_stays_usable(rt):
         assert np.array_equal(sq.get(), a * a)
         # 3. the missing rank's payload and flag are posted for the next call: it completes with the sum, twice in a row
         for rep in range(2):
-            peer = rs.randn(a.size + b.size).astype("f4")
+            # the slot's layout: every tensor starts at a multiple of four elements (1001 -> the second one at 1004)
+            pa, pb = rs.randn(a.size).astype("f4"), rs.randn(*b.shape).astype("f4")
+            peer = np.zeros(1004 + 80, "f4")
+            peer[:a.size] = pa
+            peer[1004:1004 + b.size] = pb.ravel()
             runtime.check(L.cgtb_peer_selftest_post(peer.ctypes.data_as(ctypes.c_void_p), peer.size), "post")
             runtime.check(_allreduce(L, [da, db], [oa, ob]), "peer allreduce")
             runtime.synchronize()
-            assert np.array_equal(oa.get(), a + peer[:a.size])
-            assert np.array_equal(ob.get(), b + peer[a.size:].reshape(b.shape))
+            assert np.array_equal(oa.get(), a + pa)
+            assert np.array_equal(ob.get(), b + pb)
         # a payload beyond the slot is refused before anything is launched
         big = Dev(shape=((1 << 16) // 4 + 1,), dtype="f4")
         assert _allreduce(L, [big], [big]) != 0 and "exceed the slot" in runtime.last_error()
