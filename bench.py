@@ -553,6 +553,18 @@ def run_reference(args):
     print(json.dumps(out))
 
 
+def run_only_kernel(args):
+    from cgt_b200 import runtime
+    runtime.ensure_init(0)
+    table = [e for e in cifar_kernel_table() if args.only_kernel in e["name"] or args.only_kernel in e["shape"]]
+    if not table:
+        raise SystemExit("no entry of the per-kernel list matches %r" % args.only_kernel)
+    for k in measure_kernels(table, launches=args.kernel_launches):
+        print(json.dumps({"name": k["name"], "shape": k["shape"], "us_median": round(k["us"], 2), "us_min": round(k["us_min"], 2),
+                          "kernels_per_call": k["kernels"], "algorithmic_bytes": k["bytes"], "algorithmic_flops": k["flops"],
+                          "launches": args.kernel_launches}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -563,10 +575,15 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--config", default="cifar", choices=sorted(CONFIGS))
     ap.add_argument("--no-extras", action="store_true", help="skip the per-kernel loop, parity and the CPU baseline (for ncu runs)")
+    ap.add_argument("--only-kernel", default=None, metavar="TEXT",
+                    help="run only the entries of the per-kernel list whose name or shape contains TEXT, --kernel-launches "
+                         "times each on one GPU, print their times and exit (the command that ncu captures wrap)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     args.repeats = max(args.repeats, 1)
-    if args.impl == "reference":
+    if args.only_kernel is not None:
+        run_only_kernel(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_b200(args)

@@ -80,6 +80,12 @@ def fused_source(op):
             params.append("const long* __restrict__ in%d" % k)
             hoist.append("const float s%d = (float)in%d[0];" % (k, k))
             loads.append(("none", "", "s%d" % k))
+        elif kind == 7:
+            # columns [bi, bi + W) of a matrix with rows of bk elements; W is a literal of this chain
+            params.append("const float* __restrict__ in%d, const long bk%d, const long bi%d" % (k, k, k))
+            W = op.static_shape[1]
+            loads.append(("pack", "const I row%d = (i * V) / (I)%d;\n    const Pack<float, V> p%d = load_pack<float, V>(in%d + (size_t)row%d * bk%d + bi%d "
+                          "+ ((i * V) - row%d * (I)%d));" % (k, W, k, k, k, k, k, k, W), "p%d.v[v]" % k))
         else:
             params.append("const float* __restrict__ in%d, const long bk%d, const long bi%d" % (k, k, k))
             # one value per pack when the run length is a multiple of V, else one index per element
@@ -119,9 +125,9 @@ def fused_source(op):
     lines += ["  }", "}"]
     args = []
     for (k, kind) in enumerate(op.in_kinds):
-        ctype = {0: "float", 1: "int8_t", 2: "float", 3: "long", 4: "float"}[kind]
+        ctype = {0: "float", 1: "int8_t", 2: "float", 3: "long", 4: "float", 7: "float"}[kind]
         args.append("(const %s*)in[%d]" % (ctype, k))
-        if kind == 4:
+        if kind in (4, 7):
             args += ["bk[%d]" % k, "bi[%d]" % k]
     for (q, ctype) in enumerate(outs):
         args.append("(%s*)out[%d]" % (ctype, q))
@@ -143,21 +149,87 @@ def fused_source(op):
     return _FUSED_HEAD + "\n".join(lines) + "\n"
 
 
+def rows_source(op):
+    """CUDA source of the kernel for one FusedRows program: one warp per row, element c of the row in lane c % 32,
+    slot c / 32; every operation calls the scalar template the separate kernels use; a row sum adds the lane's valid
+    slots in order and then folds the lanes with xor shuffles (16, 8, 4, 2, 1), as the library's kernel does."""
+    n_in = len(op.in_kinds)
+    lines = ["template <int E>", "__global__ void __launch_bounds__(128) rows_kernel(const long R, const long C, const void* const* in_, void* const* out_) {"]
+    params, args = [], []
+    for (k, kind) in enumerate(op.in_kinds):
+        ctype = "long" if kind == 3 else "float"
+        params.append("const %s* __restrict__ in%d" % (ctype, k))
+        args.append("(const %s*)in[%d]" % (ctype, k))
+    for q in range(len(op.out_regs)):
+        params.append("float* __restrict__ out%d" % q)
+        args.append("(float*)out[%d]" % q)
+    lines = ["template <int E>",
+             "__global__ void __launch_bounds__(128) rows_kernel(const long R, const long C, %s) {" % ", ".join(params),
+             "  const int lane = threadIdx.x & 31;",
+             "  const long row = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);",
+             "  if (row >= R) return;"]
+    for (k, kind) in enumerate(op.in_kinds):
+        lines.append("  float r%d[E];" % k)
+        if kind in (0, 6):
+            base = "in%d + row * C" % k if kind == 0 else "in%d" % k
+            lines += ["#pragma unroll", "  for (int e = 0; e < E; ++e) { const long c = lane + 32 * e; r%d[e] = c < C ? (%s)[c] : 0.0f; }" % (k, base)]
+        else:
+            src = {5: "in%d[row]" % k, 2: "in%d[0]" % k, 3: "(float)in%d[0]" % k}[kind]
+            lines += ["  { const float v = %s;" % src, "#pragma unroll", "    for (int e = 0; e < E; ++e) r%d[e] = v; }" % k]
+    for (j, (arity, code, a, b)) in enumerate(op.program):
+        d = n_in + j
+        lines.append("  float r%d[E];" % d)
+        if arity == 1:
+            lines += ["#pragma unroll", "  for (int e = 0; e < E; ++e) r%d[e] = unary_apply<float, float>(%d, r%d[e]);" % (d, code, a)]
+        elif arity == 2:
+            lines += ["#pragma unroll", "  for (int e = 0; e < E; ++e) r%d[e] = binary_apply<float, float, float>(%d, r%d[e], r%d[e]);" % (d, code, a, b)]
+        else:
+            lines += ["  { float s = 0.0f;", "#pragma unroll", "    for (int e = 0; e < E; ++e) if (lane + 32 * e < C) s += r%d[e];" % a,
+                      "#pragma unroll", "    for (int d = 16; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);",
+                      "#pragma unroll", "    for (int e = 0; e < E; ++e) r%d[e] = s; }" % d]
+    for (q, (reg, col)) in enumerate(zip(op.out_regs, op.out_cols)):
+        if col:
+            lines.append("  if (lane == 0) out%d[row] = r%d[0];" % (q, reg))
+        else:
+            lines += ["#pragma unroll", "  for (int e = 0; e < E; ++e) { const long c = lane + 32 * e; if (c < C) out%d[row * C + c] = r%d[e]; }" % (q, reg)]
+    lines.append("}")
+    call = "(R, C, %s)" % ", ".join(args)
+    lines += [
+        'extern "C" __attribute__((visibility("default"))) int cgtb_rows_launch(long R, long C, const void* const* in, void* const* out, void* stream) {',
+        "  const unsigned blocks = (unsigned)((R + 3) / 4);",
+        "  if (C <= 32) rows_kernel<1><<<blocks, 128, 0, (cudaStream_t)stream>>>%s;" % call,
+        "  else if (C <= 64) rows_kernel<2><<<blocks, 128, 0, (cudaStream_t)stream>>>%s;" % call,
+        "  else rows_kernel<4><<<blocks, 128, 0, (cudaStream_t)stream>>>%s;" % call,
+        "  return cudaPeekAtLastError() != cudaSuccess;",
+        "}",
+    ]
+    return _FUSED_HEAD + "\n".join(lines) + "\n"
+
+
 _fused_libs = {}
+
+
+def rows_launcher(op):
+    """Address of the generated launcher for a FusedRows program, or None (the library's kernel runs it then)."""
+    return _generated_launcher(rows_source(op), "rows_", "cgtb_rows_launch", "a fused row chain")
+
 
 
 def fused_launcher(op):
     """Address of the generated launcher for this program (compiled into the hash-keyed cache on first
     use), or None when generation is switched off or the compiler is not available: the library's
     register-machine kernel then runs the program."""
+    return _generated_launcher(fused_source(op), "fused_", "cgtb_fused_launch", "a fused elementwise chain")
+
+
+def _generated_launcher(src, tag, symbol, what):
     import ctypes
     import os.path as osp
     from . import compilation, utils
     if not core.get_config().get("jit_fused_elementwise", True):
         return None
-    src = fused_source(op)
     info = compilation.get_compile_info()
-    prefix = "fused_" + utils.hash_seq1(src, "fmad=false", str(compilation.CPP_ABI_VERSION))
+    prefix = tag + utils.hash_seq1(src, "fmad=false", str(compilation.CPP_ABI_VERSION))
     if prefix in _fused_libs:
         return _fused_libs[prefix][1]
     libpath = osp.join(info["CACHE_ROOT"], prefix + ".so")
@@ -171,11 +243,10 @@ def fused_launcher(op):
                               % (srcpath, libpath, info["INCLUDES"]))
             os.replace(libpath + ".tmp", libpath)
         lib = ctypes.CDLL(libpath)
-        addr = ctypes.cast(lib.cgtb_fused_launch, ctypes.c_void_p).value
+        addr = ctypes.cast(getattr(lib, symbol), ctypes.c_void_p).value
     except (RuntimeError, OSError) as err:
         import sys
-        sys.stderr.write("cgt_b200: no generated kernel for a fused elementwise chain (%s); using the built-in one\n"
-                         % str(err).splitlines()[0])
+        sys.stderr.write("cgt_b200: no generated kernel for %s (%s); using the built-in one\n" % (what, str(err).splitlines()[0]))
         _fused_libs[prefix] = (None, None)
         return None
     _fused_libs[prefix] = (lib, addr)

@@ -172,6 +172,118 @@ def _foldable_repeat(node):
     return all(b - a == 1 for (a, b) in zip(kept[:-1], kept[1:]))
 
 
+def view_leading_slices(outputs, updatetargs, node2shape):
+    """GetSli along axis 0 with step 1 and constant bounds -> LeadingSlice: the rows of a C-contiguous array are contiguous,
+    so the slice is a view at an offset instead of a copy kernel. Only where the source cannot change under the view:
+    it is an argument's device copy or any other node that no instruction writes into (no update target, no IncSli /
+    IncFlatIndices base)."""
+    all_out = list(outputs) + list(updatetargs)
+    nodes = core.topsorted(all_out)
+    written = set()
+    for node in nodes:
+        if not node.is_input() and node.op.writes_to_input >= 0:
+            written.add(node.parents[node.op.writes_to_input])
+    replace = {}
+    for node in nodes:
+        if node.is_input() or not isinstance(node.op, core.GetSli) or node.op.axis != 0 or node in all_out:
+            continue
+        (x, start, stop, step) = node.parents
+        if not all(isinstance(q.op, core.Constant) for q in (start, stop, step) if not q.is_input()) or any(q.is_input() for q in (start, stop, step)):
+            continue
+        xshp = _static_shape(node2shape[x])
+        (a, b, st) = (int(start.op.value), int(stop.op.value), int(step.op.value))
+        if st != 1 or xshp is None or not (0 <= a <= b <= xshp[0]) or x in written or x in updatetargs:
+            continue
+        if not x.is_input() and isinstance(x.op, core.InMemoryData):
+            continue   # a shared variable can be updated in place while the view is alive
+        new = core.Result(core.LeadingSlice(), [x, start, stop])
+        node2shape[new] = node2shape[node]
+        new.props.update(node.props)
+        replace[node] = new
+    if not replace:
+        return list(outputs), list(updatetargs)
+    return _rewire(outputs, updatetargs, replace)
+
+
+def fuse_slice_sums(outputs, updatetargs, node2shape):
+    """Sums of IncSli(zeros, start, stop, 1, y) over disjoint column ranges of one float32 matrix -> ScatterCols.
+
+    That is the form in which the gradient of several column slices of one matrix reaches the compiler (every
+    GetSli.pullback makes its own zero matrix and increments its slice; the contributions are then added): k zero
+    fills, k slice increments and k - 1 additions on [R, C] matrices for what is a placement of k pieces. A single
+    padded slice (no addition) is rewritten as well: it saves the fill. Returns the new (outputs, updatetargs)."""
+    all_out = list(outputs) + list(updatetargs)
+    nodes = core.topsorted(all_out)
+    children = defaultdict(list)
+    for node in nodes:
+        for par in node.parents:
+            children[par].append(node)
+    out_set = set(all_out)
+
+    def const_int(node):
+        if node.is_input() or not isinstance(node.op, core.Constant):
+            return None
+        v = np.asarray(node.op.value)
+        return int(v.reshape(-1)[0]) if v.size == 1 else None
+
+    def pad_piece(node):
+        """(offset, width, y, C) when node = IncSli{1}(Fill{0}, start, stop, 1, y) on a static float32 matrix"""
+        if node.is_input() or not isinstance(node.op, core.IncSli) or node.op.axis != 1 or node.ndim != 2 or node.dtype != "f4":
+            return None
+        (z, start, stop, step, y) = node.parents
+        if z.is_input() or not isinstance(z.op, core.Fill) or float(z.op.value) != 0.0 or len(children[z]) != 1 or z in out_set:
+            return None
+        shp, yshp = _static_shape(node2shape[node]), _static_shape(node2shape[y])
+        (a, b, st) = (const_int(start), const_int(stop), const_int(step))
+        if shp is None or yshp is None or a is None or b is None or st != 1 or y.dtype != "f4" or len(yshp) != 2:
+            return None
+        if not (0 <= a <= b <= shp[1]) or yshp != (shp[0], b - a):
+            return None
+        return (a, b - a, y, shp[1])
+
+    def collect(node, pieces):
+        """leaves of the addition tree below `node`; False when something else than padded slices is added"""
+        piece = pad_piece(node)
+        if piece is not None:
+            pieces.append(piece)
+            return True
+        if node.is_input() or not isinstance(node.op, core.ElwiseBinary) or node.op.opname != "+" or node.ndim != 2:
+            return False
+        for par in node.parents:
+            if par.ndim != 2 or len(children[par]) != 1 or par in out_set:
+                return False
+            if not collect(par, pieces):
+                return False
+        return True
+
+    replace = {}
+    covered = set()
+    for node in reversed(nodes):   # consumers first: the root of an addition tree is met before its parts
+        if node in covered or node.is_input():
+            continue
+        pieces = []
+        if not collect(node, pieces) or not pieces or len(pieces) > 8:
+            continue
+        C = pieces[0][3]
+        spans = sorted((o, o + w) for (o, w, _y, _c) in pieces)
+        if any(c != C for (_o, _w, _y, c) in pieces) or any(a1 < b0 for ((_a0, b0), (a1, _b1)) in zip(spans[:-1], spans[1:])):
+            continue
+        new = core.Result(core.ScatterCols([o for (o, _w, _y, _c) in pieces], [w for (_o, w, _y, _c) in pieces], C),
+                          [y for (_o, _w, y, _c) in pieces])
+        node2shape[new] = node2shape[node]
+        new.props.update(node.props)
+        replace[node] = new
+        stack = [node]
+        while stack:   # the tree's inner nodes are gone with it
+            q = stack.pop()
+            covered.add(q)
+            if not q.is_input() and isinstance(q.op, core.ElwiseBinary):
+                stack.extend(q.parents)
+    if not replace:
+        return list(outputs), list(updatetargs)
+    return _rewire(outputs, updatetargs, replace)
+
+
 def _row_member(node, node2shape):
     """(R, C) when `node` can live in a FusedRows group over [R, C] rows: an elementwise float32 node of static shape
     [R, C] or [R, 1] (C is None then: it fits any row length), a Sum over axis 1 of an [R, C] node, or the Repeat of
@@ -334,18 +446,47 @@ def fuse_elementwise(outputs, updatetargs, node2shape, rows=False):
     out_set = set(all_out)
     target_set = set(updatetargs)
     replace = {}
+    config_views = core.get_config().get("fuse_slice_views", True)
+
     def emit(mem):
         """One FusedElwise node for `mem` (topologically ordered); a group beyond the kernel's limits is cut in two
         (a prefix and the rest of a topological order cannot need each other both ways) and each part tried again."""
         memset = set(mem)
-        inputs, in_kinds, reg_of = [], [], {}
+        inputs, in_kinds, reg_of, views = [], [], {}, {}
+        group_shape = _static_shape(node2shape[mem[0]])
+
+        def column_view(par):
+            """(matrix, first column, row length) when `par` is a column slice (through reshapes that change nothing)
+            of a static float32 matrix and the group's index space is that slice's [R, W]"""
+            if not config_views or group_shape is None or len(group_shape) != 2 or par.dtype != "f4":
+                return None
+            q = par
+            while not q.is_input() and isinstance(q.op, core.Reshape) and _static_shape(node2shape[q]) == group_shape \
+                    and _static_shape(node2shape[q.parents[0]]) == group_shape:
+                q = q.parents[0]
+            if q.is_input() or not isinstance(q.op, core.GetSli) or q.op.axis != 1 or _static_shape(node2shape[q]) != group_shape:
+                return None
+            (x, start, _stop, step) = q.parents
+            xshp = _static_shape(node2shape[x])
+            if x.dtype != "f4" or xshp is None or len(xshp) != 2 or xshp[0] != group_shape[0]:
+                return None
+            if not (isinstance(start.op, core.Constant) and isinstance(step.op, core.Constant)) or int(step.op.value) != 1:
+                return None
+            first = int(start.op.value)
+            if first < 0 or first + group_shape[1] > xshp[1]:
+                return None
+            return (x, first, xshp[1])
 
         def input_reg(par):
             if par in reg_of:
                 return reg_of[par]
+            view = column_view(par) if par.ndim == 2 else None
             if par.ndim == 0:
                 kind = 2 if par.dtype == "f4" else 3
                 src = par
+            elif view is not None:
+                kind, src = 7, view[0]
+                views[len(inputs)] = (view[1], view[2])
             elif _foldable_repeat(par):
                 # the small operand is read directly; the Repeat node itself stays for whoever else uses it
                 kind, src = 4, par.parents[0]
@@ -386,11 +527,11 @@ def fuse_elementwise(outputs, updatetargs, node2shape, rows=False):
             if kind in (0, 1) and _same_shape(node2shape[src], node2shape[mem[0]]):
                 shape_input = k
                 break
-        if shape_input is None:
+        if shape_input is None and group_shape is None:
             return
         descr = ",".join(str(node.op) for node in mem)
         fop = core.FusedElwise(program, in_kinds, [result_reg[o] for o in outs], [o.dtype for o in outs], mem[0].ndim,
-                               shape_input, descr)
+                               shape_input, descr, views=views, static_shape=group_shape if (views or shape_input is None) else None)
         fnode = core.Result(fop, inputs)
         shp = node2shape[mem[0]]
         if len(outs) == 1:
@@ -811,11 +952,14 @@ def prebuild_fused_kernels(builders):
     for build in builders:
         cfg = build()
         outs, _usrc, utargs, analysis = simplify_for_execution([cfg.loss] + list(cfg.extra_outputs), cfg.updates)
-        o2, u2 = fuse_elementwise(outs, utargs, analysis["node2shape"])
+        o2, u2 = apply_graph_rewrites(outs, utargs, analysis["node2shape"])
         for node in core.topsorted(o2 + u2):
-            if not node.is_input() and isinstance(node.op, core.FusedElwise):
-                if codegen.fused_launcher(node.op):
-                    n += 1
+            if node.is_input():
+                continue
+            if isinstance(node.op, core.FusedElwise) and codegen.fused_launcher(node.op):
+                n += 1
+            if isinstance(node.op, core.FusedRows) and codegen.rows_launcher(node.op):
+                n += 1
     return n
 
 
@@ -1209,14 +1353,18 @@ def merge_parameter_updates(eg, update_locs):
     return eg
 
 
-def run_compilation_pipeline(inputs, outputs, updates, givens):
+def apply_graph_rewrites(outputs_simple, updatetargs_simple, node2shape):
+    """The graph rewrites that run after simplification and differentiation, in their fixed order, each under its
+    configuration switch. Returns the new (outputs, update targets)."""
     config = core.get_config()
-    outputs_simple, updatesrcs, updatetargs_simple, analysis = simplify_for_execution(outputs, updates, givens)
-    node2shape = analysis["node2shape"]
     if config["fuse_conv_dgrad"]:
         outputs_simple, updatetargs_simple = fuse_conv_dgrad(outputs_simple, updatetargs_simple, node2shape)
     if config["fuse_conv_grad_input"]:
         outputs_simple, updatetargs_simple = fuse_conv_grad_input(outputs_simple, updatetargs_simple, node2shape)
+    if config["fuse_slice_views"]:
+        outputs_simple, updatetargs_simple = view_leading_slices(outputs_simple, updatetargs_simple, node2shape)
+    if config["fuse_slice_sums"]:
+        outputs_simple, updatetargs_simple = fuse_slice_sums(outputs_simple, updatetargs_simple, node2shape)
     if config["fuse_elementwise"]:
         if config["fuse_rows"]:
             outputs_simple, updatetargs_simple = fuse_elementwise(outputs_simple, updatetargs_simple, node2shape, rows=True)
@@ -1227,6 +1375,14 @@ def run_compilation_pipeline(inputs, outputs, updates, givens):
             outputs_simple, updatetargs_simple = fuse_conv_implicit(outputs_simple, updatetargs_simple, node2shape)
         if config["pad_conv_columns"]:
             outputs_simple, updatetargs_simple = pad_conv_columns(outputs_simple, updatetargs_simple, node2shape)
+    return outputs_simple, updatetargs_simple
+
+
+def run_compilation_pipeline(inputs, outputs, updates, givens):
+    config = core.get_config()
+    outputs_simple, updatesrcs, updatetargs_simple, analysis = simplify_for_execution(outputs, updates, givens)
+    node2shape = analysis["node2shape"]
+    outputs_simple, updatetargs_simple = apply_graph_rewrites(outputs_simple, updatetargs_simple, node2shape)
     all_out = outputs_simple + updatetargs_simple
 
     nodelist = core.topsorted(all_out)
@@ -1368,7 +1524,7 @@ class ReturnByVal(_Return):
     kindname = "ReturnByVal"
 
 
-_QUICK_OPS = (core.Size, core.Reshape, core.MakeTuple, core.TupleIndex, core.GetData)
+_QUICK_OPS = (core.Size, core.Reshape, core.LeadingSlice, core.MakeTuple, core.TupleIndex, core.GetData)
 
 
 def instr_flags(instr):

@@ -1153,7 +1153,10 @@ class FusedElwise(Op):
     return_type = "byref"
     MAX_IN, MAX_OPS, MAX_OUT = 8, 16, 4
 
-    def __init__(self, program, in_kinds, out_regs, out_dtypes, ndim, shape_input, descr=""):
+    def __init__(self, program, in_kinds, out_regs, out_dtypes, ndim, shape_input, descr="", views=None, static_shape=None):
+        """views: {input index: (first column, row length of the input matrix)} for the inputs of kind 7, which are
+        [R, row length] matrices whose columns [first, first + W) the chain reads (the index space is [R, W] then);
+        static_shape: the result's extents when no input has the result's shape (shape_input None)."""
         assert 1 <= len(in_kinds) <= self.MAX_IN and 1 <= len(program) <= self.MAX_OPS and 1 <= len(out_regs) <= self.MAX_OUT
         self.program = [tuple(p) for p in program]
         self.in_kinds = list(in_kinds)
@@ -1162,12 +1165,20 @@ class FusedElwise(Op):
         self.ndim = ndim
         self.shape_input = shape_input
         self.descr = descr
+        self.views = dict(views or {})
+        self.static_shape = tuple(int(d) for d in static_shape) if static_shape is not None else None
+        assert sorted(self.views) == [k for (k, kind) in enumerate(self.in_kinds) if kind == 7]
+        assert not self.views or (self.static_shape is not None and len(self.static_shape) == 2)
+        assert shape_input is not None or self.static_shape is not None
 
     def get_diff(self, num_inputs):
         return [False] * num_inputs
 
     def shp_apply(self, inputs):
-        shp = cgt.shape(inputs[self.shape_input])
+        if self.shape_input is not None:
+            shp = cgt.shape(inputs[self.shape_input])
+        else:
+            shp = [cgt.constant(np.array(d, "i8")) for d in self.static_shape]
         return shp if len(self.out_regs) == 1 else tuple(list(shp) for _ in self.out_regs)
 
     def typ_apply(self, input_types):
@@ -1178,6 +1189,9 @@ class FusedElwise(Op):
         def arr(vals, n):
             vals = list(vals) + [0] * (n - len(vals))
             return (ctypes.c_int * n)(*vals)
+        def larr(vals):
+            vals = list(vals) + [0] * (self.MAX_IN - len(vals))
+            return (ctypes.c_long * self.MAX_IN)(*vals)
         code = {"f4": 11, "i1": 1}
         return NativeCompileInfo(None, prebuilt="cgtb_op_fused_elwise", closure_triples=[
             ("n_in", ctypes.c_int, len(self.in_kinds)),
@@ -1190,7 +1204,10 @@ class FusedElwise(Op):
             ("op_b", ctypes.c_int * self.MAX_OPS, arr([p[3] for p in self.program], self.MAX_OPS)),
             ("out_reg", ctypes.c_int * self.MAX_OUT, arr(self.out_regs, self.MAX_OUT)),
             ("out_dtype", ctypes.c_int * self.MAX_OUT, arr([code[d] for d in self.out_dtypes], self.MAX_OUT)),
-            ("launcher", ctypes.c_void_p, self._launcher())])
+            ("launcher", ctypes.c_void_p, self._launcher()),
+            ("view_width", ctypes.c_long, self.static_shape[1] if self.views else 0),
+            ("view_pitch", ctypes.c_long * self.MAX_IN, larr([self.views.get(k, (0, 0))[1] for k in range(len(self.in_kinds))])),
+            ("view_off", ctypes.c_long * self.MAX_IN, larr([self.views.get(k, (0, 0))[0] for k in range(len(self.in_kinds))]))])
 
     def _launcher(self):
         from . import codegen
@@ -1217,11 +1234,49 @@ class MultiFusedElwise(Op):
 
     def get_native_compile_info(self, input_types, devtype):
         triples = list(self.fused.get_native_compile_info(input_types, devtype).closure_triples)
-        triples = [t for t in triples if t[0] != "launcher"] + [("launcher", ctypes.c_void_p, None), ("k", ctypes.c_int, self.k)]
+        triples = [t for t in triples if t[0] not in ("launcher", "view_width", "view_pitch", "view_off")]
+        triples += [("launcher", ctypes.c_void_p, None), ("view_width", ctypes.c_long, 0), ("k", ctypes.c_int, self.k)]
         return NativeCompileInfo(None, prebuilt="cgtb_op_multi_fused_elwise", closure_triples=triples)
 
     def __repr__(self):
         return "MultiFusedElwise{%d x %s}" % (self.k, self.fused.descr)
+
+
+class ScatterCols(Op):
+    """(y_0, ..., y_{k-1}) -> [R, C] matrix of zeros with y_j ([R, width_j]) in columns [offset_j, offset_j + width_j).
+
+    Not part of the reference's Op set: compilation.fuse_slice_sums forms it from a sum of IncSli(zeros, ...) over
+    disjoint column ranges, which is how the gradient of several column slices of one matrix arrives after
+    differentiation (GetSli.pullback, cgt/core.py:1786-1790): k zero fills, k slice increments and k-1 additions
+    become one launch with the same values."""
+    available_impls = ("native_gpu",)
+    return_type = "byref"
+
+    def __init__(self, offsets, widths, C):
+        assert 1 <= len(offsets) <= 8 and len(offsets) == len(widths)
+        self.offsets = [int(o) for o in offsets]
+        self.widths = [int(w) for w in widths]
+        self.C = int(C)
+
+    def get_diff(self, num_inputs):
+        return [False] * num_inputs
+
+    def shp_apply(self, inputs):
+        return [cgt.size(inputs[0], 0), cgt.constant(np.array(self.C, "i8"))]
+
+    def typ_apply(self, input_types):
+        return TensorType("f4", 2)
+
+    def get_native_compile_info(self, input_types, devtype):
+        def arr(vals):
+            vals = list(vals) + [0] * (8 - len(vals))
+            return (ctypes.c_long * 8)(*vals)
+        return NativeCompileInfo(None, prebuilt="cgtb_op_scatter_cols", closure_triples=[
+            ("k", ctypes.c_int, len(self.offsets)), ("C", ctypes.c_long, self.C),
+            ("off", ctypes.c_long * 8, arr(self.offsets)), ("width", ctypes.c_long * 8, arr(self.widths))])
+
+    def __repr__(self):
+        return "ScatterCols{%s of %d}" % (",".join("%d:%d" % (o, o + w) for (o, w) in zip(self.offsets, self.widths)), self.C)
 
 
 class FusedRows(Op):
@@ -1277,7 +1332,12 @@ class FusedRows(Op):
             ("op_b", ctypes.c_int * F.MAX_OPS, arr([p[3] for p in self.program], F.MAX_OPS)),
             ("out_reg", ctypes.c_int * F.MAX_OUT, arr(self.out_regs, F.MAX_OUT)),
             ("out_col", ctypes.c_int * F.MAX_OUT, arr(self.out_cols, F.MAX_OUT)),
+            ("launcher", ctypes.c_void_p, self._launcher()),
             ("C", ctypes.c_int, self.C)])
+
+    def _launcher(self):
+        from . import codegen
+        return codegen.rows_launcher(self)
 
     def __repr__(self):
         return "FusedRows{%s}" % self.descr
@@ -1369,6 +1429,40 @@ class Reshape(Op):
     def get_native_compile_info(self, input_types, devtype):
         return NativeCompileInfo(None, prebuilt="cgtb_op_reshape",
                                  closure_triples=[("ndim", ctypes.c_int, len(input_types) - 1)])
+
+
+class LeadingSlice(Op):
+    """(x, start, stop) -> view of x[start:stop] along axis 0; no data movement: the rows of a C-contiguous array are
+    contiguous, so the slice is the same memory at an offset. The compiler (compilation.view_leading_slices) puts it in
+    place of GetSli{0} with step 1 (cgt/core.py:1767-1812), which copies: x[t] of a [T, batch, features] sequence is
+    taken once per time step of an unrolled recurrent network. The view retains its source."""
+    available_impls = ("python", "native_cpu", "native_gpu")
+    return_type = "byval"
+
+    def get_diff(self, num_inputs):
+        return [False] * num_inputs
+
+    def get_py_func(self, input_types):
+        def f(reads):
+            return np.ascontiguousarray(np.asarray(reads[0])[int(reads[1]):int(reads[2])])
+        return f
+
+    def shp_apply(self, inputs):
+        s = cgt.shape(inputs[0])
+        s[0] = inputs[2] - inputs[1]
+        return s
+
+    def typ_apply(self, input_types):
+        return input_types[0]
+
+    def host_inputs(self, n):
+        return (1, 2)
+
+    def get_native_compile_info(self, input_types, devtype):
+        return NativeCompileInfo(None, prebuilt="cgtb_op_leading_slice", closure_triples=[])
+
+    def __repr__(self):
+        return "LeadingSlice"
 
 
 class Concatenate(Op):
@@ -2173,7 +2267,7 @@ _DEFAULTS = dict(
     debug=False, precision="single", backend="native", cache_dir="~/.cgt_b200_cache", enable_inplace_opt=True,
     enable_simplification=True, parallel=False, num_threads=1, force_python_impl=False, debug_cpp=False, verbose=False,
     # additions for this backend
-    devtype="gpu", device_index=0, use_cuda_graphs=True, fuse_elementwise=True, jit_fused_elementwise=True, fuse_conv_dgrad=True, fuse_conv_output=True, fuse_conv_grad_input=True, fuse_conv_implicit=True, merge_parameter_updates=True, fuse_rows=True,
+    devtype="gpu", device_index=0, use_cuda_graphs=True, fuse_elementwise=True, jit_fused_elementwise=True, fuse_conv_dgrad=True, fuse_conv_output=True, fuse_conv_grad_input=True, fuse_conv_implicit=True, merge_parameter_updates=True, fuse_rows=True, fuse_slice_sums=True, fuse_slice_views=True,
     pad_conv_columns=True, profile=False,
 )
 

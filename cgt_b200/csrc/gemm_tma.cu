@@ -471,6 +471,53 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       __syncwarp();
     }
     if (!ok && lane == 0) { *abortp = 1; *(volatile int*)p.err = 4; __threadfence_system(); }
+  } else if (CONV == 2) {
+    // ------------------------------------------------ TMA producer of the filter-gradient product (one warp)
+    // A K block of this product is five boxes (four shifted windows of the source, one of the gradient), and one
+    // thread needs some 400 cycles to issue a 4-D box: issued by one thread, the loads, not the tensor core, set the
+    // pace of the loop. Here lane u issues box u; lane 0 alone waits for the stage and arms its barrier.
+    long issued = 0;
+    bool ok = true;
+    int rs = 0;
+    uint32_t rphase = 0;
+    for (long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+      const Tile c = tile_of(p, t);
+      const long y0 = (long)c.yt * UN;
+      for (int kb = 0; kb < c.nkb; ++kb) {
+        if (lane == 0) ok = mbar_wait_or_abort(smem_u32(&raw_empty[rs]), rphase ^ 1u, abortp);
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        if (!ok) break;
+        if (lane == 0) TRACE((int)issued, 0);
+        const uint32_t bar = smem_u32(&raw_full[rs]);
+        const int k0 = (int)(c.k_begin + (long)kb * kBK);
+        const uint32_t dx = smem_u32(raw0 + (size_t)rs * raw_bytes);
+        const int gkb = k0 / kBK;
+        const int b = gkb / p.wnrg, yrow0 = (gkb - b * p.wnrg) * p.wbh;
+        int nunits = p.wunits - c.xt * 4;
+        nunits = nunits > 4 ? 4 : nunits;
+        const uint32_t px_bytes = (uint32_t)p.wnpx * 128u;
+        if (lane == 0) mbar_arrive_expect_tx(bar, (uint32_t)nunits * px_bytes + (uint32_t)p.wnpx * (uint32_t)UN * 4u);
+        __syncwarp();
+        if (lane < nunits) {
+          const int unit = c.xt * 4 + lane;
+          const int tap = unit / p.ckpt, q = unit - tap * p.ckpt;
+          const int ti = tap / p.ckw, tj = tap - ti * p.ckw;
+          tma_load_4d(dx + (uint32_t)lane * 4096u, &mapX, 32 * q, tj - p.cpw, yrow0 + ti - p.cph, b, bar);
+        } else if (lane == nunits) {
+          tma_load_4d(dx + x_bytes, &mapY, (int)y0, 0, yrow0, b, bar);
+        }
+        __syncwarp();
+        ++issued;
+        if (++rs == RS) { rs = 0; rphase ^= 1u; }
+      }
+    }
+    if (lane == 0 && (!ok || *abortp)) {
+      *abortp = 1;
+      *(volatile int*)p.err = 5;
+      __threadfence_system();
+      // copies already issued still write this CTA's shared memory: wait (bounded) until they have landed
+      for (long j = (issued > RS ? issued - RS : 0); j < issued; ++j) mbar_wait(smem_u32(&raw_full[j % RS]), (uint32_t)(j / RS) & 1u);
+    }
   } else if (lane == 0) {
     // ------------------------------------------------ TMA producer (one thread)
     long issued = 0;
@@ -499,21 +546,6 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
           const int yrow0 = p.cnimg > 1 ? 0 : (tile - b0 * p.cnbands) * p.crows;
           tma_load_4d(dx, &mapX, 32 * q, p.csign * (tj - p.cpw), yrow0 + p.csign * (ti - p.cph), b0, bar);
           tma_load_3d(dx + x_bytes, &mapY, k0, (int)y0, c.batch, bar);
-        } else if (CONV == 2) {
-          // K block = wbh rows of image b; X = the same pixels of the source shifted by each of the tile's taps
-          const int gkb = k0 / kBK;
-          const int b = gkb / p.wnrg, yrow0 = (gkb - b * p.wnrg) * p.wbh;
-          int nunits = p.wunits - c.xt * 4;
-          nunits = nunits > 4 ? 4 : nunits;
-          const uint32_t px_bytes = (uint32_t)p.wnpx * 128u;
-          mbar_arrive_expect_tx(bar, (uint32_t)nunits * px_bytes + (uint32_t)p.wnpx * (uint32_t)UN * 4u);
-          for (int u = 0; u < nunits; ++u) {
-            const int unit = c.xt * 4 + u;
-            const int tap = unit / p.ckpt, q = unit - tap * p.ckpt;
-            const int ti = tap / p.ckw, tj = tap - ti * p.ckw;
-            tma_load_4d(dx + (uint32_t)u * 4096u, &mapX, 32 * q, tj - p.cpw, yrow0 + ti - p.cph, b, bar);
-          }
-          tma_load_4d(dx + x_bytes, &mapY, (int)y0, 0, yrow0, b, bar);
         } else {
           mbar_arrive_expect_tx(bar, raw_bytes);
           if (XMN) tma_load_3d(dx, &mapX, (int)x0, k0, c.batch, bar);

@@ -167,6 +167,12 @@ __global__ void fused_elwise_kernel(const FusedArgs a) {
 #pragma unroll
           for (int v = 0; v < V; ++v) r[k][v] = s;
         } break;
+        case CGTB_FIN_VIEW_F4: {  // columns [binner, binner + W) of a matrix with rows of bk elements
+          const long W = P.view_width, row = (i * V) / W, col = i * V - row * W;
+          Pack<float, V> p = load_pack<float, V>((const float*)a.in[k] + row * a.bk[k] + a.binner[k] + col);
+#pragma unroll
+          for (int v = 0; v < V; ++v) r[k][v] = p.v[v];
+        } break;
         default: {  // broadcast: one value per pack when the run length is a multiple of V, else one index per element
           const float* src = (const float*)a.in[k];
           if (a.binner[k] % V == 0) {
@@ -225,8 +231,16 @@ CGTB_API int cgtb_fused_elwise(const cgtbFusedProgram* prog, long n, const void*
     a.in[k] = in[k];
     a.bk[k] = a.binner[k] = 1;
     const int kind = prog->in_kind[k];
-    if (kind < CGTB_FIN_F4 || kind > CGTB_FIN_BCAST_F4) return fail("cgtb_fused_elwise: bad input kind %d", kind);
+    if ((kind < CGTB_FIN_F4 || kind > CGTB_FIN_BCAST_F4) && kind != CGTB_FIN_VIEW_F4) return fail("cgtb_fused_elwise: bad input kind %d", kind);
     if (kind == CGTB_FIN_F4) vec = vec && aligned16(in[k]);
+    if (kind == CGTB_FIN_VIEW_F4) {
+      const long W = prog->view_width;
+      if (W <= 0 || n % W != 0 || !bcast_k || !bcast_inner || bcast_inner[k] < 0 || bcast_inner[k] + W > bcast_k[k])
+        return fail("cgtb_fused_elwise: input %d is not a column range of width %ld inside its matrix", k, W);
+      a.bk[k] = bcast_k[k];
+      a.binner[k] = bcast_inner[k];
+      vec = vec && aligned16(in[k]) && W % kVec == 0 && bcast_k[k] % kVec == 0 && bcast_inner[k] % kVec == 0;
+    }
     if (kind == CGTB_FIN_I1) vec = vec && (((uintptr_t)in[k] & 3) == 0);
     if (kind == CGTB_FIN_BCAST_F4) {
       if (!bcast_k || !bcast_inner || bcast_k[k] <= 0 || bcast_inner[k] <= 0) return fail("cgtb_fused_elwise: bad broadcast extents");
@@ -454,12 +468,63 @@ CGTB_API int cgtb_fused_rows(const cgtbRowProgram* prog, long R, long C, const v
   a.C = C;
   for (int k = 0; k < prog->n_in; ++k) a.in[k] = in[k];
   for (int j = 0; j < prog->n_out; ++j) a.out[j] = out[j];
+  if (prog->launcher) {
+    // a kernel generated for exactly this program (same scalar templates, values in registers)
+    typedef int (*Launcher)(long, long, const void* const*, void* const*, void*);
+    if (((Launcher)prog->launcher)(R, C, a.in, a.out, (void*)rt().stream)) return fail("cgtb_fused_rows: the generated kernel failed to launch");
+    g_kernel_launches.fetch_add(1, std::memory_order_relaxed);
+    return 0;
+  }
   const int warps = 4;
   const unsigned blocks = (unsigned)cgtb_ceil_div(R, warps);
   if (C <= 32) CGTB_LAUNCH(fused_rows_kernel<1>, blocks, warps * 32, 0, a);
   else if (C <= 64) CGTB_LAUNCH(fused_rows_kernel<2>, blocks, warps * 32, 0, a);
   else CGTB_LAUNCH(fused_rows_kernel<4>, blocks, warps * 32, 0, a);
   CGTB_CHECK_LAUNCH("fused_rows");
+  return 0;
+}
+
+// Column pieces placed into a zero matrix (the sum of padded slices that the gradient of column slices is).
+constexpr int kScatterMax = 8;
+struct ScatterArgs {
+  long R, C;
+  int k;
+  long off[kScatterMax], width[kScatterMax];
+  const float* piece[kScatterMax];
+  float* out;
+};
+__global__ void scatter_cols_kernel(const ScatterArgs a) {
+  const long n = a.R * a.C;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    const long r = i / a.C, c = i - r * a.C;
+    float v = 0.f;
+    for (int j = 0; j < a.k; ++j) {
+      const long d = c - a.off[j];
+      if (d >= 0 && d < a.width[j]) { v = a.piece[j][r * a.width[j] + d]; break; }
+    }
+    a.out[i] = v;
+  }
+}
+CGTB_API int cgtb_scatter_cols(long R, long C, int k, const long* offset, const long* width, const void* const* pieces, void* out) {
+  if (!require_runtime("cgtb_scatter_cols")) return 1;
+  if (k < 1 || k > kScatterMax) return fail("cgtb_scatter_cols: between 1 and %d pieces", kScatterMax);
+  if (R <= 0 || C <= 0) return 0;
+  ScatterArgs a;
+  a.R = R;
+  a.C = C;
+  a.k = k;
+  a.out = (float*)out;
+  for (int j = 0; j < k; ++j) {
+    if (offset[j] < 0 || width[j] < 0 || offset[j] + width[j] > C) return fail("cgtb_scatter_cols: piece %d lies outside the %ld columns", j, C);
+    for (int q = 0; q < j; ++q)
+      if (offset[j] < a.off[q] + a.width[q] && a.off[q] < offset[j] + width[j]) return fail("cgtb_scatter_cols: pieces %d and %d overlap", q, j);
+    a.off[j] = offset[j];
+    a.width[j] = width[j];
+    a.piece[j] = (const float*)pieces[j];
+  }
+  const unsigned blocks = (unsigned)std::min<long>(cgtb_ceil_div(R * C, 256), 8L * rt().sm_count);
+  CGTB_LAUNCH(scatter_cols_kernel, blocks, 256, 0, a);
+  CGTB_CHECK_LAUNCH("scatter_cols");
   return 0;
 }
 

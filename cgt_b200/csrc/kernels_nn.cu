@@ -7,6 +7,7 @@
 // added in the same sequence.
 #include "runtime.h"
 #include <cfloat>
+#include <initializer_list>
 #include <type_traits>
 
 using namespace cgtb;
@@ -616,6 +617,161 @@ __global__ void lrn_backward_kernel(const T* __restrict__ x, const T* __restrict
   gx[idx] = gtop[idx] * pow(scale[idx], negative_beta) - cache_ratio * x[idx] * acc;
 }
 
+// float32 with the channel window staged in shared memory: a block takes kLrnTP consecutive pixels of one image for
+// ALL channels, reads every input element from global memory once (runs of consecutive pixels per channel, several
+// loads per thread in flight; 128-bit when the plane size allows), forms the window sums from the staged tile and
+// writes its results as the same runs. Same operations in the same order as the kernels above: same bits.
+// V = elements per access (4: HW a multiple of four and 16-byte aligned arrays).
+constexpr int kLrnTP = 64;
+template <int V>
+__global__ void __launch_bounds__(256) lrn_forward_tile_kernel(const float* __restrict__ x, float* __restrict__ top, float* __restrict__ scale,
+                                                             int C, int HW, int size, float alpha_over_size, float negative_beta) {
+  extern __shared__ float sx[];  // [C][kLrnTP]
+  constexpr int PT = kLrnTP / V;           // threads along the pixels of a tile
+  constexpr int CSTEP = 256 / PT;          // channels covered by one pass of the block
+  const int pre = (size - 1) / 2, post = size - pre - 1;
+  const int p = (threadIdx.x % PT) * V, c0 = threadIdx.x / PT;
+  const int p0 = blockIdx.x * kLrnTP;
+  const size_t base = (size_t)blockIdx.y * C * HW + p0 + p;
+  const bool live = p0 + p < HW;   // with V = 4 a group of four is inside the plane or outside it as a whole
+  for (int cb = c0; cb < C; cb += 8 * CSTEP) {
+    float v[8][V];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int c = cb + u * CSTEP;
+#pragma unroll
+      for (int q = 0; q < V; ++q) v[u][q] = 0.f;
+      if (c < C && live) {
+        if (V == 4) {
+          const float4 t = *reinterpret_cast<const float4*>(x + base + (size_t)c * HW);
+          v[u][0] = t.x; v[u][1 % V] = t.y; v[u][2 % V] = t.z; v[u][3 % V] = t.w;
+        } else {
+          v[u][0] = x[base + (size_t)c * HW];
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int c = cb + u * CSTEP;
+      if (c < C) {
+#pragma unroll
+        for (int q = 0; q < V; ++q) sx[c * kLrnTP + p + q] = v[u][q];
+      }
+    }
+  }
+  __syncthreads();
+  if (!live) return;
+  for (int c = c0; c < C; c += CSTEP) {
+    const int lo = max(c - pre, 0), hi = min(c + post, C - 1);
+    float acc[V], s[V], y[V];
+#pragma unroll
+    for (int q = 0; q < V; ++q) acc[q] = 0.f;
+    for (int k = lo; k <= hi; ++k) {
+#pragma unroll
+      for (int q = 0; q < V; ++q) {
+        const float t = sx[k * kLrnTP + p + q];
+        acc[q] += t * t;
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < V; ++q) {
+      s[q] = (float)(1. + (double)(acc[q] * alpha_over_size));
+      y[q] = sx[c * kLrnTP + p + q] * pow(s[q], negative_beta);
+    }
+    const size_t o = base + (size_t)c * HW;
+    if (V == 4) {
+      *reinterpret_cast<float4*>(scale + o) = make_float4(s[0], s[1 % V], s[2 % V], s[3 % V]);
+      *reinterpret_cast<float4*>(top + o) = make_float4(y[0], y[1 % V], y[2 % V], y[3 % V]);
+    } else {
+      scale[o] = s[0];
+      top[o] = y[0];
+    }
+  }
+}
+
+template <int V>
+__global__ void __launch_bounds__(256) lrn_backward_tile_kernel(const float* __restrict__ x, const float* __restrict__ top,
+                                                              const float* __restrict__ scale, const float* __restrict__ gtop,
+                                                              float* __restrict__ gx, int C, int HW, int size, float negative_beta,
+                                                              float cache_ratio) {
+  extern __shared__ float sr[];  // [C][kLrnTP]: gtop * top / scale
+  constexpr int PT = kLrnTP / V;
+  constexpr int CSTEP = 256 / PT;
+  const int pre = size - (size + 1) / 2, post = size - pre - 1;
+  const int p = (threadIdx.x % PT) * V, c0 = threadIdx.x / PT;
+  const int p0 = blockIdx.x * kLrnTP;
+  const size_t base = (size_t)blockIdx.y * C * HW + p0 + p;
+  const bool live = p0 + p < HW;
+  for (int cb = c0; cb < C; cb += 4 * CSTEP) {
+    float g[4][V], t[4][V], sc[4][V];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int c = cb + u * CSTEP;
+#pragma unroll
+      for (int q = 0; q < V; ++q) { g[u][q] = 0.f; t[u][q] = 0.f; sc[u][q] = 1.f; }
+      if (c < C && live) {
+        const size_t o = base + (size_t)c * HW;
+        if (V == 4) {
+          const float4 a = *reinterpret_cast<const float4*>(gtop + o), b = *reinterpret_cast<const float4*>(top + o),
+                       d = *reinterpret_cast<const float4*>(scale + o);
+          g[u][0] = a.x; g[u][1 % V] = a.y; g[u][2 % V] = a.z; g[u][3 % V] = a.w;
+          t[u][0] = b.x; t[u][1 % V] = b.y; t[u][2 % V] = b.z; t[u][3 % V] = b.w;
+          sc[u][0] = d.x; sc[u][1 % V] = d.y; sc[u][2 % V] = d.z; sc[u][3 % V] = d.w;
+        } else {
+          g[u][0] = gtop[o]; t[u][0] = top[o]; sc[u][0] = scale[o];
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int c = cb + u * CSTEP;
+      if (c < C) {
+#pragma unroll
+        for (int q = 0; q < V; ++q) sr[c * kLrnTP + p + q] = g[u][q] * t[u][q] / sc[u][q];
+      }
+    }
+  }
+  __syncthreads();
+  if (!live) return;
+  for (int c = c0; c < C; c += CSTEP) {
+    const int lo = max(c - pre, 0), hi = min(c + post, C - 1);
+    const size_t o = base + (size_t)c * HW;
+    // this thread's own elements again: they were read a moment ago and come from the cache
+    float g[V], sc[V], xv[V], acc[V], r[V];
+    if (V == 4) {
+      const float4 a = *reinterpret_cast<const float4*>(gtop + o), d = *reinterpret_cast<const float4*>(scale + o),
+                   e = *reinterpret_cast<const float4*>(x + o);
+      g[0] = a.x; g[1 % V] = a.y; g[2 % V] = a.z; g[3 % V] = a.w;
+      sc[0] = d.x; sc[1 % V] = d.y; sc[2 % V] = d.z; sc[3 % V] = d.w;
+      xv[0] = e.x; xv[1 % V] = e.y; xv[2 % V] = e.z; xv[3 % V] = e.w;
+    } else {
+      g[0] = gtop[o]; sc[0] = scale[o]; xv[0] = x[o];
+    }
+#pragma unroll
+    for (int q = 0; q < V; ++q) acc[q] = 0.f;
+    for (int k = lo; k <= hi; ++k) {
+#pragma unroll
+      for (int q = 0; q < V; ++q) acc[q] += sr[k * kLrnTP + p + q];
+    }
+#pragma unroll
+    for (int q = 0; q < V; ++q) r[q] = g[q] * pow(sc[q], negative_beta) - cache_ratio * xv[q] * acc[q];
+    if (V == 4) *reinterpret_cast<float4*>(gx + o) = make_float4(r[0], r[1 % V], r[2 % V], r[3 % V]);
+    else gx[o] = r[0];
+  }
+}
+
+static bool lrn_tile_ok(long N, int C) { return N <= 65535 && (size_t)C * kLrnTP * sizeof(float) <= 200 * 1024; }
+static bool lrn_vec4(int HW, std::initializer_list<const void*> ptrs) {
+  if (HW % 4 != 0) return false;
+  for (const void* q : ptrs) if (((uintptr_t)q & 15) != 0) return false;
+  return true;
+}
+template <typename K>
+static int lrn_smem_attr(K kernel, size_t smem) {
+  if (smem > 48 * 1024) CGTB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  return 0;
+}
+
 CGTB_API int cgtb_lrn_forward(int dtype, const void* x, long N, int C, int H, int W, int size, double alpha, double beta,
                               void* top, void* scale) {
   if (!require_runtime("cgtb_lrn_forward")) return 1;
@@ -624,6 +780,21 @@ CGTB_API int cgtb_lrn_forward(int dtype, const void* x, long N, int C, int H, in
   if (total <= 0) return 0;
   if (N > 65535 || C > 65535 || (long)C * H * W >= (1L << 31)) return fail("cgtb_lrn_forward: extents too large");
   const int HW = H * W;
+  if (dtype == cgtb_f4 && lrn_tile_ok(N, C)) {
+    const size_t smem = (size_t)C * kLrnTP * sizeof(float);
+    dim3 tgrid((unsigned)cgtb_ceil_div(HW, kLrnTP), (unsigned)N);
+    if (lrn_vec4(HW, {x, top, scale})) {
+      if (lrn_smem_attr(lrn_forward_tile_kernel<4>, smem)) return 1;
+      CGTB_LAUNCH(lrn_forward_tile_kernel<4>, tgrid, 256, smem, (const float*)x, (float*)top, (float*)scale, C, HW, size,
+                  (float)(alpha / size), (float)(-beta));
+    } else {
+      if (lrn_smem_attr(lrn_forward_tile_kernel<1>, smem)) return 1;
+      CGTB_LAUNCH(lrn_forward_tile_kernel<1>, tgrid, 256, smem, (const float*)x, (float*)top, (float*)scale, C, HW, size,
+                  (float)(alpha / size), (float)(-beta));
+    }
+    CGTB_CHECK_LAUNCH("lrn_forward");
+    return 0;
+  }
   const int threads = HW >= 256 ? 256 : (HW >= 128 ? 128 : 64);
   dim3 grid((unsigned)cgtb_ceil_div(HW, threads), (unsigned)C, (unsigned)N);
   if (dtype == cgtb_f4)
@@ -646,6 +817,21 @@ CGTB_API int cgtb_lrn_backward(int dtype, const void* x, const void* top, const 
   if (total <= 0) return 0;
   if (N > 65535 || C > 65535 || (long)C * H * W >= (1L << 31)) return fail("cgtb_lrn_backward: extents too large");
   const int HW = H * W;
+  if (dtype == cgtb_f4 && lrn_tile_ok(N, C)) {
+    const size_t smem = (size_t)C * kLrnTP * sizeof(float);
+    dim3 tgrid((unsigned)cgtb_ceil_div(HW, kLrnTP), (unsigned)N);
+    if (lrn_vec4(HW, {x, top, scale, gtop, gx})) {
+      if (lrn_smem_attr(lrn_backward_tile_kernel<4>, smem)) return 1;
+      CGTB_LAUNCH(lrn_backward_tile_kernel<4>, tgrid, 256, smem, (const float*)x, (const float*)top, (const float*)scale,
+                  (const float*)gtop, (float*)gx, C, HW, size, (float)(-beta), (float)(2. * alpha * beta / size));
+    } else {
+      if (lrn_smem_attr(lrn_backward_tile_kernel<1>, smem)) return 1;
+      CGTB_LAUNCH(lrn_backward_tile_kernel<1>, tgrid, 256, smem, (const float*)x, (const float*)top, (const float*)scale,
+                  (const float*)gtop, (float*)gx, C, HW, size, (float)(-beta), (float)(2. * alpha * beta / size));
+    }
+    CGTB_CHECK_LAUNCH("lrn_backward");
+    return 0;
+  }
   const int threads = HW >= 256 ? 256 : (HW >= 128 ? 128 : 64);
   dim3 grid((unsigned)cgtb_ceil_div(HW, threads), (unsigned)C, (unsigned)N);
   if (dtype == cgtb_f4)

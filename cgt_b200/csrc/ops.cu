@@ -176,10 +176,29 @@ OP_BYREF(cgtb_op_fused_rows) {
   cgtb_fused_rows(&P, R, C, in, out);
 }
 
+// ScatterCols: k column pieces placed into a zero matrix. Closure: k, C, offsets, widths; reads = the pieces.
+struct ScatterColsClosure { int k; long C; long off[8]; long width[8]; };
+OP_BYREF(cgtb_op_scatter_cols) {
+  const ScatterColsClosure* cl = (const ScatterColsClosure*)cl0;
+  cgtArray* w = ARR(write0);
+  if (cl->k < 1 || cl->k > 8) { fail("ScatterCols: between 1 and 8 pieces"); return; }
+  if (!on_gpu(w) || w->dtype() != cgt_f4 || w->ndim() != 2 || w->shape()[1] != cl->C) { fail("ScatterCols: the result must be a float32 GPU matrix with %ld columns", cl->C); return; }
+  const long R = w->shape()[0];
+  const void* pieces[8];
+  for (int j = 0; j < cl->k; ++j) {
+    cgtArray* y = ARR(reads[j]);
+    if (!on_gpu(y) || y->dtype() != cgt_f4 || y->size() != R * cl->width[j]) { fail("ScatterCols: piece %d is not a float32 GPU array of %ld x %ld", j, R, cl->width[j]); return; }
+    pieces[j] = y->data();
+  }
+  cgtb_scatter_cols(R, cl->C, cl->k, cl->off, cl->width, pieces, w->data());
+}
+
 // MultiFusedElwise: one FusedElwise program over k independent tensors in one launch. The closure is the program
 // followed by k; reads = the k operand lists back to back (n_in each), then the result arrays of tensors 1..k-1
 // (the instruction's own write location is tensor 0's result). The compiler forms it from k parameter updates.
 struct MultiFusedClosure { cgtbFusedProgram prog; int k; };
+// FusedElwise: the program, then for every CGTB_FIN_VIEW_F4 input the row length of its matrix and its first column
+struct FusedClosure { cgtbFusedProgram prog; long view_pitch[CGTB_FUSED_MAX_IN]; long view_off[CGTB_FUSED_MAX_IN]; };
 OP_BYREF(cgtb_op_multi_fused_elwise) {
   const MultiFusedClosure* cl = (const MultiFusedClosure*)cl0;
   const int k = cl->k, n_in = cl->prog.n_in;
@@ -228,6 +247,16 @@ OP_BYREF(cgtb_op_fused_elwise) {
     if ((kind == CGTB_FIN_F4 || kind == CGTB_FIN_I1) && x->size() != n) {
       fail("Shape error in a fused elementwise chain. You might be missing a call to cgt.broadcast(...)");
       return;
+    }
+    if (kind == CGTB_FIN_VIEW_F4) {
+      const FusedClosure* fc = (const FusedClosure*)cl0;
+      const long W = prog->view_width;
+      if (W <= 0 || n % W != 0 || x->dtype() != cgt_f4 || x->size() != (n / W) * fc->view_pitch[k]) {
+        fail("FusedElwise: operand %d is not the [%ld, %ld] matrix whose columns the chain reads", k, W > 0 ? n / W : 0, fc->view_pitch[k]);
+        return;
+      }
+      bk[k] = fc->view_pitch[k];
+      binner[k] = fc->view_off[k];
     }
     if (kind == CGTB_FIN_BCAST_F4) {
       if (x->ndim() != w->ndim()) { fail("FusedElwise: a broadcast operand must have the rank of the result"); return; }
@@ -527,6 +556,18 @@ OP_BYREF(cgtb_op_incflat) {
   if (!all_gpu({x, k, p, w})) { fail("IncFlatIndices: operands must be on the GPU"); return; }
   if (k->dtype() != cgt_i8) { fail("IncFlatIndices: indices must be int64"); return; }
   cgtb_incflat(x->dtype(), x->size(), p->size(), x->data(), (const int64_t*)k->data(), p->data(), w->data());
+}
+OP_BYVAL(cgtb_op_leading_slice) {  // rows [start, stop) of a C-contiguous array as a view that retains its source
+  cgtArray* in = ARR(reads[0]);
+  const long start = host_i8(reads[1]), stop = host_i8(reads[2]);
+  if (in->ndim() < 1 || in->ndim() > CGTB_MAX_NDIM) { fail("LeadingSlice: needs an array of 1 to %d axes", CGTB_MAX_NDIM); return nullptr; }
+  if (start < 0 || stop < start || stop > in->shape()[0]) { fail("LeadingSlice: rows [%ld, %ld) outside the %ld rows of the array", start, stop, in->shape()[0]); return nullptr; }
+  long shape[CGTB_MAX_NDIM], row = 1;
+  for (int i = 0; i < in->ndim(); ++i) shape[i] = in->shape()[i];
+  for (int i = 1; i < in->ndim(); ++i) row *= shape[i];
+  shape[0] = stop - start;
+  char* base = (char*)in->data() + (size_t)start * (size_t)row * (size_t)cgt_itemsize(in->dtype());
+  return new cgtArray(in->ndim(), shape, in->dtype(), in->devtype(), base, (cgtObject*)in);
 }
 struct ConcatClosure { int axis; int n_in; };
 OP_BYREF(cgtb_op_concatenate) {

@@ -242,7 +242,8 @@ int cgtb_binary(int op, int dt_x, int dt_y, int dt_out, long n, const void* x, c
 #define CGTB_FUSED_MAX_IN 8
 #define CGTB_FUSED_MAX_OPS 16
 #define CGTB_FUSED_MAX_OUT 4
-enum { CGTB_FIN_F4 = 0, CGTB_FIN_I1 = 1, CGTB_FIN_SCALAR_F4 = 2, CGTB_FIN_SCALAR_I8 = 3, CGTB_FIN_BCAST_F4 = 4 };
+enum { CGTB_FIN_F4 = 0, CGTB_FIN_I1 = 1, CGTB_FIN_SCALAR_F4 = 2, CGTB_FIN_SCALAR_I8 = 3, CGTB_FIN_BCAST_F4 = 4,
+       CGTB_FIN_VIEW_F4 = 7 /* columns of a wider float32 matrix, see cgtb_fused_elwise; 5 and 6 belong to cgtbRowProgram */ };
 typedef struct {
   int n_in, n_ops, n_out;
   int in_kind[CGTB_FUSED_MAX_IN];    /* CGTB_FIN_*; a scalar is a 0-d array in device memory */
@@ -255,10 +256,14 @@ typedef struct {
    * generated for this program: int f(long n, const void* const* in, const long* bcast_k,
    * const long* bcast_inner, void* const* out, int vectorised, void* stream, int sm_count), 0 on success. */
   void* launcher;
+  long view_width;                   /* row length of the index space; read only when an input is a CGTB_FIN_VIEW_F4 */
 } cgtbFusedProgram;
 /* in[k]: device pointer of input k. A CGTB_FIN_BCAST_F4 input holds bcast_k[k] values; element i of the
  * index space reads value (i / bcast_inner[k]) % bcast_k[k] (a bias [1,C,1,1] over [B,C,H,W]: k = C,
- * inner = H*W). out[q]: device pointer of output q, n elements each. */
+ * inner = H*W). A CGTB_FIN_VIEW_F4 input is a row-major matrix with rows of bcast_k[k] elements, of which columns
+ * [bcast_inner[k], bcast_inner[k] + view_width) are read: element i of the [n / view_width, view_width] index space
+ * reads in[k][(i / view_width) * bcast_k[k] + bcast_inner[k] + i % view_width] (a column slice of a matrix, GetSli
+ * along axis 1 in cgt/core.py:1767-1812, consumed without a copy). out[q]: device pointer of output q, n elements each. */
 int cgtb_fused_elwise(const cgtbFusedProgram* prog, long n, const void* const* in, const long* bcast_k,
                       const long* bcast_inner, void* const* out);
 
@@ -284,8 +289,17 @@ typedef struct {
   int op_a[CGTB_FUSED_MAX_OPS], op_b[CGTB_FUSED_MAX_OPS];
   int out_reg[CGTB_FUSED_MAX_OUT];
   int out_col[CGTB_FUSED_MAX_OUT];
+  /* NULL: the library's register-machine kernel runs the program. Otherwise the launcher of a kernel generated for
+   * this program: int f(long R, long C, const void* const* in, void* const* out, void* stream), 0 on success. */
+  void* launcher;
 } cgtbRowProgram;
 int cgtb_fused_rows(const cgtbRowProgram* prog, long R, long C, const void* const* in, void* const* out);
+
+/* out[R, C] = zeros with k float32 pieces placed side by side: piece j ([R, width[j]]) occupies columns
+ * [offset[j], offset[j] + width[j]); the pieces do not overlap. What a sum of IncSli(zeros, ...) over disjoint column
+ * ranges computes (the gradient of several GetSli of one matrix, cgt/core.py:1767-1861), in one launch and without
+ * the zero fills. k <= 8. */
+int cgtb_scatter_cols(long R, long C, int k, const long* offset, const long* width, const void* const* pieces, void* out);
 
 /* Sum / Max over a set of axes, keepdims (cgt/core.py:1663-1738) */
 int cgtb_reduce(int kind, int dtype, int ndim, const long* shape, const int* reduced, const void* in, void* out);

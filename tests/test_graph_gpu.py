@@ -176,6 +176,32 @@ def test_row_fusion_matches_separate_kernels(rt, name):
         np.testing.assert_allclose(a, b, rtol=1e-4, atol=1e-6 * max(1.0, float(np.abs(a).max())))
 
 
+@pytest.mark.parametrize("generated", [True, False])
+def test_slice_rewrites_change_no_bit(rt, generated):
+    """The LSTM's gate slices: column slices read in place by the fused chains (no GetSli launch) and the gradient of the
+    slices placed by one ScatterCols launch (no zero fills, slice increments and additions). Placing a piece next to
+    zeros and adding it to zeros give the same values, and a view reads the same words: losses and parameters are
+    identical with the rewrites on and off. generated: kernels generated per chain / the library's register machine."""
+    results = {}
+    for on in (False, True):
+        with cgt.scoped_update_config(fuse_slice_sums=on, fuse_slice_views=on, jit_fused_elementwise=generated, use_cuda_graphs=False):
+            cfg = configs.BUILDERS["lstm"](**SMALL["lstm"])
+            f = cfg.compile()
+            reprs = [repr(instr) for instr in f.eg.instrs]
+            batches = [cfg.batch(seed) for seed in range(2)]
+            losses = [np.asarray(f(*batches[i % 2])[0]).copy() for i in range(4)]
+            params = [np.asarray(p.op.get_value()).copy() for p in cfg.params]
+            results[on] = (reprs, losses, params)
+    assert not any("ScatterCols" in r for r in results[False][0]) and any("ScatterCols" in r for r in results[True][0])
+    n_getsli = [sum(1 for r in results[on][0] if "GetSli" in r and "/gpu" in r) for on in (False, True)]
+    assert n_getsli[1] < n_getsli[0]
+    assert len(results[True][0]) < len(results[False][0])
+    for (a, b) in zip(results[False][1], results[True][1]):
+        assert np.array_equal(a, b)
+    for (a, b) in zip(results[False][2], results[True][2]):
+        assert np.array_equal(a, b)
+
+
 @pytest.mark.parametrize("name", ["mlp", "cifar", "lstm"])
 def test_merged_parameter_updates_change_no_bit(rt, name):
     """The step's parameter updates as one multi-tensor launch: the same operations on the same values as one launch

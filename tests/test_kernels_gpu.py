@@ -130,6 +130,9 @@ LRNS = [
     ((2, 96, 15, 15), 5, 1e-4, 0.75),    # wide
     ((2, 5, 3, 3), 5, 1.0, 0.75),        # channels == localsize
     ((2, 7, 2, 3), 3, 0.5, 1.0),
+    ((3, 40, 9, 9), 5, 1e-2, 0.75),      # more channels than one pass of the staged kernel covers (odd plane size)
+    ((2, 130, 8, 8), 7, 1e-2, 0.75),     # the same with 128-bit accesses
+    ((130, 32, 6, 6), 5, 1e-4, 0.75),    # plane smaller than a pixel tile
 ]
 
 
@@ -645,7 +648,8 @@ class _FusedProgram(ctypes.Structure):
     _fields_ = [("n_in", ctypes.c_int), ("n_ops", ctypes.c_int), ("n_out", ctypes.c_int), ("in_kind", ctypes.c_int * 8),
                 ("op_arity", ctypes.c_int * 16), ("op_code", ctypes.c_int * 16), ("op_a", ctypes.c_int * 16),
                 ("op_b", ctypes.c_int * 16), ("out_reg", ctypes.c_int * 4), ("out_dtype", ctypes.c_int * 4),
-                ("launcher", ctypes.c_void_p)]  # NULL: the library's own kernel runs the program
+                ("launcher", ctypes.c_void_p),  # NULL: the library's own kernel runs the program
+                ("view_width", ctypes.c_long)]
 
 
 @pytest.mark.parametrize("shape", [(8, 32, 15, 15), (4, 6, 5, 7), (3, 5, 2, 2)])
@@ -694,7 +698,8 @@ def test_fused_elwise_matches_separate_kernels(rt, shape):
 class _RowProgram(ctypes.Structure):
     _fields_ = [("n_in", ctypes.c_int), ("n_ops", ctypes.c_int), ("n_out", ctypes.c_int), ("in_kind", ctypes.c_int * 8),
                 ("op_arity", ctypes.c_int * 16), ("op_code", ctypes.c_int * 16), ("op_a", ctypes.c_int * 16),
-                ("op_b", ctypes.c_int * 16), ("out_reg", ctypes.c_int * 4), ("out_col", ctypes.c_int * 4)]
+                ("op_b", ctypes.c_int * 16), ("out_reg", ctypes.c_int * 4), ("out_col", ctypes.c_int * 4),
+                ("launcher", ctypes.c_void_p)]  # NULL: the library's own kernel runs the program
 
 
 @pytest.mark.parametrize("R,C", [(128, 10), (64, 65), (1, 1), (5, 32), (1000, 33), (7, 100), (300, 128)])
@@ -746,6 +751,54 @@ def test_fused_rows_refuses_long_rows(rt):
     o = Dev(shape=(4, 1), dtype="f4")
     rc = runtime.lib().cgtb_fused_rows(ctypes.byref(P), 4, 129, (ctypes.c_void_p * 8)(d.ptr), (ctypes.c_void_p * 4)(o.ptr))
     assert rc != 0 and "128" in runtime.last_error()
+
+
+@pytest.mark.parametrize("R,W,pitch,off", [(64, 128, 512, 384), (7, 5, 13, 3), (33, 12, 40, 8)])
+def test_fused_elwise_reads_column_slices_in_place(rt, R, W, pitch, off):
+    """tanh(S[:, off:off+W]) * g with S a wider matrix: the chain reads the columns of S where they lie (the GetSli of
+    cgt/core.py:1767-1812 without its copy), bit-identical to slicing first."""
+    rs = np.random.RandomState(R + W)
+    S, g = rs.randn(R, pitch).astype("f4"), rs.randn(R, W).astype("f4")
+    dS, dg = Dev(S), Dev(g)
+    sl = Dev(np.ascontiguousarray(S[:, off:off + W]))
+    t, want = Dev(shape=(R, W), dtype="f4"), Dev(shape=(R, W), dtype="f4")
+    call("cgtb_unary", 12, code("f4"), code("f4"), R * W, sl.ptr, t.ptr)
+    call("cgtb_binary", 0, code("f4"), code("f4"), code("f4"), R * W, t.ptr, dg.ptr, want.ptr, 0, 0)
+    P = _FusedProgram()
+    P.n_in, P.n_ops, P.n_out = 2, 2, 1
+    P.in_kind[0], P.in_kind[1] = 7, 0
+    P.op_arity[0], P.op_code[0], P.op_a[0] = 1, 12, 0
+    P.op_arity[1], P.op_code[1], P.op_a[1], P.op_b[1] = 2, 0, 2, 1
+    P.out_reg[0], P.out_dtype[0] = 3, code("f4")
+    P.view_width = W
+    out = Dev(shape=(R, W), dtype="f4")
+    ins = (ctypes.c_void_p * 8)(dS.ptr, dg.ptr)
+    outs = (ctypes.c_void_p * 4)(out.ptr)
+    bk, binner = longs([pitch, 1, 1, 1, 1, 1, 1, 1]), longs([off, 1, 1, 1, 1, 1, 1, 1])
+    call("cgtb_fused_elwise", ctypes.byref(P), R * W, ins, bk, binner, outs)
+    assert np.array_equal(out.get(), want.get())
+    # a slice that sticks out of the matrix is refused
+    bad = longs([pitch, 1, 1, 1, 1, 1, 1, 1]), longs([pitch - W + 1, 1, 1, 1, 1, 1, 1, 1])
+    rc = runtime.lib().cgtb_fused_elwise(ctypes.byref(P), R * W, ins, bad[0], bad[1], outs)
+    assert rc != 0 and "column range" in runtime.last_error()
+
+
+def test_scatter_cols_places_pieces_into_zeros(rt):
+    """The gradient of three column slices of a [R, 40] matrix: zeros, then each piece added into its columns
+    (IncSli on a Fill, cgt/core.py:1786-1790, 1814-1861) and the three results added, against one launch."""
+    rs = np.random.RandomState(9)
+    R, C = 37, 40
+    pieces = [(24, rs.randn(R, 9).astype("f4")), (0, rs.randn(R, 8).astype("f4")), (12, rs.randn(R, 12).astype("f4"))]
+    want = np.zeros((R, C), "f4")
+    for (o, y) in pieces:
+        want = want + O.incsli(np.zeros((R, C), "f4"), 1, o, o + y.shape[1], 1, y)
+    devs = [Dev(y) for (_o, y) in pieces]
+    out = Dev(np.full((R, C), 7.0, "f4"))
+    ptrs = (ctypes.c_void_p * 8)(*[d.ptr for d in devs])
+    call("cgtb_scatter_cols", R, C, 3, longs([o for (o, _y) in pieces]), longs([y.shape[1] for (_o, y) in pieces]), ptrs, out.ptr)
+    assert np.array_equal(out.get(), want)
+    rc = runtime.lib().cgtb_scatter_cols(R, C, 2, longs([0, 4]), longs([8, 8]), ptrs, out.ptr)
+    assert rc != 0 and "overlap" in runtime.last_error()
 
 
 def test_reduce_over_an_empty_axis_gives_the_identity(rt):
