@@ -176,7 +176,9 @@ CGTB_API int cgtb_conv_bias_relu_ld(const float* col, long M, long K, long ldcol
     padded_w(wp);
     wuse = wp;
   }
-  {
+  // products that the dispatcher gives to the FMA kernels (below the tensor-core kernels' break-even size) take the
+  // staged path below: the same product kernel, hence the same bits, as Mul22 followed by the separate output stage
+  if (M * (long)C * K > (1L << 25)) {
     // the tensor-core kernels apply the output stage to the accumulator tile when the product is not split
     // along K: no intermediate matrix at all
     cgtb::ConvEpilogue ep = {bias, y_nchw, mask_nchw, HW};

@@ -342,7 +342,10 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   const int UN = p.UN, RS = p.raw_stages, CS = p.conv_stages;
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t x_bytes = kXRows * 128u, y_bytes = (uint32_t)UN * 128u;
-  constexpr bool XDIRECT = !XMN;  // a K-major X tile is the MMA's hi operand as it lies in the raw stage
+  // The X tile is the MMA's hi operand as it lies in the raw stage when it is K-major, and in the filter-gradient
+  // product (CONV 2), whose operands are read MN-major as the TMA unit delivers them (pixel rows of 32 channels):
+  // no transposition, only x_lo, y_hi (a copy) and y_lo are produced, by linear passes over 16-byte chunks.
+  constexpr bool XDIRECT = !XMN || CONV == 2;
   const uint32_t cx_bytes = XDIRECT ? x_bytes : 2 * x_bytes;  // conversion stage: [X hi] X lo, Y hi, Y lo
   const uint32_t conv_bytes = cx_bytes + 2 * y_bytes, raw_bytes = x_bytes + y_bytes;
   unsigned char* conv0 = smem;
@@ -361,6 +364,16 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
     mbar_init(smem_u32(&accum_bar), 1);
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (CONV == 2 && p.wnpx < kBK) {
+    // a K block holds wnpx < 32 pixel rows; the TMA boxes never write rows wnpx..31 of the 32-row sub-tiles, and the
+    // MMAs read all 32: those rows are zeroed once, in every raw stage, and stay zero
+    const int subtiles = (int)(raw_bytes / 4096u), tail16 = (kBK - p.wnpx) * 8;   // 16-byte chunks per sub-tile tail
+    for (int i = tid; i < RS * subtiles * tail16; i += kThreadsTma) {
+      const int st = i / (subtiles * tail16), r = i - st * subtiles * tail16, sub = r / tail16, c = r - sub * tail16;
+      *reinterpret_cast<uint4*>(raw0 + (size_t)st * raw_bytes + (size_t)sub * 4096 + (size_t)p.wnpx * 128 + (size_t)c * 16) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == kConvWarps) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
@@ -393,8 +406,8 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         unsigned char* cx = conv0 + (size_t)cs * conv_bytes;
         unsigned char* cy = cx + cx_bytes;
         if (CONV == 2) {
-          convert_units(rx, cx, cx + x_bytes, tid, p.wnpx);
-          convert_mnmajor(ry, cy, cy + y_bytes, UN, tid, p.wnpx);
+          convert_kmajor_lo(rx, cx, kXRows * 8, tid);          // x_lo in the raw tile's own layout
+          convert_kmajor(ry, cy, cy + y_bytes, UN * 8, tid);   // [y_hi | y_lo], likewise
         } else {
           if (XMN) convert_mnmajor(rx, cx, cx + x_bytes, kXRows, tid, kBK);
           else convert_kmajor_lo(rx, cx, kXRows * 8, tid);
@@ -433,7 +446,8 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
     // The whole warp runs the loop; per K block one elected lane issues all its MMAs and commits (no election
     // and no lane-mask operand per instruction: that form issues almost twice as fast). Two instructions per K step:
     // x_hi * [y_hi | y_lo] into columns [0, 2UN) and x_lo * y_hi into columns [0, UN).
-    const uint32_t idesc1 = make_idesc_tf32(UN), idesc2 = make_idesc_tf32(2 * UN);
+    const uint32_t idesc1 = CONV == 2 ? make_idesc_tf32_mn(UN) : make_idesc_tf32(UN);
+    const uint32_t idesc2 = CONV == 2 ? make_idesc_tf32_mn(2 * UN) : make_idesc_tf32(2 * UN);
     bool ok = true;
     int rs = 0, cs = 0;
     int tkb = 0;
@@ -447,13 +461,18 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         if (lane == 0) TRACE(tkb, 4);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t sbase = smem_u32(conv0 + (size_t)cs * conv_bytes);
-        const uint64_t dxh = make_desc(XDIRECT ? smem_u32(raw0 + (size_t)rs * raw_bytes) : sbase);
-        const uint64_t dxl = make_desc(XDIRECT ? sbase : sbase + x_bytes);
-        const uint64_t dyh = make_desc(sbase + cx_bytes);  // y_lo follows y_hi: one descriptor covers both
+        const uint32_t xh_addr = XDIRECT ? smem_u32(raw0 + (size_t)rs * raw_bytes) : sbase;
+        const uint32_t xl_addr = XDIRECT ? sbase : sbase + x_bytes;
+        // MN-major operands (CONV 2): 32-element groups (the four units of X, the 32-channel groups of [y_hi | y_lo])
+        // lie 4096 bytes apart
+        const uint64_t dxh = CONV == 2 ? make_desc_mn(xh_addr, 4096u) : make_desc(xh_addr);
+        const uint64_t dxl = CONV == 2 ? make_desc_mn(xl_addr, 4096u) : make_desc(xl_addr);
+        const uint64_t dyh = CONV == 2 ? make_desc_mn(sbase + cx_bytes, 4096u) : make_desc(sbase + cx_bytes);  // y_lo follows y_hi: one descriptor covers both
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < kBK / 8; ++kk) {
-            const uint64_t adv = (uint64_t)((kk * 32) >> 4);  // 8 tf32 = 32 bytes along K inside the swizzle row
+            // K-major: 8 tf32 = 32 bytes along K inside the swizzle row; MN-major: 8 K rows = 1024 bytes
+            const uint64_t adv = (uint64_t)((kk * (CONV == 2 ? 1024 : 32)) >> 4);
             const uint32_t first = (kb == 0 && kk == 0) ? 0u : 1u;
             mma_tf32_one(tmem_d, dxh + adv, dyh + adv, idesc2, first);
             mma_tf32_one(tmem_d, dxl + adv, dyh + adv, idesc1, 1u);
@@ -503,8 +522,10 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
           const int tap = unit / p.ckpt, q = unit - tap * p.ckpt;
           const int ti = tap / p.ckw, tj = tap - ti * p.ckw;
           tma_load_4d(dx + (uint32_t)lane * 4096u, &mapX, 32 * q, tj - p.cpw, yrow0 + ti - p.cph, b, bar);
-        } else if (lane == nunits) {
-          tma_load_4d(dx + x_bytes, &mapY, (int)y0, 0, yrow0, b, bar);
+        } else if (lane >= 4 && lane < 4 + UN / 32) {
+          // the gradient's tile as groups of 32 channels, each a sub-tile of 32 pixel rows x 128 bytes
+          const int g = lane - 4;
+          tma_load_4d(dx + x_bytes + (uint32_t)g * 4096u, &mapY, (int)y0 + 32 * g, 0, yrow0, b, bar);
         }
         __syncwarp();
         ++issued;
@@ -1337,7 +1358,7 @@ int conv_implicit_tma(const float* src, long B, int Hs, int Ws, int Cs, const fl
 int conv_wgrad_tma(const float* src, long B, int Hs, int Ws, int Cs, const float* dy, int Hd, int Wd, int N, int kh, int kw, int ph,
                    int pw, float* dw) {
   if (N <= 0 || Cs <= 0 || kh <= 0 || kw <= 0) return 0;
-  if (Cs % 32 != 0 || N % 16 != 0 || Wd > 32 || Wd <= 0 || Hd <= 0 || B <= 0 || B >= (1L << 24)) return -1;
+  if (Cs % 32 != 0 || N % 4 != 0 || Wd > 32 || Wd <= 0 || Hd <= 0 || B <= 0 || B >= (1L << 24)) return -1;
   if (((uintptr_t)src & 15) != 0 || ((uintptr_t)dy & 15) != 0) return -1;
   const long Kc = (long)kh * kw * Cs;  // columns of the result
   TmaParams p;
@@ -1353,8 +1374,8 @@ int conv_wgrad_tma(const float* src, long B, int Hs, int Ws, int Cs, const float
   p.wnrg = (int)cgtb_ceil_div(Hd, p.wbh);
   p.wnpx = p.wbh * Wd;
   const int ytiles = (int)cgtb_ceil_div(N, 128);
-  int UN = (int)(cgtb_ceil_div(cgtb_ceil_div(N, ytiles), 16) * 16);
-  if (UN * ytiles != N) return -1;
+  // whole groups of 32 channels (one 128-byte row each); channels beyond N are zero-filled by the TMA unit and never stored
+  int UN = (int)(cgtb_ceil_div(cgtb_ceil_div(N, ytiles), 32) * 32);
   p.UN = UN;
   p.tmem_cols = 32;
   while (p.tmem_cols < 2 * UN) p.tmem_cols *= 2;
@@ -1362,7 +1383,8 @@ int conv_wgrad_tma(const float* src, long B, int Hs, int Ws, int Cs, const float
   p.xrows = Kc;
   const long xtiles = cgtb_ceil_div(p.wunits, 4);
   const long nkb_total = B * p.wnrg;
-  const long conv_bytes = 2L * kXRows * 128 + 2L * UN * 128, raw_bytes = (long)kXRows * 128 + (long)UN * 128;
+  // conversion stage: x_lo, [y_hi | y_lo]; raw stage: x (read in place as x_hi), y
+  const long conv_bytes = 1L * kXRows * 128 + 2L * UN * 128, raw_bytes = (long)kXRows * 128 + (long)UN * 128;
   int conv_stages, raw_stages;
   if (!choose_stages(conv_bytes, raw_bytes, nkb_total, &conv_stages, &raw_stages)) return -1;
   const long tiles = xtiles * ytiles;
@@ -1403,15 +1425,15 @@ int conv_wgrad_tma(const float* src, long B, int Hs, int Ws, int Cs, const float
     cuuint64_t strides[3] = {(cuuint64_t)Cs * 4, (cuuint64_t)Ws * Cs * 4, (cuuint64_t)Hs * Ws * Cs * 4};
     cuuint32_t box[4] = {32, (cuuint32_t)Wd, (cuuint32_t)p.wbh, 1};
     CUresult r = fn(&mapX, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)src, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return -1;
   }
   {
     cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)Wd, (cuuint64_t)Hd, (cuuint64_t)B};
     cuuint64_t strides[3] = {(cuuint64_t)N * 4, (cuuint64_t)Wd * N * 4, (cuuint64_t)Hd * Wd * N * 4};
-    cuuint32_t box[4] = {(cuuint32_t)UN, (cuuint32_t)Wd, (cuuint32_t)p.wbh, 1};
+    cuuint32_t box[4] = {32, (cuuint32_t)Wd, (cuuint32_t)p.wbh, 1};   // one box per group of 32 channels
     CUresult r = fn(&mapY, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)dy, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return -1;
   }
   size_t smem = (size_t)conv_stages * conv_bytes + (size_t)raw_stages * raw_bytes + 1024;
@@ -1473,7 +1495,7 @@ CGTB_API int cgtb_conv_wgrad(const float* x_nhwc, long B, int H, int W, int Cin,
                 kw, H, W, ph, pw);
   int rc = cgtb::conv_wgrad_tma(x_nhwc, B, H, W, Cin, dy_nhwc, Ho, Wo, Cout, kh, kw, ph, pw, dw);
   if (rc < 0)
-    return fail("cgtb_conv_wgrad: not supported for Cin=%d (multiple of 32), Cout=%d (multiple of 16; of 128 when above 128), Wo=%d "
+    return fail("cgtb_conv_wgrad: not supported for Cin=%d (multiple of 32), Cout=%d (multiple of 4), Wo=%d "
                 "(at most 32) or an unaligned operand; use cgtb_im2col + cgtb_sgemm", Cin, Cout, Wo);
   return rc;
 }

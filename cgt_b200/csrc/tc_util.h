@@ -170,6 +170,25 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
   return d;
 }
 
+// shared-memory matrix descriptor of an MN-major 32-bit operand (the M or N index runs along the 128-byte rows, one row
+// per K index). For 32-bit elements the only MN-major layout of the tensor core is the 128-byte swizzle with 32-byte
+// atoms (layout type 1; what CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B writes): 32 consecutive M/N elements x 4 K rows
+// form one 512-byte atom in which the 32-byte chunks of row r are permuted by r % 4. `lbo` = bytes from one group of 32
+// M/N elements to the next; groups of 4 K rows are 512 bytes apart (dense rows).
+__device__ __forceinline__ uint64_t make_desc_mn(uint32_t saddr, uint32_t lbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFFu);
+  d |= (uint64_t)((lbo >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)(512 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)1 << 61;
+  return d;
+}
+// instruction descriptor as below with both operands MN-major
+__device__ __forceinline__ uint32_t make_idesc_tf32_mn(int un) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | (1u << 15) | (1u << 16) | ((uint32_t)(un >> 3) << 17) | ((uint32_t)(kXRows >> 4) << 24);
+}
+
 // instruction descriptor: D fp32, A/B tf32, both K-major, N = un, M = 128
 __device__ __forceinline__ uint32_t make_idesc_tf32(int un) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(un >> 3) << 17) | ((uint32_t)(kXRows >> 4) << 24);
