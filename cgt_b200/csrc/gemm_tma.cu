@@ -160,8 +160,12 @@ __device__ __forceinline__ void convert_kmajor(const unsigned char* raw, unsigne
 // bits itself, exactly as it cuts those of x. Non-finite inputs: a NaN stays NaN through x itself; for an
 // infinite x the split gives non-finite products whose kind is not defined (the cross term inf * y_lo is NaN
 // when y_lo is zero or of the other sign, in every variant of the 3xTF32 scheme), so no guard is spent here.
+// The residual has up to 13 significant bits and the tensor core keeps 11 of them by cutting: half a unit of the
+// last kept place is added to the bit pattern first, so that the cut rounds to nearest (the error of the product
+// falls from 2^-21 to 2^-22 of |x y|, that of a split with a rounded hi part).
 __device__ __forceinline__ uint32_t lo_of(uint32_t b) {
-  return __float_as_uint(__fadd_rn(__uint_as_float(b), -__uint_as_float(b & 0xFFFFE000u)));
+  const uint32_t r = __float_as_uint(__fadd_rn(__uint_as_float(b), -__uint_as_float(b & 0xFFFFE000u)));
+  return (r & 0x7F800000u) != 0x7F800000u ? r + 0x1000u : r;   // a NaN residual (x was NaN or infinite) stays NaN
 }
 __device__ __forceinline__ void convert_kmajor_lo(const unsigned char* raw, unsigned char* lo, int nchunks, int tid) {
   for (int c0 = tid; c0 < nchunks; c0 += 4 * kConvThreads) {
@@ -179,42 +183,6 @@ __device__ __forceinline__ void convert_kmajor_lo(const unsigned char* raw, unsi
   }
 }
 
-// raw [32 k][R rows] tile: unit q -> (row = q % R, k quad = q / R); lanes run along rows on both sides.
-// K slots at or beyond kvalid hold no data (the TMA box was shorter): they become zeros.
-__device__ __forceinline__ void convert_mnmajor(const unsigned char* raw, unsigned char* hi, unsigned char* lo, int R, int tid, int kvalid) {
-  const float* src = reinterpret_cast<const float*>(raw);
-  const int units = R * 8;
-  for (int q = tid; q < units; q += kConvThreads) {
-    const int kq = q / R, r = q - kq * R;
-    const float* s = src + (size_t)(4 * kq) * R + r;
-    const int k0 = 4 * kq;
-    const float a = k0 < kvalid ? s[0] : 0.f, b = k0 + 1 < kvalid ? s[R] : 0.f, c = k0 + 2 < kvalid ? s[2 * R] : 0.f,
-                d = k0 + 3 < kvalid ? s[3 * R] : 0.f;
-    uint4 h, l;
-    split_tf32x4(a, b, c, d, h, l);
-    const uint32_t off = tile_off(r, 4 * kq);
-    *reinterpret_cast<uint4*>(hi + off) = h;
-    *reinterpret_cast<uint4*>(lo + off) = l;
-  }
-}
-
-// raw [4 units][32 k][32 channels] tile of the filter gradient: tile row r = unit (r / 32), channel (r % 32);
-// element (r, k) lies at unit*1024 + k*32 + channel floats. Same output layout as convert_mnmajor.
-__device__ __forceinline__ void convert_units(const unsigned char* raw, unsigned char* hi, unsigned char* lo, int tid, int kvalid) {
-  const float* src = reinterpret_cast<const float*>(raw);
-  for (int q = tid; q < kXRows * 8; q += kConvThreads) {
-    const int kq = q >> 7, r = q & 127;
-    const float* s = src + (r >> 5) * 1024 + (r & 31) + (4 * kq) * 32;
-    const int k0 = 4 * kq;
-    const float a = k0 < kvalid ? s[0] : 0.f, b = k0 + 1 < kvalid ? s[32] : 0.f, c = k0 + 2 < kvalid ? s[64] : 0.f,
-                d = k0 + 3 < kvalid ? s[96] : 0.f;
-    uint4 h, l;
-    split_tf32x4(a, b, c, d, h, l);
-    const uint32_t off = tile_off(r, 4 * kq);
-    *reinterpret_cast<uint4*>(hi + off) = h;
-    *reinterpret_cast<uint4*>(lo + off) = l;
-  }
-}
 
 // Epilogue of one tile, run by the eight epilogue warps: accumulator (TMEM) -> registers -> global memory.
 template <int CONV, int NCOLGROUPS = kConvWarps / 4>
@@ -342,10 +310,12 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
   const int UN = p.UN, RS = p.raw_stages, CS = p.conv_stages;
   unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t x_bytes = kXRows * 128u, y_bytes = (uint32_t)UN * 128u;
-  // The X tile is the MMA's hi operand as it lies in the raw stage when it is K-major, and in the filter-gradient
-  // product (CONV 2), whose operands are read MN-major as the TMA unit delivers them (pixel rows of 32 channels):
-  // no transposition, only x_lo, y_hi (a copy) and y_lo are produced, by linear passes over 16-byte chunks.
-  constexpr bool XDIRECT = !XMN || CONV == 2;
+  // The X tile is the MMA's hi operand as it lies in the raw stage, whatever its storage order: a K-major tile is a
+  // box of 128 rows x 128 bytes (128-byte swizzle), an MN-major tile four boxes of 32 K rows x 128 bytes (32 rows of
+  // the operand each; 128-byte swizzle with 32-byte atoms, the tensor core's only MN-major layout for 32-bit
+  // elements), and the MMA's descriptors name the order. No transposition anywhere: only x_lo, y_hi (a copy) and
+  // y_lo are produced, by linear passes over 16-byte chunks that do not need to know the layout.
+  constexpr bool XDIRECT = true;
   const uint32_t cx_bytes = XDIRECT ? x_bytes : 2 * x_bytes;  // conversion stage: [X hi] X lo, Y hi, Y lo
   const uint32_t conv_bytes = cx_bytes + 2 * y_bytes, raw_bytes = x_bytes + y_bytes;
   unsigned char* conv0 = smem;
@@ -405,17 +375,10 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         const unsigned char* ry = rx + x_bytes;
         unsigned char* cx = conv0 + (size_t)cs * conv_bytes;
         unsigned char* cy = cx + cx_bytes;
-        if (CONV == 2) {
-          convert_kmajor_lo(rx, cx, kXRows * 8, tid);          // x_lo in the raw tile's own layout
-          convert_kmajor(ry, cy, cy + y_bytes, UN * 8, tid);   // [y_hi | y_lo], likewise
-        } else {
-          if (XMN) convert_mnmajor(rx, cx, cx + x_bytes, kXRows, tid, kBK);
-          else convert_kmajor_lo(rx, cx, kXRows * 8, tid);
-          if (tid == 0) TRACE(tkb, 6);
-          if (YMN) convert_mnmajor(ry, cy, cy + y_bytes, UN, tid, kBK);
-          else convert_kmajor(ry, cy, cy + y_bytes, UN * 8, tid);
-          if (tid == 0) TRACE(tkb, 7);
-        }
+        convert_kmajor_lo(rx, cx, kXRows * 8, tid);          // x_lo in the raw tile's own layout
+        if (tid == 0) TRACE(tkb, 6);
+        convert_kmajor(ry, cy, cy + y_bytes, UN * 8, tid);   // [y_hi | y_lo], likewise
+        if (tid == 0) TRACE(tkb, 7);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core
         __syncwarp();
         if (lane == 0) {
@@ -446,8 +409,8 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
     // The whole warp runs the loop; per K block one elected lane issues all its MMAs and commits (no election
     // and no lane-mask operand per instruction: that form issues almost twice as fast). Two instructions per K step:
     // x_hi * [y_hi | y_lo] into columns [0, 2UN) and x_lo * y_hi into columns [0, UN).
-    const uint32_t idesc1 = CONV == 2 ? make_idesc_tf32_mn(UN) : make_idesc_tf32(UN);
-    const uint32_t idesc2 = CONV == 2 ? make_idesc_tf32_mn(2 * UN) : make_idesc_tf32(2 * UN);
+    const uint32_t major_bits = (XMN ? (1u << 15) : 0u) | (YMN ? (1u << 16) : 0u);   // operand A / B is MN-major
+    const uint32_t idesc1 = make_idesc_tf32(UN) | major_bits, idesc2 = make_idesc_tf32(2 * UN) | major_bits;
     bool ok = true;
     int rs = 0, cs = 0;
     int tkb = 0;
@@ -463,19 +426,19 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         const uint32_t sbase = smem_u32(conv0 + (size_t)cs * conv_bytes);
         const uint32_t xh_addr = XDIRECT ? smem_u32(raw0 + (size_t)rs * raw_bytes) : sbase;
         const uint32_t xl_addr = XDIRECT ? sbase : sbase + x_bytes;
-        // MN-major operands (CONV 2): 32-element groups (the four units of X, the 32-channel groups of [y_hi | y_lo])
-        // lie 4096 bytes apart
-        const uint64_t dxh = CONV == 2 ? make_desc_mn(xh_addr, 4096u) : make_desc(xh_addr);
-        const uint64_t dxl = CONV == 2 ? make_desc_mn(xl_addr, 4096u) : make_desc(xl_addr);
-        const uint64_t dyh = CONV == 2 ? make_desc_mn(sbase + cx_bytes, 4096u) : make_desc(sbase + cx_bytes);  // y_lo follows y_hi: one descriptor covers both
+        // MN-major operands: groups of 32 rows of the operand (the four boxes of X, the groups of [y_hi | y_lo]) lie
+        // 4096 bytes apart
+        const uint64_t dxh = XMN ? make_desc_mn(xh_addr, 4096u) : make_desc(xh_addr);
+        const uint64_t dxl = XMN ? make_desc_mn(xl_addr, 4096u) : make_desc(xl_addr);
+        const uint64_t dyh = YMN ? make_desc_mn(sbase + cx_bytes, 4096u) : make_desc(sbase + cx_bytes);  // y_lo follows y_hi: one descriptor covers both
         if (elect_one()) {
 #pragma unroll
           for (int kk = 0; kk < kBK / 8; ++kk) {
             // K-major: 8 tf32 = 32 bytes along K inside the swizzle row; MN-major: 8 K rows = 1024 bytes
-            const uint64_t adv = (uint64_t)((kk * (CONV == 2 ? 1024 : 32)) >> 4);
+            const uint64_t advx = (uint64_t)((kk * (XMN ? 1024 : 32)) >> 4), advy = (uint64_t)((kk * (YMN ? 1024 : 32)) >> 4);
             const uint32_t first = (kb == 0 && kk == 0) ? 0u : 1u;
-            mma_tf32_one(tmem_d, dxh + adv, dyh + adv, idesc2, first);
-            mma_tf32_one(tmem_d, dxl + adv, dyh + adv, idesc1, 1u);
+            mma_tf32_one(tmem_d, dxh + advx, dyh + advy, idesc2, first);
+            mma_tf32_one(tmem_d, dxl + advx, dyh + advy, idesc1, 1u);
           }
           mma_commit(smem_u32(&conv_empty[cs]));
           if (XDIRECT) mma_commit(smem_u32(&raw_empty[rs]));
@@ -539,8 +502,51 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
       // copies already issued still write this CTA's shared memory: wait (bounded) until they have landed
       for (long j = (issued > RS ? issued - RS : 0); j < issued; ++j) mbar_wait(smem_u32(&raw_full[j % RS]), (uint32_t)(j / RS) & 1u);
     }
+  } else if (CONV == 0) {
+    // ------------------------------------------------ TMA producer of the plain product (one warp)
+    // lanes 0..3 issue the boxes of X (one when K-major, four groups of 32 rows when MN-major), lanes 4.. those of Y
+    // (one, or UN / 32 groups); lane 0 alone waits for the stage and arms its barrier. Rows and K indices beyond the
+    // operand are zero-filled by the TMA unit.
+    long issued = 0;
+    bool ok = true;
+    int rs = 0;
+    uint32_t rphase = 0;
+    const int nx = XMN ? 4 : 1, ny = YMN ? UN / 32 : 1;
+    for (long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+      const Tile c = tile_of(p, t);
+      const long x0 = (long)c.xt * kXRows, y0 = (long)c.yt * UN;
+      for (int kb = 0; kb < c.nkb; ++kb) {
+        if (lane == 0) ok = mbar_wait_or_abort(smem_u32(&raw_empty[rs]), rphase ^ 1u, abortp);
+        ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        if (!ok) break;
+        if (lane == 0) TRACE((int)issued, 0);
+        const uint32_t bar = smem_u32(&raw_full[rs]);
+        const int k0 = (int)(c.k_begin + (long)kb * kBK);
+        const uint32_t dx = smem_u32(raw0 + (size_t)rs * raw_bytes);
+        if (lane == 0) mbar_arrive_expect_tx(bar, raw_bytes);
+        __syncwarp();
+        if (lane < nx) {
+          if (XMN) tma_load_3d(dx + (uint32_t)lane * 4096u, &mapX, (int)x0 + 32 * lane, k0, c.batch, bar);
+          else tma_load_3d(dx, &mapX, k0, (int)x0, c.batch, bar);
+        } else if (lane >= 4 && lane < 4 + ny) {
+          const int g = lane - 4;
+          if (YMN) tma_load_3d(dx + x_bytes + (uint32_t)g * 4096u, &mapY, (int)y0 + 32 * g, k0, c.batch, bar);
+          else tma_load_3d(dx + x_bytes, &mapY, k0, (int)y0, c.batch, bar);
+        }
+        __syncwarp();
+        ++issued;
+        if (++rs == RS) { rs = 0; rphase ^= 1u; }
+      }
+    }
+    if (lane == 0 && (!ok || *abortp)) {
+      *abortp = 1;
+      *(volatile int*)p.err = 5;
+      __threadfence_system();
+      // copies already issued still write this CTA's shared memory: wait (bounded) until they have landed
+      for (long j = (issued > RS ? issued - RS : 0); j < issued; ++j) mbar_wait(smem_u32(&raw_full[j % RS]), (uint32_t)(j / RS) & 1u);
+    }
   } else if (lane == 0) {
-    // ------------------------------------------------ TMA producer (one thread)
+    // ------------------------------------------------ TMA producer of the per-tap implicit convolution (one thread)
     long issued = 0;
     bool ok = true;
     int rs = 0;
@@ -567,12 +573,6 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
           const int yrow0 = p.cnimg > 1 ? 0 : (tile - b0 * p.cnbands) * p.crows;
           tma_load_4d(dx, &mapX, 32 * q, p.csign * (tj - p.cpw), yrow0 + p.csign * (ti - p.cph), b0, bar);
           tma_load_3d(dx + x_bytes, &mapY, k0, (int)y0, c.batch, bar);
-        } else {
-          mbar_arrive_expect_tx(bar, raw_bytes);
-          if (XMN) tma_load_3d(dx, &mapX, (int)x0, k0, c.batch, bar);
-          else tma_load_3d(dx, &mapX, k0, (int)x0, c.batch, bar);
-          if (YMN) tma_load_3d(dx + x_bytes, &mapY, (int)y0, k0, c.batch, bar);
-          else tma_load_3d(dx + x_bytes, &mapY, k0, (int)y0, c.batch, bar);
         }
         ++issued;
         if (++rs == RS) { rs = 0; rphase ^= 1u; }
@@ -982,9 +982,9 @@ bool encode(CUtensorMap* map, const Side& s, long K, long P, int box_rows) {
   if (!fn) return false;
   cuuint64_t dims[3], strides[2];
   cuuint32_t box[3], estr[3] = {1, 1, 1};
-  if (s.mn) {
+  if (s.mn) {   // groups of 32 rows of the operand: one 128-byte row per K index
     dims[0] = (cuuint64_t)s.rows; dims[1] = (cuuint64_t)K;
-    box[0] = (cuuint32_t)box_rows; box[1] = kBK;
+    box[0] = 32; box[1] = kBK;
   } else {
     dims[0] = (cuuint64_t)K; dims[1] = (cuuint64_t)s.rows;
     box[0] = kBK; box[1] = (cuuint32_t)box_rows;
@@ -995,7 +995,7 @@ bool encode(CUtensorMap* map, const Side& s, long K, long P, int box_rows) {
   strides[1] = (cuuint64_t)(P > 1 ? s.bstride : (long)dims[1] * s.ld) * 4;
   if (dims[0] >= (1ull << 32) || dims[1] >= (1ull << 32) || strides[0] >= (1ull << 40) || strides[1] >= (1ull << 40)) return false;
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)s.base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  s.mn ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  s.mn ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
@@ -1096,8 +1096,9 @@ int sgemm_tma(int tA, int tB, long P, long M, long N, long K, const float* A, lo
   const Side& Y = p.swapped ? sA : sB;
   long ydim = Y.rows;
   int ytiles = (int)cgtb_ceil_div(ydim, 128);
-  int UN = (int)(cgtb_ceil_div(cgtb_ceil_div(ydim, ytiles), 16) * 16);
-  if (UN < 16) UN = 16;
+  const int ugran = Y.mn ? 32 : 16;   // an MN-major Y arrives in groups of 32 rows
+  int UN = (int)(cgtb_ceil_div(cgtb_ceil_div(ydim, ytiles), ugran) * ugran);
+  if (UN < ugran) UN = ugran;
   ytiles = (int)cgtb_ceil_div(ydim, UN);
   long xtiles = cgtb_ceil_div(X.rows, kXRows);
   p.UN = UN;
@@ -1105,7 +1106,7 @@ int sgemm_tma(int tA, int tB, long P, long M, long N, long K, const float* A, lo
   while (p.tmem_cols < 2 * UN) p.tmem_cols *= 2;  // hi*hi + lo*hi in [0, UN), hi*lo in [UN, 2UN)
   p.xrows = X.rows;
   p.yrows = Y.rows;
-  const long cx_bytes = X.mn ? 2L * kXRows * 128 : 1L * kXRows * 128;  // a K-major X is read in place as the hi operand
+  const long cx_bytes = 1L * kXRows * 128;  // X is read in place as the hi operand: the conversion stage holds x_lo only
   const long conv_bytes = cx_bytes + 2L * UN * 128, raw_bytes = (long)kXRows * 128 + (long)UN * 128;
   int conv_stages, raw_stages;
   long nkb_total = cgtb_ceil_div(K, kBK);
