@@ -289,42 +289,53 @@ struct FusedMultiArgs {
   long n[kMultiMaxTensors];
   const void* in[kMultiMaxTensors][kMultiMaxIn];
   float* out[kMultiMaxTensors];
+  unsigned char vec[kMultiMaxTensors];   // the tensor's arrays are 16-byte aligned: groups of four
 };
+// One element (V = 1) or one aligned group of four (V = 4) of tensor t
 template <int V>
-__global__ void fused_elwise_multi_kernel(const FusedMultiArgs a) {
+__device__ __forceinline__ void fused_multi_apply(const FusedMultiArgs& a, int t, long i) {
   const cgtbFusedProgram& P = a.prog;
+  float r[kMultiMaxIn + CGTB_FUSED_MAX_OPS][V];
+  for (int k = 0; k < P.n_in; ++k) {
+    if (P.in_kind[k] == CGTB_FIN_F4) {
+      if (V == 4) {
+        const float4 v = ((const float4*)a.in[t][k])[i];
+        r[k][0] = v.x; r[k][1 % V] = v.y; r[k][2 % V] = v.z; r[k][3 % V] = v.w;
+      } else {
+        r[k][0] = ((const float*)a.in[t][k])[i];
+      }
+    } else {
+      const float v = P.in_kind[k] == CGTB_FIN_SCALAR_F4 ? *(const float*)a.in[t][k] : (float)*(const long*)a.in[t][k];
+#pragma unroll
+      for (int q = 0; q < V; ++q) r[k][q] = v;
+    }
+  }
+  for (int o = 0; o < P.n_ops; ++o) {
+    const int dst = P.n_in + o, ra = P.op_a[o], code = P.op_code[o];
+    if (P.op_arity[o] == 1) {
+#pragma unroll
+      for (int q = 0; q < V; ++q) r[dst][q] = unary_apply<float, float>(code, r[ra][q]);
+    } else {
+      const int rb = P.op_b[o];
+#pragma unroll
+      for (int q = 0; q < V; ++q) r[dst][q] = binary_apply<float, float, float>(code, r[ra][q], r[rb][q]);
+    }
+  }
+  const int ro = P.out_reg[0];
+  if (V == 4) ((float4*)a.out[t])[i] = make_float4(r[ro][0], r[ro][1 % V], r[ro][2 % V], r[ro][3 % V]);
+  else a.out[t][i] = r[ro][0];
+}
+// blockIdx.y = tensor. A tensor whose arrays are 16-byte aligned is walked in groups of four, its last n % 4 elements
+// one by one; the others element by element.
+__global__ void fused_elwise_multi_kernel(const FusedMultiArgs a) {
   const int t = blockIdx.y;
-  const long n = a.n[t] / V;   // V = 4 only when every tensor's size is a multiple of 4 and its arrays are 16-byte aligned
-  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
-    float r[kMultiMaxIn + CGTB_FUSED_MAX_OPS][V];
-    for (int k = 0; k < P.n_in; ++k) {
-      if (P.in_kind[k] == CGTB_FIN_F4) {
-        if (V == 4) {
-          const float4 v = ((const float4*)a.in[t][k])[i];
-          r[k][0] = v.x; r[k][1 % V] = v.y; r[k][2 % V] = v.z; r[k][3 % V] = v.w;
-        } else {
-          r[k][0] = ((const float*)a.in[t][k])[i];
-        }
-      } else {
-        const float v = P.in_kind[k] == CGTB_FIN_SCALAR_F4 ? *(const float*)a.in[t][k] : (float)*(const long*)a.in[t][k];
-#pragma unroll
-        for (int q = 0; q < V; ++q) r[k][q] = v;
-      }
-    }
-    for (int o = 0; o < P.n_ops; ++o) {
-      const int dst = P.n_in + o, ra = P.op_a[o], code = P.op_code[o];
-      if (P.op_arity[o] == 1) {
-#pragma unroll
-        for (int q = 0; q < V; ++q) r[dst][q] = unary_apply<float, float>(code, r[ra][q]);
-      } else {
-        const int rb = P.op_b[o];
-#pragma unroll
-        for (int q = 0; q < V; ++q) r[dst][q] = binary_apply<float, float, float>(code, r[ra][q], r[rb][q]);
-      }
-    }
-    const int ro = P.out_reg[0];
-    if (V == 4) ((float4*)a.out[t])[i] = make_float4(r[ro][0], r[ro][1 % V], r[ro][2 % V], r[ro][3 % V]);
-    else a.out[t][i] = r[ro][0];
+  const long n = a.n[t], stride = (long)gridDim.x * blockDim.x, i0 = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (a.vec[t]) {
+    const long nv = n >> 2;
+    for (long i = i0; i < nv; i += stride) fused_multi_apply<4>(a, t, i);
+    for (long i = (nv << 2) + i0; i < n; i += stride) fused_multi_apply<1>(a, t, i);
+  } else {
+    for (long i = i0; i < n; i += stride) fused_multi_apply<1>(a, t, i);
   }
 }
 
@@ -357,17 +368,15 @@ CGTB_API int cgtb_fused_elwise_multi(const cgtbFusedProgram* prog, int ntensors,
     for (int k = 0; k < prog->n_in; ++k) a.in[t][k] = in[(size_t)t * prog->n_in + k];
   }
   if (nmax == 0) return 0;
-  bool vec = true;
-  for (int t = 0; t < ntensors && vec; ++t) {
-    if (a.n[t] % 4 != 0 || ((uintptr_t)a.out[t] & 15) != 0) vec = false;
+  for (int t = 0; t < ntensors; ++t) {
+    bool vec = ((uintptr_t)a.out[t] & 15) == 0 && a.n[t] >= 4;
     for (int k = 0; k < prog->n_in && vec; ++k)
       if (prog->in_kind[k] == CGTB_FIN_F4 && ((uintptr_t)a.in[t][k] & 15) != 0) vec = false;
+    a.vec[t] = vec ? 1 : 0;
   }
   // the largest tensor sets the row of blocks; smaller tensors leave the tail of their row idle
-  const long per_block = 256L * (vec ? 4 : 1);
-  dim3 grid((unsigned)std::min<long>(cgtb_ceil_div(nmax, per_block), 2L * rt().sm_count), (unsigned)ntensors);
-  if (vec) CGTB_LAUNCH(fused_elwise_multi_kernel<4>, grid, 256, 0, a);
-  else CGTB_LAUNCH(fused_elwise_multi_kernel<1>, grid, 256, 0, a);
+  dim3 grid((unsigned)std::min<long>(cgtb_ceil_div(nmax, 1024), 2L * rt().sm_count), (unsigned)ntensors);
+  CGTB_LAUNCH(fused_elwise_multi_kernel, grid, 256, 0, a);
   CGTB_CHECK_LAUNCH("fused_elwise_multi");
   return 0;
 }

@@ -622,10 +622,19 @@ __global__ void lrn_backward_kernel(const T* __restrict__ x, const T* __restrict
 // loads per thread in flight; 128-bit when the plane size allows), forms the window sums from the staged tile and
 // writes its results as the same runs. Same operations in the same order as the kernels above: same bits.
 // V = elements per access (4: HW a multiple of four and 16-byte aligned arrays).
-constexpr int kLrnTP = 64;
+constexpr int kLrnTP = 32;
+// scale^(-beta) for the two exponents the networks of the reference use (cgt/nn_ops/cross_channel_lrn.py: beta 0.75;
+// its test: 0.5) from square roots, which are correctly rounded: s^-0.5 = 1 / sqrt(s), s^-0.75 = 1 / (sqrt(s) * sqrt(sqrt(s))).
+// A handful of instructions instead of the hundred of powf, to within 2 units in the last place of it. mode 0: powf.
+__device__ __forceinline__ float lrn_pow(float s, float negative_beta, int mode) {
+  if (mode == 1) return __fdiv_rn(1.0f, __fsqrt_rn(s));
+  if (mode == 2) { const float r = __fsqrt_rn(s); return __fdiv_rn(1.0f, __fmul_rn(r, __fsqrt_rn(r))); }
+  return pow(s, negative_beta);
+}
+static int lrn_pow_mode(double beta) { return beta == 0.5 ? 1 : (beta == 0.75 ? 2 : 0); }
 template <int V>
 __global__ void __launch_bounds__(256) lrn_forward_tile_kernel(const float* __restrict__ x, float* __restrict__ top, float* __restrict__ scale,
-                                                             int C, int HW, int size, float alpha_over_size, float negative_beta) {
+                                                             int C, int HW, int size, float alpha_over_size, float negative_beta, int pmode) {
   extern __shared__ float sx[];  // [C][kLrnTP]
   constexpr int PT = kLrnTP / V;           // threads along the pixels of a tile
   constexpr int CSTEP = 256 / PT;          // channels covered by one pass of the block
@@ -676,7 +685,7 @@ __global__ void __launch_bounds__(256) lrn_forward_tile_kernel(const float* __re
 #pragma unroll
     for (int q = 0; q < V; ++q) {
       s[q] = (float)(1. + (double)(acc[q] * alpha_over_size));
-      y[q] = sx[c * kLrnTP + p + q] * pow(s[q], negative_beta);
+      y[q] = sx[c * kLrnTP + p + q] * lrn_pow(s[q], negative_beta, pmode);
     }
     const size_t o = base + (size_t)c * HW;
     if (V == 4) {
@@ -693,7 +702,7 @@ template <int V>
 __global__ void __launch_bounds__(256) lrn_backward_tile_kernel(const float* __restrict__ x, const float* __restrict__ top,
                                                               const float* __restrict__ scale, const float* __restrict__ gtop,
                                                               float* __restrict__ gx, int C, int HW, int size, float negative_beta,
-                                                              float cache_ratio) {
+                                                              float cache_ratio, int pmode) {
   extern __shared__ float sr[];  // [C][kLrnTP]: gtop * top / scale
   constexpr int PT = kLrnTP / V;
   constexpr int CSTEP = 256 / PT;
@@ -754,7 +763,7 @@ __global__ void __launch_bounds__(256) lrn_backward_tile_kernel(const float* __r
       for (int q = 0; q < V; ++q) acc[q] += sr[k * kLrnTP + p + q];
     }
 #pragma unroll
-    for (int q = 0; q < V; ++q) r[q] = g[q] * pow(sc[q], negative_beta) - cache_ratio * xv[q] * acc[q];
+    for (int q = 0; q < V; ++q) r[q] = g[q] * lrn_pow(sc[q], negative_beta, pmode) - cache_ratio * xv[q] * acc[q];
     if (V == 4) *reinterpret_cast<float4*>(gx + o) = make_float4(r[0], r[1 % V], r[2 % V], r[3 % V]);
     else gx[o] = r[0];
   }
@@ -786,11 +795,11 @@ CGTB_API int cgtb_lrn_forward(int dtype, const void* x, long N, int C, int H, in
     if (lrn_vec4(HW, {x, top, scale})) {
       if (lrn_smem_attr(lrn_forward_tile_kernel<4>, smem)) return 1;
       CGTB_LAUNCH(lrn_forward_tile_kernel<4>, tgrid, 256, smem, (const float*)x, (float*)top, (float*)scale, C, HW, size,
-                  (float)(alpha / size), (float)(-beta));
+                  (float)(alpha / size), (float)(-beta), lrn_pow_mode(beta));
     } else {
       if (lrn_smem_attr(lrn_forward_tile_kernel<1>, smem)) return 1;
       CGTB_LAUNCH(lrn_forward_tile_kernel<1>, tgrid, 256, smem, (const float*)x, (float*)top, (float*)scale, C, HW, size,
-                  (float)(alpha / size), (float)(-beta));
+                  (float)(alpha / size), (float)(-beta), lrn_pow_mode(beta));
     }
     CGTB_CHECK_LAUNCH("lrn_forward");
     return 0;
@@ -823,11 +832,11 @@ CGTB_API int cgtb_lrn_backward(int dtype, const void* x, const void* top, const 
     if (lrn_vec4(HW, {x, top, scale, gtop, gx})) {
       if (lrn_smem_attr(lrn_backward_tile_kernel<4>, smem)) return 1;
       CGTB_LAUNCH(lrn_backward_tile_kernel<4>, tgrid, 256, smem, (const float*)x, (const float*)top, (const float*)scale,
-                  (const float*)gtop, (float*)gx, C, HW, size, (float)(-beta), (float)(2. * alpha * beta / size));
+                  (const float*)gtop, (float*)gx, C, HW, size, (float)(-beta), (float)(2. * alpha * beta / size), lrn_pow_mode(beta));
     } else {
       if (lrn_smem_attr(lrn_backward_tile_kernel<1>, smem)) return 1;
       CGTB_LAUNCH(lrn_backward_tile_kernel<1>, tgrid, 256, smem, (const float*)x, (const float*)top, (const float*)scale,
-                  (const float*)gtop, (float*)gx, C, HW, size, (float)(-beta), (float)(2. * alpha * beta / size));
+                  (const float*)gtop, (float*)gx, C, HW, size, (float)(-beta), (float)(2. * alpha * beta / size), lrn_pow_mode(beta));
     }
     CGTB_CHECK_LAUNCH("lrn_backward");
     return 0;
