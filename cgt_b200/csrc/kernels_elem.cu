@@ -369,13 +369,16 @@ CGTB_API int cgtb_fused_elwise_multi(const cgtbFusedProgram* prog, int ntensors,
   }
   if (nmax == 0) return 0;
   for (int t = 0; t < ntensors; ++t) {
-    bool vec = ((uintptr_t)a.out[t] & 15) == 0 && a.n[t] >= 4;
+    // groups of four only for large tensors: a small one is bound by the latency of one thread's chain of operations
+    // (run from the register machine's local memory), which a group of four makes four times as long
+    bool vec = ((uintptr_t)a.out[t] & 15) == 0 && a.n[t] >= (1L << 18);
     for (int k = 0; k < prog->n_in && vec; ++k)
       if (prog->in_kind[k] == CGTB_FIN_F4 && ((uintptr_t)a.in[t][k] & 15) != 0) vec = false;
     a.vec[t] = vec ? 1 : 0;
   }
   // the largest tensor sets the row of blocks; smaller tensors leave the tail of their row idle
-  dim3 grid((unsigned)std::min<long>(cgtb_ceil_div(nmax, 1024), 2L * rt().sm_count), (unsigned)ntensors);
+  const long per_block = nmax >= (1L << 18) ? 1024 : 256;
+  dim3 grid((unsigned)std::min<long>(cgtb_ceil_div(nmax, per_block), 2L * rt().sm_count), (unsigned)ntensors);
   CGTB_LAUNCH(fused_elwise_multi_kernel, grid, 256, 0, a);
   CGTB_CHECK_LAUNCH("fused_elwise_multi");
   return 0;
