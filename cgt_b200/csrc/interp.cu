@@ -96,6 +96,7 @@ struct cgtbInterp {
   bool steady = false;                  // this run repeats the previous one as far as host bookkeeping goes
   bool host_dirty = false;              // a host data instruction of this run produced a new value
   bool prev_run_ok = false;
+  uint64_t args_read_in_place = ~0ull;  // arguments whose device buffer a captured instruction reads directly
   long last_host_ns = 0;                // host time of the last run up to the final wait for the stream
   long steady_runs = 0;
 };
@@ -252,14 +253,25 @@ CGTB_API cgtbInterp* cgtb_interp_new(cgtbGraph* g, int n_out, const long* out_lo
   {
     // Bookkeeping instructions that see an argument object directly or through other bookkeeping (views, tuples,
     // sizes, allocations shaped by them) cannot be skipped in steady runs: the caller passes new objects every time.
-    std::vector<char> from_arg((size_t)g->n_locs, 0);
+    // from_arg[loc]: the arguments (bit i = argument i, the last bit stands for all beyond 62) that location loc holds
+    // or views. An argument that a device instruction reads in place must keep its buffer for a run to be steady (the
+    // captured graphs hold that address); one that only copies (Transport, a barrier) and bookkeeping look at may
+    // move: a batch handed over in alternating staging buffers is still a steady run.
+    std::vector<uint64_t> from_arg((size_t)g->n_locs, 0);
+    uint64_t in_place = 0;
     for (auto& in : g->instrs) {
+      if (in.klass == kDevice) {
+        for (auto& r : in.reads) in_place |= from_arg[(size_t)r.idx];
+        in_place |= from_arg[(size_t)in.write.idx];
+        continue;
+      }
       if (in.klass != kMeta) continue;
-      bool dep = in.kind == kLoadArgument;
-      for (auto& r : in.reads) dep = dep || from_arg[(size_t)r.idx];
-      in.arg_view = dep;
-      if (dep) from_arg[(size_t)in.write.idx] = 1;
+      uint64_t dep = in.kind == kLoadArgument ? (1ull << (in.arg_index < 63 ? in.arg_index : 63)) : 0;
+      for (auto& r : in.reads) dep |= from_arg[(size_t)r.idx];
+      in.arg_view = dep != 0;
+      if (dep) from_arg[(size_t)in.write.idx] |= dep;
     }
+    it->args_read_in_place = in_place;
   }
   build_spans(it);
   return it;
@@ -688,22 +700,24 @@ CGTB_API int cgtb_interp_run(cgtbInterp* it, cgtbObject* args_obj, cgtbObject** 
     // as operands at launch time); for large host arrays only the shape (they are copied by a Transport)
     std::vector<uint64_t> sig;
     sig.reserve(16);
-    std::vector<cgtObject*> stack;
-    for (int i = 0; i < args->len; ++i) stack.push_back(args->getitem(i));
+    std::vector<std::pair<cgtObject*, bool>> stack;   // (object, its device address matters)
+    for (int i = 0; i < args->len; ++i)
+      stack.push_back({args->getitem(i), ((it->args_read_in_place >> (i < 63 ? i : 63)) & 1ull) != 0});
     while (!stack.empty()) {
-      cgtObject* o = stack.back();
+      cgtObject* o = stack.back().first;
+      const bool pinned = stack.back().second;
       stack.pop_back();
       if (!o) { sig.push_back(0); continue; }
       if (o->kind() == cgtObject::TupleKind) {
         cgtTuple* t = (cgtTuple*)o;
         sig.push_back(0x7475706cull + (uint64_t)t->len);
-        for (int i = 0; i < t->len; ++i) stack.push_back(t->getitem(i));
+        for (int i = 0; i < t->len; ++i) stack.push_back({t->getitem(i), pinned});
         continue;
       }
       cgtArray* a = (cgtArray*)o;
       sig.push_back(((uint64_t)a->ndim() << 16) | ((uint64_t)a->dtype() << 8) | (uint64_t)a->devtype());
       for (int d = 0; d < a->ndim(); ++d) sig.push_back((uint64_t)a->shape()[d]);
-      if (a->devtype() == cgtGPU) sig.push_back((uint64_t)(uintptr_t)a->data());
+      if (a->devtype() == cgtGPU) { if (pinned) sig.push_back((uint64_t)(uintptr_t)a->data()); }
       else if (a->nbytes() <= 64 && a->data()) {
         uint64_t buf[8] = {0};
         memcpy(buf, a->data(), (size_t)a->nbytes());
