@@ -205,6 +205,103 @@ def view_leading_slices(outputs, updatetargs, node2shape):
     return _rewire(outputs, updatetargs, replace)
 
 
+def batch_summed_products(outputs, updatetargs, node2shape):
+    """Sums over many terms of one form, as an unrolled recurrent network's parameter gradients arrive (one term per time
+    step, added one after the other): sum_t Mul22{T,N}(a_t, b_t) with equal shapes is ONE product of the operands
+    concatenated along the contracted axis, Mul22{T,N}(concat_t a_t, concat_t b_t); sum_t Sum{0}(g_t) is
+    Sum{0}(concat_t g_t). Fifty products and forty-nine additions of [in, out] matrices become two row concatenations
+    (one launch each, shared between the sums that use the same operands) and one product with a fifty times longer
+    contraction. The order of the float32 additions changes: float32 tolerance against the term-by-term graph."""
+    MIN_TERMS, MAX_PIECES = 4, 64
+    all_out = list(outputs) + list(updatetargs)
+    nodes = core.topsorted(all_out)
+    children = defaultdict(list)
+    for node in nodes:
+        for par in node.parents:
+            children[par].append(node)
+    out_set = set(all_out)
+
+    def is_add(node):
+        return (not node.is_input() and isinstance(node.op, core.ElwiseBinary) and node.op.opname == "+" and node.ndim == 2
+                and node.dtype == "f4" and all(par.ndim == 2 for par in node.parents))
+
+    def leaves_of(node, acc):
+        for par in node.parents:
+            if is_add(par) and len(children[par]) == 1 and par not in out_set:
+                leaves_of(par, acc)
+            else:
+                acc.append(par)
+
+    def form(leaf):
+        if leaf.is_input() or len(children[leaf]) != 1 or leaf in out_set or leaf.dtype != "f4":
+            return None
+        if isinstance(leaf.op, core.Mul22) and leaf.op.tA and not leaf.op.tB:
+            sa, sb = _static_shape(node2shape[leaf.parents[0]]), _static_shape(node2shape[leaf.parents[1]])
+            if sa is not None and sb is not None and all(p.dtype == "f4" for p in leaf.parents):
+                return ("mul22", sa, sb)
+        if isinstance(leaf.op, core.Sum) and tuple(leaf.op.axes) == (0,):
+            sx = _static_shape(node2shape[leaf.parents[0]])
+            if sx is not None and len(sx) == 2 and leaf.parents[0].dtype == "f4":
+                return ("sum0", sx)
+        return None
+
+    concat_cache = {}
+
+    def concat_rows(parts):
+        key = tuple(id(q) for q in parts)
+        if key not in concat_cache:
+            shp = _static_shape(node2shape[parts[0]])
+            new = core.Result(core.Concatenate(0), list(parts))
+            node2shape[new] = [core.cgt.constant(np.array(shp[0] * len(parts), "i8")), core.cgt.constant(np.array(shp[1], "i8"))]
+            concat_cache[key] = new
+        return concat_cache[key]
+
+    replace = {}
+    covered = set()
+    for node in reversed(nodes):   # the root of an addition tree comes before its inner nodes
+        if node in covered or not is_add(node):
+            continue
+        leaves = []
+        leaves_of(node, leaves)
+        stack = [node]
+        while stack:
+            q = stack.pop()
+            covered.add(q)
+            stack.extend(par for par in q.parents if is_add(par) and len(children[par]) == 1 and par not in out_set)
+        groups = defaultdict(list)
+        for leaf in leaves:
+            f = form(leaf)
+            if f is not None:
+                groups[f].append(leaf)
+        terms, batched = [], set()
+        for (f, members) in groups.items():
+            if len(members) < MIN_TERMS:
+                continue
+            for lo in range(0, len(members), MAX_PIECES):
+                chunk = members[lo:lo + MAX_PIECES]
+                if len(chunk) < 2:
+                    continue
+                if f[0] == "mul22":
+                    new = core.Result(core.Mul22(True, False), [concat_rows([m.parents[0] for m in chunk]), concat_rows([m.parents[1] for m in chunk])])
+                else:
+                    new = core.Result(core.Sum((0,)), [concat_rows([m.parents[0] for m in chunk])])
+                node2shape[new] = node2shape[chunk[0]]
+                terms.append(new)
+                batched.update(chunk)
+        if not batched:
+            continue
+        terms += [leaf for leaf in leaves if leaf not in batched]
+        total = terms[0]
+        for t in terms[1:]:
+            total = core.Result(core.ElwiseBinary("+", (False, False)), [total, t])
+            node2shape[total] = node2shape[node]
+        total.props.update(node.props)
+        replace[node] = total
+    if not replace:
+        return list(outputs), list(updatetargs)
+    return _rewire(outputs, updatetargs, replace)
+
+
 def fuse_slice_sums(outputs, updatetargs, node2shape):
     """Sums of IncSli(zeros, start, stop, 1, y) over disjoint column ranges of one float32 matrix -> ScatterCols.
 
@@ -1365,6 +1462,8 @@ def apply_graph_rewrites(outputs_simple, updatetargs_simple, node2shape):
         outputs_simple, updatetargs_simple = view_leading_slices(outputs_simple, updatetargs_simple, node2shape)
     if config["fuse_slice_sums"]:
         outputs_simple, updatetargs_simple = fuse_slice_sums(outputs_simple, updatetargs_simple, node2shape)
+    if config["batch_summed_products"]:
+        outputs_simple, updatetargs_simple = batch_summed_products(outputs_simple, updatetargs_simple, node2shape)
     if config["fuse_elementwise"]:
         if config["fuse_rows"]:
             outputs_simple, updatetargs_simple = fuse_elementwise(outputs_simple, updatetargs_simple, node2shape, rows=True)

@@ -1085,6 +1085,47 @@ __global__ void concat_part_kernel(long total, long n_in, long n_out, long inner
     out[(o * n_out + pos + i) * inner + k] = in[f];
   }
 }
+// Concatenation along axis 0: every piece is one contiguous run. One launch for all pieces (blockIdx.y = piece).
+constexpr int kConcatMax = 64;
+struct ConcatRowsArgs {
+  const unsigned char* src[kConcatMax];
+  long bytes[kConcatMax], off[kConcatMax];
+  unsigned char* out;
+};
+__global__ void concat_rows_kernel(const ConcatRowsArgs a) {
+  const int t = blockIdx.y;
+  const unsigned char* src = a.src[t];
+  unsigned char* dst = a.out + a.off[t];
+  const long n = a.bytes[t], stride = (long)gridDim.x * blockDim.x, i0 = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  if ((((uintptr_t)src | (uintptr_t)dst | (uintptr_t)n) & 15) == 0) {
+    for (long i = i0; i < (n >> 4); i += stride) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+  } else if ((((uintptr_t)src | (uintptr_t)dst | (uintptr_t)n) & 3) == 0) {
+    for (long i = i0; i < (n >> 2); i += stride) reinterpret_cast<uint32_t*>(dst)[i] = reinterpret_cast<const uint32_t*>(src)[i];
+  } else {
+    for (long i = i0; i < n; i += stride) dst[i] = src[i];
+  }
+}
+CGTB_API int cgtb_concat_rows(int n, const void* const* pieces, const long* bytes, void* out) {
+  if (!require_runtime("cgtb_concat_rows")) return 1;
+  if (n < 1 || n > kConcatMax) return fail("cgtb_concat_rows: between 1 and %d pieces", kConcatMax);
+  ConcatRowsArgs a;
+  a.out = (unsigned char*)out;
+  long off = 0, nmax = 0;
+  for (int i = 0; i < n; ++i) {
+    if (bytes[i] < 0) return fail("cgtb_concat_rows: negative size");
+    a.src[i] = (const unsigned char*)pieces[i];
+    a.bytes[i] = bytes[i];
+    a.off[i] = off;
+    off += bytes[i];
+    nmax = std::max(nmax, bytes[i]);
+  }
+  if (nmax == 0) return 0;
+  dim3 grid((unsigned)std::max<long>(1, std::min<long>(cgtb_ceil_div(nmax, 16 * 256), 32)), (unsigned)n);
+  CGTB_LAUNCH(concat_rows_kernel, grid, 256, 0, a);
+  CGTB_CHECK_LAUNCH("concat_rows");
+  return 0;
+}
+
 CGTB_API int cgtb_concat_part(int dtype, long outer, long n_in, long n_out, long inner, long pos, const void* in, void* out) {
   if (!require_runtime("cgtb_concat_part")) return 1;
   long total = outer * n_in * inner;

@@ -573,6 +573,22 @@ struct ConcatClosure { int axis; int n_in; };
 OP_BYREF(cgtb_op_concatenate) {
   ConcatClosure* cl = (ConcatClosure*)cl0;
   cgtArray* w = ARR(write0);
+  if (cl->axis == 0 && cl->n_in >= 2 && cl->n_in <= 64) {
+    // pieces are contiguous runs: one launch for all of them
+    const void* pieces[64];
+    long bytes[64], total = 0;
+    for (int i = 0; i < cl->n_in; ++i) {
+      cgtArray* x = ARR(reads[i]);
+      if (!all_gpu({x, w})) { fail("Concatenate: operands must be on the GPU"); return; }
+      if (x->dtype() != w->dtype()) { fail("Concatenate: operands of different dtypes"); return; }
+      pieces[i] = x->data();
+      bytes[i] = x->nbytes();
+      total += bytes[i];
+    }
+    if (total != w->nbytes()) { fail("Concatenate: the parts have %ld bytes, the result %ld", total, (long)w->nbytes()); return; }
+    cgtb_concat_rows(cl->n_in, pieces, bytes, w->data());
+    return;
+  }
   long pos = 0;
   for (int i = 0; i < cl->n_in; ++i) {
     cgtArray* x = ARR(reads[i]);

@@ -328,6 +328,9 @@ int cgtb_incsli(int dtype, long outer, long n_x, long inner, long start, long st
 int cgtb_getflat(int dtype, long n, const void* x, const int64_t* k, void* out);
 int cgtb_incflat(int dtype, long xsize, long n, const void* x, const int64_t* k, const void* p, void* out);
 int cgtb_concat_part(int dtype, long outer, long n_in, long n_out, long inner, long pos, const void* in, void* out);
+/* Concatenate along axis 0 in ONE launch: n <= 64 contiguous pieces of bytes[i] bytes are copied back to back into out
+ * (np.concatenate of C-contiguous arrays along their first axis, cgt/core.py:1467-1509). */
+int cgtb_concat_rows(int n, const void* const* pieces, const long* bytes, void* out);
 int cgtb_fill(int dtype, long n, double fvalue, long ivalue, void* out);
 
 /* ------------------------------------------------------------------------------------------------
