@@ -609,7 +609,30 @@ def fuse_elementwise(outputs, updatetargs, node2shape, rows=False):
                 emit(mem[:len(mem) // 2])
                 emit(mem[len(mem) // 2:])
             return
-        if not outs or (len(outs) > 1 and any(o in target_set for o in outs)):
+        if not outs:
+            return
+        if len(outs) > 1 and any(o in target_set for o in outs):
+            # an update target must be the only result of its kernel (it is written into the variable's own memory):
+            # one piece per target, holding the members that this target is the first to need (optimizers with several
+            # state variables per parameter: one chain per state variable); halves when that separates nothing
+            owner = {}
+            for t in [node for node in mem if node in target_set]:   # in topological order
+                stack = [t]
+                while stack:
+                    q = stack.pop()
+                    if q in owner:
+                        continue
+                    owner[q] = t
+                    stack.extend(par for par in q.parents if par in memset and par not in owner)
+            pieces = defaultdict(list)
+            for node in mem:
+                pieces[owner.get(node)].append(node)
+            if len(pieces) > 1:
+                for piece in pieces.values():   # each piece: the members that its target needs first, in order
+                    emit(piece)
+            elif len(mem) >= 2:
+                emit(mem[:len(mem) // 2])
+                emit(mem[len(mem) // 2:])
             return
         program, result_reg = [], {}
         for (j, node) in enumerate(mem):
@@ -1401,7 +1424,9 @@ def merge_parameter_updates(eg, update_locs):
             continue
         key = (tuple(op.program), tuple(op.in_kinds), tuple(op.out_regs))
         groups[key].append(i)
-    for (key, idxs) in groups.items():
+    # groups whose last member comes latest first: once the chains that READ a state variable's new value (the
+    # parameter's own update) have moved to the end, the chains that write it can move past their old readers
+    for (key, idxs) in sorted(groups.items(), key=lambda kv: -kv[1][-1]):
         last = idxs[-1]
         movable = []
         for i in idxs:
