@@ -259,6 +259,40 @@ def test_odd_column_rows_are_padded_for_both_products():
     assert [n for n in core.topsorted(o2 + u2) if not n.is_input() and isinstance(n.op, im2col_ops.ConvWgrad)] == wg
 
 
+def test_recurrent_graph_rewrites():
+    """The rewrites aimed at unrolled recurrent networks, on the LSTM configuration with six time steps (no GPU needed:
+    only the rewritten graph is inspected). x[t] becomes a view, the gate slices are read in place by the fused chains (no
+    GetSli is left), the gradients of the slices are placed by ScatterCols (no IncSli / Fill is left), the softmax
+    chains are FusedRows, and the per-time-step weight and bias gradient terms are one product / one reduction over
+    row-concatenated operands per parameter."""
+    T = 6
+    cfg = configs.build_lstm(seq_len=T, batch=8)
+    outs, _usrc, utargs, analysis = compilation.simplify_for_execution([cfg.loss] + list(cfg.extra_outputs), cfg.updates)
+    n2s = analysis["node2shape"]
+    before = [n for n in core.topsorted(outs + utargs) if not n.is_input()]
+    o, u = compilation.apply_graph_rewrites(outs, utargs, n2s)
+    nodes = [n for n in core.topsorted(o + u) if not n.is_input()]     # topsorted raises on a cycle
+    count = lambda pred: sum(1 for n in nodes if pred(n))
+    assert count(lambda n: isinstance(n.op, core.GetSli)) == 0
+    assert count(lambda n: isinstance(n.op, core.IncSli)) == 0
+    assert count(lambda n: isinstance(n.op, core.LeadingSlice)) == 2 * T          # x[t] and targ[t]
+    assert count(lambda n: isinstance(n.op, core.ScatterCols)) == 2 * 2 * T       # two per layer and time step
+    assert count(lambda n: isinstance(n.op, core.FusedRows)) == T
+    wgrads = [n for n in nodes if isinstance(n.op, core.Mul22) and n.op.tA and not n.op.tB]
+    assert len(wgrads) == 5 and all(isinstance(p.op, core.Concatenate) and len(p.parents) == T for n in wgrads for p in n.parents)
+    assert sum(1 for n in before if isinstance(n.op, core.Mul22) and n.op.tA and not n.op.tB) == 5 * T
+    views = [n for n in nodes if isinstance(n.op, core.FusedElwise) and n.op.views]
+    assert views and all(n.op.static_shape is not None and 7 in n.op.in_kinds for n in views)
+    assert len(nodes) < len(before) // 2
+    # every rewrite has its switch: with all of them off the graph is the simplified one
+    off = dict(fuse_slice_views=False, fuse_slice_sums=False, batch_summed_products=False, fuse_rows=False, fuse_elementwise=False,
+               fuse_conv_dgrad=False, fuse_conv_grad_input=False)
+    with cgt.scoped_update_config(**off):
+        o2, u2 = compilation.apply_graph_rewrites(*compilation.simplify_for_execution([cfg.loss] + list(cfg.extra_outputs), cfg.updates)[0:3:2], n2s)
+        assert not any(isinstance(n.op, (core.ScatterCols, core.LeadingSlice, core.FusedRows, core.FusedElwise))
+                       for n in core.topsorted(o2 + u2) if not n.is_input())
+
+
 @pytest.mark.parametrize("name,kw", [("cifar", dict(batch=4)), ("mlp", dict(batch=8)), ("lstm", dict(seq_len=3, batch=2))])
 def test_edge_copies_are_scheduled_at_the_edges(name, kw):
     """compilation._transport_schedule: the uploads of the function arguments come before every device Op, and a
