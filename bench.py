@@ -480,15 +480,15 @@ def run_b200(args):
 
 
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum, bytes per launch) of an entry point's main kernel from an
-# ncu capture at the shape listed in `per_kernel`; the summaries are under profiles/.
+# ncu capture (--set full, cold launches) at the shape listed in `per_kernel`.
 NCU_TRAFFIC = {
     "cgtb_conv_wgrad": 7418112 + 1024,
     "cgtb_conv_fwd_bias_relu_bank": 3941888,
 }
 NCU_TRAFFIC_NOTE = {
-    "cgtb_conv_wgrad": "sgemm_tma_kernel<1,1,2> at the conv2 shape, one cold launch (profiles/conv_wgrad_conv2_sgemm_tma.md): every operand "
+    "cgtb_conv_wgrad": "sgemm_tma_kernel<1,1,2> at the conv2 shape, one cold launch under ncu --set full: every operand "
                        "byte is read from DRAM once; the 0.1 MB result had not left L2 when the launch ended",
-    "cgtb_conv_fwd_bias_relu_bank": "conv_tsa_kernel at the conv2 shape, one cold launch (profiles/conv_tsa_conv2_forward.md): the input "
+    "cgtb_conv_fwd_bias_relu_bank": "conv_tsa_kernel at the conv2 shape, one cold launch under ncu --set full: the input "
                                     "is read once; the 4.6 MB of results had not left L2 when the launch ended",
 }
 
