@@ -52,7 +52,7 @@ def _declare(lib):
         "cgtb_allreduce_sum": (ci, [ci, ci, ctypes.POINTER(vp), ctypes.POINTER(vp), c_long_p]),
         "cgtb_peer_alloc": (ci, [cl, ctypes.c_char_p]), "cgtb_peer_open": (ci, [ctypes.c_char_p, ci, ci]),
         "cgtb_peer_close": (ci, []), "cgtb_peer_world": (ci, []), "cgtb_peer_slot_bytes": (cl, []),
-        "cgtb_peer_set_wait_cycles": (ci, [cl]), "cgtb_peer_timing": (ci, [c_long_p]),
+        "cgtb_peer_set_wait_cycles": (ci, [cl]), "cgtb_peer_timing": (ci, [c_long_p]), "cgtb_peer_set_two_phase_bytes": (ci, [cl]),
         "cgtb_peer_allreduce_sum": (ci, [ci, ctypes.POINTER(vp), ctypes.POINTER(vp), c_long_p]),
         "cgtb_peer_selftest_open": (ci, [cl]), "cgtb_peer_selftest_post": (ci, [vp, cl]),
         "cgtb_alloc": (vp, [ci, cl]), "cgtb_free": (None, [ci, vp]), "cgtb_memcpy": (ci, [ci, ci, vp, vp, cl, ci]),

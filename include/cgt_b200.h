@@ -350,7 +350,7 @@ int cgtb_comm_destroy(void);
 int cgtb_allreduce_sum(int dtype, int n, const void* const* in, void* const* out, const long* counts);
 
 /* The same exchange for small float32 payloads as ONE kernel over peer memory (no library collective, so the call is
- * an ordinary launch that a CUDA graph can hold). Every rank: cgtb_peer_alloc (its symmetric buffer: two slots of
+ * an ordinary launch that a CUDA graph can hold). Every rank: cgtb_peer_alloc (its symmetric buffer: two data and two result slots of
  * slot_bytes; returns the 64-byte cudaIpc handle), the host side gathers the handles of all ranks, cgtb_peer_open maps
  * them (ranks on one node, at most 8). cgtb_peer_allreduce_sum: out[i] = sum over ranks of in[i], summed in rank order on
  * every rank (replicas stay bit-identical). The kernel's waits for the other ranks are bounded by a cycle budget
@@ -367,6 +367,10 @@ int cgtb_peer_close(void);
 int cgtb_peer_world(void);
 long cgtb_peer_slot_bytes(void);
 int cgtb_peer_set_wait_cycles(long cycles);
+/* payloads of more than `bytes` (default one megabyte; 0: every payload) take the two-phase kernel: every rank sums one
+ * slice of the elements over all ranks into its result slot, then all ranks collect the slices; each element crosses
+ * the links twice whatever the number of ranks instead of once per peer */
+int cgtb_peer_set_two_phase_bytes(long bytes);
 /* out3: calls so far, nanoseconds spent until every rank's flag was seen, nanoseconds start to end (block 0's clock,
  * summed over the calls): tells waiting for slower ranks from the exchange itself */
 int cgtb_peer_timing(long* out3);

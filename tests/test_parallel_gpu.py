@@ -24,8 +24,10 @@ def _n_gpus():
     return torch.cuda.device_count()
 
 
-@pytest.mark.parametrize("config", ["mlp", "cifar"])
-def test_two_gpu_ranks_match_one_gpu(rt, tmp_path, config):
+@pytest.mark.parametrize("config,two_phase", [("mlp", False), ("cifar", False), ("cifar", True)])
+def test_two_gpu_ranks_match_one_gpu(rt, tmp_path, config, two_phase):
+    """two_phase: every payload goes through the two-phase peer kernel (each rank sums one slice, all collect the slices),
+    which otherwise serves payloads beyond a megabyte."""
     if _n_gpus() < 2:
         pytest.skip("needs two GPUs")
     world, per_rank = 2, 8
@@ -34,6 +36,8 @@ def test_two_gpu_ranks_match_one_gpu(rt, tmp_path, config):
     for rank in range(world):
         env = dict(os.environ, RANK=str(rank), LOCAL_RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1",
                    MASTER_PORT=str(port), DP_OUT=str(tmp_path / "params"), DP_BACKEND="gpu", DP_CONFIG=config)
+        if two_phase:
+            env["CGTB_PEER_TWO_PHASE_BYTES"] = "0"
         procs.append(subprocess.Popen([sys.executable, osp.join(HERE, "dp_worker.py")], env=env, stdout=subprocess.PIPE,
                                       stderr=subprocess.PIPE, text=True))
     outs = []
