@@ -302,6 +302,102 @@ def batch_summed_products(outputs, updatetargs, node2shape):
     return _rewire(outputs, updatetargs, replace)
 
 
+def batch_shared_weight_products(outputs, updatetargs, node2shape):
+    """Products that share their right operand and do not need each other: Mul22{N,N}(a_t, W) or Mul22{N,T}(a_t, W) for
+    many t with a_t of one shape, none of which depends on another's result (the input-to-hidden products of an unrolled
+    recurrent layer over all time steps, the output projection, the matching data-gradient products) become ONE product
+    of the row-concatenated a_t with W; every original result is a LeadingSlice view of it. When the a_t are the
+    consecutive leading slices of one array, that array itself (reshaped) is the concatenation. Same sums in the same
+    order per output element as far as the kernels' tiling allows: float32 tolerance."""
+    MIN_TERMS, MAX_PIECES = 4, 64
+    all_out = list(outputs) + list(updatetargs)
+    nodes = core.topsorted(all_out)
+    out_set = set(all_out)
+    topo = dict((n, i) for (i, n) in enumerate(nodes))
+    groups = defaultdict(list)
+    for node in nodes:
+        if node.is_input() or not isinstance(node.op, core.Mul22) or node.op.tA or node in out_set or node.dtype != "f4":
+            continue
+        (a, w) = node.parents
+        sa, sw = _static_shape(node2shape[a]), _static_shape(node2shape[w])
+        if sa is None or sw is None or a.dtype != "f4" or w.dtype != "f4":
+            continue
+        groups[(id(w), node.op.tB, sa, sw)].append(node)
+
+    def depends_on_any(start, targets, floor):
+        """does `start` depend on a node of `targets`? (nodes before topological index `floor` cannot)"""
+        seen, stack = set(), [start]
+        while stack:
+            q = stack.pop()
+            if q in seen or topo[q] < floor:
+                continue
+            seen.add(q)
+            if q in targets:
+                return True
+            stack.extend(q.parents)
+        return False
+
+    def as_whole_array(parts):
+        """the array of which `parts` are, in order, the consecutive leading slices (through reshapes to [rows, cols]);
+        None otherwise"""
+        src, pos = None, 0
+        for q in parts:
+            while not q.is_input() and isinstance(q.op, core.Reshape):
+                q = q.parents[0]
+            if q.is_input() or not isinstance(q.op, core.LeadingSlice):
+                return None
+            (x, start, stop) = q.parents
+            if src is None:
+                src = x
+            if x is not src or not isinstance(start.op, core.Constant) or not isinstance(stop.op, core.Constant):
+                return None
+            if int(start.op.value) != pos:
+                return None
+            pos = int(stop.op.value)
+        shp = _static_shape(node2shape[src]) if src is not None else None
+        return src if shp is not None and pos == shp[0] else None
+
+    # row concatenations that the graph already holds (made for the summed products of the same operands)
+    existing = {}
+    for node in nodes:
+        if not node.is_input() and isinstance(node.op, core.Concatenate) and node.op.axis == 0:
+            existing[tuple(id(q) for q in node.parents)] = node
+    replace = {}
+    for (key, members) in groups.items():
+        if len(members) < MIN_TERMS:
+            continue
+        memberset = set(members)
+        floor = min(topo[m] for m in members)
+        if any(depends_on_any(m.parents[0], memberset, floor) for m in members):
+            continue
+        (rows, cols) = key[2]
+        for lo in range(0, len(members), MAX_PIECES):
+            chunk = members[lo:lo + MAX_PIECES]
+            if len(chunk) < 2:
+                continue
+            parts = [m.parents[0] for m in chunk]
+            total = core.cgt.constant(np.array(rows * len(chunk), "i8"))
+            ncol = core.cgt.constant(np.array(cols, "i8"))
+            whole = as_whole_array(parts)
+            if whole is not None:
+                acat = core.Result(core.Reshape(), [whole, total, ncol])
+            else:
+                acat = existing.get(tuple(id(q) for q in parts)) or core.Result(core.Concatenate(0), parts)
+            node2shape[acat] = [total, ncol]
+            z = core.Result(core.Mul22(False, chunk[0].op.tB), [acat, chunk[0].parents[1]])
+            zcols = _static_shape(node2shape[chunk[0]])[1]
+            node2shape[z] = [total, core.cgt.constant(np.array(zcols, "i8"))]
+            for (t, m) in enumerate(chunk):
+                view = core.Result(core.LeadingSlice(), [z, core.cgt.constant(np.array(t * rows, "i8")),
+                                                         core.cgt.constant(np.array((t + 1) * rows, "i8"))])
+                node2shape[view] = node2shape[m]
+                view.props.update(m.props)
+                replace[m] = view
+    if not replace:
+        return list(outputs), list(updatetargs)
+    return _rewire(outputs, updatetargs, replace)
+
+
 def fuse_slice_sums(outputs, updatetargs, node2shape):
     """Sums of IncSli(zeros, start, stop, 1, y) over disjoint column ranges of one float32 matrix -> ScatterCols.
 
@@ -1489,6 +1585,7 @@ def apply_graph_rewrites(outputs_simple, updatetargs_simple, node2shape):
         outputs_simple, updatetargs_simple = fuse_slice_sums(outputs_simple, updatetargs_simple, node2shape)
     if config["batch_summed_products"]:
         outputs_simple, updatetargs_simple = batch_summed_products(outputs_simple, updatetargs_simple, node2shape)
+        outputs_simple, updatetargs_simple = batch_shared_weight_products(outputs_simple, updatetargs_simple, node2shape)
     if config["fuse_elementwise"]:
         if config["fuse_rows"]:
             outputs_simple, updatetargs_simple = fuse_elementwise(outputs_simple, updatetargs_simple, node2shape, rows=True)

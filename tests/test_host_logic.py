@@ -275,7 +275,12 @@ def test_recurrent_graph_rewrites():
     count = lambda pred: sum(1 for n in nodes if pred(n))
     assert count(lambda n: isinstance(n.op, core.GetSli)) == 0
     assert count(lambda n: isinstance(n.op, core.IncSli)) == 0
-    assert count(lambda n: isinstance(n.op, core.LeadingSlice)) == 2 * T          # x[t] and targ[t]
+    # x[t] and targ[t], and the per-time-step views of the five batched shared-weight products
+    assert count(lambda n: isinstance(n.op, core.LeadingSlice)) == 2 * T + 5 * T
+    # the hidden-to-hidden products stay (each needs the step before it); input-to-hidden of both layers and the output
+    # projection are one product each, so are the two data-gradient products that do not feed a recurrence
+    assert count(lambda n: isinstance(n.op, core.Mul22) and not n.op.tA and not n.op.tB) == 2 * T + 3
+    assert count(lambda n: isinstance(n.op, core.Mul22) and not n.op.tA and n.op.tB) == 2 * (T - 1) + 2   # h at t = 0 is a constant
     assert count(lambda n: isinstance(n.op, core.ScatterCols)) == 2 * 2 * T       # two per layer and time step
     assert count(lambda n: isinstance(n.op, core.FusedRows)) == T
     wgrads = [n for n in nodes if isinstance(n.op, core.Mul22) and n.op.tA and not n.op.tB]
@@ -283,7 +288,7 @@ def test_recurrent_graph_rewrites():
     assert sum(1 for n in before if isinstance(n.op, core.Mul22) and n.op.tA and not n.op.tB) == 5 * T
     views = [n for n in nodes if isinstance(n.op, core.FusedElwise) and n.op.views]
     assert views and all(n.op.static_shape is not None and 7 in n.op.in_kinds for n in views)
-    assert len(nodes) < len(before) // 2
+    assert len(nodes) < 0.6 * len(before)
     # every rewrite has its switch: with all of them off the graph is the simplified one
     off = dict(fuse_slice_views=False, fuse_slice_sums=False, batch_summed_products=False, fuse_rows=False, fuse_elementwise=False,
                fuse_conv_dgrad=False, fuse_conv_grad_input=False)
