@@ -56,31 +56,6 @@ __device__ __forceinline__ bool mbar_wait_or_abort(uint32_t bar, uint32_t parity
   }
   return false;
 }
-// non-blocking test of a phase (mbarrier.test_wait): unlike try_wait it never suspends the thread
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.b32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return done != 0;
-}
-// bounded, abortable wait on the critical path of a pipeline (a hand-off that is expected within hundreds of cycles):
-// polls with test_wait, so the thread resumes as soon as the phase completes instead of at the end of a suspension
-__device__ __forceinline__ bool mbar_spin_or_abort(uint32_t bar, uint32_t parity, const volatile int* abort_flag) {
-  const long long t0 = clock64();
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-    if (mbar_test(bar, parity)) return true;
-    if ((spin & 1023u) == 1023u) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitCycles) return false;
-    }
-  }
-  return false;
-}
 // bounded, abortable wait for a role that has nothing else to do for a long time (epilogue warps waiting for a whole
 // tile): sleeps between polls so that it does not take issue slots and shared-memory bandwidth from the working warps
 __device__ __forceinline__ bool mbar_wait_sleepy(uint32_t bar, uint32_t parity, const volatile int* abort_flag) {
