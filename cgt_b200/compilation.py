@@ -1100,6 +1100,56 @@ def _conv_channels_ok(n):
     return n % 16 == 0 and (n <= 128 or n % 128 == 0)
 
 
+def fuse_conv_direct(outputs, updatetargs, node2shape):
+    """Im2Col of an image with 3 channels (5 x 5 filters, pad 2, stride 1, 32 pixels wide, 32 filters) whose column matrix
+    feeds only the layer's forward product (ConvBiasRelu) and its filter gradient (Mul22{T,N}(dy, col)): both are
+    computed directly from the image (ConvDirectFwd, ConvDirectWgrad) and the column matrix, 25 times the image, is
+    never formed. Runs before pad_conv_columns, which would otherwise widen that matrix."""
+    from .nn_ops import im2col as im2col_ops
+    all_out = list(outputs) + list(updatetargs)
+    nodes = core.topsorted(all_out)
+    children = defaultdict(list)
+    for node in nodes:
+        for par in node.parents:
+            children[par].append(node)
+    out_set = set(all_out)
+    replace = {}
+    for im in nodes:
+        if im.is_input() or not isinstance(im.op, im2col_ops.Im2Col) or im.op.pitch or im.dtype != "f4" or im in out_set:
+            continue
+        info = im.op.info
+        if tuple(info) != (5, 5, 2, 2, 1, 1) or len(children[im]) != 1:
+            continue
+        x = im.parents[0]
+        xs = _static_shape(node2shape[x]) if x in node2shape else None
+        if xs is None or len(xs) != 4 or xs[1] != 3 or xs[3] != 32 or xs[2] % 8 != 0 or x.dtype != "f4":
+            continue
+        r = children[im][0]
+        if not isinstance(r.op, core.Reshape) or r in out_set or r.ndim != 2 or r.parents[0] is not im:
+            continue
+        fwd = [c for c in children[r] if isinstance(c.op, im2col_ops.ConvBiasRelu) and c.parents[0] is r and r not in c.parents[1:]]
+        wgs = [c for c in children[r] if isinstance(c.op, core.Mul22) and c.op.tA and not c.op.tB and c.parents[1] is r
+               and c.parents[0] is not r and c.dtype == "f4" and c not in out_set]
+        if len(fwd) != 1 or len(fwd) + len(wgs) != len(children[r]) or len(wgs) > 1:
+            continue
+        f = fwd[0]
+        wshape = _static_shape(node2shape[f.parents[1]])
+        if wshape != (32, 75):
+            continue
+        new_f = core.Result(im2col_ops.ConvDirectFwd(info), [x] + list(f.parents[1:]))
+        node2shape[new_f] = node2shape[f]
+        new_f.props.update(f.props)
+        replace[f] = new_f
+        for c in wgs:
+            new_w = core.Result(im2col_ops.ConvDirectWgrad(info, 32), [x, c.parents[0]])
+            node2shape[new_w] = node2shape[c]
+            new_w.props.update(c.props)
+            replace[c] = new_w
+    if not replace:
+        return list(outputs), list(updatetargs)
+    return _rewire(outputs, updatetargs, replace)
+
+
 def pad_conv_columns(outputs, updatetargs, node2shape):
     """Widen the rows of a float32 column matrix whose length Z = C*kh*kw is not a multiple of four (a 3-channel
     5x5 convolution: 75) to the next multiple, so that every row starts on a 16-byte boundary and the products
@@ -1594,6 +1644,8 @@ def apply_graph_rewrites(outputs_simple, updatetargs_simple, node2shape):
             outputs_simple, updatetargs_simple = fuse_conv_output(outputs_simple, updatetargs_simple, node2shape)
         if config["fuse_conv_output"] and config["fuse_conv_implicit"]:
             outputs_simple, updatetargs_simple = fuse_conv_implicit(outputs_simple, updatetargs_simple, node2shape)
+        if config["fuse_conv_output"] and config["fuse_conv_direct"]:
+            outputs_simple, updatetargs_simple = fuse_conv_direct(outputs_simple, updatetargs_simple, node2shape)
         if config["pad_conv_columns"]:
             outputs_simple, updatetargs_simple = pad_conv_columns(outputs_simple, updatetargs_simple, node2shape)
     return outputs_simple, updatetargs_simple

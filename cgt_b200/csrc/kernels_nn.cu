@@ -854,3 +854,264 @@ CGTB_API int cgtb_lrn_backward(int dtype, const void* x, const void* top, const 
   CGTB_CHECK_LAUNCH("lrn_backward");
   return 0;
 }
+
+
+// ================================================================================================
+// Direct convolution of a layer with very few input channels (CIFAR conv1: 3 -> 32 channels, 5 x 5, pad 2, 32 x 32
+// images). Through a column matrix this layer costs an im2col that writes 25 times the image, a forward product and
+// a filter-gradient product that both stream that matrix again: three HBM-bound passes over 40 MB for 0.63 GFLOP.
+// Here a block takes 8 image rows of one image: the input rows with their halo (3 x 12 x 36 floats) live in shared
+// memory, the sums in registers. Shared memory hands 128 bytes per clock to the registers of an SM while its FMA
+// pipes retire 128 FMAs, so every float read from shared memory has to feed at least 4 FMAs of its thread; both
+// kernels are tiled for that.
+//   forward: a thread owns one image column x 8 rows x 8 output channels (64 sums); a warp is the 32 columns of one
+//     channel group. Per (input channel, filter column) it reads its 12 input values once (conflict-free), then per
+//     filter row two 128-bit broadcast reads of 8 weights feed 64 FMAs. The filters sit in shared memory as
+//     [tap][channel] with the 4-channel groups XOR-swizzled by the tap, which spreads the transposing fill over
+//     8 banks. The epilogue adds the bias and writes relu and mask as NCHW planes (a warp writes 32 consecutive
+//     pixels of one plane).
+//   filter gradient: a thread owns 2 output channels x the 25 taps of one input channel (50 sums) for one image row
+//     of the band; walking along the row it keeps a 5 x 5 window of input values in registers (5 new values per
+//     pixel) and reads the pixel's 2 gradients: 7 floats feed 50 FMAs. The 8 rows of the band are added in row order
+//     through shared memory, each block leaves its 32 x 75 partial result, and the partial results are added in block
+//     order by the split-K fold kernel (reproducible).
+// ================================================================================================
+namespace {
+constexpr int kDcRows = 8;   // image rows per block
+constexpr int kDcFwdThreads = 128, kDcWgradThreads = 384;
+
+// Input rows y0-PAD .. y0+kDcRows+PAD of one image with a zero halo, as xs[ci][row][PAD + column]. Every thread issues
+// all of its 128-bit loads before it stores any of them, so a block pays one memory latency for the band.
+template <int CIN, int KS, int WIDTH, int NT>
+__device__ __forceinline__ void conv_direct_load_band(float (*xs)[kDcRows + KS - 1][WIDTH + KS], const float* __restrict__ xb, int H, int y0,
+                                                      int tid) {
+  constexpr int PAD = KS / 2, HR = kDcRows + KS - 1, Q = WIDTH / 4, NV = CIN * HR * Q, ROUNDS = (NV + NT - 1) / NT;
+  float4 v[ROUNDS];
+#pragma unroll
+  for (int t = 0; t < ROUNDS; ++t) {
+    const int e = tid + t * NT, row = e / Q, ci = row / HR, hy = row - ci * HR, gy = y0 + hy - PAD;
+    v[t] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (e < NV && gy >= 0 && gy < H) v[t] = *reinterpret_cast<const float4*>(xb + ((size_t)ci * H + gy) * WIDTH + 4 * (e % Q));
+  }
+#pragma unroll
+  for (int t = 0; t < ROUNDS; ++t) {
+    const int e = tid + t * NT, row = e / Q, ci = row / HR, hy = row - ci * HR;
+    if (e < NV) {
+      float* d = &xs[ci][hy][PAD + 4 * (e % Q)];
+      d[0] = v[t].x; d[1] = v[t].y; d[2] = v[t].z; d[3] = v[t].w;
+    }
+  }
+  for (int e = tid; e < CIN * HR * 2 * PAD; e += NT) {   // halo columns
+    const int row = e / (2 * PAD), c = e - row * 2 * PAD;
+    xs[row / HR][row % HR][c < PAD ? c : WIDTH + c] = 0.f;
+  }
+}
+
+template <int CIN, int KS, int COUT, int WIDTH>
+__global__ void __launch_bounds__(kDcFwdThreads) conv_direct_fwd_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                                        const float* __restrict__ bias, int H, float* __restrict__ y,
+                                                                        int8_t* __restrict__ mask) {
+  constexpr int HR = kDcRows + KS - 1, K = CIN * KS * KS, CG = 8, WP = COUT + 4, WROUNDS = (K * COUT + kDcFwdThreads - 1) / kDcFwdThreads;
+  static_assert(WIDTH == 32 && COUT == CG * (kDcFwdThreads / 32), "a warp is the 32 columns of one group of 8 channels");
+  __shared__ float xs[CIN][HR][WIDTH + KS];   // row pitch 37 floats: a warp's column reads are conflict-free
+  __shared__ __align__(16) float ws[K][WP];   // [tap][channel]; pitch 36 floats spreads the transposing stores over 8 banks
+  __shared__ float bs[COUT];
+  const int tid = threadIdx.x, cg = tid >> 5, lane = tid & 31;
+  const int bands = H / kDcRows, b = blockIdx.x / bands, y0 = (blockIdx.x % bands) * kDcRows;
+  {
+    float wv[WROUNDS];
+#pragma unroll
+    for (int t = 0; t < WROUNDS; ++t) {
+      const int e = tid + t * kDcFwdThreads;
+      wv[t] = e < K * COUT ? w[e] : 0.f;
+    }
+    conv_direct_load_band<CIN, KS, WIDTH, kDcFwdThreads>(xs, x + (size_t)b * CIN * H * WIDTH, H, y0, tid);
+#pragma unroll
+    for (int t = 0; t < WROUNDS; ++t) {   // w[oc][k] -> ws[k][oc]
+      const int e = tid + t * kDcFwdThreads, oc = e / K, k = e - oc * K;
+      if (e < K * COUT) ws[k][oc] = wv[t];
+    }
+    if (tid < COUT) bs[tid] = bias[tid];
+  }
+  __syncthreads();
+  float acc[kDcRows][CG];
+#pragma unroll
+  for (int r = 0; r < kDcRows; ++r)
+#pragma unroll
+    for (int q = 0; q < CG; ++q) acc[r][q] = 0.f;
+#pragma unroll 1
+  for (int ci = 0; ci < CIN; ++ci) {
+    const float* xcol = &xs[ci][0][lane];
+    const float* wrow = &ws[ci * KS * KS][cg * CG];
+#pragma unroll
+    for (int j = 0; j < KS; ++j) {
+      float xc[HR];
+#pragma unroll
+      for (int r = 0; r < HR; ++r) xc[r] = xcol[r * (WIDTH + KS) + j];
+#pragma unroll
+      for (int i = 0; i < KS; ++i) {
+        const float4 wa = *reinterpret_cast<const float4*>(wrow + (i * KS + j) * WP);
+        const float4 wb = *reinterpret_cast<const float4*>(wrow + (i * KS + j) * WP + 4);
+#pragma unroll
+        for (int r = 0; r < kDcRows; ++r) {
+          const float xv = xc[r + i];
+          acc[r][0] = fmaf(xv, wa.x, acc[r][0]);
+          acc[r][1] = fmaf(xv, wa.y, acc[r][1]);
+          acc[r][2] = fmaf(xv, wa.z, acc[r][2]);
+          acc[r][3] = fmaf(xv, wa.w, acc[r][3]);
+          acc[r][4] = fmaf(xv, wb.x, acc[r][4]);
+          acc[r][5] = fmaf(xv, wb.y, acc[r][5]);
+          acc[r][6] = fmaf(xv, wb.z, acc[r][6]);
+          acc[r][7] = fmaf(xv, wb.w, acc[r][7]);
+        }
+      }
+    }
+  }
+  const size_t plane = (size_t)H * WIDTH;
+  float* yo = y + ((size_t)b * COUT + cg * CG) * plane + (size_t)y0 * WIDTH + lane;
+  int8_t* mo = mask + ((size_t)b * COUT + cg * CG) * plane + (size_t)y0 * WIDTH + lane;
+#pragma unroll
+  for (int q = 0; q < CG; ++q) {
+    const float bv = bs[cg * CG + q];
+#pragma unroll
+    for (int r = 0; r < kDcRows; ++r) {
+      const float t = acc[r][q] + bv;
+      const int8_t m = (int8_t)(t >= 0.f);
+      mo[q * plane + r * WIDTH] = m;
+      yo[q * plane + r * WIDTH] = t * (float)m;
+    }
+  }
+}
+
+template <int CIN, int KS, int COUT, int WIDTH>
+__global__ void __launch_bounds__(kDcWgradThreads, 2) conv_direct_wgrad_kernel(const float* __restrict__ x, const float* __restrict__ dy,
+                                                                              int H, float* __restrict__ part) {
+  constexpr int HR = kDcRows + KS - 1, K = CIN * KS * KS, NPIX = kDcRows * WIDTH, NPAIR = COUT / 2, NQ = NPIX * COUT / 4;
+  constexpr int DROUNDS = (NQ + kDcWgradThreads - 1) / kDcWgradThreads;
+  static_assert(NPAIR * CIN * kDcRows == kDcWgradThreads && kDcRows == 8, "one thread per (channel pair, input channel, band row)");
+  __shared__ float xs[CIN][HR][WIDTH + KS];
+  // [NPIX][COUT] gradients during the sweep, then up to 4 x [COUT*K] sums of the row tree
+  extern __shared__ __align__(16) float dys[];
+  const int tid = threadIdx.x;
+  const int bands = H / kDcRows, b = blockIdx.x / bands, y0 = (blockIdx.x % bands) * kDcRows;
+  {
+    const float4* dsrc = reinterpret_cast<const float4*>(dy + ((size_t)b * H + y0) * WIDTH * COUT);   // NPIX * COUT contiguous floats
+    float4 dv[DROUNDS];
+#pragma unroll
+    for (int t = 0; t < DROUNDS; ++t) {
+      const int e = tid + t * kDcWgradThreads;
+      dv[t] = e < NQ ? dsrc[e] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    conv_direct_load_band<CIN, KS, WIDTH, kDcWgradThreads>(xs, x + (size_t)b * CIN * H * WIDTH, H, y0, tid);
+#pragma unroll
+    for (int t = 0; t < DROUNDS; ++t) {
+      const int e = tid + t * kDcWgradThreads;
+      if (e < NQ) reinterpret_cast<float4*>(dys)[e] = dv[t];
+    }
+  }
+  __syncthreads();
+  const int pair = tid % NPAIR, rest = tid / NPAIR, ci = rest % CIN, row = rest / CIN;
+  float acc[2][KS][KS];
+#pragma unroll
+  for (int i = 0; i < KS; ++i)
+#pragma unroll
+    for (int j = 0; j < KS; ++j) acc[0][i][j] = acc[1][i][j] = 0.f;
+  float xw[KS][KS];   // xw[i][c % KS] = xs[ci][row + i][c] for the KS columns under the current pixel
+  const float* xrow = &xs[ci][row][0];
+#pragma unroll
+  for (int i = 0; i < KS; ++i)
+#pragma unroll
+    for (int c = 0; c < KS - 1; ++c) xw[i][c] = xrow[i * (WIDTH + KS) + c];
+  const float2* drow = reinterpret_cast<const float2*>(dys) + (size_t)row * WIDTH * NPAIR + pair;
+#pragma unroll
+  for (int pc = 0; pc < WIDTH; ++pc) {
+#pragma unroll
+    for (int i = 0; i < KS; ++i) xw[i][(pc + KS - 1) % KS] = xrow[i * (WIDTH + KS) + pc + KS - 1];
+    const float2 d = drow[pc * NPAIR];
+#pragma unroll
+    for (int i = 0; i < KS; ++i)
+#pragma unroll
+      for (int j = 0; j < KS; ++j) {
+        const float xv = xw[i][(pc + j) % KS];
+        acc[0][i][j] = fmaf(d.x, xv, acc[0][i][j]);
+        acc[1][i][j] = fmaf(d.y, xv, acc[1][i][j]);
+      }
+  }
+  __syncthreads();   // every thread is done with the gradients: their space now holds the tree's sums
+  // rows are added as ((r0+r4) + (r2+r6)) + ((r1+r5) + (r3+r7)): the upper half of the live rows hands its sums over
+  const int col0 = (2 * pair) * K + ci * KS * KS;
+#pragma unroll
+  for (int half = kDcRows / 2; half >= 1; half /= 2) {
+    if (row >= half && row < 2 * half) {
+      float* dst = dys + (size_t)(row - half) * COUT * K + col0;
+#pragma unroll
+      for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int t = 0; t < KS * KS; ++t) dst[a * K + t] = acc[a][t / KS][t % KS];
+    }
+    __syncthreads();
+    if (row < half) {
+      const float* src = dys + (size_t)row * COUT * K + col0;
+#pragma unroll
+      for (int a = 0; a < 2; ++a)
+#pragma unroll
+        for (int t = 0; t < KS * KS; ++t) acc[a][t / KS][t % KS] += src[a * K + t];
+    }
+    __syncthreads();
+  }
+  if (row == 0) {
+    float* dst = dys + col0;
+#pragma unroll
+    for (int a = 0; a < 2; ++a)
+#pragma unroll
+      for (int t = 0; t < KS * KS; ++t) dst[a * K + t] = acc[a][t / KS][t % KS];
+  }
+  __syncthreads();
+  float* dst = part + (size_t)blockIdx.x * COUT * K;
+  for (int e = tid; e < COUT * K; e += kDcWgradThreads) dst[e] = dys[e];
+}
+bool conv_direct_ok(long B, int Cin, int H, int W, int Cout, int kh, int kw, int ph, int pw) {
+  return Cin == 3 && kh == 5 && kw == 5 && ph == 2 && pw == 2 && Cout == 32 && W == 32 && H % kDcRows == 0 && H > 0 && B > 0 &&
+         B * (H / kDcRows) < (1L << 30);
+}
+}  // namespace
+
+namespace cgtb {
+void tc_splitk_fold(long P, long M, long N, int nsplit, const float* part, float* C, long ldc, long strideC);
+}
+
+CGTB_API int cgtb_conv_direct_fwd_bias_relu(const float* x, long B, int Cin, int H, int W, const float* w, int Cout, int kh, int kw, int ph,
+                                            int pw, const float* bias, float* y, signed char* mask) {
+  if (!require_runtime("cgtb_conv_direct_fwd_bias_relu")) return 1;
+  if (B <= 0) return 0;
+  if (!conv_direct_ok(B, Cin, H, W, Cout, kh, kw, ph, pw))
+    return fail("cgtb_conv_direct_fwd_bias_relu: not supported for Cin=%d kh=%d kw=%d pad=%d,%d Cout=%d H=%d W=%d (3, 5, 5, 2, 2, 32, multiple of 8, 32)",
+                Cin, kh, kw, ph, pw, Cout, H, W);
+  const unsigned blocks = (unsigned)(B * (H / kDcRows));
+  CGTB_LAUNCH((conv_direct_fwd_kernel<3, 5, 32, 32>), blocks, kDcFwdThreads, 0, x, w, bias, H, y, (int8_t*)mask);
+  CGTB_CHECK_LAUNCH("conv_direct_fwd");
+  return 0;
+}
+CGTB_API int cgtb_conv_direct_wgrad(const float* x, long B, int Cin, int H, int W, const float* dy, int Cout, int kh, int kw, int ph, int pw,
+                                    float* dw) {
+  if (!require_runtime("cgtb_conv_direct_wgrad")) return 1;
+  if (B <= 0) return 0;
+  if (!conv_direct_ok(B, Cin, H, W, Cout, kh, kw, ph, pw) || ((uintptr_t)dy & 15) != 0)
+    return fail("cgtb_conv_direct_wgrad: not supported for Cin=%d kh=%d kw=%d pad=%d,%d Cout=%d H=%d W=%d (3, 5, 5, 2, 2, 32, multiple of 8, 32) or an unaligned gradient",
+                Cin, kh, kw, ph, pw, Cout, H, W);
+  const long blocks = B * (H / kDcRows);
+  const int K = Cin * kh * kw;
+  float* part = (float*)scratch((size_t)blocks * Cout * K * sizeof(float));
+  if (!part) return 1;
+  const size_t smem = std::max<size_t>((size_t)kDcRows * 32 * 32, (size_t)(kDcRows / 2) * Cout * K) * sizeof(float);
+  static bool attr = false;
+  if (!attr) {
+    CGTB_CUDA_TRY(cudaFuncSetAttribute(conv_direct_wgrad_kernel<3, 5, 32, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr = true;
+  }
+  CGTB_LAUNCH((conv_direct_wgrad_kernel<3, 5, 32, 32>), (unsigned)blocks, kDcWgradThreads, smem, x, dy, H, part);
+  if (blocks > 1) cgtb::tc_splitk_fold(1, Cout, K, (int)blocks, part, dw, K, 0);
+  else CGTB_CUDA_TRY(cudaMemcpyAsync(dw, part, (size_t)Cout * K * sizeof(float), cudaMemcpyDeviceToDevice, rt().stream));
+  CGTB_CHECK_LAUNCH("conv_direct_wgrad");
+  return 0;
+}

@@ -356,6 +356,38 @@ OP_BYREF(cgtb_op_conv_bias_relu) {
   cgtb_conv_bias_relu_ld((const float*)col->data(), M, K, ldcol, (const float*)w->data(), (int)C, (const float*)bias->data(), HW,
                          (float*)y->data(), (int8_t*)mask->data());
 }
+// ConvDirectFwd / ConvDirectWgrad: the first layer of an image network directly from the NCHW image (closure: the six
+// ints of the reference's conv_closure; the filter gradient adds the number of filters)
+struct ConvDirectClosure { int kh, kw, ph, pw, sv, sh, cout; };
+OP_BYREF(cgtb_op_conv_direct_fwd) {
+  const ConvDirectClosure* cl = (const ConvDirectClosure*)cl0;
+  cgtArray *x = ARR(reads[0]), *w = ARR(reads[1]), *bias = ARR(reads[2]);
+  cgtTuple* out = (cgtTuple*)write0;
+  cgtArray *mask = ARR(out->getitem(0)), *y = ARR(out->getitem(1));
+  if (!all_gpu({x, w, bias, mask, y})) { fail("ConvDirectFwd: operands must be on the GPU"); return; }
+  if (x->ndim() != 4 || y->ndim() != 4 || x->dtype() != cgt_f4 || cl->sv != 1 || cl->sh != 1) { fail("ConvDirectFwd: a stride-1 convolution of a float32 NCHW image"); return; }
+  const long* xs = x->shape();
+  const long* d = y->shape();
+  if (d[0] != xs[0] || d[2] != xs[2] || d[3] != xs[3] || w->size() != d[1] * xs[1] * cl->kh * cl->kw || bias->size() != d[1] || mask->size() != y->size()) {
+    fail("ConvDirectFwd: operand shapes do not fit together");
+    return;
+  }
+  cgtb_conv_direct_fwd_bias_relu((const float*)x->data(), xs[0], (int)xs[1], (int)xs[2], (int)xs[3], (const float*)w->data(), (int)d[1], cl->kh,
+                                 cl->kw, cl->ph, cl->pw, (const float*)bias->data(), (float*)y->data(), (signed char*)mask->data());
+}
+OP_BYREF(cgtb_op_conv_direct_wgrad) {
+  const ConvDirectClosure* cl = (const ConvDirectClosure*)cl0;
+  cgtArray *x = ARR(reads[0]), *dy = ARR(reads[1]), *out = ARR(write0);
+  if (!all_gpu({x, dy, out})) { fail("ConvDirectWgrad: operands must be on the GPU"); return; }
+  if (x->ndim() != 4 || x->dtype() != cgt_f4 || dy->dtype() != cgt_f4 || cl->sv != 1 || cl->sh != 1) { fail("ConvDirectWgrad: a stride-1 convolution of a float32 NCHW image"); return; }
+  const long* xs = x->shape();
+  if (dy->size() != xs[0] * xs[2] * xs[3] * cl->cout || out->size() != (long)cl->cout * xs[1] * cl->kh * cl->kw) {
+    fail("ConvDirectWgrad: operand shapes do not fit together");
+    return;
+  }
+  cgtb_conv_direct_wgrad((const float*)x->data(), xs[0], (int)xs[1], (int)xs[2], (int)xs[3], (const float*)dy->data(), cl->cout, cl->kh, cl->kw,
+                         cl->ph, cl->pw, (float*)out->data());
+}
 // ConvWgrad: (dy [M,C], col [M,ldcol]) -> dy^T * col[:, :K] as [C,K]: the filter gradient from a column matrix
 // with padded rows; K is the output's second extent
 OP_BYREF(cgtb_op_conv_wgrad) {

@@ -209,6 +209,67 @@ class ConvWgrad(core.Op):
         return "ConvWgrad{%d}" % self.k
 
 
+class ConvDirectFwd(core.Op):
+    """(x NCHW [B,Cin,H,W], W [Cout, Cin*kh*kw], bias [1,Cout,1,1], B, Cout, H, W) -> tuple(mask i1, relu f4), both NCHW:
+    the forward pass of a stride-1 "same" convolution layer on very few input channels, computed directly from the image.
+
+    Not part of the reference's Op set. The compiler substitutes it (compilation.fuse_conv_direct) for
+    Im2Col -> ConvBiasRelu (cgt/nn.py:87-100, 228-233, 44-45) when the layer has 3 input channels, 5 x 5 filters and 32
+    filters on images 32 pixels wide: the column matrix of such a layer is 25 times its input. Float32 tolerance against
+    the column-matrix path (the sums run tap by tap in FMA arithmetic)."""
+    available_impls = ("native_gpu",)
+
+    def __init__(self, info):
+        self.info = info
+
+    def get_diff(self, n):
+        return [False] * n
+
+    def shp_apply(self, inputs):
+        shp = list(inputs[3:])
+        return (shp, list(shp))
+
+    def typ_apply(self, inputs):
+        return core.TupleType(core.TensorType("i1", 4), core.TensorType("f4", 4))
+
+    def host_inputs(self, n):
+        return tuple(range(3, n))
+
+    def get_native_compile_info(self, input_types, devtype):
+        return core.NativeCompileInfo(None, prebuilt="cgtb_op_conv_direct_fwd", closure_triples=info2closure(self.info))
+
+    def __repr__(self):
+        return "ConvDirectFwd{%s}" % (tuple(self.info),)
+
+
+class ConvDirectWgrad(core.Op):
+    """(x NCHW [B,Cin,H,W], dy channels-last with B*H*W*Cout elements) -> [Cout, Cin*kh*kw]: the filter gradient of the same
+    layer, directly from the image (compilation.fuse_conv_direct puts it in place of the Mul22{T,N} / ConvWgrad on the
+    column matrix). Partial results per block of image rows, added in block order."""
+    available_impls = ("native_gpu",)
+
+    def __init__(self, info, cout):
+        self.info = info
+        self.cout = int(cout)
+
+    def get_diff(self, n):
+        return [False] * n
+
+    def shp_apply(self, inputs):
+        info = self.info
+        return [core.cgt.constant(self.cout), core.cgt.size(inputs[0], 1) * (info.kernel_h * info.kernel_w)]
+
+    def typ_apply(self, inputs):
+        return core.TensorType("f4", 2)
+
+    def get_native_compile_info(self, input_types, devtype):
+        return core.NativeCompileInfo(None, prebuilt="cgtb_op_conv_direct_wgrad",
+                                      closure_triples=info2closure(self.info) + [("cout", ctypes.c_int, self.cout)])
+
+    def __repr__(self):
+        return "ConvDirectWgrad{%s}" % (tuple(self.info),)
+
+
 class ConvFwdBiasRelu(core.Op):
     """(x NHWC [B,H,W,Cin], filters, bias [1,Cout,1,1], B, Cout, Ho, Wo) -> tuple(mask i1, relu f4), both NCHW
     [B,Cout,Ho,Wo]: the forward pass of a stride-1 convolution layer in one kernel. The filters are the layer's bank

@@ -301,6 +301,19 @@ int cgtb_fused_rows(const cgtbRowProgram* prog, long R, long C, const void* cons
  * the zero fills. k <= 8. */
 int cgtb_scatter_cols(long R, long C, int k, const long* offset, const long* width, const void* const* pieces, void* out);
 
+/* A stride-1 "same" convolution layer on very few input channels (the first layer of an image network: 3 channels,
+ * 5 x 5 filters, 32 filters, images 32 pixels wide), forward with bias + relu + mask and filter gradient, computed
+ * directly from the NCHW image with FMA tiles: no column matrix (the reference forms Im2Col then Mul22,
+ * cgt/nn.py:93-100, include/im2col.h:6-28; with 3 input channels the column matrix is 25 times the image and the
+ * product has only 75 terms per output). x [B, Cin, H, W]; w [Cout][Cin*kh*kw] (the bank as stored); y / mask NCHW
+ * [B, Cout, H, W]; dy channels-last [B, H, W, Cout]; dw [Cout][Cin*kh*kw]. Supported: Cin 3, kh = kw = 5, ph = pw = 2,
+ * Cout 32, W 32, H a multiple of 8; anything else is refused (use cgtb_im2col + cgtb_conv_bias_relu / cgtb_sgemm).
+ * Sums run in float32 FMA order (tap by tap), not in the GEMM's: float32 tolerance against the column-matrix path. */
+int cgtb_conv_direct_fwd_bias_relu(const float* x_nchw, long B, int Cin, int H, int W, const float* w, int Cout, int kh, int kw, int ph,
+                                   int pw, const float* bias, float* y_nchw, signed char* mask_nchw);
+int cgtb_conv_direct_wgrad(const float* x_nchw, long B, int Cin, int H, int W, const float* dy_nhwc, int Cout, int kh, int kw, int ph,
+                           int pw, float* dw);
+
 /* Sum / Max over a set of axes, keepdims (cgt/core.py:1663-1738) */
 int cgtb_reduce(int kind, int dtype, int ndim, const long* shape, const int* reduced, const void* in, void* out);
 

@@ -138,7 +138,7 @@ def test_elementwise_fusion_changes_no_bit(rt, name, generated):
         # fused chains, and they change the order of the sums: off on both sides here
         # (the row chains sum in another order as well: off)
         with cgt.scoped_update_config(fuse_elementwise=fuse, jit_fused_elementwise=generated, pad_conv_columns=False,
-                                      fuse_conv_implicit=False, fuse_rows=False, use_cuda_graphs=False):
+                                      fuse_conv_implicit=False, fuse_conv_direct=False, fuse_rows=False, use_cuda_graphs=False):
             cfg = configs.BUILDERS[name](**SMALL[name])
             f = cfg.compile()
             n_fused = sum(1 for instr in f.eg.instrs if "FusedElwise" in repr(instr))
@@ -174,6 +174,24 @@ def test_row_fusion_matches_separate_kernels(rt, name):
         np.testing.assert_allclose(a, b, rtol=2e-5)
     for (a, b) in zip(results[False][3], results[True][3]):
         np.testing.assert_allclose(a, b, rtol=1e-4, atol=1e-6 * max(1.0, float(np.abs(a).max())))
+
+
+def test_conv_direct_substitution(rt):
+    """The compiler computes the 3-channel first layer of the CIFAR-shape convnet directly from the image (no column
+    matrix): losses and parameters stay within the float32 tolerance of the column-matrix graph."""
+    res = {}
+    for fuse in (False, True):
+        with cgt.scoped_update_config(fuse_conv_direct=fuse, use_cuda_graphs=False):
+            cfg = configs.build_cifar(batch=16)
+            f = cfg.compile()
+            reprs = [repr(i) for i in f.eg.instrs]
+            losses = [float(f(*cfg.batch(s))[0]) for s in range(4)]
+            res[fuse] = (reprs, losses, [np.asarray(p.op.get_value()).copy() for p in cfg.params])
+    assert any("ConvDirectFwd" in r for r in res[True][0]) and any("ConvDirectWgrad" in r for r in res[True][0])
+    assert not any("Im2Col" in r for r in res[True][0]) and any("Im2Col" in r for r in res[False][0])
+    np.testing.assert_allclose(res[True][1], res[False][1], rtol=1e-4)
+    for (a, b) in zip(res[False][2], res[True][2]):
+        np.testing.assert_allclose(a, b, rtol=1e-3, atol=1e-5 * max(1.0, float(np.abs(a).max())))
 
 
 @pytest.mark.parametrize("generated", [True, False])
@@ -249,7 +267,7 @@ def test_conv_output_substitution_changes_no_bit(rt):
     for fuse in (False, True):
         # padded column rows apply only next to ConvBiasRelu and change which product kernel runs: off here; the
         # convolutions without a column matrix sum in another order: off here too
-        with cgt.scoped_update_config(fuse_conv_output=fuse, pad_conv_columns=False, fuse_conv_implicit=False, use_cuda_graphs=False):
+        with cgt.scoped_update_config(fuse_conv_output=fuse, pad_conv_columns=False, fuse_conv_implicit=False, fuse_conv_direct=False, use_cuda_graphs=False):
             cfg = configs.BUILDERS["cifar"](**SMALL["cifar"])
             f = cfg.compile()
             names = [repr(instr) for instr in f.eg.instrs]
@@ -270,7 +288,7 @@ def test_padded_column_rows(rt, name, n_padded):
     become ConvBiasRelu on the padded matrix and ConvWgrad; losses and parameters stay within float32 tolerance."""
     res = {}
     for pad in (False, True):
-        with cgt.scoped_update_config(pad_conv_columns=pad, use_cuda_graphs=False):
+        with cgt.scoped_update_config(pad_conv_columns=pad, fuse_conv_direct=False, use_cuda_graphs=False):
             cfg = configs.BUILDERS[name](**SMALL[name])
             f = cfg.compile()
             names = [repr(instr) for instr in f.eg.instrs]
@@ -434,7 +452,7 @@ def test_conv_implicit_substitution(rt, name):
     parameters stay within float32 tolerance of the graph that keeps them."""
     res = {}
     for fuse in (False, True):
-        with cgt.scoped_update_config(fuse_conv_implicit=fuse, use_cuda_graphs=False):
+        with cgt.scoped_update_config(fuse_conv_implicit=fuse, fuse_conv_direct=False, use_cuda_graphs=False):
             cfg = configs.BUILDERS[name](**SMALL[name])
             f = cfg.compile()
             names = [repr(instr) for instr in f.eg.instrs]

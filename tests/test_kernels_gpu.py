@@ -545,6 +545,42 @@ def test_conv_wgrad_matches_gemm_on_im2col(rt, B, Cin, H, W, Cout, k, pad):
     np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-5 * scale)
 
 
+@pytest.mark.parametrize("B,H", [(2, 32), (5, 8), (128, 32)])
+def test_conv_direct_first_layer(rt, B, H):
+    """The 3-channel first layer computed directly from the NCHW image: forward with bias, relu and mask against the
+    reference's own path restated on the CPU (im2col_cpu -> sgemm -> + bias -> relu, cgt/nn.py:87-100, 44-45), and the
+    filter gradient against Mul22{T,N}(dy, col) of the same column matrix, both adjudicated in float64."""
+    rs = np.random.RandomState(B * 7 + H)
+    Cin, W, Cout, k, pad = 3, 32, 32, 5, 2
+    x = rs.randn(B, Cin, H, W).astype("f4")
+    w = (rs.randn(Cout, Cin * k * k) * 0.1).astype("f4")
+    bias = rs.randn(Cout).astype("f4")
+    col = O.im2col(x, (k, k), (pad, pad), (1, 1)).reshape(B * H * W, Cin * k * k)
+    exact = (col.astype("f8") @ w.astype("f8").T + bias.astype("f8")).reshape(B, H, W, Cout).transpose(0, 3, 1, 2)
+    want32 = (O.mul22(col, w, False, True) + bias).reshape(B, H, W, Cout).transpose(0, 3, 1, 2)
+    dx, dw_, db = Dev(x), Dev(w), Dev(bias)
+    y, mask = Dev(shape=(B, Cout, H, W), dtype="f4"), Dev(shape=(B, Cout, H, W), dtype="i1")
+    call("cgtb_conv_direct_fwd_bias_relu", dx.ptr, B, Cin, H, W, dw_.ptr, Cout, k, k, pad, pad, db.ptr, y.ptr, mask.ptr)
+    got, gm = y.get(), mask.get()
+    err = np.abs(got - np.maximum(exact, 0))
+    assert err.max() <= 4 * np.abs(np.maximum(want32, 0) - np.maximum(exact, 0)).max() + 1e-5
+    sure = np.abs(exact) > 1e-4     # the mask is (t >= 0): compare where rounding cannot flip the sign
+    assert np.array_equal(gm[sure].astype(bool), exact[sure] >= 0)
+    assert np.array_equal(got, np.where(gm.astype(bool), got, 0.0).astype("f4"))
+    # filter gradient
+    dy = rs.randn(B, H, W, Cout).astype("f4")
+    exact_w = dy.reshape(-1, Cout).astype("f8").T @ col.astype("f8")
+    want_w = O.mul22(dy.reshape(-1, Cout), col, True, False)
+    ddy, out = Dev(dy), Dev(np.full((Cout, Cin * k * k), np.nan, "f4"))
+    call("cgtb_conv_direct_wgrad", dx.ptr, B, Cin, H, W, ddy.ptr, Cout, k, k, pad, pad, out.ptr)
+    got_w = out.get()
+    scale = np.sqrt(B * H * W)
+    assert np.abs(got_w - exact_w).max() <= 4 * np.abs(want_w - exact_w).max() + 1e-5 * scale
+    # another layer is refused, not approximated
+    rc = runtime.lib().cgtb_conv_direct_wgrad(dx.ptr, B, 4, H, W, ddy.ptr, Cout, k, k, pad, pad, out.ptr)
+    assert rc != 0 and "not supported" in runtime.last_error()
+
+
 def test_conv_implicit_refuses_unsupported_extents(rt):
     d = Dev(shape=(64,), dtype="f4")
     L = runtime.lib()
