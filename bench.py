@@ -191,20 +191,17 @@ def cifar_kernel_table(B=BATCH):
     def add(name, shape, nbytes, flops, fn):
         table.append(dict(name=name, shape=shape, bytes=int(nbytes), flops=int(flops), fn=fn))
 
-    # conv1: 3 -> 32 channels, 32x32, through a column matrix with rows of 76 entries
+    # conv1: 3 -> 32 channels, 32x32, direct convolution (no column matrix)
     x1 = _dev(rs.randn(B, 3, 32, 32).astype("f4"))
-    col1 = _dev(np.zeros((B * 1024, 76), "f4"))
     w1, b1 = _dev((rs.randn(32, 75) * 0.1).astype("f4")), _dev(rs.randn(32).astype("f4"))
     y1, m1 = _dev(np.zeros((B, 32, 1024), "f4")), _dev(np.zeros((B, 32, 1024), "i1"))
     dy1, dw1 = _dev(rs.randn(B * 1024, 32).astype("f4")), _dev(np.zeros((32, 75), "f4"))
     M1 = B * 1024
-    add("cgtb_im2col_ld", "conv1 %dx3x32x32 k5 p2 -> [%d,76]" % (B, M1), 4 * (B * 3 * 1024 + M1 * 76), 0,
-        lambda: L.cgtb_im2col_ld(f4, _ptr(x1), B, 3, 32, 32, 5, 5, 2, 2, 1, 1, 76, _ptr(col1)))
-    add("cgtb_conv_bias_relu_ld", "conv1 forward %dx32x75 (ld 76) + bias + relu -> NCHW" % M1,
-        4 * (M1 * 76 + 32 * 75 + 32 + M1 * 32) + M1 * 32, 2 * M1 * 32 * 75,
-        lambda: L.cgtb_conv_bias_relu_ld(_ptr(col1), M1, 75, 76, _ptr(w1), 32, _ptr(b1), 1024, _ptr(y1), _ptr(m1)))
-    add("cgtb_sgemm", "conv1 filter gradient 32x75 K=%d (ldb 76)" % M1, 4 * (M1 * 32 + M1 * 76 + 32 * 75), 2 * M1 * 32 * 75,
-        lambda: L.cgtb_sgemm(1, 0, 32, 75, M1, _ptr(dy1), 32, _ptr(col1), 76, _ptr(dw1), 75, 0))
+    add("cgtb_conv_direct_fwd_bias_relu", "conv1 forward %dx3x32x32 * 32x3x5x5 + bias + relu -> NCHW" % B,
+        4 * (B * 3 * 1024 + 32 * 75 + 32 + M1 * 32) + M1 * 32, 2 * M1 * 32 * 75,
+        lambda: L.cgtb_conv_direct_fwd_bias_relu(_ptr(x1), B, 3, 32, 32, _ptr(w1), 32, 5, 5, 2, 2, _ptr(b1), _ptr(y1), _ptr(m1)))
+    add("cgtb_conv_direct_wgrad", "conv1 filter gradient 32x75 over %d pixels" % M1, 4 * (B * 3 * 1024 + M1 * 32 + 32 * 75), 2 * M1 * 32 * 75,
+        lambda: L.cgtb_conv_direct_wgrad(_ptr(x1), B, 3, 32, 32, _ptr(dy1), 32, 5, 5, 2, 2, _ptr(dw1)))
 
     # conv2 / conv3: stride-1 convolutions on 32-channel inputs, without a column matrix
     def conv_layer(tag, Cin, H, Cout):

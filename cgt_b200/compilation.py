@@ -1100,6 +1100,41 @@ def _conv_channels_ok(n):
     return n % 16 == 0 and (n <= 128 or n % 128 == 0)
 
 
+def _direct_wgrad_with_relu(c, x, info, children, out_set, node2shape, replace):
+    """The filter gradient c = Mul22{T,N}(Reshape(TupleIndex{0}(ReluGradNHWC(mask, g))), col) of a first layer: when the
+    channels-last gradient has no other reader, c and the bias gradient TupleIndex{1} become the two outputs of one
+    ConvDirectWgradRelu(x, mask, g). Returns True when it registered the replacements."""
+    from .nn_ops import im2col as im2col_ops
+    r2 = c.parents[0]
+    if r2.is_input() or not isinstance(r2.op, core.Reshape) or r2 in out_set or len(children[r2]) != 1:
+        return False
+    t0 = r2.parents[0]
+    if t0.is_input() or not isinstance(t0.op, core.TupleIndex) or t0.op.idx != 0 or t0 in out_set or len(children[t0]) != 1:
+        return False
+    rg = t0.parents[0]
+    if rg.is_input() or not isinstance(rg.op, im2col_ops.ReluGradNHWC) or rg in out_set:
+        return False
+    others = [t for t in children[rg] if t is not t0]
+    if any(t.is_input() or not isinstance(t.op, core.TupleIndex) or t.op.idx != 1 for t in others):
+        return False
+    (mask, g) = rg.parents
+    gs = _static_shape(node2shape[g]) if g in node2shape else None
+    xs = _static_shape(node2shape[x])
+    if gs is None or gs != (xs[0], 32, xs[2], xs[3]) or mask.dtype != "i1" or g.dtype != "f4":
+        return False
+    new = core.Result(im2col_ops.ConvDirectWgradRelu(info, 32), [x, mask, g])
+    node2shape[new] = (node2shape[c], node2shape[rg][1])
+    new.props.update(c.props)
+    dw = core.Result(core.TupleIndex(0), [new])
+    node2shape[dw] = node2shape[c]
+    replace[c] = dw
+    for t in others:
+        db = core.Result(core.TupleIndex(1), [new])
+        node2shape[db] = node2shape[t]
+        replace[t] = db
+    return True
+
+
 def fuse_conv_direct(outputs, updatetargs, node2shape):
     """Im2Col of an image with 3 channels (5 x 5 filters, pad 2, stride 1, 32 pixels wide, 32 filters) whose column matrix
     feeds only the layer's forward product (ConvBiasRelu) and its filter gradient (Mul22{T,N}(dy, col)): both are
@@ -1141,6 +1176,9 @@ def fuse_conv_direct(outputs, updatetargs, node2shape):
         new_f.props.update(f.props)
         replace[f] = new_f
         for c in wgs:
+            fused = _direct_wgrad_with_relu(c, x, info, children, out_set, node2shape, replace)
+            if fused:
+                continue
             new_w = core.Result(im2col_ops.ConvDirectWgrad(info, 32), [x, c.parents[0]])
             node2shape[new_w] = node2shape[c]
             new_w.props.update(c.props)

@@ -983,18 +983,54 @@ __global__ void __launch_bounds__(kDcFwdThreads) conv_direct_fwd_kernel(const fl
   }
 }
 
-template <int CIN, int KS, int COUT, int WIDTH>
+// RELU: the gradient arrives as the NCHW gradient g of the layer's relu output with the relu's NCHW mask; the kernel
+// forms dy = mask * g while it stages the band and also leaves the band's bias gradient (the sum of dy over its
+// pixels) behind the 32 x 75 partial result.
+template <int CIN, int KS, int COUT, int WIDTH, bool RELU>
 __global__ void __launch_bounds__(kDcWgradThreads, 2) conv_direct_wgrad_kernel(const float* __restrict__ x, const float* __restrict__ dy,
-                                                                              int H, float* __restrict__ part) {
+                                                                              const int8_t* __restrict__ mask, int H,
+                                                                              float* __restrict__ part) {
   constexpr int HR = kDcRows + KS - 1, K = CIN * KS * KS, NPIX = kDcRows * WIDTH, NPAIR = COUT / 2, NQ = NPIX * COUT / 4;
-  constexpr int DROUNDS = (NQ + kDcWgradThreads - 1) / kDcWgradThreads;
+  constexpr int DROUNDS = (NQ + kDcWgradThreads - 1) / kDcWgradThreads, SROUNDS = (NPIX * COUT + kDcWgradThreads - 1) / kDcWgradThreads;
+  constexpr int DP = RELU ? COUT + 1 : COUT;   // floats per pixel in dys; the odd pitch keeps the transposing stores conflict-free
+  constexpr int PSTRIDE = COUT * K + (RELU ? COUT : 0);
   static_assert(NPAIR * CIN * kDcRows == kDcWgradThreads && kDcRows == 8, "one thread per (channel pair, input channel, band row)");
+  static_assert(!RELU || (COUT == 32 && NPIX == 256), "the bias gradient is summed by 8 x 32 threads over 32 pixels each");
   __shared__ float xs[CIN][HR][WIDTH + KS];
-  // [NPIX][COUT] gradients during the sweep, then up to 4 x [COUT*K] sums of the row tree
+  __shared__ float bsum[8][COUT];
+  // [NPIX][DP] gradients during the sweep, then up to 4 x [COUT*K] sums of the row tree
   extern __shared__ __align__(16) float dys[];
   const int tid = threadIdx.x;
   const int bands = H / kDcRows, b = blockIdx.x / bands, y0 = (blockIdx.x % bands) * kDcRows;
-  {
+  if constexpr (RELU) {
+    // channel c's 256 values of the band are contiguous in its NCHW plane
+    const size_t base = (size_t)b * COUT * H * WIDTH + (size_t)y0 * WIDTH;
+    const float* gsrc = dy + base;
+    const int8_t* msrc = mask + base;
+    float gv[SROUNDS];
+    int8_t mv[SROUNDS];
+#pragma unroll
+    for (int t = 0; t < SROUNDS; ++t) {
+      const int e = tid + t * kDcWgradThreads, c = e / NPIX, px = e - c * NPIX;
+      const bool ok = e < NPIX * COUT;
+      gv[t] = ok ? gsrc[(size_t)c * H * WIDTH + px] : 0.f;
+      mv[t] = ok ? msrc[(size_t)c * H * WIDTH + px] : (int8_t)0;
+    }
+    conv_direct_load_band<CIN, KS, WIDTH, kDcWgradThreads>(xs, x + (size_t)b * CIN * H * WIDTH, H, y0, tid);
+#pragma unroll
+    for (int t = 0; t < SROUNDS; ++t) {
+      const int e = tid + t * kDcWgradThreads, c = e / NPIX, px = e - c * NPIX;
+      if (e < NPIX * COUT) dys[px * DP + c] = gv[t] * (float)mv[t];
+    }
+    __syncthreads();
+    if (tid < 8 * COUT) {   // bias gradient: 8 segments of 32 pixels per channel, added in segment order below
+      const int c = tid % COUT, seg = tid / COUT;
+      float sum = 0.f;
+#pragma unroll 8
+      for (int q = 0; q < NPIX / 8; ++q) sum += dys[(seg * (NPIX / 8) + q) * DP + c];
+      bsum[seg][c] = sum;
+    }
+  } else {
     const float4* dsrc = reinterpret_cast<const float4*>(dy + ((size_t)b * H + y0) * WIDTH * COUT);   // NPIX * COUT contiguous floats
     float4 dv[DROUNDS];
 #pragma unroll
@@ -1022,12 +1058,14 @@ __global__ void __launch_bounds__(kDcWgradThreads, 2) conv_direct_wgrad_kernel(c
   for (int i = 0; i < KS; ++i)
 #pragma unroll
     for (int c = 0; c < KS - 1; ++c) xw[i][c] = xrow[i * (WIDTH + KS) + c];
-  const float2* drow = reinterpret_cast<const float2*>(dys) + (size_t)row * WIDTH * NPAIR + pair;
+  const float* drow = dys + (size_t)row * WIDTH * DP + 2 * pair;
 #pragma unroll
   for (int pc = 0; pc < WIDTH; ++pc) {
 #pragma unroll
     for (int i = 0; i < KS; ++i) xw[i][(pc + KS - 1) % KS] = xrow[i * (WIDTH + KS) + pc + KS - 1];
-    const float2 d = drow[pc * NPAIR];
+    float2 d;
+    if constexpr (RELU) d = make_float2(drow[pc * DP], drow[pc * DP + 1]);
+    else d = *reinterpret_cast<const float2*>(drow + pc * DP);
 #pragma unroll
     for (int i = 0; i < KS; ++i)
 #pragma unroll
@@ -1067,8 +1105,33 @@ __global__ void __launch_bounds__(kDcWgradThreads, 2) conv_direct_wgrad_kernel(c
       for (int t = 0; t < KS * KS; ++t) dst[a * K + t] = acc[a][t / KS][t % KS];
   }
   __syncthreads();
-  float* dst = part + (size_t)blockIdx.x * COUT * K;
+  float* dst = part + (size_t)blockIdx.x * PSTRIDE;
   for (int e = tid; e < COUT * K; e += kDcWgradThreads) dst[e] = dys[e];
+  if constexpr (RELU) {
+    if (tid < COUT)
+      dst[COUT * K + tid] = ((bsum[0][tid] + bsum[1][tid]) + (bsum[2][tid] + bsum[3][tid])) +
+                            ((bsum[4][tid] + bsum[5][tid]) + (bsum[6][tid] + bsum[7][tid]));
+  }
+}
+
+// Ordered sum of the blocks' partial results [nsplit][n0 + n1] into out0[n0] and out1[n1]: thread group g adds splits
+// g, g+8, ... in order and the eight sums are combined as a fixed tree (the arithmetic of the split-K fold).
+__global__ void __launch_bounds__(256) conv_direct_fold_kernel(const float* __restrict__ part, int nsplit, int n0, int n1,
+                                                               float* __restrict__ out0, float* __restrict__ out1) {
+  __shared__ float sums[8][33];
+  const int lane = threadIdx.x & 31, g = threadIdx.x >> 5, total = n0 + n1;
+  const int e = blockIdx.x * 32 + lane;
+  float acc = 0.f;
+  if (e < total)
+    for (int s2 = g; s2 < nsplit; s2 += 8) acc += part[(size_t)s2 * total + e];
+  sums[g][lane] = acc;
+  __syncthreads();
+  if (g == 0 && e < total) {
+    const float r = ((sums[0][lane] + sums[1][lane]) + (sums[2][lane] + sums[3][lane])) +
+                    ((sums[4][lane] + sums[5][lane]) + (sums[6][lane] + sums[7][lane]));
+    if (e < n0) out0[e] = r;
+    else out1[e - n0] = r;
+  }
 }
 bool conv_direct_ok(long B, int Cin, int H, int W, int Cout, int kh, int kw, int ph, int pw) {
   return Cin == 3 && kh == 5 && kw == 5 && ph == 2 && pw == 2 && Cout == 32 && W == 32 && H % kDcRows == 0 && H > 0 && B > 0 &&
@@ -1092,26 +1155,42 @@ CGTB_API int cgtb_conv_direct_fwd_bias_relu(const float* x, long B, int Cin, int
   CGTB_CHECK_LAUNCH("conv_direct_fwd");
   return 0;
 }
-CGTB_API int cgtb_conv_direct_wgrad(const float* x, long B, int Cin, int H, int W, const float* dy, int Cout, int kh, int kw, int ph, int pw,
-                                    float* dw) {
-  if (!require_runtime("cgtb_conv_direct_wgrad")) return 1;
+static int conv_direct_wgrad_any(const char* who, const float* x, long B, int Cin, int H, int W, const float* dy, const signed char* mask,
+                                 int Cout, int kh, int kw, int ph, int pw, float* dw, float* dbias) {
+  if (!require_runtime(who)) return 1;
   if (B <= 0) return 0;
-  if (!conv_direct_ok(B, Cin, H, W, Cout, kh, kw, ph, pw) || ((uintptr_t)dy & 15) != 0)
-    return fail("cgtb_conv_direct_wgrad: not supported for Cin=%d kh=%d kw=%d pad=%d,%d Cout=%d H=%d W=%d (3, 5, 5, 2, 2, 32, multiple of 8, 32) or an unaligned gradient",
-                Cin, kh, kw, ph, pw, Cout, H, W);
+  const bool relu = mask != nullptr;
+  if (!conv_direct_ok(B, Cin, H, W, Cout, kh, kw, ph, pw) || ((uintptr_t)dy & 15) != 0 || ((uintptr_t)x & 15) != 0)
+    return fail("%s: not supported for Cin=%d kh=%d kw=%d pad=%d,%d Cout=%d H=%d W=%d (3, 5, 5, 2, 2, 32, multiple of 8, 32) or an unaligned operand",
+                who, Cin, kh, kw, ph, pw, Cout, H, W);
   const long blocks = B * (H / kDcRows);
-  const int K = Cin * kh * kw;
-  float* part = (float*)scratch((size_t)blocks * Cout * K * sizeof(float));
+  const int K = Cin * kh * kw, pstride = Cout * K + (relu ? Cout : 0);
+  float* part = (float*)scratch((size_t)blocks * pstride * sizeof(float));
   if (!part) return 1;
-  const size_t smem = std::max<size_t>((size_t)kDcRows * 32 * 32, (size_t)(kDcRows / 2) * Cout * K) * sizeof(float);
+  const size_t smem = std::max<size_t>((size_t)kDcRows * 32 * 33, (size_t)(kDcRows / 2) * Cout * K) * sizeof(float);
   static bool attr = false;
   if (!attr) {
-    CGTB_CUDA_TRY(cudaFuncSetAttribute(conv_direct_wgrad_kernel<3, 5, 32, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CGTB_CUDA_TRY(cudaFuncSetAttribute(conv_direct_wgrad_kernel<3, 5, 32, 32, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CGTB_CUDA_TRY(cudaFuncSetAttribute(conv_direct_wgrad_kernel<3, 5, 32, 32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr = true;
   }
-  CGTB_LAUNCH((conv_direct_wgrad_kernel<3, 5, 32, 32>), (unsigned)blocks, kDcWgradThreads, smem, x, dy, H, part);
-  if (blocks > 1) cgtb::tc_splitk_fold(1, Cout, K, (int)blocks, part, dw, K, 0);
-  else CGTB_CUDA_TRY(cudaMemcpyAsync(dw, part, (size_t)Cout * K * sizeof(float), cudaMemcpyDeviceToDevice, rt().stream));
-  CGTB_CHECK_LAUNCH("conv_direct_wgrad");
+  if (relu) {
+    CGTB_LAUNCH((conv_direct_wgrad_kernel<3, 5, 32, 32, true>), (unsigned)blocks, kDcWgradThreads, smem, x, dy, (const int8_t*)mask, H, part);
+    CGTB_LAUNCH(conv_direct_fold_kernel, (unsigned)cgtb_ceil_div(pstride, 32), 256, 0, part, (int)blocks, Cout * K, Cout, dw, dbias);
+  } else {
+    CGTB_LAUNCH((conv_direct_wgrad_kernel<3, 5, 32, 32, false>), (unsigned)blocks, kDcWgradThreads, smem, x, dy, (const int8_t*)nullptr, H, part);
+    if (blocks > 1) cgtb::tc_splitk_fold(1, Cout, K, (int)blocks, part, dw, K, 0);
+    else CGTB_CUDA_TRY(cudaMemcpyAsync(dw, part, (size_t)Cout * K * sizeof(float), cudaMemcpyDeviceToDevice, rt().stream));
+  }
+  CGTB_CHECK_LAUNCH(who);
   return 0;
+}
+CGTB_API int cgtb_conv_direct_wgrad(const float* x, long B, int Cin, int H, int W, const float* dy, int Cout, int kh, int kw, int ph, int pw,
+                                    float* dw) {
+  return conv_direct_wgrad_any("cgtb_conv_direct_wgrad", x, B, Cin, H, W, dy, nullptr, Cout, kh, kw, ph, pw, dw, nullptr);
+}
+CGTB_API int cgtb_conv_direct_wgrad_relu(const float* x, long B, int Cin, int H, int W, const signed char* mask, const float* g, int Cout,
+                                         int kh, int kw, int ph, int pw, float* dw, float* dbias) {
+  if (!mask || !dbias) return fail("cgtb_conv_direct_wgrad_relu: mask and dbias are required");
+  return conv_direct_wgrad_any("cgtb_conv_direct_wgrad_relu", x, B, Cin, H, W, g, mask, Cout, kh, kw, ph, pw, dw, dbias);
 }

@@ -388,6 +388,26 @@ OP_BYREF(cgtb_op_conv_direct_wgrad) {
   cgtb_conv_direct_wgrad((const float*)x->data(), xs[0], (int)xs[1], (int)xs[2], (int)xs[3], (const float*)dy->data(), cl->cout, cl->kh, cl->kw,
                          cl->ph, cl->pw, (float*)out->data());
 }
+// ConvDirectWgradRelu: (x NCHW, relu mask i1 NCHW, g f4 NCHW) -> tuple(filter gradient [Cout, Cin*kh*kw], bias gradient [1,Cout,1,1])
+OP_BYREF(cgtb_op_conv_direct_wgrad_relu) {
+  const ConvDirectClosure* cl = (const ConvDirectClosure*)cl0;
+  cgtArray *x = ARR(reads[0]), *mask = ARR(reads[1]), *g = ARR(reads[2]);
+  cgtTuple* out = (cgtTuple*)write0;
+  cgtArray *dw = ARR(out->getitem(0)), *db = ARR(out->getitem(1));
+  if (!all_gpu({x, mask, g, dw, db})) { fail("ConvDirectWgradRelu: operands must be on the GPU"); return; }
+  if (x->ndim() != 4 || x->dtype() != cgt_f4 || g->dtype() != cgt_f4 || mask->dtype() != cgt_i1 || cl->sv != 1 || cl->sh != 1) {
+    fail("ConvDirectWgradRelu: a stride-1 convolution of a float32 NCHW image, an int8 mask and a float32 gradient");
+    return;
+  }
+  const long* xs = x->shape();
+  if (g->size() != xs[0] * xs[2] * xs[3] * cl->cout || mask->size() != g->size() || dw->size() != (long)cl->cout * xs[1] * cl->kh * cl->kw ||
+      db->size() != cl->cout) {
+    fail("ConvDirectWgradRelu: operand shapes do not fit together");
+    return;
+  }
+  cgtb_conv_direct_wgrad_relu((const float*)x->data(), xs[0], (int)xs[1], (int)xs[2], (int)xs[3], (const signed char*)mask->data(),
+                              (const float*)g->data(), cl->cout, cl->kh, cl->kw, cl->ph, cl->pw, (float*)dw->data(), (float*)db->data());
+}
 // ConvWgrad: (dy [M,C], col [M,ldcol]) -> dy^T * col[:, :K] as [C,K]: the filter gradient from a column matrix
 // with padded rows; K is the output's second extent
 OP_BYREF(cgtb_op_conv_wgrad) {

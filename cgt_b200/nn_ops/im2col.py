@@ -270,6 +270,37 @@ class ConvDirectWgrad(core.Op):
         return "ConvDirectWgrad{%s}" % (tuple(self.info),)
 
 
+class ConvDirectWgradRelu(core.Op):
+    """(x NCHW [B,Cin,H,W], relu mask i1 NCHW [B,Cout,H,W], g f4 NCHW) -> tuple(filter gradient [Cout, Cin*kh*kw], bias
+    gradient [1,Cout,1,1]): ConvDirectWgrad fed by the layer's backward inputs. compilation.fuse_conv_direct puts it in
+    place of ReluGradNHWC + ConvDirectWgrad when the channels-last gradient has no other reader (a first layer has no
+    data gradient), so that gradient is never written; the kernel forms mask * g while it stages its tile."""
+    available_impls = ("native_gpu",)
+
+    def __init__(self, info, cout):
+        self.info = info
+        self.cout = int(cout)
+
+    def get_diff(self, n):
+        return [False] * n
+
+    def shp_apply(self, inputs):
+        info = self.info
+        one = core.cgt.constant(1)
+        c = core.cgt.constant(self.cout)
+        return ([c, core.cgt.size(inputs[0], 1) * (info.kernel_h * info.kernel_w)], [one, c, one, one])
+
+    def typ_apply(self, inputs):
+        return core.TupleType(core.TensorType("f4", 2), core.TensorType("f4", 4))
+
+    def get_native_compile_info(self, input_types, devtype):
+        return core.NativeCompileInfo(None, prebuilt="cgtb_op_conv_direct_wgrad_relu",
+                                      closure_triples=info2closure(self.info) + [("cout", ctypes.c_int, self.cout)])
+
+    def __repr__(self):
+        return "ConvDirectWgradRelu{%s}" % (tuple(self.info),)
+
+
 class ConvFwdBiasRelu(core.Op):
     """(x NHWC [B,H,W,Cin], filters, bias [1,Cout,1,1], B, Cout, Ho, Wo) -> tuple(mask i1, relu f4), both NCHW
     [B,Cout,Ho,Wo]: the forward pass of a stride-1 convolution layer in one kernel. The filters are the layer's bank

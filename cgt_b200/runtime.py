@@ -109,6 +109,7 @@ def _declare(lib):
         "cgtb_concat_rows": (ci, [ci, vp, c_long_p, vp]),
         "cgtb_conv_direct_fwd_bias_relu": (ci, [vp, cl, ci, ci, ci, vp, ci, ci, ci, ci, ci, vp, vp, vp]),
         "cgtb_conv_direct_wgrad": (ci, [vp, cl, ci, ci, ci, vp, ci, ci, ci, ci, ci, vp]),
+        "cgtb_conv_direct_wgrad_relu": (ci, [vp, cl, ci, ci, ci, vp, vp, ci, ci, ci, ci, ci, vp, vp]),
         "cgtb_reduce_rkr_f32_static": (ci, [ci, cl, cl, cl, vp, vp]), "cgtb_reduce_static_max_k": (cl, []),
     }
     for (name, (restype, argtypes)) in sig.items():

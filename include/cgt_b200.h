@@ -313,6 +313,12 @@ int cgtb_conv_direct_fwd_bias_relu(const float* x_nchw, long B, int Cin, int H, 
                                    int pw, const float* bias, float* y_nchw, signed char* mask_nchw);
 int cgtb_conv_direct_wgrad(const float* x_nchw, long B, int Cin, int H, int W, const float* dy_nhwc, int Cout, int kh, int kw, int ph,
                            int pw, float* dw);
+/* The same filter gradient taken straight from the layer's backward inputs: dy = mask * g with the relu's NCHW mask
+ * (int8 0/1) and the NCHW gradient g of the relu output (the reference's ElwiseBinary multiply, cgt/nn.py:44-45
+ * differentiated), formed while the kernel stages its tile; dbias[Cout] = sum of dy over batch and pixels (the
+ * reference's Sum{0,2,3}). Neither dy nor its channels-last copy is written. */
+int cgtb_conv_direct_wgrad_relu(const float* x_nchw, long B, int Cin, int H, int W, const signed char* mask_nchw, const float* g_nchw,
+                                int Cout, int kh, int kw, int ph, int pw, float* dw, float* dbias);
 
 /* Sum / Max over a set of axes, keepdims (cgt/core.py:1663-1738) */
 int cgtb_reduce(int kind, int dtype, int ndim, const long* shape, const int* reduced, const void* in, void* out);

@@ -187,7 +187,9 @@ def test_conv_direct_substitution(rt):
             reprs = [repr(i) for i in f.eg.instrs]
             losses = [float(f(*cfg.batch(s))[0]) for s in range(4)]
             res[fuse] = (reprs, losses, [np.asarray(p.op.get_value()).copy() for p in cfg.params])
-    assert any("ConvDirectFwd" in r for r in res[True][0]) and any("ConvDirectWgrad" in r for r in res[True][0])
+    assert any("ConvDirectFwd" in r for r in res[True][0]) and any("ConvDirectWgradRelu" in r for r in res[True][0])
+    # the first layer's channels-last gradient is never formed: one ReluGradNHWC per later layer is left
+    assert sum("op:ReluGradNHWC" in r for r in res[True][0]) == sum("op:ReluGradNHWC" in r for r in res[False][0]) - 1
     assert not any("Im2Col" in r for r in res[True][0]) and any("Im2Col" in r for r in res[False][0])
     np.testing.assert_allclose(res[True][1], res[False][1], rtol=1e-4)
     for (a, b) in zip(res[False][2], res[True][2]):

@@ -576,6 +576,26 @@ def test_conv_direct_first_layer(rt, B, H):
     got_w = out.get()
     scale = np.sqrt(B * H * W)
     assert np.abs(got_w - exact_w).max() <= 4 * np.abs(want_w - exact_w).max() + 1e-5 * scale
+    # the same gradient from the layer's backward inputs: dy = mask * g (both NCHW), plus the bias gradient
+    g = rs.randn(B, Cout, H, W).astype("f4")
+    m = (rs.rand(B, Cout, H, W) < 0.5).astype("i1")
+    dy2 = np.ascontiguousarray((g * m).transpose(0, 2, 3, 1))
+    exact_w2 = dy2.reshape(-1, Cout).astype("f8").T @ col.astype("f8")
+    want_w2 = O.mul22(dy2.reshape(-1, Cout), col, True, False)
+    dg, dm, out2, outb = Dev(g), Dev(m), Dev(np.full((Cout, Cin * k * k), np.nan, "f4")), Dev(np.full((Cout,), np.nan, "f4"))
+    call("cgtb_conv_direct_wgrad_relu", dx.ptr, B, Cin, H, W, dm.ptr, dg.ptr, Cout, k, k, pad, pad, out2.ptr, outb.ptr)
+    assert np.abs(out2.get() - exact_w2).max() <= 4 * np.abs(want_w2 - exact_w2).max() + 1e-5 * scale
+    exact_b = (g.astype("f8") * m).sum(axis=(0, 2, 3))
+    want_b = (g * m).sum(axis=(0, 2, 3), dtype="f4")
+    assert np.abs(outb.get() - exact_b).max() <= 4 * np.abs(want_b - exact_b).max() + 1e-5 * scale
+    # given the product it forms, it adds in the order of the channels-last entry point (whose fold of fewer than 16
+    # partial results adds them one after the other instead): identical bits
+    ddy2 = Dev(dy2)
+    call("cgtb_conv_direct_wgrad", dx.ptr, B, Cin, H, W, ddy2.ptr, Cout, k, k, pad, pad, out.ptr)
+    if B * (H // 8) >= 16:
+        assert np.array_equal(out.get(), out2.get())
+    else:
+        np.testing.assert_allclose(out.get(), out2.get(), rtol=1e-4, atol=1e-5 * scale)
     # another layer is refused, not approximated
     rc = runtime.lib().cgtb_conv_direct_wgrad(dx.ptr, B, 4, H, W, ddy.ptr, Cout, k, k, pad, pad, out.ptr)
     assert rc != 0 and "not supported" in runtime.last_error()
