@@ -344,7 +344,7 @@ def test_conv_grad_input_substitution(rt):
     changes, so losses and parameters agree to float32 tolerance."""
     res = {}
     for fuse in (False, True):
-        with cgt.scoped_update_config(fuse_conv_grad_input=fuse, use_cuda_graphs=False):
+        with cgt.scoped_update_config(fuse_conv_grad_input=fuse, fuse_conv_direct=False, use_cuda_graphs=False):
             cfg = configs.BUILDERS["cifar"](**SMALL["cifar"])
             f = cfg.compile()
             names = [repr(instr) for instr in f.eg.instrs]
