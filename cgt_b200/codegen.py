@@ -157,7 +157,7 @@ def rows_source(op):
     lines = ["template <int E>", "__global__ void __launch_bounds__(128) rows_kernel(const long R, const long C, const void* const* in_, void* const* out_) {"]
     params, args = [], []
     for (k, kind) in enumerate(op.in_kinds):
-        ctype = "long" if kind == 3 else "float"
+        ctype = "long" if kind in (3, 8) else "float"
         params.append("const %s* __restrict__ in%d" % (ctype, k))
         args.append("(const %s*)in[%d]" % (ctype, k))
     for q in range(len(op.out_regs)):
@@ -173,6 +173,9 @@ def rows_source(op):
         if kind in (0, 6):
             base = "in%d + row * C" % k if kind == 0 else "in%d" % k
             lines += ["#pragma unroll", "  for (int e = 0; e < E; ++e) { const long c = lane + 32 * e; r%d[e] = c < C ? (%s)[c] : 0.0f; }" % (k, base)]
+        elif kind == 8:
+            lines += ["  { const long hot = in%d[row];" % k, "#pragma unroll",
+                      "    for (int e = 0; e < E; ++e) r%d[e] = (lane + 32 * e == hot) ? 1.0f : 0.0f; }" % k]
         else:
             src = {5: "in%d[row]" % k, 2: "in%d[0]" % k, 3: "(float)in%d[0]" % k}[kind]
             lines += ["  { const float v = %s;" % src, "#pragma unroll", "    for (int e = 0; e < E; ++e) r%d[e] = v; }" % k]
@@ -184,7 +187,8 @@ def rows_source(op):
         elif arity == 2:
             lines += ["#pragma unroll", "  for (int e = 0; e < E; ++e) r%d[e] = binary_apply<float, float, float>(%d, r%d[e], r%d[e]);" % (d, code, a, b)]
         else:
-            lines += ["  { float s = 0.0f;", "#pragma unroll", "    for (int e = 0; e < E; ++e) if (lane + 32 * e < C) s += r%d[e];" % a,
+            cond = "lane + 32 * e < C" if arity == 3 else "lane + 32 * e < C && r%d[e] != 0.0f" % b
+            lines += ["  { float s = 0.0f;", "#pragma unroll", "    for (int e = 0; e < E; ++e) if (%s) s += r%d[e];" % (cond, a),
                       "#pragma unroll", "    for (int d = 16; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);",
                       "#pragma unroll", "    for (int e = 0; e < E; ++e) r%d[e] = s; }" % d]
     for (q, (reg, col)) in enumerate(zip(op.out_regs, op.out_cols)):

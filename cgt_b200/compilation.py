@@ -495,6 +495,11 @@ def _row_member(node, node2shape):
         if tuple(op.axes) != (1,) or par.dtype != "f4" or pshp is None or not (1 < pshp[1] <= max_c):
             return None
         return (R, pshp[1])
+    if isinstance(op, core.MaskedRowSum):
+        pshp = _static_shape(node2shape[node.parents[0]])
+        if pshp is None or not (1 < pshp[1] <= max_c) or any(par.dtype != "f4" for par in node.parents):
+            return None
+        return (R, pshp[1])
     if isinstance(op, core.Repeat):
         par = node.parents[0]
         pshp = _static_shape(node2shape[par])
@@ -507,6 +512,82 @@ def _row_member(node, node2shape):
         if Cn <= max_c:
             return (R, Cn)
     return None
+
+
+def fuse_flat_index_rows(outputs, updatetargs, node2shape):
+    """x[arange(R), idx] on a float32 [R, C] matrix and its gradient, as row arithmetic. The front end spells the
+    selection as GetFlatIndices(x, arange(R)*C + idx) (after constant folding: a constant vector 0, C, 2C, ... plus idx)
+    and differentiates it into IncFlatIndices(zeros[R, C], the same indices, g). With H = OneHotRows{C}(idx):
+        GetFlatIndices(x, K + idx)                -> Reshape(MaskedRowSum(x, H), [R])   (the row's selected element)
+        IncFlatIndices(Fill{0}[R, C], K + idx, g) -> H * Repeat{1}(Reshape(g, [R, 1]), C)
+    Every row holds exactly one selected element, so both forms give the reference's values (MaskedRowSum selects, it
+    does not multiply: an infinite log-probability elsewhere in the row stays out; a row whose gradient g is not finite
+    becomes NaN as a whole, where the reference leaves zeros beside the one element). For C <= 128 the row pass then takes them into the FusedRows chain around them, and the index
+    arithmetic, the zero fill, the increment and the gather are no longer launched. Runs before fuse_elementwise."""
+    all_out = list(outputs) + list(updatetargs)
+    nodes = core.topsorted(all_out)
+    out_set = set(all_out)
+    const = lambda v: core.cgt.constant(np.array(v, "i8"))
+
+    def row_index(ind, R, C):
+        """idx when `ind` is (constant vector arange(R)*C) + idx with idx an int64 [R] node"""
+        if ind.is_input() or not isinstance(ind.op, core.ElwiseBinary) or ind.op.opname != "+" or ind.dtype != "i8" or ind.ndim != 1:
+            return None
+        for (k, other) in ((ind.parents[0], ind.parents[1]), (ind.parents[1], ind.parents[0])):
+            if isinstance(getattr(k, "op", None), core.Constant) and other.ndim == 1 and other.dtype == "i8":
+                v = np.asarray(k.op.value)
+                if v.shape == (R,) and np.array_equal(v, np.arange(R, dtype="i8") * C):
+                    return other
+        return None
+
+    hot_of, replace = {}, {}
+
+    def hot(idx, R, C):
+        key = (idx, C)
+        if key not in hot_of:
+            h = core.Result(core.OneHotRows(C), [idx])
+            node2shape[h] = [const(R), const(C)]
+            hot_of[key] = h
+        return hot_of[key]
+
+    for node in nodes:
+        if node.is_input() or node in out_set or node.dtype != "f4":
+            continue
+        if isinstance(node.op, core.GetFlatIndices):
+            (x, ind) = node.parents
+            shp = _static_shape(node2shape[x]) if x in node2shape else None
+            if shp is None or len(shp) != 2 or x.dtype != "f4" or not (1 < shp[1] <= core.FusedRows.MAX_C):
+                continue
+            (R, C) = shp
+            idx = row_index(ind, R, C)
+            if idx is None:
+                continue
+            rowsum = core.Result(core.MaskedRowSum(), [x, hot(idx, R, C)])
+            node2shape[rowsum] = [const(R), const(1)]
+            new = core.Result(core.Reshape(), [rowsum, const(R)])
+            node2shape[new] = [const(R)]
+            replace[node] = new
+        elif isinstance(node.op, core.IncFlatIndices):
+            (z, ind, g) = node.parents
+            shp = _static_shape(node2shape[node]) if node in node2shape else None
+            if shp is None or len(shp) != 2 or not (1 < shp[1] <= core.FusedRows.MAX_C) or g.dtype != "f4" or g.ndim != 1:
+                continue
+            if z.is_input() or not isinstance(z.op, core.Fill) or float(z.op.value) != 0.0:
+                continue
+            (R, C) = shp
+            idx = row_index(ind, R, C)
+            if idx is None:
+                continue
+            gcol = core.Result(core.Reshape(), [g, const(R), const(1)])
+            node2shape[gcol] = [const(R), const(1)]
+            grep = core.Result(core.Repeat([1]), [gcol, const(C)])
+            node2shape[grep] = [const(R), const(C)]
+            new = core.Result(core.ElwiseBinary("*", (False, False)), [hot(idx, R, C), grep])
+            node2shape[new] = [const(R), const(C)]
+            replace[node] = new
+    if not replace:
+        return list(outputs), list(updatetargs)
+    return _rewire(outputs, updatetargs, replace)
 
 
 def fuse_elementwise(outputs, updatetargs, node2shape, rows=False):
@@ -578,8 +659,11 @@ def fuse_elementwise(outputs, updatetargs, node2shape, rows=False):
                     continue
                 cands.append(g)
             chosen = None
+
+            def n_ops(g):   # a Repeat costs the row kernel nothing: the value already sits in every lane
+                return sum(1 for m in members[g] if not isinstance(m.op, core.Repeat)) if rows else len(members[g])
             for g in cands:
-                if len(members[g]) >= core.FusedElwise.MAX_OPS:
+                if n_ops(g) >= core.FusedElwise.MAX_OPS:
                     continue
                 # other parents' groups that neither depend on g nor g on them (x.W + b and h.U + c: two
                 # independent chains that meet in this node) are merged into g
@@ -589,7 +673,7 @@ def fuse_elementwise(outputs, updatetargs, node2shape, rows=False):
                         continue
                     if not all(mergeable(m, g2) for m in merged):
                         continue
-                    if sum(len(members[m]) for m in merged) + len(members[g2]) >= core.FusedElwise.MAX_OPS:
+                    if sum(n_ops(m) for m in merged) + n_ops(g2) >= core.FusedElwise.MAX_OPS:
                         continue
                     merged.append(g2)
                 outside = 0
@@ -764,7 +848,7 @@ def fuse_elementwise(outputs, updatetargs, node2shape, rows=False):
 
     def emit_rows(mem):
         """One FusedRows node for `mem`, if it holds a sum; halves of a group beyond the kernel's limits are tried again."""
-        if not any(isinstance(node.op, core.Sum) for node in mem):
+        if not any(isinstance(node.op, (core.Sum, core.MaskedRowSum)) for node in mem):
             return
         F = core.FusedElwise
         memset = set(mem)
@@ -788,7 +872,9 @@ def fuse_elementwise(outputs, updatetargs, node2shape, rows=False):
                 shp = _static_shape(node2shape[par])
                 if par.dtype != "f4" or shp is None or len(shp) != 2:
                     return None
-                if isinstance(par.op, core.Repeat) and not par.is_input() and list(par.op.axes) == [0] and shp[1] == C \
+                if not par.is_input() and isinstance(par.op, core.OneHotRows) and shp[1] == C and par.parents[0].dtype == "i8":
+                    kind, src = 8, par.parents[0]      # the selection matrix of a column number per row: read the numbers
+                elif isinstance(par.op, core.Repeat) and not par.is_input() and list(par.op.axes) == [0] and shp[1] == C \
                         and par.parents[0].dtype == "f4":
                     kind, src = 6, par.parents[0]      # a [1, C] row repeated down the rows: read the row itself
                 elif shp[1] == C:
@@ -824,6 +910,8 @@ def fuse_elementwise(outputs, updatetargs, node2shape, rows=False):
                 continue
             if isinstance(node.op, core.Sum):
                 program.append((3, 0, regs[0], 0))
+            elif isinstance(node.op, core.MaskedRowSum):
+                program.append((4, 0, regs[0], regs[1]))
             elif isinstance(node.op, core.ElwiseUnary):
                 program.append((1, core.UNARY_OPCODE[node.op.opname], regs[0], 0))
             else:
@@ -831,7 +919,7 @@ def fuse_elementwise(outputs, updatetargs, node2shape, rows=False):
             result_reg[node] = n_in + len(program) - 1
         shape_input = None
         for (k, kind) in enumerate(in_kinds):
-            if kind in (0, 5):
+            if kind in (0, 5, 8):
                 shape_input = k
                 break
         if shape_input is None:
@@ -1675,6 +1763,8 @@ def apply_graph_rewrites(outputs_simple, updatetargs_simple, node2shape):
         outputs_simple, updatetargs_simple = batch_summed_products(outputs_simple, updatetargs_simple, node2shape)
         outputs_simple, updatetargs_simple = batch_shared_weight_products(outputs_simple, updatetargs_simple, node2shape)
     if config["fuse_elementwise"]:
+        if config["fuse_rows"] and config["fuse_flat_index_rows"]:
+            outputs_simple, updatetargs_simple = fuse_flat_index_rows(outputs_simple, updatetargs_simple, node2shape)
         if config["fuse_rows"]:
             outputs_simple, updatetargs_simple = fuse_elementwise(outputs_simple, updatetargs_simple, node2shape, rows=True)
         outputs_simple, updatetargs_simple = fuse_elementwise(outputs_simple, updatetargs_simple, node2shape)

@@ -1285,8 +1285,9 @@ class FusedRows(Op):
     each costs far more in launch latency than in bytes.
 
     Not part of the reference's Op set: compilation.fuse_elementwise(rows=True) forms these nodes. ``program`` as in
-    FusedElwise plus (3, 0, a, 0): the sum of register a over the row. ``in_kinds``: 0 an [R, C] array, 5 an [R, 1]
-    array, 6 a [1, C] array, 2 / 3 scalars. ``out_cols[j]``: output j is [R, 1] rather than [R, C]. ``shape_input``: an
+    FusedElwise plus (3, 0, a, 0): the sum of register a over the row, and (4, 0, a, b): the sum of the elements of a
+    where register b is not zero (MaskedRowSum). ``in_kinds``: 0 an [R, C] array, 5 an [R, 1]
+    array, 6 a [1, C] array, 2 / 3 scalars, 8 an int64 [R] array of column numbers read as OneHotRows of it. ``out_cols[j]``: output j is [R, 1] rather than [R, C]. ``shape_input``: an
     input whose axis 0 gives R."""
     available_impls = ("native_gpu",)
     return_type = "byref"
@@ -1429,6 +1430,75 @@ class Reshape(Op):
     def get_native_compile_info(self, input_types, devtype):
         return NativeCompileInfo(None, prebuilt="cgtb_op_reshape",
                                  closure_triples=[("ndim", ctypes.c_int, len(input_types) - 1)])
+
+
+class OneHotRows(Op):
+    """(idx int64 [R]) -> float32 [R, C] with a one in column idx[r] of row r, zeros elsewhere.
+
+    Not part of the reference's Op set. compilation.fuse_flat_index_rows writes x[arange(R), idx] on an [R, C] matrix
+    (GetFlatIndices on arange(R)*C + idx, cgt/core.py:1781-1812) as Sum{1}(x * OneHotRows(idx)) and its gradient
+    (IncFlatIndices on zeros, cgt/core.py:1814-1860) as OneHotRows(idx) * g, so that both join the row chain around them
+    (a softmax cross-entropy and its pullback become one FusedRows launch, which reads idx itself: input kind 8); a
+    OneHotRows node left outside such a chain is written by its own kernel."""
+    available_impls = ("python", "native_gpu")
+    return_type = "byref"
+
+    def __init__(self, C):
+        self.C = int(C)
+
+    def get_diff(self, num_inputs):
+        return [False] * num_inputs
+
+    def get_py_func(self, input_types):
+        def f(reads, write):
+            idx = np.asarray(reads[0]).astype("i8").reshape(-1)
+            write[...] = (np.arange(self.C, dtype="i8")[None, :] == idx[:, None]).astype("f4")
+        return f
+
+    def shp_apply(self, inputs):
+        return [cgt.size(inputs[0], 0), cgt.constant(np.array(self.C, "i8"))]
+
+    def typ_apply(self, input_types):
+        return TensorType("f4", 2)
+
+    def get_native_compile_info(self, input_types, devtype):
+        return NativeCompileInfo(None, prebuilt="cgtb_op_onehot_rows", closure_triples=[("C", ctypes.c_long, self.C)])
+
+    def __repr__(self):
+        return "OneHotRows{%d}" % self.C
+
+
+class MaskedRowSum(Op):
+    """(x f4 [R, C], m f4 [R, C]) -> [R, 1]: the sum of each row's elements of x where m is not zero. With
+    m = OneHotRows(idx) it is x[r, idx[r]] itself: the element is selected, not multiplied by one and added to zero
+    products, so an infinite element elsewhere in the row (a log-probability of -inf) stays out of the result as it
+    does with the reference's GetFlatIndices (cgt/core.py:1781-1812).
+
+    Not part of the reference's Op set: compilation.fuse_flat_index_rows forms it; in a FusedRows program it is the
+    entry (4, 0, a, b)."""
+    available_impls = ("python", "native_gpu")
+    return_type = "byref"
+
+    def get_diff(self, num_inputs):
+        return [False] * num_inputs
+
+    def get_py_func(self, input_types):
+        def f(reads, write):
+            (x, m) = (np.asarray(reads[0]), np.asarray(reads[1]))
+            write[...] = np.where(m != 0, x, np.float32(0)).sum(axis=1, keepdims=True, dtype="f4")
+        return f
+
+    def shp_apply(self, inputs):
+        return [cgt.size(inputs[0], 0), cgt.constant(np.array(1, "i8"))]
+
+    def typ_apply(self, input_types):
+        return TensorType("f4", 2)
+
+    def get_native_compile_info(self, input_types, devtype):
+        return NativeCompileInfo(None, prebuilt="cgtb_op_masked_row_sum", closure_triples=[])
+
+    def __repr__(self):
+        return "MaskedRowSum"
 
 
 class LeadingSlice(Op):
@@ -2267,7 +2337,7 @@ _DEFAULTS = dict(
     debug=False, precision="single", backend="native", cache_dir="~/.cgt_b200_cache", enable_inplace_opt=True,
     enable_simplification=True, parallel=False, num_threads=1, force_python_impl=False, debug_cpp=False, verbose=False,
     # additions for this backend
-    devtype="gpu", device_index=0, use_cuda_graphs=True, fuse_elementwise=True, jit_fused_elementwise=True, fuse_conv_dgrad=True, fuse_conv_output=True, fuse_conv_grad_input=True, fuse_conv_implicit=True, fuse_conv_direct=True, merge_parameter_updates=True, fuse_rows=True, fuse_slice_sums=True, fuse_slice_views=True, batch_summed_products=True,
+    devtype="gpu", device_index=0, use_cuda_graphs=True, fuse_elementwise=True, jit_fused_elementwise=True, fuse_conv_dgrad=True, fuse_conv_output=True, fuse_conv_grad_input=True, fuse_conv_implicit=True, fuse_conv_direct=True, fuse_flat_index_rows=True, merge_parameter_updates=True, fuse_rows=True, fuse_slice_sums=True, fuse_slice_views=True, batch_summed_products=True,
     pad_conv_columns=True, profile=False,
 )
 

@@ -411,6 +411,10 @@ __global__ void fused_rows_kernel(const RowArgs a) {
         const long c = lane + 32 * e;
         r[k][e] = c < C ? src[c] : 0.0f;
       }
+    } else if (kind == CGTB_FIN_ROWHOT) {
+      const long hot = ((const long*)a.in[k])[row];
+#pragma unroll
+      for (int e = 0; e < E; ++e) r[k][e] = (lane + 32 * e == hot) ? 1.0f : 0.0f;
     } else {
       const float v = kind == CGTB_FIN_COL ? ((const float*)a.in[k])[row]
                                            : (kind == CGTB_FIN_SCALAR_F4 ? *(const float*)a.in[k] : (float)*(const long*)a.in[k]);
@@ -429,9 +433,16 @@ __global__ void fused_rows_kernel(const RowArgs a) {
       for (int e = 0; e < E; ++e) r[dst][e] = binary_apply<float, float, float>(code, r[ra][e], r[rb][e]);
     } else {
       float s = 0.0f;
+      if (arity == 3) {
 #pragma unroll
-      for (int e = 0; e < E; ++e)
-        if (lane + 32 * e < C) s += r[ra][e];
+        for (int e = 0; e < E; ++e)
+          if (lane + 32 * e < C) s += r[ra][e];
+      } else {   // 4: the elements of a where b is not zero (no product: an infinite unselected element stays out)
+        const int rb = P.op_b[o];
+#pragma unroll
+        for (int e = 0; e < E; ++e)
+          if (lane + 32 * e < C && r[rb][e] != 0.0f) s += r[ra][e];
+      }
 #pragma unroll
       for (int d = 16; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
 #pragma unroll
@@ -453,6 +464,46 @@ __global__ void fused_rows_kernel(const RowArgs a) {
   }
 }
 
+namespace {
+__global__ void onehot_rows_kernel(const long* __restrict__ idx, long R, long C, float* __restrict__ out) {
+  const long n = R * C;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    const long r = i / C;
+    out[i] = (i - r * C == idx[r]) ? 1.0f : 0.0f;
+  }
+}
+}  // namespace
+namespace {
+__global__ void masked_row_sum_kernel(const float* __restrict__ x, const float* __restrict__ m, long R, long C, float* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const long row = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= R) return;
+  float s = 0.0f;
+  for (long c = lane; c < C; c += 32)
+    if (m[row * C + c] != 0.0f) s += x[row * C + c];
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+  if (lane == 0) out[row] = s;
+}
+}  // namespace
+CGTB_API int cgtb_masked_row_sum(const float* x, const float* m, long R, long C, float* out) {
+  if (!require_runtime("cgtb_masked_row_sum")) return 1;
+  if (R < 0 || C < 1) return fail("cgtb_masked_row_sum: R >= 0 and C >= 1");
+  if (R == 0) return 0;
+  CGTB_LAUNCH(masked_row_sum_kernel, (unsigned)cgtb_ceil_div(R, 4), 128, 0, x, m, R, C, out);
+  CGTB_CHECK_LAUNCH("masked_row_sum");
+  return 0;
+}
+CGTB_API int cgtb_onehot_rows(const long* idx, long R, long C, float* out) {
+  if (!require_runtime("cgtb_onehot_rows")) return 1;
+  if (R < 0 || C < 1) return fail("cgtb_onehot_rows: R >= 0 and C >= 1");
+  if (R == 0) return 0;
+  const long blocks = std::min<long>(cgtb_ceil_div(R * C, 256), (long)rt().sm_count * 8);
+  CGTB_LAUNCH(onehot_rows_kernel, (unsigned)blocks, 256, 0, idx, R, C, out);
+  CGTB_CHECK_LAUNCH("onehot_rows");
+  return 0;
+}
+
 CGTB_API int cgtb_fused_rows(const cgtbRowProgram* prog, long R, long C, const void* const* in, void* const* out) {
   if (!require_runtime("cgtb_fused_rows")) return 1;
   if (!prog || prog->n_in < 1 || prog->n_in > CGTB_FUSED_MAX_IN || prog->n_ops < 1 || prog->n_ops > CGTB_FUSED_MAX_OPS || prog->n_out < 1 ||
@@ -461,12 +512,13 @@ CGTB_API int cgtb_fused_rows(const cgtbRowProgram* prog, long R, long C, const v
   if (C < 1 || C > 128) return fail("cgtb_fused_rows: rows of 1 to 128 elements, got %ld", C);
   for (int k = 0; k < prog->n_in; ++k) {
     const int kind = prog->in_kind[k];
-    if (kind != CGTB_FIN_F4 && kind != CGTB_FIN_SCALAR_F4 && kind != CGTB_FIN_SCALAR_I8 && kind != CGTB_FIN_COL && kind != CGTB_FIN_ROW)
+    if (kind != CGTB_FIN_F4 && kind != CGTB_FIN_SCALAR_F4 && kind != CGTB_FIN_SCALAR_I8 && kind != CGTB_FIN_COL && kind != CGTB_FIN_ROW &&
+        kind != CGTB_FIN_ROWHOT)
       return fail("cgtb_fused_rows: unsupported input kind %d", kind);
   }
   for (int o = 0; o < prog->n_ops; ++o) {
     const int lim = prog->n_in + o, ar = prog->op_arity[o];
-    if (ar < 1 || ar > 3 || prog->op_a[o] < 0 || prog->op_a[o] >= lim || (ar == 2 && (prog->op_b[o] < 0 || prog->op_b[o] >= lim)) ||
+    if (ar < 1 || ar > 4 || prog->op_a[o] < 0 || prog->op_a[o] >= lim || ((ar == 2 || ar == 4) && (prog->op_b[o] < 0 || prog->op_b[o] >= lim)) ||
         (ar == 1 && (prog->op_code[o] < 0 || prog->op_code[o] >= (int)CGTB_U_COUNT)) ||
         (ar == 2 && (prog->op_code[o] < 0 || prog->op_code[o] >= (int)CGTB_B_COUNT)))
       return fail("cgtb_fused_rows: malformed program");

@@ -165,8 +165,8 @@ OP_BYREF(cgtb_op_fused_rows) {
   for (int k = 0; k < P.n_in; ++k) {
     cgtArray* x = ARR(reads[k]);
     const int kind = P.in_kind[k];
-    const long want = kind == CGTB_FIN_F4 ? R * C : (kind == CGTB_FIN_COL ? R : (kind == CGTB_FIN_ROW ? C : 1));
-    const bool scalar_i8 = kind == CGTB_FIN_SCALAR_I8;
+    const long want = kind == CGTB_FIN_F4 ? R * C : ((kind == CGTB_FIN_COL || kind == CGTB_FIN_ROWHOT) ? R : (kind == CGTB_FIN_ROW ? C : 1));
+    const bool scalar_i8 = kind == CGTB_FIN_SCALAR_I8 || kind == CGTB_FIN_ROWHOT;
     if (x->devtype() != cgtGPU || x->size() != want || x->dtype() != (scalar_i8 ? cgt_i8 : cgt_f4)) {
       fail("FusedRows: operand %d has the wrong size, dtype or device", k);
       return;
@@ -174,6 +174,29 @@ OP_BYREF(cgtb_op_fused_rows) {
     in[k] = x->data();
   }
   cgtb_fused_rows(&P, R, C, in, out);
+}
+
+// OneHotRows: (idx int64 [R]) -> float32 [R, C] with a one in column idx[r] of row r. Closure: C.
+struct OneHotRowsClosure { long C; };
+OP_BYREF(cgtb_op_onehot_rows) {
+  const OneHotRowsClosure* cl = (const OneHotRowsClosure*)cl0;
+  cgtArray *idx = ARR(reads[0]), *w = ARR(write0);
+  if (!on_gpu(idx) || !on_gpu(w) || idx->dtype() != cgt_i8 || w->dtype() != cgt_f4 || w->size() != idx->size() * cl->C) {
+    fail("OneHotRows: an int64 GPU vector of R column numbers and a float32 GPU result of R x %ld", cl->C);
+    return;
+  }
+  cgtb_onehot_rows((const long*)idx->data(), idx->size(), cl->C, (float*)w->data());
+}
+
+// MaskedRowSum: (x f4 [R, C], m f4 [R, C]) -> [R, 1]: the sum of each row's elements where m is not zero
+OP_BYREF(cgtb_op_masked_row_sum) {
+  cgtArray *x = ARR(reads[0]), *m = ARR(reads[1]), *w = ARR(write0);
+  if (!all_gpu({x, m, w}) || x->ndim() != 2 || x->dtype() != cgt_f4 || m->dtype() != cgt_f4 || w->dtype() != cgt_f4 || m->size() != x->size() ||
+      w->size() != x->shape()[0]) {
+    fail("MaskedRowSum: two float32 GPU matrices of one shape [R, C] and a float32 GPU result of R elements");
+    return;
+  }
+  cgtb_masked_row_sum((const float*)x->data(), (const float*)m->data(), x->shape()[0], x->shape()[1], (float*)w->data());
 }
 
 // ScatterCols: k column pieces placed into a zero matrix. Closure: k, C, offsets, widths; reads = the pieces.

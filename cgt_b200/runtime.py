@@ -105,6 +105,8 @@ def _declare(lib):
         "cgtb_fused_elwise": (ci, [vp, cl, vp, c_long_p, c_long_p, vp]),
         "cgtb_fused_elwise_multi": (ci, [vp, ci, c_long_p, vp, vp]),
         "cgtb_fused_rows": (ci, [vp, cl, cl, vp, vp]),
+        "cgtb_onehot_rows": (ci, [vp, cl, cl, vp]),
+        "cgtb_masked_row_sum": (ci, [vp, vp, cl, cl, vp]),
         "cgtb_scatter_cols": (ci, [cl, cl, ci, c_long_p, c_long_p, vp, vp]),
         "cgtb_concat_rows": (ci, [ci, vp, c_long_p, vp]),
         "cgtb_conv_direct_fwd_bias_relu": (ci, [vp, cl, ci, ci, ci, vp, ci, ci, ci, ci, ci, vp, vp, vp]),

@@ -276,11 +276,13 @@ int cgtb_fused_elwise_multi(const cgtbFusedProgram* prog, int ntensors, const lo
 /* A chain of elementwise operations and row sums over the rows of an [R, C] matrix, C <= 128, in one launch (a softmax,
  * its logarithm and its pullback are such chains): one warp per row, values in registers, a row sum by warp shuffles.
  * Registers hold either one value per element of the row or one value per row; in_kind: CGTB_FIN_F4 an [R, C] array,
- * CGTB_FIN_COL an [R] array (one value per row), CGTB_FIN_ROW a [C] array (the same for every row), or a scalar.
+ * CGTB_FIN_COL an [R] array (one value per row), CGTB_FIN_ROW a [C] array (the same for every row), a scalar, or
+ * CGTB_FIN_ROWHOT an int64 [R] array of column numbers: the register holds 1 in column in[row] of the row and 0 elsewhere
+ * (the matrix that cgtb_onehot_rows writes, never formed).
  * op_arity 1 / 2 as in cgtbFusedProgram; op_arity 3: the sum of register op_a over the row (kept in every lane).
  * out_col[j] != 0: output j has one value per row ([R]), else [R, C]. The sum order differs from cgtb_reduce: results
  * agree with the separate launches to rounding, not bit for bit. No counterpart in the reference. */
-enum { CGTB_FIN_COL = 5, CGTB_FIN_ROW = 6 };
+enum { CGTB_FIN_COL = 5, CGTB_FIN_ROW = 6, CGTB_FIN_ROWHOT = 8 };
 typedef struct {
   int n_in, n_ops, n_out;
   int in_kind[CGTB_FUSED_MAX_IN];
@@ -294,6 +296,15 @@ typedef struct {
   void* launcher;
 } cgtbRowProgram;
 int cgtb_fused_rows(const cgtbRowProgram* prog, long R, long C, const void* const* in, void* const* out);
+
+/* out[r][c] = (c == idx[r]) ? 1 : 0, float32 [R, C]; idx int64 [R]. The selection matrix behind x[arange(R), idx]
+ * (GetFlatIndices, cgt/core.py:1781-1812) and its gradient (IncFlatIndices on zeros, cgt/core.py:1814-1860) on the rows of
+ * an [R, C] matrix: x[r, idx[r]] = sum_c x[r][c] * out[r][c]. A row whose index is outside [0, C) is all zeros. */
+int cgtb_onehot_rows(const long* idx, long R, long C, float* out);
+/* out[r] = sum over c of x[r][c] where m[r][c] != 0 (float32 [R, C] -> [R]); lane c % 32 adds its elements in order, the
+ * lanes are folded by xor shuffles. With m = cgtb_onehot_rows(idx) this is x[r][idx[r]] exactly: selected, not
+ * multiplied, so an infinite element outside the selection does not reach the result. */
+int cgtb_masked_row_sum(const float* x, const float* m, long R, long C, float* out);
 
 /* out[R, C] = zeros with k float32 pieces placed side by side: piece j ([R, width[j]]) occupies columns
  * [offset[j], offset[j] + width[j]); the pieces do not overlap. What a sum of IncSli(zeros, ...) over disjoint column

@@ -176,6 +176,29 @@ def test_row_fusion_matches_separate_kernels(rt, name):
         np.testing.assert_allclose(a, b, rtol=1e-4, atol=1e-6 * max(1.0, float(np.abs(a).max())))
 
 
+@pytest.mark.parametrize("name", ["mlp", "cifar"])
+@pytest.mark.parametrize("generated", [True, False])
+def test_flat_index_rows_substitution(rt, name, generated):
+    """logprobs[arange(batch), y] and its gradient inside the softmax row chain (the labels are read by the FusedRows
+    kernel; no index arithmetic, zero fill, increment or gather is launched): the selected elements are the same
+    numbers, so the losses agree to the last bits of the row-sum order and the parameters to float32 tolerance;
+    fewer kernels per step. generated: the kernel generated for the chain / the library's register machine."""
+    res = {}
+    for on in (False, True):
+        with cgt.scoped_update_config(fuse_flat_index_rows=on, jit_fused_elementwise=generated, use_cuda_graphs=False):
+            cfg = configs.BUILDERS[name](**SMALL[name])
+            f = cfg.compile()
+            reprs = [repr(i) for i in f.eg.instrs]
+            batches = [cfg.batch(seed) for seed in range(2)]
+            losses = [float(f(*batches[i % 2])[0]) for i in range(6)]
+            res[on] = (reprs, losses, [np.asarray(p.op.get_value()).copy() for p in cfg.params], f.stats()["last_kernel_launches"])
+    assert any("FlatIndices" in r for r in res[False][0]) and not any("FlatIndices" in r for r in res[True][0])
+    assert res[True][3] <= res[False][3] - 3
+    np.testing.assert_allclose(res[True][1], res[False][1], rtol=1e-5)
+    for (a, b) in zip(res[False][2], res[True][2]):
+        np.testing.assert_allclose(a, b, rtol=1e-3, atol=1e-5 * max(1.0, float(np.abs(a).max())))
+
+
 def test_conv_direct_substitution(rt):
     """The compiler computes the 3-channel first layer of the CIFAR-shape convnet directly from the image (no column
     matrix): losses and parameters stay within the float32 tolerance of the column-matrix graph."""

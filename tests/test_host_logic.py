@@ -259,6 +259,39 @@ def test_odd_column_rows_are_padded_for_both_products():
     assert [n for n in core.topsorted(o2 + u2) if not n.is_input() and isinstance(n.op, im2col_ops.ConvWgrad)] == wg
 
 
+def test_flat_index_rows_rewrite():
+    """logprobs[arange(batch), y] and its gradient on the MLP configuration (no GPU needed: only the rewritten graph is
+    inspected, and the new Ops' host implementations are evaluated with numpy): GetFlatIndices / IncFlatIndices / the
+    zero fill / the index addition disappear, and one FusedRows node reads the labels themselves (input kind 8) and
+    holds the selection as entry (4, 0, a, b)."""
+    cfg = configs.build_mlp(batch=16)
+    outs, _usrc, utargs, analysis = compilation.simplify_for_execution([cfg.loss] + list(cfg.extra_outputs), cfg.updates)
+    n2s = analysis["node2shape"]
+    before = [n for n in core.topsorted(outs + utargs) if not n.is_input()]
+    assert any(isinstance(n.op, core.GetFlatIndices) for n in before) and any(isinstance(n.op, core.IncFlatIndices) for n in before)
+    o, u = compilation.apply_graph_rewrites(outs, utargs, n2s)
+    nodes = [n for n in core.topsorted(o + u) if not n.is_input()]
+    assert not any(isinstance(n.op, (core.GetFlatIndices, core.IncFlatIndices, core.OneHotRows, core.MaskedRowSum)) for n in nodes)
+    rows = [n for n in nodes if isinstance(n.op, core.FusedRows)]
+    assert len(rows) == 1 and 8 in rows[0].op.in_kinds and any(p[0] == 4 for p in rows[0].op.program)
+    assert rows[0].parents[rows[0].op.in_kinds.index(8)].dtype == "i8"
+    # with the switch off the flat-index Ops stay
+    with cgt.scoped_update_config(fuse_flat_index_rows=False):
+        outs2, _s, utargs2, analysis2 = compilation.simplify_for_execution([cfg.loss] + list(cfg.extra_outputs), cfg.updates)
+        o2, u2 = compilation.apply_graph_rewrites(outs2, utargs2, analysis2["node2shape"])
+    assert any(isinstance(n.op, core.GetFlatIndices) for n in core.topsorted(o2 + u2) if not n.is_input())
+    # host implementations of the two Ops
+    rs = np.random.RandomState(0)
+    x, idx = rs.randn(5, 7).astype("f4"), np.array([6, 0, 3, 3, 1], "i8")
+    x[2, 0] = -np.inf
+    hot = np.empty((5, 7), "f4")
+    core.OneHotRows(7).get_py_func(None)([idx], hot)
+    assert np.array_equal(hot, (np.arange(7)[None, :] == idx[:, None]).astype("f4"))
+    pick = np.empty((5, 1), "f4")
+    core.MaskedRowSum().get_py_func(None)([x, hot], pick)
+    assert np.array_equal(pick[:, 0], x[np.arange(5), idx])
+
+
 def test_recurrent_graph_rewrites():
     """The rewrites aimed at unrolled recurrent networks, on the LSTM configuration with six time steps (no GPU needed:
     only the rewritten graph is inspected). x[t] becomes a view, the gate slices are read in place by the fused chains (no

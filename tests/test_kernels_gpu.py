@@ -798,6 +798,43 @@ def test_fused_rows_softmax_chain(rt, R, C):
     np.testing.assert_allclose(o_sum.get(), red.get(), rtol=3e-6)
 
 
+@pytest.mark.parametrize("R,C", [(128, 10), (64, 65), (3, 128), (1000, 33)])
+def test_row_selection_kernels(rt, R, C):
+    """x[arange(R), idx] and its gradient as row arithmetic: cgtb_onehot_rows against the reference's
+    IncFlatIndices(zeros, arange(R)*C + idx, ones) (cgt/core.py:1814-1860), cgtb_masked_row_sum against
+    GetFlatIndices (cgt/core.py:1781-1812) bit for bit, with a -inf outside the selection that must not reach the
+    result, and the same through one cgtb_fused_rows program (input kind 8, entry (4, 0, a, b))."""
+    rs = np.random.RandomState(R + C)
+    x = rs.randn(R, C).astype("f4")
+    idx = rs.randint(0, C, size=R).astype("i8")
+    x[0, (idx[0] + 1) % C] = -np.inf
+    g = rs.randn(R).astype("f4")
+    flat = np.arange(R, dtype="i8") * C + idx
+    hot_np = O.incflat(np.zeros((R, C), "f4"), flat, np.ones(R, "f4"))
+    assert np.array_equal(hot_np, (np.arange(C)[None, :] == idx[:, None]).astype("f4"))
+    dx, didx, dg = Dev(x), Dev(idx), Dev(g.reshape(R, 1))
+    hot, pick = Dev(np.full((R, C), np.nan, "f4")), Dev(np.full((R, 1), np.nan, "f4"))
+    call("cgtb_onehot_rows", didx.ptr, R, C, hot.ptr)
+    assert np.array_equal(hot.get(), hot_np)
+    call("cgtb_masked_row_sum", dx.ptr, hot.ptr, R, C, pick.ptr)
+    assert np.array_equal(pick.get().reshape(R), O.getflat(x, flat))
+    # one program: 0 x, 1 idx (kind 8), 2 g [R,1]; 3 = pick(0 where 1), 4 = hot * g
+    P = _RowProgram()
+    P.n_in, P.n_ops, P.n_out = 3, 2, 2
+    for (k, kind) in enumerate([0, 8, 5]):
+        P.in_kind[k] = kind
+    for (j, (ar, opc, a, b)) in enumerate([(4, 0, 0, 1), (2, 0, 1, 2)]):
+        P.op_arity[j], P.op_code[j], P.op_a[j], P.op_b[j] = ar, opc, a, b
+    for (q, (reg, col)) in enumerate([(3, 1), (4, 0)]):
+        P.out_reg[q], P.out_col[q] = reg, col
+    o_pick, o_grad = Dev(np.full((R, 1), np.nan, "f4")), Dev(np.full((R, C), np.nan, "f4"))
+    ins = (ctypes.c_void_p * 8)(dx.ptr, didx.ptr, dg.ptr)
+    outs = (ctypes.c_void_p * 4)(o_pick.ptr, o_grad.ptr)
+    call("cgtb_fused_rows", ctypes.byref(P), R, C, ins, outs)
+    assert np.array_equal(o_pick.get().reshape(R), x.reshape(-1)[flat])
+    assert np.array_equal(o_grad.get(), hot_np * g[:, None])
+
+
 def test_fused_rows_refuses_long_rows(rt):
     P = _RowProgram()
     P.n_in, P.n_ops, P.n_out = 1, 1, 1
