@@ -406,8 +406,9 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
     }
   } else if (warp == kConvWarps) {
     // ------------------------------------------------ MMA issuer
-    // The whole warp runs the loop; per K block one elected lane issues all its MMAs and commits (no election
-    // and no lane-mask operand per instruction: that form issues almost twice as fast). Two instructions per K step:
+    // ONE thread runs the loop: it waits for the stage, issues all MMAs of the K block and commits (no election, no
+    // lane-mask operand per instruction, no warp-wide poll of the barrier and no warp synchronisation per K block:
+    // the issue loop is what bounds these kernels, 45-50 cycles per tcgen05.mma). Two instructions per K step:
     // x_hi * [y_hi | y_lo] into columns [0, 2UN) and x_lo * y_hi into columns [0, UN).
     const uint32_t major_bits = (XMN ? (1u << 15) : 0u) | (YMN ? (1u << 16) : 0u);   // operand A / B is MN-major
     const uint32_t idesc1 = make_idesc_tf32(UN) | major_bits, idesc2 = make_idesc_tf32(2 * UN) | major_bits;
@@ -416,12 +417,13 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
     int tkb = 0;
     (void)tkb;
     uint32_t cphase = 0;
+    if (elect_one())
     for (long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
       const Tile c = tile_of(p, t);
       for (int kb = 0; kb < c.nkb; ++kb) {
         ok = mbar_wait_or_abort(smem_u32(&conv_full[cs]), cphase, abortp);
         if (!ok) break;
-        if (lane == 0) TRACE(tkb, 4);
+        TRACE(tkb, 4);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t sbase = smem_u32(conv0 + (size_t)cs * conv_bytes);
         const uint32_t xh_addr = XDIRECT ? smem_u32(raw0 + (size_t)rs * raw_bytes) : sbase;
@@ -431,28 +433,25 @@ sgemm_tma_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         const uint64_t dxh = XMN ? make_desc_mn(xh_addr, 4096u) : make_desc(xh_addr);
         const uint64_t dxl = XMN ? make_desc_mn(xl_addr, 4096u) : make_desc(xl_addr);
         const uint64_t dyh = YMN ? make_desc_mn(sbase + cx_bytes, 4096u) : make_desc(sbase + cx_bytes);  // y_lo follows y_hi: one descriptor covers both
-        if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < kBK / 8; ++kk) {
-            // K-major: 8 tf32 = 32 bytes along K inside the swizzle row; MN-major: 8 K rows = 1024 bytes
-            const uint64_t advx = (uint64_t)((kk * (XMN ? 1024 : 32)) >> 4), advy = (uint64_t)((kk * (YMN ? 1024 : 32)) >> 4);
-            const uint32_t first = (kb == 0 && kk == 0) ? 0u : 1u;
-            mma_tf32_one(tmem_d, dxh + advx, dyh + advy, idesc2, first);
-            mma_tf32_one(tmem_d, dxl + advx, dyh + advy, idesc1, 1u);
-          }
-          mma_commit(smem_u32(&conv_empty[cs]));
-          if (XDIRECT) mma_commit(smem_u32(&raw_empty[rs]));
+        for (int kk = 0; kk < kBK / 8; ++kk) {
+          // K-major: 8 tf32 = 32 bytes along K inside the swizzle row; MN-major: 8 K rows = 1024 bytes
+          const uint64_t advx = (uint64_t)((kk * (XMN ? 1024 : 32)) >> 4), advy = (uint64_t)((kk * (YMN ? 1024 : 32)) >> 4);
+          const uint32_t first = (kb == 0 && kk == 0) ? 0u : 1u;
+          mma_tf32_one(tmem_d, dxh + advx, dyh + advy, idesc2, first);
+          mma_tf32_one(tmem_d, dxl + advx, dyh + advy, idesc1, 1u);
         }
-        __syncwarp();
-        if (lane == 0) TRACE(tkb, 5);
+        mma_commit(smem_u32(&conv_empty[cs]));
+        if (XDIRECT) mma_commit(smem_u32(&raw_empty[rs]));
+        TRACE(tkb, 5);
         ++tkb;
         if (++rs == RS) rs = 0;
         if (++cs == CS) { cs = 0; cphase ^= 1u; }
       }
-      if (ok && c.nkb > 0 && elect_one()) mma_commit(smem_u32(&accum_bar));
-      __syncwarp();
+      if (ok && c.nkb > 0) mma_commit(smem_u32(&accum_bar));
     }
-    if (!ok && lane == 0) { *abortp = 1; *(volatile int*)p.err = 4; __threadfence_system(); }
+    if (!ok) { *abortp = 1; *(volatile int*)p.err = 4; __threadfence_system(); }
+    __syncwarp();
   } else if (CONV == 2) {
     // ------------------------------------------------ TMA producer of the filter-gradient product (one warp)
     // A K block of this product is five boxes (four shifted windows of the source, one of the gradient), and one
@@ -774,7 +773,7 @@ conv_tsa_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant_
       }
     }
   } else if (warp == kCvtWarps) {
-    // ------------------------------------------------ MMA issuer (whole warp; one elected lane issues per K block)
+    // ------------------------------------------------ MMA issuer (one thread: waits, issues the K block's MMAs, commits)
     const uint32_t idesc1 = make_idesc_tf32(UN), idesc2 = make_idesc_tf32(2 * UN);
     bool ok = true;
     int as = 0;
@@ -782,6 +781,7 @@ conv_tsa_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant_
     (void)tkb;
     uint32_t aphase = 0;
     uint32_t it = 0;
+    if (elect_one())
     for (long t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, ++it) {
       const Tile c = tile_of(p, t);
       // accumulator it % NACC: the epilogue warps must have drained its previous tile
@@ -793,29 +793,26 @@ conv_tsa_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant_
       for (int kb = 0; kb < c.nkb; ++kb) {
         ok = mbar_wait_or_abort(smem_u32(&a_full[as]), aphase, abortp);
         if (!ok) break;
-        if (lane == 0) TRACE(tkb, 4);
+        TRACE(tkb, 4);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a_hi = tmem_d + acol0 + (uint32_t)as * 64u, a_lo = a_hi + 32u;
         const uint64_t dyh = make_desc(smem_u32(w0 + (size_t)as * w_bytes));  // w_lo follows w_hi
-        if (elect_one()) {
 #pragma unroll
-          for (int kk = 0; kk < kBK / 8; ++kk) {
-            const uint64_t adv = (uint64_t)((kk * 32) >> 4);
-            const uint32_t first = (kb == 0 && kk == 0) ? 0u : 1u;
-            mma_tf32_ts_one(tmem_acc, a_hi + (uint32_t)(kk * 8), dyh + adv, idesc2, first);
-            mma_tf32_ts_one(tmem_acc, a_lo + (uint32_t)(kk * 8), dyh + adv, idesc1, 1u);
-          }
-          mma_commit(smem_u32(&a_empty[as]));
+        for (int kk = 0; kk < kBK / 8; ++kk) {
+          const uint64_t adv = (uint64_t)((kk * 32) >> 4);
+          const uint32_t first = (kb == 0 && kk == 0) ? 0u : 1u;
+          mma_tf32_ts_one(tmem_acc, a_hi + (uint32_t)(kk * 8), dyh + adv, idesc2, first);
+          mma_tf32_ts_one(tmem_acc, a_lo + (uint32_t)(kk * 8), dyh + adv, idesc1, 1u);
         }
-        __syncwarp();
-        if (lane == 0) TRACE(tkb, 5);
+        mma_commit(smem_u32(&a_empty[as]));
+        TRACE(tkb, 5);
         ++tkb;
         if (++as == AS) { as = 0; aphase ^= 1u; }
       }
-      if (ok && elect_one()) mma_commit(smem_u32(&accum_full[ab]));
-      __syncwarp();
+      if (ok) mma_commit(smem_u32(&accum_full[ab]));
     }
-    if (!ok && lane == 0) { *abortp = 1; *(volatile int*)p.err = 4; __threadfence_system(); }
+    if (!ok) { *abortp = 1; *(volatile int*)p.err = 4; __threadfence_system(); }
+    __syncwarp();
   } else if (warp == kCvtWarps + 1) {
     if (lane == 0) {
       // ---------------------------------------------- halo producer: the input rows of tile `it` into buffer it % HB

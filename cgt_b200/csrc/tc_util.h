@@ -46,6 +46,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 }
 // bounded wait that also gives up as soon as another role of the CTA has raised `*abort_flag`
 __device__ __forceinline__ bool mbar_wait_or_abort(uint32_t bar, uint32_t parity, const volatile int* abort_flag) {
+  if (mbar_try(bar, parity)) return true;   // the common case in a pipeline that runs ahead: no clock read
   const long long t0 = clock64();
   for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
     if (mbar_try(bar, parity)) return true;
