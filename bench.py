@@ -311,6 +311,7 @@ def timed_blocks(f, batches, steps, warmup, repeats, flush=True, prefetch=False)
             if flush:
                 runtime.l2_flush()
                 runtime.synchronize()
+            parallel.device_barrier()   # N > 1: the ranks' streams start the step together (outside the timed region)
             e0.record()
             if prefetch:
                 f.prefetch(*batches[(it + 1) % nb])
@@ -415,7 +416,9 @@ def run_b200(args):
             "scaling": "weak", "vs_baseline": None, "dtype": "f32 (3xTF32 tensor-core GEMM where used, fp32 elsewhere)",
             "data": "synthetic",
             "config": {"workload": meta["workload"], "global_batch": BATCH * world, "parallelism": "dp%d" % world,
-                       "l2": "flushed between timed steps (256 MiB memset, untimed)", "cuda_graphs": bool(st["segments_captured"]),
+                       "l2": "flushed between timed steps (256 MiB memset, untimed)",
+                       "rank_alignment": ("one-float NCCL all-reduce queued before the start event of every timed step (untimed)"
+                                          if world > 1 else None), "cuda_graphs": bool(st["segments_captured"]),
                        "timing": "median of %d blocks of %d steps; every block between a barrier and a synchronisation, max over ranks" % (R, K),
                        "kernels_per_step": int(st["last_kernel_launches"]), "graph_launches_per_step": int(st["last_graph_launches"])},
             "e2e": {"value": e2e["value"], "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,

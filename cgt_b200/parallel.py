@@ -102,6 +102,23 @@ def barrier():
         dist.barrier()
 
 
+def device_barrier():
+    """Queues, on the runtime's stream, a collective that completes only when every rank's stream has reached the same
+    point (an NCCL all-reduce of one float, outside any captured graph): what follows it on the streams starts on all
+    GPUs within a few microseconds, whatever the skew between the host processes. False (and nothing queued) with one
+    process. Every rank must call it the same number of times."""
+    if not _state["comm"]:
+        return False
+    from . import runtime
+    if _state.get("barrier_word") is None:
+        _state["barrier_word"] = runtime.device_array(np.zeros((1,), "f4"))
+    w = _state["barrier_word"]
+    ptrs = (ctypes.c_void_p * 1)(w.data)
+    runtime.check(runtime.lib().cgtb_allreduce_sum(runtime._dtype_code(np.dtype("f4")), 1, ptrs, ptrs, (ctypes.c_long * 1)(1)),
+                  "cgtb_allreduce_sum")
+    return True
+
+
 def all_max(value):
     """max over ranks of a host float (timing reduction)"""
     if _state["world"] == 1:
