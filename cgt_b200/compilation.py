@@ -1276,6 +1276,52 @@ def fuse_conv_direct(outputs, updatetargs, node2shape):
     return _rewire(outputs, updatetargs, replace)
 
 
+def hoist_filter_splits(outputs, updatetargs, node2shape):
+    """ConvFwdBiasRelu / ConvDgrad on a layer's stored filter bank each start with a small kernel that writes the
+    bank's K-major [w_hi | w_lo] copy. All such copies of the step (at most eight per node) are made by one
+    SplitFilterBanks node instead, and the convolutions take their copy as an extra input: four launches become one in
+    the CIFAR-shape step. Applies to banks of static shape; needs at least two convolutions to pay."""
+    from .nn_ops import im2col as im2col_ops
+    all_out = list(outputs) + list(updatetargs)
+    nodes = core.topsorted(all_out)
+    jobs_nodes = []
+    for node in nodes:
+        if node.is_input() or not isinstance(node.op, (im2col_ops.ConvFwdBiasRelu, im2col_ops.ConvDgrad)):
+            continue
+        if not node.op.w_bank or node.op.pre:
+            continue
+        bank = node.parents[1]
+        shp = _static_shape(node2shape[bank]) if bank in node2shape else None
+        if shp is None or len(shp) != 4 or bank.dtype != "f4":
+            continue
+        taps = shp[2] * shp[3]
+        if isinstance(node.op, im2col_ops.ConvFwdBiasRelu):
+            job = (shp[0], shp[1], taps, 1)        # bank [Cout, Cin, kh, kw]: rows = Cout, source channels = Cin
+        else:
+            job = (shp[1], shp[0], taps, 2)        # the same bank read for the data gradient: rows = Cin, source channels = Cout
+        jobs_nodes.append((node, bank, job))
+    if len(jobs_nodes) < 2:
+        return list(outputs), list(updatetargs)
+    replace = {}
+    const = lambda v: core.cgt.constant(np.array(v, "i8"))
+    for lo in range(0, len(jobs_nodes), im2col_ops.SplitFilterBanks.MAX_JOBS):
+        chunk = jobs_nodes[lo:lo + im2col_ops.SplitFilterBanks.MAX_JOBS]
+        banks = []
+        for (_node, bank, _job) in chunk:
+            if bank not in banks:
+                banks.append(bank)
+        split = core.Result(im2col_ops.SplitFilterBanks([(banks.index(bank),) + job for (_node, bank, job) in chunk]), banks)
+        node2shape[split] = tuple([const(2), const(job[0]), const(job[2] * job[1])] for (_node, _bank, job) in chunk)
+        for (j, (node, _bank, job)) in enumerate(chunk):
+            piece = core.Result(core.TupleIndex(j), [split])
+            node2shape[piece] = [const(2), const(job[0]), const(job[2] * job[1])]
+            new = core.Result(type(node.op)(node.op.info, w_bank=True, pre=True), list(node.parents) + [piece])
+            node2shape[new] = node2shape[node]
+            new.props.update(node.props)
+            replace[node] = new
+    return _rewire(outputs, updatetargs, replace)
+
+
 def pad_conv_columns(outputs, updatetargs, node2shape):
     """Widen the rows of a float32 column matrix whose length Z = C*kh*kw is not a multiple of four (a 3-channel
     5x5 convolution: 75) to the next multiple, so that every row starts on a 16-byte boundary and the products
@@ -1776,6 +1822,8 @@ def apply_graph_rewrites(outputs_simple, updatetargs_simple, node2shape):
             outputs_simple, updatetargs_simple = fuse_conv_direct(outputs_simple, updatetargs_simple, node2shape)
         if config["pad_conv_columns"]:
             outputs_simple, updatetargs_simple = pad_conv_columns(outputs_simple, updatetargs_simple, node2shape)
+    if config["hoist_filter_splits"]:
+        outputs_simple, updatetargs_simple = hoist_filter_splits(outputs_simple, updatetargs_simple, node2shape)
     return outputs_simple, updatetargs_simple
 
 

@@ -939,6 +939,31 @@ __global__ void split_filter_kernel(const float* __restrict__ W, int N, int Cs, 
   }
 }
 
+// The same split for several (bank, layout) jobs in one launch: job = blockIdx.y.
+constexpr int kMaxSplitJobs = 8;
+struct SplitJobs {
+  const float* W[kMaxSplitJobs];
+  float* out[kMaxSplitJobs];
+  int N[kMaxSplitJobs], Cs[kMaxSplitJobs], kk[kMaxSplitJobs], layout[kMaxSplitJobs];
+};
+__global__ void split_filter_banks_kernel(const SplitJobs jobs) {
+  const int j = blockIdx.y;
+  const float* __restrict__ W = jobs.W[j];
+  float* __restrict__ out = jobs.out[j];
+  const int N = jobs.N[j], Cs = jobs.Cs[j], kk = jobs.kk[j], layout = jobs.layout[j];
+  const long K = (long)kk * Cs, n = (long)N * K;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / K);
+    const int k = (int)(i - (long)r * K);
+    const int tap = k / Cs, c = k - tap * Cs;
+    const float w = layout == 1 ? W[((long)r * Cs + c) * kk + tap] : W[((long)c * N + r) * kk + tap];
+    uint32_t h, l;
+    split_tf32(w, h, l);
+    out[i] = __uint_as_float(h);
+    out[n + i] = __uint_as_float(l);
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -1057,7 +1082,8 @@ bool use_tsa() {
 bool split_y(const Side& Y, long K, int UN, float* dst, long Kp, CUtensorMap* mapY, int filter_layout = 0, int Cs = 0, int kk = 0) {
   const long n = Y.rows * Kp;
   const unsigned blocks = (unsigned)std::min<long>(cgtb_ceil_div(n, 256), 8L * rt().sm_count);
-  if (filter_layout) CGTB_LAUNCH(split_filter_kernel, blocks, 256, 0, Y.base, (int)Y.rows, Cs, kk, filter_layout, 1, dst);
+  if (filter_layout < 0) { /* dst already holds [2][rows][Kp] (cgtb_split_filter_banks) */ }
+  else if (filter_layout) CGTB_LAUNCH(split_filter_kernel, blocks, 256, 0, Y.base, (int)Y.rows, Cs, kk, filter_layout, 1, dst);
   else CGTB_LAUNCH(split_rows_kernel, blocks, 256, 0, Y.base, Y.rows, K, Y.ld, Y.mn ? 1 : 0, dst, Kp);
   EncodeTiledFn fn = encoder();
   if (!fn) return false;
@@ -1168,7 +1194,7 @@ int sgemm_tma(int tA, int tB, long P, long M, long N, long K, const float* A, lo
 // is applied to the accumulator (forward product of a layer).
 // returns 0 done, 1 error, -1 not eligible
 int conv_implicit_tma(const float* src, long B, int Hs, int Ws, int Cs, const float* wr, int w_layout, int N, int Hd, int Wd, int kh,
-                      int kw, int ph, int pw, int sign, float* out, const ConvEpilogue* ep) {
+                      int kw, int ph, int pw, int sign, float* out, const ConvEpilogue* ep, const float* presplit) {
   if (B <= 0 || N <= 0 || Hd <= 0 || Wd <= 0) return 0;
   if (Cs % 32 != 0 || N % 16 != 0 || Wd > 128 || B >= (1L << 30) || kh <= 0 || kw <= 0) return -1;
   if (((uintptr_t)src & 15) != 0 || ((uintptr_t)wr & 15) != 0) return -1;
@@ -1298,7 +1324,9 @@ int conv_implicit_tma(const float* src, long B, int Hs, int Ws, int Cs, const fl
   p.total_tiles = tiles * ytiles * nsplit;
   const long total = B * (long)N * HW;
   // the pre-split filters (or, for the kernel that converts in its loop, the rearranged copy of a filter bank)
-  const size_t split_bytes = tsa ? ((((size_t)2 * N * K * sizeof(float)) + 255) & ~(size_t)255)
+  if (presplit && (((uintptr_t)presplit & 15) != 0)) presplit = nullptr;
+  // `presplit`: [w_hi | w_lo] of these filters in the kernel's layout, made earlier in the step (cgtb_split_filter_banks)
+  const size_t split_bytes = tsa ? (presplit ? 0 : ((((size_t)2 * N * K * sizeof(float)) + 255) & ~(size_t)255))
                                  : (w_layout ? ((((size_t)N * K * sizeof(float)) + 255) & ~(size_t)255) : 0);
   const size_t slab_bytes = nsplit > 1 ? (size_t)nsplit * total * sizeof(float) : 0;
   char* blk = nullptr;
@@ -1320,7 +1348,9 @@ int conv_implicit_tma(const float* src, long B, int Hs, int Ws, int Cs, const fl
   }
   Side Y = {wr, K, false, N, 0};
   if (tsa) {
-    if (!split_y(Y, K, UN, (float*)blk, K, &mapY, w_layout, Cs, kh * kw)) return -1;
+    if (presplit ? !split_y(Y, K, UN, const_cast<float*>(presplit), K, &mapY, -1)
+                 : !split_y(Y, K, UN, (float*)blk, K, &mapY, w_layout, Cs, kh * kw))
+      return -1;
     static bool cfg = false;
     if (!cfg) {
       CGTB_CUDA_TRY(cudaFuncSetAttribute(conv_tsa_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 2048));
@@ -1445,10 +1475,10 @@ int conv_wgrad_tma(const float* src, long B, int Hs, int Ws, int Cs, const float
 }  // namespace cgtb
 
 static int conv_dgrad_any(const float* dy_nhwc, long B, int Ho, int Wo, int Cin, const float* w, int layout, int C, int H, int W, int kh,
-                          int kw, int ph, int pw, float* dx_nchw) {
+                          int kw, int ph, int pw, float* dx_nchw, const float* presplit = nullptr) {
   if (!require_runtime("cgtb_conv_dgrad")) return 1;
   if (C > 128) return fail("cgtb_conv_dgrad: at most 128 image channels");
-  int rc = cgtb::conv_implicit_tma(dy_nhwc, B, Ho, Wo, Cin, w, layout, C, H, W, kh, kw, ph, pw, -1, dx_nchw, nullptr);
+  int rc = cgtb::conv_implicit_tma(dy_nhwc, B, Ho, Wo, Cin, w, layout, C, H, W, kh, kw, ph, pw, -1, dx_nchw, nullptr, presplit);
   if (rc < 0)
     return fail("cgtb_conv_dgrad: not supported for Cin=%d (multiple of 32), C=%d (multiple of 16, at most 128), W=%d (at most 128) "
                 "or an unaligned operand; use cgtb_sgemm + cgtb_col2im", Cin, C, W);
@@ -1464,13 +1494,13 @@ CGTB_API int cgtb_conv_dgrad_bank(const float* dy_nhwc, long B, int Ho, int Wo, 
 }
 
 static int conv_fwd_any(const float* x_nhwc, long B, int H, int W, int Cin, const float* w, int layout, int Cout, int Ho, int Wo, int kh,
-                        int kw, int ph, int pw, const float* bias, float* y_nchw, int8_t* mask_nchw) {
+                        int kw, int ph, int pw, const float* bias, float* y_nchw, int8_t* mask_nchw, const float* presplit = nullptr) {
   if (!require_runtime("cgtb_conv_fwd_bias_relu")) return 1;
   if (Ho != H + 2 * ph - kh + 1 || Wo != W + 2 * pw - kw + 1)
     return fail("cgtb_conv_fwd_bias_relu: output %dx%d is not that of a stride-1 %dx%d convolution of %dx%d with padding %d,%d", Ho, Wo,
                 kh, kw, H, W, ph, pw);
   cgtb::ConvEpilogue ep = {bias, y_nchw, mask_nchw, (long)Ho * Wo};
-  int rc = cgtb::conv_implicit_tma(x_nhwc, B, H, W, Cin, w, layout, Cout, Ho, Wo, kh, kw, ph, pw, +1, nullptr, &ep);
+  int rc = cgtb::conv_implicit_tma(x_nhwc, B, H, W, Cin, w, layout, Cout, Ho, Wo, kh, kw, ph, pw, +1, nullptr, &ep, presplit);
   if (rc < 0)
     return fail("cgtb_conv_fwd_bias_relu: not supported for Cin=%d (multiple of 32), Cout=%d (multiple of 16; of 128 when above 128), "
                 "Wo=%d (at most 128) or an unaligned operand; use cgtb_im2col + cgtb_conv_bias_relu", Cin, Cout, Wo);
@@ -1483,6 +1513,39 @@ CGTB_API int cgtb_conv_fwd_bias_relu(const float* x_nhwc, long B, int H, int W, 
 CGTB_API int cgtb_conv_fwd_bias_relu_bank(const float* x_nhwc, long B, int H, int W, int Cin, const float* w_bank, int Cout, int Ho,
                                           int Wo, int kh, int kw, int ph, int pw, const float* bias, float* y_nchw, int8_t* mask_nchw) {
   return conv_fwd_any(x_nhwc, B, H, W, Cin, w_bank, 1, Cout, Ho, Wo, kh, kw, ph, pw, bias, y_nchw, mask_nchw);
+}
+
+CGTB_API int cgtb_conv_fwd_bias_relu_pre(const float* x_nhwc, long B, int H, int W, int Cin, const float* w_bank, const float* w_split,
+                                         int Cout, int Ho, int Wo, int kh, int kw, int ph, int pw, const float* bias, float* y_nchw,
+                                         int8_t* mask_nchw) {
+  return conv_fwd_any(x_nhwc, B, H, W, Cin, w_bank, 1, Cout, Ho, Wo, kh, kw, ph, pw, bias, y_nchw, mask_nchw, w_split);
+}
+CGTB_API int cgtb_conv_dgrad_pre(const float* dy_nhwc, long B, int Ho, int Wo, int Cin, const float* w_bank, const float* w_split, int C,
+                                 int H, int W, int kh, int kw, int ph, int pw, float* dx_nchw) {
+  return conv_dgrad_any(dy_nhwc, B, Ho, Wo, Cin, w_bank, 2, C, H, W, kh, kw, ph, pw, dx_nchw, w_split);
+}
+CGTB_API int cgtb_split_filter_banks(int njobs, const float* const* banks, const int* n_out, const int* n_src, const int* taps,
+                                     const int* layout, float* const* out) {
+  if (!require_runtime("cgtb_split_filter_banks")) return 1;
+  if (njobs < 1 || njobs > kMaxSplitJobs) return fail("cgtb_split_filter_banks: between 1 and %d jobs", kMaxSplitJobs);
+  SplitJobs jobs;
+  memset(&jobs, 0, sizeof(jobs));
+  long most = 0;
+  for (int j = 0; j < njobs; ++j) {
+    if (!banks[j] || !out[j] || n_out[j] < 1 || n_src[j] < 1 || taps[j] < 1 || (layout[j] != 1 && layout[j] != 2))
+      return fail("cgtb_split_filter_banks: job %d: null pointer, empty extent or a layout other than 1 (forward) / 2 (data gradient)", j);
+    jobs.W[j] = banks[j];
+    jobs.out[j] = out[j];
+    jobs.N[j] = n_out[j];
+    jobs.Cs[j] = n_src[j];
+    jobs.kk[j] = taps[j];
+    jobs.layout[j] = layout[j];
+    most = std::max<long>(most, (long)n_out[j] * n_src[j] * taps[j]);
+  }
+  const unsigned bx = (unsigned)std::min<long>(cgtb_ceil_div(most, 256), 2L * rt().sm_count);
+  CGTB_LAUNCH(split_filter_banks_kernel, dim3(bx, (unsigned)njobs), 256, 0, jobs);
+  CGTB_CHECK_LAUNCH("split_filter_banks");
+  return 0;
 }
 
 CGTB_API int cgtb_conv_wgrad(const float* x_nhwc, long B, int H, int W, int Cin, const float* dy_nhwc, int Ho, int Wo, int Cout, int kh,

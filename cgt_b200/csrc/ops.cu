@@ -344,7 +344,7 @@ OP_BYREF(cgtb_op_batched_mul22) {
 // ------------------------------------------------------------------------------------------------
 struct ConvClosure { int kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w; };
 // the same followed by a flag: the filter operand is the layer's bank in its own layout, not a rearranged copy
-struct ConvClosureW { int kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w, w_bank; };
+struct ConvClosureW { int kernel_h, kernel_w, pad_h, pad_w, stride_h, stride_w, w_bank, pre; };   // pre: the last read is the bank's [w_hi | w_lo] copy
 OP_BYREF(cgtb_op_im2col) {
   ConvClosure* cl = (ConvClosure*)cl0;
   cgtArray *im = ARR(reads[0]), *col = ARR(write0);
@@ -473,6 +473,13 @@ OP_BYREF(cgtb_op_conv_dgrad) {
     fail("ConvDgrad: operand shapes do not fit together");
     return;
   }
+  if (cl->pre) {
+    cgtArray* sp = ARR(reads[6]);
+    if (!cl->w_bank || !on_gpu(sp) || sp->dtype() != cgt_f4 || sp->size() != 2 * wr->size()) { fail("ConvDgrad: the split filter copy does not fit the bank"); return; }
+    cgtb_conv_dgrad_pre((const float*)dy->data(), s[0], (int)s[1], (int)s[2], (int)s[3], (const float*)wr->data(), (const float*)sp->data(), (int)d[1],
+                        (int)d[2], (int)d[3], cl->kernel_h, cl->kernel_w, cl->pad_h, cl->pad_w, (float*)dx->data());
+    return;
+  }
   (cl->w_bank ? cgtb_conv_dgrad_bank : cgtb_conv_dgrad)((const float*)dy->data(), s[0], (int)s[1], (int)s[2], (int)s[3], (const float*)wr->data(), (int)d[1], (int)d[2],
                   (int)d[3], cl->kernel_h, cl->kernel_w, cl->pad_h, cl->pad_w, (float*)dx->data());
 }
@@ -494,9 +501,37 @@ OP_BYREF(cgtb_op_conv_fwd_bias_relu) {
     fail("ConvFwdBiasRelu: operand shapes do not fit together");
     return;
   }
+  if (cl->pre) {
+    cgtArray* sp = ARR(reads[7]);
+    if (!cl->w_bank || !on_gpu(sp) || sp->dtype() != cgt_f4 || sp->size() != 2 * wr->size()) { fail("ConvFwdBiasRelu: the split filter copy does not fit the bank"); return; }
+    cgtb_conv_fwd_bias_relu_pre((const float*)x->data(), s[0], (int)s[1], (int)s[2], (int)s[3], (const float*)wr->data(), (const float*)sp->data(),
+                                (int)d[1], (int)d[2], (int)d[3], cl->kernel_h, cl->kernel_w, cl->pad_h, cl->pad_w, (const float*)bias->data(),
+                                (float*)y->data(), (int8_t*)mask->data());
+    return;
+  }
   (cl->w_bank ? cgtb_conv_fwd_bias_relu_bank : cgtb_conv_fwd_bias_relu)((const float*)x->data(), s[0], (int)s[1], (int)s[2], (int)s[3], (const float*)wr->data(), (int)d[1],
                           (int)d[2], (int)d[3], cl->kernel_h, cl->kernel_w, cl->pad_h, cl->pad_w, (const float*)bias->data(),
                           (float*)y->data(), (int8_t*)mask->data());
+}
+// SplitFilterBanks: (banks...) -> tuple of [2, n_out, taps * n_src] copies, job j from read src[j]; one launch for all
+struct SplitBanksClosure { int njobs; int src[8]; int n_out[8]; int n_src[8]; int taps[8]; int layout[8]; };
+OP_BYREF(cgtb_op_split_filter_banks) {
+  const SplitBanksClosure* cl = (const SplitBanksClosure*)cl0;
+  if (cl->njobs < 1 || cl->njobs > 8) { fail("SplitFilterBanks: between 1 and 8 jobs"); return; }
+  cgtTuple* out = (cgtTuple*)write0;
+  const float* banks[8];
+  float* outs[8];
+  for (int j = 0; j < cl->njobs; ++j) {
+    cgtArray *w = ARR(reads[cl->src[j]]), *o = ARR(out->getitem(j));
+    const long n = (long)cl->n_out[j] * cl->n_src[j] * cl->taps[j];
+    if (!on_gpu(w) || !on_gpu(o) || w->dtype() != cgt_f4 || o->dtype() != cgt_f4 || w->size() != n || o->size() != 2 * n) {
+      fail("SplitFilterBanks: job %d: a float32 GPU bank of %ld elements and a float32 GPU result of twice as many", j, n);
+      return;
+    }
+    banks[j] = (const float*)w->data();
+    outs[j] = (float*)o->data();
+  }
+  cgtb_split_filter_banks(cl->njobs, banks, cl->n_out, cl->n_src, cl->taps, cl->layout, outs);
 }
 // ConvWgradImplicit: (x NHWC [B,H,W,Cin], dy NHWC [B,Ho,Wo,Cout]) -> filter gradient [Cout, Cin*kh*kw]
 OP_BYREF(cgtb_op_conv_wgrad_implicit) {

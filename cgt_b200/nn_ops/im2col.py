@@ -4,6 +4,8 @@ Column layout is channels-last, ``[B, Ho, Wo, C*kh*kw]`` with column channel ``(
 so ``Mul22(F,T)(col.reshape(B*Ho*Wo, Z), W.reshape(L, Z))`` is the cross-correlation.
 """
 import ctypes
+
+import numpy as np
 from collections import namedtuple
 
 from .. import core
@@ -99,26 +101,28 @@ class ConvDgrad(core.Op):
     the extents allow; the column matrix is then neither written nor read."""
     available_impls = ("native_gpu",)
 
-    def __init__(self, info, w_bank=False):
+    def __init__(self, info, w_bank=False, pre=False):
         assert info.stride_h == 1 and info.stride_w == 1
         self.info = info
         self.w_bank = bool(w_bank)
+        self.pre = bool(pre)    # a seventh input: the bank's [w_hi | w_lo] copy from SplitFilterBanks
 
     def get_diff(self, n):
         return [False] * n
 
     def shp_apply(self, inputs):
-        return list(inputs[2:])
+        return list(inputs[2:6])
 
     def typ_apply(self, inputs):
         return core.TensorType("f4", 4)
 
     def host_inputs(self, n):
-        return tuple(range(2, n))
+        return (2, 3, 4, 5)
 
     def get_native_compile_info(self, input_types, devtype):
         return core.NativeCompileInfo(None, prebuilt="cgtb_op_conv_dgrad",
-                                      closure_triples=info2closure(self.info) + [("w_bank", ctypes.c_int, int(self.w_bank))])
+                                      closure_triples=info2closure(self.info) + [("w_bank", ctypes.c_int, int(self.w_bank)),
+                                                                                ("pre", ctypes.c_int, int(self.pre))])
 
     def __repr__(self):
         return "ConvDgrad{%s}" % (tuple(self.info),)
@@ -313,30 +317,68 @@ class ConvFwdBiasRelu(core.Op):
     tolerance against the Op sequence."""
     available_impls = ("native_gpu",)
 
-    def __init__(self, info, w_bank=False):
+    def __init__(self, info, w_bank=False, pre=False):
         assert info.stride_h == 1 and info.stride_w == 1
         self.info = info
         self.w_bank = bool(w_bank)
+        self.pre = bool(pre)    # an eighth input: the bank's [w_hi | w_lo] copy from SplitFilterBanks
 
     def get_diff(self, n):
         return [False] * n
 
     def shp_apply(self, inputs):
-        shp = list(inputs[3:])
+        shp = list(inputs[3:7])
         return (shp, list(shp))
 
     def typ_apply(self, inputs):
         return core.TupleType(core.TensorType("i1", 4), core.TensorType("f4", 4))
 
     def host_inputs(self, n):
-        return tuple(range(3, n))
+        return (3, 4, 5, 6)
 
     def get_native_compile_info(self, input_types, devtype):
         return core.NativeCompileInfo(None, prebuilt="cgtb_op_conv_fwd_bias_relu",
-                                      closure_triples=info2closure(self.info) + [("w_bank", ctypes.c_int, int(self.w_bank))])
+                                      closure_triples=info2closure(self.info) + [("w_bank", ctypes.c_int, int(self.w_bank)),
+                                                                                ("pre", ctypes.c_int, int(self.pre))])
 
     def __repr__(self):
         return "ConvFwdBiasRelu{%s}" % (tuple(self.info),)
+
+
+class SplitFilterBanks(core.Op):
+    """(filter banks...) -> tuple of float32 [2, n_out, taps * n_src] arrays, one per job: the K-major [w_hi | w_lo] copy
+    that ConvFwdBiasRelu (layout 1) or ConvDgrad (layout 2) of a layer needs of its bank, all made by ONE launch.
+    jobs: (input index, n_out, n_src, taps, layout). The convolution calls otherwise make that copy themselves, one
+    small launch each; the banks change only with the parameter update, so the compiler
+    (compilation.hoist_filter_splits) makes all copies of a step here, ahead of its first convolution. Same bits."""
+    available_impls = ("native_gpu",)
+    MAX_JOBS = 8
+
+    def __init__(self, jobs):
+        assert 1 <= len(jobs) <= self.MAX_JOBS
+        self.jobs = [tuple(int(v) for v in job) for job in jobs]
+
+    def get_diff(self, n):
+        return [False] * n
+
+    def shp_apply(self, inputs):
+        c = lambda v: core.cgt.constant(np.array(v, "i8"))
+        return tuple([c(2), c(n_out), c(taps * n_src)] for (_src, n_out, n_src, taps, _layout) in self.jobs)
+
+    def typ_apply(self, inputs):
+        return core.TupleType(*[core.TensorType("f4", 3) for _ in self.jobs])
+
+    def get_native_compile_info(self, input_types, devtype):
+        def arr(k):
+            vals = [job[k] for job in self.jobs] + [0] * (self.MAX_JOBS - len(self.jobs))
+            return (ctypes.c_int * self.MAX_JOBS)(*vals)
+        return core.NativeCompileInfo(None, prebuilt="cgtb_op_split_filter_banks", closure_triples=[
+            ("njobs", ctypes.c_int, len(self.jobs)), ("src", ctypes.c_int * self.MAX_JOBS, arr(0)),
+            ("n_out", ctypes.c_int * self.MAX_JOBS, arr(1)), ("n_src", ctypes.c_int * self.MAX_JOBS, arr(2)),
+            ("taps", ctypes.c_int * self.MAX_JOBS, arr(3)), ("layout", ctypes.c_int * self.MAX_JOBS, arr(4))])
+
+    def __repr__(self):
+        return "SplitFilterBanks{%d}" % len(self.jobs)
 
 
 class ConvWgradImplicit(core.Op):

@@ -90,6 +90,9 @@ def _declare(lib):
         "cgtb_conv_wgrad": (ci, [vp, cl, ci, ci, ci, vp] + [ci] * 7 + [vp]),
         "cgtb_conv_dgrad_bank": (ci, [vp, cl, ci, ci, ci, vp] + [ci] * 7 + [vp]),
         "cgtb_conv_fwd_bias_relu_bank": (ci, [vp, cl, ci, ci, ci, vp] + [ci] * 7 + [vp, vp, vp]),
+        "cgtb_conv_fwd_bias_relu_pre": (ci, [vp, cl, ci, ci, ci, vp, vp] + [ci] * 7 + [vp, vp, vp]),
+        "cgtb_conv_dgrad_pre": (ci, [vp, cl, ci, ci, ci, vp, vp] + [ci] * 7 + [vp]),
+        "cgtb_split_filter_banks": (ci, [ci, ctypes.POINTER(vp), c_int_p, c_int_p, c_int_p, c_int_p, ctypes.POINTER(vp)]),
         "cgtb_conv_bias_relu": (ci, [vp, cl, cl, vp, ci, vp, cl, vp, vp]),
         "cgtb_conv_bias_relu_ld": (ci, [vp, cl, cl, cl, vp, ci, vp, cl, vp, vp]),
         "cgtb_relu_grad_nhwc": (ci, [vp, vp, cl, ci, cl, vp, vp]),

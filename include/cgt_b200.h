@@ -212,6 +212,21 @@ int cgtb_conv_wgrad(const float* x_nhwc, long B, int H, int W, int Cin, const fl
 int cgtb_conv_dgrad_bank(const float* dy_nhwc, long B, int Ho, int Wo, int Cin, const float* w_bank, int C, int H, int W,
                          int kh, int kw, int ph, int pw, float* dx_nchw);
 
+/* The filter splitting of the two calls above as a step of its own, for all layers at once. The convolution kernels
+ * take their filters as K-major [w_hi | w_lo] (3xTF32 operands; K runs over (tap, source channel)); cgtb_conv_fwd_bias_relu_bank and
+ * cgtb_conv_dgrad_bank make that copy in a small kernel of their own on every call. The filters change only when the
+ * parameters are updated, so a training step can make all copies in ONE launch before its first convolution:
+ * job j reads banks[j] ([n_out, n_src, taps] for layout 1, the forward product; [n_src, n_out, taps] for layout 2, the
+ * data gradient) and writes out[j], float32 [2][n_out][taps * n_src], 16-byte aligned. At most 8 jobs.
+ * cgtb_conv_fwd_bias_relu_pre / cgtb_conv_dgrad_pre are the two calls with such a copy passed in (w_split; the bank is
+ * still passed and is used when the extents send the call to the kernel that converts in its loop). Same bits. */
+int cgtb_split_filter_banks(int njobs, const float* const* banks, const int* n_out, const int* n_src, const int* taps,
+                            const int* layout, float* const* out);
+int cgtb_conv_fwd_bias_relu_pre(const float* x_nhwc, long B, int H, int W, int Cin, const float* w_bank, const float* w_split, int Cout,
+                                int Ho, int Wo, int kh, int kw, int ph, int pw, const float* bias, float* y_nchw, int8_t* mask_nchw);
+int cgtb_conv_dgrad_pre(const float* dy_nhwc, long B, int Ho, int Wo, int Cin, const float* w_bank, const float* w_split, int C, int H,
+                        int W, int kh, int kw, int ph, int pw, float* dx_nchw);
+
 /* Output stage of a convolution layer in one call: Mul22(col, w^T) -> NCHW -> + bias -> relu with its mask.
  * Replaces the Op sequence Mul22, Reshape, Transpose{0,3,1,2}, Repeat, ElwiseBinary +, >=, * of cgt/nn.py:87-100,
  * 44-45, 228-233; values are bit-identical to that sequence run through cgtb_sgemm and the elementwise kernels.

@@ -199,6 +199,29 @@ def test_flat_index_rows_substitution(rt, name, generated):
         np.testing.assert_allclose(a, b, rtol=1e-3, atol=1e-5 * max(1.0, float(np.abs(a).max())))
 
 
+@pytest.mark.parametrize("name", ["cifar", "wide"])
+def test_filter_splits_hoisted_change_no_bit(rt, name):
+    """The [w_hi | w_lo] copies of all filter banks made by one SplitFilterBanks launch at the head of the step instead of
+    one small kernel inside every convolution call: the same copies, so losses and parameters are identical; fewer
+    kernels per step."""
+    res = {}
+    for on in (False, True):
+        with cgt.scoped_update_config(hoist_filter_splits=on, use_cuda_graphs=False):
+            cfg = configs.BUILDERS[name](**SMALL[name])
+            f = cfg.compile()
+            reprs = [repr(i) for i in f.eg.instrs]
+            batches = [cfg.batch(seed) for seed in range(2)]
+            losses = [np.asarray(f(*batches[i % 2])[0]).copy() for i in range(5)]
+            res[on] = (reprs, losses, [np.asarray(p.op.get_value()).copy() for p in cfg.params], f.stats()["last_kernel_launches"])
+    n_split = sum("op:SplitFilterBanks" in r for r in res[True][0])
+    assert n_split == 1 and not any("SplitFilterBanks" in r for r in res[False][0])
+    assert res[True][3] < res[False][3]
+    for (a, b) in zip(res[False][1], res[True][1]):
+        assert np.array_equal(a, b)
+    for (a, b) in zip(res[False][2], res[True][2]):
+        assert np.array_equal(a, b)
+
+
 def test_conv_direct_substitution(rt):
     """The compiler computes the 3-channel first layer of the CIFAR-shape convnet directly from the image (no column
     matrix): losses and parameters stay within the float32 tolerance of the column-matrix graph."""

@@ -526,6 +526,49 @@ def test_conv_fwd_bias_relu_matches_im2col_then_gemm(rt, B, Cin, H, W, Cout, k, 
     assert (got[~on] == 0).all()
 
 
+@pytest.mark.parametrize("B,Cin,H,W,Cout,k,pad", [(8, 32, 15, 15, 32, 5, 2), (128, 32, 6, 6, 64, 5, 2), (6, 96, 6, 6, 256, 5, 2),
+                                                  (3, 32, 20, 9, 16, 3, 1)])
+def test_conv_with_filters_split_ahead(rt, B, Cin, H, W, Cout, k, pad):
+    """cgtb_split_filter_banks makes the [w_hi | w_lo] copies of a layer's bank for the forward product and for the data
+    gradient in one launch; cgtb_conv_fwd_bias_relu_pre / cgtb_conv_dgrad_pre given those copies return the bits of
+    cgtb_conv_fwd_bias_relu_bank / cgtb_conv_dgrad_bank, which split on every call."""
+    rs = np.random.RandomState(46)
+    Ho, Wo = H + 2 * pad - k + 1, W + 2 * pad - k + 1
+    xn = rs.randn(B, H, W, Cin).astype("f4")
+    Wf = (rs.randn(Cout, Cin, k, k) / np.sqrt(Cin * k * k)).astype("f4")
+    bias = (0.1 * rs.randn(Cout)).astype("f4")
+    dyn = rs.randn(B, Ho, Wo, Cout).astype("f4")
+    dx, dw, db, ddy = Dev(xn), Dev(Wf), Dev(bias), Dev(dyn)
+    s_fwd, s_dg = Dev(np.full((2, Cout, k * k * Cin), np.nan, "f4")), Dev(np.full((2, Cin, k * k * Cout), np.nan, "f4"))
+    banks = (ctypes.c_void_p * 2)(dw.ptr, dw.ptr)
+    outs = (ctypes.c_void_p * 2)(s_fwd.ptr, s_dg.ptr)
+    call("cgtb_split_filter_banks", 2, banks, ints((Cout, Cin)), ints((Cin, Cout)), ints((k * k, k * k)), ints((1, 2)), outs)
+    hi, lo = s_fwd.get()
+    want = Wf.transpose(0, 2, 3, 1).reshape(Cout, -1)      # K runs over (tap, input channel)
+    assert np.abs(hi + lo - want).max() <= 2.0 ** -21 * np.abs(want).max()
+    assert ((hi.view("u4") & 0x1FFF) == 0).all() and ((lo.view("u4") & 0x1FFF) == 0).all()
+    y0, m0 = Dev(np.full((B, Cout, Ho * Wo), np.nan, "f4")), Dev(np.full((B, Cout, Ho * Wo), 7, "i1"))
+    y1, m1 = Dev(np.full((B, Cout, Ho * Wo), np.nan, "f4")), Dev(np.full((B, Cout, Ho * Wo), 7, "i1"))
+    call("cgtb_conv_fwd_bias_relu_bank", dx.ptr, B, H, W, Cin, dw.ptr, Cout, Ho, Wo, k, k, pad, pad, db.ptr, y0.ptr, m0.ptr)
+    k0 = runtime.kernel_launches()
+    call("cgtb_conv_fwd_bias_relu_pre", dx.ptr, B, H, W, Cin, dw.ptr, s_fwd.ptr, Cout, Ho, Wo, k, k, pad, pad, db.ptr, y1.ptr, m1.ptr)
+    n_pre = runtime.kernel_launches() - k0
+    assert np.array_equal(y0.get(), y1.get()) and np.array_equal(m0.get(), m1.get())
+    if Cin <= 128 and Cout % 32 == 0:      # data gradient: at most 128 image channels, gradient channels in groups of 32
+        g0, g1 = Dev(np.full((B, Cin, H * W), np.nan, "f4")), Dev(np.full((B, Cin, H * W), np.nan, "f4"))
+        k0 = runtime.kernel_launches()
+        call("cgtb_conv_dgrad_bank", ddy.ptr, B, Ho, Wo, Cout, dw.ptr, Cin, H, W, k, k, pad, pad, g0.ptr)
+        n_bank = runtime.kernel_launches() - k0
+        k0 = runtime.kernel_launches()
+        call("cgtb_conv_dgrad_pre", ddy.ptr, B, Ho, Wo, Cout, dw.ptr, s_dg.ptr, Cin, H, W, k, k, pad, pad, g1.ptr)
+        assert runtime.kernel_launches() - k0 == n_bank - 1
+        assert np.array_equal(g0.get(), g1.get())
+    assert n_pre == 1
+    # more than eight jobs, or a layout that is neither, are refused
+    rc = runtime.lib().cgtb_split_filter_banks(2, banks, ints((Cout, Cin)), ints((Cin, Cout)), ints((k * k, k * k)), ints((1, 3)), outs)
+    assert rc != 0 and "layout" in runtime.last_error()
+
+
 @pytest.mark.parametrize("B,Cin,H,W,Cout,k,pad", CONV_IMPLICIT + [(2, 32, 9, 32, 16, 3, 1), (3, 32, 5, 17, 32, 3, 1)])
 def test_conv_wgrad_matches_gemm_on_im2col(rt, B, Cin, H, W, Cout, k, pad):
     """cgtb_conv_wgrad against the product it replaces, evaluated by the CPU oracle: Mul22{T,N}(dy, Im2Col(x))."""
