@@ -477,6 +477,194 @@ def fuse_slice_sums(outputs, updatetargs, node2shape):
     return _rewire(outputs, updatetargs, replace)
 
 
+def split_gate_columns(outputs, updatetargs, node2shape):
+    """Elementwise arithmetic on column blocks of one matrix, written per block.
+
+    A recurrent cell computes its gates on slabs of a [R, 4H] matrix: sigmoid on columns [0, 3H), slices of the result
+    per gate; the gradient arrives as ScatterCols of the gates' gradients, multiplied as a slab by the slab's
+    derivative and placed again into [R, 4H]. The arithmetic is elementwise, so it can be done per gate on [R, H]
+    blocks, which lets one fused chain hold a whole cell (all its nodes then have one shape) instead of one chain per
+    slab shape. Three local rewrites, repeated until nothing changes; the values do not change by a bit:
+      * f(ScatterCols(p_1..p_k), y) for an elementwise binary f whose first or second operand is a ScatterCols that
+        covers all columns and has no other reader -> ScatterCols(f(p_1, y[:, cols_1]), ..., f(p_k, y[:, cols_k]));
+      * a ScatterCols piece that is itself such a ScatterCols -> its pieces at shifted offsets (one placement);
+      * x[:, a:b] of an elementwise unary node, or of a binary node with a scalar operand, all of whose readers are
+        column slices -> the same operation on (operand)[:, a:b]; slices of slices are composed;
+      * a Reshape to the shape its operand already has -> the operand.
+    A slice of anything else stays a GetSli, which the fused chains read in place."""
+    const = lambda v: core.cgt.constant(np.array(v, "i8"))
+
+    def const_int(node):
+        if not isinstance(getattr(node, "op", None), core.Constant):
+            return None
+        v = np.asarray(node.op.value)
+        return int(v.reshape(-1)[0]) if v.size == 1 else None
+
+    def shape2(node):
+        shp = _static_shape(node2shape[node]) if node in node2shape else None
+        return shp if shp is not None and len(shp) == 2 else None
+
+    def ident(q):
+        """q without reshapes that change nothing"""
+        while not q.is_input() and isinstance(q.op, core.Reshape) and shape2(q) is not None and shape2(q) == shape2(q.parents[0]):
+            q = q.parents[0]
+        return q
+
+    def col_slice(n):
+        """(x, a, b) when n = x[:, a:b] with constant bounds on a static float32 matrix"""
+        if n.is_input() or not isinstance(n.op, core.GetSli) or n.op.axis != 1 or n.dtype != "f4":
+            return None
+        (x, start, stop, step) = n.parents
+        (a, b, st) = (const_int(start), const_int(stop), const_int(step))
+        xs = shape2(x)
+        if xs is None or a is None or b is None or st != 1 or not (0 <= a < b <= xs[1]) or shape2(n) != (xs[0], b - a):
+            return None
+        return (x, a, b)
+
+    def full_cover(sc):
+        spans = sorted((o, o + w) for (o, w) in zip(sc.op.offsets, sc.op.widths))
+        return spans[0][0] == 0 and spans[-1][1] == sc.op.C and all(b0 == a1 for ((_a0, b0), (a1, _b1)) in zip(spans[:-1], spans[1:]))
+
+    def pushable(e):
+        """an elementwise node through which a column slice may be moved to its operand"""
+        if e.is_input() or e.dtype != "f4" or shape2(e) is None or not _fusable(e):
+            return False
+        if isinstance(e.op, core.ElwiseUnary):
+            return True
+        return isinstance(e.op, core.ElwiseBinary) and sum(e.op.scalar_mask) == 1
+
+    cache = {}
+
+    def sliced(node, a, b):
+        """a node with the value of node[:, a:b]"""
+        node = ident(node)
+        shp = shape2(node)
+        if a == 0 and b == shp[1]:
+            return node
+        key = (node, a, b)
+        if key in cache:
+            return cache[key]
+        cs = col_slice(node)
+        if cs is not None:
+            new = sliced(cs[0], cs[1] + a, cs[1] + b)
+        elif pushable(node):
+            pars = [par if par.ndim == 0 else sliced(par, a, b) for par in node.parents]
+            new = core.Result(node.op, pars)
+            node2shape[new] = [const(shp[0]), const(b - a)]
+        elif not node.is_input() and isinstance(node.op, core.ScatterCols) and (a, b - a) in list(zip(node.op.offsets, node.op.widths)):
+            new = ident(node.parents[list(zip(node.op.offsets, node.op.widths)).index((a, b - a))])
+        else:
+            new = core.Result(core.GetSli(1), [node, const(a), const(b), const(1)])
+            node2shape[new] = [const(shp[0]), const(b - a)]
+        cache[key] = new
+        return new
+
+    for _round in range(8):
+        all_out = list(outputs) + list(updatetargs)
+        nodes = core.topsorted(all_out)
+        children = defaultdict(list)
+        for node in nodes:
+            for par in node.parents:
+                children[par].append(node)
+        out_set = set(all_out)
+
+        def sole_reader(q, reader):
+            """q (below identity reshapes of `reader`'s operand) is read by nothing else"""
+            while True:
+                if q in out_set or len(children[q]) != 1:
+                    return False
+                c = children[q][0]
+                if c is reader:
+                    return True
+                if not (isinstance(c.op, core.Reshape) and shape2(c) is not None and shape2(c) == shape2(q)):
+                    return False
+                q = c
+
+        replace = {}
+        for node in nodes:
+            if node.is_input() or node in out_set or node.dtype != "f4" or shape2(node) is None:
+                continue
+            op = node.op
+            # a reshape that changes nothing stands between two elementwise nodes that one chain could hold
+            if isinstance(op, core.Reshape):
+                if ident(node) is not node:
+                    replace[node] = ident(node)
+                continue
+            # elementwise binary on a placed matrix -> placed results of the per-piece operation
+            if isinstance(op, core.ElwiseBinary) and op.scalar_mask == (False, False) and _fusable(node) and node.parents[0] is not node.parents[1]:
+                done = False
+                for pos in (0, 1):
+                    sc = ident(node.parents[pos])
+                    other = node.parents[1 - pos]
+                    if sc.is_input() or not isinstance(sc.op, core.ScatterCols) or sc.dtype != "f4" or shape2(other) != shape2(node) \
+                            or other.dtype != "f4" or not full_cover(sc) or not sole_reader(sc, node) or sc in replace:
+                        continue
+                    pieces = []
+                    for (piece, o, w) in zip(sc.parents, sc.op.offsets, sc.op.widths):
+                        ops = [ident(piece), sliced(other, o, o + w)]
+                        if pos == 1:
+                            ops.reverse()
+                        q = core.Result(op, ops)
+                        node2shape[q] = [const(shape2(node)[0]), const(w)]
+                        pieces.append(q)
+                    new = core.Result(core.ScatterCols(sc.op.offsets, sc.op.widths, sc.op.C), pieces)
+                    node2shape[new] = node2shape[node]
+                    new.props.update(node.props)
+                    replace[node] = new
+                    done = True
+                    break
+                if done:
+                    continue
+            # a placed piece that is itself a placement
+            if isinstance(op, core.ScatterCols):
+                offsets, widths, pieces, changed = [], [], [], False
+                for (piece, o, w) in zip(node.parents, op.offsets, op.widths):
+                    inner = ident(piece)
+                    if not inner.is_input() and isinstance(inner.op, core.ScatterCols) and inner.op.C == w and inner not in replace \
+                            and sole_reader(inner, node) and len(offsets) + len(inner.parents) <= 8:
+                        for (q, io, iw) in zip(inner.parents, inner.op.offsets, inner.op.widths):
+                            offsets.append(o + io)
+                            widths.append(iw)
+                            pieces.append(q)
+                        changed = True
+                    else:
+                        offsets.append(o)
+                        widths.append(w)
+                        pieces.append(piece)
+                if changed and len(pieces) <= 8:
+                    new = core.Result(core.ScatterCols(offsets, widths, op.C), pieces)
+                    node2shape[new] = node2shape[node]
+                    new.props.update(node.props)
+                    replace[node] = new
+                continue
+            # a column slice of an elementwise node that only column slices read
+            cs = col_slice(node)
+            if cs is not None:
+                src = ident(cs[0])
+                if (pushable(src) or col_slice(src) is not None) and src not in out_set:
+                    readers_ok = True
+                    stack = [src]
+                    seen_r = set()
+                    q0 = cs[0]
+                    # every reader of src (through identity reshapes) is a column slice
+                    front = [src]
+                    while front and readers_ok:
+                        q = front.pop()
+                        for c in children[q]:
+                            if isinstance(c.op, core.Reshape) and shape2(c) is not None and shape2(c) == shape2(q) and c not in out_set:
+                                front.append(c)
+                            elif col_slice(c) is None:
+                                readers_ok = False
+                    if readers_ok:
+                        new = sliced(cs[0], cs[1], cs[2])
+                        if new is not node:
+                            replace[node] = new
+        if not replace:
+            break
+        outputs, updatetargs = _rewire(outputs, updatetargs, replace)
+    return list(outputs), list(updatetargs)
+
+
 def _row_member(node, node2shape):
     """(R, C) when `node` can live in a FusedRows group over [R, C] rows: an elementwise float32 node of static shape
     [R, C] or [R, 1] (C is None then: it fits any row length), a Sum over axis 1 of an [R, C] node, or the Repeat of
@@ -1805,6 +1993,8 @@ def apply_graph_rewrites(outputs_simple, updatetargs_simple, node2shape):
         outputs_simple, updatetargs_simple = view_leading_slices(outputs_simple, updatetargs_simple, node2shape)
     if config["fuse_slice_sums"]:
         outputs_simple, updatetargs_simple = fuse_slice_sums(outputs_simple, updatetargs_simple, node2shape)
+    if config["fuse_slice_sums"] and config["split_gate_columns"]:
+        outputs_simple, updatetargs_simple = split_gate_columns(outputs_simple, updatetargs_simple, node2shape)
     if config["batch_summed_products"]:
         outputs_simple, updatetargs_simple = batch_summed_products(outputs_simple, updatetargs_simple, node2shape)
         outputs_simple, updatetargs_simple = batch_shared_weight_products(outputs_simple, updatetargs_simple, node2shape)

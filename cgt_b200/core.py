@@ -1151,7 +1151,7 @@ class FusedElwise(Op):
     leave the group. With several outputs the node is tuple-valued."""
     available_impls = ("native_gpu",)
     return_type = "byref"
-    MAX_IN, MAX_OPS, MAX_OUT = 8, 16, 4
+    MAX_IN, MAX_OPS, MAX_OUT = 12, 32, 12
 
     def __init__(self, program, in_kinds, out_regs, out_dtypes, ndim, shape_input, descr="", views=None, static_shape=None):
         """views: {input index: (first column, row length of the input matrix)} for the inputs of kind 7, which are
@@ -2337,7 +2337,7 @@ _DEFAULTS = dict(
     debug=False, precision="single", backend="native", cache_dir="~/.cgt_b200_cache", enable_inplace_opt=True,
     enable_simplification=True, parallel=False, num_threads=1, force_python_impl=False, debug_cpp=False, verbose=False,
     # additions for this backend
-    devtype="gpu", device_index=0, use_cuda_graphs=True, fuse_elementwise=True, jit_fused_elementwise=True, fuse_conv_dgrad=True, fuse_conv_output=True, fuse_conv_grad_input=True, fuse_conv_implicit=True, fuse_conv_direct=True, fuse_flat_index_rows=True, hoist_filter_splits=True, merge_parameter_updates=True, fuse_rows=True, fuse_slice_sums=True, fuse_slice_views=True, batch_summed_products=True,
+    devtype="gpu", device_index=0, use_cuda_graphs=True, fuse_elementwise=True, jit_fused_elementwise=True, fuse_conv_dgrad=True, fuse_conv_output=True, fuse_conv_grad_input=True, fuse_conv_implicit=True, fuse_conv_direct=True, fuse_flat_index_rows=True, hoist_filter_splits=True, split_gate_columns=True, merge_parameter_updates=True, fuse_rows=True, fuse_slice_sums=True, fuse_slice_views=True, batch_summed_products=True,
     pad_conv_columns=True, profile=False,
 )
 

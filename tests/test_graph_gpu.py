@@ -222,6 +222,27 @@ def test_filter_splits_hoisted_change_no_bit(rt, name):
         assert np.array_equal(a, b)
 
 
+@pytest.mark.parametrize("generated", [True, False])
+def test_gate_columns_split_changes_no_bit(rt, generated):
+    """The LSTM's gate arithmetic written per gate on [batch, hidden] blocks (split_gate_columns) instead of on slabs of
+    the [batch, 4 * hidden] pre-activation: elementwise work on the same elements, so losses and parameters are
+    identical; one chain then holds a whole cell, and far fewer kernels are launched per step."""
+    results = {}
+    for on in (False, True):
+        with cgt.scoped_update_config(split_gate_columns=on, jit_fused_elementwise=generated, use_cuda_graphs=False):
+            cfg = configs.BUILDERS["lstm"](**SMALL["lstm"])
+            f = cfg.compile()
+            batches = [cfg.batch(seed) for seed in range(2)]
+            losses = [np.asarray(f(*batches[i % 2])[0]).copy() for i in range(4)]
+            params = [np.asarray(p.op.get_value()).copy() for p in cfg.params]
+            results[on] = (f.stats()["last_kernel_launches"], losses, params)
+    assert results[True][0] < 0.9 * results[False][0]
+    for (a, b) in zip(results[False][1], results[True][1]):
+        assert np.array_equal(a, b)
+    for (a, b) in zip(results[False][2], results[True][2]):
+        assert np.array_equal(a, b)
+
+
 def test_conv_direct_substitution(rt):
     """The compiler computes the 3-channel first layer of the CIFAR-shape convnet directly from the image (no column
     matrix): losses and parameters stay within the float32 tolerance of the column-matrix graph."""

@@ -314,7 +314,18 @@ def test_recurrent_graph_rewrites():
     # projection are one product each, so are the two data-gradient products that do not feed a recurrence
     assert count(lambda n: isinstance(n.op, core.Mul22) and not n.op.tA and not n.op.tB) == 2 * T + 3
     assert count(lambda n: isinstance(n.op, core.Mul22) and not n.op.tA and n.op.tB) == 2 * (T - 1) + 2   # h at t = 0 is a constant
-    assert count(lambda n: isinstance(n.op, core.ScatterCols)) == 2 * 2 * T       # two per layer and time step
+    # one placement of the four gates' gradients per layer and time step (two, per slab shape, without split_gate_columns)
+    assert count(lambda n: isinstance(n.op, core.ScatterCols)) == 2 * T
+    assert all(len(n.parents) == 4 for n in nodes if isinstance(n.op, core.ScatterCols))
+    with cgt.scoped_update_config(split_gate_columns=False):
+        sim = compilation.simplify_for_execution([cfg.loss] + list(cfg.extra_outputs), cfg.updates)
+        o1, u1 = compilation.apply_graph_rewrites(sim[0], sim[2], sim[3]["node2shape"])
+        nodes1 = [n for n in core.topsorted(o1 + u1) if not n.is_input()]
+        assert sum(1 for n in nodes1 if isinstance(n.op, core.ScatterCols)) == 2 * 2 * T
+        # per gate, every node of a cell has one shape: one chain holds the cell's forward arithmetic, and fewer launches remain
+        launches = lambda ns: sum(1 for n in ns if isinstance(n.op, (core.FusedElwise, core.ScatterCols, core.ElwiseBinary, core.ElwiseUnary))
+                                  and n.ndim > 0)
+        assert launches(nodes) < 0.7 * launches(nodes1)
     assert count(lambda n: isinstance(n.op, core.FusedRows)) == T
     wgrads = [n for n in nodes if isinstance(n.op, core.Mul22) and n.op.tA and not n.op.tB]
     assert len(wgrads) == 5 and all(isinstance(p.op, core.Concatenate) and len(p.parents) == T for n in wgrads for p in n.parents)
@@ -323,7 +334,7 @@ def test_recurrent_graph_rewrites():
     assert views and all(n.op.static_shape is not None and 7 in n.op.in_kinds for n in views)
     assert len(nodes) < 0.6 * len(before)
     # every rewrite has its switch: with all of them off the graph is the simplified one
-    off = dict(fuse_slice_views=False, fuse_slice_sums=False, batch_summed_products=False, fuse_rows=False, fuse_elementwise=False,
+    off = dict(fuse_slice_views=False, fuse_slice_sums=False, split_gate_columns=False, batch_summed_products=False, fuse_rows=False, fuse_elementwise=False,
                fuse_conv_dgrad=False, fuse_conv_grad_input=False)
     with cgt.scoped_update_config(**off):
         o2, u2 = compilation.apply_graph_rewrites(*compilation.simplify_for_execution([cfg.loss] + list(cfg.extra_outputs), cfg.updates)[0:3:2], n2s)

@@ -743,10 +743,13 @@ def test_relu_grad_nhwc_matches_op_sequence(rt, B, C, H, W):
     assert np.abs(got - exact).max() <= 2 * np.abs(want - exact).max() + tol
 
 
+from cgt_b200.core import FusedElwise as _F   # the limits of include/cgt_b200.h (CGTB_FUSED_MAX_*)
+
+
 class _FusedProgram(ctypes.Structure):
-    _fields_ = [("n_in", ctypes.c_int), ("n_ops", ctypes.c_int), ("n_out", ctypes.c_int), ("in_kind", ctypes.c_int * 8),
-                ("op_arity", ctypes.c_int * 16), ("op_code", ctypes.c_int * 16), ("op_a", ctypes.c_int * 16),
-                ("op_b", ctypes.c_int * 16), ("out_reg", ctypes.c_int * 4), ("out_dtype", ctypes.c_int * 4),
+    _fields_ = [("n_in", ctypes.c_int), ("n_ops", ctypes.c_int), ("n_out", ctypes.c_int), ("in_kind", ctypes.c_int * _F.MAX_IN),
+                ("op_arity", ctypes.c_int * _F.MAX_OPS), ("op_code", ctypes.c_int * _F.MAX_OPS), ("op_a", ctypes.c_int * _F.MAX_OPS),
+                ("op_b", ctypes.c_int * _F.MAX_OPS), ("out_reg", ctypes.c_int * _F.MAX_OUT), ("out_dtype", ctypes.c_int * _F.MAX_OUT),
                 ("launcher", ctypes.c_void_p),  # NULL: the library's own kernel runs the program
                 ("view_width", ctypes.c_long)]
 
@@ -780,8 +783,8 @@ def test_fused_elwise_matches_separate_kernels(rt, shape):
     for (q, (reg, dt)) in enumerate([(5, "i1"), (6, "f4"), (8, "f4")]):
         P.out_reg[q], P.out_dtype[q] = reg, code(dt)
     om, o2, o4 = Dev(shape=shape, dtype="i1"), Dev(shape=shape, dtype="f4"), Dev(shape=shape, dtype="f4")
-    ins = (ctypes.c_void_p * 8)(dx.ptr, db.ptr, dz.ptr, dd.ptr)
-    outs = (ctypes.c_void_p * 4)(om.ptr, o2.ptr, o4.ptr)
+    ins = (ctypes.c_void_p * _F.MAX_IN)(dx.ptr, db.ptr, dz.ptr, dd.ptr)
+    outs = (ctypes.c_void_p * _F.MAX_OUT)(om.ptr, o2.ptr, o4.ptr)
     bk, binner = longs([1, C, 1, 1, 1, 1, 1, 1]), longs([1, H * W, 1, 1, 1, 1, 1, 1])
     call("cgtb_fused_elwise", ctypes.byref(P), n, ins, bk, binner, outs)
     assert np.array_equal(om.get(), m.get())
@@ -795,9 +798,9 @@ def test_fused_elwise_matches_separate_kernels(rt, shape):
 
 
 class _RowProgram(ctypes.Structure):
-    _fields_ = [("n_in", ctypes.c_int), ("n_ops", ctypes.c_int), ("n_out", ctypes.c_int), ("in_kind", ctypes.c_int * 8),
-                ("op_arity", ctypes.c_int * 16), ("op_code", ctypes.c_int * 16), ("op_a", ctypes.c_int * 16),
-                ("op_b", ctypes.c_int * 16), ("out_reg", ctypes.c_int * 4), ("out_col", ctypes.c_int * 4),
+    _fields_ = [("n_in", ctypes.c_int), ("n_ops", ctypes.c_int), ("n_out", ctypes.c_int), ("in_kind", ctypes.c_int * _F.MAX_IN),
+                ("op_arity", ctypes.c_int * _F.MAX_OPS), ("op_code", ctypes.c_int * _F.MAX_OPS), ("op_a", ctypes.c_int * _F.MAX_OPS),
+                ("op_b", ctypes.c_int * _F.MAX_OPS), ("out_reg", ctypes.c_int * _F.MAX_OUT), ("out_col", ctypes.c_int * _F.MAX_OUT),
                 ("launcher", ctypes.c_void_p)]  # NULL: the library's own kernel runs the program
 
 
@@ -823,8 +826,8 @@ def test_fused_rows_softmax_chain(rt, R, C):
     for (q, (reg, col)) in enumerate([(8, 0), (6, 1), (14, 0)]):
         P.out_reg[q], P.out_col[q] = reg, col
     o_log, o_sum, o_dl = Dev(shape=(R, C), dtype="f4"), Dev(shape=(R, 1), dtype="f4"), Dev(shape=(R, C), dtype="f4")
-    ins = (ctypes.c_void_p * 8)(dx.ptr, db.ptr, dg.ptr, dsc.ptr)
-    outs = (ctypes.c_void_p * 4)(o_log.ptr, o_sum.ptr, o_dl.ptr)
+    ins = (ctypes.c_void_p * _F.MAX_IN)(dx.ptr, db.ptr, dg.ptr, dsc.ptr)
+    outs = (ctypes.c_void_p * _F.MAX_OUT)(o_log.ptr, o_sum.ptr, o_dl.ptr)
     call("cgtb_fused_rows", ctypes.byref(P), R, C, ins, outs)
     e = np.exp(x.astype("f8") + bias.astype("f8"))
     ssum = e.sum(axis=1, keepdims=True)
@@ -871,8 +874,8 @@ def test_row_selection_kernels(rt, R, C):
     for (q, (reg, col)) in enumerate([(3, 1), (4, 0)]):
         P.out_reg[q], P.out_col[q] = reg, col
     o_pick, o_grad = Dev(np.full((R, 1), np.nan, "f4")), Dev(np.full((R, C), np.nan, "f4"))
-    ins = (ctypes.c_void_p * 8)(dx.ptr, didx.ptr, dg.ptr)
-    outs = (ctypes.c_void_p * 4)(o_pick.ptr, o_grad.ptr)
+    ins = (ctypes.c_void_p * _F.MAX_IN)(dx.ptr, didx.ptr, dg.ptr)
+    outs = (ctypes.c_void_p * _F.MAX_OUT)(o_pick.ptr, o_grad.ptr)
     call("cgtb_fused_rows", ctypes.byref(P), R, C, ins, outs)
     assert np.array_equal(o_pick.get().reshape(R), x.reshape(-1)[flat])
     assert np.array_equal(o_grad.get(), hot_np * g[:, None])
@@ -885,7 +888,7 @@ def test_fused_rows_refuses_long_rows(rt):
     P.out_reg[0], P.out_col[0] = 1, 1
     d = Dev(shape=(4, 129), dtype="f4")
     o = Dev(shape=(4, 1), dtype="f4")
-    rc = runtime.lib().cgtb_fused_rows(ctypes.byref(P), 4, 129, (ctypes.c_void_p * 8)(d.ptr), (ctypes.c_void_p * 4)(o.ptr))
+    rc = runtime.lib().cgtb_fused_rows(ctypes.byref(P), 4, 129, (ctypes.c_void_p * _F.MAX_IN)(d.ptr), (ctypes.c_void_p * _F.MAX_OUT)(o.ptr))
     assert rc != 0 and "128" in runtime.last_error()
 
 
@@ -908,13 +911,13 @@ def test_fused_elwise_reads_column_slices_in_place(rt, R, W, pitch, off):
     P.out_reg[0], P.out_dtype[0] = 3, code("f4")
     P.view_width = W
     out = Dev(shape=(R, W), dtype="f4")
-    ins = (ctypes.c_void_p * 8)(dS.ptr, dg.ptr)
-    outs = (ctypes.c_void_p * 4)(out.ptr)
-    bk, binner = longs([pitch, 1, 1, 1, 1, 1, 1, 1]), longs([off, 1, 1, 1, 1, 1, 1, 1])
+    ins = (ctypes.c_void_p * _F.MAX_IN)(dS.ptr, dg.ptr)
+    outs = (ctypes.c_void_p * _F.MAX_OUT)(out.ptr)
+    bk, binner = longs([pitch] + [1] * (_F.MAX_IN - 1)), longs([off] + [1] * (_F.MAX_IN - 1))
     call("cgtb_fused_elwise", ctypes.byref(P), R * W, ins, bk, binner, outs)
     assert np.array_equal(out.get(), want.get())
     # a slice that sticks out of the matrix is refused
-    bad = longs([pitch, 1, 1, 1, 1, 1, 1, 1]), longs([pitch - W + 1, 1, 1, 1, 1, 1, 1, 1])
+    bad = longs([pitch] + [1] * (_F.MAX_IN - 1)), longs([pitch - W + 1] + [1] * (_F.MAX_IN - 1))
     rc = runtime.lib().cgtb_fused_elwise(ctypes.byref(P), R * W, ins, bad[0], bad[1], outs)
     assert rc != 0 and "column range" in runtime.last_error()
 
@@ -930,7 +933,7 @@ def test_scatter_cols_places_pieces_into_zeros(rt):
         want = want + O.incsli(np.zeros((R, C), "f4"), 1, o, o + y.shape[1], 1, y)
     devs = [Dev(y) for (_o, y) in pieces]
     out = Dev(np.full((R, C), 7.0, "f4"))
-    ptrs = (ctypes.c_void_p * 8)(*[d.ptr for d in devs])
+    ptrs = (ctypes.c_void_p * _F.MAX_IN)(*[d.ptr for d in devs])
     call("cgtb_scatter_cols", R, C, 3, longs([o for (o, _y) in pieces]), longs([y.shape[1] for (_o, y) in pieces]), ptrs, out.ptr)
     assert np.array_equal(out.get(), want)
     rc = runtime.lib().cgtb_scatter_cols(R, C, 2, longs([0, 4]), longs([8, 8]), ptrs, out.ptr)
