@@ -302,6 +302,102 @@ def batch_summed_products(outputs, updatetargs, node2shape):
     return _rewire(outputs, updatetargs, replace)
 
 
+def batch_scalar_sums(outputs, updatetargs, node2shape):
+    """A scalar accumulated term by term, loss = ((0 - X_0.sum()) - X_1.sum()) - ... with one [R, C] matrix per time step:
+    every term is a full reduction on the GPU, a copy of one float to the host and a host subtraction. Terms of one
+    sign and one matrix shape (at least four) become ONE reduction over the row-concatenated matrices,
+    +/- Sum{0,1}(concat_t X_t): one concatenation, one reduction, one copy. The order of the float32 additions changes:
+    float32 tolerance against the term-by-term graph (the value is the reported loss; no gradient flows through it,
+    this runs after differentiation)."""
+    MIN_TERMS, MAX_PIECES = 4, 64
+    all_out = list(outputs) + list(updatetargs)
+    nodes = core.topsorted(all_out)
+    children = defaultdict(list)
+    for node in nodes:
+        for par in node.parents:
+            children[par].append(node)
+    out_set = set(all_out)
+
+    def is_acc(node):
+        return (not node.is_input() and isinstance(node.op, core.ElwiseBinary) and node.op.opname in ("+", "-") and node.ndim == 0
+                and node.dtype == "f4"
+                and all(par.ndim == 0 and (par.dtype == "f4" or isinstance(getattr(par, "op", None), core.Constant)) for par in node.parents))
+
+    def terms_of(node, sign, acc):
+        for (pos, par) in enumerate(node.parents):
+            sg = -sign if (node.op.opname == "-" and pos == 1) else sign
+            while (not par.is_input() and isinstance(par.op, core.ElwiseUnary) and par.op.opname == "neg" and par.ndim == 0
+                   and len(children[par]) == 1 and par not in out_set):
+                (sg, par) = (-sg, par.parents[0])     # 0 - x arrives as neg(x)
+            if is_acc(par) and len(children[par]) == 1 and par not in out_set:
+                terms_of(par, sg, acc)
+            else:
+                acc.append((sg, par))
+
+    def full_sum(term):
+        """X when term = X.sum() of a static float32 matrix read by nothing else"""
+        q = term
+        while not q.is_input() and isinstance(q.op, core.Reshape) and len(children[q]) == 1 and q not in out_set:
+            q = q.parents[0]
+        if q.is_input() or not isinstance(q.op, core.Sum) or len(children[q]) != 1 or q in out_set:
+            return None
+        x = q.parents[0]
+        shp = _static_shape(node2shape[x]) if x in node2shape else None
+        if shp is None or len(shp) != 2 or x.dtype != "f4" or sorted(q.op.axes) != [0, 1]:
+            return None
+        return x
+
+    const = lambda v: core.cgt.constant(np.array(v, "i8"))
+    replace, covered = {}, set()
+    for node in reversed(nodes):
+        if node in covered or not is_acc(node):
+            continue
+        terms = []
+        terms_of(node, 1, terms)
+        stack = [node]
+        while stack:
+            q = stack.pop()
+            covered.add(q)
+            stack.extend(par for par in q.parents if is_acc(par) and len(children[par]) == 1 and par not in out_set)
+        groups = defaultdict(list)
+        for (k, (sg, t)) in enumerate(terms):
+            x = full_sum(t)
+            if x is not None:
+                groups[(sg, _static_shape(node2shape[x]))].append((k, x))
+        batched, new_terms = set(), []
+        for ((sg, shp), members) in groups.items():
+            if len(members) < MIN_TERMS:
+                continue
+            for lo in range(0, len(members), MAX_PIECES):
+                chunk = members[lo:lo + MAX_PIECES]
+                if len(chunk) < 2:
+                    continue
+                cat = core.Result(core.Concatenate(0), [x for (_k, x) in chunk])
+                node2shape[cat] = [const(shp[0] * len(chunk)), const(shp[1])]
+                tot = core.Result(core.Sum((0, 1)), [cat])
+                node2shape[tot] = [const(1), const(1)]
+                sc = core.Result(core.Reshape(), [tot])
+                node2shape[sc] = []
+                new_terms.append((sg, sc))
+                batched.update(k for (k, _x) in chunk)
+        if not batched:
+            continue
+        rest = [(sg, t) for (k, (sg, t)) in enumerate(terms) if k not in batched] + new_terms
+        rest.sort(key=lambda st: -st[0])      # a positive term first, if there is one
+        (sg0, total) = rest[0]
+        if sg0 < 0:
+            total = core.Result(core.ElwiseUnary("neg"), [total])
+            node2shape[total] = []
+        for (sg, t) in rest[1:]:
+            total = core.Result(core.ElwiseBinary("+" if sg > 0 else "-", (True, True)), [total, t])
+            node2shape[total] = []
+        total.props.update(node.props)
+        replace[node] = total
+    if not replace:
+        return list(outputs), list(updatetargs)
+    return _rewire(outputs, updatetargs, replace)
+
+
 def batch_shared_weight_products(outputs, updatetargs, node2shape):
     """Products that share their right operand and do not need each other: Mul22{N,N}(a_t, W) or Mul22{N,T}(a_t, W) for
     many t with a_t of one shape, none of which depends on another's result (the input-to-hidden products of an unrolled
@@ -1998,6 +2094,7 @@ def apply_graph_rewrites(outputs_simple, updatetargs_simple, node2shape):
     if config["batch_summed_products"]:
         outputs_simple, updatetargs_simple = batch_summed_products(outputs_simple, updatetargs_simple, node2shape)
         outputs_simple, updatetargs_simple = batch_shared_weight_products(outputs_simple, updatetargs_simple, node2shape)
+        outputs_simple, updatetargs_simple = batch_scalar_sums(outputs_simple, updatetargs_simple, node2shape)
     if config["fuse_elementwise"]:
         if config["fuse_rows"] and config["fuse_flat_index_rows"]:
             outputs_simple, updatetargs_simple = fuse_flat_index_rows(outputs_simple, updatetargs_simple, node2shape)

@@ -1151,7 +1151,7 @@ class FusedElwise(Op):
     leave the group. With several outputs the node is tuple-valued."""
     available_impls = ("native_gpu",)
     return_type = "byref"
-    MAX_IN, MAX_OPS, MAX_OUT = 12, 32, 12
+    MAX_IN, MAX_OPS, MAX_OUT = 16, 32, 12
 
     def __init__(self, program, in_kinds, out_regs, out_dtypes, ndim, shape_input, descr="", views=None, static_shape=None):
         """views: {input index: (first column, row length of the input matrix)} for the inputs of kind 7, which are

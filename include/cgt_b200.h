@@ -254,7 +254,7 @@ int cgtb_binary(int op, int dt_x, int dt_y, int dt_out, long n, const void* x, c
  * Values are float32 or 0/1 truth values; every operation is carried out exactly as the separate
  * kernels of cgtb_unary / cgtb_binary do it, so the results have the same bits.
  * Registers 0 .. n_in-1 hold the inputs, register n_in+j the result of operation j. */
-#define CGTB_FUSED_MAX_IN 12
+#define CGTB_FUSED_MAX_IN 16
 #define CGTB_FUSED_MAX_OPS 32
 #define CGTB_FUSED_MAX_OUT 12
 enum { CGTB_FIN_F4 = 0, CGTB_FIN_I1 = 1, CGTB_FIN_SCALAR_F4 = 2, CGTB_FIN_SCALAR_I8 = 3, CGTB_FIN_BCAST_F4 = 4,

@@ -327,6 +327,13 @@ def test_recurrent_graph_rewrites():
                                   and n.ndim > 0)
         assert launches(nodes) < 0.7 * launches(nodes1)
     assert count(lambda n: isinstance(n.op, core.FusedRows)) == T
+    # the loss is accumulated term by term, one full reduction per time step: batch_scalar_sums leaves one reduction over
+    # the row-concatenated terms (T >= 4 terms of one shape)
+    full = lambda ns, rows: sum(1 for n in ns if isinstance(n.op, core.Sum) and sorted(n.op.axes) == [0, 1]
+                                and compilation._static_shape(n2s.get(n.parents[0], [])) == (rows, 65))
+    assert sum(1 for n in before if isinstance(n.op, core.Sum) and sorted(n.op.axes) == [0, 1]
+               and compilation._static_shape(n2s[n.parents[0]]) == (8, 65)) == T
+    assert full(nodes, 8) == 0 and full(nodes, 8 * T) == 1
     wgrads = [n for n in nodes if isinstance(n.op, core.Mul22) and n.op.tA and not n.op.tB]
     assert len(wgrads) == 5 and all(isinstance(p.op, core.Concatenate) and len(p.parents) == T for n in wgrads for p in n.parents)
     assert sum(1 for n in before if isinstance(n.op, core.Mul22) and n.op.tA and not n.op.tB) == 5 * T
