@@ -1147,9 +1147,9 @@ CGTB_API int cgtb_conv_direct_fwd_bias_relu(const float* x, long B, int Cin, int
                                             int pw, const float* bias, float* y, signed char* mask) {
   if (!require_runtime("cgtb_conv_direct_fwd_bias_relu")) return 1;
   if (B <= 0) return 0;
-  if (!conv_direct_ok(B, Cin, H, W, Cout, kh, kw, ph, pw))
-    return fail("cgtb_conv_direct_fwd_bias_relu: not supported for Cin=%d kh=%d kw=%d pad=%d,%d Cout=%d H=%d W=%d (3, 5, 5, 2, 2, 32, multiple of 8, 32)",
-                Cin, kh, kw, ph, pw, Cout, H, W);
+  if (!conv_direct_ok(B, Cin, H, W, Cout, kh, kw, ph, pw) || ((uintptr_t)x & 15) != 0)   // the image rows are read as 128-bit words
+    return fail("cgtb_conv_direct_fwd_bias_relu: not supported for Cin=%d kh=%d kw=%d pad=%d,%d Cout=%d H=%d W=%d (3, 5, 5, 2, 2, 32, multiple of 8, 32) "
+                "or an image that does not start on a 16-byte boundary", Cin, kh, kw, ph, pw, Cout, H, W);
   const unsigned blocks = (unsigned)(B * (H / kDcRows));
   CGTB_LAUNCH((conv_direct_fwd_kernel<3, 5, 32, 32>), blocks, kDcFwdThreads, 0, x, w, bias, H, y, (int8_t*)mask);
   CGTB_CHECK_LAUNCH("conv_direct_fwd");

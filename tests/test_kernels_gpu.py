@@ -639,6 +639,10 @@ def test_conv_direct_first_layer(rt, B, H):
         assert np.array_equal(out.get(), out2.get())
     else:
         np.testing.assert_allclose(out.get(), out2.get(), rtol=1e-4, atol=1e-5 * scale)
+    # an image that does not start on a 16-byte boundary is refused before any launch (its rows are read as 128-bit words)
+    k0 = runtime.kernel_launches()
+    rc = runtime.lib().cgtb_conv_direct_fwd_bias_relu(ctypes.c_void_p(dx.w.data + 4), B, Cin, H, W, dw_.ptr, Cout, k, k, pad, pad, db.ptr, y.ptr, mask.ptr)
+    assert rc != 0 and "16-byte" in runtime.last_error() and runtime.kernel_launches() == k0
     # another layer is refused, not approximated
     rc = runtime.lib().cgtb_conv_direct_wgrad(dx.ptr, B, 4, H, W, ddy.ptr, Cout, k, k, pad, pad, out.ptr)
     assert rc != 0 and "not supported" in runtime.last_error()
