@@ -573,6 +573,79 @@ def fuse_slice_sums(outputs, updatetargs, node2shape):
     return _rewire(outputs, updatetargs, replace)
 
 
+def fuse_product_sums(outputs, updatetargs, node2shape):
+    """z = (X + Repeat(b)) + (Mul22(h, U) + Repeat(c)), the pre-activation of a layer fed by two inputs (an unrolled
+    recurrent cell forms it once per layer and time step) -> Mul22BiasAdd(h, U, c, X, b): the three additions run in
+    the output stage of the product, in the same association, so no bit changes; one launch instead of two. Only for
+    products that Mul22 gives to its FMA-tile kernel (the output stage lives there), whose result and whose sum with its
+    bias have no other reader."""
+    all_out = list(outputs) + list(updatetargs)
+    nodes = core.topsorted(all_out)
+    children = defaultdict(list)
+    for node in nodes:
+        for par in node.parents:
+            children[par].append(node)
+    out_set = set(all_out)
+
+    def is_add(n):
+        return (not n.is_input() and isinstance(n.op, core.ElwiseBinary) and n.op.opname == "+" and n.op.scalar_mask == (False, False)
+                and n.dtype == "f4" and n.ndim == 2)
+
+    def row_repeat(n, N):
+        """the [1, N] row when n = Repeat{0}(row)"""
+        if n.is_input() or not isinstance(n.op, core.Repeat) or list(n.op.axes) != [0] or n.dtype != "f4":
+            return None
+        row = n.parents[0]
+        shp = _static_shape(node2shape[row]) if row in node2shape else None
+        return row if shp == (1, N) else None
+
+    def affine(n, N, want_product):
+        """(x, row) when n = x + Repeat{0}(row) is read once; with want_product x must be a Mul22 read once"""
+        if not is_add(n) or n in out_set or len(children[n]) != 1:
+            return None
+        for (x, r) in ((n.parents[0], n.parents[1]), (n.parents[1], n.parents[0])):
+            row = row_repeat(r, N)
+            if row is None or x.dtype != "f4":
+                continue
+            if want_product and (x.is_input() or not isinstance(x.op, core.Mul22) or len(children[x]) != 1 or x in out_set):
+                continue
+            return (x, row)
+        return None
+
+    replace = {}
+    for z in nodes:
+        if not is_add(z) or z in out_set:
+            continue
+        shp = _static_shape(node2shape[z]) if z in node2shape else None
+        if shp is None:
+            continue
+        (M, N) = shp
+        for (p, q) in ((z.parents[0], z.parents[1]), (z.parents[1], z.parents[0])):
+            prod = affine(p, N, True)
+            side = affine(q, N, False)
+            if prod is None or side is None or p is q:
+                continue
+            (m, c_row) = prod
+            (x, b_row) = side
+            if _static_shape(node2shape[x]) != (M, N):
+                continue
+            (tA, tB) = (m.op.tA, m.op.tB)
+            ashp = _static_shape(node2shape[m.parents[0]])
+            if ashp is None or any(par.dtype != "f4" for par in m.parents):
+                continue
+            K = ashp[0] if tA else ashp[1]
+            if M * N <= 2048 or (not tA and tB) or M * N * K > (1 << 25):
+                continue     # not a product of the FMA-tile kernel
+            new = core.Result(core.Mul22BiasAdd(tA, tB), [m.parents[0], m.parents[1], c_row, x, b_row])
+            node2shape[new] = node2shape[z]
+            new.props.update(z.props)
+            replace[z] = new
+            break
+    if not replace:
+        return list(outputs), list(updatetargs)
+    return _rewire(outputs, updatetargs, replace)
+
+
 def split_gate_columns(outputs, updatetargs, node2shape):
     """Elementwise arithmetic on column blocks of one matrix, written per block.
 
@@ -2095,6 +2168,8 @@ def apply_graph_rewrites(outputs_simple, updatetargs_simple, node2shape):
         outputs_simple, updatetargs_simple = batch_summed_products(outputs_simple, updatetargs_simple, node2shape)
         outputs_simple, updatetargs_simple = batch_shared_weight_products(outputs_simple, updatetargs_simple, node2shape)
         outputs_simple, updatetargs_simple = batch_scalar_sums(outputs_simple, updatetargs_simple, node2shape)
+    if config["fuse_product_sums"]:    # after the batching: the products over all time steps are views by now
+        outputs_simple, updatetargs_simple = fuse_product_sums(outputs_simple, updatetargs_simple, node2shape)
     if config["fuse_elementwise"]:
         if config["fuse_rows"] and config["fuse_flat_index_rows"]:
             outputs_simple, updatetargs_simple = fuse_flat_index_rows(outputs_simple, updatetargs_simple, node2shape)

@@ -1966,6 +1966,36 @@ class Mul22(Op):
     __str__ = __repr__
 
 
+class Mul22BiasAdd(Op):
+    """(A, B, bias [1,N], addend [M,N], addend_bias [1,N]) -> (addend + addend_bias) + (op(A).op(B) + bias).
+
+    Not part of the reference's Op set. compilation.fuse_product_sums forms it from the sum of two affine
+    pre-activations, (x.W + b) + (h.U + c) (nn.Affine twice, cgt/nn.py:190-215, as an unrolled recurrent cell has it once
+    per layer and time step): the three additions run in the output stage of the product h.U, in the association of
+    the separate Ops, so the result has their bits. Only products that Mul22 gives to its FMA-tile kernel."""
+    available_impls = ("native_gpu",)
+
+    def __init__(self, tA, tB):
+        self.tA = bool(tA)
+        self.tB = bool(tB)
+
+    def get_diff(self, num_inputs):
+        return [False] * num_inputs
+
+    def shp_apply(self, inputs):
+        return [cgt.size(inputs[0], 1 if self.tA else 0), cgt.size(inputs[1], 0 if self.tB else 1)]
+
+    def typ_apply(self, input_types):
+        return TensorType("f4", 2)
+
+    def get_native_compile_info(self, input_types, devtype):
+        return NativeCompileInfo(None, prebuilt="cgtb_op_mul22_bias_add",
+                                 closure_triples=[("tA", ctypes.c_bool, self.tA), ("tB", ctypes.c_bool, self.tB), ("handle", ctypes.c_void_p, 0)])
+
+    def __repr__(self):
+        return "Mul22BiasAdd{%s,%s}" % ("T" if self.tA else "N", "T" if self.tB else "N")
+
+
 class BatchedMul22(Op):
     """Per-batch matrix product over the leading axis (cgt/core.py:2231-2288)."""
     available_impls = ("python", "native_cpu", "native_gpu")
@@ -2337,7 +2367,7 @@ _DEFAULTS = dict(
     debug=False, precision="single", backend="native", cache_dir="~/.cgt_b200_cache", enable_inplace_opt=True,
     enable_simplification=True, parallel=False, num_threads=1, force_python_impl=False, debug_cpp=False, verbose=False,
     # additions for this backend
-    devtype="gpu", device_index=0, use_cuda_graphs=True, fuse_elementwise=True, jit_fused_elementwise=True, fuse_conv_dgrad=True, fuse_conv_output=True, fuse_conv_grad_input=True, fuse_conv_implicit=True, fuse_conv_direct=True, fuse_flat_index_rows=True, hoist_filter_splits=True, split_gate_columns=True, merge_parameter_updates=True, fuse_rows=True, fuse_slice_sums=True, fuse_slice_views=True, batch_summed_products=True,
+    devtype="gpu", device_index=0, use_cuda_graphs=True, fuse_elementwise=True, jit_fused_elementwise=True, fuse_conv_dgrad=True, fuse_conv_output=True, fuse_conv_grad_input=True, fuse_conv_implicit=True, fuse_conv_direct=True, fuse_flat_index_rows=True, hoist_filter_splits=True, split_gate_columns=True, fuse_product_sums=True, merge_parameter_updates=True, fuse_rows=True, fuse_slice_sums=True, fuse_slice_views=True, batch_summed_products=True,
     pad_conv_columns=True, profile=False,
 )
 

@@ -55,6 +55,20 @@ CGTB_API int cgtb_sgemm(int tA, int tB, long M, long N, long K, const float* A, 
                         long ldc, int impl) {
   return cgtb::sgemm_dispatch(tA, tB, 1, M, N, K, A, lda, 0, B, ldb, 0, C, ldc, 0, impl);
 }
+namespace cgtb {
+int sgemm_tile16_bias_add(int tA, int tB, long M, long N, long K, const float* A, long lda, const float* B, long ldb, const float* bias,
+                          const float* addend, long ldd, const float* addend_bias, float* C, long ldc);
+}
+CGTB_API int cgtb_sgemm_bias_add(int tA, int tB, long M, long N, long K, const float* A, long lda, const float* B, long ldb,
+                                 const float* bias, const float* addend, long ldd, const float* addend_bias, float* C, long ldc) {
+  if (!cgtb::require_runtime("cgtb_sgemm_bias_add")) return 1;
+  if (addend_bias && !addend) return cgtb::fail("cgtb_sgemm_bias_add: addend_bias without addend");
+  const int rc = cgtb::sgemm_tile16_bias_add(tA, tB, M, N, K, A, lda, B, ldb, bias, addend, ldd, addend_bias, C, ldc);
+  if (rc < 0)
+    return cgtb::fail("cgtb_sgemm_bias_add: M=%ld N=%ld K=%ld (tA=%d tB=%d) is not a product of the FMA-tile kernel (M*N > 2048, M*N*K <= 2^25, "
+                      "not A.B^T); use cgtb_sgemm and add afterwards", M, N, K, tA, tB);
+  return rc;
+}
 CGTB_API int cgtb_sgemm_batched(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA,
                                 const float* B, long ldb, long strideB, float* C, long ldc, long strideC, int impl) {
   return cgtb::sgemm_dispatch(tA, tB, P, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC, impl);

@@ -248,10 +248,19 @@ __global__ void __launch_bounds__(256) sgemm_small_nt4_kernel(long M, long N, lo
 // that are contiguous for either storage order, the next slice's words already in flight while the current one is
 // used; the groups' partial sums are added in group order. One fixed order of operations: reproducible.
 namespace {
+// Output stage: C = (addend + addend_bias) + (A.B + bias) with row vectors bias, addend_bias [N] and a matrix addend
+// [M, N]; every pointer may be null. Plain float32 additions in exactly this association: the sum of two affine
+// pre-activations (x.W + b) + (h.U + c) as the separate kernels form it.
+struct TileEpilogue {
+  const float* bias;
+  const float* addend;
+  long ldd;
+  const float* addend_bias;
+};
 template <int KS>
 __global__ void __launch_bounds__(256 * KS) sgemm_tile16_kernel(int tA, int tB, long M, long N, long K, const float* __restrict__ A, long lda,
                                                                long strideA, const float* __restrict__ B, long ldb, long strideB,
-                                                               float* __restrict__ C, long ldc, long strideC) {
+                                                               float* __restrict__ C, long ldc, long strideC, const TileEpilogue ep) {
   __shared__ float As[KS][16][17];  // [m][k]
   __shared__ float Bs[KS][16][17];  // [k][n]
   const int tx = threadIdx.x & 15, ty = (threadIdx.x >> 4) & 15, kz = threadIdx.x >> 8;
@@ -293,24 +302,43 @@ __global__ void __launch_bounds__(256 * KS) sgemm_tile16_kernel(int tA, int tB, 
       for (int z = 1; z < KS; ++z) acc += As[z][ty][tx];
     }
   }
-  if (kz == 0 && m0 + ty < M && n0 + tx < N) C[(m0 + ty) * ldc + n0 + tx] = acc;
+  if (kz == 0 && m0 + ty < M && n0 + tx < N) {
+    const long m = m0 + ty, n = n0 + tx;
+    if (ep.bias) acc = __fadd_rn(acc, ep.bias[n]);
+    if (ep.addend) {
+      float t = ep.addend[m * ep.ldd + n];
+      if (ep.addend_bias) t = __fadd_rn(t, ep.addend_bias[n]);
+      acc = __fadd_rn(t, acc);
+    }
+    C[m * ldc + n] = acc;
+  }
 }
 }  // namespace
 
 namespace cgtb {
 // returns 0 done, -1 not eligible
-int sgemm_tile16(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B, long ldb,
-                 long strideB, float* C, long ldc, long strideC) {
+static int sgemm_tile16_ep(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B, long ldb,
+                           long strideB, float* C, long ldc, long strideC, const TileEpilogue& ep) {
   if (P <= 0 || M <= 0 || N <= 0) return 0;
   if (K <= 0 || M * N * K > (1L << 25) || P > 65535 || cgtb_ceil_div(M, 16) > 65535) return -1;
   dim3 grid((unsigned)cgtb_ceil_div(N, 16), (unsigned)cgtb_ceil_div(M, 16), (unsigned)P);
   const long blocks = (long)grid.x * grid.y * grid.z;
   if (blocks < 4L * rt().sm_count && K >= 64)
-    CGTB_LAUNCH(sgemm_tile16_kernel<4>, grid, 1024, 0, tA, tB, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC);
+    CGTB_LAUNCH(sgemm_tile16_kernel<4>, grid, 1024, 0, tA, tB, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC, ep);
   else
-    CGTB_LAUNCH(sgemm_tile16_kernel<1>, grid, 256, 0, tA, tB, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC);
+    CGTB_LAUNCH(sgemm_tile16_kernel<1>, grid, 256, 0, tA, tB, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC, ep);
   CGTB_CHECK_LAUNCH("sgemm_tile16");
   return 0;
+}
+int sgemm_tile16(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA, const float* B, long ldb,
+                 long strideB, float* C, long ldc, long strideC) {
+  return sgemm_tile16_ep(tA, tB, P, M, N, K, A, lda, strideA, B, ldb, strideB, C, ldc, strideC, TileEpilogue{nullptr, nullptr, 0, nullptr});
+}
+// the FMA-tile product with its output stage; -1 when the product is not one the dispatcher gives to that kernel
+int sgemm_tile16_bias_add(int tA, int tB, long M, long N, long K, const float* A, long lda, const float* B, long ldb, const float* bias,
+                          const float* addend, long ldd, const float* addend_bias, float* C, long ldc) {
+  if (M * N <= 2048 || (!tA && tB)) return -1;   // the dispatcher sends these to the warp-per-output kernel
+  return sgemm_tile16_ep(tA, tB, 1, M, N, K, A, lda, 0, B, ldb, 0, C, ldc, 0, TileEpilogue{bias, addend, ldd, addend_bias});
 }
 
 // returns 0 done, -1 not a small product

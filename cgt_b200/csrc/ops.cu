@@ -325,6 +325,22 @@ OP_BYREF(cgtb_op_mul22) {
   else
     fail("Mul22: unsupported dtype %d", (int)A->dtype());
 }
+// Mul22BiasAdd: (A, B, bias [1,N], addend [M,N], addend_bias [1,N]) -> (addend + addend_bias) + (A.B + bias)
+OP_BYREF(cgtb_op_mul22_bias_add) {
+  Mul22Closure* cl = (Mul22Closure*)cl0;
+  cgtArray *A = ARR(reads[0]), *B = ARR(reads[1]), *bias = ARR(reads[2]), *add = ARR(reads[3]), *abias = ARR(reads[4]), *C = ARR(write0);
+  if (!all_gpu({A, B, bias, add, abias, C})) { fail("Mul22BiasAdd: operands must be on the GPU"); return; }
+  long lda = A->shape()[1], ldb = B->shape()[1], ldc = C->shape()[1];
+  long M = C->shape()[0], N = C->shape()[1], K = A->shape()[cl->tA ? 0 : 1];
+  long Kb = B->shape()[cl->tB ? 1 : 0], Ma = A->shape()[cl->tA ? 1 : 0], Nb = B->shape()[cl->tB ? 0 : 1];
+  if (K != Kb || M != Ma || N != Nb || A->dtype() != cgt_f4 || B->dtype() != cgt_f4 || bias->dtype() != cgt_f4 || add->dtype() != cgt_f4 ||
+      abias->dtype() != cgt_f4 || bias->size() != N || abias->size() != N || add->size() != M * N) {
+    fail("Mul22BiasAdd: operand shapes do not fit together");
+    return;
+  }
+  cgtb_sgemm_bias_add(cl->tA, cl->tB, M, N, K, (const float*)A->data(), lda, (const float*)B->data(), ldb, (const float*)bias->data(),
+                      (const float*)add->data(), N, (const float*)abias->data(), (float*)C->data(), ldc);
+}
 struct BMul22Closure { bool tA; bool tB; };
 OP_BYREF(cgtb_op_batched_mul22) {
   BMul22Closure* cl = (BMul22Closure*)cl0;

@@ -79,6 +79,7 @@ def _declare(lib):
         "cgtb_apply_byref": (ci, [vp, vp, ci, ctypes.POINTER(vp), vp]),
         "cgtb_sgemm": (ci, [ci, ci, cl, cl, cl, vp, cl, vp, cl, vp, cl, ci]),
         "cgtb_sgemm_batched": (ci, [ci, ci, cl, cl, cl, cl, vp, cl, cl, vp, cl, cl, vp, cl, cl, ci]),
+        "cgtb_sgemm_bias_add": (ci, [ci, ci, cl, cl, cl, vp, cl, vp, cl, vp, vp, cl, vp, vp, cl]),
         "cgtb_dgemm": (ci, [ci, ci, cl, cl, cl, vp, cl, vp, cl, vp, cl]),
         "cgtb_im2col": (ci, [ci, vp, cl] + [ci] * 9 + [vp]), "cgtb_col2im": (ci, [ci, vp, cl] + [ci] * 9 + [vp]),
         "cgtb_max_pool": (ci, [ci, vp, cl] + [ci] * 11 + [vp, vp]),

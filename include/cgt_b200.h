@@ -150,6 +150,15 @@ int cgtb_sgemm(int tA, int tB, long M, long N, long K, const float* A, long lda,
 /* BatchedMul22 (cgt/core.py:2272-2286): P independent products, operands strideX apart */
 int cgtb_sgemm_batched(int tA, int tB, long P, long M, long N, long K, const float* A, long lda, long strideA,
                        const float* B, long ldb, long strideB, float* C, long ldc, long strideC, int impl);
+
+/* C = (addend + addend_bias) + (op(A).op(B) + bias): a product with the additions that follow it in an affine layer fed by
+ * two inputs, z = (x.W + b) + (h.U + c) (cgt/nn.py Affine applied twice and added, as the reference's recurrent demos
+ * do), in the product's output stage. bias, addend_bias: [N] rows; addend: [M, N] with row pitch ldd; each may be null
+ * (addend_bias only with addend). The additions are plain float32 additions in exactly this association, so the result
+ * has the bits of cgtb_sgemm followed by the three additions. Only products that cgtb_sgemm gives to its FMA-tile
+ * kernel (M*N > 2048, M*N*K <= 2^25, not A.B^T); others are refused. */
+int cgtb_sgemm_bias_add(int tA, int tB, long M, long N, long K, const float* A, long lda, const float* B, long ldb,
+                        const float* bias, const float* addend, long ldd, const float* addend_bias, float* C, long ldc);
 int cgtb_dgemm(int tA, int tB, long M, long N, long K, const double* A, long lda, const double* B, long ldb,
                double* C, long ldc);
 

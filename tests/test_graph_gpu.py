@@ -222,6 +222,28 @@ def test_filter_splits_hoisted_change_no_bit(rt, name):
         assert np.array_equal(a, b)
 
 
+def test_product_sums_in_the_output_stage_change_no_bit(rt):
+    """(x.W + b) + (h.U + c) with the three additions in the output stage of the product h.U (fuse_product_sums): the
+    additions keep their association, so the LSTM's losses and parameters are identical; one launch less per layer and
+    time step."""
+    results = {}
+    for on in (False, True):
+        with cgt.scoped_update_config(fuse_product_sums=on, use_cuda_graphs=False):
+            cfg = configs.BUILDERS["lstm"](seq_len=6, batch=64)
+            f = cfg.compile()
+            reprs = [repr(i) for i in f.eg.instrs]
+            batches = [cfg.batch(seed) for seed in range(2)]
+            losses = [np.asarray(f(*batches[i % 2])[0]).copy() for i in range(4)]
+            params = [np.asarray(p.op.get_value()).copy() for p in cfg.params]
+            results[on] = (reprs, f.stats()["last_kernel_launches"], losses, params)
+    assert sum("op:Mul22BiasAdd" in r for r in results[True][0]) == 2 * 6 and not any("Mul22BiasAdd" in r for r in results[False][0])
+    assert results[True][1] <= results[False][1] - 2 * 6
+    for (a, b) in zip(results[False][2], results[True][2]):
+        assert np.array_equal(a, b)
+    for (a, b) in zip(results[False][3], results[True][3]):
+        assert np.array_equal(a, b)
+
+
 @pytest.mark.parametrize("generated", [True, False])
 def test_gate_columns_split_changes_no_bit(rt, generated):
     """The LSTM's gate arithmetic written per gate on [batch, hidden] blocks (split_gate_columns) instead of on slabs of

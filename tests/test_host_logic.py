@@ -312,7 +312,9 @@ def test_recurrent_graph_rewrites():
     assert count(lambda n: isinstance(n.op, core.LeadingSlice)) == 2 * T + 5 * T
     # the hidden-to-hidden products stay (each needs the step before it); input-to-hidden of both layers and the output
     # projection are one product each, so are the two data-gradient products that do not feed a recurrence
-    assert count(lambda n: isinstance(n.op, core.Mul22) and not n.op.tA and not n.op.tB) == 2 * T + 3
+    assert count(lambda n: isinstance(n.op, core.Mul22) and not n.op.tA and not n.op.tB) == 3
+    # each hidden-to-hidden product carries the sum of the two pre-activations in its output stage
+    assert count(lambda n: isinstance(n.op, core.Mul22BiasAdd)) == 2 * T
     assert count(lambda n: isinstance(n.op, core.Mul22) and not n.op.tA and n.op.tB) == 2 * (T - 1) + 2   # h at t = 0 is a constant
     # one placement of the four gates' gradients per layer and time step (two, per slab shape, without split_gate_columns)
     assert count(lambda n: isinstance(n.op, core.ScatterCols)) == 2 * T

@@ -885,6 +885,40 @@ def test_row_selection_kernels(rt, R, C):
     assert np.array_equal(o_grad.get(), hot_np * g[:, None])
 
 
+@pytest.mark.parametrize("tA,tB,M,N,K", [(0, 0, 64, 512, 128), (0, 0, 8, 512, 65), (1, 0, 37, 130, 50), (1, 1, 64, 96, 31)])
+def test_sgemm_bias_add_has_the_bits_of_the_separate_kernels(rt, tA, tB, M, N, K):
+    """cgtb_sgemm_bias_add = (addend + addend_bias) + (A.B + bias) in the product's output stage, against cgtb_sgemm
+    followed by the three additions as separate kernels (the rows repeated by cgtb_repeat): identical bits. Products that
+    the dispatcher does not give to the FMA-tile kernel are refused."""
+    rs = np.random.RandomState(M + N + K)
+    A = rs.randn(*((K, M) if tA else (M, K))).astype("f4")
+    B = rs.randn(*((N, K) if tB else (K, N))).astype("f4")
+    bias, abias, addend = rs.randn(1, N).astype("f4"), rs.randn(1, N).astype("f4"), rs.randn(M, N).astype("f4")
+    dA, dB, dbias, dabias, dadd = Dev(A), Dev(B), Dev(bias), Dev(abias), Dev(addend)
+    lda, ldb = A.shape[1], B.shape[1]
+    prod, rep1, rep2, t1, t2, want = (Dev(shape=(M, N), dtype="f4") for _ in range(6))
+    call("cgtb_sgemm", tA, tB, M, N, K, dA.ptr, lda, dB.ptr, ldb, prod.ptr, N, 0)
+    call("cgtb_repeat", code("f4"), 2, longs((M, N)), ints([1, 0]), dbias.ptr, rep1.ptr)
+    call("cgtb_repeat", code("f4"), 2, longs((M, N)), ints([1, 0]), dabias.ptr, rep2.ptr)
+    call("cgtb_binary", 1, code("f4"), code("f4"), code("f4"), M * N, prod.ptr, rep1.ptr, t2.ptr, 0, 0)
+    call("cgtb_binary", 1, code("f4"), code("f4"), code("f4"), M * N, dadd.ptr, rep2.ptr, t1.ptr, 0, 0)
+    call("cgtb_binary", 1, code("f4"), code("f4"), code("f4"), M * N, t1.ptr, t2.ptr, want.ptr, 0, 0)
+    got = Dev(np.full((M, N), np.nan, "f4"))
+    k0 = runtime.kernel_launches()
+    call("cgtb_sgemm_bias_add", tA, tB, M, N, K, dA.ptr, lda, dB.ptr, ldb, dbias.ptr, dadd.ptr, N, dabias.ptr, got.ptr, N)
+    assert runtime.kernel_launches() - k0 == 1
+    assert np.array_equal(got.get(), want.get())
+    exact = (addend.astype("f8") + abias) + ((A.T if tA else A).astype("f8") @ (B.T if tB else B).astype("f8") + bias)
+    np.testing.assert_allclose(got.get(), exact, rtol=1e-4, atol=1e-4 * np.sqrt(K))
+    # without the optional operands it is the plain product
+    call("cgtb_sgemm_bias_add", tA, tB, M, N, K, dA.ptr, lda, dB.ptr, ldb, None, None, 0, None, got.ptr, N)
+    assert np.array_equal(got.get(), prod.get())
+    # A.B^T and few outputs belong to the warp-per-output kernel: refused here
+    L = runtime.lib()
+    assert L.cgtb_sgemm_bias_add(0, 1, 64, 128, 512, dA.ptr, 512, dB.ptr, 512, None, None, 0, None, got.ptr, 128) != 0
+    assert "FMA-tile" in runtime.last_error()
+
+
 def test_fused_rows_refuses_long_rows(rt):
     P = _RowProgram()
     P.n_in, P.n_ops, P.n_out = 1, 1, 1
