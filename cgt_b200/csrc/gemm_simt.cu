@@ -203,10 +203,11 @@ __global__ void __launch_bounds__(256) sgemm_small_nt4_kernel(long M, long N, lo
   for (int i = 0; i < 4; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-  for (long k0 = l; k0 < K; k0 += 64) {
-    float av[2][4], bv[2][4];
+  constexpr int U = 8;   // 64 loads per lane in flight: the kernel is bound by the latency of its load rounds
+  for (long k0 = l; k0 < K; k0 += 32 * U) {
+    float av[U][4], bv[U][4];
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
+    for (int u = 0; u < U; ++u) {
       const long k = k0 + 32 * u;
       const bool ok = k < K;
 #pragma unroll
@@ -216,7 +217,7 @@ __global__ void __launch_bounds__(256) sgemm_small_nt4_kernel(long M, long N, lo
       }
     }
 #pragma unroll
-    for (int u = 0; u < 2; ++u)
+    for (int u = 0; u < U; ++u)
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
