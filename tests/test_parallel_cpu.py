@@ -74,3 +74,5 @@ def test_single_rank_is_the_identity():
     g = [x * 2.0]
     assert parallel.allreduce_mean(g) == g
     assert [a.tolist() for a in parallel.shard([np.arange(8).reshape(4, 2)], 1, 2)] == [[[4, 5], [6, 7]]]
+    # without a communicator there is nothing to line up with: the device-side barrier queues nothing
+    assert parallel.device_barrier() is False
