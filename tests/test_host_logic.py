@@ -259,6 +259,44 @@ def test_odd_column_rows_are_padded_for_both_products():
     assert [n for n in core.topsorted(o2 + u2) if not n.is_input() and isinstance(n.op, im2col_ops.ConvWgrad)] == wg
 
 
+def test_convnet_graph_rewrites():
+    """The rewrites aimed at the CIFAR-shape convnet, on its batch-16 graph (no GPU needed: only the rewritten graph is
+    inspected). No column matrix is left: the 3-channel first layer is computed directly (ConvDirectFwd, and
+    ConvDirectWgradRelu, which absorbs that layer's relu and bias gradients), conv2 / conv3 are implicit convolutions
+    whose filter banks are split by one SplitFilterBanks node with four jobs; the softmax loss with the label selection
+    and its pullback is one FusedRows node; every switch turns its rewrite off."""
+    from cgt_b200.nn_ops import im2col as im2col_ops
+    cfg = configs.build_cifar(batch=16)
+
+    def rewritten(**flags):
+        with cgt.scoped_update_config(**flags):
+            sim = compilation.simplify_for_execution([cfg.loss] + list(cfg.extra_outputs), cfg.updates)
+            o, u = compilation.apply_graph_rewrites(sim[0], sim[2], sim[3]["node2shape"])
+        return [n for n in core.topsorted(o + u) if not n.is_input()]     # topsorted raises on a cycle
+
+    nodes = rewritten()
+    count = lambda ns, cls: sum(1 for n in ns if isinstance(n.op, cls))
+    assert count(nodes, im2col_ops.Im2Col) == 0 and count(nodes, im2col_ops.Col2Im) == 0
+    assert count(nodes, im2col_ops.ConvDirectFwd) == 1 and count(nodes, im2col_ops.ConvDirectWgradRelu) == 1
+    assert count(nodes, im2col_ops.ConvFwdBiasRelu) == 2 and count(nodes, im2col_ops.ConvDgrad) == 2
+    assert count(nodes, im2col_ops.ConvWgradImplicit) == 2 and count(nodes, im2col_ops.ReluGradNHWC) == 2
+    splits = [n for n in nodes if isinstance(n.op, im2col_ops.SplitFilterBanks)]
+    assert len(splits) == 1 and len(splits[0].op.jobs) == 4 and len(splits[0].parents) == 2
+    assert sorted(job[4] for job in splits[0].op.jobs) == [1, 1, 2, 2]       # two forward products, two data gradients
+    assert all(n.op.pre and len(n.parents) == (8 if isinstance(n.op, im2col_ops.ConvFwdBiasRelu) else 7)
+               for n in nodes if isinstance(n.op, (im2col_ops.ConvFwdBiasRelu, im2col_ops.ConvDgrad)))
+    rows = [n for n in nodes if isinstance(n.op, core.FusedRows)]
+    assert len(rows) == 1 and 8 in rows[0].op.in_kinds
+    assert count(nodes, core.GetFlatIndices) == 0 and count(nodes, core.IncFlatIndices) == 0
+    # the switches
+    off = rewritten(fuse_conv_direct=False)
+    assert count(off, im2col_ops.Im2Col) == 1 and count(off, im2col_ops.ConvDirectFwd) == 0 and count(off, im2col_ops.ReluGradNHWC) == 3
+    off = rewritten(hoist_filter_splits=False)
+    assert count(off, im2col_ops.SplitFilterBanks) == 0 and not any(n.op.pre for n in off if isinstance(n.op, im2col_ops.ConvDgrad))
+    off = rewritten(fuse_flat_index_rows=False)
+    assert count(off, core.GetFlatIndices) == 1 and count(off, core.IncFlatIndices) == 1
+
+
 def test_flat_index_rows_rewrite():
     """logprobs[arange(batch), y] and its gradient on the MLP configuration (no GPU needed: only the rewritten graph is
     inspected, and the new Ops' host implementations are evaluated with numpy): GetFlatIndices / IncFlatIndices / the
