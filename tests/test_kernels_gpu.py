@@ -245,7 +245,7 @@ def test_reduce(rt, shape, axes, kind, dtype):
     if kind == "max" or dtype == "i8":
         assert np.array_equal(got, want)
     else:
-        # a parallel sum cannot follow the sequential fp32 order; both are judged against float64
+        # a parallel sum cannot follow the sequential fp32 order; both are compared with float64
         exact = x.astype("f8").sum(axis=tuple(axes), keepdims=True)
         n = x.size / max(want.size, 1)
         tol = 1e-4 * np.abs(exact) + 1e-5 * max(1.0, np.sqrt(n))
